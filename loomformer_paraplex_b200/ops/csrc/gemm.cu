@@ -1,0 +1,329 @@
+// Segmented-K, optionally batched bf16 GEMM on the 5th-generation tensor cores.
+//
+//   C[m, g, n] (+)= sum_seg sum_k A_seg[m, g?, k] * B[n, g?, b_k0(seg) + k]   (+ bias[g, n])
+//
+// * operands are staged by TMA (128-byte swizzle) into a multi-stage shared-memory ring,
+// * one elected thread issues tcgen05.mma (M=128, N=BN, K=16) with the fp32 accumulator in TMEM,
+// * four epilogue warps read the accumulator back with tcgen05.ld and store bf16 or fp32,
+// * the kernel is persistent (one CTA per SM loops over tiles) and double-buffers the TMEM
+//   accumulator so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// "Segmented K": the reduction dimension may be the concatenation of up to MAX_SEG different
+// tensors (e.g. the Paraplex phase input [Q_g | Kctx_g | C_g | u | D_g]); each segment has its own
+// tensor map whose extent bounds the segment, so ragged tails are zero-filled by the TMA unit.
+// "Batched": every operand is a [rows, heads, cols] view; a batched operand indexes `heads` with the
+// tile's group id, an unbatched one uses group 0.  Either operand may be K-major (reduction index
+// contiguous) or MN-major (the other index contiguous), which covers forward, data-gradient and
+// weight-gradient GEMMs without materialising transposes.
+//
+// This kernel replaces the library GEMMs of the reference (F.linear / cublasGemmStridedBatchedEx,
+// reference kernels/beta_space/beta_space_launcher.cu:57-151) and its operand pack/unpack kernels
+// (beta_space_kernel.cuh:86-271): nothing is gathered or scattered through global memory.
+#include "sm100.cuh"
+#include "tma_host.h"
+#include "loom_c_api.h"
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;          // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int MAX_SEG = 4;
+constexpr int NUM_THREADS = 192;  // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
+
+struct Seg {
+  CUtensorMap a;
+  int k_len;      // reduction length of this segment
+  int a_k0;       // offset of the segment along A's reduction index
+  int b_k0;       // offset of the segment along B's reduction index
+  int a_batched;
+};
+
+struct Params {
+  CUtensorMap b;
+  Seg seg[MAX_SEG];
+  int nseg;
+  int b_batched;
+  void* c;
+  long long ldc;        // row pitch of C (elements)
+  long long ldc_head;   // group pitch of C (elements)
+  const float* bias;    // [heads * n_per_head] or nullptr
+  int M, n_per_head, heads;
+  int accumulate;       // C += result (read-modify-write in the epilogue)
+  int out_fp32;
+  int a_lbo, a_sbo, b_lbo, b_sbo;
+  int* status;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN >= 256) ? 4 : ((BN >= 128) ? 6 : 8);
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : 2 * BN;
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_kernel(const __grid_constant__ Params p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* empty = full + C::STAGES;
+  uint64_t* acc_full = empty + C::STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  volatile int* status = p.status;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 128); }
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.n_per_head + BN - 1) / BN;
+  const int total = tiles_m * tiles_n * p.heads;
+  int kblocks = 0;
+  for (int s = 0; s < p.nseg; ++s) kblocks += (p.seg[s].k_len + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&p.b);
+      for (int s = 0; s < p.nseg; ++s) tma_prefetch_desc(&p.seg[s].a);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+        const int tm = tile % tiles_m;
+        const int tn = (tile / tiles_m) % tiles_n;
+        const int g = tile / (tiles_m * tiles_n);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int s = 0; s < p.nseg && ok; ++s) {
+          const Seg& sg = p.seg[s];
+          const int ag = sg.a_batched ? g : 0;
+          const int bg = p.b_batched ? g : 0;
+          for (int k = 0; k < sg.k_len; k += BK, ++it) {
+            const int st = it % C::STAGES;
+            const uint32_t ph = (it / C::STAGES) & 1;
+            if (!mbar_wait(&empty[st], ph ^ 1, status, 101)) { ok = false; break; }
+            uint8_t* sa = smem + st * C::STAGE_BYTES;
+            uint8_t* sb = sa + C::A_BYTES;
+            mbar_expect_tx(&full[st], C::STAGE_BYTES);
+            if (A_MN) {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j)
+                tma_load_3d(sa + j * 8192, &sg.a, &full[st], m0 + 64 * j, sg.a_k0 + k, ag);
+            } else {
+              tma_load_3d(sa, &sg.a, &full[st], sg.a_k0 + k, m0, ag);
+            }
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_3d(sb + j * 8192, &p.b, &full[st], n0 + 64 * j, sg.b_k0 + k, bg);
+            } else {
+              tma_load_3d(sb, &p.b, &full[st], sg.b_k0 + k, n0, bg);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++tcount) {
+        const uint32_t acc = tcount & 1;
+        if (!mbar_wait(&acc_empty[acc], ((tcount >> 1) & 1) ^ 1, status, 102)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int st = it % C::STAGES;
+          if (!mbar_wait(&full[st], (it / C::STAGES) & 1, status, 103)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + st * C::STAGE_BYTES);
+          const uint32_t sb = sa + C::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint32_t a_off = A_MN ? k * (UMMA_K * 128) : k * (UMMA_K * 2);
+            const uint32_t b_off = B_MN ? k * (UMMA_K * 128) : k * (UMMA_K * 2);
+            const uint64_t da = make_smem_desc_sw128(sa + a_off, p.a_lbo, p.a_sbo);
+            const uint64_t db = make_smem_desc_sw128(sb + b_off, p.b_lbo, p.b_sbo);
+            mma_bf16_ss(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          mma_commit(&empty[st]);       // frees the smem stage when these MMAs retire
+        }
+        if (ok) mma_commit(&acc_full[acc]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5)
+    const int q = warp & 3;             // TMEM lane quadrant this warp may access
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++tcount) {
+      const int tm = tile % tiles_m;
+      const int tn = (tile / tiles_m) % tiles_n;
+      const int g = tile / (tiles_m * tiles_n);
+      const uint32_t acc = tcount & 1;
+      if (!mbar_wait(&acc_full[acc], (tcount >> 1) & 1, status, 104)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tm * BM + q * 32 + lane;
+      const int n0 = tn * BN;
+      const uint32_t taddr = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
+      const long long c_row = (long long)row * p.ldc + (long long)g * p.ldc_head;
+      const float* bias = p.bias ? p.bias + (long long)g * p.n_per_head : nullptr;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c0, r);
+        tmem_ld_wait();
+        const int n = n0 + c0;
+        if (row < p.M && n < p.n_per_head) {
+          const int nvalid = min(32, p.n_per_head - n);
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if (bias) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (i < nvalid) v[i] += bias[n + i];
+          }
+          if (p.out_fp32) {
+            float* dst = reinterpret_cast<float*>(p.c) + c_row + n;
+            if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                if (p.accumulate) { float4 old = *reinterpret_cast<float4*>(dst + i); o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
+                *reinterpret_cast<float4*>(dst + i) = o;
+              }
+            } else {
+              for (int i = 0; i < nvalid; ++i) dst[i] = p.accumulate ? dst[i] + v[i] : v[i];
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + c_row + n;
+            if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                if (p.accumulate) {
+                  uint4 old = *reinterpret_cast<uint4*>(dst + i);
+                  const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(ob[j]); v[i + 2 * j] += f.x; v[i + 2 * j + 1] += f.y; }
+                }
+                uint4 o;
+                __nv_bfloat162* ob2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) ob2[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
+                *reinterpret_cast<uint4*>(dst + i) = o;
+              }
+            } else {
+              for (int i = 0; i < nvalid; ++i) {
+                float x = v[i];
+                if (p.accumulate) x += __bfloat162float(dst[i]);
+                dst[i] = __float2bfloat16(x);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+bool fill_map(CUtensorMap* map, const LoomOperand& o, bool mn_major, int box_mn) {
+  // view [rows, heads, cols]: dims (cols, rows, heads)
+  tma_host::EncodeTiledFn fn = tma_host::encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)o.cols, (cuuint64_t)o.rows, (cuuint64_t)(o.heads > 0 ? o.heads : 1)};
+  cuuint64_t strides[2] = {(cuuint64_t)o.ld_row * 2, (cuuint64_t)(o.heads > 1 ? o.ld_head : o.ld_row * o.rows) * 2};
+  if (o.heads <= 1) strides[1] = (cuuint64_t)o.ld_row * 2 * (cuuint64_t)o.rows;
+  cuuint32_t box[3];
+  box[0] = 64;
+  box[1] = mn_major ? 64u : (cuuint32_t)box_mn;
+  box[2] = 1;
+  cuuint32_t elem[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(o.ptr), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+int launch(const Params& p, int sms, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.n_per_head + BN - 1) / BN) * p.heads;
+  const int grid = tiles < sms ? tiles : sms;
+  gemm_kernel<BN, A_MN, B_MN><<<grid, NUM_THREADS, C::SMEM, stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
+template <int BN>
+int dispatch_major(const Params& p, bool a_mn, bool b_mn, int sms, cudaStream_t stream) {
+  if (a_mn) return b_mn ? launch<BN, true, true>(p, sms, stream) : launch<BN, true, false>(p, sms, stream);
+  return b_mn ? launch<BN, false, true>(p, sms, stream) : launch<BN, false, false>(p, sms, stream);
+}
+
+}  // namespace
+
+extern "C" int loom_gemm_bf16(const LoomGemm* g, cudaStream_t stream) {
+  if (g->nseg < 1 || g->nseg > MAX_SEG) return -1;
+  if (g->bn != 64 && g->bn != 128 && g->bn != 256) return -2;
+  Params p;
+  memset(&p, 0, sizeof(p));
+  const bool a_mn = g->a_mn_major != 0, b_mn = g->b_mn_major != 0;
+  if (!fill_map(&p.b, g->b, b_mn, g->bn)) return -3;
+  for (int s = 0; s < g->nseg; ++s) {
+    if (!fill_map(&p.seg[s].a, g->a[s], a_mn, BM)) return -4;
+    p.seg[s].k_len = g->k_len[s];
+    p.seg[s].a_k0 = g->a_k0[s];
+    p.seg[s].b_k0 = g->b_k0[s];
+    p.seg[s].a_batched = g->a[s].heads > 1 ? 1 : 0;
+  }
+  p.nseg = g->nseg;
+  p.b_batched = g->b.heads > 1 ? 1 : 0;
+  p.c = g->c; p.ldc = g->ldc; p.ldc_head = g->ldc_head; p.bias = g->bias;
+  p.M = g->M; p.n_per_head = g->N; p.heads = g->heads > 0 ? g->heads : 1;
+  p.accumulate = g->accumulate; p.out_fp32 = g->out_fp32; p.status = g->status;
+  // K-major: 8-row groups are 1024 B apart (SBO); LBO unused.  MN-major: 64-element blocks along MN are
+  // 8192 B apart (LBO), 8-row groups along K are 1024 B apart (SBO).
+  p.a_lbo = a_mn ? 8192 : 0; p.a_sbo = 1024;
+  p.b_lbo = b_mn ? 8192 : 0; p.b_sbo = 1024;
+  if (g->swap_mn_strides) {
+    if (a_mn) { p.a_lbo = 1024; p.a_sbo = 8192; }
+    if (b_mn) { p.b_lbo = 1024; p.b_sbo = 8192; }
+  }
+  static int sms = 0;
+  if (sms == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+  switch (g->bn) {
+    case 64: return dispatch_major<64>(p, a_mn, b_mn, sms, stream);
+    case 128: return dispatch_major<128>(p, a_mn, b_mn, sms, stream);
+    default: return dispatch_major<256>(p, a_mn, b_mn, sms, stream);
+  }
+}

@@ -1,0 +1,70 @@
+"""Data-parallel gradient synchronisation over the flat gradient buffer.
+
+Back ends
+---------
+``collective``  ``torch.distributed.all_reduce`` (NCCL on GPUs, gloo on CPU) over one contiguous
+                fp32 range -- the measured baseline.
+``p2p``         the fused sm_100a kernel (``ops/csrc/comm.cu``): every rank reduces its shard by
+                reading the peers' gradient buffers over NVLink, applies clip + AdamW/ATOM to the
+                shard in the same pass, and writes the refreshed fp32/bf16 parameters into every
+                peer's buffers -- reduce-scatter, optimizer and all-gather in one launch.
+
+The reference wraps its model in ``torch.nn.parallel.DistributedDataParallel`` with 64 MiB
+buckets (``loomformer.py:4783-4792``) and re-broadcasts every module buffer from rank 0 before
+each forward; here buffers that matter (the per-layer phase anchors) are synchronised
+explicitly and only they.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import dist as pdist
+
+
+class GradSync:
+    def __init__(self, flat, model, backend: str = "collective", anchor_mode: str = "mean") -> None:
+        self.flat, self.model = flat, model
+        self.world = dist.get_world_size() if pdist.initialized() else 1
+        self.backend = backend if self.world > 1 else "none"
+        self.anchor_mode = anchor_mode
+        self._anchors: Optional[List[torch.Tensor]] = None
+        if self.world > 1:
+            self.broadcast_parameters()
+
+    def broadcast_parameters(self) -> None:
+        """Every rank starts from rank 0's weights and buffers (what DDP does at construction)."""
+        dist.broadcast(self.flat.params, src=0)
+        self.flat.refresh_shadow()
+        for b in self.model.buffers():
+            if b.is_floating_point() and b.numel() == 1:
+                dist.broadcast(b, src=0)
+
+    def all_reduce_grads(self) -> None:
+        if self.backend == "none":
+            return
+        g = self.flat.grads
+        dist.all_reduce(g)
+        g.mul_(1.0 / self.world)
+
+    def sync_anchors(self) -> None:
+        """Keep each layer's phase-anchor EMA identical on all ranks.
+
+        ``mean``: average of the ranks' updated anchors (every rank's data contributes);
+        ``rank0``: rank 0's value wins, which is what the reference's per-forward buffer
+        broadcast amounts to (use it to match a reference loss curve).
+        """
+        if self.world <= 1:
+            return
+        if self._anchors is None:
+            self._anchors = [b.ffn.beta_anchor for b in self.model.blocks]
+        packed = torch.stack([a.detach().float() for a in self._anchors])
+        if self.anchor_mode == "rank0":
+            dist.broadcast(packed, src=0)
+        else:
+            dist.all_reduce(packed)
+            packed.mul_(1.0 / self.world)
+        for a, v in zip(self._anchors, packed.unbind(0)):
+            a.copy_(v)

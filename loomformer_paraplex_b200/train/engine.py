@@ -1,0 +1,124 @@
+"""Training engine: the public "one optimizer step" API.
+
+``TrainEngine.step(batch)`` takes a ``[B, T+1]`` token batch (host pinned memory or device),
+copies it to the device, runs forward + fp32 cross-entropy + backward for each micro-batch,
+synchronises gradients across ranks, clips by global norm, applies the optimizer and returns the
+mean loss as a device scalar.  Nothing inside synchronises with the host; callers decide when
+to read the loss.
+
+It replaces the body of the reference's training loop (``loomformer.py:5064-5170``): seeds, LR
+schedule, parameter groups by ``(weight_decay, lr_mult)``, gradient accumulation with the
+collective skipped on non-final micro-batches, fp32 CE, global-norm clip and the non-finite
+guards (one fused finite flag instead of a host sync per parameter).
+"""
+from __future__ import annotations
+
+import contextlib
+import math
+import re
+from typing import Dict, Optional
+
+import torch
+import torch.nn.functional as F
+
+from ..config import Config
+from ..optim.flat import FlatOptimizer, FlatParams
+from ..parallel import dist as pdist
+from ..parallel.ddp import GradSync
+from .schedule import lr_at
+
+
+def train_lr_overrides(model, cfg: Config) -> Dict[str, float]:
+    """Apply ``cfg.train_lr`` (freeze flags + absolute per-tensor learning rates, matched by name with
+    the ``blocks.N.`` prefix stripped; first match wins) and return ``{param_name: lr_mult}``."""
+    entries = cfg.train_lr or []
+    out: Dict[str, float] = {}
+    if not entries:
+        return out
+    strip = re.compile(r"^blocks\.\d+\.")
+    matched = 0
+    for name, p in model.named_parameters():
+        canon = strip.sub("", name)
+        for e in entries:
+            if e.get("name") == canon:
+                p.requires_grad_(bool(e.get("train", True)))
+                if "lr" in e:
+                    out[name] = float(e["lr"]) / float(cfg.lr)
+                matched += 1
+                break
+    total = sum(1 for _ in model.parameters())
+    pdist.rank0_print(f"[loomcloner] train_lr: {matched}/{total} parameters matched an override "
+                      f"({len(entries)} entries, {sum(1 for e in entries if not e.get('train', True))} frozen)")
+    return out
+
+
+class TrainEngine:
+    def __init__(self, cfg: Config, model, device: torch.device, *, optimizer: Optional[str] = None,
+                 grad_sync: str = "collective", anchor_mode: str = "mean", loss_mask_ignore: int = -100) -> None:
+        self.cfg, self.model, self.device = cfg, model, device
+        self.accum = max(1, int(cfg.grad_accum_steps or 1))
+        self.amp = cfg.amp_dtype if device.type == "cuda" else "fp32"
+        lr_mults = train_lr_overrides(model, cfg)
+        self.flat = FlatParams(model, want_bf16_shadow=(device.type == "cuda"))
+        no_decay = {"tria_agg.pool.logit_scale_raw"}
+        self.opt_name = str(optimizer or cfg.optimizer or "adamw").lower()
+        self.opt = FlatOptimizer(self.flat, self.opt_name, lr=cfg.lr, weight_decay=cfg.weight_decay,
+                                 grad_clip=cfg.grad_clip, no_decay=no_decay, lr_mults=lr_mults)
+        self.sync = GradSync(self.flat, model, backend=grad_sync, anchor_mode=anchor_mode)
+        self.step_idx = 0           # completed optimizer steps
+        self.ignore_index = loss_mask_ignore
+        self.last_fire_count = torch.zeros((), dtype=torch.long, device=device)
+
+    # ------------------------------------------------------------------ pieces
+    def _autocast(self):
+        if self.device.type != "cuda" or self.amp in ("fp32", "off"):
+            return contextlib.nullcontext()
+        return torch.autocast("cuda", dtype=torch.bfloat16 if self.amp == "bf16" else torch.float16)
+
+    def loss_fn(self, x, y, attn_mask=None, position_ids=None) -> torch.Tensor:
+        ops = self.model._opset(self.model.emb.weight)
+        if ops is not None and hasattr(ops, "loss"):
+            return ops.loss(self.model, x, y, attn_mask, position_ids, self.ignore_index)
+        with self._autocast():
+            logits = self.model(x, attn_mask=attn_mask, position_ids=position_ids)
+        return F.cross_entropy(logits.float().reshape(-1, logits.shape[-1]), y.reshape(-1),
+                               ignore_index=self.ignore_index)
+
+    def to_device(self, batch: torch.Tensor) -> torch.Tensor:
+        return batch.to(self.device, non_blocking=True) if batch.device != self.device else batch
+
+    # ------------------------------------------------------------------ one optimizer step
+    def step(self, batch, targets: Optional[torch.Tensor] = None, attn_mask=None, position_ids=None) -> torch.Tensor:
+        """``batch`` is ``[B, T+1]`` tokens (inputs ``[:, :-1]``, targets ``[:, 1:]``) or, with explicit
+        ``targets``, ``[B, T]`` inputs.  With ``grad_accum_steps > 1`` pass a list of micro-batches."""
+        micro = batch if isinstance(batch, (list, tuple)) else [batch]
+        self.model.train()
+        self.flat.zero_grad()
+        total = None
+        for mb in micro:
+            mb = self.to_device(mb)
+            if targets is None:
+                x, y = mb[:, :-1], mb[:, 1:]
+            else:
+                x, y = mb, self.to_device(targets)
+            loss = self.loss_fn(x, y, attn_mask, position_ids)
+            (loss / float(len(micro))).backward()
+            fm = self.model.last_tria_fire_mask
+            if fm is not None:
+                self.last_fire_count += fm.sum()
+            total = loss.detach() if total is None else total + loss.detach()
+        self.sync.all_reduce_grads()
+        self.opt.set_lr(lr_at(self.cfg, self.step_idx))
+        self.opt.step()
+        self.sync.sync_anchors()
+        self.step_idx += 1
+        return total / float(len(micro))
+
+    def check_finite(self, loss: torch.Tensor) -> None:
+        """Host-side guard (one sync): raise if the loss or the last gradient norm was not finite."""
+        lv = float(loss)
+        if not math.isfinite(lv):
+            raise RuntimeError(f"non-finite training loss: loss={lv:.9g} optimizer={self.opt_name} step={self.step_idx}")
+        if not self.opt.grads_finite():
+            raise RuntimeError("non-finite gradient detected before optimizer step: "
+                               f"optimizer={self.opt_name} step={self.step_idx} (update was skipped on device)")
