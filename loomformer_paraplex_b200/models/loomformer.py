@@ -302,8 +302,8 @@ class Model(nn.Module):
         else:
             position_ids = position_ids.to(device=idx.device, dtype=torch.long)
         ops = self._opset(self.emb.weight)
-        if ops is not None:
-            return ops.forward(self, idx, attn_mask, position_ids)
+        if ops is not None and attn_mask is None and not torch.is_grad_enabled() and not self.ablation:
+            return ops.run(idx, None, position_ids, None, want_grad=False)[1].float()
         if self.d.tria and self.d.tria_temporal and not self.ablation:
             return self._forward_chunked(idx, attn_mask, position_ids)
         return self._forward_flat(idx, attn_mask, position_ids)

@@ -30,7 +30,7 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;          // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int MAX_SEG = 4;
+constexpr int MAX_SEG = 5;
 constexpr int NUM_THREADS = 192;  // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
 
 struct Seg {

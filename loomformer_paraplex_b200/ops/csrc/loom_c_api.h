@@ -19,8 +19,8 @@ typedef struct {
 // C[m, g, n] (+)= sum_s A_s[m, g, :k_len[s]] . B[n, g, b_k0[s] : b_k0[s]+k_len[s]]  (+ bias)
 // K-major operand: reduction index = cols.  MN-major operand: reduction index = rows.
 typedef struct {
-  LoomOperand a[4];
-  int k_len[4], a_k0[4], b_k0[4];
+  LoomOperand a[5];
+  int k_len[5], a_k0[5], b_k0[5];
   int nseg;
   LoomOperand b;
   int a_mn_major, b_mn_major;
@@ -35,6 +35,17 @@ typedef struct {
 } LoomGemm;
 
 int loom_gemm_bf16(const LoomGemm* g, cudaStream_t stream);
+
+// ---- flat optimizer (optim.cu) ----
+int loom_grad_norm(const float* grads, long long n, float max_norm, float* partial, int nparts, float* stats,
+                   float* atom_out, cudaStream_t stream);
+int loom_adamw_flat(float* p, const float* g, float* m, float* v, void* shadow_bf16, const float* lr_mult,
+                    const float* wd_blk, const float* active, const float* stats, const float* hyper,
+                    long long nblk, cudaStream_t stream);
+int loom_atom_flat(float* p, const float* g, float* m, float* v, void* shadow_bf16, const float* lr_mult,
+                   const float* wd_blk, const float* cnt_blk, float* gprev, float* pnode, float* trust,
+                   const float* stats, const float* hyper, float* atom_out, long long nblk, cudaStream_t stream);
+int loom_cast_shadow(const float* p, void* shadow_bf16, long long n, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,505 @@
+"""Fused execution plan: hand-written forward and backward over whole temporal chunks.
+
+The composed plan (``models/loomformer.py``) leaves differentiation to autograd, one node per
+PyTorch op.  Here the whole training step is a fixed sequence of fat kernels:
+
+* forward of a chunk = L x { QKV GEMM, RoPE + cache write, dual-context attention, out-proj GEMM,
+  depth read, readout GEMM, add+LayerNorm, depth K/V GEMM, depth read, readout GEMM, up-projection
+  GEMMs (real / gate / segmented imaginary), fused Paraplex core + Tria step, down GEMM, add+LayerNorm,
+  depth K/V GEMM } followed by the temporal endpoint (+PolARM);
+* backward walks the chunks in reverse and the layers of each chunk in reverse, accumulating weight
+  gradients straight into the flat fp32 gradient buffer, key/value gradients into per-layer fp32
+  cache-gradient buffers and depth-history gradients into one history-gradient buffer.
+
+Nothing in the sequence depends on host-side values (no ``.item()``), so a whole optimizer step can
+be captured in one CUDA graph.  The kernels come from a *kernel set*: ``CudaKernels`` (sm_100a) on a
+B200, ``TorchKernels`` (``ops/twins.py``) elsewhere, which lets this file be verified on a CPU
+against autograd of the composed plan.
+
+Structure of the reference being replaced: ``loomformer.py:3544-3635`` (block), ``3686-3766`` (chunk
+stack), ``3788-3893`` (chunked forward); its per-op ``autograd.Function`` wrappers and the Tria
+replay tape (``tria.py:279-709``) have no counterpart because carriers are stored, not replayed.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..config import FANIN_GAIN
+from .twins import TorchKernels
+
+
+def make_kernels(device: torch.device):
+    if device.type == "cuda":
+        from .kernels import CudaKernels
+        return CudaKernels()
+    return TorchKernels()
+
+
+class FusedPlan:
+    def __init__(self, model, kernels=None, flat=None, compute_dtype: Optional[torch.dtype] = None) -> None:
+        self.model, self.d = model, model.d
+        dev = model.emb.weight.device
+        self.K = kernels if kernels is not None else make_kernels(dev)
+        self.flat = flat
+        self.adt = compute_dtype or (torch.bfloat16 if dev.type == "cuda" else torch.float32)
+        self._wcache: Dict[int, torch.Tensor] = {}
+        self.anchor_sync = None        # optional callable(sumsq [L], count) for cross-rank anchor statistics
+
+    # ------------------------------------------------------------------ parameter access
+    def bind(self, flat) -> None:
+        self.flat = flat
+        self._wcache.clear()
+
+    def w(self, p: torch.Tensor) -> torch.Tensor:
+        """Weight in the compute dtype (bf16 shadow on a GPU, the fp32 parameter itself on a CPU)."""
+        if self.adt == torch.float32:
+            return p.data
+        if self.flat is not None and self.flat.shadow is not None:
+            key = id(p)
+            v = self._wcache.get(key)
+            if v is None:
+                v = self.flat.shadow_of(p)
+                self._wcache[key] = v
+            return v
+        return p.data.to(self.adt)
+
+    @staticmethod
+    def g(p: torch.Tensor) -> torch.Tensor:
+        if p.grad is None:
+            p.grad = torch.zeros_like(p.data, dtype=torch.float32)
+        return p.grad
+
+    # ------------------------------------------------------------------ public entry points
+    def forward(self, model, idx, attn_mask, position_ids):
+        if attn_mask is not None or torch.is_grad_enabled():
+            # arbitrary masks and autograd-through-logits go through the composed plan
+            if model.d.tria and model.d.tria_temporal and not model.ablation:
+                return model._forward_chunked(idx, attn_mask, position_ids)
+            return model._forward_flat(idx, attn_mask, position_ids)
+        return self.run(idx, None, position_ids, None, want_grad=False)[1]
+
+    def loss(self, model, x, y, attn_mask, position_ids, ignore_index, segment_ids=None):
+        if attn_mask is not None or model.ablation:
+            raise NotImplementedError("the fused plan takes segment_ids, not dense masks")
+        return _FusedLoss.apply(self, x, y, position_ids, segment_ids, ignore_index, self._hook())
+
+    def _hook(self) -> torch.Tensor:
+        # a differentiable dummy so autograd calls _FusedLoss.backward
+        return torch.zeros((), device=self.model.emb.weight.device, requires_grad=True)
+
+    # ------------------------------------------------------------------ the step
+    def run(self, idx, y, position_ids, seg, want_grad: bool, ignore_index: int = -100, grad_scale: float = 1.0):
+        """Forward (and, with ``want_grad``, backward into ``param.grad``).  Returns (loss, logits)."""
+        m, d, K = self.model, self.d, self.K
+        B, T = idx.shape
+        dev = idx.device
+        if position_ids is None:
+            position_ids = torch.arange(T, device=dev).view(1, T).expand(B, T)
+        chunked = d.tria and d.tria_temporal and not m.ablation
+        if chunked:
+            reset, fire, cuts = m.fire_plan(idx, position_ids)
+        else:
+            reset, fire, cuts = m._doc_reset(position_ids), None, []
+        cut_set = set(cuts)
+        stops = cuts + ([T - 1] if not cuts or cuts[-1] != T - 1 else [])
+        training = m.training and want_grad
+        emb_w = self.w(m.emb.weight)
+        h_emb = emb_w[idx]                                              # [B,T,N]
+        cos_all, sin_all = m.rope_cos[position_ids], m.rope_sin[position_ids]     # [B,T,HD] fp32
+        tok_reset = position_ids.eq(0)
+        L = d.layers
+        kc = [torch.zeros(B, T, d.kvh, d.hd, dtype=self.adt, device=dev) for _ in range(L)]
+        vc = [torch.zeros(B, T, d.kvh, d.hd, dtype=self.adt, device=dev) for _ in range(L)]
+        traces: Optional[List[torch.Tensor]] = None
+        temporal = None
+        tapes, h_parts, keys, key_valid, key_pos = [], [], [], [], []
+        s = 0
+        for bp in stops:
+            e = min(bp + 1, T)
+            if e <= s:
+                continue
+            seed, seed_valid = None, None
+            if chunked and temporal is not None:
+                seed, seed_valid = temporal, fire[:, s - 1] & ~reset[:, s]
+            tape = self._chunk_forward(h_emb[:, s:e], cos_all[:, s:e], sin_all[:, s:e], tok_reset[:, s:e], seg,
+                                       s, e, kc, vc, traces, seed, seed_valid, training, want_grad)
+            traces = tape["trace_out"]
+            tape.update(s=s, e=e, seed=seed, seed_valid=seed_valid, temporal_in=temporal, fired=None,
+                        has_endpoint=False, key_index=None)
+            if chunked:
+                local_reset = reset[:, s:e].clone()
+                if seed_valid is not None:
+                    local_reset[:, 0] |= seed_valid
+                tape["local_reset"] = local_reset
+                if e != T or (e - 1) in cut_set:
+                    fired = fire[:, e - 1] if (e - 1) in cut_set else None
+                    temporal = K.temporal_fwd(tape["depth"].view(B, e - s, d.hidden, 9), local_reset, temporal,
+                                              fired, m.d_polarm_beta)
+                    tape["has_endpoint"], tape["fired"] = True, fired
+                    if fired is not None:
+                        tape["key_index"] = len(keys)
+                        keys.append(temporal); key_valid.append(fired); key_pos.append(e - 1)
+            h_parts.append(tape["h_out"].view(B, e - s, d.n))
+            if not want_grad:
+                tape = {"s": s, "e": e}
+            tapes.append(tape)
+            s = e
+        h = torch.cat(h_parts, dim=1) if len(h_parts) > 1 else h_parts[0]
+        m.last_tria_fire_mask = fire
+        # ---- sparse readout of the boundary keys
+        ro = None
+        if keys:
+            ro = self._readout_forward(h, torch.stack(keys, 1), torch.stack(key_valid, 1),
+                                       torch.tensor(key_pos, device=dev), seg)
+            h = ro["h_out"]
+        hn = K.rms_norm_fwd(h, m.ln_final.weight) if m.ln_final is not None else h
+        logits = K.linear(hn.reshape(B * T, d.n), self.w(m.head.weight)).view(B, T, d.vocab)
+        if y is None:
+            return None, logits
+        loss, dlogits = K.ce_fwd_bwd(logits.view(B * T, d.vocab), y.reshape(-1), ignore_index,
+                                     grad_scale if want_grad else None)
+        if not want_grad:
+            return loss, logits
+        # =============================================================== backward
+        hn2 = hn.reshape(B * T, d.n)
+        K.linear_wgrad(dlogits, hn2, self.g(m.head.weight))
+        dh = K.linear_dgrad(dlogits, self.w(m.head.weight)).view(B, T, d.n)
+        del dlogits, logits
+        if m.ln_final is not None:
+            dh = K.rms_norm_bwd(dh, h, m.ln_final.weight, self.g(m.ln_final.weight))
+        dkeys = None
+        if ro is not None:
+            dh, dkeys = self._readout_backward(ro, dh)
+        dkc = [torch.zeros(B, T, d.kvh, d.hd, dtype=torch.float32, device=dev) for _ in range(L)]
+        dvc = [torch.zeros(B, T, d.kvh, d.hd, dtype=torch.float32, device=dev) for _ in range(L)]
+        d_emb = torch.empty(B, T, d.n, dtype=self.adt, device=dev)
+        dtraces: Optional[List[Optional[torch.Tensor]]] = None
+        dtemporal = None                      # gradient w.r.t. the temporal state entering the NEXT chunk
+        for tape in reversed(tapes):
+            s, e = tape["s"], tape["e"]
+            ddepth = None
+            if tape["has_endpoint"]:
+                dstate = dtemporal
+                if tape["key_index"] is not None and dkeys is not None:
+                    gk = dkeys[:, tape["key_index"]]
+                    dstate = gk if dstate is None else dstate + gk
+                if dstate is not None:
+                    ddepth, dprev = K.temporal_bwd(dstate, tape["depth"].view(B, e - s, d.hidden, 9),
+                                                   tape["local_reset"], tape["temporal_in"], tape["fired"],
+                                                   m.d_polarm_beta)
+                    dtemporal = dprev
+                else:
+                    dtemporal = None
+            else:
+                dtemporal = None
+            dx, dtraces, dseed = self._chunk_backward(tape, dh[:, s:e], ddepth, dtraces, kc, vc, dkc, dvc, seg)
+            d_emb[:, s:e] = dx.view(B, e - s, d.n)
+            if dseed is not None:
+                dtemporal = dseed if dtemporal is None else dtemporal + dseed
+            tape.clear()
+        self.g(m.emb.weight).index_add_(0, idx.reshape(-1), d_emb.view(B * T, d.n).float())
+        return loss, None
+
+    # ------------------------------------------------------------------ depth-attention helpers
+    def _project_state(self, x2d, slot, hist_k, hist_v, tape_layer, key):
+        """K/V projection of a residual-stream state into history slot ``slot``."""
+        m, d, K = self.model, self.d, self.K
+        M = x2d.shape[0]
+        kv = K.linear(x2d, self.w(m.depth_attn.kv_weight))
+        k, v = kv[:, :d.n].view(M, d.qh, d.hd), kv[:, d.n:].view(M, d.qh, d.hd)
+        if d.depth_qkv_rms:
+            tape_layer[key + "_kv_raw"] = kv
+            k, v = K.fixed_rms_fwd(k, FANIN_GAIN), K.fixed_rms_fwd(v, FANIN_GAIN * d.deepnorm_beta)
+        hist_k[slot], hist_v[slot] = k, v
+
+    def _project_state_bwd(self, x2d, slot, dhist_k, dhist_v, tape_layer, key):
+        """Gradient of :meth:`_project_state` w.r.t. its input; accumulates the weight gradient."""
+        m, d, K = self.model, self.d, self.K
+        M = x2d.shape[0]
+        dk, dv = dhist_k[slot], dhist_v[slot]
+        if d.depth_qkv_rms:
+            kv = tape_layer[key + "_kv_raw"]
+            dk = K.fixed_rms_bwd(dk, kv[:, :d.n].view(M, d.qh, d.hd), FANIN_GAIN)
+            dv = K.fixed_rms_bwd(dv, kv[:, d.n:].view(M, d.qh, d.hd), FANIN_GAIN * d.deepnorm_beta)
+        dkv = torch.cat((dk.reshape(M, d.n), dv.reshape(M, d.n)), -1).to(self.adt)
+        K.linear_wgrad(dkv, x2d, self.g(m.depth_attn.kv_weight))
+        return K.linear_dgrad(dkv, self.w(m.depth_attn.kv_weight))
+
+    def _depth_query(self, sub):
+        da, d = self.model.depth_attn, self.d
+        q = da.q_params.data[sub].float()
+        if d.depth_qkv_rms:
+            q = self.K.fixed_rms_fwd(q, d.fanin_std(d.hd))
+        return q
+
+    def _depth_query_bwd(self, sub, gq):
+        da, d = self.model.depth_attn, self.d
+        if d.depth_qkv_rms:
+            gq = self.K.fixed_rms_bwd(gq, da.q_params.data[sub].float(), d.fanin_std(d.hd))
+        self.g(da.q_params)[sub].add_(gq)
+
+    def _readout_w(self, sub):
+        da = self.model.depth_attn
+        return self.w(da.w_o_weight)[sub] if da.w_o is None else self.w(da.w_o.weight)
+
+    def _readout_g(self, sub):
+        da = self.model.depth_attn
+        return self.g(da.w_o_weight)[sub] if da.w_o is None else self.g(da.w_o.weight)
+
+    # ------------------------------------------------------------------ chunk forward
+    def _chunk_forward(self, h_emb, cos, sin, tok_reset, seg, s, e, kc, vc, traces_in, seed, seed_valid,
+                       training, want_grad):
+        m, d, K = self.model, self.d, self.K
+        B, Tc, N = h_emb.shape
+        M = B * Tc
+        dev = h_emb.device
+        L = d.layers
+        S = 2 * L
+        hist_k = torch.empty(S, M, d.qh, d.hd, dtype=self.adt, device=dev)
+        hist_v = torch.empty(S, M, d.qh, d.hd, dtype=self.adt, device=dev)
+        h = h_emb.reshape(M, N).contiguous()
+        tape = {"layers": [], "hist_k": hist_k, "hist_v": hist_v, "h_emb": h, "cos": cos, "sin": sin, "B": B,
+                "emb_l": {}}
+        self._project_state(h, 0, hist_k, hist_v, tape["emb_l"], "emb")
+        reset_flat = tok_reset.reshape(M)
+        c_prev, p_in = None, None
+        trace_out = []
+        use_tria = d.tria and not m.ablation
+        for bi, blk in enumerate(m.blocks):
+            last = bi == L - 1
+            t: Dict[str, object] = {"h_in": h}
+            # --- attention
+            qkv = K.linear(h, self.w(blk.attn.qkv_weight)).view(B, Tc, -1)
+            qkc = torch.empty(M, 3, d.qh, d.hd, dtype=self.adt, device=dev)     # sectors: rotated Q, A@K, A@V
+            K.rope_store(d, qkv, cos, sin, qkc, kc[bi], vc[bi], s)
+            t["lse"] = K.attn_fwd(d, qkc, kc[bi], vc[bi], s, e, seg)
+            t["qkc"] = qkc
+            a = K.linear(qkc[:, 2].reshape(M, N), self.w(blk.attn.o.weight))
+            # --- depth read 2bi, residual, LN
+            sub = 2 * bi
+            m1, t["lse1"] = K.dread_fwd(d, self._depth_query(sub), hist_k, hist_v, sub + 1)
+            m1 = m1.reshape(M, N)
+            s1 = K.linear(m1, self._readout_w(sub))
+            u, t["x1"], t["mean1"], t["rstd1"] = K.add_ln_fwd(s1, a, blk.ln_attn.weight.data, blk.ln_attn.bias.data,
+                                                              d.branch_rms_cap)
+            t["m1"], t["u"] = m1, u
+            if d.branch_rms_cap is not None:
+                t["s1"], t["a"] = s1, a
+            self._project_state(u, sub + 1, hist_k, hist_v, t, "u")
+            m2, t["lse2"] = K.dread_fwd(d, self._depth_query(sub + 1), hist_k, hist_v, sub + 2)
+            t["m2"] = m2
+            s2 = K.linear(m2.reshape(M, N), self._readout_w(sub + 1))
+            # --- Paraplex FFN
+            ffn = blk.ffn
+            x_real = K.linear(u, self.w(ffn.w1_real.weight))
+            gate_lin = K.linear(u, self.w(ffn.gate_proj.weight), ffn.gate_proj.bias.data) if ffn.gate_proj is not None else None
+            beta_lin = K.imag_fwd(d, qkc, u, m2, self.w(ffn.w1_imag))
+            alpha_gate = ffn.identity_gate.alpha().detach() if (ffn.identity_gate is not None and p_in is not None) else None
+            gate_w = ffn.gate_selector.weights().detach() if (use_tria and not last) else None
+            anchor = None
+            core_in = {"x_real": x_real, "p_in": p_in, "alpha_gate": alpha_gate, "b_real": ffn.w1_real.bias.data,
+                       "gate_lin": gate_lin, "beta_lin": beta_lin, "b_imag": ffn.w1_imag_bias.data,
+                       "w_trace": ffn.w1_imag_trace.data, "trace_in": None if traces_in is None else traces_in[bi],
+                       "reset": reset_flat, "c_prev": c_prev, "seed": seed if bi == 0 else None,
+                       "seed_valid": seed_valid if bi == 0 else None, "gate_w": gate_w,
+                       "axis": (bi % 3) if use_tria else None, "tria_alpha": m.tria_alpha, "B": B}
+            out = K.ffn_core_fwd(d, x_real, p_in, alpha_gate, core_in["b_real"], gate_lin, beta_lin, core_in["b_imag"],
+                                 core_in["w_trace"], core_in["trace_in"], reset_flat, None, c_prev, core_in["seed"],
+                                 core_in["seed_valid"], gate_w, core_in["axis"], m.tria_alpha, B)
+            if d.phase_secant:
+                if training:
+                    n_el = float(M * d.hidden)
+                    rad = (out["beta_sq_sum"] / n_el).sqrt().clamp_min(1e-4)
+                    ffn.beta_anchor.mul_(ffn.beta_anchor_decay).add_(rad.to(ffn.beta_anchor.dtype),
+                                                                      alpha=1.0 - ffn.beta_anchor_decay)
+                anchor = ffn.beta_anchor.detach().clone()
+            core_in["anchor"] = anchor
+            t["core"] = core_in
+            o = out["o"]
+            t["o"] = o
+            trace_out.append(out["trace_out"])
+            c_prev, p_in = out["c"], out["p_out"]
+            f = K.linear(o, self.w(ffn.w2.weight), ffn.w2.bias.data)
+            h, t["x2"], t["mean2"], t["rstd2"] = K.add_ln_fwd(s2, f, blk.ln_ffn.weight.data, blk.ln_ffn.bias.data,
+                                                              d.branch_rms_cap)
+            if d.branch_rms_cap is not None:
+                t["s2"], t["f"] = s2, f
+            t["h_out"] = h
+            if not last:
+                self._project_state(h, sub + 2, hist_k, hist_v, t, "h")
+            tape["layers"].append(t)
+        tape["h_out"] = h
+        tape["depth"] = c_prev
+        tape["trace_out"] = trace_out
+        return tape
+
+    # ------------------------------------------------------------------ chunk backward
+    def _chunk_backward(self, tape, dh_out, ddepth, dtraces_out, kc, vc, dkc, dvc, seg):
+        """Reverse pass over the layers of one chunk.
+
+        dh_out [B,Tc,N]: gradient of the chunk's final hidden states; ddepth [B,Tc,H,9] or None: gradient of
+        the last layer's carriers (from the temporal endpoint); dtraces_out: per-layer gradient of the phase
+        trace handed to the next chunk.  Returns (d h_emb [M,N], per-layer d trace_in, d seed)."""
+        m, d, K = self.model, self.d, self.K
+        B, s, e = tape["B"], tape["s"], tape["e"]
+        Tc = e - s
+        M, N, L = B * Tc, d.n, d.layers
+        dev = dh_out.device
+        hist_k, hist_v = tape["hist_k"], tape["hist_v"]
+        dhk = torch.zeros(hist_k.shape, dtype=torch.float32, device=dev)
+        dhv = torch.zeros(hist_v.shape, dtype=torch.float32, device=dev)
+        dh = dh_out.reshape(M, N).to(self.adt)
+        dc = None if ddepth is None else ddepth.reshape(M, d.hidden, 9)
+        dp_out = None
+        dseed = None
+        dtraces_in: List[Optional[torch.Tensor]] = [None] * L
+        cap = d.branch_rms_cap
+        for bi in range(L - 1, -1, -1):
+            blk, t = m.blocks[bi], tape["layers"][bi]
+            ffn = blk.ffn
+            last = bi == L - 1
+            sub = 2 * bi
+            if not last:
+                dh = dh + self._project_state_bwd(t["h_out"], sub + 2, dhk, dhv, t, "h")
+            # --- LN2 and the two addends
+            ds2, df = K.add_ln_bwd(dh, t["x2"], t["mean2"], t["rstd2"], blk.ln_ffn.weight.data,
+                                   self.g(blk.ln_ffn.weight), self.g(blk.ln_ffn.bias), cap, t.get("s2"), t.get("f"))
+            # --- w2
+            K.linear_wgrad(df, t["o"], self.g(ffn.w2.weight))
+            K.colsum_add(df, self.g(ffn.w2.bias))
+            do = K.linear_dgrad(df, self.w(ffn.w2.weight))
+            # --- Paraplex core + Tria
+            core = t["core"]
+            gr = K.ffn_core_bwd(d, core, do, dc, dp_out, None if dtraces_out is None else dtraces_out[bi])
+            dx_real, dbeta = gr["d_x_real"].to(self.adt), gr["d_beta_lin"].to(self.adt)
+            dtraces_in[bi] = gr.get("d_trace_in")
+            dc, dp_out = gr.get("d_c_prev"), gr.get("d_p_in")
+            if gr.get("d_seed") is not None:
+                dseed = gr["d_seed"]
+            self.g(ffn.w1_real.bias).add_(gr["d_b_real"])
+            self.g(ffn.w1_imag_bias).add_(gr["d_b_imag"])
+            self.g(ffn.w1_imag_trace).add_(gr["d_w_trace"])
+            if gr.get("d_alpha_gate") is not None and ffn.identity_gate.raw_alpha.requires_grad:
+                ig = ffn.identity_gate
+                self.g(ig.raw_alpha).add_(gr["d_alpha_gate"] * ig.alpha_max * (1.0 - torch.tanh(ig.raw_alpha.data) ** 2))
+            if gr.get("d_gate_w") is not None and ffn.gate_selector.logits.requires_grad:
+                w9 = core["gate_w"].float()
+                gw9 = gr["d_gate_w"]
+                self.g(ffn.gate_selector.logits).add_(w9 * (gw9 - (gw9 * w9).sum()))
+            u = t["u"]
+            K.linear_wgrad(dx_real, u, self.g(ffn.w1_real.weight))
+            du = K.linear_dgrad(dx_real, self.w(ffn.w1_real.weight))
+            if ffn.gate_proj is not None:
+                dgl = gr["d_gate_lin"].to(self.adt)
+                K.linear_wgrad(dgl, u, self.g(ffn.gate_proj.weight))
+                K.colsum_add(dgl, self.g(ffn.gate_proj.bias))
+                du = du + K.linear_dgrad(dgl, self.w(ffn.gate_proj.weight))
+            dqkc, du_i, dm2_i = K.imag_bwd(d, dbeta, t["qkc"], u, t["m2"], self.w(ffn.w1_imag), self.g(ffn.w1_imag))
+            du = du + du_i
+            # --- depth read 2bi+1 (its output feeds the readout GEMM and the imaginary projection)
+            K.linear_wgrad(ds2, t["m2"].reshape(M, N), self._readout_g(sub + 1))
+            dm2 = K.linear_dgrad(ds2, self._readout_w(sub + 1)).view(M, d.qh, d.hd) + dm2_i
+            gq = torch.zeros(d.qh, d.hd, dtype=torch.float32, device=dev)
+            K.dread_bwd(d, dm2, t["m2"], t["lse2"], self._depth_query(sub + 1), hist_k, hist_v, sub + 2, dhk, dhv, gq)
+            self._depth_query_bwd(sub + 1, gq)
+            du = du + self._project_state_bwd(u, sub + 1, dhk, dhv, t, "u")
+            # --- LN1
+            ds1, da = K.add_ln_bwd(du, t["x1"], t["mean1"], t["rstd1"], blk.ln_attn.weight.data,
+                                   self.g(blk.ln_attn.weight), self.g(blk.ln_attn.bias), cap, t.get("s1"), t.get("a"))
+            K.linear_wgrad(ds1, t["m1"], self._readout_g(sub))
+            dm1 = K.linear_dgrad(ds1, self._readout_w(sub)).view(M, d.qh, d.hd)
+            gq = torch.zeros(d.qh, d.hd, dtype=torch.float32, device=dev)
+            K.dread_bwd(d, dm1, t["m1"].view(M, d.qh, d.hd), t["lse1"], self._depth_query(sub), hist_k, hist_v,
+                        sub + 1, dhk, dhv, gq)
+            self._depth_query_bwd(sub, gq)
+            # --- attention
+            qkc = t["qkc"]
+            K.linear_wgrad(da, qkc[:, 2].reshape(M, N), self.g(blk.attn.o.weight))
+            dqkc[:, 2] = dqkc[:, 2] + K.linear_dgrad(da, self.w(blk.attn.o.weight)).view(M, d.qh, d.hd)
+            dq_attn = K.attn_bwd(d, dqkc, qkc, kc[bi], vc[bi], t["lse"], s, e, seg, dkc[bi], dvc[bi])
+            dq = dq_attn.reshape(B, Tc, d.qh, d.hd).float() + dqkc[:, 0].reshape(B, Tc, d.qh, d.hd).float()
+            dqkv = K.rope_bwd(d, dq, dkc[bi][:, s:e], dvc[bi][:, s:e], tape["cos"], tape["sin"], self.adt).view(M, -1)
+            K.linear_wgrad(dqkv, t["h_in"], self.g(blk.attn.qkv_weight))
+            dh = K.linear_dgrad(dqkv, self.w(blk.attn.qkv_weight))
+        dh = dh + self._project_state_bwd(tape["h_emb"], 0, dhk, dhv, tape["emb_l"], "emb")
+        return dh, dtraces_in, dseed
+
+    # ------------------------------------------------------------------ readout
+    def _readout_forward(self, h, doc_keys, valid, key_pos, seg):
+        """doc_keys [B,Kn,H,9] fp32 -> pooled 9-vectors -> keys [B,Kn,N]; masked cross-attention added to h."""
+        m, d, K = self.model, self.d, self.K
+        agg, fca = m.tria_agg, m.tria_final_ca
+        B, T, N = h.shape
+        Kn = key_pos.numel()
+        score_w = agg.score_w().detach().float()
+        pooled = K.slot_pool_fwd(doc_keys, score_w)                                   # [B,Kn,9] fp32
+        z = torch.addmm(agg.reader.proj.bias.data, pooled.view(B * Kn, 9), agg.reader.proj.weight.data.t())
+        a = torch.addmm(agg.up.bias.data, z, agg.up.weight.data.t()).to(self.adt)     # [B*Kn,N]
+        q = K.linear(h.reshape(B * T, N), self.w(fca.w_qk.weight)).view(B, T, N)
+        k = K.linear(a, self.w(fca.w_qk.weight)).view(B, Kn, N)
+        v = K.linear(a, self.w(fca.w_v.weight)).view(B, Kn, N)
+        allowed = key_pos.view(1, 1, Kn) <= torch.arange(T, device=h.device).view(1, T, 1)
+        allowed = allowed & valid[:, None, :]
+        if seg is not None:
+            allowed = allowed & (seg.unsqueeze(-1) == seg[:, key_pos].unsqueeze(1))
+        out = K.cross_attn_fwd(q, k, v, allowed, fca.scale)
+        gamma = fca.gamma().detach()
+        h_out = (h.float() + gamma * out.float()).to(h.dtype)
+        return {"h": h, "h_out": h_out, "doc_keys": doc_keys, "score_w": score_w, "pooled": pooled, "z": z, "a": a,
+                "q": q, "k": k, "v": v, "allowed": allowed, "out": out, "gamma": gamma}
+
+    def _readout_backward(self, ro, dh_out):
+        m, d, K = self.model, self.d, self.K
+        agg, fca = m.tria_agg, m.tria_final_ca
+        h = ro["h"]
+        B, T, N = h.shape
+        Kn = ro["k"].shape[1]
+        gamma = ro["gamma"]
+        dgamma = (dh_out.float() * ro["out"].float()).sum()
+        self.g(fca.raw_gamma).add_(dgamma * fca.gamma_max * (1.0 - torch.tanh(fca.raw_gamma.data) ** 2))
+        dout = (dh_out.float() * gamma).to(self.adt)
+        dq, dk, dv = K.cross_attn_bwd(dout, ro["q"], ro["k"], ro["v"], ro["allowed"], fca.scale)
+        dq, dk, dv = dq.to(self.adt).reshape(B * T, N), dk.to(self.adt).reshape(B * Kn, N), dv.to(self.adt).reshape(B * Kn, N)
+        a = ro["a"]
+        K.linear_wgrad(dq, h.reshape(B * T, N), self.g(fca.w_qk.weight))
+        K.linear_wgrad(dk, a, self.g(fca.w_qk.weight))
+        K.linear_wgrad(dv, a, self.g(fca.w_v.weight))
+        dh = dh_out + K.linear_dgrad(dq, self.w(fca.w_qk.weight)).view(B, T, N)
+        da = (K.linear_dgrad(dk, self.w(fca.w_qk.weight)) + K.linear_dgrad(dv, self.w(fca.w_v.weight))).float()
+        # tiny fp32 tail: up (32->N) and proj (9->32)
+        self.g(agg.up.weight).add_(da.t() @ ro["z"]); self.g(agg.up.bias).add_(da.sum(0))
+        dz = da @ agg.up.weight.data
+        pooled = ro["pooled"].view(B * Kn, 9)
+        self.g(agg.reader.proj.weight).add_(dz.t() @ pooled); self.g(agg.reader.proj.bias).add_(dz.sum(0))
+        dpooled = (dz @ agg.reader.proj.weight.data).view(B, Kn, 9)
+        dkeys, dscore = K.slot_pool_bwd(dpooled, ro["doc_keys"], ro["score_w"])
+        # score_w = normalize(key_proj^T query) * softplus(logit_scale_raw): differentiate the 9-vector by autograd
+        with torch.enable_grad():
+            kp = agg.reader.key_proj.weight.detach().requires_grad_(True)
+            qy = agg.pool.query.detach().requires_grad_(True)
+            ls = agg.pool.logit_scale_raw.detach().requires_grad_(True)
+            w9 = torch.nn.functional.normalize(torch.mv(kp.t(), qy), dim=0, eps=1e-6) * torch.nn.functional.softplus(ls)
+            g_kp, g_q, g_ls = torch.autograd.grad(w9, [kp, qy, ls], dscore.to(w9.dtype))
+        self.g(agg.reader.key_proj.weight).add_(g_kp)
+        self.g(agg.pool.query).add_(g_q)
+        self.g(agg.pool.logit_scale_raw).add_(g_ls)
+        return dh, dkeys
+
+
+class _FusedLoss(torch.autograd.Function):
+    """Loss node of the fused plan: forward and backward both run in ``forward`` (gradients are written
+    straight into ``param.grad``); ``backward`` only checks the incoming scale."""
+
+    @staticmethod
+    def forward(ctx, plan, x, y, position_ids, seg, ignore_index, hook):
+        with torch.no_grad():
+            loss, _ = plan.run(x, y, position_ids, seg, want_grad=True, ignore_index=ignore_index,
+                               grad_scale=plan.pending_scale if hasattr(plan, "pending_scale") else 1.0)
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        return (None,) * 7

@@ -173,11 +173,11 @@ class FlatOptimizer:
     @torch.no_grad()
     def step(self) -> None:
         self.step_count += 1
-        self.compute_clip()
         from ..ops import native
         if self.flat.device.type == "cuda" and native.available():
             native.optimizer_step(self)
         else:
+            self.compute_clip()
             self._step_torch()
 
     @torch.no_grad()

@@ -65,6 +65,9 @@ class TrainEngine:
         self.opt = FlatOptimizer(self.flat, self.opt_name, lr=cfg.lr, weight_decay=cfg.weight_decay,
                                  grad_clip=cfg.grad_clip, no_decay=no_decay, lr_mults=lr_mults)
         self.sync = GradSync(self.flat, model, backend=grad_sync, anchor_mode=anchor_mode)
+        self.plan = model._opset(model.emb.weight) if not model.ablation else None   # fused plan on CUDA
+        if self.plan is not None:
+            self.plan.bind(self.flat)
         self.step_idx = 0           # completed optimizer steps
         self.ignore_index = loss_mask_ignore
         self.last_fire_count = torch.zeros((), dtype=torch.long, device=device)
@@ -76,9 +79,6 @@ class TrainEngine:
         return torch.autocast("cuda", dtype=torch.bfloat16 if self.amp == "bf16" else torch.float16)
 
     def loss_fn(self, x, y, attn_mask=None, position_ids=None) -> torch.Tensor:
-        ops = self.model._opset(self.model.emb.weight)
-        if ops is not None and hasattr(ops, "loss"):
-            return ops.loss(self.model, x, y, attn_mask, position_ids, self.ignore_index)
         with self._autocast():
             logits = self.model(x, attn_mask=attn_mask, position_ids=position_ids)
         return F.cross_entropy(logits.float().reshape(-1, logits.shape[-1]), y.reshape(-1),
@@ -88,7 +88,8 @@ class TrainEngine:
         return batch.to(self.device, non_blocking=True) if batch.device != self.device else batch
 
     # ------------------------------------------------------------------ one optimizer step
-    def step(self, batch, targets: Optional[torch.Tensor] = None, attn_mask=None, position_ids=None) -> torch.Tensor:
+    def step(self, batch, targets: Optional[torch.Tensor] = None, attn_mask=None, position_ids=None,
+             segment_ids=None) -> torch.Tensor:
         """``batch`` is ``[B, T+1]`` tokens (inputs ``[:, :-1]``, targets ``[:, 1:]``) or, with explicit
         ``targets``, ``[B, T]`` inputs.  With ``grad_accum_steps > 1`` pass a list of micro-batches."""
         micro = batch if isinstance(batch, (list, tuple)) else [batch]
@@ -101,8 +102,17 @@ class TrainEngine:
                 x, y = mb[:, :-1], mb[:, 1:]
             else:
                 x, y = mb, self.to_device(targets)
-            loss = self.loss_fn(x, y, attn_mask, position_ids)
-            (loss / float(len(micro))).backward()
+            if self.plan is not None and attn_mask is None:
+                with torch.no_grad():
+                    loss, _ = self.plan.run(x, y, position_ids, segment_ids, want_grad=True,
+                                            ignore_index=self.ignore_index, grad_scale=1.0 / float(len(micro)))
+            else:
+                if segment_ids is not None and attn_mask is None:
+                    T = x.shape[1]
+                    attn_mask = ((segment_ids[:, :, None] == segment_ids[:, None, :])
+                                 & torch.ones(T, T, dtype=torch.bool, device=x.device).tril()).unsqueeze(1)
+                loss = self.loss_fn(x, y, attn_mask, position_ids)
+                (loss / float(len(micro))).backward()
             fm = self.model.last_tria_fire_mask
             if fm is not None:
                 self.last_fire_count += fm.sum()

@@ -1,0 +1,86 @@
+"""tcgen05/TMA GEMM against fp32 PyTorch matmul for every operand-major combination, odd sizes,
+batched heads and K segments."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _k():
+    from loomformer_paraplex_b200.ops import kernels
+    return kernels
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6))
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (2048, 768, 768), (300, 200, 136), (128, 3072, 768)])
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_kmajor_linear(M, N, K, bn):
+    k = _k()
+    torch.manual_seed(0)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda")
+    c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    k.gemm([x], [K], w, c, M=M, N=N, bias=bias, bn=bn)
+    ref = x.float() @ w.float().t() + bias
+    k.check_status(c.device)
+    assert _rel(c, ref) < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 128, 128), (2048, 768, 3072), (264, 200, 136)])
+def test_dgrad_mn_major_b(M, N, K):
+    k = _k()
+    torch.manual_seed(1)
+    dy = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)          # reduction over K
+    w = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)           # [reduction, out] -> MN-major B
+    c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    k.gemm([dy], [K], w, c, M=M, N=N, b_mn=True)
+    k.check_status(c.device)
+    assert _rel(c, dy.float() @ w.float()) < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (3072, 768, 2048), (200, 136, 264)])
+def test_wgrad_both_mn_major_fp32_accumulate(M, N, K):
+    k = _k()
+    torch.manual_seed(2)
+    dy = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)          # [reduction, out rows]
+    x = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)           # [reduction, out cols]
+    g = torch.randn(M, N, device="cuda")
+    ref = g + dy.float().t() @ x.float()
+    k.gemm([dy], [K], x, g, M=M, N=N, a_mn=True, b_mn=True, accumulate=True)
+    k.check_status(g.device)
+    assert _rel(g, ref) < 1e-2
+
+
+def test_segmented_batched_imag_projection():
+    from types import SimpleNamespace
+    from loomformer_paraplex_b200.ops.twins import TorchKernels
+    k = _k()
+    for open_sectors in (False, True):
+        qh, hd, hpq = 8, 96, 384
+        n = qh * hd
+        d = SimpleNamespace(qh=qh, hd=hd, hpq=hpq, n=n, hidden=qh * hpq, open_sectors=open_sectors,
+                            imag_in=(4 * n + hd) if open_sectors else (n + 4 * hd))
+        M = 384
+        torch.manual_seed(3)
+        qkc = torch.randn(M, 3, qh, hd, device="cuda", dtype=torch.bfloat16)
+        u = torch.randn(M, n, device="cuda", dtype=torch.bfloat16)
+        m2 = torch.randn(M, qh, hd, device="cuda", dtype=torch.bfloat16)
+        w = (torch.randn(d.hidden, d.imag_in, device="cuda") * 0.05).to(torch.bfloat16)
+        ck, tk = k.CudaKernels(), TorchKernels()
+        out = ck.imag_fwd(d, qkc, u, m2, w)
+        ref = tk.imag_fwd(d, qkc.float(), u.float(), m2.float(), w.float())
+        assert _rel(out, ref) < 1.5e-2
+        dbeta = torch.randn(M, d.hidden, device="cuda", dtype=torch.bfloat16)
+        g1 = torch.zeros(d.hidden, d.imag_in, device="cuda")
+        g2 = torch.zeros_like(g1)
+        a1 = ck.imag_bwd(d, dbeta, qkc, u, m2, w, g1)
+        a2 = tk.imag_bwd(d, dbeta.float(), qkc.float(), u.float(), m2.float(), w.float(), g2)
+        k.check_status(u.device)
+        assert not ck.fallbacks, ck.fallbacks
+        assert _rel(g1, g2) < 1.5e-2
+        for x1, x2 in zip(a1, a2):
+            assert _rel(x1, x2) < 1.5e-2
