@@ -96,6 +96,113 @@ void cast_shadow(torch::Tensor p, torch::Tensor shadow) {
   TORCH_CHECK(rc == 0, "loom_cast_shadow failed: ", rc);
 }
 
+typedef c10::optional<torch::Tensor> OptT;
+const void* cp(const OptT& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+void* mp(const OptT& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+const float* cf(const OptT& t) { return t.has_value() ? (const float*)t->data_ptr() : nullptr; }
+float* mf(const OptT& t) { return t.has_value() ? (float*)t->data_ptr() : nullptr; }
+const uint8_t* cu8(const OptT& t) { return t.has_value() ? (const uint8_t*)t->data_ptr() : nullptr; }
+
+// forward when bwd == false, backward otherwise; tensors not used by a direction may be None.
+void ffn_core(bool bwd, int64_t B, int64_t Tc, int64_t H, int64_t axis, bool secant, double powlu_m, double tria_alpha,
+              double phase_floor, OptT alpha_gate, OptT anchor, torch::Tensor x_real, OptT p_in, torch::Tensor b_real,
+              OptT gate_lin, torch::Tensor beta_lin, torch::Tensor b_imag, torch::Tensor w_trace, OptT trace_in,
+              OptT reset, OptT c_prev, OptT seed, OptT seed_valid, OptT gate_w,
+              OptT o_out, OptT c_out, OptT p_out, OptT trace_out, OptT beta_sq_sum,
+              OptT d_o, OptT d_c, OptT d_pout, OptT dtrace_out,
+              OptT dx_real, OptT dp_in, OptT dgate_lin, OptT dbeta, OptT gz, OptT dc_prev, OptT dseed, OptT dtrace_in,
+              OptT g_b_real, OptT g_w_trace, OptT g_b_imag, OptT g_scalars) {
+  const c10::cuda::CUDAGuard guard(x_real.device());
+  LoomFfnCore a{};
+  a.B = (int)B; a.Tc = (int)Tc; a.H = (int)H; a.axis = (int)axis; a.secant = secant;
+  a.powlu_m = (float)powlu_m; a.tria_alpha = (float)tria_alpha; a.phase_floor = (float)phase_floor;
+  a.alpha_gate = cf(alpha_gate); a.anchor = cf(anchor);
+  a.x_real = x_real.data_ptr(); a.p_in = cp(p_in); a.b_real = (const float*)b_real.data_ptr();
+  a.gate_lin = cp(gate_lin); a.beta_lin = beta_lin.data_ptr(); a.b_imag = (const float*)b_imag.data_ptr();
+  a.w_trace = (const float*)w_trace.data_ptr(); a.trace_in = cf(trace_in); a.reset = cu8(reset);
+  a.c_prev = cp(c_prev); a.seed = cf(seed); a.seed_valid = cu8(seed_valid); a.gate_w = cf(gate_w);
+  a.o_out = mp(o_out); a.c_out = mp(c_out); a.p_out = mp(p_out); a.trace_out = mf(trace_out); a.beta_sq_sum = mf(beta_sq_sum);
+  a.d_o = cp(d_o); a.d_c = cp(d_c); a.d_pout = cp(d_pout); a.dtrace_out = cf(dtrace_out);
+  a.dx_real = mp(dx_real); a.dp_in = mp(dp_in); a.dgate_lin = mp(dgate_lin); a.dbeta = mp(dbeta); a.gz = mf(gz);
+  a.dc_prev = mp(dc_prev); a.dseed = mf(dseed); a.dtrace_in = mf(dtrace_in);
+  a.g_b_real = mf(g_b_real); a.g_w_trace = mf(g_w_trace); a.g_b_imag = mf(g_b_imag); a.g_scalars = mf(g_scalars);
+  int rc = bwd ? loom_ffn_core_bwd(&a, cur_stream()) : loom_ffn_core_fwd(&a, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_ffn_core failed: ", rc);
+}
+
+void rope_store(torch::Tensor qkv, torch::Tensor cs, torch::Tensor sn, torch::Tensor qkc, torch::Tensor kcache,
+                torch::Tensor vcache, int64_t M, int64_t Tc, int64_t T, int64_t s, int64_t QH, int64_t KVH, int64_t HD) {
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  int rc = loom_rope_store(qkv.data_ptr(), fptr(cs), fptr(sn), qkc.data_ptr(), kcache.data_ptr(), vcache.data_ptr(),
+                           (int)M, (int)Tc, (int)T, (int)s, (int)QH, (int)KVH, (int)HD, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_rope_store failed: ", rc);
+}
+
+void rope_bwd(torch::Tensor dq_attn, torch::Tensor dqkc, torch::Tensor dkc, torch::Tensor dvc, torch::Tensor cs,
+              torch::Tensor sn, torch::Tensor dqkv, int64_t M, int64_t Tc, int64_t T, int64_t s, int64_t QH, int64_t KVH,
+              int64_t HD) {
+  const c10::cuda::CUDAGuard guard(dqkv.device());
+  int rc = loom_rope_bwd(dq_attn.data_ptr(), dqkc.data_ptr(), fptr(dkc), fptr(dvc), fptr(cs), fptr(sn), dqkv.data_ptr(),
+                         (int)M, (int)Tc, (int)T, (int)s, (int)QH, (int)KVH, (int)HD, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_rope_bwd failed: ", rc);
+}
+
+void dread(bool bwd, torch::Tensor q, torch::Tensor hk, torch::Tensor hv, torch::Tensor out, torch::Tensor lse, OptT dm,
+           OptT dhk, OptT dhv, OptT gq, int64_t n, int64_t MQ, int64_t QH, int64_t HD) {
+  const c10::cuda::CUDAGuard guard(hk.device());
+  int rc = loom_dread(bwd, fptr(q), hk.data_ptr(), hv.data_ptr(), out.data_ptr(), fptr(lse), cp(dm), mf(dhk), mf(dhv),
+                      mf(gq), (int)n, MQ, (int)QH, (int)HD, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_dread failed: ", rc);
+}
+
+void add_ln_fwd(torch::Tensor a, torch::Tensor b, torch::Tensor w, torch::Tensor bias, torch::Tensor y, torch::Tensor x,
+                torch::Tensor mean, torch::Tensor rstd, int64_t M, int64_t N, double eps) {
+  const c10::cuda::CUDAGuard guard(a.device());
+  int rc = loom_add_ln_fwd(a.data_ptr(), b.data_ptr(), fptr(w), fptr(bias), y.data_ptr(), x.data_ptr(), fptr(mean),
+                           fptr(rstd), (int)M, (int)N, (float)eps, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_add_ln_fwd failed: ", rc);
+}
+
+void add_ln_bwd(torch::Tensor dy, torch::Tensor x, torch::Tensor mean, torch::Tensor rstd, torch::Tensor w,
+                torch::Tensor dx, torch::Tensor gw, torch::Tensor gb, int64_t M, int64_t N) {
+  const c10::cuda::CUDAGuard guard(dy.device());
+  int rc = loom_add_ln_bwd(dy.data_ptr(), x.data_ptr(), fptr(mean), fptr(rstd), fptr(w), dx.data_ptr(), fptr(gw),
+                           fptr(gb), (int)M, (int)N, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_add_ln_bwd failed: ", rc);
+}
+
+void colsum(torch::Tensor dy, torch::Tensor gb, int64_t M, int64_t N) {
+  const c10::cuda::CUDAGuard guard(dy.device());
+  int rc = loom_colsum(dy.data_ptr(), fptr(gb), (int)M, (int)N, dy.stride(0), cur_stream());
+  TORCH_CHECK(rc == 0, "loom_colsum failed: ", rc);
+}
+
+void ce(torch::Tensor logits, torch::Tensor targets, torch::Tensor nll, torch::Tensor scale, int64_t ignore_index,
+        bool write_grad) {
+  const c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(logits.is_contiguous() && targets.scalar_type() == torch::kInt64 && targets.is_contiguous(), "bad CE inputs");
+  int rc = loom_ce(logits.data_ptr(), (const long long*)targets.data_ptr(), fptr(nll), fptr(scale), logits.size(0),
+                   (int)logits.size(1), ignore_index, write_grad, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_ce failed: ", rc);
+}
+
+void temporal_fwd(torch::Tensor depth, torch::Tensor reset, OptT state_in, OptT fired, double beta, torch::Tensor state_out,
+                  torch::Tensor raw_out, OptT ckpt, int64_t B, int64_t Tc, int64_t H) {
+  const c10::cuda::CUDAGuard guard(depth.device());
+  int rc = loom_temporal_fwd(depth.data_ptr(), (const uint8_t*)reset.data_ptr(), cf(state_in), cu8(fired), (float)beta,
+                             fptr(state_out), fptr(raw_out), mf(ckpt), (int)B, (int)Tc, (int)H, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_temporal_fwd failed: ", rc);
+}
+
+void temporal_bwd(torch::Tensor depth, torch::Tensor reset, OptT state_in, OptT fired, double beta, torch::Tensor raw,
+                  OptT ckpt, torch::Tensor dstate, torch::Tensor ddepth, OptT dstate_in, int64_t B, int64_t Tc, int64_t H) {
+  const c10::cuda::CUDAGuard guard(depth.device());
+  int rc = loom_temporal_bwd(depth.data_ptr(), (const uint8_t*)reset.data_ptr(), cf(state_in), cu8(fired), (float)beta,
+                             fptr(raw), cf(ckpt), fptr(dstate), ddepth.data_ptr(), mf(dstate_in), (int)B, (int)Tc, (int)H,
+                             cur_stream());
+  TORCH_CHECK(rc == 0, "loom_temporal_bwd failed: ", rc);
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -104,4 +211,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw_flat", &adamw_flat, "AdamW over the flat parameter buffer");
   m.def("atom_flat", &atom_flat, "ATOM over the flat parameter buffer");
   m.def("cast_shadow", &cast_shadow, "fp32 -> bf16 parameter shadow");
+  m.def("ffn_core", &ffn_core, "fused Paraplex core + Tria step (forward / backward)");
+  m.def("rope_store", &rope_store, "RoPE + KV cache write");
+  m.def("rope_bwd", &rope_bwd, "inverse RoPE of the q/k/v gradients");
+  m.def("dread", &dread, "depth-attention read (forward / backward)");
+  m.def("add_ln_fwd", &add_ln_fwd, "residual add + LayerNorm");
+  m.def("add_ln_bwd", &add_ln_bwd, "residual add + LayerNorm backward");
+  m.def("colsum", &colsum, "column sums into an fp32 accumulator");
+  m.def("ce", &ce, "cross-entropy over bf16 logits with in-place gradient");
+  m.def("temporal_fwd", &temporal_fwd, "temporal carry endpoint + PolARM");
+  m.def("temporal_bwd", &temporal_bwd, "temporal carry endpoint backward");
 }

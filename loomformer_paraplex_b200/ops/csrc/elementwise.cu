@@ -1,0 +1,529 @@
+// Bandwidth-bound kernels of the fused plan: RoPE + KV-cache write, depth-attention read, residual add +
+// LayerNorm, column sums, cross-entropy.  bf16 storage, fp32 math, 16-byte vector accesses.
+//
+// Reference counterparts: rotary embedding (loomformer.py:2983-2985), depth_attn warp kernels
+// (kernels/depth_attn/depth_attn_kernel.cuh:444-651), ATen LayerNorm / cross_entropy.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include "loom_c_api.h"
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+typedef __nv_bfloat162 bf2;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const bf2* p = reinterpret_cast<const bf2*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(p[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  bf2* p = reinterpret_cast<bf2*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+
+// ----------------------------------------------------------------------------------------------
+// RoPE (rotate-half) of q and k, cache write.  One thread per (row, head, pair index).
+// qkv [M, N+2KV]; cos/sin [M, HD] fp32; q_out = sector 0 of qkc [M, 3, QH, HD]; caches [B, T, KVH, HD].
+// ----------------------------------------------------------------------------------------------
+__global__ void rope_store_kernel(const bf16* __restrict__ qkv, const float* __restrict__ cs, const float* __restrict__ sn,
+                                  bf16* __restrict__ qkc, bf16* __restrict__ kcache, bf16* __restrict__ vcache,
+                                  int M, int Tc, int T, int s_off, int QH, int KVH, int HD) {
+  const int half = HD / 2;
+  const int heads = QH + 2 * KVH;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)M * heads * half) return;
+  const int j = (int)(idx % half);
+  const int hh = (int)((idx / half) % heads);
+  const int m = (int)(idx / ((long long)half * heads));
+  const int N = QH * HD, ld = N + 2 * KVH * HD;
+  const bf16* src = qkv + (long long)m * ld + hh * HD;
+  const float x1 = __bfloat162float(src[j]), x2 = __bfloat162float(src[j + half]);
+  const int b = m / Tc, t = m % Tc;
+  if (hh < QH + KVH) {
+    const float c1 = cs[(long long)m * HD + j], c2 = cs[(long long)m * HD + j + half];
+    const float s1 = sn[(long long)m * HD + j], s2 = sn[(long long)m * HD + j + half];
+    const float y1 = x1 * c1 - x2 * s1, y2 = x2 * c2 + x1 * s2;
+    bf16* dst = (hh < QH) ? qkc + (long long)m * 3 * N + hh * HD
+                          : kcache + (((long long)b * T + s_off + t) * KVH + (hh - QH)) * HD;
+    dst[j] = __float2bfloat16(y1); dst[j + half] = __float2bfloat16(y2);
+  } else {
+    bf16* dst = vcache + (((long long)b * T + s_off + t) * KVH + (hh - QH - KVH)) * HD;
+    dst[j] = __float2bfloat16(x1); dst[j + half] = __float2bfloat16(x2);
+  }
+}
+
+// Inverse rotation: dqkv = [R^T (dq_attn + dq_direct), R^T dk, dv].
+// dq_attn [M,QH,HD] bf16; dq_direct = sector 0 of dqkc [M,3,QH,HD] bf16; dk/dv = fp32 cache-gradient rows.
+__global__ void rope_bwd_kernel(const bf16* __restrict__ dq_attn, const bf16* __restrict__ dqkc,
+                                const float* __restrict__ dkc, const float* __restrict__ dvc,
+                                const float* __restrict__ cs, const float* __restrict__ sn, bf16* __restrict__ dqkv,
+                                int M, int Tc, int T, int s_off, int QH, int KVH, int HD) {
+  const int half = HD / 2;
+  const int heads = QH + 2 * KVH;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)M * heads * half) return;
+  const int j = (int)(idx % half);
+  const int hh = (int)((idx / half) % heads);
+  const int m = (int)(idx / ((long long)half * heads));
+  const int N = QH * HD, ld = N + 2 * KVH * HD;
+  const int b = m / Tc, t = m % Tc;
+  bf16* dst = dqkv + (long long)m * ld + hh * HD;
+  float g1, g2;
+  if (hh < QH) {
+    const long long a = ((long long)m * QH + hh) * HD, d = (long long)m * 3 * N + hh * HD;
+    g1 = __bfloat162float(dq_attn[a + j]) + __bfloat162float(dqkc[d + j]);
+    g2 = __bfloat162float(dq_attn[a + j + half]) + __bfloat162float(dqkc[d + j + half]);
+  } else {
+    const int kh = (hh < QH + KVH) ? hh - QH : hh - QH - KVH;
+    const float* src = ((hh < QH + KVH) ? dkc : dvc) + (((long long)b * T + s_off + t) * KVH + kh) * HD;
+    g1 = src[j]; g2 = src[j + half];
+  }
+  if (hh < QH + KVH) {
+    const float c1 = cs[(long long)m * HD + j], c2 = cs[(long long)m * HD + j + half];
+    const float s1 = sn[(long long)m * HD + j], s2 = sn[(long long)m * HD + j + half];
+    // forward: y1 = x1 c1 - x2 s1 ; y2 = x2 c2 + x1 s2
+    dst[j] = __float2bfloat16(g1 * c1 + g2 * s2);
+    dst[j + half] = __float2bfloat16(g2 * c2 - g1 * s1);
+  } else {
+    dst[j] = __float2bfloat16(g1); dst[j + half] = __float2bfloat16(g2);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
+// Depth-attention read.  G lanes (G = power of two >= HD/8) own one (row, head); each lane holds 8 dims.
+// hist_k / hist_v: [S, M, QH, HD] bf16;  q: [QH, HD] fp32;  out: [M, QH, HD] bf16;  lse: [M, QH] fp32.
+// ----------------------------------------------------------------------------------------------
+template <int G>
+__global__ void __launch_bounds__(256) dread_fwd_kernel(const float* __restrict__ q, const bf16* __restrict__ hk,
+                                                        const bf16* __restrict__ hv, bf16* __restrict__ out,
+                                                        float* __restrict__ lse, int n, long long MQ, int QH, int HD,
+                                                        float scale) {
+  const long long gid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / G;
+  const int l = threadIdx.x % G;
+  if (gid >= MQ) return;                    // whole G-lane groups leave together
+  const unsigned mask = __activemask();
+  const int g = (int)(gid % QH);
+  const bool act = l * 8 < HD;
+  float qv[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) qv[i] = act ? q[g * HD + l * 8 + i] * scale : 0.f;
+  const long long stride = MQ * HD, base = gid * HD + l * 8;
+  float mx = -INFINITY, den = 0.f, acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int s = 0; s < n; ++s) {
+    float kf[8], vf[8];
+    if (act) {
+      unpack8(*reinterpret_cast<const uint4*>(hk + s * stride + base), kf);
+      unpack8(*reinterpret_cast<const uint4*>(hv + s * stride + base), vf);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { kf[i] = 0.f; vf[i] = 0.f; }
+    }
+    float d = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) d += qv[i] * kf[i];
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) d += __shfl_xor_sync(mask, d, o, G);
+    const float nm = fmaxf(mx, d);
+    const float corr = __expf(mx - nm), p = __expf(d - nm);
+    den = den * corr + p;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = acc[i] * corr + p * vf[i];
+    mx = nm;
+  }
+  const float inv = 1.f / den;
+  if (act) {
+    float o8[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o8[i] = acc[i] * inv;
+    *reinterpret_cast<uint4*>(out + base) = pack8(o8);
+  }
+  if (l == 0) lse[gid] = mx + __logf(den);
+}
+
+// Backward: dhv[s] += w_s dm ; dhk[s] += dsc_s q/sqrt(HD) ; gq partial sums -> atomics per block.
+template <int G>
+__global__ void __launch_bounds__(256) dread_bwd_kernel(const float* __restrict__ q, const bf16* __restrict__ hk,
+                                                        const bf16* __restrict__ hv, const bf16* __restrict__ dm,
+                                                        const bf16* __restrict__ mo, const float* __restrict__ lse,
+                                                        float* __restrict__ dhk, float* __restrict__ dhv,
+                                                        float* __restrict__ gq, int n, long long MQ, int QH, int HD,
+                                                        float scale) {
+  extern __shared__ float sh_gq[];           // [QH*HD]
+  for (int i = threadIdx.x; i < QH * HD; i += blockDim.x) sh_gq[i] = 0.f;
+  __syncthreads();
+  const long long gid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / G;
+  const int l = threadIdx.x % G;
+  if (gid < MQ) {
+    const unsigned mask = __activemask();
+    const int g = (int)(gid % QH);
+    const bool act = l * 8 < HD;
+    float qv[8], dmf[8], mf[8], gql[8];
+    const long long stride = MQ * HD, base = gid * HD + l * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { qv[i] = act ? q[g * HD + l * 8 + i] : 0.f; gql[i] = 0.f; dmf[i] = 0.f; mf[i] = 0.f; }
+    if (act) {
+      unpack8(*reinterpret_cast<const uint4*>(dm + base), dmf);
+      unpack8(*reinterpret_cast<const uint4*>(mo + base), mf);
+    }
+    float dd = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dd += dmf[i] * mf[i];
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) dd += __shfl_xor_sync(mask, dd, o, G);
+    const float L = lse[gid];
+    for (int s = 0; s < n; ++s) {
+      float kf[8], vf[8];
+      if (act) {
+        unpack8(*reinterpret_cast<const uint4*>(hk + s * stride + base), kf);
+        unpack8(*reinterpret_cast<const uint4*>(hv + s * stride + base), vf);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { kf[i] = 0.f; vf[i] = 0.f; }
+      }
+      float d = 0.f, dv = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { d += qv[i] * kf[i]; dv += dmf[i] * vf[i]; }
+#pragma unroll
+      for (int o = G / 2; o > 0; o >>= 1) {
+        d += __shfl_xor_sync(mask, d, o, G);
+        dv += __shfl_xor_sync(mask, dv, o, G);
+      }
+      const float w = __expf(d * scale - L);
+      const float dsc = w * (dv - dd) * scale;
+      if (act) {
+        float* pk = dhk + s * stride + base;
+        float* pv = dhv + s * stride + base;
+#pragma unroll
+        for (int i = 0; i < 8; i += 4) {
+          float4 a = *reinterpret_cast<float4*>(pk + i), b = *reinterpret_cast<float4*>(pv + i);
+          a.x += dsc * qv[i]; a.y += dsc * qv[i + 1]; a.z += dsc * qv[i + 2]; a.w += dsc * qv[i + 3];
+          b.x += w * dmf[i]; b.y += w * dmf[i + 1]; b.z += w * dmf[i + 2]; b.w += w * dmf[i + 3];
+          *reinterpret_cast<float4*>(pk + i) = a; *reinterpret_cast<float4*>(pv + i) = b;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) gql[i] += dsc * kf[i];
+      }
+    }
+    if (act) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(&sh_gq[g * HD + l * 8 + i], gql[i]);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < QH * HD; i += blockDim.x) {
+    const float v = sh_gq[i];
+    if (v != 0.f) atomicAdd(gq + i, v);
+  }
+}
+
+
+// ----------------------------------------------------------------------------------------------
+// y = LayerNorm(a + b) * w + bias.  One warp per row, NCH 16-byte chunks per lane (N <= 256*NCH).
+// The pre-norm sum is rounded to bf16 first (it is what the backward pass re-reads).
+// ----------------------------------------------------------------------------------------------
+template <int NCH>
+__global__ void __launch_bounds__(256) add_ln_fwd_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b,
+                                                         const float* __restrict__ w, const float* __restrict__ bias,
+                                                         bf16* __restrict__ y, bf16* __restrict__ x,
+                                                         float* __restrict__ mean, float* __restrict__ rstd, int M, int N,
+                                                         float eps) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  float v[NCH][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int col = (lane + 32 * c) * 8;
+    if (col < N) {
+      float fa[8], fb[8];
+      unpack8(*reinterpret_cast<const uint4*>(a + (long long)row * N + col), fa);
+      unpack8(*reinterpret_cast<const uint4*>(b + (long long)row * N + col), fb);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) fa[i] += fb[i];
+      const uint4 packed = pack8(fa);
+      *reinterpret_cast<uint4*>(x + (long long)row * N + col) = packed;
+      unpack8(packed, v[c]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sum += v[c][i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[c][i] = 0.f;
+    }
+  }
+  const float mu = warp_sum(sum) / N;
+  float var = 0.f;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int col = (lane + 32 * c) * 8;
+    if (col < N) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { const float d = v[c][i] - mu; var += d * d; }
+    }
+  }
+  const float rs = rsqrtf(warp_sum(var) / N + eps);
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int col = (lane + 32 * c) * 8;
+    if (col < N) {
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = (v[c][i] - mu) * rs * w[col + i] + bias[col + i];
+      *reinterpret_cast<uint4*>(y + (long long)row * N + col) = pack8(o);
+    }
+  }
+  if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+}
+
+// dx = rstd * (g w - mean(g w) - xhat mean(g w xhat));  gw += sum_rows g xhat;  gb += sum_rows g.
+template <int NCH>
+__global__ void __launch_bounds__(256) add_ln_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                                         const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                         const float* __restrict__ w, bf16* __restrict__ dx,
+                                                         float* __restrict__ gw, float* __restrict__ gb, int M, int N) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float aw[NCH][8], ab[NCH][8];
+#pragma unroll
+  for (int c = 0; c < NCH; ++c)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { aw[c][i] = 0.f; ab[c][i] = 0.f; }
+  for (int row = blockIdx.x * 8 + warp; row < M; row += gridDim.x * 8) {
+    const float mu = mean[row], rs = rstd[row];
+    float g[NCH][8], xh[NCH][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = (lane + 32 * c) * 8;
+      if (col < N) {
+        float xf[8];
+        unpack8(*reinterpret_cast<const uint4*>(dy + (long long)row * N + col), g[c]);
+        unpack8(*reinterpret_cast<const uint4*>(x + (long long)row * N + col), xf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[c][i] = (xf[i] - mu) * rs;
+          aw[c][i] += g[c][i] * xh[c][i];
+          ab[c][i] += g[c][i];
+          g[c][i] *= w[col + i];
+          s1 += g[c][i];
+          s2 += g[c][i] * xh[c][i];
+        }
+      }
+    }
+    s1 = warp_sum(s1) / N;
+    s2 = warp_sum(s2) / N;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = (lane + 32 * c) * 8;
+      if (col < N) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rs * (g[c][i] - s1 - xh[c][i] * s2);
+        *reinterpret_cast<uint4*>(dx + (long long)row * N + col) = pack8(o);
+      }
+    }
+  }
+  // reduce the 8 warps of the block through shared memory, then one atomic per column
+  extern __shared__ float shm[];     // [2][8][N]
+  float* sw = shm;
+  float* sb = shm + 8 * N;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int col = (lane + 32 * c) * 8;
+    if (col < N) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { sw[warp * N + col + i] = aw[c][i]; sb[warp * N + col + i] = ab[c][i]; }
+    }
+  }
+  __syncthreads();
+  for (int col = threadIdx.x; col < N; col += blockDim.x) {
+    float tw = 0.f, tb = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) { tw += sw[r * N + col]; tb += sb[r * N + col]; }
+    atomicAdd(gw + col, tw);
+    atomicAdd(gb + col, tb);
+  }
+}
+
+// gb[n] += sum_m dy[m, n]
+__global__ void __launch_bounds__(256) colsum_kernel(const bf16* __restrict__ dy, float* __restrict__ gb, int M, int N,
+                                                     long long ld) {
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  const int col = (blockIdx.x * 64 + tx) * 2;
+  float a0 = 0.f, a1 = 0.f;
+  if (col < N) {
+    for (int r = blockIdx.y * 64 + ty; r < min(M, (int)(blockIdx.y + 1) * 64); r += 4) {
+      const float2 v = __bfloat1622float2(*reinterpret_cast<const bf2*>(dy + (long long)r * ld + col));
+      a0 += v.x; a1 += v.y;
+    }
+  }
+  __shared__ float sh[2][4][64];
+  sh[0][ty][tx] = a0; sh[1][ty][tx] = a1;
+  __syncthreads();
+  if (ty == 0 && col < N) {
+    float t0 = 0.f, t1 = 0.f;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) { t0 += sh[0][r][tx]; t1 += sh[1][r][tx]; }
+    atomicAdd(gb + col, t0);
+    if (col + 1 < N) atomicAdd(gb + col + 1, t1);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
+// Cross-entropy over bf16 logits, one block per row: nll[row] and (optionally) in-place
+// d logits = (softmax - onehot) * scale, scale read from device memory (grad_scale / #valid targets).
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ float block_reduce(float v, float* sh, bool is_max) {
+  v = is_max ? warp_max(v) : warp_sum(v);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) sh[w] = v;
+  __syncthreads();
+  float r = (threadIdx.x < (blockDim.x >> 5)) ? sh[threadIdx.x] : (is_max ? -INFINITY : 0.f);
+  if (w == 0) r = is_max ? warp_max(r) : warp_sum(r);
+  if (threadIdx.x == 0) sh[32] = r;
+  __syncthreads();
+  return sh[32];
+}
+
+__global__ void __launch_bounds__(256) ce_kernel(bf16* __restrict__ logits, const long long* __restrict__ targets,
+                                                 float* __restrict__ nll, const float* __restrict__ scale_ptr, int V,
+                                                 long long ignore_index, int write_grad) {
+  __shared__ float sh[33];
+  const long long row = blockIdx.x;
+  bf16* L = logits + row * V;
+  const long long tgt = targets[row];
+  const bool valid = tgt != ignore_index;
+  float mx = -INFINITY;
+  for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(L + c), f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mx = fmaxf(mx, f[i]);
+  }
+  mx = block_reduce(mx, sh, true);
+  float se = 0.f;
+  for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(L + c), f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) se += __expf(f[i] - mx);
+  }
+  se = block_reduce(se, sh, false);
+  const float lse = mx + __logf(se);
+  if (threadIdx.x == 0) nll[row] = valid ? lse - __bfloat162float(L[valid ? tgt : 0]) : 0.f;
+  if (!write_grad) return;
+  const float sc = valid ? *scale_ptr : 0.f;
+  const float inv = 1.f / se;
+  for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(L + c), f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float p = __expf(f[i] - mx) * inv;
+      if (valid && c + i == tgt) p -= 1.f;
+      f[i] = p * sc;
+    }
+    *reinterpret_cast<uint4*>(L + c) = pack8(f);
+  }
+}
+
+}  // namespace
+
+extern "C" int loom_rope_store(const void* qkv, const float* cs, const float* sn, void* qkc, void* kcache, void* vcache,
+                               int M, int Tc, int T, int s_off, int QH, int KVH, int HD, cudaStream_t st) {
+  const long long n = (long long)M * (QH + 2 * KVH) * (HD / 2);
+  rope_store_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const bf16*)qkv, cs, sn, (bf16*)qkc, (bf16*)kcache,
+                                                                 (bf16*)vcache, M, Tc, T, s_off, QH, KVH, HD);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int loom_rope_bwd(const void* dq_attn, const void* dqkc, const float* dkc, const float* dvc, const float* cs,
+                             const float* sn, void* dqkv, int M, int Tc, int T, int s_off, int QH, int KVH, int HD,
+                             cudaStream_t st) {
+  const long long n = (long long)M * (QH + 2 * KVH) * (HD / 2);
+  rope_bwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const bf16*)dq_attn, (const bf16*)dqkc, dkc, dvc, cs, sn,
+                                                               (bf16*)dqkv, M, Tc, T, s_off, QH, KVH, HD);
+  return (int)cudaGetLastError();
+}
+
+template <int G>
+static int dread_launch(int bwd, const float* q, const void* hk, const void* hv, void* out, float* lse, const void* dm,
+                        float* dhk, float* dhv, float* gq, int n, long long MQ, int QH, int HD, cudaStream_t st) {
+  const float scale = rsqrtf((float)HD);
+  const long long threads = MQ * G;
+  const unsigned grid = (unsigned)((threads + 255) / 256);
+  if (!bwd) {
+    dread_fwd_kernel<G><<<grid, 256, 0, st>>>(q, (const bf16*)hk, (const bf16*)hv, (bf16*)out, lse, n, MQ, QH, HD, scale);
+  } else {
+    dread_bwd_kernel<G><<<grid, 256, QH * HD * sizeof(float), st>>>(q, (const bf16*)hk, (const bf16*)hv, (const bf16*)dm,
+                                                                    (const bf16*)out, lse, dhk, dhv, gq, n, MQ, QH, HD, scale);
+  }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int loom_dread(int bwd, const float* q, const void* hk, const void* hv, void* out, float* lse, const void* dm,
+                          float* dhk, float* dhv, float* gq, int n, long long MQ, int QH, int HD, cudaStream_t st) {
+  if (HD % 8 || HD > 128) return -1;
+  const int chunks = HD / 8;
+  if (chunks <= 2) return dread_launch<2>(bwd, q, hk, hv, out, lse, dm, dhk, dhv, gq, n, MQ, QH, HD, st);
+  if (chunks <= 4) return dread_launch<4>(bwd, q, hk, hv, out, lse, dm, dhk, dhv, gq, n, MQ, QH, HD, st);
+  if (chunks <= 8) return dread_launch<8>(bwd, q, hk, hv, out, lse, dm, dhk, dhv, gq, n, MQ, QH, HD, st);
+  return dread_launch<16>(bwd, q, hk, hv, out, lse, dm, dhk, dhv, gq, n, MQ, QH, HD, st);
+}
+
+extern "C" int loom_add_ln_fwd(const void* a, const void* b, const float* w, const float* bias, void* y, void* x,
+                               float* mean, float* rstd, int M, int N, float eps, cudaStream_t st) {
+  if (N % 8 || N > 1024) return -1;
+  const unsigned grid = (M + 7) / 8;
+  const int nch = (N + 255) / 256;
+#define LN_F(K) add_ln_fwd_kernel<K><<<grid, 256, 0, st>>>((const bf16*)a, (const bf16*)b, w, bias, (bf16*)y, (bf16*)x, mean, rstd, M, N, eps)
+  if (nch == 1) LN_F(1); else if (nch == 2) LN_F(2); else if (nch == 3) LN_F(3); else LN_F(4);
+#undef LN_F
+  return (int)cudaGetLastError();
+}
+
+extern "C" int loom_add_ln_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const float* w,
+                               void* dx, float* gw, float* gb, int M, int N, cudaStream_t st) {
+  if (N % 8 || N > 1024) return -1;
+  unsigned grid = (M + 7) / 8;
+  if (grid > 592) grid = 592;
+  const int nch = (N + 255) / 256;
+  const size_t shm = 2 * 8 * N * sizeof(float);
+#define LN_B(K) do { if (shm > 48 * 1024) cudaFuncSetAttribute(add_ln_bwd_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shm); \
+    add_ln_bwd_kernel<K><<<grid, 256, shm, st>>>((const bf16*)dy, (const bf16*)x, mean, rstd, w, (bf16*)dx, gw, gb, M, N); } while (0)
+  if (nch == 1) LN_B(1); else if (nch == 2) LN_B(2); else if (nch == 3) LN_B(3); else LN_B(4);
+#undef LN_B
+  return (int)cudaGetLastError();
+}
+
+extern "C" int loom_colsum(const void* dy, float* gb, int M, int N, long long ld, cudaStream_t st) {
+  if (N % 2) return -1;
+  dim3 grid((N / 2 + 63) / 64, (M + 63) / 64);
+  colsum_kernel<<<grid, 256, 0, st>>>((const bf16*)dy, gb, M, N, ld);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int loom_ce(void* logits, const long long* targets, float* nll, const float* scale_ptr, long long M, int V,
+                       long long ignore_index, int write_grad, cudaStream_t st) {
+  if (V % 8) return -1;
+  ce_kernel<<<(unsigned)M, 256, 0, st>>>((bf16*)logits, targets, nll, scale_ptr, V, ignore_index, write_grad);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,510 @@
+// Fused Paraplex core + Tria depth step (forward and backward).
+//
+// One pass per (token, neuron) does everything between the up-projection GEMMs and the down GEMM:
+//   R = X (1 + a p_in) + b_r ;  beta = beta_lin + b_i ;  s0 = sin(pi/2 beta / sqrt(1+beta^2))
+//   z = s0 + w_t * s0[previous token] ;  I = z / sqrt(1+z^2) ;  A = softplus(gate)
+//   O = (R + A I) * A^(m/(sqrt(A)+1)) * sigmoid(A)
+//   T = (I3 + alpha K(tanh(x/rms x))) R_axis, x = (R I, R O, I O) ;  C = N(T C_prev)  (or N(T seed) / N(T))
+//   p_out = <w9, vec(C)>
+// The reference spreads this over an element-wise Paraplex kernel, a reduction kernel, an anchor
+// kernel pair and one Tria kernel per variant (reference kernels/paraplex/paraplex_kernel.cuh:111-298,
+// kernels/tria/tria_step_gate/tria_step_gate_kernel.cuh, tria_init_seed_kernel.cuh), re-reading R, I, O
+// from global memory in between; here they stay in registers.
+//
+// Carriers are stored plane-major: c[k][m][h], k = 0..8 (row-major 3x3 index), bf16, so that every
+// thread's loads are 4-byte bf16x2 accesses that coalesce to full 128-byte lines across a warp.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include "loom_c_api.h"
+
+namespace {
+
+constexpr float HALF_PI = 1.5707963267948966f;
+typedef __nv_bfloat162 bf2;
+
+__device__ __forceinline__ float2 ld2(const __nv_bfloat16* p) { return __bfloat1622float2(*reinterpret_cast<const bf2*>(p)); }
+__device__ __forceinline__ void st2(__nv_bfloat16* p, float a, float b) { *reinterpret_cast<bf2*>(p) = __floats2bfloat162_rn(a, b); }
+
+__device__ __forceinline__ float phase_s0(float beta) { return sinf(HALF_PI * beta * rsqrtf(1.f + beta * beta)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+
+__device__ __forceinline__ float phase_slope(float beta, int secant, float anchor, float s_anchor, float floor_) {
+  const float inv = rsqrtf(1.f + beta * beta);
+  const float x = HALF_PI * beta * inv;
+  const float dx = HALF_PI * inv * inv * inv;
+  if (secant) {
+    const float gap = beta - anchor;
+    if (fabsf(gap) < 1e-4f) return cosf(x) * dx;
+    return (sinf(x) - s_anchor) / gap;
+  }
+  return fmaxf(cosf(x), floor_) * dx;
+}
+
+// T = (I + alpha K(a,b,c)) R_axis laid out row-major
+__device__ __forceinline__ void build_T(int axis, float a, float b, float c, float (&T)[9]) {
+  if (axis == 0) { T[0] = -c; T[1] = -1.f; T[2] = b; T[3] = 1.f; T[4] = -c; T[5] = -a; T[6] = a; T[7] = b; T[8] = 1.f; }
+  else if (axis == 1) { T[0] = 1.f; T[1] = b; T[2] = c; T[3] = c; T[4] = -a; T[5] = -1.f; T[6] = -b; T[7] = 1.f; T[8] = -a; }
+  else { T[0] = -b; T[1] = -c; T[2] = 1.f; T[3] = a; T[4] = 1.f; T[5] = c; T[6] = -1.f; T[7] = a; T[8] = -b; }
+}
+__device__ __forceinline__ void grad_abc(int axis, const float (&g)[9], float& ga, float& gb, float& gc) {
+  if (axis == 0) { ga = -g[5] + g[6]; gb = g[2] + g[7]; gc = -g[0] - g[4]; }
+  else if (axis == 1) { ga = -g[4] - g[8]; gb = g[1] - g[6]; gc = g[2] + g[3]; }
+  else { ga = g[3] + g[7]; gb = -g[0] - g[8]; gc = -g[1] + g[5]; }
+}
+
+struct CoreScalars {
+  float alpha_gate;   // a = 0.25 tanh(raw) (0 when there is no incoming gate value)
+  float powlu_m;
+  float tria_alpha;
+  float floor_;
+  int axis;           // -1: no Tria
+  int secant;
+  int Tc, H, M, B;
+  const float* alpha_ptr;    // device scalars, so no launch argument depends on a host read-back
+  const float* anchor_ptr;
+};
+
+// ----------------------------------------------------------------------------------------------
+// forward: one thread per (m, h-pair)
+// ----------------------------------------------------------------------------------------------
+struct FwdElem {
+  float r, gs, i, o, s0;
+  float C[9];
+  float p;
+};
+
+__device__ __forceinline__ void core_forward_elem(const CoreScalars& S, float x, float pin, int has_pin, float b_r,
+                                                  float glin, int has_glin, float beta, float prev, float w_t,
+                                                  const float* cprev, const float* seed, const float* w9, FwdElem& E) {
+  E.r = has_pin ? x * (1.f + S.alpha_gate * pin) + b_r : x + b_r;
+  E.gs = has_glin ? glin : E.r;
+  E.s0 = phase_s0(beta);
+  const float z = E.s0 + w_t * prev;
+  E.i = z * rsqrtf(1.f + z * z);
+  const float A = fmaxf(softplus_f(E.gs), 1e-12f);
+  const float P = E.r + A * E.i;
+  const float G = __powf(A, S.powlu_m / (sqrtf(A) + 1.f)) * sigmoid_f(A);
+  E.o = P * G;
+  if (S.axis >= 0) {
+    const float x0 = E.r * E.i, x1 = E.r * E.o, x2 = E.i * E.o;
+    const float n3 = rsqrtf((x0 * x0 + x1 * x1 + x2 * x2) * (1.f / 3.f) + 1e-6f);
+    const float a = S.tria_alpha * tanhf(x0 * n3), b = S.tria_alpha * tanhf(x1 * n3), c = S.tria_alpha * tanhf(x2 * n3);
+    float T[9], pre[9];
+    build_T(S.axis, a, b, c, T);
+    const float* R = cprev ? cprev : seed;
+    if (R) {
+#pragma unroll
+      for (int rr = 0; rr < 3; ++rr)
+#pragma unroll
+        for (int cc = 0; cc < 3; ++cc)
+          pre[rr * 3 + cc] = T[rr * 3] * R[cc] + T[rr * 3 + 1] * R[3 + cc] + T[rr * 3 + 2] * R[6 + cc];
+    } else {
+#pragma unroll
+      for (int k = 0; k < 9; ++k) pre[k] = T[k];
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 9; ++k) ss += pre[k] * pre[k];
+    const float inv = rsqrtf(ss * (1.f / 9.f) + 1e-6f);
+    float p = 0.f;
+#pragma unroll
+    for (int k = 0; k < 9; ++k) { E.C[k] = pre[k] * inv; if (w9) p += w9[k] * E.C[k]; }
+    E.p = p;
+  }
+}
+
+__global__ void __launch_bounds__(256) ffn_core_fwd_kernel(
+    CoreScalars S_in, const __nv_bfloat16* __restrict__ x_real, const __nv_bfloat16* __restrict__ p_in,
+    const float* __restrict__ b_real, const __nv_bfloat16* __restrict__ gate_lin,
+    const __nv_bfloat16* __restrict__ beta_lin, const float* __restrict__ b_imag, const float* __restrict__ w_trace,
+    const float* __restrict__ trace_in, const uint8_t* __restrict__ reset, const __nv_bfloat16* __restrict__ c_prev,
+    const float* __restrict__ seed, const uint8_t* __restrict__ seed_valid, const float* __restrict__ gate_w,
+    __nv_bfloat16* __restrict__ o_out, __nv_bfloat16* __restrict__ c_out, __nv_bfloat16* __restrict__ p_out,
+    float* __restrict__ trace_out, float* __restrict__ beta_sq_sum) {
+  CoreScalars S = S_in;
+  S.alpha_gate = S.alpha_ptr ? *S.alpha_ptr : 0.f;
+  const int H = S.H, Hp = H >> 1;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  float bsq = 0.f;
+  if (idx < (long long)S.M * Hp) {
+    const int m = (int)(idx / Hp), h = (int)(idx % Hp) * 2;
+    const int b = m / S.Tc, t = m % S.Tc;
+    const long long e = (long long)m * H + h;
+    const float2 x = ld2(x_real + e);
+    float2 pin = make_float2(0.f, 0.f), gl = make_float2(0.f, 0.f);
+    if (p_in) pin = ld2(p_in + e);
+    if (gate_lin) gl = ld2(gate_lin + e);
+    const float2 bl = ld2(beta_lin + e);
+    const float bi0 = b_imag[h], bi1 = b_imag[h + 1];
+    const float beta0 = bl.x + bi0, beta1 = bl.y + bi1;
+    bsq = beta0 * beta0 + beta1 * beta1;
+    float prev0 = 0.f, prev1 = 0.f;
+    const bool rs = reset && reset[m];
+    if (!rs) {
+      if (t == 0) { if (trace_in) { prev0 = trace_in[(long long)b * H + h]; prev1 = trace_in[(long long)b * H + h + 1]; } }
+      else { const float2 bp = ld2(beta_lin + e - H); prev0 = phase_s0(bp.x + bi0); prev1 = phase_s0(bp.y + bi1); }
+    }
+    float w9[9];
+    const bool has_w = gate_w != nullptr;
+    if (has_w) {
+#pragma unroll
+      for (int k = 0; k < 9; ++k) w9[k] = gate_w[k];
+    }
+    float cp0[9], cp1[9];
+    const float *r0 = nullptr, *r1 = nullptr, *sd0 = nullptr, *sd1 = nullptr;
+    const long long plane = (long long)S.M * H;
+    if (S.axis >= 0) {
+      if (c_prev) {
+#pragma unroll
+        for (int k = 0; k < 9; ++k) { float2 v = ld2(c_prev + k * plane + e); cp0[k] = v.x; cp1[k] = v.y; }
+        r0 = cp0; r1 = cp1;
+      } else if (seed && t == 0 && seed_valid[b]) {
+        const float* sp = seed + ((long long)b * H + h) * 9;
+#pragma unroll
+        for (int k = 0; k < 9; ++k) { cp0[k] = sp[k]; cp1[k] = sp[9 + k]; }
+        sd0 = cp0; sd1 = cp1;
+      }
+    }
+    FwdElem E0, E1;
+    core_forward_elem(S, x.x, pin.x, p_in != nullptr, b_real[h], gl.x, gate_lin != nullptr, beta0, prev0, w_trace[h],
+                      r0, sd0, has_w ? w9 : nullptr, E0);
+    core_forward_elem(S, x.y, pin.y, p_in != nullptr, b_real[h + 1], gl.y, gate_lin != nullptr, beta1, prev1,
+                      w_trace[h + 1], r1, sd1, has_w ? w9 : nullptr, E1);
+    st2(o_out + e, E0.o, E1.o);
+    if (t == S.Tc - 1) { trace_out[(long long)b * H + h] = E0.s0; trace_out[(long long)b * H + h + 1] = E1.s0; }
+    if (S.axis >= 0) {
+#pragma unroll
+      for (int k = 0; k < 9; ++k) st2(c_out + k * plane + e, E0.C[k], E1.C[k]);
+      if (has_w) st2(p_out + e, E0.p, E1.p);
+    }
+  }
+  // sum of beta^2 for the anchor statistic
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) bsq += __shfl_xor_sync(0xffffffffu, bsq, o);
+  __shared__ float sh[8];
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = bsq;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int i = 0; i < 8; ++i) tot += sh[i];
+    atomicAdd(beta_sq_sum, tot);
+  }
+}
+
+
+// ----------------------------------------------------------------------------------------------
+// backward, pass A: everything except the phase slope (which needs the next token's g_z)
+// ----------------------------------------------------------------------------------------------
+struct BwdElem {
+  float dx, dpin, dgl, gz, gr, dwt, dalpha;
+  float dR[9];
+  float dw9[9];
+};
+
+__device__ __forceinline__ void core_backward_elem(const CoreScalars& S, float x, float pin, int has_pin, float b_r,
+                                                   float glin, int has_glin, float beta, float prev, float w_t,
+                                                   const float* R, const float* w9, float dO, const float* dC,
+                                                   float dpo, int has_dpo, BwdElem& E) {
+  const float r = has_pin ? x * (1.f + S.alpha_gate * pin) + b_r : x + b_r;
+  const float gs = has_glin ? glin : r;
+  const float s0 = phase_s0(beta);
+  const float z = s0 + w_t * prev;
+  const float zi = rsqrtf(1.f + z * z);
+  const float i = z * zi;
+  const float sp = softplus_f(gs);
+  const float A = fmaxf(sp, 1e-12f);
+  const float sqA = sqrtf(A);
+  const float ex = S.powlu_m / (sqA + 1.f);
+  const float sig = sigmoid_f(A);
+  const float G = __powf(A, ex) * sig;
+  const float P = r + A * i;
+  const float o = P * G;
+  float g_r = 0.f, g_i = 0.f, g_o = dO;
+#pragma unroll
+  for (int k = 0; k < 9; ++k) { E.dR[k] = 0.f; E.dw9[k] = 0.f; }
+  if (S.axis >= 0 && (dC != nullptr || has_dpo)) {
+    const float x0 = r * i, x1 = r * o, x2 = i * o;
+    const float n3 = rsqrtf((x0 * x0 + x1 * x1 + x2 * x2) * (1.f / 3.f) + 1e-6f);
+    const float y0 = x0 * n3, y1 = x1 * n3, y2 = x2 * n3;
+    const float t0 = tanhf(y0), t1 = tanhf(y1), t2 = tanhf(y2);
+    float T[9], pre[9], C[9], gC[9], gpre[9], gT[9];
+    build_T(S.axis, S.tria_alpha * t0, S.tria_alpha * t1, S.tria_alpha * t2, T);
+    if (R) {
+#pragma unroll
+      for (int rr = 0; rr < 3; ++rr)
+#pragma unroll
+        for (int cc = 0; cc < 3; ++cc)
+          pre[rr * 3 + cc] = T[rr * 3] * R[cc] + T[rr * 3 + 1] * R[3 + cc] + T[rr * 3 + 2] * R[6 + cc];
+    } else {
+#pragma unroll
+      for (int k = 0; k < 9; ++k) pre[k] = T[k];
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 9; ++k) ss += pre[k] * pre[k];
+    const float inv = rsqrtf(ss * (1.f / 9.f) + 1e-6f);
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < 9; ++k) {
+      C[k] = pre[k] * inv;
+      gC[k] = (dC ? dC[k] : 0.f) + (has_dpo ? dpo * w9[k] : 0.f);
+      if (has_dpo) E.dw9[k] = dpo * C[k];
+      dot += gC[k] * C[k];
+    }
+    dot *= (1.f / 9.f);
+#pragma unroll
+    for (int k = 0; k < 9; ++k) gpre[k] = (gC[k] - C[k] * dot) * inv;
+    if (R) {
+#pragma unroll
+      for (int rr = 0; rr < 3; ++rr)
+#pragma unroll
+        for (int cc = 0; cc < 3; ++cc) {
+          gT[rr * 3 + cc] = gpre[rr * 3] * R[cc * 3] + gpre[rr * 3 + 1] * R[cc * 3 + 1] + gpre[rr * 3 + 2] * R[cc * 3 + 2];
+          E.dR[rr * 3 + cc] = T[rr] * gpre[cc] + T[3 + rr] * gpre[3 + cc] + T[6 + rr] * gpre[6 + cc];
+        }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 9; ++k) gT[k] = gpre[k];
+    }
+    float ga, gb, gc;
+    grad_abc(S.axis, gT, ga, gb, gc);
+    const float gy0 = ga * S.tria_alpha * (1.f - t0 * t0), gy1 = gb * S.tria_alpha * (1.f - t1 * t1),
+                gy2 = gc * S.tria_alpha * (1.f - t2 * t2);
+    const float doty = (gy0 * y0 + gy1 * y1 + gy2 * y2) * (1.f / 3.f);
+    const float gx0 = (gy0 - y0 * doty) * n3, gx1 = (gy1 - y1 * doty) * n3, gx2 = (gy2 - y2 * doty) * n3;
+    g_r += gx0 * i + gx1 * o;
+    g_i += gx0 * r + gx2 * o;
+    g_o += gx1 * r + gx2 * i;
+  }
+  const float gP = g_o * G, gG = g_o * P;
+  g_r += gP;
+  g_i += gP * A;
+  float gA = gP * i;
+  if (sp >= 1e-12f) {
+    const float de = -S.powlu_m / ((sqA + 1.f) * (sqA + 1.f)) * (0.5f / sqA);
+    gA += gG * G * (ex / A + de * __logf(A) + (1.f - sig));
+  } else {
+    gA = 0.f;
+  }
+  const float g_gs = gA * sigmoid_f(gs);
+  E.gz = g_i * zi * zi * zi;
+  E.dwt = E.gz * prev;
+  if (has_glin) E.dgl = g_gs; else { g_r += g_gs; E.dgl = 0.f; }
+  E.gr = g_r;
+  E.dx = has_pin ? g_r * (1.f + S.alpha_gate * pin) : g_r;
+  E.dpin = has_pin ? g_r * x * S.alpha_gate : 0.f;
+  E.dalpha = has_pin ? g_r * x * pin : 0.f;
+}
+
+constexpr int TILE_ROWS = 32;
+
+__global__ void __launch_bounds__(256) ffn_core_bwd_a_kernel(
+    CoreScalars S_in, const __nv_bfloat16* __restrict__ x_real, const __nv_bfloat16* __restrict__ p_in,
+    const float* __restrict__ b_real, const __nv_bfloat16* __restrict__ gate_lin,
+    const __nv_bfloat16* __restrict__ beta_lin, const float* __restrict__ b_imag, const float* __restrict__ w_trace,
+    const float* __restrict__ trace_in, const uint8_t* __restrict__ reset, const __nv_bfloat16* __restrict__ c_prev,
+    const float* __restrict__ seed, const uint8_t* __restrict__ seed_valid, const float* __restrict__ gate_w,
+    const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ d_c, const __nv_bfloat16* __restrict__ d_pout,
+    __nv_bfloat16* __restrict__ dx_real, __nv_bfloat16* __restrict__ dp_in, __nv_bfloat16* __restrict__ dgate_lin,
+    float* __restrict__ gz, __nv_bfloat16* __restrict__ dc_prev, float* __restrict__ dseed, float* __restrict__ dtrace_in,
+    float* __restrict__ g_b_real, float* __restrict__ g_w_trace, float* __restrict__ g_scalars /* [0]=alpha, [1..9]=w9 */) {
+  CoreScalars S = S_in;
+  S.alpha_gate = S.alpha_ptr ? *S.alpha_ptr : 0.f;
+  const int H = S.H;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  const int h = (blockIdx.x * 64 + tx) * 2;
+  const bool col_ok = h < H;
+  const long long plane = (long long)S.M * H;
+  float w9[9];
+  const bool has_w = gate_w != nullptr && d_pout != nullptr;
+  if (has_w) {
+#pragma unroll
+    for (int k = 0; k < 9; ++k) w9[k] = gate_w[k];
+  }
+  float acc_br0 = 0.f, acc_br1 = 0.f, acc_wt0 = 0.f, acc_wt1 = 0.f, acc_alpha = 0.f;
+  float acc_w9[9];
+#pragma unroll
+  for (int k = 0; k < 9; ++k) acc_w9[k] = 0.f;
+  if (col_ok) {
+    const float br0 = b_real[h], br1 = b_real[h + 1], bi0 = b_imag[h], bi1 = b_imag[h + 1];
+    const float wt0 = w_trace[h], wt1 = w_trace[h + 1];
+    for (int j = 0; j < TILE_ROWS / 4; ++j) {
+      const int m = blockIdx.y * TILE_ROWS + ty + 4 * j;
+      if (m >= S.M) break;
+      const int b = m / S.Tc, t = m % S.Tc;
+      const long long e = (long long)m * H + h;
+      const float2 x = ld2(x_real + e);
+      float2 pin = make_float2(0.f, 0.f), gl = make_float2(0.f, 0.f), dpo = make_float2(0.f, 0.f);
+      if (p_in) pin = ld2(p_in + e);
+      if (gate_lin) gl = ld2(gate_lin + e);
+      if (has_w) dpo = ld2(d_pout + e);
+      const float2 bl = ld2(beta_lin + e);
+      const float2 dO = ld2(d_o + e);
+      float prev0 = 0.f, prev1 = 0.f;
+      const bool rs = reset && reset[m];
+      if (!rs) {
+        if (t == 0) { if (trace_in) { prev0 = trace_in[(long long)b * H + h]; prev1 = trace_in[(long long)b * H + h + 1]; } }
+        else { const float2 bp = ld2(beta_lin + e - H); prev0 = phase_s0(bp.x + bi0); prev1 = phase_s0(bp.y + bi1); }
+      }
+      float R0[9], R1[9], dC0[9], dC1[9];
+      const float *r0 = nullptr, *r1 = nullptr;
+      bool from_seed = false;
+      if (S.axis >= 0) {
+        if (c_prev) {
+#pragma unroll
+          for (int k = 0; k < 9; ++k) { float2 v = ld2(c_prev + k * plane + e); R0[k] = v.x; R1[k] = v.y; }
+          r0 = R0; r1 = R1;
+        } else if (seed && t == 0 && seed_valid[b]) {
+          const float* sp = seed + ((long long)b * H + h) * 9;
+#pragma unroll
+          for (int k = 0; k < 9; ++k) { R0[k] = sp[k]; R1[k] = sp[9 + k]; }
+          r0 = R0; r1 = R1; from_seed = true;
+        }
+        if (d_c) {
+#pragma unroll
+          for (int k = 0; k < 9; ++k) { float2 v = ld2(d_c + k * plane + e); dC0[k] = v.x; dC1[k] = v.y; }
+        }
+      }
+      BwdElem E0, E1;
+      core_backward_elem(S, x.x, pin.x, p_in != nullptr, br0, gl.x, gate_lin != nullptr, bl.x + bi0, prev0, wt0, r0,
+                         has_w ? w9 : nullptr, dO.x, d_c ? dC0 : nullptr, dpo.x, has_w, E0);
+      core_backward_elem(S, x.y, pin.y, p_in != nullptr, br1, gl.y, gate_lin != nullptr, bl.y + bi1, prev1, wt1, r1,
+                         has_w ? w9 : nullptr, dO.y, d_c ? dC1 : nullptr, dpo.y, has_w, E1);
+      st2(dx_real + e, E0.dx, E1.dx);
+      if (dp_in) st2(dp_in + e, E0.dpin, E1.dpin);
+      if (dgate_lin) st2(dgate_lin + e, E0.dgl, E1.dgl);
+      *reinterpret_cast<float2*>(gz + e) = make_float2(E0.gz, E1.gz);
+      if (c_prev && dc_prev) {
+#pragma unroll
+        for (int k = 0; k < 9; ++k) st2(dc_prev + k * plane + e, E0.dR[k], E1.dR[k]);
+      } else if (from_seed && dseed) {
+        float* sp = dseed + ((long long)b * H + h) * 9;
+#pragma unroll
+        for (int k = 0; k < 9; ++k) { sp[k] = E0.dR[k]; sp[9 + k] = E1.dR[k]; }
+      }
+      if (t == 0 && dtrace_in) {
+        dtrace_in[(long long)b * H + h] = rs ? 0.f : E0.gz * wt0;
+        dtrace_in[(long long)b * H + h + 1] = rs ? 0.f : E1.gz * wt1;
+      }
+      acc_br0 += E0.gr; acc_br1 += E1.gr; acc_wt0 += E0.dwt; acc_wt1 += E1.dwt;
+      acc_alpha += E0.dalpha + E1.dalpha;
+#pragma unroll
+      for (int k = 0; k < 9; ++k) acc_w9[k] += E0.dw9[k] + E1.dw9[k];
+    }
+  }
+  // column sums: reduce the four row-groups of the block, then one atomic per column
+  __shared__ float sh[4][4][64];
+  sh[0][ty][tx] = acc_br0; sh[1][ty][tx] = acc_br1; sh[2][ty][tx] = acc_wt0; sh[3][ty][tx] = acc_wt1;
+  __syncthreads();
+  if (ty == 0 && col_ok) {
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) { a0 += sh[0][r][tx]; a1 += sh[1][r][tx]; a2 += sh[2][r][tx]; a3 += sh[3][r][tx]; }
+    atomicAdd(g_b_real + h, a0); atomicAdd(g_b_real + h + 1, a1);
+    atomicAdd(g_w_trace + h, a2); atomicAdd(g_w_trace + h + 1, a3);
+  }
+  // scalar sums
+  float sc[10];
+  sc[0] = acc_alpha;
+#pragma unroll
+  for (int k = 0; k < 9; ++k) sc[1 + k] = acc_w9[k];
+  __shared__ float shs[8][10];
+#pragma unroll
+  for (int k = 0; k < 10; ++k) {
+    float v = sc[k];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) shs[threadIdx.x >> 5][k] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < 10) {
+    float v = 0.f;
+    for (int w = 0; w < 8; ++w) v += shs[w][threadIdx.x];
+    if (v != 0.f) atomicAdd(g_scalars + threadIdx.x, v);
+  }
+}
+
+// backward, pass B: dbeta = (g_z[m] + w_t g_z[m+1] (same row, no reset) + dtrace_out at the last token) * slope
+__global__ void __launch_bounds__(256) ffn_core_bwd_b_kernel(
+    CoreScalars S, const float* __restrict__ gz, const __nv_bfloat16* __restrict__ beta_lin,
+    const float* __restrict__ b_imag, const float* __restrict__ w_trace, const uint8_t* __restrict__ reset,
+    const float* __restrict__ dtrace_out, __nv_bfloat16* __restrict__ dbeta, float* __restrict__ g_b_imag) {
+  const int H = S.H;
+  const float anchor = (S.secant && S.anchor_ptr) ? *S.anchor_ptr : 0.f;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  const int h = (blockIdx.x * 64 + tx) * 2;
+  const bool col_ok = h < H;
+  const float s_anchor = S.secant ? phase_s0(anchor) : 0.f;
+  float acc0 = 0.f, acc1 = 0.f;
+  if (col_ok) {
+    const float bi0 = b_imag[h], bi1 = b_imag[h + 1], wt0 = w_trace[h], wt1 = w_trace[h + 1];
+    for (int j = 0; j < TILE_ROWS / 4; ++j) {
+      const int m = blockIdx.y * TILE_ROWS + ty + 4 * j;
+      if (m >= S.M) break;
+      const int b = m / S.Tc, t = m % S.Tc;
+      const long long e = (long long)m * H + h;
+      float2 g = *reinterpret_cast<const float2*>(gz + e);
+      if (t < S.Tc - 1) {
+        if (!(reset && reset[m + 1])) {
+          const float2 gn = *reinterpret_cast<const float2*>(gz + e + H);
+          g.x += wt0 * gn.x; g.y += wt1 * gn.y;
+        }
+      } else if (dtrace_out) {
+        g.x += dtrace_out[(long long)b * H + h]; g.y += dtrace_out[(long long)b * H + h + 1];
+      }
+      const float2 bl = ld2(beta_lin + e);
+      const float d0 = g.x * phase_slope(bl.x + bi0, S.secant, anchor, s_anchor, S.floor_);
+      const float d1 = g.y * phase_slope(bl.y + bi1, S.secant, anchor, s_anchor, S.floor_);
+      st2(dbeta + e, d0, d1);
+      acc0 += d0; acc1 += d1;
+    }
+  }
+  __shared__ float sh[2][4][64];
+  sh[0][ty][tx] = acc0; sh[1][ty][tx] = acc1;
+  __syncthreads();
+  if (ty == 0 && col_ok) {
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) { a0 += sh[0][r][tx]; a1 += sh[1][r][tx]; }
+    atomicAdd(g_b_imag + h, a0); atomicAdd(g_b_imag + h + 1, a1);
+  }
+}
+
+CoreScalars make_scalars(const LoomFfnCore* a) {
+  CoreScalars S;
+  S.alpha_gate = 0.f; S.alpha_ptr = a->alpha_gate; S.anchor_ptr = a->anchor; S.powlu_m = a->powlu_m; S.tria_alpha = a->tria_alpha; S.floor_ = a->phase_floor;
+  S.axis = a->axis; S.secant = a->secant; S.Tc = a->Tc; S.H = a->H; S.M = a->B * a->Tc; S.B = a->B;
+  return S;
+}
+
+}  // namespace
+
+extern "C" int loom_ffn_core_fwd(const LoomFfnCore* a, cudaStream_t stream) {
+  if (a->H % 2) return -1;
+  CoreScalars S = make_scalars(a);
+  const long long n = (long long)S.M * (S.H / 2);
+  ffn_core_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
+      S, (const __nv_bfloat16*)a->x_real, (const __nv_bfloat16*)a->p_in, a->b_real, (const __nv_bfloat16*)a->gate_lin,
+      (const __nv_bfloat16*)a->beta_lin, a->b_imag, a->w_trace, a->trace_in, a->reset, (const __nv_bfloat16*)a->c_prev,
+      a->seed, a->seed_valid, a->gate_w, (__nv_bfloat16*)a->o_out, (__nv_bfloat16*)a->c_out, (__nv_bfloat16*)a->p_out,
+      a->trace_out, a->beta_sq_sum);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int loom_ffn_core_bwd(const LoomFfnCore* a, cudaStream_t stream) {
+  if (a->H % 2) return -1;
+  CoreScalars S = make_scalars(a);
+  dim3 grid((S.H / 2 + 63) / 64, (S.M + TILE_ROWS - 1) / TILE_ROWS);
+  ffn_core_bwd_a_kernel<<<grid, 256, 0, stream>>>(
+      S, (const __nv_bfloat16*)a->x_real, (const __nv_bfloat16*)a->p_in, a->b_real, (const __nv_bfloat16*)a->gate_lin,
+      (const __nv_bfloat16*)a->beta_lin, a->b_imag, a->w_trace, a->trace_in, a->reset, (const __nv_bfloat16*)a->c_prev,
+      a->seed, a->seed_valid, a->gate_w, (const __nv_bfloat16*)a->d_o, (const __nv_bfloat16*)a->d_c,
+      (const __nv_bfloat16*)a->d_pout, (__nv_bfloat16*)a->dx_real, (__nv_bfloat16*)a->dp_in, (__nv_bfloat16*)a->dgate_lin,
+      a->gz, (__nv_bfloat16*)a->dc_prev, a->dseed, a->dtrace_in, a->g_b_real, a->g_w_trace, a->g_scalars);
+  ffn_core_bwd_b_kernel<<<grid, 256, 0, stream>>>(S, a->gz, (const __nv_bfloat16*)a->beta_lin, a->b_imag, a->w_trace,
+                                                  a->reset, a->dtrace_out, (__nv_bfloat16*)a->dbeta, a->g_b_imag);
+  return (int)cudaGetLastError();
+}

@@ -47,6 +47,59 @@ int loom_atom_flat(float* p, const float* g, float* m, float* v, void* shadow_bf
                    const float* stats, const float* hyper, float* atom_out, long long nblk, cudaStream_t stream);
 int loom_cast_shadow(const float* p, void* shadow_bf16, long long n, cudaStream_t stream);
 
+// ---- fused Paraplex core + Tria step (ffn_core.cu) ----
+// Activations are bf16 [M, H] with M = B*Tc rows ordered (b, t); carriers are bf16 planes [9][M][H].
+// Null pointers switch optional inputs/outputs off.  Gradient accumulators (g_*) are fp32 and are
+// added to atomically.
+typedef struct {
+  int B, Tc, H;
+  int axis;                 // Tria axis 0..2, or -1 when Tria is off
+  int secant;               // phase slope mode
+  float powlu_m, tria_alpha, phase_floor;
+  const float* alpha_gate;  // device scalar 0.25*tanh(raw) or null (no incoming gate value)
+  const float* anchor;      // device scalar (secant mode)
+  const void* x_real; const void* p_in; const float* b_real;
+  const void* gate_lin;     // null: the gate reads R itself
+  const void* beta_lin; const float* b_imag; const float* w_trace;
+  const float* trace_in;    // [B,H] or null
+  const uint8_t* reset;     // [M] or null
+  const void* c_prev;       // planes or null
+  const float* seed;        // [B,H,9] or null
+  const uint8_t* seed_valid;
+  const float* gate_w;      // [9] soft-maxed, or null
+  // forward outputs
+  void* o_out; void* c_out; void* p_out; float* trace_out; float* beta_sq_sum;
+  // backward inputs
+  const void* d_o; const void* d_c; const void* d_pout; const float* dtrace_out;
+  // backward outputs
+  void* dx_real; void* dp_in; void* dgate_lin; void* dbeta; float* gz; void* dc_prev; float* dseed; float* dtrace_in;
+  float* g_b_real; float* g_w_trace; float* g_b_imag; float* g_scalars;   // g_scalars: [0] d alpha_gate, [1..9] d gate_w
+} LoomFfnCore;
+int loom_ffn_core_fwd(const LoomFfnCore* a, cudaStream_t stream);
+int loom_ffn_core_bwd(const LoomFfnCore* a, cudaStream_t stream);
+
+// ---- bandwidth-bound kernels (elementwise.cu) ----
+int loom_rope_store(const void* qkv, const float* cs, const float* sn, void* qkc, void* kcache, void* vcache, int M,
+                    int Tc, int T, int s_off, int QH, int KVH, int HD, cudaStream_t st);
+int loom_rope_bwd(const void* dq_attn, const void* dqkc, const float* dkc, const float* dvc, const float* cs,
+                  const float* sn, void* dqkv, int M, int Tc, int T, int s_off, int QH, int KVH, int HD, cudaStream_t st);
+int loom_dread(int bwd, const float* q, const void* hk, const void* hv, void* out, float* lse, const void* dm, float* dhk,
+               float* dhv, float* gq, int n, long long MQ, int QH, int HD, cudaStream_t st);
+int loom_add_ln_fwd(const void* a, const void* b, const float* w, const float* bias, void* y, void* x, float* mean,
+                    float* rstd, int M, int N, float eps, cudaStream_t st);
+int loom_add_ln_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const float* w, void* dx,
+                    float* gw, float* gb, int M, int N, cudaStream_t st);
+int loom_colsum(const void* dy, float* gb, int M, int N, long long ld, cudaStream_t st);
+int loom_ce(void* logits, const long long* targets, float* nll, const float* scale_ptr, long long M, int V,
+            long long ignore_index, int write_grad, cudaStream_t st);
+
+// ---- temporal carry endpoint + PolARM (temporal.cu) ----
+int loom_temporal_fwd(const void* depth, const uint8_t* reset, const float* state_in, const uint8_t* fired, float beta,
+                      float* state_out, float* raw_out, float* ckpt, int B, int Tc, int H, cudaStream_t st);
+int loom_temporal_bwd(const void* depth, const uint8_t* reset, const float* state_in, const uint8_t* fired, float beta,
+                      const float* raw, const float* ckpt, const float* dstate, void* ddepth, float* dstate_in, int B,
+                      int Tc, int H, cudaStream_t st);
+
 #ifdef __cplusplus
 }
 #endif

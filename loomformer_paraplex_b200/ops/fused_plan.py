@@ -136,8 +136,8 @@ class FusedPlan:
                 tape["local_reset"] = local_reset
                 if e != T or (e - 1) in cut_set:
                     fired = fire[:, e - 1] if (e - 1) in cut_set else None
-                    temporal = K.temporal_fwd(tape["depth"].view(B, e - s, d.hidden, 9), local_reset, temporal,
-                                              fired, m.d_polarm_beta)
+                    temporal, tape["t_aux"] = K.temporal_fwd(tape["depth"], B, e - s, d.hidden, local_reset, temporal,
+                                                             fired, m.d_polarm_beta)
                     tape["has_endpoint"], tape["fired"] = True, fired
                     if fired is not None:
                         tape["key_index"] = len(keys)
@@ -187,9 +187,8 @@ class FusedPlan:
                     gk = dkeys[:, tape["key_index"]]
                     dstate = gk if dstate is None else dstate + gk
                 if dstate is not None:
-                    ddepth, dprev = K.temporal_bwd(dstate, tape["depth"].view(B, e - s, d.hidden, 9),
-                                                   tape["local_reset"], tape["temporal_in"], tape["fired"],
-                                                   m.d_polarm_beta)
+                    ddepth, dprev = K.temporal_bwd(dstate, tape["depth"], B, e - s, d.hidden, tape["local_reset"],
+                                                   tape["temporal_in"], tape["fired"], m.d_polarm_beta, tape["t_aux"])
                     dtemporal = dprev
                 else:
                     dtemporal = None
@@ -352,7 +351,7 @@ class FusedPlan:
         dhk = torch.zeros(hist_k.shape, dtype=torch.float32, device=dev)
         dhv = torch.zeros(hist_v.shape, dtype=torch.float32, device=dev)
         dh = dh_out.reshape(M, N).to(self.adt)
-        dc = None if ddepth is None else ddepth.reshape(M, d.hidden, 9)
+        dc = ddepth                      # carrier-layout gradient (opaque to the plan)
         dp_out = None
         dseed = None
         dtraces_in: List[Optional[torch.Tensor]] = [None] * L
@@ -373,15 +372,18 @@ class FusedPlan:
             do = K.linear_dgrad(df, self.w(ffn.w2.weight))
             # --- Paraplex core + Tria
             core = t["core"]
+            core["g_b_real"], core["g_b_imag"] = self.g(ffn.w1_real.bias), self.g(ffn.w1_imag_bias)
+            core["g_w_trace"] = self.g(ffn.w1_imag_trace)
             gr = K.ffn_core_bwd(d, core, do, dc, dp_out, None if dtraces_out is None else dtraces_out[bi])
             dx_real, dbeta = gr["d_x_real"].to(self.adt), gr["d_beta_lin"].to(self.adt)
             dtraces_in[bi] = gr.get("d_trace_in")
             dc, dp_out = gr.get("d_c_prev"), gr.get("d_p_in")
             if gr.get("d_seed") is not None:
                 dseed = gr["d_seed"]
-            self.g(ffn.w1_real.bias).add_(gr["d_b_real"])
-            self.g(ffn.w1_imag_bias).add_(gr["d_b_imag"])
-            self.g(ffn.w1_imag_trace).add_(gr["d_w_trace"])
+            if gr.get("d_b_real") is not None:          # the native kernel accumulates these itself
+                core["g_b_real"].add_(gr["d_b_real"])
+                core["g_b_imag"].add_(gr["d_b_imag"])
+                core["g_w_trace"].add_(gr["d_w_trace"])
             if gr.get("d_alpha_gate") is not None and ffn.identity_gate.raw_alpha.requires_grad:
                 ig = ffn.identity_gate
                 self.g(ig.raw_alpha).add_(gr["d_alpha_gate"] * ig.alpha_max * (1.0 - torch.tanh(ig.raw_alpha.data) ** 2))
@@ -420,8 +422,8 @@ class FusedPlan:
             K.linear_wgrad(da, qkc[:, 2].reshape(M, N), self.g(blk.attn.o.weight))
             dqkc[:, 2] = dqkc[:, 2] + K.linear_dgrad(da, self.w(blk.attn.o.weight)).view(M, d.qh, d.hd)
             dq_attn = K.attn_bwd(d, dqkc, qkc, kc[bi], vc[bi], t["lse"], s, e, seg, dkc[bi], dvc[bi])
-            dq = dq_attn.reshape(B, Tc, d.qh, d.hd).float() + dqkc[:, 0].reshape(B, Tc, d.qh, d.hd).float()
-            dqkv = K.rope_bwd(d, dq, dkc[bi][:, s:e], dvc[bi][:, s:e], tape["cos"], tape["sin"], self.adt).view(M, -1)
+            dqkv = K.rope_bwd(d, dq_attn.reshape(B, Tc, d.qh, d.hd), dqkc, dkc[bi], dvc[bi], s, e, tape["cos"],
+                              tape["sin"], self.adt).view(M, -1)
             K.linear_wgrad(dqkv, t["h_in"], self.g(blk.attn.qkv_weight))
             dh = K.linear_dgrad(dqkv, self.w(blk.attn.qkv_weight))
         dh = dh + self._project_state_bwd(tape["h_emb"], 0, dhk, dhv, tape["emb_l"], "emb")

@@ -182,3 +182,209 @@ class CudaKernels(TorchKernels):
             shared(3 * hd, u, du)
             per_head(3 * hd + n, m2v, dm2)
         return dqkc, du, dm2
+
+
+def _bf16c(t: torch.Tensor) -> torch.Tensor:
+    return t if (t.dtype == torch.bfloat16 and t.is_contiguous()) else t.to(torch.bfloat16).contiguous()
+
+
+def _f32c(t: torch.Tensor) -> torch.Tensor:
+    return t if (t.dtype == torch.float32 and t.is_contiguous()) else t.float().contiguous()
+
+
+def _opt(t, fn):
+    return None if t is None else fn(t)
+
+
+class _ElementwiseMixin:
+    """Native versions of the bandwidth-bound operations (see csrc/elementwise.cu, ffn_core.cu, temporal.cu)."""
+
+    # ------------------------------------------------------------------ rope
+    def rope_store(self, d, qkv, cos, sin, qkc, kcache, vcache, s):
+        B, Tc, _ = qkv.shape
+        if qkv.dtype != torch.bfloat16 or d.hd % 2:
+            self.fallbacks["rope_store"] += 1
+            return super().rope_store(d, qkv, cos, sin, qkc, kcache, vcache, s)
+        native.ext().rope_store(qkv.contiguous(), _f32c(cos).view(B * Tc, d.hd), _f32c(sin).view(B * Tc, d.hd), qkc,
+                                kcache, vcache, B * Tc, Tc, kcache.shape[1], s, d.qh, d.kvh, d.hd)
+        native.count()
+
+    def rope_bwd(self, d, dq_attn, dqkc, dkc, dvc, s, e, cos, sin, out_dtype):
+        B, Tc = dq_attn.shape[:2]
+        if out_dtype != torch.bfloat16:
+            self.fallbacks["rope_bwd"] += 1
+            return super().rope_bwd(d, dq_attn, dqkc, dkc, dvc, s, e, cos, sin, out_dtype)
+        out = torch.empty(B, Tc, d.n + 2 * d.kv_dim, dtype=torch.bfloat16, device=dq_attn.device)
+        native.ext().rope_bwd(_bf16c(dq_attn), _bf16c(dqkc), dkc, dvc, _f32c(cos).view(B * Tc, d.hd),
+                              _f32c(sin).view(B * Tc, d.hd), out, B * Tc, Tc, dkc.shape[1], s, d.qh, d.kvh, d.hd)
+        native.count()
+        return out
+
+    # ------------------------------------------------------------------ depth attention
+    def _dread_ok(self, d, hist_k):
+        return hist_k.dtype == torch.bfloat16 and hist_k.is_contiguous() and d.hd % 8 == 0 and d.hd <= 128
+
+    def dread_fwd(self, d, q_row, hist_k, hist_v, n):
+        if not self._dread_ok(d, hist_k):
+            self.fallbacks["dread_fwd"] += 1
+            return super().dread_fwd(d, q_row, hist_k, hist_v, n)
+        M = hist_k.shape[1]
+        out = torch.empty(M, d.qh, d.hd, dtype=torch.bfloat16, device=hist_k.device)
+        lse = torch.empty(M, d.qh, dtype=torch.float32, device=hist_k.device)
+        native.ext().dread(False, _f32c(q_row), hist_k, hist_v, out, lse, None, None, None, None, n, M * d.qh, d.qh, d.hd)
+        native.count()
+        return out, lse
+
+    def dread_bwd(self, d, dm, m, lse, q_row, hist_k, hist_v, n, dhist_k, dhist_v, gq):
+        if not self._dread_ok(d, hist_k):
+            self.fallbacks["dread_bwd"] += 1
+            return super().dread_bwd(d, dm, m, lse, q_row, hist_k, hist_v, n, dhist_k, dhist_v, gq)
+        M = hist_k.shape[1]
+        native.ext().dread(True, _f32c(q_row), hist_k, hist_v, _bf16c(m), lse, _bf16c(dm), dhist_k, dhist_v, gq, n,
+                           M * d.qh, d.qh, d.hd)
+        native.count()
+
+    # ------------------------------------------------------------------ add + LayerNorm
+    def add_ln_fwd(self, a, b, w, bias, cap, eps=1e-5):
+        M, N = a.shape
+        if cap is not None or N % 8 or N > 1024 or a.dtype != torch.bfloat16:
+            self.fallbacks["add_ln_fwd"] += 1
+            return super().add_ln_fwd(a, b, w, bias, cap, eps)
+        y, x = torch.empty_like(a), torch.empty_like(a)
+        mean = torch.empty(M, dtype=torch.float32, device=a.device)
+        rstd = torch.empty(M, dtype=torch.float32, device=a.device)
+        native.ext().add_ln_fwd(a.contiguous(), _bf16c(b), w, bias, y, x, mean, rstd, M, N, eps)
+        native.count()
+        return y, x, mean, rstd
+
+    def add_ln_bwd(self, dy, x, mean, rstd, w, gw, gb, cap, a, b):
+        M, N = x.shape
+        if cap is not None or N % 8 or N > 1024 or x.dtype != torch.bfloat16:
+            self.fallbacks["add_ln_bwd"] += 1
+            return super().add_ln_bwd(dy, x, mean, rstd, w, gw, gb, cap, a, b)
+        dx = torch.empty_like(x)
+        native.ext().add_ln_bwd(_bf16c(dy), x, mean, rstd, w, dx, gw, gb, M, N)
+        native.count()
+        return dx, dx
+
+    def colsum_add(self, dy, gb):
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.dtype != torch.bfloat16 or dy2.shape[1] % 2 or dy2.stride(1) != 1 or not gb.is_contiguous():
+            self.fallbacks["colsum_add"] += 1
+            return super().colsum_add(dy, gb)
+        native.ext().colsum(dy2, gb, dy2.shape[0], dy2.shape[1])
+        native.count()
+
+    # ------------------------------------------------------------------ loss
+    def ce_fwd_bwd(self, logits, targets, ignore_index, grad_scale):
+        if logits.dtype != torch.bfloat16 or logits.shape[1] % 8 or not logits.is_contiguous():
+            self.fallbacks["ce"] += 1
+            return super().ce_fwd_bwd(logits, targets, ignore_index, grad_scale)
+        M = logits.shape[0]
+        targets = targets.contiguous()
+        n = targets.ne(ignore_index).sum().clamp(min=1).float()
+        nll = torch.empty(M, dtype=torch.float32, device=logits.device)
+        scale = ((grad_scale if grad_scale is not None else 0.0) / n).reshape(1)
+        native.ext().ce(logits, targets, nll, scale, ignore_index, grad_scale is not None)
+        native.count()
+        return nll.sum() / n, (logits if grad_scale is not None else None)
+
+    # ------------------------------------------------------------------ paraplex core + tria
+    def _core_ok(self, d, x_real):
+        return x_real.dtype == torch.bfloat16 and d.hidden % 2 == 0 and d.activation == "pvpowlu"
+
+    def ffn_core_fwd(self, d, x_real, p_in, alpha_gate, b_real, gate_lin, beta_lin, b_imag, w_trace, trace_in,
+                     reset, anchor, c_prev, seed, seed_valid, gate_w, axis, tria_alpha, B):
+        if not self._core_ok(d, x_real):
+            self.fallbacks["ffn_core_fwd"] += 1
+            return super().ffn_core_fwd(d, x_real, p_in, alpha_gate, b_real, gate_lin, beta_lin, b_imag, w_trace,
+                                        trace_in, reset, anchor, c_prev, seed, seed_valid, gate_w, axis, tria_alpha, B)
+        M, H = x_real.shape
+        dev = x_real.device
+        o = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
+        c = torch.empty(9, M, H, dtype=torch.bfloat16, device=dev) if axis is not None else None
+        p_out = torch.empty(M, H, dtype=torch.bfloat16, device=dev) if (axis is not None and gate_w is not None) else None
+        trace_out = torch.empty(B, H, dtype=torch.float32, device=dev)
+        bsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        native.ext().ffn_core(
+            False, B, M // B, H, -1 if axis is None else axis, bool(d.phase_secant), d.powlu_m, tria_alpha, d.phase_floor,
+            _opt(alpha_gate if p_in is not None else None, lambda t: _f32c(t).reshape(1)), None,
+            x_real, _opt(p_in, _bf16c), _f32c(b_real), _opt(gate_lin, _bf16c), _bf16c(beta_lin), _f32c(b_imag),
+            _f32c(w_trace), _opt(trace_in, _f32c), _opt(reset, lambda t: t.contiguous()), c_prev,
+            _opt(seed, _f32c), _opt(seed_valid, lambda t: t.contiguous()), _opt(gate_w, _f32c),
+            o, c, p_out, trace_out, bsq, None, None, None, None, None, None, None, None, None, None, None, None,
+            None, None, None, None)
+        native.count()
+        return {"r": None, "gsrc": None, "o": o, "i": None, "trace_out": trace_out, "beta_sq_sum": bsq[0], "c": c,
+                "p_out": p_out}
+
+    def ffn_core_bwd(self, d, saved, do, dc, dp_out, dtrace_out):
+        x_real = saved["x_real"]
+        if not self._core_ok(d, x_real):
+            self.fallbacks["ffn_core_bwd"] += 1
+            return super().ffn_core_bwd(d, saved, do, dc, dp_out, dtrace_out)
+        M, H = x_real.shape
+        B, dev = saved["B"], x_real.device
+        p_in, gate_lin, c_prev, seed, trace_in = (saved.get(k) for k in ("p_in", "gate_lin", "c_prev", "seed", "trace_in"))
+        axis = saved.get("axis")
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        dx = torch.empty(M, H, **bf)
+        dpin = torch.empty(M, H, **bf) if p_in is not None else None
+        dgl = torch.empty(M, H, **bf) if gate_lin is not None else None
+        dbeta = torch.empty(M, H, **bf)
+        gz = torch.empty(M, H, dtype=torch.float32, device=dev)
+        dcp = torch.empty(9, M, H, **bf) if (c_prev is not None and axis is not None) else None
+        dseed = torch.zeros(B, H, 9, dtype=torch.float32, device=dev) if (seed is not None and axis is not None) else None
+        dtr = torch.zeros(B, H, dtype=torch.float32, device=dev) if trace_in is not None else None
+        gsc = torch.zeros(10, dtype=torch.float32, device=dev)
+        gate_w = saved.get("gate_w")
+        native.ext().ffn_core(
+            True, B, M // B, H, -1 if axis is None else axis, bool(d.phase_secant), d.powlu_m, saved.get("tria_alpha") or 0.0,
+            d.phase_floor,
+            _opt(saved.get("alpha_gate") if p_in is not None else None, lambda t: _f32c(t).reshape(1)),
+            _opt(saved.get("anchor"), lambda t: _f32c(t).reshape(1)),
+            x_real, _opt(p_in, _bf16c), _f32c(saved["b_real"]), _opt(gate_lin, _bf16c), _bf16c(saved["beta_lin"]),
+            _f32c(saved["b_imag"]), _f32c(saved["w_trace"]), _opt(trace_in, _f32c),
+            _opt(saved.get("reset"), lambda t: t.contiguous()), c_prev, _opt(seed, _f32c),
+            _opt(saved.get("seed_valid"), lambda t: t.contiguous()), _opt(gate_w, _f32c),
+            None, None, None, None, None,
+            _bf16c(do), _opt(dc, _bf16c), _opt(dp_out if gate_w is not None else None, _bf16c), _opt(dtrace_out, _f32c),
+            dx, dpin, dgl, dbeta, gz, dcp, dseed, dtr,
+            saved["g_b_real"], saved["g_w_trace"], saved["g_b_imag"], gsc)
+        native.count(2)
+        return {"d_x_real": dx, "d_p_in": dpin, "d_gate_lin": dgl, "d_beta_lin": dbeta, "d_trace_in": dtr,
+                "d_c_prev": dcp, "d_seed": dseed, "d_b_real": None, "d_b_imag": None, "d_w_trace": None,
+                "d_alpha_gate": gsc[0] if p_in is not None else None,
+                "d_gate_w": gsc[1:10] if gate_w is not None else None}
+
+    # ------------------------------------------------------------------ temporal endpoint
+    def temporal_fwd(self, depth, B, Tc, H, reset, state, fired, polarm_beta):
+        if not (depth.dim() == 3 and depth.shape[0] == 9):          # carriers came from the PyTorch twin
+            self.fallbacks["temporal_fwd"] += 1
+            return super().temporal_fwd(depth, B, Tc, H, reset, state, fired, polarm_beta)
+        dev = depth.device
+        out = torch.empty(B, H, 9, dtype=torch.float32, device=dev)
+        raw = torch.empty(B, H, 9, dtype=torch.float32, device=dev)
+        nck = Tc // 32
+        ck = torch.empty(nck, B, H, 9, dtype=torch.float32, device=dev) if nck > 0 else None
+        native.ext().temporal_fwd(depth, reset.contiguous(), _opt(state, _f32c), _opt(fired, lambda t: t.contiguous()),
+                                  polarm_beta, out, raw, ck, B, Tc, H)
+        native.count()
+        return out, {"raw": raw, "ckpt": ck}
+
+    def temporal_bwd(self, dstate, depth, B, Tc, H, reset, state, fired, polarm_beta, aux):
+        if aux is None or "raw" not in aux:
+            self.fallbacks["temporal_bwd"] += 1
+            return super().temporal_bwd(dstate, depth, B, Tc, H, reset, state, fired, polarm_beta, aux)
+        dev = depth.device
+        ddepth = torch.empty_like(depth)
+        dprev = torch.empty(B, H, 9, dtype=torch.float32, device=dev) if state is not None else None
+        native.ext().temporal_bwd(depth, reset.contiguous(), _opt(state, _f32c), _opt(fired, lambda t: t.contiguous()),
+                                  polarm_beta, aux["raw"], aux["ckpt"], _f32c(dstate.reshape(B, H, 9)), ddepth, dprev,
+                                  B, Tc, H)
+        native.count()
+        return ddepth, dprev
+
+
+class CudaKernels(_ElementwiseMixin, CudaKernels):      # noqa: F811  (final kernel set = GEMMs + element-wise kernels)
+    pass

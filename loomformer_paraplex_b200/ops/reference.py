@@ -220,7 +220,7 @@ def tria_compose(
     """
     t = build_tria(r, i, o, alpha, axis)
     if prev is not None:
-        pre = torch.matmul(t, prev)
+        pre = torch.matmul(t, prev.to(t.dtype))
     elif seed is not None:
         first = torch.matmul(t[:, 0], seed.to(t.dtype))
         first = torch.where(seed_valid.to(torch.bool)[:, None, None, None], first, t[:, 0])

@@ -92,9 +92,12 @@ class TorchKernels:
         kcache[:, s:s + Tc] = R.apply_rope(k.view(B, Tc, d.kvh, d.hd), c, s_)
         vcache[:, s:s + Tc] = v.view(B, Tc, d.kvh, d.hd)
 
-    def rope_bwd(self, d, dq, dk, dv, cos, sin, out_dtype):
-        """Inverse rotation of the q / k gradients and packing into d(qkv) [B,Tc,N+2KV]."""
-        B, Tc = dq.shape[:2]
+    def rope_bwd(self, d, dq_attn, dqkc, dkc, dvc, s, e, cos, sin, out_dtype):
+        """Inverse rotation of the q / k gradients and packing into d(qkv) [B,Tc,N+2KV].  The q gradient is the
+        attention part plus sector 0 of ``dqkc``; k/v gradients are rows [s,e) of the fp32 cache gradients."""
+        B, Tc = dq_attn.shape[:2]
+        dq = dq_attn.float() + dqkc[:, 0].reshape(B, Tc, d.qh, d.hd).float()
+        dk, dv = dkc[:, s:e], dvc[:, s:e]
         c, s_ = cos.unsqueeze(2).float(), sin.unsqueeze(2).float()
 
         def inv(g):
@@ -267,23 +270,27 @@ class TorchKernels:
         return {"d_" + k: g for (k, _), g in zip(ins, res)}
 
     # ------------------------------------------------------------------ temporal endpoint (+ PolARM)
-    def temporal_fwd(self, depth, reset, state, fired, polarm_beta):
-        """depth [B,Tc,H,9]; reset [B,Tc]; state [B,H,9] fp32 or None; fired [B] bool or None (PolARM
-        applied to fired rows).  Returns the new fp32 state [B,H,9]."""
+    def temporal_fwd(self, depth, B, Tc, H, reset, state, fired, polarm_beta):
+        """depth: last-layer carriers of the chunk in this kernel set's carrier layout (here [M,H,9]);
+        reset [B,Tc]; state [B,H,9] fp32 or None; fired [B] bool or None (PolARM applied to fired rows).
+        Returns (new fp32 state [B,H,9], aux for the backward pass)."""
+        return self._temporal(depth.reshape(B, Tc, H, 9), reset, state, fired, polarm_beta), None
+
+    def _temporal(self, depth, reset, state, fired, polarm_beta):
         B, Tc, H, _ = depth.shape
         st = R.temporal_endpoint(depth.view(B, Tc, H, 3, 3), reset, None if state is None else state.view(B, H, 3, 3))
         if fired is not None:
             st = torch.where(fired[:, None, None, None], R.polarm(st, polarm_beta), st)
         return st.reshape(B, H, 9)
 
-    def temporal_bwd(self, dstate_out, depth, reset, state, fired, polarm_beta):
-        dl = depth.detach().float().requires_grad_(True)
+    def temporal_bwd(self, dstate_out, depth, B, Tc, H, reset, state, fired, polarm_beta, aux):
+        dl = depth.detach().float().reshape(B, Tc, H, 9).requires_grad_(True)
         sl = None if state is None else state.detach().float().requires_grad_(True)
         with torch.enable_grad():
-            out = self.temporal_fwd(dl, reset, sl, fired, polarm_beta)
+            out = self._temporal(dl, reset, sl, fired, polarm_beta)
             ins = [dl] + ([sl] if sl is not None else [])
-            res = torch.autograd.grad(out, ins, dstate_out.float(), allow_unused=True)
-        return res[0], (res[1] if sl is not None else None)
+            res = torch.autograd.grad(out, ins, dstate_out.float().reshape(out.shape), allow_unused=True)
+        return res[0].reshape(B * Tc, H, 9), (res[1] if sl is not None else None)
 
     # ------------------------------------------------------------------ readout
     def slot_pool_fwd(self, keys, score_w):

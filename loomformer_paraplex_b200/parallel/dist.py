@@ -119,6 +119,7 @@ def init(device_pref: Optional[str] = None, timeout_s: float = 600.0) -> Tuple[t
         subset = parse_cuda_list(pref)
         dev = torch.device(f"cuda:{subset[0]}") if subset is not None else torch.device(pref)
     if dev.type == "cuda":
+        dev = torch.device("cuda", dev.index if dev.index is not None else torch.cuda.current_device())
         torch.cuda.set_device(dev)
     return dev, 1, 0
 

@@ -1,0 +1,200 @@
+"""Each native bandwidth-bound kernel against its PyTorch twin evaluated in fp32 on the same bf16 inputs."""
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _sets():
+    from loomformer_paraplex_b200.ops.kernels import CudaKernels
+    from loomformer_paraplex_b200.ops.twins import TorchKernels
+    return CudaKernels(), TorchKernels()
+
+
+def _close(a, b, tol=2e-2, name=""):
+    a, b = a.float(), b.float()
+    err = float((a - b).abs().max())
+    ref = float(b.abs().max()) + 1e-6
+    assert err <= tol * ref + 1e-5, (name, err, ref)
+
+
+def _dims(qh=8, hd=96, kvh=2, hidden=3072, **kw):
+    base = dict(qh=qh, hd=hd, kvh=kvh, group=qh // kvh, n=qh * hd, kv_dim=kvh * hd, hidden=hidden, hpq=hidden // qh,
+                activation="pvpowlu", powlu_m=3.0, phase_floor=0.05, phase_secant=True)
+    base.update(kw)
+    return SimpleNamespace(**base)
+
+
+def bf(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("hd", [32, 96])
+def test_rope_store_and_bwd(hd):
+    ck, tk = _sets()
+    d = _dims(hd=hd)
+    B, Tc, T, s = 3, 40, 100, 24
+    torch.manual_seed(0)
+    qkv = bf(B, Tc, d.n + 2 * d.kv_dim)
+    ang = torch.rand(B, Tc, hd // 2, device="cuda") * 6
+    cos, sin = torch.cat((ang.cos(), ang.cos()), -1) * 1.1, torch.cat((ang.sin(), ang.sin()), -1) * 1.1
+    outs = []
+    for k in (ck, tk):
+        qkc = torch.zeros(B * Tc, 3, d.qh, hd, device="cuda", dtype=torch.bfloat16)
+        kc = torch.zeros(B, T, d.kvh, hd, device="cuda", dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+        k.rope_store(d, qkv, cos, sin, qkc, kc, vc, s)
+        outs.append((qkc, kc, vc))
+    for x, y in zip(*outs):
+        _close(x, y, 1e-2)
+    dq = bf(B, Tc, d.qh, hd); dqkc = bf(B * Tc, 3, d.qh, hd)
+    dkc, dvc = torch.randn(B, T, d.kvh, hd, device="cuda"), torch.randn(B, T, d.kvh, hd, device="cuda")
+    a = ck.rope_bwd(d, dq, dqkc, dkc, dvc, s, s + Tc, cos, sin, torch.bfloat16)
+    b = tk.rope_bwd(d, dq, dqkc, dkc, dvc, s, s + Tc, cos, sin, torch.float32)
+    _close(a, b, 1e-2)
+
+
+@pytest.mark.parametrize("hd,qh", [(32, 4), (64, 15), (96, 8)])
+def test_depth_read(hd, qh):
+    ck, tk = _sets()
+    d = _dims(qh=qh, hd=hd, kvh=1)
+    S, M, n = 7, 333, 5
+    torch.manual_seed(1)
+    hk, hv = bf(S, M, qh, hd), bf(S, M, qh, hd)
+    q = torch.randn(qh, hd, device="cuda")
+    m1, l1 = ck.dread_fwd(d, q, hk, hv, n)
+    m2, l2 = tk.dread_fwd(d, q, hk.float(), hv.float(), n)
+    _close(m1, m2); _close(l1, l2, 1e-3)
+    dm = bf(M, qh, hd)
+    g1 = [torch.randn(S, M, qh, hd, device="cuda") for _ in range(2)] + [torch.zeros(qh, hd, device="cuda")]
+    g2 = [x.clone() for x in g1]
+    ck.dread_bwd(d, dm, m1, l1, q, hk, hv, n, *g1)
+    tk.dread_bwd(d, dm.float(), m1.float(), l1, q, hk.float(), hv.float(), n, *g2)
+    for x, y, nm in zip(g1, g2, ("dk", "dv", "gq")):
+        _close(x, y, 2e-2, nm)
+    assert not ck.fallbacks, ck.fallbacks
+
+
+@pytest.mark.parametrize("N", [128, 768, 960])
+def test_add_layernorm(N):
+    ck, tk = _sets()
+    M = 517
+    torch.manual_seed(2)
+    a, b = bf(M, N), bf(M, N)
+    w, bias = torch.randn(N, device="cuda"), torch.randn(N, device="cuda")
+    y1, x1, mu1, rs1 = ck.add_ln_fwd(a, b, w, bias, None)
+    y2, x2, mu2, rs2 = tk.add_ln_fwd(a, b, w, bias, None)
+    _close(y1, y2, 1e-2); _close(mu1, mu2, 1e-3); _close(rs1, rs2, 1e-3)
+    dy = bf(M, N)
+    gw1, gb1, gw2, gb2 = (torch.zeros(N, device="cuda") for _ in range(4))
+    d1, _ = ck.add_ln_bwd(dy, x1, mu1, rs1, w, gw1, gb1, None, None, None)
+    d2, _ = tk.add_ln_bwd(dy.float(), x1.float(), mu1, rs1, w, gw2, gb2, None, None, None)
+    _close(d1, d2, 1e-2); _close(gw1, gw2, 1e-3); _close(gb1, gb2, 1e-3)
+    g1, g2 = torch.zeros(N, device="cuda"), torch.zeros(N, device="cuda")
+    ck.colsum_add(dy, g1); tk.colsum_add(dy, g2)
+    _close(g1, g2, 1e-3)
+    assert not ck.fallbacks, ck.fallbacks
+
+
+def test_cross_entropy():
+    ck, tk = _sets()
+    torch.manual_seed(3)
+    M, V = 300, 8192
+    logits = bf(M, V, scale=3.0)
+    tgt = torch.randint(0, V, (M,), device="cuda")
+    tgt[:17] = -100
+    l2, g2 = tk.ce_fwd_bwd(logits.float(), tgt, -100, 0.5)
+    l1, g1 = ck.ce_fwd_bwd(logits.clone(), tgt, -100, 0.5)
+    assert abs(float(l1) - float(l2)) < 2e-3
+    _close(g1, g2, 1e-2)
+
+
+def _core_case(ck, tk, d, B, Tc, *, p_in, c_prev, seed, gate_lin, gate_w, trace, reset, axis):
+    M, H = B * Tc, d.hidden
+    x_real, beta_lin = bf(M, H), bf(M, H, scale=1.5)
+    pin = bf(M, H, scale=0.5) if p_in else None
+    glin = bf(M, H) if gate_lin else None
+    alpha = torch.tensor(0.17, device="cuda")
+    b_real, b_imag, w_tr = (torch.randn(H, device="cuda") * 0.3 for _ in range(3))
+    tr_in = torch.rand(B, H, device="cuda") * 2 - 1 if trace else None
+    rs = (torch.rand(M, device="cuda") < 0.05) if reset else None
+    cp_t = torch.randn(M, H, 9, device="cuda").to(torch.bfloat16) if c_prev else None
+    sd = torch.randn(B, H, 9, device="cuda") if seed else None
+    sv = (torch.rand(B, device="cuda") < 0.6) if seed else None
+    gw = torch.softmax(torch.randn(9, device="cuda"), 0) if gate_w else None
+    anchor = torch.tensor(0.8, device="cuda")
+    planes = lambda t: None if t is None else t.permute(2, 0, 1).contiguous()
+    o1 = ck.ffn_core_fwd(d, x_real, pin, alpha, b_real, glin, beta_lin, b_imag, w_tr, tr_in, rs, None, planes(cp_t),
+                         sd, sv, gw, axis, 0.05, B)
+    f = lambda t: None if t is None else t.float()
+    o2 = tk.ffn_core_fwd(d, f(x_real), f(pin), alpha, b_real, f(glin), f(beta_lin), b_imag, w_tr, tr_in, rs, None,
+                         f(cp_t), sd, sv, gw, axis, 0.05, B)
+    _close(o1["o"], o2["o"], 2e-2, "o"); _close(o1["trace_out"], o2["trace_out"], 1e-3, "trace")
+    assert abs(float(o1["beta_sq_sum"]) / float(o2["beta_sq_sum"]) - 1) < 1e-3
+    if axis is not None:
+        _close(o1["c"].permute(1, 2, 0), o2["c"], 2e-2, "c")
+        if gw is not None:
+            _close(o1["p_out"], o2["p_out"], 2e-2, "p_out")
+    # backward
+    do = bf(M, H, scale=0.1)
+    dc_t = (torch.randn(M, H, 9, device="cuda") * 0.1).to(torch.bfloat16) if axis is not None else None
+    dpo = bf(M, H, scale=0.1) if (axis is not None and gw is not None) else None
+    dtr = torch.randn(B, H, device="cuda") * 0.1
+    saved = {"x_real": x_real, "p_in": pin, "alpha_gate": alpha, "b_real": b_real, "gate_lin": glin, "beta_lin": beta_lin,
+             "b_imag": b_imag, "w_trace": w_tr, "trace_in": tr_in, "reset": rs, "anchor": anchor, "c_prev": planes(cp_t),
+             "seed": sd, "seed_valid": sv, "gate_w": gw, "axis": axis, "tria_alpha": 0.05, "B": B,
+             "g_b_real": torch.zeros(H, device="cuda"), "g_b_imag": torch.zeros(H, device="cuda"),
+             "g_w_trace": torch.zeros(H, device="cuda")}
+    g1 = ck.ffn_core_bwd(d, saved, do, planes(dc_t), dpo, dtr)
+    saved2 = dict(saved, c_prev=cp_t)
+    g2 = tk.ffn_core_bwd(d, saved2, do, dc_t, dpo, dtr)
+    for k in ("d_x_real", "d_p_in", "d_gate_lin", "d_beta_lin", "d_trace_in", "d_seed"):
+        if g2.get(k) is not None:
+            _close(g1[k], g2[k], 3e-2, k)
+    if cp_t is not None:
+        _close(g1["d_c_prev"].permute(1, 2, 0), g2["d_c_prev"], 3e-2, "d_c_prev")
+    _close(saved["g_b_real"], g2["d_b_real"], 2e-2, "g_b_real")
+    _close(saved["g_b_imag"], g2["d_b_imag"], 2e-2, "g_b_imag")
+    _close(saved["g_w_trace"], g2["d_w_trace"], 2e-2, "g_w_trace")
+    if pin is not None:
+        assert abs(float(g1["d_alpha_gate"]) - float(g2["d_alpha_gate"])) <= 2e-2 * abs(float(g2["d_alpha_gate"])) + 1e-2
+    if gw is not None and axis is not None:
+        _close(g1["d_gate_w"], g2["d_gate_w"], 2e-2, "d_gate_w")
+
+
+@pytest.mark.parametrize("secant", [True, False])
+def test_ffn_core_variants(secant):
+    ck, tk = _sets()
+    d = _dims(hidden=256, phase_secant=secant)
+    torch.manual_seed(4)
+    _core_case(ck, tk, d, 3, 20, p_in=False, c_prev=False, seed=False, gate_lin=False, gate_w=True, trace=False, reset=False, axis=0)
+    _core_case(ck, tk, d, 3, 20, p_in=True, c_prev=True, seed=False, gate_lin=False, gate_w=True, trace=True, reset=True, axis=1)
+    _core_case(ck, tk, d, 3, 20, p_in=False, c_prev=False, seed=True, gate_lin=True, gate_w=True, trace=True, reset=True, axis=0)
+    _core_case(ck, tk, d, 3, 20, p_in=True, c_prev=True, seed=False, gate_lin=True, gate_w=False, trace=True, reset=False, axis=2)
+    _core_case(ck, tk, d, 2, 16, p_in=False, c_prev=False, seed=False, gate_lin=False, gate_w=False, trace=True, reset=True, axis=None)
+    assert not ck.fallbacks, ck.fallbacks
+
+
+@pytest.mark.parametrize("Tc", [128, 70])
+def test_temporal_endpoint(Tc):
+    ck, tk = _sets()
+    torch.manual_seed(5)
+    B, H = 3, 64
+    base = torch.eye(3, device="cuda").reshape(1, 1, 9) + 0.3 * torch.randn(B * Tc, H, 9, device="cuda")
+    depth_t = base.to(torch.bfloat16)
+    reset = torch.rand(B, Tc, device="cuda") < 0.02
+    state = torch.eye(3, device="cuda").reshape(1, 1, 9) + 0.2 * torch.randn(B, H, 9, device="cuda")
+    fired = torch.tensor([True, False, True], device="cuda")
+    planes = depth_t.permute(2, 0, 1).contiguous()
+    for st, fr in ((state, fired), (None, None)):
+        s1, aux = ck.temporal_fwd(planes, B, Tc, H, reset, st, fr, 0.1)
+        s2, _ = tk.temporal_fwd(depth_t.float(), B, Tc, H, reset, st, fr, 0.1)
+        _close(s1, s2, 2e-3, "state")
+        g = torch.randn(B, H, 9, device="cuda")
+        d1, p1 = ck.temporal_bwd(g, planes, B, Tc, H, reset, st, fr, 0.1, aux)
+        d2, p2 = tk.temporal_bwd(g, depth_t.float(), B, Tc, H, reset, st, fr, 0.1, None)
+        _close(d1.permute(1, 2, 0), d2, 3e-2, "ddepth")
+        if st is not None:
+            _close(p1, p2, 3e-2, "dstate_in")
