@@ -140,10 +140,10 @@ void rope_store(torch::Tensor qkv, torch::Tensor cs, torch::Tensor sn, torch::Te
 
 void rope_bwd(torch::Tensor dq_attn, torch::Tensor dqkc, torch::Tensor dkc, torch::Tensor dvc, torch::Tensor cs,
               torch::Tensor sn, torch::Tensor dqkv, int64_t M, int64_t Tc, int64_t T, int64_t s, int64_t QH, int64_t KVH,
-              int64_t HD) {
+              int64_t HD, int64_t G) {
   const c10::cuda::CUDAGuard guard(dqkv.device());
   int rc = loom_rope_bwd(dq_attn.data_ptr(), dqkc.data_ptr(), fptr(dkc), fptr(dvc), fptr(cs), fptr(sn), dqkv.data_ptr(),
-                         (int)M, (int)Tc, (int)T, (int)s, (int)QH, (int)KVH, (int)HD, cur_stream());
+                         (int)M, (int)Tc, (int)T, (int)s, (int)QH, (int)KVH, (int)HD, (int)G, cur_stream());
   TORCH_CHECK(rc == 0, "loom_rope_bwd failed: ", rc);
 }
 
@@ -203,6 +203,21 @@ void temporal_bwd(torch::Tensor depth, torch::Tensor reset, OptT state_in, OptT 
   TORCH_CHECK(rc == 0, "loom_temporal_bwd failed: ", rc);
 }
 
+void attn(bool bwd, torch::Tensor qkc, torch::Tensor kcache, torch::Tensor vcache, torch::Tensor lse, OptT seg,
+          OptT dqkc, OptT dq_attn, OptT dk_heads, OptT dv_heads, int64_t B, int64_t QH, int64_t KVH, int64_t HD,
+          int64_t Tc, int64_t T, int64_t s, int64_t e, torch::Tensor status) {
+  const c10::cuda::CUDAGuard guard(qkc.device());
+  TORCH_CHECK(qkc.is_contiguous() && kcache.is_contiguous() && vcache.is_contiguous(), "attention operands must be contiguous");
+  LoomAttn a{};
+  a.qkc = qkc.data_ptr(); a.kcache = kcache.data_ptr(); a.vcache = vcache.data_ptr(); a.lse = fptr(lse);
+  a.seg = seg.has_value() ? (const int*)seg->data_ptr() : nullptr;
+  a.dqkc = cp(dqkc); a.dq_attn = mp(dq_attn); a.dk_heads = mf(dk_heads); a.dv_heads = mf(dv_heads);
+  a.B = (int)B; a.QH = (int)QH; a.KVH = (int)KVH; a.HD = (int)HD; a.Tc = (int)Tc; a.T = (int)T; a.s = (int)s; a.e = (int)e;
+  a.status = status.data_ptr<int>();
+  int rc = bwd ? loom_attn_bwd(&a, cur_stream()) : loom_attn_fwd(&a, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_attn failed: ", rc);
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -220,5 +235,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("colsum", &colsum, "column sums into an fp32 accumulator");
   m.def("ce", &ce, "cross-entropy over bf16 logits with in-place gradient");
   m.def("temporal_fwd", &temporal_fwd, "temporal carry endpoint + PolARM");
+  m.def("attn", &attn, "dual-context causal GQA attention (forward / backward)");
   m.def("temporal_bwd", &temporal_bwd, "temporal carry endpoint backward");
 }

@@ -73,7 +73,7 @@ __global__ void rope_store_kernel(const bf16* __restrict__ qkv, const float* __r
 __global__ void rope_bwd_kernel(const bf16* __restrict__ dq_attn, const bf16* __restrict__ dqkc,
                                 const float* __restrict__ dkc, const float* __restrict__ dvc,
                                 const float* __restrict__ cs, const float* __restrict__ sn, bf16* __restrict__ dqkv,
-                                int M, int Tc, int T, int s_off, int QH, int KVH, int HD) {
+                                int M, int Tc, int T, int s_off, int QH, int KVH, int HD, int G) {
   const int half = HD / 2;
   const int heads = QH + 2 * KVH;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -90,9 +90,11 @@ __global__ void rope_bwd_kernel(const bf16* __restrict__ dq_attn, const bf16* __
     g1 = __bfloat162float(dq_attn[a + j]) + __bfloat162float(dqkc[d + j]);
     g2 = __bfloat162float(dq_attn[a + j + half]) + __bfloat162float(dqkc[d + j + half]);
   } else {
+    // the cache-gradient slab holds G heads per kv head (G = 1, or the GQA group size for per-query-head slabs)
     const int kh = (hh < QH + KVH) ? hh - QH : hh - QH - KVH;
-    const float* src = ((hh < QH + KVH) ? dkc : dvc) + (((long long)b * T + s_off + t) * KVH + kh) * HD;
-    g1 = src[j]; g2 = src[j + half];
+    const float* src = ((hh < QH + KVH) ? dkc : dvc) + (((long long)b * T + s_off + t) * KVH * G + kh * G) * HD;
+    g1 = 0.f; g2 = 0.f;
+    for (int gq = 0; gq < G; ++gq) { g1 += src[gq * HD + j]; g2 += src[gq * HD + j + half]; }
   }
   if (hh < QH + KVH) {
     const float c1 = cs[(long long)m * HD + j], c2 = cs[(long long)m * HD + j + half];
@@ -457,10 +459,10 @@ extern "C" int loom_rope_store(const void* qkv, const float* cs, const float* sn
 
 extern "C" int loom_rope_bwd(const void* dq_attn, const void* dqkc, const float* dkc, const float* dvc, const float* cs,
                              const float* sn, void* dqkv, int M, int Tc, int T, int s_off, int QH, int KVH, int HD,
-                             cudaStream_t st) {
+                             int G, cudaStream_t st) {
   const long long n = (long long)M * (QH + 2 * KVH) * (HD / 2);
   rope_bwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const bf16*)dq_attn, (const bf16*)dqkc, dkc, dvc, cs, sn,
-                                                               (bf16*)dqkv, M, Tc, T, s_off, QH, KVH, HD);
+                                                               (bf16*)dqkv, M, Tc, T, s_off, QH, KVH, HD, G);
   return (int)cudaGetLastError();
 }
 

@@ -82,7 +82,8 @@ int loom_ffn_core_bwd(const LoomFfnCore* a, cudaStream_t stream);
 int loom_rope_store(const void* qkv, const float* cs, const float* sn, void* qkc, void* kcache, void* vcache, int M,
                     int Tc, int T, int s_off, int QH, int KVH, int HD, cudaStream_t st);
 int loom_rope_bwd(const void* dq_attn, const void* dqkc, const float* dkc, const float* dvc, const float* cs,
-                  const float* sn, void* dqkv, int M, int Tc, int T, int s_off, int QH, int KVH, int HD, cudaStream_t st);
+                  const float* sn, void* dqkv, int M, int Tc, int T, int s_off, int QH, int KVH, int HD, int G,
+                  cudaStream_t st);
 int loom_dread(int bwd, const float* q, const void* hk, const void* hv, void* out, float* lse, const void* dm, float* dhk,
                float* dhv, float* gq, int n, long long MQ, int QH, int HD, cudaStream_t st);
 int loom_add_ln_fwd(const void* a, const void* b, const float* w, const float* bias, void* y, void* x, float* mean,
@@ -99,6 +100,20 @@ int loom_temporal_fwd(const void* depth, const uint8_t* reset, const float* stat
 int loom_temporal_bwd(const void* depth, const uint8_t* reset, const float* state_in, const uint8_t* fired, float beta,
                       const float* raw, const float* ckpt, const float* dstate, void* ddepth, float* dstate_in, int B,
                       int Tc, int H, cudaStream_t st);
+
+// ---- dual-context attention (attention_fwd.cu / attention_bwd.cu) ----
+// qkc [B*Tc, 3, QH, HD] bf16 (sector 0 = rotated queries, 1 = A@K, 2 = A@V); caches [B, T, KVH, HD] bf16;
+// lse [B, QH, Tc] fp32; seg [B, T] int32 or null.  The chunk's queries sit at absolute positions [s, e).
+// Backward: dqkc same layout as qkc (sectors 1, 2 are read); dq_attn [B*Tc, QH, HD] bf16 out;
+// dk_heads / dv_heads [B, T, QH, HD] fp32 are per-query-head key/value gradient slabs (+=, no atomics).
+typedef struct {
+  const void* qkc; const void* kcache; const void* vcache; float* lse; const int* seg;
+  const void* dqkc; void* dq_attn; float* dk_heads; float* dv_heads;
+  int B, QH, KVH, HD, Tc, T, s, e;
+  int* status;
+} LoomAttn;
+int loom_attn_fwd(const LoomAttn* a, cudaStream_t stream);
+int loom_attn_bwd(const LoomAttn* a, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

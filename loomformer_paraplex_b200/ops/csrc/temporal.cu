@@ -17,7 +17,7 @@
 namespace {
 
 typedef __nv_bfloat16 bf16;
-constexpr int CKPT = 32;
+constexpr int CKPT = 16;
 constexpr float EPS = 1e-6f;
 
 __device__ __forceinline__ void mat3(const float* A, const float* B, float* C) {   // C = A B

@@ -173,8 +173,8 @@ class FusedPlan:
         dkeys = None
         if ro is not None:
             dh, dkeys = self._readout_backward(ro, dh)
-        dkc = [torch.zeros(B, T, d.kvh, d.hd, dtype=torch.float32, device=dev) for _ in range(L)]
-        dvc = [torch.zeros(B, T, d.kvh, d.hd, dtype=torch.float32, device=dev) for _ in range(L)]
+        dkc = [K.alloc_kv_grad(d, B, T, dev) for _ in range(L)]
+        dvc = [K.alloc_kv_grad(d, B, T, dev) for _ in range(L)]
         d_emb = torch.empty(B, T, d.n, dtype=self.adt, device=dev)
         dtraces: Optional[List[Optional[torch.Tensor]]] = None
         dtemporal = None                      # gradient w.r.t. the temporal state entering the NEXT chunk

@@ -216,9 +216,48 @@ class _ElementwiseMixin:
             return super().rope_bwd(d, dq_attn, dqkc, dkc, dvc, s, e, cos, sin, out_dtype)
         out = torch.empty(B, Tc, d.n + 2 * d.kv_dim, dtype=torch.bfloat16, device=dq_attn.device)
         native.ext().rope_bwd(_bf16c(dq_attn), _bf16c(dqkc), dkc, dvc, _f32c(cos).view(B * Tc, d.hd),
-                              _f32c(sin).view(B * Tc, d.hd), out, B * Tc, Tc, dkc.shape[1], s, d.qh, d.kvh, d.hd)
+                              _f32c(sin).view(B * Tc, d.hd), out, B * Tc, Tc, dkc.shape[1], s, d.qh, d.kvh, d.hd,
+                              dkc.shape[2] // d.kvh)
         native.count()
         return out
+
+    # ------------------------------------------------------------------ attention
+    def _attn_ok(self, d, qkc, s, e):
+        return qkc.dtype == torch.bfloat16 and d.hd % 16 == 0 and d.hd <= 128 and (e - s) <= 128
+
+    def attn_fwd(self, d, qkc, kcache, vcache, s, e, seg):
+        if not self._attn_ok(d, qkc, s, e):
+            self.fallbacks["attn_fwd"] += 1
+            return super().attn_fwd(d, qkc, kcache, vcache, s, e, seg)
+        B, T = kcache.shape[0], kcache.shape[1]
+        Tc = e - s
+        lse = torch.empty(B, d.qh, Tc, dtype=torch.float32, device=qkc.device)
+        seg32 = None if seg is None else (seg if seg.dtype == torch.int32 else seg.to(torch.int32)).contiguous()
+        native.ext().attn(False, qkc, kcache, vcache, lse, seg32, None, None, None, None, B, d.qh, d.kvh, d.hd, Tc, T,
+                          s, e, status_word(qkc.device))
+        native.count()
+        return lse
+
+    def alloc_kv_grad(self, d, B, T, device):
+        """Per-query-head key/value gradient slabs (the GQA group sum happens in rope_bwd)."""
+        if d.hd % 16 or d.hd > 128:
+            return super().alloc_kv_grad(d, B, T, device)
+        return torch.zeros(B, T, d.qh, d.hd, dtype=torch.float32, device=device)
+
+    def attn_bwd(self, d, dqkc, qkc, kcache, vcache, lse, s, e, seg, dkcache, dvcache):
+        if not self._attn_ok(d, qkc, s, e) or dkcache.shape[2] != d.qh:
+            self.fallbacks["attn_bwd"] += 1
+            if dkcache.shape[2] != d.kvh:
+                raise RuntimeError("attention backward fallback needs kv-head shaped gradient buffers")
+            return super().attn_bwd(d, dqkc, qkc, kcache, vcache, lse, s, e, seg, dkcache, dvcache)
+        B, T = kcache.shape[0], kcache.shape[1]
+        Tc = e - s
+        dq = torch.empty(B * Tc, d.qh, d.hd, dtype=torch.bfloat16, device=qkc.device)
+        seg32 = None if seg is None else (seg if seg.dtype == torch.int32 else seg.to(torch.int32)).contiguous()
+        native.ext().attn(True, qkc, kcache, vcache, lse, seg32, _bf16c(dqkc), dq, dkcache, dvcache, B, d.qh, d.kvh, d.hd,
+                          Tc, T, s, e, status_word(qkc.device))
+        native.count()
+        return dq
 
     # ------------------------------------------------------------------ depth attention
     def _dread_ok(self, d, hist_k):
@@ -365,7 +404,7 @@ class _ElementwiseMixin:
         dev = depth.device
         out = torch.empty(B, H, 9, dtype=torch.float32, device=dev)
         raw = torch.empty(B, H, 9, dtype=torch.float32, device=dev)
-        nck = Tc // 32
+        nck = Tc // 16          # must match CKPT in csrc/temporal.cu
         ck = torch.empty(nck, B, H, 9, dtype=torch.float32, device=dev) if nck > 0 else None
         native.ext().temporal_fwd(depth, reset.contiguous(), _opt(state, _f32c), _opt(fired, lambda t: t.contiguous()),
                                   polarm_beta, out, raw, ck, B, Tc, H)

@@ -116,6 +116,10 @@ class TorchKernels:
             ok = ok & (seg[:, None, s:e, None] == seg[:, None, None, :e])
         return ok
 
+    def alloc_kv_grad(self, d, B, T, device):
+        """fp32 accumulator for key/value gradients of one layer's cache."""
+        return torch.zeros(B, T, d.kvh, d.hd, dtype=torch.float32, device=device)
+
     def attn_fwd(self, d, qkc, kcache, vcache, s, e, seg):
         """Dual-context attention of the chunk's queries against cache rows [0,e).  Fills
         qkc[:,1] (A@K) and qkc[:,2] (A@V); returns log-sum-exp [B,QH,Tc] (fp32)."""
