@@ -236,13 +236,13 @@ __global__ void __launch_bounds__(THREADS, 1) attn_bwd_kernel(const __grid_const
           tmem_ld_32x32(tDKV + lane_off + c, a);
           tmem_ld_wait();
           if (key < p.e) {
+            // fire-and-forget vector reductions: no read latency on the critical path.  The slab slice
+            // belongs to this CTA alone, so the adds never contend and their order is fixed.
             const int nv = min(32, p.HD - c);
-            for (int i = 0; i < nv; i += 4) {
-              float4 o = *reinterpret_cast<float4*>(dst + c + i);
-              o.x += __uint_as_float(a[i]); o.y += __uint_as_float(a[i + 1]);
-              o.z += __uint_as_float(a[i + 2]); o.w += __uint_as_float(a[i + 3]);
-              *reinterpret_cast<float4*>(dst + c + i) = o;
-            }
+            for (int i = 0; i < nv; i += 4)
+              asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                           ::"l"(dst + c + i), "f"(__uint_as_float(a[i])), "f"(__uint_as_float(a[i + 1])),
+                             "f"(__uint_as_float(a[i + 2])), "f"(__uint_as_float(a[i + 3])) : "memory");
           }
         }
         tc_fence_before();

@@ -218,6 +218,27 @@ void attn(bool bwd, torch::Tensor qkc, torch::Tensor kcache, torch::Tensor vcach
   TORCH_CHECK(rc == 0, "loom_attn failed: ", rc);
 }
 
+void p2p_grad_step(int64_t W, int64_t rank, int64_t nblk, std::vector<int64_t> grads, std::vector<int64_t> params,
+                   std::vector<int64_t> shadow, std::vector<int64_t> sync, int64_t mc_grads, torch::Tensor m,
+                   torch::Tensor v, torch::Tensor lr_mult, torch::Tensor wd, torch::Tensor active, torch::Tensor hyper,
+                   torch::Tensor stats, torch::Tensor sumsq, double max_norm, torch::Tensor status) {
+  const c10::cuda::CUDAGuard guard(m.device());
+  TORCH_CHECK((int64_t)grads.size() == W && (int64_t)params.size() == W && (int64_t)shadow.size() == W &&
+              (int64_t)sync.size() == W && W <= 8, "peer pointer lists must have one entry per rank (<= 8)");
+  LoomP2P a{};
+  a.W = (int)W; a.rank = (int)rank; a.nblk = nblk;
+  for (int i = 0; i < W; ++i) {
+    a.grads[i] = reinterpret_cast<float*>(grads[i]); a.params[i] = reinterpret_cast<float*>(params[i]);
+    a.shadow[i] = reinterpret_cast<void*>(shadow[i]); a.sync[i] = reinterpret_cast<int*>(sync[i]);
+  }
+  a.mc_grads = reinterpret_cast<float*>(mc_grads);
+  a.m = fptr(m); a.v = fptr(v); a.lr_mult = fptr(lr_mult); a.wd_blk = fptr(wd); a.active = fptr(active);
+  a.hyper = fptr(hyper); a.stats = fptr(stats); a.sumsq_local = fptr(sumsq); a.max_norm = (float)max_norm;
+  a.status = status.data_ptr<int>();
+  int rc = loom_p2p_grad_step(&a, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_p2p_grad_step failed: ", rc);
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -235,6 +256,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("colsum", &colsum, "column sums into an fp32 accumulator");
   m.def("ce", &ce, "cross-entropy over bf16 logits with in-place gradient");
   m.def("temporal_fwd", &temporal_fwd, "temporal carry endpoint + PolARM");
+  m.def("p2p_grad_step", &p2p_grad_step, "fused gradient reduce-scatter + AdamW + parameter all-gather over peer memory");
   m.def("attn", &attn, "dual-context causal GQA attention (forward / backward)");
   m.def("temporal_bwd", &temporal_bwd, "temporal carry endpoint backward");
 }

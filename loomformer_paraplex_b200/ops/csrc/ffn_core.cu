@@ -301,7 +301,7 @@ __device__ __forceinline__ void core_backward_elem(const CoreScalars& S, float x
 
 constexpr int TILE_ROWS = 32;
 
-__global__ void __launch_bounds__(256) ffn_core_bwd_a_kernel(
+__global__ void __launch_bounds__(256, 2) ffn_core_bwd_a_kernel(
     CoreScalars S_in, const __nv_bfloat16* __restrict__ x_real, const __nv_bfloat16* __restrict__ p_in,
     const float* __restrict__ b_real, const __nv_bfloat16* __restrict__ gate_lin,
     const __nv_bfloat16* __restrict__ beta_lin, const float* __restrict__ b_imag, const float* __restrict__ w_trace,

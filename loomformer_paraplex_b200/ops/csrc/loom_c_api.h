@@ -115,6 +115,21 @@ typedef struct {
 int loom_attn_fwd(const LoomAttn* a, cudaStream_t stream);
 int loom_attn_bwd(const LoomAttn* a, cudaStream_t stream);
 
+// ---- fused gradient reduce-scatter + AdamW + parameter all-gather over peer memory (comm.cu) ----
+typedef struct {
+  int W, rank;
+  long long nblk;                 // number of 256-element blocks of the flat buffers
+  float* grads[8]; float* params[8]; void* shadow[8]; int* sync[8];   // peer-mapped symmetric buffers
+  float* mc_grads;                // NVSwitch multicast mapping of the gradient buffers or null
+  float* m; float* v;             // local optimizer moments (full-size; only the own shard is touched)
+  const float* lr_mult; const float* wd_blk; const float* active; const float* hyper;
+  float* stats;                   // [0] norm, [1] clip, [2] finite
+  float* sumsq_local;             // one float, zero before the first call
+  float max_norm;
+  int* status;
+} LoomP2P;
+int loom_p2p_grad_step(const LoomP2P* a, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -57,11 +57,9 @@ def gemm(a_list: List[torch.Tensor], k_len: List[int], b: torch.Tensor, c: torch
     native.count()
 
 
-def optimizer_step(opt) -> None:
-    """Native flat optimizer step (norm -> clip -> AdamW/ATOM -> bf16 shadow), three launches."""
-    ext = native.ext()
-    f = opt.flat
-    dev = f.device
+def upload_hyper(opt) -> torch.Tensor:
+    """Step-dependent optimizer scalars -> device array (async copy from a rotating pinned buffer)."""
+    dev = opt.flat.device
     if not hasattr(opt, "_hyper_dev"):
         opt._hyper_ring = [torch.zeros(8, dtype=torch.float32).pin_memory() for _ in range(8)]
         opt._hyper_dev = torch.zeros(8, dtype=torch.float32, device=dev)
@@ -73,6 +71,14 @@ def optimizer_step(opt) -> None:
     h[4], h[5] = 1.0 - b1 ** t, 1.0 - b2 ** t
     h[6] = 1.0 if (opt.kind == "atom" and t <= opt.bootstrap_steps) else 0.0
     opt._hyper_dev.copy_(h, non_blocking=True)
+    return opt._hyper_dev
+
+
+def optimizer_step(opt) -> None:
+    """Native flat optimizer step (norm -> clip -> AdamW/ATOM -> bf16 shadow), three launches."""
+    ext = native.ext()
+    f = opt.flat
+    upload_hyper(opt)
     atom_out = opt.atom_out if opt.kind == "atom" else None
     ext.grad_norm(f.grads, opt.grad_clip, opt._partial, opt.stats, atom_out)
     if opt.kind == "adamw":

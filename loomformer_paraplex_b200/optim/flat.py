@@ -45,7 +45,9 @@ class Segment:
 class FlatParams:
     """Owns the flat parameter / gradient / bf16-shadow buffers of a model."""
 
-    def __init__(self, model: nn.Module, want_bf16_shadow: bool = False) -> None:
+    def __init__(self, model: nn.Module, want_bf16_shadow: bool = False, alloc=None) -> None:
+        """``alloc(name, numel, dtype, device)`` may supply the backing storage (e.g. peer-mapped symmetric
+        memory for the fused NVLink gradient step); the default is ordinary device memory."""
         seen: Dict[int, str] = {}
         self.segments: List[Segment] = []
         off = 0
@@ -59,9 +61,10 @@ class FlatParams:
         self.total = off
         dev = self.segments[0].param.device
         self.device = dev
-        self.params = torch.zeros(off, dtype=torch.float32, device=dev)
-        self.grads = torch.zeros(off, dtype=torch.float32, device=dev)
-        self.shadow = torch.zeros(off, dtype=torch.bfloat16, device=dev) if want_bf16_shadow else None
+        mk = alloc or (lambda name, n, dt, d: torch.zeros(n, dtype=dt, device=d))
+        self.params = mk("params", off, torch.float32, dev)
+        self.grads = mk("grads", off, torch.float32, dev)
+        self.shadow = mk("shadow", off, torch.bfloat16, dev) if want_bf16_shadow else None
         for s in self.segments:
             view = self.params[s.offset:s.offset + s.numel].view_as(s.param)
             view.copy_(s.param.data)

@@ -25,14 +25,37 @@ from . import dist as pdist
 
 
 class GradSync:
-    def __init__(self, flat, model, backend: str = "collective", anchor_mode: str = "mean") -> None:
+    def __init__(self, flat, model, backend: str = "collective", anchor_mode: str = "mean", symm=None) -> None:
         self.flat, self.model = flat, model
         self.world = dist.get_world_size() if pdist.initialized() else 1
         self.backend = backend if self.world > 1 else "none"
         self.anchor_mode = anchor_mode
+        self.symm = symm
         self._anchors: Optional[List[torch.Tensor]] = None
+        if self.backend == "p2p":
+            if symm is None or flat.shadow is None:
+                raise RuntimeError("grad_sync='p2p' needs symmetric flat buffers on CUDA")
+            dev = flat.device
+            self.sync_words = symm.alloc("sync", 64, torch.int32, dev)
+            self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+            self.use_multimem = False
         if self.world > 1:
             self.broadcast_parameters()
+
+    def fused_step(self, opt) -> None:
+        """Reduce-scatter + clip + AdamW on the own shard + all-gather in three launches over peer memory."""
+        from ..ops import kernels, native
+        if opt.kind != "adamw":
+            raise NotImplementedError("the fused NVLink step implements AdamW; use grad_sync='collective' for ATOM")
+        f, s = self.flat, self.symm
+        opt.step_count += 1
+        hyper = kernels.upload_hyper(opt)
+        mc = s.multicast_ptr("grads") if self.use_multimem else 0
+        native.ext().p2p_grad_step(self.world, dist.get_rank(), f.nblk, s.peer_ptrs("grads"), s.peer_ptrs("params"),
+                                   s.peer_ptrs("shadow"), s.peer_ptrs("sync"), mc, opt.m, opt.v, opt.lr_mult_blk,
+                                   opt.wd_blk, opt.active_blk, hyper, opt.stats, self.sumsq, opt.grad_clip,
+                                   kernels.status_word(f.device))
+        native.count(3)
 
     def broadcast_parameters(self) -> None:
         """Every rank starts from rank 0's weights and buffers (what DDP does at construction)."""

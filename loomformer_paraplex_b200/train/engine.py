@@ -59,12 +59,18 @@ class TrainEngine:
         self.accum = max(1, int(cfg.grad_accum_steps or 1))
         self.amp = cfg.amp_dtype if device.type == "cuda" else "fp32"
         lr_mults = train_lr_overrides(model, cfg)
-        self.flat = FlatParams(model, want_bf16_shadow=(device.type == "cuda"))
+        self.symm = None
+        alloc = None
+        if grad_sync == "p2p" and pdist.initialized() and device.type == "cuda":
+            from ..parallel.symm import SymmetricBuffers
+            self.symm = SymmetricBuffers()
+            alloc = self.symm.alloc
+        self.flat = FlatParams(model, want_bf16_shadow=(device.type == "cuda"), alloc=alloc)
         no_decay = {"tria_agg.pool.logit_scale_raw"}
         self.opt_name = str(optimizer or cfg.optimizer or "adamw").lower()
         self.opt = FlatOptimizer(self.flat, self.opt_name, lr=cfg.lr, weight_decay=cfg.weight_decay,
                                  grad_clip=cfg.grad_clip, no_decay=no_decay, lr_mults=lr_mults)
-        self.sync = GradSync(self.flat, model, backend=grad_sync, anchor_mode=anchor_mode)
+        self.sync = GradSync(self.flat, model, backend=grad_sync, anchor_mode=anchor_mode, symm=self.symm)
         self.plan = model._opset(model.emb.weight) if not model.ablation else None   # fused plan on CUDA
         if self.plan is not None:
             self.plan.bind(self.flat)
@@ -117,9 +123,12 @@ class TrainEngine:
             if fm is not None:
                 self.last_fire_count += fm.sum()
             total = loss.detach() if total is None else total + loss.detach()
-        self.sync.all_reduce_grads()
         self.opt.set_lr(lr_at(self.cfg, self.step_idx))
-        self.opt.step()
+        if self.sync.backend == "p2p":
+            self.sync.fused_step(self.opt)
+        else:
+            self.sync.all_reduce_grads()
+            self.opt.step()
         self.sync.sync_anchors()
         self.step_idx += 1
         return total / float(len(micro))

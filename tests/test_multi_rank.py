@@ -1,0 +1,38 @@
+"""Multi-rank behaviour: gloo ranks on CPU (always), and on >= 2 GPUs the fused NVLink gradient step
+against the NCCL all-reduce + local optimizer baseline."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _launch(mode, out, device_kind, nproc, port):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "mp_worker.py"),
+           mode, out, device_kind]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return torch.load(out)
+
+
+def test_gloo_ddp_two_ranks_stay_in_sync(tmp_path):
+    res = _launch("collective", str(tmp_path / "cpu.pt"), "cpu", 2, 29611)
+    assert res["same"]
+    assert res["losses"][-1] < res["losses"][0]
+
+
+@pytest.mark.gpu
+def test_fused_p2p_step_matches_nccl_baseline(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    a = _launch("collective", str(tmp_path / "nccl.pt"), "cuda", 2, 29612)
+    b = _launch("p2p", str(tmp_path / "p2p.pt"), "cuda", 2, 29613)
+    assert a["same"] and b["same"]
+    diff = float((a["params"] - b["params"]).abs().max())
+    assert diff < 5e-4, diff
+    assert abs(a["losses"][-1] - b["losses"][-1]) < 5e-2
