@@ -263,7 +263,7 @@ class Model(nn.Module):
         return h, carry, states
 
     # ------------------------------------------------------------------ fire plan
-    def fire_plan(self, idx: torch.Tensor, position_ids: torch.Tensor):
+    def fire_plan(self, idx: torch.Tensor, position_ids: torch.Tensor, last_may_fire: bool = False):
         """Reset mask, fire mask and the sorted list of cut columns for a chunked forward.
 
         A row fires at column ``i`` when ``(i+1) % W == 0`` (never at the last column, and not when
@@ -279,7 +279,10 @@ class Model(nn.Module):
             explicit = torch.zeros(B, T, dtype=torch.bool, device=idx.device)
         if self.tria_hard_fire_enabled:
             grid = (torch.arange(T, device=idx.device) + 1).remainder(W).eq(0)
-            grid[-1] = False
+            # A training sequence never fires at its last index.  A prompt that will be continued by the decoder
+            # does (the decoder's rule: fire when the next position starts a new window and still fits).
+            if not (last_may_fire and T < self.d.seq_len):
+                grid[-1] = False
         else:
             grid = torch.zeros(T, dtype=torch.bool, device=idx.device)
         next_reset = torch.zeros_like(reset)
@@ -287,6 +290,8 @@ class Model(nn.Module):
         fire = (grid.view(1, T) & ~next_reset) | explicit
         if self.carry_token_id is None:
             cuts = list(range(W - 1, T - 1, W)) if self.tria_hard_fire_enabled else []
+            if cuts is not None and bool(grid[-1]):
+                cuts.append(T - 1)
         else:
             cuts = (grid | explicit.any(dim=0)).nonzero().flatten().tolist()
         return reset, fire, cuts

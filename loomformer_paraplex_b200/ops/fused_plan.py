@@ -91,8 +91,10 @@ class FusedPlan:
         return torch.zeros((), device=self.model.emb.weight.device, requires_grad=True)
 
     # ------------------------------------------------------------------ the step
-    def run(self, idx, y, position_ids, seg, want_grad: bool, ignore_index: int = -100, grad_scale: float = 1.0):
-        """Forward (and, with ``want_grad``, backward into ``param.grad``).  Returns (loss, logits)."""
+    def run(self, idx, y, position_ids, seg, want_grad: bool, ignore_index: int = -100, grad_scale: float = 1.0,
+            return_state: bool = False):
+        """Forward (and, with ``want_grad``, backward into ``param.grad``).  Returns (loss, logits); with
+        ``return_state`` (inference) additionally the caches a decoder needs to continue the sequences."""
         m, d, K = self.model, self.d, self.K
         B, T = idx.shape
         dev = idx.device
@@ -100,7 +102,7 @@ class FusedPlan:
             position_ids = torch.arange(T, device=dev).view(1, T).expand(B, T)
         chunked = d.tria and d.tria_temporal and not m.ablation
         if chunked:
-            reset, fire, cuts = m.fire_plan(idx, position_ids)
+            reset, fire, cuts = m.fire_plan(idx, position_ids, last_may_fire=return_state)
         else:
             reset, fire, cuts = m._doc_reset(position_ids), None, []
         cut_set = set(cuts)
@@ -134,7 +136,7 @@ class FusedPlan:
                 if seed_valid is not None:
                     local_reset[:, 0] |= seed_valid
                 tape["local_reset"] = local_reset
-                if e != T or (e - 1) in cut_set:
+                if e != T or (e - 1) in cut_set or return_state:
                     fired = fire[:, e - 1] if (e - 1) in cut_set else None
                     temporal, tape["t_aux"] = K.temporal_fwd(tape["depth"], B, e - s, d.hidden, local_reset, temporal,
                                                              fired, m.d_polarm_beta)
@@ -157,6 +159,17 @@ class FusedPlan:
             h = ro["h_out"]
         hn = K.rms_norm_fwd(h, m.ln_final.weight) if m.ln_final is not None else h
         logits = K.linear(hn.reshape(B * T, d.n), self.w(m.head.weight)).view(B, T, d.vocab)
+        if return_state:
+            state = {"kc": kc, "vc": vc, "traces": traces, "temporal": temporal, "n_keys": len(keys),
+                     "pending": fire[:, T - 1] if (chunked and fire is not None) else None}
+            if temporal is None and chunked:
+                state["pending"] = None
+            if ro is not None:
+                Kn = len(keys)
+                state["ca_k"], state["ca_v"], state["ca_valid"] = ro["k"], ro["v"], torch.stack(key_valid, 1)
+            if chunked and state["pending"] is None:
+                state["pending"] = torch.zeros(B, dtype=torch.bool, device=dev)
+            return None, logits, state
         if y is None:
             return None, logits
         loss, dlogits = K.ce_fwd_bwd(logits.view(B * T, d.vocab), y.reshape(-1), ignore_index,

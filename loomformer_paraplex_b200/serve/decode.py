@@ -1,0 +1,270 @@
+"""Graph-replayed incremental decoding.
+
+``DecodeEngine`` keeps every piece of per-sequence state in preallocated device tensors (KV caches, per-layer phase
+traces, the Tria temporal carrier, the sparse final cross-attention key cache) and advances all sequences of a batch
+by one token per call.  The step contains no host-side control flow -- the shared position, the fire decision, the
+conditional key append and the greedy/top-k choice are all device-side -- so it is captured once in a CUDA graph and
+replayed per token.  The reference decodes with a Python loop of ~25 launches per layer plus several ``.item()``
+synchronisations per token and prefills token by token (reference ``loomformer.py:3951-4091``, ``loomchat.py:338-380``).
+
+Prefill runs the prompt through the chunked fused forward once and converts its caches into decode state.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from ..config import FANIN_GAIN
+from ..ops import reference as R
+
+
+class DecodeEngine:
+    def __init__(self, model, batch: int, max_len: Optional[int] = None, use_graph: bool = True,
+                 dtype: Optional[torch.dtype] = None) -> None:
+        self.m, self.d = model, model.d
+        d = self.d
+        self.B = int(batch)
+        self.S = int(max_len or d.seq_len)
+        dev = model.emb.weight.device
+        self.dev = dev
+        self.dt = dtype or (torch.bfloat16 if dev.type == "cuda" else torch.float32)
+        self.use_graph = bool(use_graph and dev.type == "cuda")
+        B, S, L = self.B, self.S, d.layers
+        z = lambda *s, dtype=None: torch.zeros(*s, dtype=dtype or self.dt, device=dev)
+        self.kc, self.vc = z(L, B, S, d.kvh, d.hd), z(L, B, S, d.kvh, d.hd)
+        self.trace = z(L, B, d.hidden, dtype=torch.float32)
+        self.carry = z(B, d.hidden, 3, 3, dtype=torch.float32)
+        self.have_carry = z(1, dtype=torch.bool)
+        self.pending = z(B, dtype=torch.bool)
+        self.ca_k, self.ca_v = z(B, S, d.n), z(B, S, d.n)
+        self.ca_valid = z(B, S, dtype=torch.bool)
+        self.ca_len = z(1, dtype=torch.long)
+        self.pos = z(1, dtype=torch.long)
+        self.tok_in = z(B, dtype=torch.long)
+        self.logits = z(B, d.vocab, dtype=torch.float32)
+        self.next_tok = z(B, dtype=torch.long)
+        self._graph = None
+        self._w = {}
+        self.refresh_weights()
+
+    # ------------------------------------------------------------------ weights in the compute dtype
+    def refresh_weights(self) -> None:
+        self._w = {id(p): p.detach().to(self.dt) for p in self.m.parameters()}
+
+    def w(self, p):
+        return self._w[id(p)]
+
+    # ------------------------------------------------------------------ state management
+    def reset(self) -> None:
+        for t in (self.kc, self.vc, self.trace, self.carry, self.ca_k, self.ca_v):
+            t.zero_()
+        self.have_carry.zero_(); self.pending.zero_(); self.ca_valid.zero_(); self.ca_len.zero_(); self.pos.zero_()
+
+    @torch.no_grad()
+    def prefill(self, prompt: torch.Tensor) -> torch.Tensor:
+        """Ingest ``prompt`` [B, T0] (equal lengths) and return the logits of its last position [B, V]."""
+        self.reset()
+        B, T0 = prompt.shape
+        assert B == self.B and T0 <= self.S
+        plan = self.m._opset(self.m.emb.weight)
+        if plan is not None and not self.m.ablation:
+            _, logits, st = plan.run(prompt, None, None, None, want_grad=False, return_state=True)
+            L = self.d.layers
+            for l in range(L):
+                self.kc[l, :, :T0] = st["kc"][l][:, :T0]
+                self.vc[l, :, :T0] = st["vc"][l][:, :T0]
+                self.trace[l] = st["traces"][l].float()
+            if st["temporal"] is not None:
+                self.carry.copy_(st["temporal"].view(B, self.d.hidden, 3, 3))
+                self.have_carry.fill_(True)
+                self.pending.copy_(st["pending"])
+            n = st["n_keys"]
+            if n:
+                self.ca_k[:, :n], self.ca_v[:, :n] = st["ca_k"], st["ca_v"]
+                self.ca_valid[:, :n] = st["ca_valid"]
+            self.ca_len.fill_(n)
+            self.pos.fill_(T0)
+            return logits[:, -1].float()
+        out = None
+        for t in range(T0):
+            out = self.step(prompt[:, t])
+        return out
+
+    # ------------------------------------------------------------------ one token
+    @torch.no_grad()
+    def step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """Feed ``tokens`` [B] at the current position; returns logits [B, V] (a view that the next call overwrites)."""
+        self.tok_in.copy_(tokens)
+        if not self.use_graph:
+            self._step_impl()
+            return self.logits
+        if self._graph is None:
+            # warm-up on a side stream (allocator / lazy init), with state restored afterwards
+            snap = [t.clone() for t in self._state()]
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._step_impl()
+            torch.cuda.current_stream().wait_stream(s)
+            for t, c in zip(self._state(), snap):
+                t.copy_(c)
+            self._graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self._graph):
+                self._step_impl()
+            for t, c in zip(self._state(), snap):
+                t.copy_(c)
+        self._graph.replay()
+        return self.logits
+
+    def _state(self):
+        return [self.kc, self.vc, self.trace, self.carry, self.have_carry, self.pending, self.ca_k, self.ca_v,
+                self.ca_valid, self.ca_len, self.pos]
+
+    def _lin(self, x, p, bias=None):
+        y = F.linear(x, self.w(p))
+        return y if bias is None else y + self.w(bias)
+
+    def _step_impl(self) -> None:
+        m, d = self.m, self.d
+        B, S, dt = self.B, self.S, self.dt
+        pos = self.pos                                   # [1]
+        h = self.w(m.emb.weight)[self.tok_in]            # [B, N]
+        cos = m.rope_cos.index_select(0, pos).to(dt).view(1, 1, d.hd)
+        sin = m.rope_sin.index_select(0, pos).to(dt).view(1, 1, d.hd)
+        key_ok = (torch.arange(S, device=self.dev) <= pos).view(1, 1, S)
+        da = m.depth_attn
+        scale = 1.0 / math.sqrt(d.hd)
+
+        def project(x):
+            kv = self._lin(x, da.kv_weight)
+            k, v = kv[:, :d.n].view(B, d.qh, d.hd), kv[:, d.n:].view(B, d.qh, d.hd)
+            if d.depth_qkv_rms:
+                k, v = R.fixed_rms(k, FANIN_GAIN), R.fixed_rms(v, FANIN_GAIN * d.deepnorm_beta)
+            return k, v
+
+        hist_k, hist_v = [], []
+        k0, v0 = project(h)
+        hist_k.append(k0); hist_v.append(v0)
+
+        def read(sub):
+            q = da.query(sub).to(dt)
+            hk, hv = torch.stack(hist_k), torch.stack(hist_v)          # [n,B,QH,HD]
+            wts = torch.softmax((hk.float() * q.float()).sum(-1) * scale, dim=0)
+            mm = (wts.unsqueeze(-1) * hv.float()).sum(0).to(dt)
+            return F.linear(mm.reshape(B, d.n), self.w(da.w_o_weight)[sub] if da.w_o is None else self.w(da.w_o.weight)), mm
+
+        cap = (lambda t: R.capped_rms(t, d.branch_rms_cap)) if (d.branch_rms_cap is not None and m.decode_applies_rms_cap) else (lambda t: t)
+        is_bos = pos.eq(0)
+        seed_valid = self.pending & ~is_bos & self.have_carry
+        carry_c, p_in = None, None
+        use_tria = d.tria and not m.ablation
+        for bi, blk in enumerate(m.blocks):
+            last = bi == d.layers - 1
+            qkv = self._lin(h, blk.attn.qkv_weight)
+            q = R.apply_rope(qkv[:, :d.n].view(B, d.qh, d.hd), cos, sin)
+            k = R.apply_rope(qkv[:, d.n:d.n + d.kv_dim].view(B, d.kvh, d.hd), cos, sin)
+            v = qkv[:, d.n + d.kv_dim:].view(B, d.kvh, d.hd)
+            self.kc[bi].index_copy_(1, pos, k.unsqueeze(1))
+            self.vc[bi].index_copy_(1, pos, v.unsqueeze(1))
+            kk = self.kc[bi].view(B, S, d.kvh, 1, d.hd).expand(B, S, d.kvh, d.group, d.hd).reshape(B, S, d.qh, d.hd)
+            vv = self.vc[bi].view(B, S, d.kvh, 1, d.hd).expand(B, S, d.kvh, d.group, d.hd).reshape(B, S, d.qh, d.hd)
+            sc = torch.einsum("bhd,bshd->bhs", q.float(), kk.float()) * scale
+            a = torch.softmax(sc.masked_fill(~key_ok, float("-inf")), dim=-1)
+            k_ctx = torch.einsum("bhs,bshd->bhd", a, kk.float()).to(dt)
+            c = torch.einsum("bhs,bshd->bhd", a, vv.float()).to(dt)
+            attn_out = self._lin(c.reshape(B, d.n), blk.attn.o.weight)
+            sub = 2 * bi
+            skip, _ = read(sub)
+            u = F.layer_norm((cap(skip) + cap(attn_out)).float(), (d.n,), blk.ln_attn.weight, blk.ln_attn.bias).to(dt)
+            ku, vu = project(u)
+            hist_k.append(ku); hist_v.append(vu)
+            skip2, d_sel = read(sub + 1)
+            ffn = blk.ffn
+            wx = self._lin(u, ffn.w1_real.weight)
+            if ffn.identity_gate is not None and p_in is not None:
+                r = wx * (1.0 + ffn.identity_gate.alpha().to(dt) * p_in) + self.w(ffn.w1_real.bias)
+            else:
+                r = wx + self.w(ffn.w1_real.bias)
+            gsrc = self._lin(u, ffn.gate_proj.weight, ffn.gate_proj.bias) if ffn.gate_proj is not None else r
+            w3 = self.w(ffn.w1_imag).view(d.qh, d.hpq, d.imag_in)
+            if d.open_sectors:
+                shared = torch.cat((k_ctx.reshape(B, d.n), c.reshape(B, d.n), u, d_sel.reshape(B, d.n)), -1)
+                a_in = torch.cat((q, shared.unsqueeze(1).expand(B, d.qh, 4 * d.n)), -1)
+            else:
+                a_in = torch.cat((q, k_ctx, c, u.unsqueeze(1).expand(B, d.qh, d.n), d_sel), -1)
+            beta = (torch.einsum("bgk,ghk->bgh", a_in, w3).reshape(B, d.hidden).float() + ffn.w1_imag_bias)
+            s0 = torch.sin(R.HALF_PI * beta * torch.rsqrt(1.0 + beta * beta))
+            prev = torch.where(is_bos, torch.zeros_like(self.trace[bi]), self.trace[bi])
+            zz = s0 + prev * ffn.w1_imag_trace
+            i_sq = zz * torch.rsqrt(1.0 + zz * zz)
+            self.trace[bi].copy_(s0)
+            amp = F.softplus(gsrc.float())
+            rf = r.float()
+            if m.ablation:
+                p_act = rf + amp
+            else:
+                p_act = rf + amp * i_sq
+            o = (p_act * R.powlu_gate(amp, d.powlu_m)) if d.activation == "pvpowlu" else (
+                F.gelu(p_act) if d.activation == "gelu" else R.powlu(p_act, d.powlu_m))
+            if use_tria:
+                t3 = R.build_tria(rf, i_sq, o, m.tria_alpha, bi % 3)                      # [B,H,3,3]
+                if bi == 0:
+                    pre = torch.where(seed_valid[:, None, None, None], torch.matmul(t3, self.carry), t3)
+                else:
+                    pre = torch.matmul(t3, carry_c)
+                carry_c = R.normalize9(pre)
+                p_in = None if last else (carry_c.reshape(B, d.hidden, 9) * ffn.gate_selector.weights()).sum(-1).to(dt)
+            f = self._lin(o.to(dt), ffn.w2.weight, ffn.w2.bias)
+            h = F.layer_norm((cap(skip2) + cap(f)).float(), (d.n,), blk.ln_ffn.weight, blk.ln_ffn.bias).to(dt)
+            if not last:
+                kh, vh = project(h)
+                hist_k.append(kh); hist_v.append(vh)
+        if use_tria:
+            reset_now = self.pending | is_bos | (not d.tria_temporal) | ~self.have_carry
+            cont = R.normalize9(torch.matmul(carry_c, self.carry))
+            doc = torch.where(reset_now[:, None, None, None], carry_c, cont)
+            W = m.tria_window
+            hard = ((pos + 1) % W == 0) & (pos + 1 < d.seq_len) & bool(m.tria_hard_fire_enabled)
+            fire = hard.expand(B)
+            if m.carry_token_id is not None:
+                fire = fire | self.tok_in.eq(int(m.carry_token_id))
+            doc = torch.where(fire[:, None, None, None], R.polarm(doc, m.d_polarm_beta), doc)
+            fca, agg = m.tria_final_ca, m.tria_agg
+            a_t = agg(doc.unsqueeze(1)).to(dt)[:, 0]                                   # [B,N]
+            any_fire = fire.any()
+            slot = self.ca_len.clamp(max=S - 1)
+            newk, newv = self._lin(a_t, fca.w_qk.weight), self._lin(a_t, fca.w_v.weight)
+            oldk, oldv = self.ca_k.index_select(1, slot), self.ca_v.index_select(1, slot)
+            oldm = self.ca_valid.index_select(1, slot)
+            self.ca_k.index_copy_(1, slot, torch.where(any_fire, newk.unsqueeze(1), oldk))
+            self.ca_v.index_copy_(1, slot, torch.where(any_fire, newv.unsqueeze(1), oldv))
+            self.ca_valid.index_copy_(1, slot, torch.where(any_fire, fire.unsqueeze(1), oldm))
+            self.ca_len.add_(any_fire.long())
+            allowed = self.ca_valid & (torch.arange(S, device=self.dev).view(1, S) < self.ca_len)
+            qv = self._lin(h, fca.w_qk.weight)
+            out = R.masked_cross_attention(qv.float().unsqueeze(1), self.ca_k.float(), self.ca_v.float(),
+                                           allowed.unsqueeze(1), fca.scale)[:, 0]
+            h = (h.float() + fca.gamma() * out).to(dt)
+            self.carry.copy_(doc)
+            self.pending.copy_(fire)
+            self.have_carry.fill_(True)
+        hn = m.ln_final(h) if m.ln_final is not None else h
+        self.logits.copy_(F.linear(hn.to(dt), self.w(m.head.weight)).float())
+        self.next_tok.copy_(self.logits.argmax(-1))
+        self.pos.add_(1)
+
+    # ------------------------------------------------------------------ convenience
+    @torch.no_grad()
+    def generate(self, prompt: torch.Tensor, max_new: int) -> torch.Tensor:
+        """Greedy continuation of an equal-length prompt batch; returns ``[B, max_new]`` token ids."""
+        logits = self.prefill(prompt)
+        tok = logits.argmax(-1)
+        out = [tok]
+        for _ in range(max_new - 1):
+            self.step(tok)
+            tok = self.next_tok.clone()
+            out.append(tok)
+        return torch.stack(out, dim=1)

@@ -1,0 +1,53 @@
+"""Decode engine: token-by-token equals Model.step, and batched prefill through the fused plan hands over a state
+from which decoding continues exactly as if every prompt token had been stepped."""
+import pytest
+import torch
+
+from loomformer_paraplex_b200.config import Config
+from loomformer_paraplex_b200.models.loomformer import Model
+from loomformer_paraplex_b200.ops.fused_plan import FusedPlan
+from loomformer_paraplex_b200.ops.twins import TorchKernels
+from loomformer_paraplex_b200.serve.decode import DecodeEngine
+
+KW = dict(vocab=61, seq_len=40, model_dim=None, n_q_heads=4, head_dim=8, n_kv_heads=2, hidden=None, hidden_mult=3.0,
+          layers=3, activation="pvpowlu", tied_embeddings=False, tria_carry_enabled=True, tria_temporal_auto=False,
+          tria_temporal_window=6, tria_carrier_alpha=0.05, tria_gamma_max=0.8, tria_raw_gamma_init=0.25)
+
+
+def _model(**extra):
+    torch.manual_seed(0)
+    m = Model(Config(**dict(KW, **extra))).eval()
+    with torch.no_grad():
+        for _, p in m.named_parameters():
+            if p.abs().max() == 0:
+                p.normal_(0.0, 0.2)
+    return m
+
+
+@pytest.mark.parametrize("extra", [dict(), dict(phase_sectors="open", paraplex_gate_proj=True, depth_attn_qkv_rms=True,
+                                                depth_attn_readout="per-sublayer", final_norm=True)])
+def test_engine_step_equals_model_step(extra):
+    m = _model(**extra)
+    x = torch.randint(0, 61, (2, 25))
+    eng = DecodeEngine(m, batch=2, use_graph=False)
+    st = None
+    for t in range(25):
+        ref, st = m.step(x[:, t], t, st)
+        got = eng.step(x[:, t])
+        assert torch.allclose(ref, got, atol=3e-5, rtol=1e-4), (t, float((ref - got).abs().max()))
+
+
+@pytest.mark.parametrize("T0", [11, 12, 18, 7])
+def test_prefill_then_decode_matches_stepping(T0):
+    m = _model()
+    x = torch.randint(0, 61, (2, 30))
+    ref = DecodeEngine(m, batch=2, use_graph=False)
+    for t in range(T0):
+        last = ref.step(x[:, t]).clone()
+    m.ops = FusedPlan(m, kernels=TorchKernels(), compute_dtype=torch.float32)
+    eng = DecodeEngine(m, batch=2, use_graph=False)
+    got = eng.prefill(x[:, :T0])
+    assert torch.allclose(last, got, atol=5e-5, rtol=1e-4), float((last - got).abs().max())
+    for t in range(T0, 30):
+        a, b = ref.step(x[:, t]), eng.step(x[:, t])
+        assert torch.allclose(a, b, atol=5e-5, rtol=1e-4), (t, float((a - b).abs().max()))
