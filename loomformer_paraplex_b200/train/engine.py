@@ -54,11 +54,12 @@ def train_lr_overrides(model, cfg: Config) -> Dict[str, float]:
 
 class TrainEngine:
     def __init__(self, cfg: Config, model, device: torch.device, *, optimizer: Optional[str] = None,
-                 grad_sync: str = "collective", anchor_mode: str = "mean", loss_mask_ignore: int = -100) -> None:
+                 grad_sync: str = "collective", anchor_mode: str = "mean", loss_mask_ignore: int = -100,
+                 train_lr: bool = True) -> None:
         self.cfg, self.model, self.device = cfg, model, device
         self.accum = max(1, int(cfg.grad_accum_steps or 1))
         self.amp = cfg.amp_dtype if device.type == "cuda" else "fp32"
-        lr_mults = train_lr_overrides(model, cfg)
+        lr_mults = train_lr_overrides(model, cfg) if train_lr else {}
         self.symm = None
         alloc = None
         if grad_sync == "p2p" and pdist.initialized() and device.type == "cuda":
@@ -103,21 +104,25 @@ class TrainEngine:
         self.flat.zero_grad()
         total = None
         for mb in micro:
-            mb = self.to_device(mb)
-            if targets is None:
+            if isinstance(mb, dict):     # a packed micro-batch carrying its own targets and reset state
+                x, y = self.to_device(mb["x"]), self.to_device(mb["y"])
+                position_ids, segment_ids = mb.get("position_ids"), mb.get("segment_ids")
+            elif targets is None:
+                mb = self.to_device(mb)
                 x, y = mb[:, :-1], mb[:, 1:]
             else:
-                x, y = mb, self.to_device(targets)
+                x, y = self.to_device(mb), self.to_device(targets)
+            mask_i = attn_mask
             if self.plan is not None and attn_mask is None:
                 with torch.no_grad():
                     loss, _ = self.plan.run(x, y, position_ids, segment_ids, want_grad=True,
                                             ignore_index=self.ignore_index, grad_scale=1.0 / float(len(micro)))
             else:
-                if segment_ids is not None and attn_mask is None:
+                if segment_ids is not None and mask_i is None:
                     T = x.shape[1]
-                    attn_mask = ((segment_ids[:, :, None] == segment_ids[:, None, :])
-                                 & torch.ones(T, T, dtype=torch.bool, device=x.device).tril()).unsqueeze(1)
-                loss = self.loss_fn(x, y, attn_mask, position_ids)
+                    mask_i = ((segment_ids[:, :, None] == segment_ids[:, None, :])
+                              & torch.ones(T, T, dtype=torch.bool, device=x.device).tril()).unsqueeze(1)
+                loss = self.loss_fn(x, y, mask_i, position_ids)
                 (loss / float(len(micro))).backward()
             fm = self.model.last_tria_fire_mask
             if fm is not None:

@@ -199,11 +199,13 @@ def train(cfg: Config, dataset: str, device: torch.device, ckpt_out: Optional[st
             w0 = time.time()
             micro = [stream.next_batch() for _ in range(accum)]
             data_wait += time.time() - w0
-            pos, seg = doc_reset_state(micro[0][:, :-1], eos_id)
-            if accum > 1 and eos_id is not None:
-                raise NotImplementedError("grad_accum_steps > 1 with document resets: call engine.step per micro-batch")
-            loss = engine.step(micro if accum > 1 else micro[0], position_ids=pos if seg is not None else None,
-                               segment_ids=seg)
+            packed = []
+            for mb in micro:
+                mb = engine.to_device(mb)
+                pos, seg = doc_reset_state(mb[:, :-1], eos_id)
+                packed.append({"x": mb[:, :-1], "y": mb[:, 1:], "position_ids": pos if seg is not None else None,
+                               "segment_ids": seg})
+            loss = engine.step(packed)
             tokens_step = sum(int(b[:, 1:].numel()) for b in micro)
             if step == 1 or step % log_every == 0 or step == int(cfg.steps):
                 engine.check_finite(loss)

@@ -84,3 +84,27 @@ def test_checkpoint_loads_in_reference_and_back(workdir):
     x = torch.randint(0, 300, (2, 40))
     with torch.no_grad():
         assert torch.allclose(ref.eval()(x), mine(x), atol=3e-5, rtol=1e-4)
+
+
+def test_sft_train_and_resume(workdir):
+    """Fine-tune the pre-trained checkpoint on chat records, stop at a run-point, resume from it."""
+    d = str(workdir)
+    if not os.path.exists(os.path.join(d, "m.pt")):
+        pytest.skip("training test did not run")
+    rng = np.random.default_rng(1)
+    with open(os.path.join(d, "chat.jsonl"), "w") as fh:
+        for i in range(40):
+            fh.write(json.dumps({"messages": [
+                {"role": "user", "content": " ".join(rng.choice(WORDS, 5))},
+                {"role": "assistant", "content": " ".join(rng.choice(WORDS, 6))}]}) + "\n")
+    sft = os.path.join(ROOT, "loomsft.py")
+    out = run([sft, "--smoke-test"], d)
+    assert "[loomsft smoke] OK" in out
+    out = run([sft, "--config", "cfg.yaml", "--sft-dataset", "chat.jsonl", "--val-dataset", "chat.jsonl",
+               "--init-checkpoint", "m.pt", "--checkpoint", "s.pt", "--device", "cpu"], d)
+    assert "[loomsft] step      4" in out and "eval_loss" in out and "[loomsft] saved -> s.pt" in out
+    assert os.path.exists(os.path.join(d, "s.runpoint_step4.pt"))
+    out = run([sft, "--config", "cfg.yaml", "--sft-dataset", "chat.jsonl", "--resume", "s.runpoint_step4.pt",
+               "--checkpoint", "s2.pt", "--device", "cpu"], d)
+    assert "continuing from step 4/6" in out
+    assert torch.load(os.path.join(d, "s2.pt"), weights_only=True)["step"] == 6
