@@ -53,9 +53,15 @@ class DecodeEngine:
     # ------------------------------------------------------------------ weights in the compute dtype
     def refresh_weights(self) -> None:
         self._w = {id(p): p.detach().to(self.dt) for p in self.m.parameters()}
+        self._graph = None
 
     def w(self, p):
         return self._w[id(p)]
+
+    def invalidate(self) -> None:
+        """Drop the captured graph: call after changing a hyper-parameter that the step bakes in as a constant
+        (temporal window, carrier alpha, PolARM beta) or after ``refresh_weights`` replaced the weight copies."""
+        self._graph = None
 
     # ------------------------------------------------------------------ state management
     def reset(self) -> None:

@@ -96,8 +96,17 @@ def checkpoint_cfg(cfg) -> Dict[str, Any]:
 
 def save_checkpoint(path: str, cfg, model, optimizer, optimizer_name: str, step: int, tokens_seen: int,
                     ablation: bool = False) -> None:
+    # parameters are views into one flat buffer: clone each so the file holds tensors, not the whole buffer per
+    # entry, while tensors that alias each other (tied embeddings) stay one tensor in the file
+    copies: Dict[Any, torch.Tensor] = {}
+    state = {}
+    for k, v in model.state_dict().items():
+        key = (v.data_ptr(), tuple(v.shape), tuple(v.stride()), v.dtype)
+        if key not in copies:
+            copies[key] = v.detach().clone().cpu()
+        state[k] = copies[key]
     blob = {"cfg": checkpoint_cfg(cfg), "model_kind": "loomformer", "ffn_type": "paraplex", "ablation": bool(ablation),
-            "model": {k: v.detach().clone().cpu() for k, v in model.state_dict().items()},
+            "model": state,
             "optimizer_name": optimizer_name, "optimizer": None if optimizer is None else optimizer.state_dict(),
             "step": int(step), "tokens_seen": int(tokens_seen)}
     tmp = path + f".tmp.{os.getpid()}"

@@ -1,0 +1,141 @@
+"""Packaging (.aio), chat session, sampler and stream renderer on CPU."""
+import io
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from loomformer_paraplex_b200.config import Config
+from loomformer_paraplex_b200.data.tokenizers import BPETokenizer, train_tokenizer
+from loomformer_paraplex_b200.models.loomformer import Model
+from loomformer_paraplex_b200.serve import chat as ch
+from loomformer_paraplex_b200.serve import package as pk
+from loomformer_paraplex_b200.train import checkpoint as ckpt
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+WORDS = "alpha beta gamma delta epsilon zeta eta theta iota kappa lambda mu".split()
+
+
+@pytest.fixture(scope="module")
+def packed(tmp_path_factory):
+    d = tmp_path_factory.mktemp("pack")
+    tokp = str(d / "tok.json")
+    train_tokenizer("", 320, tokp, texts=[" ".join(WORDS)] * 50)
+    tok = BPETokenizer.load(tokp)
+    cfg = Config(vocab=tok.vocab_size, tokenizer=tokp, seq_len=96, model_dim=64, n_q_heads=4, n_kv_heads=2, hidden=1024,
+                 layers=2, activation="pvpowlu", tria_carry_enabled=True, tria_temporal_auto=False,
+                 tria_temporal_window=16, tied_embeddings=True)
+    torch.manual_seed(0)
+    model = Model(cfg)
+    ckpt.save_checkpoint(str(d / "m.pt"), cfg, model, None, "adamw", 3, 123)
+    return d, tok, cfg, model
+
+
+def test_pack_quantises_only_large_matrices_and_keeps_aliases(packed):
+    d, tok, cfg, model = packed
+    out = str(d / "m.aio")
+    man = pk.build_package(str(d / "m.pt"), str(d / "tok.json"), os.path.join(ROOT, "chat_template.jinja"), out, "bf16",
+                           min_quant_elements=4096)
+    pkg = pk.load_aio(out)
+    st = pkg["checkpoint"]["model"]
+    assert pkg["format"] == "loom.aio" and pkg["version"] == 1 and "optimizer" not in pkg["checkpoint"]
+    assert st["emb.weight"].dtype == torch.bfloat16
+    assert st["emb.weight"].data_ptr() == st["head.weight"].data_ptr()          # tie survives packing
+    for name, t in st.items():
+        if t.is_floating_point() and (t.ndim < 2 or "norm" in name or "beta_anchor" in name or name.endswith(".bias")):
+            assert t.dtype == torch.float32, name
+    q = man["quantization"]
+    assert q["changed_tensors"] > 0 and q["packed_tensor_bytes"] < q["source_bytes"] and q["decisions"]["alias"] == 1
+    assert man["assets"]["tokenizer"]["bytes"] == os.path.getsize(d / "tok.json")
+    with pytest.raises(ValueError):
+        pk.parse_quant("int3")
+
+
+def test_pack_cli_roundtrip_and_reference_reads_it(packed):
+    d, *_ = packed
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    tool = os.path.join(ROOT, "loompack.py")
+    r = subprocess.run([sys.executable, tool, "pack", "m.pt", "--tokenizer", "tok.json", "--template",
+                        os.path.join(ROOT, "chat_template.jinja"), "-o", "cli.aio", "--quant", "fp16"], cwd=d, env=env,
+                       capture_output=True, text=True)
+    assert r.returncode == 0 and "[loompack] cli.aio:" in r.stdout and "quant=fp16" in r.stdout, r.stderr
+    r = subprocess.run([sys.executable, tool, "inspect", "cli.aio", "--keys"], cwd=d, env=env, capture_output=True, text=True)
+    assert '"format": "loom.aio"' in r.stdout and "emb.weight" in r.stdout
+    r = subprocess.run([sys.executable, tool, "extract", "cli.aio", "-d", "x"], cwd=d, env=env, capture_output=True, text=True)
+    assert r.returncode == 0 and sorted(os.listdir(d / "x")) == ["chat_template.jinja", "manifest.json", "model.pt", "tokenizer.json"]
+    r = subprocess.run([sys.executable, tool, "inspect", "m.pt"], cwd=d, env=env, capture_output=True, text=True)
+    assert r.returncode == 1 and "loompack:" in r.stderr
+    # the reference's own loader accepts the archive
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if os.path.isdir(ref):
+        code = ("import sys; sys.path.insert(0, %r); import loompack; p = loompack.load_aio('cli.aio'); "
+                "print(p['manifest']['model']['state_keys'])" % ref)
+        r = subprocess.run([sys.executable, "-c", code], cwd=d, capture_output=True, text=True)
+        assert r.returncode == 0 and int(r.stdout.strip()) > 10, r.stderr
+
+
+def test_sampler():
+    logits = torch.tensor([0.0, 5.0, 1.0, 4.9])
+    assert ch.sample_next(logits, 0.0, 0, 0.0) == 1
+    g = torch.Generator().manual_seed(0)
+    draws = {ch.sample_next(logits, 1.0, 2, 0.0, g) for _ in range(200)}
+    assert draws == {1, 3}
+    draws = {ch.sample_next(logits, 1.0, 0, 0.5, g) for _ in range(200)}
+    assert draws <= {1, 3} and 1 in draws
+    assert {ch.sample_next(logits, 1.0, 0, 1e-6, g) for _ in range(20)} == {1}
+
+
+def test_stream_renderer_dims_think_and_buffers_tool_calls():
+    buf = io.StringIO()
+    r = ch.StreamRenderer(buf)
+    full = 'hi <think>plan</think>ok <tool_call>{"name": "f"}</tool_call> done'
+    for i in range(1, len(full) + 1, 3):
+        r.feed(full[:i])
+    r.feed(full)
+    r.flush()
+    out = buf.getvalue()
+    assert "<think>" not in out and "<tool_call>" not in out
+    assert "tool_call: {\"name\": \"f\"}" in out and out.startswith("hi ") and out.rstrip().endswith("done")
+
+
+def test_chat_session_generates_and_applies_settings(packed):
+    d, tok, cfg, model = packed
+    out = str(d / "chat.aio")
+    pk.build_package(str(d / "m.pt"), str(d / "tok.json"), os.path.join(ROOT, "chat_template.jinja"), out, "none")
+    s = ch.Settings(device="cpu", dtype="fp32", temperature=0.0, top_k=0, top_p=0.9, max_new=6, window=0, alpha=0.05, beta=0.1)
+    sess = ch.ChatSession(out, s)
+    assert s.window == 16 and abs(s.alpha - cfg.tria_carrier_alpha) < 1e-12
+    msgs = [{"role": "user", "content": "alpha beta"}]
+    buf = io.StringIO()
+    reply, interrupted = sess.generate_turn(msgs, out=buf)
+    assert reply["role"] == "assistant" and not interrupted
+    # greedy engine output equals the model's own token-by-token step path
+    ids = sess.chat.render_prompt_ids(msgs)
+    st, lg = None, None
+    with torch.no_grad():
+        for p, t in enumerate(ids):
+            lg, st = sess.model.step(torch.tensor([t]), p, st)
+        want = []
+        for i in range(6):
+            n = int(lg[0].argmax())
+            if n in sess.chat.stop_ids:
+                break
+            want.append(n)
+            lg, st = sess.model.step(torch.tensor([n]), len(ids) + i, st)
+    assert reply["content"] == tok.decode(want, skip_special_tokens=True) or reply.get("tool_calls")
+    assert sess.set("beta", "1.5") is not None and sess.set("alpha", "-1") is not None and sess.set("window", "0") is not None
+    assert sess.set("window", "8") is None and sess.cfg.tria_temporal_window == 8
+    assert sess.set("beta", "0.2") is None and sess.cfg.tria_polarm_beta == 0.2
+    assert sess.set("dtype", "int8") is not None and sess.set("top_k", "x") == "couldn't parse 'x' for top_k"
+    assert sess.set("device", "cuda:0") is not None or torch.cuda.is_available()
+    handled, leave = ch.handle_command("/reset", sess, msgs)
+    assert handled and not leave and msgs == []
+    assert ch.handle_command("/system be brief", sess, msgs) == (True, False) and msgs[0]["role"] == "system"
+    assert ch.handle_command("/ex", sess, msgs) == (True, True)
+    assert ch.handle_command("/temperature 0.3", sess, msgs) == (True, False) and s.temperature == 0.3
+    assert ch.handle_command("hello", sess, msgs) == (False, False)
+    with pytest.raises(ValueError):
+        ch.load_aio(str(d / "m.pt"), torch.device("cpu"))
