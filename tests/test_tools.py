@@ -139,3 +139,92 @@ def test_chat_session_generates_and_applies_settings(packed):
     assert ch.handle_command("hello", sess, msgs) == (False, False)
     with pytest.raises(ValueError):
         ch.load_aio(str(d / "m.pt"), torch.device("cpu"))
+
+
+def _fake_llama(d, hidden_size=32, heads=4, kv=2, inter=86, layers=2, vocab=64):
+    import json as js
+    from loomformer_paraplex_b200.tools import cloner as cl
+    os.makedirs(d, exist_ok=True)
+    js.dump({"architectures": ["LlamaForCausalLM"], "hidden_size": hidden_size, "num_attention_heads": heads,
+             "num_key_value_heads": kv, "num_hidden_layers": layers, "vocab_size": vocab, "rope_theta": 10000.0,
+             "max_position_embeddings": 64, "tie_word_embeddings": True, "intermediate_size": inter,
+             "_name_or_path": "tiny/llama"}, open(os.path.join(d, "config.json"), "w"))
+    g = torch.Generator().manual_seed(0)
+    hd = hidden_size // heads
+    T = {"model.embed_tokens.weight": torch.randn(vocab, hidden_size, generator=g).bfloat16(),
+         "model.norm.weight": torch.ones(hidden_size).bfloat16()}
+    for i in range(layers):
+        p = f"model.layers.{i}."
+        T[p + "input_layernorm.weight"] = torch.rand(hidden_size, generator=g).bfloat16()
+        T[p + "post_attention_layernorm.weight"] = torch.rand(hidden_size, generator=g).bfloat16()
+        T[p + "self_attn.q_proj.weight"] = torch.randn(heads * hd, hidden_size, generator=g).bfloat16()
+        T[p + "self_attn.k_proj.weight"] = torch.randn(kv * hd, hidden_size, generator=g).bfloat16()
+        T[p + "self_attn.v_proj.weight"] = torch.randn(kv * hd, hidden_size, generator=g).bfloat16()
+        T[p + "self_attn.o_proj.weight"] = torch.randn(hidden_size, heads * hd, generator=g).bfloat16()
+        T[p + "mlp.up_proj.weight"] = torch.randn(inter, hidden_size, generator=g).bfloat16()
+        T[p + "mlp.gate_proj.weight"] = torch.randn(inter, hidden_size, generator=g).bfloat16()
+        T[p + "mlp.down_proj.weight"] = torch.randn(hidden_size, inter, generator=g).bfloat16()
+    cl.write_safetensors(os.path.join(d, "model.safetensors"), T)
+    return T
+
+
+def test_cloner_scan_and_clone(tmp_path):
+    from loomformer_paraplex_b200.tools import cloner as cl
+    from loomformer_paraplex_b200.train.engine import train_lr_overrides
+    donor_dir = str(tmp_path / "donor")
+    T = _fake_llama(donor_dir)
+    from safetensors.torch import load_file            # the file written by the minimal writer is standard
+    assert torch.equal(load_file(os.path.join(donor_dir, "model.safetensors"))["model.norm.weight"], T["model.norm.weight"])
+    back = cl.read_safetensors(os.path.join(donor_dir, "model.safetensors"))
+    assert all(torch.equal(back[k], T[k]) for k in T)
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    tool = os.path.join(ROOT, "loomcloner.py")
+    y = str(tmp_path / "clone.yaml")
+    r = subprocess.run([sys.executable, tool, "--scan", donor_dir, "--out", y, "--steps", "90", "--lr", "1e-4",
+                        "--paraplex-gate-proj", "--final-norm"], env=env, capture_output=True, text=True)
+    assert r.returncode == 0 and "mapping=llama" in r.stdout, r.stderr
+    cfg = Config.from_yaml(y)
+    assert (cfg.model_dim, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cfg.layers, cfg.vocab) == (32, 4, 2, 8, 2, 64)
+    assert cfg.hidden == 88 and cfg.warmup_steps == 3 and cfg.optimizer == "atom" and cfg.cloned and cfg.cloned_from == "tiny/llama"
+    assert cfg.paraplex_gate_proj and cfg.final_norm and cfg.tied_embeddings
+    byname = {e["name"]: e for e in cfg.train_lr}
+    assert abs(byname["attn.qkv_weight"]["lr"] - 1e-5) < 1e-12 and abs(byname["ln_ffn.bias"]["lr"] - 1e-4) < 1e-12
+    assert "not divisible by n_q_heads=4" in open(y).read()
+    out = str(tmp_path / "clone.pt")
+    r = subprocess.run([sys.executable, tool, "--clone", y, "--donor", donor_dir, "--out", out], env=env,
+                       capture_output=True, text=True)
+    assert r.returncode == 0 and "saved ->" in r.stdout, r.stdout + r.stderr
+    blob = torch.load(out, weights_only=True)
+    st = blob["model"]
+    assert blob["cloned"] and blob["step"] == 0 and st["emb.weight"].dtype == torch.bfloat16
+    assert torch.equal(st["blocks.1.attn.qkv_weight"], torch.cat([T["model.layers.1.self_attn.q_proj.weight"],
+                       T["model.layers.1.self_attn.k_proj.weight"], T["model.layers.1.self_attn.v_proj.weight"]], 0))
+    assert torch.equal(st["blocks.0.ffn.w1_real.weight"][:86], T["model.layers.0.mlp.up_proj.weight"])
+    assert float(st["blocks.0.ffn.w1_real.weight"][86:].abs().sum()) == 0.0
+    assert torch.equal(st["blocks.0.ffn.w2.weight"][:, :86], T["model.layers.0.mlp.down_proj.weight"])
+    assert torch.equal(st["blocks.0.ffn.gate_proj.weight"][:86], T["model.layers.0.mlp.gate_proj.weight"])
+    assert torch.equal(st["ln_final.weight"], T["model.norm.weight"]) and torch.equal(st["emb.weight"], T["model.embed_tokens.weight"])
+    assert yaml_resume(y) == out
+    # the generated overrides bind to real parameter names
+    cfg2 = Config.from_yaml(y)
+    model = Model(cfg2)
+    mults = train_lr_overrides(model, cfg2)
+    assert abs(mults["blocks.0.attn.qkv_weight"] - 0.1) < 1e-9 and abs(mults["blocks.1.ln_attn.bias"] - 1.0) < 1e-9
+
+
+def yaml_resume(path):
+    import yaml
+    return yaml.safe_load(open(path))["resume"]
+
+
+def test_every_shipped_config_loads_and_resolves():
+    from loomformer_paraplex_b200.config import resolve
+    names = sorted(os.listdir(os.path.join(ROOT, "cfg")))
+    assert {"alt.yaml", "alt2.yaml", "chk.yaml", "chk_sft.yaml", "mini.yaml", "nano.yaml", "nano_chk.yaml", "nano_sft.yaml",
+            "sft.yaml", "smol360.yaml"} <= set(names)
+    for n in names:
+        cfg = Config.from_yaml(os.path.join(ROOT, "cfg", n))
+        d = resolve(cfg, calibrate=False)
+        assert d.n == d.qh * d.hd and d.hidden % d.qh == 0, n
+    nano = resolve(Config.from_yaml(os.path.join(ROOT, "cfg", "nano.yaml")), calibrate=False)
+    assert (nano.n, nano.qh, nano.kvh, nano.hd, nano.hidden, nano.layers) == (768, 8, 2, 96, 3072, 10)
