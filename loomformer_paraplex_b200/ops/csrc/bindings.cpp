@@ -24,10 +24,11 @@ LoomOperand operand(const torch::Tensor& t, bool& ok) {
 
 // General entry: see LoomGemm.  `a_list` holds the K segments.
 void gemm(std::vector<torch::Tensor> a_list, std::vector<int64_t> k_len, std::vector<int64_t> a_k0,
-          std::vector<int64_t> b_k0, torch::Tensor b, bool a_mn, bool b_mn, torch::Tensor c,
+          std::vector<int64_t> b_k0, std::vector<torch::Tensor> b_list, bool a_mn, bool b_mn, torch::Tensor c,
           c10::optional<torch::Tensor> bias, int64_t M, int64_t N, int64_t heads, bool accumulate, int64_t bn,
           bool swap_mn, torch::Tensor status) {
-  TORCH_CHECK(a_list.size() >= 1 && a_list.size() <= 5, "1..5 K segments");
+  TORCH_CHECK(a_list.size() >= 1 && a_list.size() <= 16, "1..16 K segments");
+  TORCH_CHECK(b_list.size() == 1 || b_list.size() == a_list.size(), "B: one operand, or one per segment");
   TORCH_CHECK(c.is_cuda() && c.stride(-1) == 1, "C must be a CUDA tensor with unit inner stride");
   TORCH_CHECK(c.scalar_type() == torch::kBFloat16 || c.scalar_type() == torch::kFloat32, "C must be bf16 or fp32");
   const c10::cuda::CUDAGuard guard(c.device());
@@ -39,8 +40,16 @@ void gemm(std::vector<torch::Tensor> a_list, std::vector<int64_t> k_len, std::ve
     g.k_len[i] = (int)k_len[i]; g.a_k0[i] = (int)a_k0[i]; g.b_k0[i] = (int)b_k0[i];
   }
   g.nseg = (int)a_list.size();
-  g.b = operand(b, ok);
-  TORCH_CHECK(ok, "bad B operand");
+  if (b_list.size() == 1) {
+    g.b = operand(b_list[0], ok);
+    TORCH_CHECK(ok, "bad B operand");
+  } else {
+    g.b_per_seg = 1;
+    for (size_t i = 0; i < b_list.size(); ++i) {
+      g.bseg[i] = operand(b_list[i], ok);
+      TORCH_CHECK(ok, "bad B operand ", i);
+    }
+  }
   g.a_mn_major = a_mn; g.b_mn_major = b_mn;
   g.c = c.data_ptr();
   g.ldc = c.stride(0);

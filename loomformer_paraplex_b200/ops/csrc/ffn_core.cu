@@ -44,12 +44,16 @@ __device__ __forceinline__ float phase_slope(float beta, int secant, float ancho
 }
 
 // T = (I + alpha K(a,b,c)) R_axis laid out row-major
-__device__ __forceinline__ void build_T(int axis, float a, float b, float c, float (&T)[9]) {
+template <int AXIS>
+__device__ __forceinline__ void build_T(float a, float b, float c, float (&T)[9]) {
+  constexpr int axis = AXIS;
   if (axis == 0) { T[0] = -c; T[1] = -1.f; T[2] = b; T[3] = 1.f; T[4] = -c; T[5] = -a; T[6] = a; T[7] = b; T[8] = 1.f; }
   else if (axis == 1) { T[0] = 1.f; T[1] = b; T[2] = c; T[3] = c; T[4] = -a; T[5] = -1.f; T[6] = -b; T[7] = 1.f; T[8] = -a; }
   else { T[0] = -b; T[1] = -c; T[2] = 1.f; T[3] = a; T[4] = 1.f; T[5] = c; T[6] = -1.f; T[7] = a; T[8] = -b; }
 }
-__device__ __forceinline__ void grad_abc(int axis, const float (&g)[9], float& ga, float& gb, float& gc) {
+template <int AXIS>
+__device__ __forceinline__ void grad_abc(const float (&g)[9], float& ga, float& gb, float& gc) {
+  constexpr int axis = AXIS;
   if (axis == 0) { ga = -g[5] + g[6]; gb = g[2] + g[7]; gc = -g[0] - g[4]; }
   else if (axis == 1) { ga = -g[4] - g[8]; gb = g[1] - g[6]; gc = g[2] + g[3]; }
   else { ga = g[3] + g[7]; gb = -g[0] - g[8]; gc = -g[1] + g[5]; }
@@ -76,9 +80,11 @@ struct FwdElem {
   float p;
 };
 
+template <int AXIS>
 __device__ __forceinline__ void core_forward_elem(const CoreScalars& S, float x, float pin, int has_pin, float b_r,
                                                   float glin, int has_glin, float beta, float prev, float w_t,
-                                                  const float* cprev, const float* seed, const float* w9, FwdElem& E) {
+                                                  const float (&R)[9], bool has_R, const float (&w9)[9], bool has_w,
+                                                  FwdElem& E) {
   E.r = has_pin ? x * (1.f + S.alpha_gate * pin) + b_r : x + b_r;
   E.gs = has_glin ? glin : E.r;
   E.s0 = phase_s0(beta);
@@ -88,14 +94,13 @@ __device__ __forceinline__ void core_forward_elem(const CoreScalars& S, float x,
   const float P = E.r + A * E.i;
   const float G = __powf(A, S.powlu_m / (sqrtf(A) + 1.f)) * sigmoid_f(A);
   E.o = P * G;
-  if (S.axis >= 0) {
+  if (AXIS >= 0) {
     const float x0 = E.r * E.i, x1 = E.r * E.o, x2 = E.i * E.o;
     const float n3 = rsqrtf((x0 * x0 + x1 * x1 + x2 * x2) * (1.f / 3.f) + 1e-6f);
     const float a = S.tria_alpha * tanhf(x0 * n3), b = S.tria_alpha * tanhf(x1 * n3), c = S.tria_alpha * tanhf(x2 * n3);
     float T[9], pre[9];
-    build_T(S.axis, a, b, c, T);
-    const float* R = cprev ? cprev : seed;
-    if (R) {
+    build_T<AXIS>(a, b, c, T);
+    if (has_R) {
 #pragma unroll
       for (int rr = 0; rr < 3; ++rr)
 #pragma unroll
@@ -111,11 +116,12 @@ __device__ __forceinline__ void core_forward_elem(const CoreScalars& S, float x,
     const float inv = rsqrtf(ss * (1.f / 9.f) + 1e-6f);
     float p = 0.f;
 #pragma unroll
-    for (int k = 0; k < 9; ++k) { E.C[k] = pre[k] * inv; if (w9) p += w9[k] * E.C[k]; }
+    for (int k = 0; k < 9; ++k) { E.C[k] = pre[k] * inv; if (has_w) p += w9[k] * E.C[k]; }
     E.p = p;
   }
 }
 
+template <int AXIS>
 __global__ void __launch_bounds__(256) ffn_core_fwd_kernel(
     CoreScalars S_in, const __nv_bfloat16* __restrict__ x_real, const __nv_bfloat16* __restrict__ p_in,
     const float* __restrict__ b_real, const __nv_bfloat16* __restrict__ gate_lin,
@@ -149,33 +155,35 @@ __global__ void __launch_bounds__(256) ffn_core_fwd_kernel(
     }
     float w9[9];
     const bool has_w = gate_w != nullptr;
-    if (has_w) {
 #pragma unroll
-      for (int k = 0; k < 9; ++k) w9[k] = gate_w[k];
-    }
-    float cp0[9], cp1[9];
-    const float *r0 = nullptr, *r1 = nullptr, *sd0 = nullptr, *sd1 = nullptr;
+    for (int k = 0; k < 9; ++k) w9[k] = has_w ? gate_w[k] : 0.f;
+    float cp0[9], cp1[9];          // carrier entering the step (previous depth, or the temporal seed at t = 0)
+    bool has_R = false;
     const long long plane = (long long)S.M * H;
-    if (S.axis >= 0) {
+    if (AXIS >= 0) {
       if (c_prev) {
 #pragma unroll
         for (int k = 0; k < 9; ++k) { float2 v = ld2(c_prev + k * plane + e); cp0[k] = v.x; cp1[k] = v.y; }
-        r0 = cp0; r1 = cp1;
+        has_R = true;
       } else if (seed && t == 0 && seed_valid[b]) {
         const float* sp = seed + ((long long)b * H + h) * 9;
 #pragma unroll
         for (int k = 0; k < 9; ++k) { cp0[k] = sp[k]; cp1[k] = sp[9 + k]; }
-        sd0 = cp0; sd1 = cp1;
+        has_R = true;
       }
     }
+    if (!has_R) {
+#pragma unroll
+      for (int k = 0; k < 9; ++k) { cp0[k] = 0.f; cp1[k] = 0.f; }
+    }
     FwdElem E0, E1;
-    core_forward_elem(S, x.x, pin.x, p_in != nullptr, b_real[h], gl.x, gate_lin != nullptr, beta0, prev0, w_trace[h],
-                      r0, sd0, has_w ? w9 : nullptr, E0);
-    core_forward_elem(S, x.y, pin.y, p_in != nullptr, b_real[h + 1], gl.y, gate_lin != nullptr, beta1, prev1,
-                      w_trace[h + 1], r1, sd1, has_w ? w9 : nullptr, E1);
+    core_forward_elem<AXIS>(S, x.x, pin.x, p_in != nullptr, b_real[h], gl.x, gate_lin != nullptr, beta0, prev0, w_trace[h],
+                            cp0, has_R, w9, has_w, E0);
+    core_forward_elem<AXIS>(S, x.y, pin.y, p_in != nullptr, b_real[h + 1], gl.y, gate_lin != nullptr, beta1, prev1,
+                            w_trace[h + 1], cp1, has_R, w9, has_w, E1);
     st2(o_out + e, E0.o, E1.o);
     if (t == S.Tc - 1) { trace_out[(long long)b * H + h] = E0.s0; trace_out[(long long)b * H + h + 1] = E1.s0; }
-    if (S.axis >= 0) {
+    if (AXIS >= 0) {
 #pragma unroll
       for (int k = 0; k < 9; ++k) st2(c_out + k * plane + e, E0.C[k], E1.C[k]);
       if (has_w) st2(p_out + e, E0.p, E1.p);
@@ -204,35 +212,41 @@ struct BwdElem {
   float dw9[9];
 };
 
+template <int AXIS>
 __device__ __forceinline__ void core_backward_elem(const CoreScalars& S, float x, float pin, int has_pin, float b_r,
                                                    float glin, int has_glin, float beta, float prev, float w_t,
-                                                   const float* R, const float* w9, float dO, const float* dC,
-                                                   float dpo, int has_dpo, BwdElem& E) {
+                                                   const float (&R)[9], bool has_R, const float (&w9)[9], float dO,
+                                                   const float (&dC)[9], bool has_dc, float dpo, bool has_dpo,
+                                                   BwdElem& E) {
   const float r = has_pin ? x * (1.f + S.alpha_gate * pin) + b_r : x + b_r;
   const float gs = has_glin ? glin : r;
   const float s0 = phase_s0(beta);
   const float z = s0 + w_t * prev;
   const float zi = rsqrtf(1.f + z * z);
   const float i = z * zi;
-  const float sp = softplus_f(gs);
+  // softplus and the sigmoid needed for its derivative share one exponential
+  const float egs = __expf(fminf(gs, 30.f));
+  const float sp = gs > 20.f ? gs : (gs < -15.f ? egs : __logf(1.f + egs));
+  const float sig_gs = gs > 20.f ? 1.f : egs / (1.f + egs);
   const float A = fmaxf(sp, 1e-12f);
   const float sqA = sqrtf(A);
   const float ex = S.powlu_m / (sqA + 1.f);
   const float sig = sigmoid_f(A);
-  const float G = __powf(A, ex) * sig;
+  const float lg2A = __log2f(A);                 // shared by A^ex and d/dA A^ex
+  const float G = exp2f(ex * lg2A) * sig;
   const float P = r + A * i;
   const float o = P * G;
   float g_r = 0.f, g_i = 0.f, g_o = dO;
 #pragma unroll
   for (int k = 0; k < 9; ++k) { E.dR[k] = 0.f; E.dw9[k] = 0.f; }
-  if (S.axis >= 0 && (dC != nullptr || has_dpo)) {
+  if (AXIS >= 0 && (has_dc || has_dpo)) {
     const float x0 = r * i, x1 = r * o, x2 = i * o;
     const float n3 = rsqrtf((x0 * x0 + x1 * x1 + x2 * x2) * (1.f / 3.f) + 1e-6f);
     const float y0 = x0 * n3, y1 = x1 * n3, y2 = x2 * n3;
     const float t0 = tanhf(y0), t1 = tanhf(y1), t2 = tanhf(y2);
     float T[9], pre[9], C[9], gC[9], gpre[9], gT[9];
-    build_T(S.axis, S.tria_alpha * t0, S.tria_alpha * t1, S.tria_alpha * t2, T);
-    if (R) {
+    build_T<AXIS>(S.tria_alpha * t0, S.tria_alpha * t1, S.tria_alpha * t2, T);
+    if (has_R) {
 #pragma unroll
       for (int rr = 0; rr < 3; ++rr)
 #pragma unroll
@@ -250,14 +264,14 @@ __device__ __forceinline__ void core_backward_elem(const CoreScalars& S, float x
 #pragma unroll
     for (int k = 0; k < 9; ++k) {
       C[k] = pre[k] * inv;
-      gC[k] = (dC ? dC[k] : 0.f) + (has_dpo ? dpo * w9[k] : 0.f);
+      gC[k] = (has_dc ? dC[k] : 0.f) + (has_dpo ? dpo * w9[k] : 0.f);
       if (has_dpo) E.dw9[k] = dpo * C[k];
       dot += gC[k] * C[k];
     }
     dot *= (1.f / 9.f);
 #pragma unroll
     for (int k = 0; k < 9; ++k) gpre[k] = (gC[k] - C[k] * dot) * inv;
-    if (R) {
+    if (has_R) {
 #pragma unroll
       for (int rr = 0; rr < 3; ++rr)
 #pragma unroll
@@ -270,7 +284,7 @@ __device__ __forceinline__ void core_backward_elem(const CoreScalars& S, float x
       for (int k = 0; k < 9; ++k) gT[k] = gpre[k];
     }
     float ga, gb, gc;
-    grad_abc(S.axis, gT, ga, gb, gc);
+    grad_abc<AXIS>(gT, ga, gb, gc);
     const float gy0 = ga * S.tria_alpha * (1.f - t0 * t0), gy1 = gb * S.tria_alpha * (1.f - t1 * t1),
                 gy2 = gc * S.tria_alpha * (1.f - t2 * t2);
     const float doty = (gy0 * y0 + gy1 * y1 + gy2 * y2) * (1.f / 3.f);
@@ -285,11 +299,11 @@ __device__ __forceinline__ void core_backward_elem(const CoreScalars& S, float x
   float gA = gP * i;
   if (sp >= 1e-12f) {
     const float de = -S.powlu_m / ((sqA + 1.f) * (sqA + 1.f)) * (0.5f / sqA);
-    gA += gG * G * (ex / A + de * __logf(A) + (1.f - sig));
+    gA += gG * G * (ex / A + de * (lg2A * 0.6931471805599453f) + (1.f - sig));
   } else {
     gA = 0.f;
   }
-  const float g_gs = gA * sigmoid_f(gs);
+  const float g_gs = gA * sig_gs;
   E.gz = g_i * zi * zi * zi;
   E.dwt = E.gz * prev;
   if (has_glin) E.dgl = g_gs; else { g_r += g_gs; E.dgl = 0.f; }
@@ -301,6 +315,7 @@ __device__ __forceinline__ void core_backward_elem(const CoreScalars& S, float x
 
 constexpr int TILE_ROWS = 32;
 
+template <int AXIS>
 __global__ void __launch_bounds__(256, 2) ffn_core_bwd_a_kernel(
     CoreScalars S_in, const __nv_bfloat16* __restrict__ x_real, const __nv_bfloat16* __restrict__ p_in,
     const float* __restrict__ b_real, const __nv_bfloat16* __restrict__ gate_lin,
@@ -320,10 +335,8 @@ __global__ void __launch_bounds__(256, 2) ffn_core_bwd_a_kernel(
   const long long plane = (long long)S.M * H;
   float w9[9];
   const bool has_w = gate_w != nullptr && d_pout != nullptr;
-  if (has_w) {
 #pragma unroll
-    for (int k = 0; k < 9; ++k) w9[k] = gate_w[k];
-  }
+  for (int k = 0; k < 9; ++k) w9[k] = has_w ? gate_w[k] : 0.f;
   float acc_br0 = 0.f, acc_br1 = 0.f, acc_wt0 = 0.f, acc_wt1 = 0.f, acc_alpha = 0.f;
   float acc_w9[9];
 #pragma unroll
@@ -350,29 +363,36 @@ __global__ void __launch_bounds__(256, 2) ffn_core_bwd_a_kernel(
         else { const float2 bp = ld2(beta_lin + e - H); prev0 = phase_s0(bp.x + bi0); prev1 = phase_s0(bp.y + bi1); }
       }
       float R0[9], R1[9], dC0[9], dC1[9];
-      const float *r0 = nullptr, *r1 = nullptr;
-      bool from_seed = false;
-      if (S.axis >= 0) {
+      bool has_R = false, from_seed = false;
+      if (AXIS >= 0) {
         if (c_prev) {
 #pragma unroll
           for (int k = 0; k < 9; ++k) { float2 v = ld2(c_prev + k * plane + e); R0[k] = v.x; R1[k] = v.y; }
-          r0 = R0; r1 = R1;
+          has_R = true;
         } else if (seed && t == 0 && seed_valid[b]) {
           const float* sp = seed + ((long long)b * H + h) * 9;
 #pragma unroll
           for (int k = 0; k < 9; ++k) { R0[k] = sp[k]; R1[k] = sp[9 + k]; }
-          r0 = R0; r1 = R1; from_seed = true;
+          has_R = true; from_seed = true;
         }
         if (d_c) {
 #pragma unroll
           for (int k = 0; k < 9; ++k) { float2 v = ld2(d_c + k * plane + e); dC0[k] = v.x; dC1[k] = v.y; }
         }
       }
+      if (!has_R) {
+#pragma unroll
+        for (int k = 0; k < 9; ++k) { R0[k] = 0.f; R1[k] = 0.f; }
+      }
+      if (AXIS < 0 || !d_c) {
+#pragma unroll
+        for (int k = 0; k < 9; ++k) { dC0[k] = 0.f; dC1[k] = 0.f; }
+      }
       BwdElem E0, E1;
-      core_backward_elem(S, x.x, pin.x, p_in != nullptr, br0, gl.x, gate_lin != nullptr, bl.x + bi0, prev0, wt0, r0,
-                         has_w ? w9 : nullptr, dO.x, d_c ? dC0 : nullptr, dpo.x, has_w, E0);
-      core_backward_elem(S, x.y, pin.y, p_in != nullptr, br1, gl.y, gate_lin != nullptr, bl.y + bi1, prev1, wt1, r1,
-                         has_w ? w9 : nullptr, dO.y, d_c ? dC1 : nullptr, dpo.y, has_w, E1);
+      core_backward_elem<AXIS>(S, x.x, pin.x, p_in != nullptr, br0, gl.x, gate_lin != nullptr, bl.x + bi0, prev0, wt0, R0,
+                               has_R, w9, dO.x, dC0, d_c != nullptr, dpo.x, has_w, E0);
+      core_backward_elem<AXIS>(S, x.y, pin.y, p_in != nullptr, br1, gl.y, gate_lin != nullptr, bl.y + bi1, prev1, wt1, R1,
+                               has_R, w9, dO.y, dC1, d_c != nullptr, dpo.y, has_w, E1);
       st2(dx_real + e, E0.dx, E1.dx);
       if (dp_in) st2(dp_in + e, E0.dpin, E1.dpin);
       if (dgate_lin) st2(dgate_lin + e, E0.dgl, E1.dgl);
@@ -486,11 +506,19 @@ extern "C" int loom_ffn_core_fwd(const LoomFfnCore* a, cudaStream_t stream) {
   if (a->H % 2) return -1;
   CoreScalars S = make_scalars(a);
   const long long n = (long long)S.M * (S.H / 2);
-  ffn_core_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
-      S, (const __nv_bfloat16*)a->x_real, (const __nv_bfloat16*)a->p_in, a->b_real, (const __nv_bfloat16*)a->gate_lin,
-      (const __nv_bfloat16*)a->beta_lin, a->b_imag, a->w_trace, a->trace_in, a->reset, (const __nv_bfloat16*)a->c_prev,
-      a->seed, a->seed_valid, a->gate_w, (__nv_bfloat16*)a->o_out, (__nv_bfloat16*)a->c_out, (__nv_bfloat16*)a->p_out,
-      a->trace_out, a->beta_sq_sum);
+#define LOOM_FWD(AX)                                                                                              \
+  ffn_core_fwd_kernel<AX><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(                                       \
+      S, (const __nv_bfloat16*)a->x_real, (const __nv_bfloat16*)a->p_in, a->b_real, (const __nv_bfloat16*)a->gate_lin, \
+      (const __nv_bfloat16*)a->beta_lin, a->b_imag, a->w_trace, a->trace_in, a->reset, (const __nv_bfloat16*)a->c_prev, \
+      a->seed, a->seed_valid, a->gate_w, (__nv_bfloat16*)a->o_out, (__nv_bfloat16*)a->c_out, (__nv_bfloat16*)a->p_out,  \
+      a->trace_out, a->beta_sq_sum)
+  switch (S.axis) {      // the axis is a template argument so the +-1 entries of R_axis fold into the products
+    case 0: LOOM_FWD(0); break;
+    case 1: LOOM_FWD(1); break;
+    case 2: LOOM_FWD(2); break;
+    default: LOOM_FWD(-1); break;
+  }
+#undef LOOM_FWD
   return (int)cudaGetLastError();
 }
 
@@ -498,12 +526,20 @@ extern "C" int loom_ffn_core_bwd(const LoomFfnCore* a, cudaStream_t stream) {
   if (a->H % 2) return -1;
   CoreScalars S = make_scalars(a);
   dim3 grid((S.H / 2 + 63) / 64, (S.M + TILE_ROWS - 1) / TILE_ROWS);
-  ffn_core_bwd_a_kernel<<<grid, 256, 0, stream>>>(
-      S, (const __nv_bfloat16*)a->x_real, (const __nv_bfloat16*)a->p_in, a->b_real, (const __nv_bfloat16*)a->gate_lin,
-      (const __nv_bfloat16*)a->beta_lin, a->b_imag, a->w_trace, a->trace_in, a->reset, (const __nv_bfloat16*)a->c_prev,
-      a->seed, a->seed_valid, a->gate_w, (const __nv_bfloat16*)a->d_o, (const __nv_bfloat16*)a->d_c,
-      (const __nv_bfloat16*)a->d_pout, (__nv_bfloat16*)a->dx_real, (__nv_bfloat16*)a->dp_in, (__nv_bfloat16*)a->dgate_lin,
-      a->gz, (__nv_bfloat16*)a->dc_prev, a->dseed, a->dtrace_in, a->g_b_real, a->g_w_trace, a->g_scalars);
+#define LOOM_BWD(AX)                                                                                              \
+  ffn_core_bwd_a_kernel<AX><<<grid, 256, 0, stream>>>(                                                            \
+      S, (const __nv_bfloat16*)a->x_real, (const __nv_bfloat16*)a->p_in, a->b_real, (const __nv_bfloat16*)a->gate_lin, \
+      (const __nv_bfloat16*)a->beta_lin, a->b_imag, a->w_trace, a->trace_in, a->reset, (const __nv_bfloat16*)a->c_prev, \
+      a->seed, a->seed_valid, a->gate_w, (const __nv_bfloat16*)a->d_o, (const __nv_bfloat16*)a->d_c,                  \
+      (const __nv_bfloat16*)a->d_pout, (__nv_bfloat16*)a->dx_real, (__nv_bfloat16*)a->dp_in, (__nv_bfloat16*)a->dgate_lin, \
+      a->gz, (__nv_bfloat16*)a->dc_prev, a->dseed, a->dtrace_in, a->g_b_real, a->g_w_trace, a->g_scalars)
+  switch (S.axis) {
+    case 0: LOOM_BWD(0); break;
+    case 1: LOOM_BWD(1); break;
+    case 2: LOOM_BWD(2); break;
+    default: LOOM_BWD(-1); break;
+  }
+#undef LOOM_BWD
   ffn_core_bwd_b_kernel<<<grid, 256, 0, stream>>>(S, a->gz, (const __nv_bfloat16*)a->beta_lin, a->b_imag, a->w_trace,
                                                   a->reset, a->dtrace_out, (__nv_bfloat16*)a->dbeta, a->g_b_imag);
   return (int)cudaGetLastError();

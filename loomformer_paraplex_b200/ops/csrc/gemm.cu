@@ -11,6 +11,9 @@
 // "Segmented K": the reduction dimension may be the concatenation of up to MAX_SEG different
 // tensors (e.g. the Paraplex phase input [Q_g | Kctx_g | C_g | u | D_g]); each segment has its own
 // tensor map whose extent bounds the segment, so ragged tails are zero-filled by the TMA unit.
+// With `b_per_seg` every segment also brings its own B operand: that is how the weight gradients of
+// all temporal chunks of a step (dY_c^T X_c, c = 0..15) become ONE launch with a 16x longer reduction
+// instead of sixteen short ones.
 // "Batched": every operand is a [rows, heads, cols] view; a batched operand indexes `heads` with the
 // tile's group id, an unbatched one uses group 0.  Either operand may be K-major (reduction index
 // contiguous) or MN-major (the other index contiguous), which covers forward, data-gradient and
@@ -30,11 +33,12 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;          // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int MAX_SEG = 5;
+constexpr int MAX_SEG = 16;
 constexpr int NUM_THREADS = 192;  // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
 
 struct Seg {
   CUtensorMap a;
+  CUtensorMap b;  // used only when every segment brings its own B operand (grouped weight gradients)
   int k_len;      // reduction length of this segment
   int a_k0;       // offset of the segment along A's reduction index
   int b_k0;       // offset of the segment along B's reduction index
@@ -46,6 +50,7 @@ struct Params {
   Seg seg[MAX_SEG];
   int nseg;
   int b_batched;
+  int b_per_seg;
   void* c;
   long long ldc;        // row pitch of C (elements)
   long long ldc_head;   // group pitch of C (elements)
@@ -102,8 +107,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_kernel(const __grid_const
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (elect_one()) {
-      tma_prefetch_desc(&p.b);
-      for (int s = 0; s < p.nseg; ++s) tma_prefetch_desc(&p.seg[s].a);
+      if (!p.b_per_seg) tma_prefetch_desc(&p.b);
+      for (int s = 0; s < p.nseg; ++s) { tma_prefetch_desc(&p.seg[s].a); if (p.b_per_seg) tma_prefetch_desc(&p.seg[s].b); }
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
@@ -113,6 +118,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_kernel(const __grid_const
         const int m0 = tm * BM, n0 = tn * BN;
         for (int s = 0; s < p.nseg && ok; ++s) {
           const Seg& sg = p.seg[s];
+          const CUtensorMap* bmap = p.b_per_seg ? &sg.b : &p.b;
           const int ag = sg.a_batched ? g : 0;
           const int bg = p.b_batched ? g : 0;
           for (int k = 0; k < sg.k_len; k += BK, ++it) {
@@ -132,9 +138,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_kernel(const __grid_const
             if (B_MN) {
 #pragma unroll
               for (int j = 0; j < BN / 64; ++j)
-                tma_load_3d(sb + j * 8192, &p.b, &full[st], n0 + 64 * j, sg.b_k0 + k, bg);
+                tma_load_3d(sb + j * 8192, bmap, &full[st], n0 + 64 * j, sg.b_k0 + k, bg);
             } else {
-              tma_load_3d(sb, &p.b, &full[st], sg.b_k0 + k, n0, bg);
+              tma_load_3d(sb, bmap, &full[st], sg.b_k0 + k, n0, bg);
             }
           }
         }
@@ -298,16 +304,18 @@ extern "C" int loom_gemm_bf16(const LoomGemm* g, cudaStream_t stream) {
   Params p;
   memset(&p, 0, sizeof(p));
   const bool a_mn = g->a_mn_major != 0, b_mn = g->b_mn_major != 0;
-  if (!fill_map(&p.b, g->b, b_mn, g->bn)) return -3;
+  p.b_per_seg = g->b_per_seg ? 1 : 0;
+  if (!p.b_per_seg && !fill_map(&p.b, g->b, b_mn, g->bn)) return -3;
   for (int s = 0; s < g->nseg; ++s) {
     if (!fill_map(&p.seg[s].a, g->a[s], a_mn, BM)) return -4;
+    if (p.b_per_seg && !fill_map(&p.seg[s].b, g->bseg[s], b_mn, g->bn)) return -3;
     p.seg[s].k_len = g->k_len[s];
     p.seg[s].a_k0 = g->a_k0[s];
     p.seg[s].b_k0 = g->b_k0[s];
     p.seg[s].a_batched = g->a[s].heads > 1 ? 1 : 0;
   }
   p.nseg = g->nseg;
-  p.b_batched = g->b.heads > 1 ? 1 : 0;
+  p.b_batched = (p.b_per_seg ? g->bseg[0].heads : g->b.heads) > 1 ? 1 : 0;
   p.c = g->c; p.ldc = g->ldc; p.ldc_head = g->ldc_head; p.bias = g->bias;
   p.M = g->M; p.n_per_head = g->N; p.heads = g->heads > 0 ? g->heads : 1;
   p.accumulate = g->accumulate; p.out_fp32 = g->out_fp32; p.status = g->status;

@@ -19,10 +19,12 @@ typedef struct {
 // C[m, g, n] (+)= sum_s A_s[m, g, :k_len[s]] . B[n, g, b_k0[s] : b_k0[s]+k_len[s]]  (+ bias)
 // K-major operand: reduction index = cols.  MN-major operand: reduction index = rows.
 typedef struct {
-  LoomOperand a[5];
-  int k_len[5], a_k0[5], b_k0[5];
+  LoomOperand a[16];
+  int k_len[16], a_k0[16], b_k0[16];
   int nseg;
   LoomOperand b;
+  LoomOperand bseg[16];  // per-segment B operands, used instead of `b` when b_per_seg != 0
+  int b_per_seg;
   int a_mn_major, b_mn_major;
   void* c;
   long long ldc, ldc_head;

@@ -213,6 +213,7 @@ class FusedPlan:
                 dtemporal = dseed if dtemporal is None else dtemporal + dseed
             tape.clear()
         self.g(m.emb.weight).index_add_(0, idx.reshape(-1), d_emb.view(B * T, d.n).float())
+        K.flush_wgrads()
         return loss, None
 
     # ------------------------------------------------------------------ depth-attention helpers

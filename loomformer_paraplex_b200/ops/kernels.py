@@ -46,13 +46,14 @@ def _pick_bn(M: int, N: int, heads: int = 1) -> int:
     return 64 if N <= 64 else 128
 
 
-def gemm(a_list: List[torch.Tensor], k_len: List[int], b: torch.Tensor, c: torch.Tensor, *, M: int, N: int,
+def gemm(a_list: List[torch.Tensor], k_len: List[int], b, c: torch.Tensor, *, M: int, N: int,
          heads: int = 1, a_mn: bool = False, b_mn: bool = False, a_k0: Optional[List[int]] = None,
          b_k0: Optional[List[int]] = None, bias: Optional[torch.Tensor] = None, accumulate: bool = False,
          bn: Optional[int] = None, swap_mn: bool = False) -> None:
     ext = native.ext()
     n = len(a_list)
-    ext.gemm(a_list, k_len, a_k0 or [0] * n, b_k0 or [0] * n, b, a_mn, b_mn, c, bias, M, N, heads, accumulate,
+    ext.gemm(a_list, k_len, a_k0 or [0] * n, b_k0 or [0] * n, b if isinstance(b, (list, tuple)) else [b], a_mn, b_mn,
+             c, bias, M, N, heads, accumulate,
              bn or _pick_bn(M, N, heads), swap_mn, status_word(c.device))
     native.count()
 
@@ -93,9 +94,40 @@ def optimizer_step(opt) -> None:
 class CudaKernels(TorchKernels):
     name = "cuda"
 
-    def __init__(self) -> None:
+    WGRAD_GROUP = 16      # weight-gradient products of this many chunks go out as one launch
+
+    def __init__(self, defer_wgrad: bool = True) -> None:
         native.ext()
         self.fallbacks: Counter = Counter()
+        self.defer_wgrad = defer_wgrad
+        self._wq: dict = {}
+
+    # ------------------------------------------------------------------ grouped weight gradients
+    def _wgrad(self, dy, x, gw, M, N, heads=1):
+        """gw[M, (heads,) N] += dy^T x.  The chunk-serial backward produces one such product per chunk for every
+        weight; with a reduction length of only B*Tc rows each is a short, poorly filled GEMM.  They are queued
+        instead (the operands stay alive in the queue) and issued as ONE launch whose reduction runs over all
+        queued chunks -- same arithmetic, one pass over the fp32 gradient instead of sixteen."""
+        if not self.defer_wgrad:
+            gemm([dy], [dy.shape[0]], x, gw, M=M, N=N, heads=heads, a_mn=True, b_mn=True, accumulate=True)
+            return
+        key = (gw.data_ptr(), M, N, heads, tuple(gw.stride()))
+        ent = self._wq.get(key)
+        if ent is None:
+            ent = self._wq[key] = ([], [], gw)
+        ent[0].append(dy)
+        ent[1].append(x)
+        if len(ent[0]) >= self.WGRAD_GROUP:
+            self._flush_one(key)
+
+    def _flush_one(self, key):
+        dys, xs, gw = self._wq.pop(key)
+        _, M, N, heads, _ = key
+        gemm(dys, [t.shape[0] for t in dys], xs, gw, M=M, N=N, heads=heads, a_mn=True, b_mn=True, accumulate=True)
+
+    def flush_wgrads(self) -> None:
+        for key in list(self._wq):
+            self._flush_one(key)
 
     # ------------------------------------------------------------------ GEMMs
     def linear(self, x, w, bias=None, out_dtype=None):
@@ -124,7 +156,7 @@ class CudaKernels(TorchKernels):
         if not (_tma_ok(dy2) and _tma_ok(x2) and gw.dtype == torch.float32 and gw.stride(-1) == 1 and gw.dim() == 2):
             self.fallbacks["linear_wgrad"] += 1
             return super().linear_wgrad(dy, x, gw)
-        gemm([dy2], [dy2.shape[0]], x2, gw, M=dy2.shape[1], N=x2.shape[1], a_mn=True, b_mn=True, accumulate=True)
+        self._wgrad(dy2, x2, gw, dy2.shape[1], x2.shape[1])
 
     # ------------------------------------------------------------------ imaginary projection
     def imag_fwd(self, d, qkc, u, m2, w_imag):
@@ -168,12 +200,11 @@ class CudaKernels(TorchKernels):
         def per_head(col0, a_src, c_dst):
             # data gradient of a head-local sector and its weight gradient
             gemm([db3], [d.hpq], w3[:, :, col0:col0 + hd], c_dst, M=M, N=hd, heads=d.qh, b_mn=True)
-            gemm([db3], [M], a_src, g3[:, :, col0:col0 + hd], M=d.hpq, N=hd, heads=d.qh, a_mn=True, b_mn=True,
-                 accumulate=True)
+            self._wgrad(db3, a_src, g3[:, :, col0:col0 + hd], d.hpq, hd, d.qh)
 
         def shared(col0, a_src2d, c_dst2d):
             gemm([dbeta], [H], w_imag[:, col0:col0 + n], c_dst2d, M=M, N=n, b_mn=True)
-            gemm([dbeta], [M], a_src2d, gw_imag[:, col0:col0 + n], M=H, N=n, a_mn=True, b_mn=True, accumulate=True)
+            self._wgrad(dbeta, a_src2d, gw_imag[:, col0:col0 + n], H, n)
 
         if d.open_sectors:
             per_head(0, qkc[:, 0], dqkc[:, 0])

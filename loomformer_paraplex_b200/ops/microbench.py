@@ -1,0 +1,207 @@
+"""Per-kernel microbenchmarks with roofline fractions.
+
+``python -m loomformer_paraplex_b200.ops.microbench --op ffn_core_bwd --tokens 8192`` times one native op on
+113M-model shapes with CUDA events (warm-up, L2 flushed between iterations by writing a buffer larger than L2) and
+reports achieved bytes/s and FLOP/s against the measured peaks of the machine (``MEASURED_PEAKS.json`` at the
+repository root when present: STREAM-style copy bandwidth and cuBLAS bf16 throughput).  ``--op all`` prints a table.
+The same entry is what profiler captures run, so a capture and a timing describe the same launch."""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from types import SimpleNamespace
+from typing import Callable, Dict, Tuple
+
+import torch
+
+from . import kernels as kmod
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks() -> Tuple[Dict[str, float], str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"])}, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def dims(qh=8, hd=96, kvh=2, hidden=3072) -> SimpleNamespace:
+    return SimpleNamespace(qh=qh, hd=hd, kvh=kvh, group=qh // kvh, n=qh * hd, kv_dim=kvh * hd, hidden=hidden,
+                           hpq=hidden // qh, activation="pvpowlu", powlu_m=3.0, phase_floor=0.05, phase_secant=True)
+
+
+def bf(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def nbytes(*ts) -> int:
+    return sum(t.numel() * t.element_size() for t in ts if t is not None)
+
+
+# every builder returns (callable, algorithmic bytes, algorithmic flops)
+def case_linear(K, M, n_in=768, n_out=3072):
+    x, w = bf(M, n_in), bf(n_out, n_in, scale=0.03)
+    y = K.linear(x, w)
+    return (lambda: K.linear(x, w)), nbytes(x, w, y), 2.0 * M * n_in * n_out
+
+
+def case_wgrad(K, M, n_in=768, n_out=3072):
+    x, dy = bf(M, n_in), bf(M, n_out, scale=0.1)
+    g = torch.zeros(n_out, n_in, device="cuda")
+    def run():
+        K.linear_wgrad(dy, x, g)
+        K.flush_wgrads()
+    return run, nbytes(x, dy, g) + nbytes(g), 2.0 * M * n_in * n_out
+
+
+def case_wgrad_grouped(K, M, n_in=768, n_out=3072, chunks=16):
+    """The same product cut into 16 chunk-sized pieces and issued as one grouped launch."""
+    rows = M // chunks
+    xs, dys = [bf(rows, n_in) for _ in range(chunks)], [bf(rows, n_out, scale=0.1) for _ in range(chunks)]
+    g = torch.zeros(n_out, n_in, device="cuda")
+    def run():
+        for dy, x in zip(dys, xs):
+            K.linear_wgrad(dy, x, g)
+        K.flush_wgrads()
+    return run, nbytes(*xs, *dys, g) + nbytes(g), 2.0 * M * n_in * n_out
+
+
+def case_dgrad(K, M, n_in=768, n_out=3072):
+    dy, w = bf(M, n_out, scale=0.1), bf(n_out, n_in, scale=0.03)
+    dx = K.linear_dgrad(dy, w)
+    return (lambda: K.linear_dgrad(dy, w)), nbytes(dy, w, dx), 2.0 * M * n_in * n_out
+
+
+def _core_inputs(M, B, H):
+    x_real, beta_lin, pin = bf(M, H), bf(M, H, scale=1.5), bf(M, H, scale=0.5)
+    alpha = torch.tensor(0.17, device="cuda")
+    b_real, b_imag, w_tr = (torch.randn(H, device="cuda") * 0.3 for _ in range(3))
+    tr_in = torch.rand(B, H, device="cuda") * 2 - 1
+    cp = bf(9, M, H)
+    gw = torch.softmax(torch.randn(9, device="cuda"), 0)
+    return x_real, beta_lin, pin, alpha, b_real, b_imag, w_tr, tr_in, cp, gw
+
+
+def case_ffn_core_fwd(K, M, Tc=128):
+    d = dims()
+    B, H = M // Tc, d.hidden
+    x_real, beta_lin, pin, alpha, b_real, b_imag, w_tr, tr_in, cp, gw = _core_inputs(M, B, H)
+    run = lambda: K.ffn_core_fwd(d, x_real, pin, alpha, b_real, None, beta_lin, b_imag, w_tr, tr_in, None, None, cp, None,
+                                 None, gw, 1, 0.05, B)
+    o = run()
+    return run, nbytes(x_real, beta_lin, pin, cp, o["o"], o["c"], o["p_out"]), 0.0
+
+
+def case_ffn_core_bwd(K, M, Tc=128):
+    d = dims()
+    B, H = M // Tc, d.hidden
+    x_real, beta_lin, pin, alpha, b_real, b_imag, w_tr, tr_in, cp, gw = _core_inputs(M, B, H)
+    saved = {"x_real": x_real, "p_in": pin, "alpha_gate": alpha, "b_real": b_real, "gate_lin": None, "beta_lin": beta_lin,
+             "b_imag": b_imag, "w_trace": w_tr, "trace_in": tr_in, "reset": None, "anchor": torch.tensor(0.8, device="cuda"),
+             "c_prev": cp, "seed": None, "seed_valid": None, "gate_w": gw, "axis": 1, "tria_alpha": 0.05, "B": B,
+             "g_b_real": torch.zeros(H, device="cuda"), "g_b_imag": torch.zeros(H, device="cuda"),
+             "g_w_trace": torch.zeros(H, device="cuda")}
+    do, dc, dpo = bf(M, H, scale=0.1), bf(9, M, H, scale=0.1), bf(M, H, scale=0.1)
+    dtr = torch.randn(B, H, device="cuda") * 0.1
+    run = lambda: K.ffn_core_bwd(d, saved, do, dc, dpo, dtr)
+    g = run()
+    return run, nbytes(x_real, beta_lin, pin, cp, do, dc, dpo, g["d_x_real"], g["d_p_in"], g["d_beta_lin"], g["d_c_prev"]), 0.0
+
+
+def _attn_inputs(M, Tc, T):
+    d = dims()
+    B = M // Tc
+    s = T - Tc
+    kc, vc = bf(B, T, d.kvh, d.hd), bf(B, T, d.kvh, d.hd)
+    qkc = torch.zeros(M, 3, d.qh, d.hd, device="cuda", dtype=torch.bfloat16)
+    qkc[:, 0] = bf(M, d.qh, d.hd)
+    return d, B, s, kc, vc, qkc
+
+
+def case_attn_fwd(K, M, Tc=128, T=1024):
+    d, B, s, kc, vc, qkc = _attn_inputs(M, Tc, T)
+    run = lambda: K.attn_fwd(d, qkc, kc, vc, s, T, None)
+    # S = Q K^T, then [A V | A K]: 3 products of 2*Tc*T*hd per head; causal tail of the chunk ignored
+    return run, nbytes(qkc, kc, vc), 3 * 2.0 * B * d.qh * Tc * T * d.hd
+
+
+def case_attn_bwd(K, M, Tc=128, T=1024):
+    d, B, s, kc, vc, qkc = _attn_inputs(M, Tc, T)
+    lse = K.attn_fwd(d, qkc, kc, vc, s, T, None)
+    dqkc = bf(M, 3, d.qh, d.hd, scale=0.3)
+    dk, dv = K.alloc_kv_grad(d, B, T, qkc.device), K.alloc_kv_grad(d, B, T, qkc.device)
+    run = lambda: K.attn_bwd(d, dqkc, qkc, kc, vc, lse, s, T, None, dk, dv)
+    # S, dP (two contexts), dQ, dK (two terms), dV: 7 products
+    return run, nbytes(qkc, dqkc, kc, vc) + 2 * nbytes(dk, dv), 7 * 2.0 * B * d.qh * Tc * T * d.hd
+
+
+def case_optimizer(K, M):
+    from ..optim.flat import FlatOptimizer, FlatParams
+    lin = torch.nn.Linear(4096, max(256, M // 4), bias=False).cuda()        # ~M*1024 parameters
+    flat = FlatParams(lin, want_bf16_shadow=True)
+    opt = FlatOptimizer(flat, "adamw", lr=1e-3, weight_decay=0.01, grad_clip=1.0)
+    flat.grads.normal_()
+    n = flat.params.numel()
+    return (lambda: opt.step()), n * (4 * 7 + 2) + n * 4, 0.0     # norm pass reads g; update reads p,g,m,v writes p,m,v,shadow
+
+
+CASES: Dict[str, Callable] = {"linear": case_linear, "dgrad": case_dgrad, "wgrad": case_wgrad,
+                              "wgrad_grouped": case_wgrad_grouped, "ffn_core_fwd": case_ffn_core_fwd,
+                              "ffn_core_bwd": case_ffn_core_bwd, "attn_fwd": case_attn_fwd, "attn_bwd": case_attn_bwd,
+                              "optimizer": case_optimizer}
+
+
+def time_op(fn, iters: int, warmup: int, flush: torch.Tensor) -> float:
+    """Median milliseconds over ``iters`` launches, each preceded by an L2 flush outside the timed events."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        flush.add_(1)                                   # evicts L2 (buffer larger than L2)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def run(op: str, tokens: int, iters: int, warmup: int) -> Dict[str, float]:
+    K = kmod.CudaKernels()
+    fn, byts, flops = CASES[op](K, tokens)
+    flush = torch.zeros(160 * 1024 * 1024 // 4, device="cuda")
+    ms = time_op(fn, iters, warmup, flush)
+    kmod.check_status(torch.device("cuda"))
+    assert not K.fallbacks, f"library fallback used: {dict(K.fallbacks)}"
+    pk, kind = peaks()
+    gbs, tfl = byts / ms / 1e6, flops / ms / 1e9
+    return {"op": op, "tokens": tokens, "ms": ms, "GB/s": gbs, "TFLOP/s": tfl, "frac_hbm": gbs / pk["hbm_gbs"],
+            "frac_bf16": tfl / pk["bf16_tflops"], "peaks": kind}
+
+
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--op", default="all", choices=["all"] + sorted(CASES))
+    ap.add_argument("--tokens", type=int, default=32768, help="rows M = batch x chunk tokens")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args(argv)
+    torch.manual_seed(0)
+    print(f"{'op':14s} {'tokens':>7s} {'ms':>9s} {'GB/s':>9s} {'of HBM':>7s} {'TFLOP/s':>9s} {'of bf16':>8s}")
+    for op in (sorted(CASES) if a.op == "all" else [a.op]):
+        r = run(op, a.tokens, a.iters, a.warmup)
+        print(f"{r['op']:14s} {r['tokens']:7d} {r['ms']:9.4f} {r['GB/s']:9.1f} {r['frac_hbm']:7.3f} {r['TFLOP/s']:9.1f} "
+              f"{r['frac_bf16']:8.3f}   ({r['peaks']} peaks)")
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()

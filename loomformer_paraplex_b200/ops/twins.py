@@ -188,6 +188,9 @@ class TorchKernels:
         r = torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)
         return (target * r * (g - xf * r * r * (g * xf).mean(-1, keepdim=True)))
 
+    def flush_wgrads(self) -> None:
+        """Issue any weight-gradient products that a kernel set queued for grouping (nothing is queued here)."""
+
     # ------------------------------------------------------------------ add + (cap) + LayerNorm
     def add_ln_fwd(self, a, b, w, bias, cap, eps=1e-5):
         """y = LN(cap(a) + cap(b)).  Returns (y, x, mean, rstd) with x the pre-norm sum."""

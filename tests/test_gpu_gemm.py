@@ -78,9 +78,38 @@ def test_segmented_batched_imag_projection():
         g1 = torch.zeros(d.hidden, d.imag_in, device="cuda")
         g2 = torch.zeros_like(g1)
         a1 = ck.imag_bwd(d, dbeta, qkc, u, m2, w, g1)
+        ck.flush_wgrads()
         a2 = tk.imag_bwd(d, dbeta.float(), qkc.float(), u.float(), m2.float(), w.float(), g2)
         k.check_status(u.device)
         assert not ck.fallbacks, ck.fallbacks
         assert _rel(g1, g2) < 1.5e-2
         for x1, x2 in zip(a1, a2):
             assert _rel(x1, x2) < 1.5e-2
+
+
+def test_grouped_wgrad_queue_equals_per_chunk_products():
+    """Sixteen queued chunk products leave as one launch with per-segment operands; a ragged queue flushes on demand."""
+    k = _k()
+    torch.manual_seed(5)
+    for chunks, rows in ((16, 256), (5, 200)):
+        ck = k.CudaKernels()
+        out, n_in = 384, 264
+        g = torch.randn(out, n_in, device="cuda")
+        ref = g.clone()
+        g3 = torch.zeros(48, 8, 72, device="cuda")           # batched (per-head) gradient view
+        ref3 = g3.clone()
+        for c in range(chunks):
+            dy = torch.randn(rows, out, device="cuda", dtype=torch.bfloat16)
+            x = torch.randn(rows, n_in, device="cuda", dtype=torch.bfloat16)
+            ck.linear_wgrad(dy, x, g)
+            ref += dy.float().t() @ x.float()
+            dyh = torch.randn(rows, 8, 48, device="cuda", dtype=torch.bfloat16)
+            xh = torch.randn(rows, 8, 72, device="cuda", dtype=torch.bfloat16)
+            ck._wgrad(dyh, xh, g3, 48, 72, 8)
+            ref3 += torch.einsum("rhm,rhn->mhn", dyh.float(), xh.float())
+        if chunks == 16:
+            assert not ck._wq                                  # a full group left by itself
+        ck.flush_wgrads()
+        k.check_status(g.device)
+        assert not ck.fallbacks and not ck._wq
+        assert _rel(g, ref) < 1e-2 and _rel(g3, ref3) < 1e-2
