@@ -138,7 +138,7 @@ class Model(nn.Module):
     @staticmethod
     def _doc_reset(position_ids: torch.Tensor) -> torch.Tensor:
         reset = position_ids.eq(0)
-        reset[:, 0] = True
+        reset[:, 0].fill_(True)          # fill_ takes the scalar as a kernel argument (no host-to-device copy)
         return reset
 
     # ------------------------------------------------------------------ attention (composed plan)
@@ -263,7 +263,7 @@ class Model(nn.Module):
         return h, carry, states
 
     # ------------------------------------------------------------------ fire plan
-    def fire_plan(self, idx: torch.Tensor, position_ids: torch.Tensor, last_may_fire: bool = False):
+    def fire_plan(self, idx: torch.Tensor, position_ids: torch.Tensor, last_may_fire: bool = False, cuts=None):
         """Reset mask, fire mask and the sorted list of cut columns for a chunked forward.
 
         A row fires at column ``i`` when ``(i+1) % W == 0`` (never at the last column, and not when
@@ -278,19 +278,24 @@ class Model(nn.Module):
         else:
             explicit = torch.zeros(B, T, dtype=torch.bool, device=idx.device)
         if self.tria_hard_fire_enabled:
-            grid = (torch.arange(T, device=idx.device) + 1).remainder(W).eq(0)
+            ar = torch.arange(T, device=idx.device)
+            grid = (ar + 1).remainder(W).eq(0)
             # A training sequence never fires at its last index.  A prompt that will be continued by the decoder
             # does (the decoder's rule: fire when the next position starts a new window and still fits).
-            if not (last_may_fire and T < self.d.seq_len):
-                grid[-1] = False
+            last_fires = bool(last_may_fire and T < self.d.seq_len and T % W == 0)      # known on the host
+            if not last_fires:
+                grid = grid & ar.ne(T - 1)          # device-side: a scalar store would be a host-to-device copy
         else:
             grid = torch.zeros(T, dtype=torch.bool, device=idx.device)
+            last_fires = False
         next_reset = torch.zeros_like(reset)
         next_reset[:, :-1] = reset[:, 1:]
         fire = (grid.view(1, T) & ~next_reset) | explicit
-        if self.carry_token_id is None:
+        if cuts is not None:
+            cuts = list(cuts)                       # the caller already knows them (no device read-back here)
+        elif self.carry_token_id is None:
             cuts = list(range(W - 1, T - 1, W)) if self.tria_hard_fire_enabled else []
-            if cuts is not None and bool(grid[-1]):
+            if last_fires:
                 cuts.append(T - 1)
         else:
             cuts = (grid | explicit.any(dim=0)).nonzero().flatten().tolist()

@@ -156,6 +156,28 @@ void rope_bwd(torch::Tensor dq_attn, torch::Tensor dqkc, torch::Tensor dkc, torc
   TORCH_CHECK(rc == 0, "loom_rope_bwd failed: ", rc);
 }
 
+void dread_stage(torch::Tensor a, c10::optional<torch::Tensor> b, torch::Tensor mo, torch::Tensor dm, torch::Tensor dd,
+                 int64_t MQ, int64_t HD) {
+  const c10::cuda::CUDAGuard guard(a.device());
+  TORCH_CHECK(a.is_contiguous() && mo.is_contiguous() && dm.is_contiguous() && (!b.has_value() || b->is_contiguous()),
+              "dread_stage: contiguous operands");
+  int rc = loom_dread_stage(a.data_ptr(), b.has_value() ? b->data_ptr() : nullptr, mo.data_ptr(), dm.data_ptr(),
+                            dd.data_ptr<float>(), MQ, (int)HD, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_dread_stage failed: ", rc);
+}
+
+void dread_slot_bwd(torch::Tensor q_all, torch::Tensor hk, torch::Tensor hv, torch::Tensor dm_all, torch::Tensor lse_all,
+                    torch::Tensor dd_all, torch::Tensor dk, torch::Tensor dv, torch::Tensor gq_all, int64_t sub0, int64_t S,
+                    int64_t M, int64_t QH, int64_t HD) {
+  const c10::cuda::CUDAGuard guard(hk.device());
+  TORCH_CHECK(hk.is_contiguous() && hv.is_contiguous() && dm_all.is_contiguous() && dk.is_contiguous() && dv.is_contiguous(),
+              "dread_slot_bwd: contiguous operands");
+  int rc = loom_dread_slot_bwd(q_all.data_ptr<float>(), hk.data_ptr(), hv.data_ptr(), dm_all.data_ptr(),
+                               lse_all.data_ptr<float>(), dd_all.data_ptr<float>(), dk.data_ptr(), dv.data_ptr(),
+                               gq_all.data_ptr<float>(), (int)sub0, (int)S, (int)M, (int)QH, (int)HD, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_dread_slot_bwd failed: ", rc);
+}
+
 void dread(bool bwd, torch::Tensor q, torch::Tensor hk, torch::Tensor hv, torch::Tensor out, torch::Tensor lse, OptT dm,
            OptT dhk, OptT dhv, OptT gq, int64_t n, int64_t MQ, int64_t QH, int64_t HD) {
   const c10::cuda::CUDAGuard guard(hk.device());
@@ -260,6 +282,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rope_store", &rope_store, "RoPE + KV cache write");
   m.def("rope_bwd", &rope_bwd, "inverse RoPE of the q/k/v gradients");
   m.def("dread", &dread, "depth-attention read (forward / backward)");
+  m.def("dread_stage", &dread_stage, "store a sublayer's read gradient (bf16) and its <dm, m> row scalars");
+  m.def("dread_slot_bwd", &dread_slot_bwd, "gradient of one history slot over every sublayer that read it");
   m.def("add_ln_fwd", &add_ln_fwd, "residual add + LayerNorm");
   m.def("add_ln_bwd", &add_ln_bwd, "residual add + LayerNorm backward");
   m.def("colsum", &colsum, "column sums into an fp32 accumulator");

@@ -1,0 +1,240 @@
+// Depth-attention backward, organised per history slot.
+//
+// Sublayer `sub` of a chunk reads history slots 0..sub with a softmax over slots:
+//     w[sub,s] = exp(<q_sub, k_s>/sqrt(HD) - lse_sub),   m_sub = sum_s w[sub,s] v_s .
+// A gradient pass organised per sublayer has to add every sublayer's contribution into fp32
+// accumulators of ALL earlier slots -- read-modify-write traffic that grows with the square of the
+// depth (about 20 bytes per element per (sublayer, slot) pair).  The slot's gradient is only consumed
+// when the backward sweep reaches the layer that produced the slot, and by then every sublayer that
+// reads it has already delivered its output gradient dm_sub.  So the sweep stores dm_sub (bf16) and
+// the per-row scalar dd_sub = <dm_sub, m_sub>, and ONE launch per slot forms
+//     dv_s = sum_{sub>=s} w[sub,s] dm_sub ,   dk_s = sum_{sub>=s} dsc[sub,s] q_sub / sqrt(HD),
+//     dsc[sub,s] = w[sub,s] (<dm_sub, v_s> - dd_sub),
+// reading k_s, v_s once, each dm_sub once (2 bytes per element per pair) and writing dk_s, dv_s once,
+// with no accumulator in memory.  The query gradients gq[sub] += sum_rows dsc[sub,s] k_s / sqrt(HD)
+// are reduced in registers by a block that serves a single head, then flushed once.
+//
+// The reference computes the same quantities with one kernel per sublayer over all earlier slots
+// (reference kernels/depth_attn/depth_attn_kernel.cuh:515-651).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "loom_c_api.h"
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(p[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+
+// dm = a (+ b) stored as bf16, dd = <dm, m> per (row, head).  G lanes per (row, head), 8 dims per lane.
+template <int G>
+__global__ void __launch_bounds__(256) dread_stage_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b,
+                                                          const bf16* __restrict__ mo, bf16* __restrict__ dm,
+                                                          float* __restrict__ dd, long long MQ, int HD) {
+  const long long gid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / G;
+  const int l = threadIdx.x % G;
+  if (gid >= MQ) return;
+  const unsigned mask = __activemask();
+  float s = 0.f;
+  if (l * 8 < HD) {
+    const long long base = gid * HD + l * 8;
+    float x[8], y[8], m[8];
+    unpack8(*reinterpret_cast<const uint4*>(a + base), x);
+    if (b) {
+      unpack8(*reinterpret_cast<const uint4*>(b + base), y);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] += y[i];
+    }
+    const uint4 packed = pack8(x);
+    *reinterpret_cast<uint4*>(dm + base) = packed;
+    unpack8(packed, x);                       // dd must see the rounded values the slot kernel will read
+    unpack8(*reinterpret_cast<const uint4*>(mo + base), m);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += x[i] * m[i];
+  }
+#pragma unroll
+  for (int o = G / 2; o > 0; o >>= 1) s += __shfl_xor_sync(mask, s, o, G);
+  if (l == 0) dd[gid] = s;
+}
+
+// grid: (row blocks, QH).  q_all [S,QH,HD] fp32; dm_all [S,M,QH,HD] bf16; lse_all, dd_all [S,M,QH] fp32;
+// hk, hv: the slot's K and V [M,QH,HD] bf16; dk, dv out [M,QH,HD] bf16; gq_all [S,QH,HD] fp32 (+=).
+//
+// A block serves one head and walks over tiles of TILE rows.  Phase 1: each G-lane group keeps one row's k, v and
+// the two accumulators in registers and loops over the reading sublayers; the scalar dsc[row][sub] and the row's k
+// go to shared memory.  Phase 2: the block re-maps to (sublayer, dim) pairs and adds sum_rows dsc * k into
+// per-thread registers, so the query gradients need neither shared-memory atomics nor per-row global traffic;
+// they leave the block once, at the end.
+constexpr int MAX_PAIRS = 10;      // ceil(20 sublayers * 128 dims / 256 threads)
+
+template <int G>
+__global__ void __launch_bounds__(256) dread_slot_bwd_kernel(const float* __restrict__ q_all, const bf16* __restrict__ hk,
+                                                             const bf16* __restrict__ hv, const bf16* __restrict__ dm_all,
+                                                             const float* __restrict__ lse_all,
+                                                             const float* __restrict__ dd_all, bf16* __restrict__ dk,
+                                                             bf16* __restrict__ dv, float* __restrict__ gq_all, int sub0,
+                                                             int S, int M, int QH, int HD, float scale) {
+  constexpr int NGRP = 256 / G;
+  constexpr int TILE = 2 * NGRP;              // rows per tile: every group takes two
+  extern __shared__ float sh[];               // [nsub][HD] queries | [TILE][nsub] dsc | [TILE][HD] k rows
+  const int g = blockIdx.y;
+  const int nsub = S - sub0;
+  float* sq = sh;
+  float* sd = sq + nsub * HD;
+  float* sk = sd + TILE * nsub;
+  for (int i = threadIdx.x; i < nsub * HD; i += blockDim.x) {
+    const int jj = i / HD, c = i % HD;
+    sq[i] = q_all[((long long)(sub0 + jj) * QH + g) * HD + c];
+  }
+  float gacc[MAX_PAIRS];
+#pragma unroll
+  for (int i = 0; i < MAX_PAIRS; ++i) gacc[i] = 0.f;
+  __syncthreads();
+  const int l = threadIdx.x % G, grp = threadIdx.x / G;
+  const bool act = l * 8 < HD;
+  const long long MQ = (long long)M * QH;
+  const int npairs = nsub * HD;
+  for (int m0 = blockIdx.x * TILE; m0 < M; m0 += gridDim.x * TILE) {
+#pragma unroll 1
+    for (int rr = 0; rr < 2; ++rr) {
+      const int row = grp * 2 + rr;
+      const int m = m0 + row;
+      const bool live = m < M;                 // uniform within a group
+      const long long rh = (long long)(live ? m : 0) * QH + g;
+      const long long base = rh * HD + l * 8;
+      float kf[8], vf[8], ak[8], av[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { kf[i] = 0.f; vf[i] = 0.f; ak[i] = 0.f; av[i] = 0.f; }
+      if (act && live) {
+        unpack8(*reinterpret_cast<const uint4*>(hk + base), kf);
+        unpack8(*reinterpret_cast<const uint4*>(hv + base), vf);
+      }
+      if (act) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sk[row * HD + l * 8 + i] = kf[i];
+      }
+#pragma unroll 4
+      for (int jj = 0; jj < nsub; ++jj) {       // unrolled so the independent dm / lse / dd loads of four sublayers overlap
+        const long long so = (long long)(sub0 + jj);
+        float dmf[8], qv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { dmf[i] = 0.f; qv[i] = 0.f; }
+        if (act && live) {
+          unpack8(*reinterpret_cast<const uint4*>(dm_all + so * MQ * HD + base), dmf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) qv[i] = sq[jj * HD + l * 8 + i];
+        }
+        float d = 0.f, dvv = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { d += qv[i] * kf[i]; dvv += dmf[i] * vf[i]; }
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) {
+          d += __shfl_xor_sync(0xffffffffu, d, o, G);
+          dvv += __shfl_xor_sync(0xffffffffu, dvv, o, G);
+        }
+        float w = 0.f, dsc = 0.f;
+        if (live) {
+          w = __expf(d * scale - lse_all[so * MQ + rh]);
+          dsc = w * (dvv - dd_all[so * MQ + rh]) * scale;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { ak[i] += dsc * qv[i]; av[i] += w * dmf[i]; }
+        if (l == 0) sd[row * nsub + jj] = dsc;
+      }
+      if (act && live) {
+        *reinterpret_cast<uint4*>(dk + base) = pack8(ak);
+        *reinterpret_cast<uint4*>(dv + base) = pack8(av);
+      }
+    }
+    __syncthreads();
+    // phase 2: query-gradient partials of this tile
+#pragma unroll
+    for (int pi = 0; pi < MAX_PAIRS; ++pi) {
+      const int pidx = threadIdx.x + pi * 256;
+      if (pidx < npairs) {
+        const int jj = pidx / HD, c = pidx % HD;
+        float a = 0.f;
+#pragma unroll 8
+        for (int r = 0; r < TILE; ++r) a += sd[r * nsub + jj] * sk[r * HD + c];
+        gacc[pi] += a;
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int pi = 0; pi < MAX_PAIRS; ++pi) {
+    const int pidx = threadIdx.x + pi * 256;
+    if (pidx < npairs && gacc[pi] != 0.f) {
+      const int jj = pidx / HD, c = pidx % HD;
+      atomicAdd(gq_all + ((long long)(sub0 + jj) * QH + g) * HD + c, gacc[pi]);
+    }
+  }
+}
+
+template <int G>
+int launch_stage(const void* a, const void* b, const void* mo, void* dm, float* dd, long long MQ, int HD, cudaStream_t st) {
+  const long long threads = MQ * G;
+  dread_stage_kernel<G><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>((const bf16*)a, (const bf16*)b, (const bf16*)mo,
+                                                                            (bf16*)dm, dd, MQ, HD);
+  return (int)cudaGetLastError();
+}
+
+template <int G>
+int launch_slot(const float* q_all, const void* hk, const void* hv, const void* dm_all, const float* lse_all,
+                const float* dd_all, void* dk, void* dv, float* gq_all, int sub0, int S, int M, int QH, int HD,
+                cudaStream_t st) {
+  const int nsub = S - sub0;
+  constexpr int TILE = 2 * (256 / G);
+  if ((long long)nsub * HD > 256LL * MAX_PAIRS) return -2;
+  const size_t shm = ((size_t)nsub * HD + (size_t)TILE * nsub + (size_t)TILE * HD) * sizeof(float);
+  if (shm > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(dread_slot_bwd_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shm);
+    if (e != cudaSuccess) return (int)e;
+  }
+  static int sms = 0;
+  if (sms == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+  int bx = (sms * 4 + QH - 1) / QH;                 // about four resident blocks per SM over all heads
+  const int need = (M + TILE - 1) / TILE;
+  if (bx > need) bx = need;
+  if (bx < 1) bx = 1;
+  dim3 grid(bx, QH);
+  dread_slot_bwd_kernel<G><<<grid, 256, shm, st>>>(q_all, (const bf16*)hk, (const bf16*)hv, (const bf16*)dm_all, lse_all,
+                                                   dd_all, (bf16*)dk, (bf16*)dv, gq_all, sub0, S, M, QH, HD,
+                                                   rsqrtf((float)HD));
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" int loom_dread_stage(const void* a, const void* b, const void* mo, void* dm, float* dd, long long MQ, int HD,
+                                cudaStream_t st) {
+  if (HD % 8 || HD > 128) return -1;
+  const int chunks = HD / 8;
+  if (chunks <= 2) return launch_stage<2>(a, b, mo, dm, dd, MQ, HD, st);
+  if (chunks <= 4) return launch_stage<4>(a, b, mo, dm, dd, MQ, HD, st);
+  if (chunks <= 8) return launch_stage<8>(a, b, mo, dm, dd, MQ, HD, st);
+  return launch_stage<16>(a, b, mo, dm, dd, MQ, HD, st);
+}
+
+extern "C" int loom_dread_slot_bwd(const float* q_all, const void* hk, const void* hv, const void* dm_all,
+                                   const float* lse_all, const float* dd_all, void* dk, void* dv, float* gq_all, int sub0,
+                                   int S, int M, int QH, int HD, cudaStream_t st) {
+  if (HD % 8 || HD > 128 || sub0 < 0 || sub0 >= S) return -1;
+  const int chunks = HD / 8;
+  if (chunks <= 2) return launch_slot<2>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, st);
+  if (chunks <= 4) return launch_slot<4>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, st);
+  if (chunks <= 8) return launch_slot<8>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, st);
+  return launch_slot<16>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, st);
+}

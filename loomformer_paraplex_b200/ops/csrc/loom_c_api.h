@@ -86,6 +86,12 @@ int loom_rope_store(const void* qkv, const float* cs, const float* sn, void* qkc
 int loom_rope_bwd(const void* dq_attn, const void* dqkc, const float* dkc, const float* dvc, const float* cs,
                   const float* sn, void* dqkv, int M, int Tc, int T, int s_off, int QH, int KVH, int HD, int G,
                   cudaStream_t st);
+// depth-attention backward organised per history slot (depth_read_bwd.cu)
+int loom_dread_stage(const void* a, const void* b_or_null, const void* m_out, void* dm, float* dd, long long MQ, int HD,
+                     cudaStream_t st);
+int loom_dread_slot_bwd(const float* q_all, const void* hk_slot, const void* hv_slot, const void* dm_all,
+                        const float* lse_all, const float* dd_all, void* dk, void* dv, float* gq_all, int sub0, int S,
+                        int M, int QH, int HD, cudaStream_t st);
 int loom_dread(int bwd, const float* q, const void* hk, const void* hv, void* out, float* lse, const void* dm, float* dhk,
                float* dhv, float* gq, int n, long long MQ, int QH, int HD, cudaStream_t st);
 int loom_add_ln_fwd(const void* a, const void* b, const float* w, const float* bias, void* y, void* x, float* mean,

@@ -46,6 +46,7 @@ class FusedPlan:
         self.flat = flat
         self.adt = compute_dtype or (torch.bfloat16 if dev.type == "cuda" else torch.float32)
         self._wcache: Dict[int, torch.Tensor] = {}
+        self._consts: Dict[tuple, torch.Tensor] = {}
         self.anchor_sync = None        # optional callable(sumsq [L], count) for cross-rank anchor statistics
 
     # ------------------------------------------------------------------ parameter access
@@ -65,6 +66,15 @@ class FusedPlan:
                 self._wcache[key] = v
             return v
         return p.data.to(self.adt)
+
+    def _const(self, values: tuple, dev) -> torch.Tensor:
+        """Small integer constants as a cached device tensor (no host-to-device copy once a shape has been seen,
+        which keeps the step free of pageable copies and therefore capturable in a CUDA graph)."""
+        key = (values, str(dev))
+        t = self._consts.get(key)
+        if t is None:
+            t = self._consts[key] = torch.tensor(values, device=dev)
+        return t
 
     @staticmethod
     def g(p: torch.Tensor) -> torch.Tensor:
@@ -92,7 +102,7 @@ class FusedPlan:
 
     # ------------------------------------------------------------------ the step
     def run(self, idx, y, position_ids, seg, want_grad: bool, ignore_index: int = -100, grad_scale: float = 1.0,
-            return_state: bool = False):
+            return_state: bool = False, cuts=None):
         """Forward (and, with ``want_grad``, backward into ``param.grad``).  Returns (loss, logits); with
         ``return_state`` (inference) additionally the caches a decoder needs to continue the sequences."""
         m, d, K = self.model, self.d, self.K
@@ -102,7 +112,7 @@ class FusedPlan:
             position_ids = torch.arange(T, device=dev).view(1, T).expand(B, T)
         chunked = d.tria and d.tria_temporal and not m.ablation
         if chunked:
-            reset, fire, cuts = m.fire_plan(idx, position_ids, last_may_fire=return_state)
+            reset, fire, cuts = m.fire_plan(idx, position_ids, last_may_fire=return_state, cuts=cuts)
         else:
             reset, fire, cuts = m._doc_reset(position_ids), None, []
         cut_set = set(cuts)
@@ -155,7 +165,7 @@ class FusedPlan:
         ro = None
         if keys:
             ro = self._readout_forward(h, torch.stack(keys, 1), torch.stack(key_valid, 1),
-                                       torch.tensor(key_pos, device=dev), seg)
+                                       self._const(tuple(key_pos), dev), seg)
             h = ro["h_out"]
         hn = K.rms_norm_fwd(h, m.ln_final.weight) if m.ln_final is not None else h
         logits = K.linear(hn.reshape(B * T, d.n), self.w(m.head.weight)).view(B, T, d.vocab)
@@ -228,11 +238,13 @@ class FusedPlan:
             k, v = K.fixed_rms_fwd(k, FANIN_GAIN), K.fixed_rms_fwd(v, FANIN_GAIN * d.deepnorm_beta)
         hist_k[slot], hist_v[slot] = k, v
 
-    def _project_state_bwd(self, x2d, slot, dhist_k, dhist_v, tape_layer, key):
-        """Gradient of :meth:`_project_state` w.r.t. its input; accumulates the weight gradient."""
+    def _project_state_bwd(self, x2d, slot, dstate, hist_k, hist_v, tape_layer, key):
+        """Gradient of :meth:`_project_state` w.r.t. its input; accumulates the weight gradient.  The slot's own
+        gradient is formed here, in one pass over every sublayer that read the slot."""
         m, d, K = self.model, self.d, self.K
         M = x2d.shape[0]
-        dk, dv = dhist_k[slot], dhist_v[slot]
+        dk, dv = K.dread_slot_bwd(d, slot, dstate["q"], hist_k, hist_v, dstate["dm"], dstate["lse"], dstate["dd"],
+                                  dstate["gq"])
         if d.depth_qkv_rms:
             kv = tape_layer[key + "_kv_raw"]
             dk = K.fixed_rms_bwd(dk, kv[:, :d.n].view(M, d.qh, d.hd), FANIN_GAIN)
@@ -362,8 +374,14 @@ class FusedPlan:
         M, N, L = B * Tc, d.n, d.layers
         dev = dh_out.device
         hist_k, hist_v = tape["hist_k"], tape["hist_v"]
-        dhk = torch.zeros(hist_k.shape, dtype=torch.float32, device=dev)
-        dhv = torch.zeros(hist_v.shape, dtype=torch.float32, device=dev)
+        # depth attention: every sublayer's read gradient is staged; a slot's gradient is formed when the sweep reaches
+        # the layer that produced the slot (by then all of its readers have been staged)
+        S = 2 * L
+        dst = {"q": torch.stack([self._depth_query(sub) for sub in range(S)]).contiguous(),
+               "dm": torch.empty(S, M, d.qh, d.hd, dtype=self.adt, device=dev),
+               "lse": torch.empty(S, M, d.qh, dtype=torch.float32, device=dev),
+               "dd": torch.empty(S, M, d.qh, dtype=torch.float32, device=dev),
+               "gq": torch.zeros(S, d.qh, d.hd, dtype=torch.float32, device=dev)}
         dh = dh_out.reshape(M, N).to(self.adt)
         dc = ddepth                      # carrier-layout gradient (opaque to the plan)
         dp_out = None
@@ -376,7 +394,7 @@ class FusedPlan:
             last = bi == L - 1
             sub = 2 * bi
             if not last:
-                dh = dh + self._project_state_bwd(t["h_out"], sub + 2, dhk, dhv, t, "h")
+                dh = dh + self._project_state_bwd(t["h_out"], sub + 2, dst, hist_k, hist_v, t, "h")
             # --- LN2 and the two addends
             ds2, df = K.add_ln_bwd(dh, t["x2"], t["mean2"], t["rstd2"], blk.ln_ffn.weight.data,
                                    self.g(blk.ln_ffn.weight), self.g(blk.ln_ffn.bias), cap, t.get("s2"), t.get("f"))
@@ -417,20 +435,15 @@ class FusedPlan:
             du = du + du_i
             # --- depth read 2bi+1 (its output feeds the readout GEMM and the imaginary projection)
             K.linear_wgrad(ds2, t["m2"].reshape(M, N), self._readout_g(sub + 1))
-            dm2 = K.linear_dgrad(ds2, self._readout_w(sub + 1)).view(M, d.qh, d.hd) + dm2_i
-            gq = torch.zeros(d.qh, d.hd, dtype=torch.float32, device=dev)
-            K.dread_bwd(d, dm2, t["m2"], t["lse2"], self._depth_query(sub + 1), hist_k, hist_v, sub + 2, dhk, dhv, gq)
-            self._depth_query_bwd(sub + 1, gq)
-            du = du + self._project_state_bwd(u, sub + 1, dhk, dhv, t, "u")
+            K.dread_stage(d, K.linear_dgrad(ds2, self._readout_w(sub + 1)).view(M, d.qh, d.hd), dm2_i, t["m2"], t["lse2"],
+                          dst, sub + 1)
+            du = du + self._project_state_bwd(u, sub + 1, dst, hist_k, hist_v, t, "u")
             # --- LN1
             ds1, da = K.add_ln_bwd(du, t["x1"], t["mean1"], t["rstd1"], blk.ln_attn.weight.data,
                                    self.g(blk.ln_attn.weight), self.g(blk.ln_attn.bias), cap, t.get("s1"), t.get("a"))
             K.linear_wgrad(ds1, t["m1"], self._readout_g(sub))
-            dm1 = K.linear_dgrad(ds1, self._readout_w(sub)).view(M, d.qh, d.hd)
-            gq = torch.zeros(d.qh, d.hd, dtype=torch.float32, device=dev)
-            K.dread_bwd(d, dm1, t["m1"].view(M, d.qh, d.hd), t["lse1"], self._depth_query(sub), hist_k, hist_v,
-                        sub + 1, dhk, dhv, gq)
-            self._depth_query_bwd(sub, gq)
+            K.dread_stage(d, K.linear_dgrad(ds1, self._readout_w(sub)).view(M, d.qh, d.hd), None,
+                          t["m1"].view(M, d.qh, d.hd), t["lse1"], dst, sub)
             # --- attention
             qkc = t["qkc"]
             K.linear_wgrad(da, qkc[:, 2].reshape(M, N), self.g(blk.attn.o.weight))
@@ -440,7 +453,9 @@ class FusedPlan:
                               tape["sin"], self.adt).view(M, -1)
             K.linear_wgrad(dqkv, t["h_in"], self.g(blk.attn.qkv_weight))
             dh = K.linear_dgrad(dqkv, self.w(blk.attn.qkv_weight))
-        dh = dh + self._project_state_bwd(tape["h_emb"], 0, dhk, dhv, tape["emb_l"], "emb")
+        dh = dh + self._project_state_bwd(tape["h_emb"], 0, dst, hist_k, hist_v, tape["emb_l"], "emb")
+        for sub in range(S):
+            self._depth_query_bwd(sub, dst["gq"][sub])
         return dh, dtraces_in, dseed
 
     # ------------------------------------------------------------------ readout

@@ -320,6 +320,28 @@ class _ElementwiseMixin:
                            M * d.qh, d.qh, d.hd)
         native.count()
 
+    def dread_stage(self, d, a, b, m, lse, dst, sub):
+        dm_all = dst["dm"]
+        if not (dm_all.dtype == torch.bfloat16 and d.hd % 8 == 0 and d.hd <= 128):
+            self.fallbacks["dread_stage"] += 1
+            return super().dread_stage(d, a, b, m, lse, dst, sub)
+        M = dm_all.shape[1]
+        native.ext().dread_stage(_bf16c(a), _opt(b, _bf16c), _bf16c(m), dm_all[sub], dst["dd"][sub], M * d.qh, d.hd)
+        dst["lse"][sub].copy_(lse)
+        native.count()
+
+    def dread_slot_bwd(self, d, slot, q_all, hist_k, hist_v, dm_all, lse_all, dd_all, gq_all):
+        if not (self._dread_ok(d, hist_k) and dm_all.dtype == torch.bfloat16):
+            self.fallbacks["dread_slot_bwd"] += 1
+            return super().dread_slot_bwd(d, slot, q_all, hist_k, hist_v, dm_all, lse_all, dd_all, gq_all)
+        S, M = dm_all.shape[0], dm_all.shape[1]
+        dk = torch.empty(M, d.qh, d.hd, dtype=torch.bfloat16, device=hist_k.device)
+        dv = torch.empty_like(dk)
+        native.ext().dread_slot_bwd(q_all, hist_k[slot], hist_v[slot], dm_all, lse_all, dd_all, dk, dv, gq_all, slot, S, M,
+                                    d.qh, d.hd)
+        native.count()
+        return dk, dv
+
     # ------------------------------------------------------------------ add + LayerNorm
     def add_ln_fwd(self, a, b, w, bias, cap, eps=1e-5):
         M, N = a.shape

@@ -140,6 +140,27 @@ def case_attn_bwd(K, M, Tc=128, T=1024):
     return run, nbytes(qkc, dqkc, kc, vc) + 2 * nbytes(dk, dv), 7 * 2.0 * B * d.qh * Tc * T * d.hd
 
 
+def case_dread_slot_bwd(K, M, S=20, slot=5):
+    """Gradient of one depth-history slot over the 15 sublayers that read it (10-layer model)."""
+    d = dims()
+    hk, hv = bf(S, M, d.qh, d.hd), bf(S, M, d.qh, d.hd)
+    q_all = torch.randn(S, d.qh, d.hd, device="cuda")
+    dm, lse, dd = bf(S, M, d.qh, d.hd, scale=0.3), torch.randn(S, M, d.qh, device="cuda") + 3, torch.randn(S, M, d.qh, device="cuda")
+    gq = torch.zeros(S, d.qh, d.hd, device="cuda")
+    run = lambda: K.dread_slot_bwd(d, slot, q_all, hk, hv, dm, lse, dd, gq)
+    dk, dv = run()
+    return run, nbytes(hk[slot], hv[slot], dk, dv) + nbytes(dm[slot:], lse[slot:], dd[slot:]), 0.0
+
+
+def case_dread_fwd(K, M, S=20, n=11):
+    d = dims()
+    hk, hv = bf(S, M, d.qh, d.hd), bf(S, M, d.qh, d.hd)
+    q = torch.randn(d.qh, d.hd, device="cuda")
+    run = lambda: K.dread_fwd(d, q, hk, hv, n)
+    out, lse = run()
+    return run, nbytes(hk[:n], hv[:n], out, lse), 0.0
+
+
 def case_optimizer(K, M):
     from ..optim.flat import FlatOptimizer, FlatParams
     lin = torch.nn.Linear(4096, max(256, M // 4), bias=False).cuda()        # ~M*1024 parameters
@@ -153,6 +174,7 @@ def case_optimizer(K, M):
 CASES: Dict[str, Callable] = {"linear": case_linear, "dgrad": case_dgrad, "wgrad": case_wgrad,
                               "wgrad_grouped": case_wgrad_grouped, "ffn_core_fwd": case_ffn_core_fwd,
                               "ffn_core_bwd": case_ffn_core_bwd, "attn_fwd": case_attn_fwd, "attn_bwd": case_attn_bwd,
+                              "dread_slot_bwd": case_dread_slot_bwd, "dread_fwd": case_dread_fwd,
                               "optimizer": case_optimizer}
 
 

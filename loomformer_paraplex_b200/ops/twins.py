@@ -180,6 +180,26 @@ class TorchKernels:
         dhist_k[:n].add_(dsc.unsqueeze(-1) * q_row.float())
         gq.add_((dsc.unsqueeze(-1) * k).sum((0, 1)))
 
+    def dread_stage(self, d, a, b, m, lse, dst, sub):
+        """Stage sublayer ``sub``'s read gradient: ``dm[sub] = a (+ b)``, ``dd[sub] = <dm, m>``, ``lse[sub] = lse``."""
+        dm = a if b is None else a + b
+        dst["dm"][sub] = dm.to(dst["dm"].dtype)
+        dst["dd"][sub] = (dst["dm"][sub].float() * m.float()).sum(-1)
+        dst["lse"][sub] = lse
+
+    def dread_slot_bwd(self, d, slot, q_all, hist_k, hist_v, dm_all, lse_all, dd_all, gq_all):
+        """Gradient of history slot ``slot`` summed over the sublayers ``slot..S-1`` that read it -> (dk, dv)
+        [M,QH,HD]; adds those sublayers' query gradients into ``gq_all``."""
+        inv = 1.0 / math.sqrt(d.hd)
+        k, v = hist_k[slot].float(), hist_v[slot].float()
+        q, dmf = q_all[slot:].float(), dm_all[slot:].float()
+        w = torch.exp(torch.einsum("mgh,ngh->nmg", k, q) * inv - lse_all[slot:])
+        dsc = w * ((dmf * v).sum(-1) - dd_all[slot:]) * inv
+        gq_all[slot:].add_(torch.einsum("nmg,mgh->ngh", dsc, k))
+        dk = torch.einsum("nmg,ngh->mgh", dsc, q)
+        dv = (w.unsqueeze(-1) * dmf).sum(0)
+        return dk.to(hist_k.dtype), dv.to(hist_v.dtype)
+
     def fixed_rms_fwd(self, x, target):
         return R.fixed_rms(x, target)
 

@@ -14,6 +14,7 @@ guards (one fused finite flag instead of a host sync per parameter).
 from __future__ import annotations
 
 import contextlib
+import os
 import math
 import re
 from typing import Dict, Optional
@@ -55,7 +56,7 @@ def train_lr_overrides(model, cfg: Config) -> Dict[str, float]:
 class TrainEngine:
     def __init__(self, cfg: Config, model, device: torch.device, *, optimizer: Optional[str] = None,
                  grad_sync: str = "collective", anchor_mode: str = "mean", loss_mask_ignore: int = -100,
-                 train_lr: bool = True) -> None:
+                 train_lr: bool = True, cuda_graph: Optional[bool] = None) -> None:
         self.cfg, self.model, self.device = cfg, model, device
         self.accum = max(1, int(cfg.grad_accum_steps or 1))
         self.amp = cfg.amp_dtype if device.type == "cuda" else "fp32"
@@ -75,6 +76,13 @@ class TrainEngine:
         self.plan = model._opset(model.emb.weight) if not model.ablation else None   # fused plan on CUDA
         if self.plan is not None:
             self.plan.bind(self.flat)
+        # Whole forward+backward of a micro-batch as one CUDA graph: the fused plan issues several thousand launches per
+        # step and the host cannot enqueue them as fast as a B200 retires them.  On by default on CUDA, off with
+        # LOOM_CUDA_GRAPH=0 or ``cfg.graph: false`` given explicitly through ``cuda_graph``.
+        if cuda_graph is None:
+            cuda_graph = os.environ.get("LOOM_CUDA_GRAPH", "1") != "0"
+        self.use_graph = bool(cuda_graph and device.type == "cuda" and self.plan is not None)
+        self._graphs: Dict[tuple, dict] = {}
         self.step_idx = 0           # completed optimizer steps
         self.ignore_index = loss_mask_ignore
         self.last_fire_count = torch.zeros((), dtype=torch.long, device=device)
@@ -93,6 +101,52 @@ class TrainEngine:
 
     def to_device(self, batch: torch.Tensor) -> torch.Tensor:
         return batch.to(self.device, non_blocking=True) if batch.device != self.device else batch
+
+    # ------------------------------------------------------------------ graph-replayed micro-batch
+    GRAPH_WARMUP = 2        # eager runs per shape before capture (lazy kernel attributes, allocator, constant caches)
+
+    def _graphed_micro(self, x, y, position_ids, segment_ids, scale: float) -> torch.Tensor:
+        """Forward + backward of one micro-batch (gradients accumulate into the flat buffer).  The first runs of a
+        shape are eager; then the launch sequence is captured once and replayed with the inputs copied into the
+        graph's static buffers.  Chunk boundaries are part of the graph, so a batch whose ``<CARRY>`` columns differ
+        gets its own graph (their positions are read back once per step only when the tokenizer has that token)."""
+        from ..ops import native
+        m = self.model
+        cuts = None
+        if m.carry_token_id is not None and m.d.tria and m.d.tria_temporal:
+            pos = position_ids if position_ids is not None else \
+                torch.arange(x.shape[1], device=x.device).view(1, -1).expand(x.shape[0], -1)
+            cuts = tuple(m.fire_plan(x, pos)[2])
+        key = (tuple(x.shape), position_ids is not None, segment_ids is not None, cuts, float(scale))
+        ent = self._graphs.setdefault(key, {"runs": 0, "graph": None})
+        if ent["graph"] is None and ent["runs"] < self.GRAPH_WARMUP:
+            ent["runs"] += 1
+            with torch.no_grad():
+                loss, _ = self.plan.run(x, y, position_ids, segment_ids, want_grad=True, ignore_index=self.ignore_index,
+                                        grad_scale=scale, cuts=cuts)
+            return loss
+        if ent["graph"] is None:
+            ent["x"], ent["y"] = x.clone(), y.clone()
+            ent["pos"] = None if position_ids is None else position_ids.clone()
+            ent["seg"] = None if segment_ids is None else segment_ids.clone()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            before = native.launches()
+            with torch.no_grad(), torch.cuda.graph(g):
+                ent["loss"], _ = self.plan.run(ent["x"], ent["y"], ent["pos"], ent["seg"], want_grad=True,
+                                               ignore_index=self.ignore_index, grad_scale=scale, cuts=cuts)
+                ent["fire"] = m.last_tria_fire_mask
+            ent["launches"] = native.launches() - before
+            ent["graph"] = g
+        ent["x"].copy_(x); ent["y"].copy_(y)
+        if ent["pos"] is not None:
+            ent["pos"].copy_(position_ids)
+        if ent["seg"] is not None:
+            ent["seg"].copy_(segment_ids)
+        ent["graph"].replay()
+        native.count(ent["launches"])
+        m.last_tria_fire_mask = ent["fire"]
+        return ent["loss"].clone()
 
     # ------------------------------------------------------------------ one optimizer step
     def step(self, batch, targets: Optional[torch.Tensor] = None, attn_mask=None, position_ids=None,
@@ -114,9 +168,13 @@ class TrainEngine:
                 x, y = self.to_device(mb), self.to_device(targets)
             mask_i = attn_mask
             if self.plan is not None and attn_mask is None:
-                with torch.no_grad():
-                    loss, _ = self.plan.run(x, y, position_ids, segment_ids, want_grad=True,
-                                            ignore_index=self.ignore_index, grad_scale=1.0 / float(len(micro)))
+                scale = 1.0 / float(len(micro))
+                if self.use_graph:
+                    loss = self._graphed_micro(x, y, position_ids, segment_ids, scale)
+                else:
+                    with torch.no_grad():
+                        loss, _ = self.plan.run(x, y, position_ids, segment_ids, want_grad=True,
+                                                ignore_index=self.ignore_index, grad_scale=scale)
             else:
                 if segment_ids is not None and mask_i is None:
                     T = x.shape[1]

@@ -252,3 +252,30 @@ def test_attention_backward(hd, qh, kvh, Tc, s):
     g = qh // kvh
     _close((dk1 - 1.0).view(B, T, kvh, g, hd).sum(3), dk2, 3e-2, "dk")
     _close(dv1.view(B, T, kvh, g, hd).sum(3), dv2, 3e-2, "dv")
+
+
+@pytest.mark.parametrize("hd,qh", [(96, 8), (32, 4)])
+def test_depth_read_backward_per_slot(hd, qh):
+    """Staged per-slot backward equals the sum of per-sublayer contributions evaluated in fp32."""
+    ck, tk = _sets()
+    d = _dims(qh=qh, hd=hd, kvh=qh)
+    S, M = 6, 200
+    torch.manual_seed(9)
+    hk, hv = bf(S, M, qh, hd), bf(S, M, qh, hd)
+    q_all = torch.randn(S, qh, hd, device="cuda")
+    mk = lambda dt: {"q": q_all, "dm": torch.zeros(S, M, qh, hd, dtype=dt, device="cuda"),
+                     "lse": torch.zeros(S, M, qh, device="cuda"), "dd": torch.zeros(S, M, qh, device="cuda"),
+                     "gq": torch.zeros(S, qh, hd, device="cuda")}
+    d1, d2 = mk(torch.bfloat16), mk(torch.float32)
+    for sub in range(S):
+        m_out, lse = tk.dread_fwd(d, q_all[sub], hk.float(), hv.float(), sub + 1)
+        a, b = bf(M, qh, hd, scale=0.3), (bf(M, qh, hd, scale=0.3) if sub % 2 else None)
+        ck.dread_stage(d, a, b, m_out.to(torch.bfloat16), lse, d1, sub)
+        tk.dread_stage(d, a.float(), None if b is None else b.float(), m_out.to(torch.bfloat16).float(), lse, d2, sub)
+    _close(d1["dm"], d2["dm"], 1e-2, "dm"); _close(d1["dd"], d2["dd"], 2e-2, "dd")
+    for slot in (0, 3, S - 1):
+        k1, v1 = ck.dread_slot_bwd(d, slot, q_all, hk, hv, d1["dm"], d1["lse"], d1["dd"], d1["gq"])
+        k2, v2 = tk.dread_slot_bwd(d, slot, q_all, hk.float(), hv.float(), d2["dm"], d2["lse"], d2["dd"], d2["gq"])
+        _close(k1, k2, 2e-2, "dk"); _close(v1, v2, 2e-2, "dv")
+    _close(d1["gq"], d2["gq"], 2e-2, "gq")
+    assert not ck.fallbacks, ck.fallbacks
