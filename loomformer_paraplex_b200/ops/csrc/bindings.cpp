@@ -156,6 +156,49 @@ void rope_bwd(torch::Tensor dq_attn, torch::Tensor dqkc, torch::Tensor dkc, torc
   TORCH_CHECK(rc == 0, "loom_rope_bwd failed: ", rc);
 }
 
+void slot_pool(bool bwd, torch::Tensor keys, torch::Tensor w9, torch::Tensor pooled, torch::Tensor stats,
+               c10::optional<torch::Tensor> dpooled, c10::optional<torch::Tensor> dkeys, c10::optional<torch::Tensor> dw9_part,
+               int64_t BK, int64_t H) {
+  const c10::cuda::CUDAGuard guard(keys.device());
+  int rc;
+  if (!bwd) rc = loom_slot_pool_fwd(fptr(keys), fptr(w9), fptr(pooled), fptr(stats), (int)BK, (int)H, cur_stream());
+  else rc = loom_slot_pool_bwd(fptr(keys), fptr(w9), fptr(pooled), fptr(stats), fptr(*dpooled), fptr(*dkeys), fptr(*dw9_part),
+                               (int)BK, (int)H, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_slot_pool failed: ", rc);
+}
+
+void cross_attn(bool bwd, torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor allowed_or_dout, torch::Tensor out_or_dq,
+                torch::Tensor prob, c10::optional<torch::Tensor> ds, c10::optional<torch::Tensor> dk,
+                c10::optional<torch::Tensor> dv, int64_t B, int64_t T, int64_t Kn, int64_t N, double scale) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(q.is_contiguous() && k.is_contiguous() && v.is_contiguous() && allowed_or_dout.is_contiguous(), "cross_attn: contiguous");
+  int rc;
+  if (!bwd) rc = loom_cross_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), (const uint8_t*)allowed_or_dout.data_ptr(),
+                                     out_or_dq.data_ptr(), fptr(prob), (int)B, (int)T, (int)Kn, (int)N, (float)scale, cur_stream());
+  else rc = loom_cross_attn_bwd(allowed_or_dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), fptr(prob), fptr(*ds),
+                                out_or_dq.data_ptr(), dk->data_ptr(), dv->data_ptr(), (int)B, (int)T, (int)Kn, (int)N,
+                                (float)scale, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_cross_attn failed: ", rc);
+}
+
+void fixed_rms(bool bwd, c10::optional<torch::Tensor> dy, torch::Tensor x, torch::Tensor out, int64_t rows, int64_t heads,
+               int64_t HD, int64_t ld, double target, double eps) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  int rc = loom_fixed_rms(bwd, dy.has_value() ? dy->data_ptr() : nullptr, x.data_ptr(), out.data_ptr(), rows, (int)heads,
+                          (int)HD, ld, (float)target, (float)eps, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_fixed_rms failed: ", rc);
+}
+
+void rms_norm(bool bwd, c10::optional<torch::Tensor> dy, torch::Tensor x, torch::Tensor w, torch::Tensor out,
+              c10::optional<torch::Tensor> gw_part, int64_t M, int64_t N, double eps) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  int rc;
+  if (!bwd) rc = loom_rms_norm_fwd(x.data_ptr(), fptr(w), out.data_ptr(), (int)M, (int)N, (float)eps, cur_stream());
+  else rc = loom_rms_norm_bwd(dy->data_ptr(), x.data_ptr(), fptr(w), out.data_ptr(), fptr(*gw_part), (int)gw_part->size(0),
+                              (int)M, (int)N, (float)eps, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_rms_norm failed: ", rc);
+}
+
 void dread_stage(torch::Tensor a, c10::optional<torch::Tensor> b, torch::Tensor mo, torch::Tensor dm, torch::Tensor dd,
                  int64_t MQ, int64_t HD) {
   const c10::cuda::CUDAGuard guard(a.device());
@@ -282,6 +325,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rope_store", &rope_store, "RoPE + KV cache write");
   m.def("rope_bwd", &rope_bwd, "inverse RoPE of the q/k/v gradients");
   m.def("dread", &dread, "depth-attention read (forward / backward)");
+  m.def("slot_pool", &slot_pool, "softmax pooling of boundary carriers over neurons (forward / backward)");
+  m.def("cross_attn", &cross_attn, "token rows attending to the boundary keys (forward / backward)");
+  m.def("fixed_rms", &fixed_rms, "x * target / rms(x) over head_dim (forward / backward)");
+  m.def("rms_norm", &rms_norm, "weighted RMSNorm over the model width (forward / backward)");
   m.def("dread_stage", &dread_stage, "store a sublayer's read gradient (bf16) and its <dm, m> row scalars");
   m.def("dread_slot_bwd", &dread_slot_bwd, "gradient of one history slot over every sublayer that read it");
   m.def("add_ln_fwd", &add_ln_fwd, "residual add + LayerNorm");

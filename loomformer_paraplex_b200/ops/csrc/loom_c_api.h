@@ -86,6 +86,20 @@ int loom_rope_store(const void* qkv, const float* cs, const float* sn, void* qkc
 int loom_rope_bwd(const void* dq_attn, const void* dqkc, const float* dkc, const float* dvc, const float* cs,
                   const float* sn, void* dqkv, int M, int Tc, int T, int s_off, int QH, int KVH, int HD, int G,
                   cudaStream_t st);
+// ---- Tria readout and RMS-type norms (readout.cu) ----
+int loom_slot_pool_fwd(const float* keys, const float* w9, float* pooled, float* stats, int BK, int H, cudaStream_t st);
+int loom_slot_pool_bwd(const float* keys, const float* w9, const float* pooled, const float* stats, const float* dpooled,
+                       float* dkeys, float* dw9_part, int BK, int H, cudaStream_t st);
+int loom_cross_attn_fwd(const void* q, const void* k, const void* v, const uint8_t* allowed, void* out, float* prob, int B,
+                        int T, int Kn, int N, float scale, cudaStream_t st);
+int loom_cross_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const float* prob, float* ds, void* dq,
+                        void* dk, void* dv, int B, int T, int Kn, int N, float scale, cudaStream_t st);
+int loom_fixed_rms(int bwd, const void* dy, const void* x, void* out, long long rows, int heads, int HD, long long ld,
+                   float target, float eps, cudaStream_t st);
+int loom_rms_norm_fwd(const void* x, const float* w, void* y, int M, int N, float eps, cudaStream_t st);
+int loom_rms_norm_bwd(const void* dy, const void* x, const float* w, void* dx, float* gw_part, int nblocks, int M, int N,
+                      float eps, cudaStream_t st);
+
 // depth-attention backward organised per history slot (depth_read_bwd.cu)
 int loom_dread_stage(const void* a, const void* b_or_null, const void* m_out, void* dm, float* dd, long long MQ, int HD,
                      cudaStream_t st);

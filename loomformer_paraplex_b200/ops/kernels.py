@@ -455,6 +455,115 @@ class _ElementwiseMixin:
                 "d_alpha_gate": gsc[0] if p_in is not None else None,
                 "d_gate_w": gsc[1:10] if gate_w is not None else None}
 
+    # ------------------------------------------------------------------ readout: slot pool and sparse cross attention
+    def slot_pool_fwd(self, keys, score_w):
+        if not (keys.dtype == torch.float32 and keys.is_contiguous() and keys.dim() == 4):
+            self.fallbacks["slot_pool_fwd"] += 1
+            return super().slot_pool_fwd(keys, score_w)
+        B, Kn, H, _ = keys.shape
+        pooled = torch.empty(B, Kn, 9, dtype=torch.float32, device=keys.device)
+        self._pool_stats = torch.empty(B * Kn, 2, dtype=torch.float32, device=keys.device)
+        self._pool_out = pooled
+        native.ext().slot_pool(False, keys, _f32c(score_w), pooled, self._pool_stats, None, None, None, B * Kn, H)
+        native.count()
+        return pooled
+
+    def slot_pool_bwd(self, dpooled, keys, score_w):
+        st = getattr(self, "_pool_stats", None)
+        if st is None or not (keys.dtype == torch.float32 and keys.is_contiguous()) or st.shape[0] != keys.shape[0] * keys.shape[1]:
+            self.fallbacks["slot_pool_bwd"] += 1
+            return super().slot_pool_bwd(dpooled, keys, score_w)
+        B, Kn, H, _ = keys.shape
+        dkeys = torch.empty_like(keys)
+        part = torch.empty(B * Kn, 9, dtype=torch.float32, device=keys.device)
+        native.ext().slot_pool(True, keys, _f32c(score_w), self._pool_out, st, _f32c(dpooled), dkeys, part, B * Kn, H)
+        native.count()
+        return dkeys, part.sum(0)
+
+    def cross_attn_fwd(self, q, k, v, allowed, scale):
+        B, T, N = q.shape
+        Kn = k.shape[1]
+        if not (q.dtype == torch.bfloat16 and N % 8 == 0 and N <= 1024 and 1 <= Kn <= 1024):
+            self.fallbacks["cross_attn_fwd"] += 1
+            return super().cross_attn_fwd(q, k, v, allowed, scale)
+        out = torch.empty_like(q)
+        self._ca_prob = torch.empty(B, T, Kn, dtype=torch.float32, device=q.device)
+        native.ext().cross_attn(False, q.contiguous(), k.contiguous(), v.contiguous(), allowed.to(torch.uint8).contiguous(),
+                                out, self._ca_prob, None, None, None, B, T, Kn, N, float(scale))
+        native.count()
+        return out
+
+    def cross_attn_bwd(self, dout, q, k, v, allowed, scale):
+        B, T, N = q.shape
+        Kn = k.shape[1]
+        prob = getattr(self, "_ca_prob", None)
+        if prob is None or prob.shape != (B, T, Kn) or q.dtype != torch.bfloat16:
+            self.fallbacks["cross_attn_bwd"] += 1
+            return super().cross_attn_bwd(dout, q, k, v, allowed, scale)
+        ds = torch.empty_like(prob)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        native.ext().cross_attn(True, q.contiguous(), k.contiguous(), v.contiguous(), _bf16c(dout), dq, prob, ds, dk, dv,
+                                B, T, Kn, N, float(scale))
+        native.count(2)
+        return dq, dk, dv
+
+    # ------------------------------------------------------------------ RMS-type norms
+    @staticmethod
+    def _rows_view(x):
+        """[M, heads, HD] bf16 view with contiguous heads -> (rows, heads, HD, row pitch) or None."""
+        if x.dim() != 3 or x.dtype != torch.bfloat16 or x.stride(2) != 1 or x.stride(1) != x.shape[2]:
+            return None
+        if x.shape[2] % 8 or x.shape[2] > 128 or x.data_ptr() % 16 or (x.stride(0) * 2) % 16:
+            return None
+        return x.shape[0] * x.shape[1], x.shape[1], x.shape[2], x.stride(0)
+
+    def fixed_rms_fwd(self, x, target):
+        rv = self._rows_view(x)
+        if rv is None:
+            if x.numel() > 65536:
+                self.fallbacks["fixed_rms_fwd"] += 1
+            return super().fixed_rms_fwd(x, target)
+        rows, heads, hd, ld = rv
+        y = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+        native.ext().fixed_rms(False, None, x, y, rows, heads, hd, ld, float(target), 1e-6)
+        native.count()
+        return y
+
+    def fixed_rms_bwd(self, dy, x, target, eps=1e-6):
+        rv = self._rows_view(x)
+        if rv is None or dy.dtype != torch.bfloat16 or not dy.is_contiguous():
+            if x.numel() > 65536:
+                self.fallbacks["fixed_rms_bwd"] += 1
+            return super().fixed_rms_bwd(dy, x, target, eps)
+        rows, heads, hd, ld = rv
+        dx = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+        native.ext().fixed_rms(True, dy, x, dx, rows, heads, hd, ld, float(target), float(eps))
+        native.count()
+        return dx
+
+    def rms_norm_fwd(self, x, w, eps=1e-6):
+        N = x.shape[-1]
+        if not (x.dtype == torch.bfloat16 and x.is_contiguous() and N % 8 == 0 and N <= 1024):
+            self.fallbacks["rms_norm_fwd"] += 1
+            return super().rms_norm_fwd(x, w, eps)
+        y = torch.empty_like(x)
+        native.ext().rms_norm(False, None, x, _f32c(w), y, None, x.numel() // N, N, float(eps))
+        native.count()
+        return y
+
+    def rms_norm_bwd(self, dy, x, w, gw, eps=1e-6):
+        N = x.shape[-1]
+        if not (x.dtype == torch.bfloat16 and x.is_contiguous() and N % 8 == 0 and N <= 1024):
+            self.fallbacks["rms_norm_bwd"] += 1
+            return super().rms_norm_bwd(dy, x, w, gw, eps)
+        M = x.numel() // N
+        dx = torch.empty_like(x)
+        part = torch.empty(min(296, -(-M // 8)), N, dtype=torch.float32, device=x.device)
+        native.ext().rms_norm(True, _bf16c(dy), x, _f32c(w), dx, part, M, N, float(eps))
+        gw.add_(part.sum(0))
+        native.count()
+        return dx
+
     # ------------------------------------------------------------------ temporal endpoint
     def temporal_fwd(self, depth, B, Tc, H, reset, state, fired, polarm_beta):
         if not (depth.dim() == 3 and depth.shape[0] == 9):          # carriers came from the PyTorch twin

@@ -279,3 +279,59 @@ def test_depth_read_backward_per_slot(hd, qh):
         _close(k1, k2, 2e-2, "dk"); _close(v1, v2, 2e-2, "dv")
     _close(d1["gq"], d2["gq"], 2e-2, "gq")
     assert not ck.fallbacks, ck.fallbacks
+
+
+def test_slot_pool_forward_backward():
+    ck, tk = _sets()
+    torch.manual_seed(11)
+    B, Kn, H = 3, 5, 700
+    keys = torch.randn(B, Kn, H, 9, device="cuda")
+    w9 = torch.randn(9, device="cuda") * 2
+    p1, p2 = ck.slot_pool_fwd(keys, w9), tk.slot_pool_fwd(keys, w9)
+    _close(p1, p2, 1e-4, "pooled")
+    dp = torch.randn(B, Kn, 9, device="cuda")
+    (dk1, dw1), (dk2, dw2) = ck.slot_pool_bwd(dp, keys, w9), tk.slot_pool_bwd(dp, keys, w9)
+    _close(dk1, dk2, 1e-3, "dkeys"); _close(dw1, dw2, 1e-3, "dw9")
+    assert not ck.fallbacks, ck.fallbacks
+
+
+@pytest.mark.parametrize("N,Kn,T", [(768, 16, 256), (256, 3, 100), (1024, 40, 64)])
+def test_sparse_cross_attention(N, Kn, T):
+    ck, tk = _sets()
+    torch.manual_seed(12)
+    B = 2
+    q, k, v = bf(B, T, N, scale=0.3), bf(B, Kn, N, scale=0.3), bf(B, Kn, N)
+    key_pos = torch.sort(torch.randperm(T, device="cuda")[:Kn]).values
+    allowed = key_pos.view(1, 1, Kn) <= torch.arange(T, device="cuda").view(1, T, 1)
+    allowed = allowed & (torch.rand(B, 1, Kn, device="cuda") < 0.8)
+    scale = N ** -0.5
+    o1 = ck.cross_attn_fwd(q, k, v, allowed, scale)
+    o2 = tk.cross_attn_fwd(q.float(), k.float(), v.float(), allowed, scale)
+    _close(o1, o2, 2e-2, "out")
+    none = ~allowed.any(-1)
+    assert bool(none.any()) and float(o1[none].abs().max()) == 0.0        # rows without a key give exactly zero
+    dout = bf(B, T, N, scale=0.2)
+    g1 = ck.cross_attn_bwd(dout, q, k, v, allowed, scale)
+    g2 = tk.cross_attn_bwd(dout.float(), q.float(), k.float(), v.float(), allowed, scale)
+    for a, b_, nm in zip(g1, g2, ("dq", "dk", "dv")):
+        _close(a, b_, 3e-2, nm)
+    assert not ck.fallbacks, ck.fallbacks
+
+
+def test_rms_type_norms():
+    ck, tk = _sets()
+    torch.manual_seed(13)
+    M, qh, hd = 300, 8, 96
+    kv = bf(M, 2 * qh * hd)
+    xv = kv[:, qh * hd:].view(M, qh, hd)                       # strided view, as the depth K/V projection produces it
+    y1, y2 = ck.fixed_rms_fwd(xv, 0.88), tk.fixed_rms_fwd(xv.float(), 0.88)
+    _close(y1, y2, 1e-2, "fixed_rms")
+    dy = bf(M, qh, hd, scale=0.3)
+    _close(ck.fixed_rms_bwd(dy, xv, 0.88), tk.fixed_rms_bwd(dy.float(), xv.float(), 0.88), 2e-2, "fixed_rms_bwd")
+    x, w = bf(M, 768), torch.rand(768, device="cuda") + 0.5
+    _close(ck.rms_norm_fwd(x, w), tk.rms_norm_fwd(x.float(), w), 1e-2, "rms_norm")
+    g = bf(M, 768, scale=0.3)
+    gw1, gw2 = torch.zeros(768, device="cuda"), torch.zeros(768, device="cuda")
+    _close(ck.rms_norm_bwd(g, x, w, gw1), tk.rms_norm_bwd(g.float(), x.float(), w, gw2), 2e-2, "rms_norm_bwd")
+    _close(gw1, gw2, 2e-2, "rms_norm_gw")
+    assert not ck.fallbacks, ck.fallbacks
