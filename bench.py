@@ -88,7 +88,7 @@ def parse():
     ap.add_argument("--micro-batch", type=int, default=16)
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=None, help="debug only: a non-default value makes the number invalid")
-    ap.add_argument("--grad-sync", default="auto", choices=["auto", "collective", "p2p"])
+    ap.add_argument("--grad-sync", default="auto", choices=["auto", "collective", "p2p", "fsdp"])
     return ap.parse_args()
 
 
@@ -131,7 +131,8 @@ def emit(args, impl, ms, clocks, world, extra):
         "clocks": clocks,
         "config": {"model": "113M reference architecture (cfg/nano.yaml dims; BASELINE names it cfg/chk.yaml)",
                    "global_batch": args.micro_batch * world, "seq_len": args.seq_len,
-                   "parallelism": f"dp{world}", "optimizer": args.optimizer,
+                   "parallelism": (f"fsdp{world}" if getattr(args, "grad_sync", "") == "fsdp" else f"dp{world}"),
+                   "grad_sync": getattr(args, "grad_sync", "auto"), "optimizer": args.optimizer,
                    "l2": "per-step working set >> 126 MB L2, no explicit flush",
                    "layers": MODEL_KW["layers"] if args.layers is None else args.layers},
     }

@@ -88,7 +88,7 @@ def main() -> None:
     ap.add_argument("--smoke-test", action="store_true")
     ap.add_argument("--ablation", action="store_true", help="diagnostic: skip imag/phase and use s=1")
     ap.add_argument("--quiet", action="store_true", help="--train only: detach into the background, log to a file")
-    ap.add_argument("--grad-sync", type=str, default="auto", choices=("auto", "collective", "p2p"),
+    ap.add_argument("--grad-sync", type=str, default="auto", choices=("auto", "collective", "p2p", "fsdp"),
                     help="multi-GPU gradient path: NCCL all-reduce or the fused NVLink reduce-scatter+AdamW+all-gather kernel")
     args = ap.parse_args()
 

@@ -26,7 +26,7 @@ LoomOperand operand(const torch::Tensor& t, bool& ok) {
 void gemm(std::vector<torch::Tensor> a_list, std::vector<int64_t> k_len, std::vector<int64_t> a_k0,
           std::vector<int64_t> b_k0, std::vector<torch::Tensor> b_list, bool a_mn, bool b_mn, torch::Tensor c,
           c10::optional<torch::Tensor> bias, int64_t M, int64_t N, int64_t heads, bool accumulate, int64_t bn,
-          bool swap_mn, torch::Tensor status) {
+          bool swap_mn, torch::Tensor status, std::vector<int64_t> b_peer_ptrs, int64_t gather_rank) {
   TORCH_CHECK(a_list.size() >= 1 && a_list.size() <= 16, "1..16 K segments");
   TORCH_CHECK(b_list.size() == 1 || b_list.size() == a_list.size(), "B: one operand, or one per segment");
   TORCH_CHECK(c.is_cuda() && c.stride(-1) == 1, "C must be a CUDA tensor with unit inner stride");
@@ -62,6 +62,11 @@ void gemm(std::vector<torch::Tensor> a_list, std::vector<int64_t> k_len, std::ve
   g.accumulate = accumulate; g.out_fp32 = c.scalar_type() == torch::kFloat32;
   g.bn = (int)bn; g.swap_mn_strides = swap_mn;
   g.status = status.data_ptr<int>();
+  if (b_peer_ptrs.size() > 1) {
+    TORCH_CHECK(b_peer_ptrs.size() <= 8 && b_list.size() == 1, "gather: up to 8 ranks, one B operand");
+    g.gather_world = (int)b_peer_ptrs.size(); g.gather_rank = (int)gather_rank;
+    for (size_t i = 0; i < b_peer_ptrs.size(); ++i) g.b_peer_ptr[i] = reinterpret_cast<const void*>(b_peer_ptrs[i]);
+  }
   int rc = loom_gemm_bf16(&g, cur_stream());
   TORCH_CHECK(rc == 0, "loom_gemm_bf16 failed with code ", rc);
 }
@@ -295,7 +300,9 @@ void attn(bool bwd, torch::Tensor qkc, torch::Tensor kcache, torch::Tensor vcach
 void p2p_grad_step(int64_t W, int64_t rank, int64_t nblk, std::vector<int64_t> grads, std::vector<int64_t> params,
                    std::vector<int64_t> shadow, std::vector<int64_t> sync, int64_t mc_grads, torch::Tensor m,
                    torch::Tensor v, torch::Tensor lr_mult, torch::Tensor wd, torch::Tensor active, torch::Tensor hyper,
-                   torch::Tensor stats, torch::Tensor sumsq, double max_norm, torch::Tensor status) {
+                   torch::Tensor stats, torch::Tensor sumsq, double max_norm, torch::Tensor status,
+                   c10::optional<torch::Tensor> owner_blk, c10::optional<torch::Tensor> slot_blk,
+                   c10::optional<torch::Tensor> replicate_blk) {
   const c10::cuda::CUDAGuard guard(m.device());
   TORCH_CHECK((int64_t)grads.size() == W && (int64_t)params.size() == W && (int64_t)shadow.size() == W &&
               (int64_t)sync.size() == W && W <= 8, "peer pointer lists must have one entry per rank (<= 8)");
@@ -309,6 +316,13 @@ void p2p_grad_step(int64_t W, int64_t rank, int64_t nblk, std::vector<int64_t> g
   a.m = fptr(m); a.v = fptr(v); a.lr_mult = fptr(lr_mult); a.wd_blk = fptr(wd); a.active = fptr(active);
   a.hyper = fptr(hyper); a.stats = fptr(stats); a.sumsq_local = fptr(sumsq); a.max_norm = (float)max_norm;
   a.status = status.data_ptr<int>();
+  if (owner_blk.has_value()) {
+    TORCH_CHECK(slot_blk.has_value() && replicate_blk.has_value(), "owner, slot and replicate maps come together");
+    TORCH_CHECK(owner_blk->scalar_type() == torch::kUInt8 && replicate_blk->scalar_type() == torch::kUInt8 &&
+                slot_blk->scalar_type() == torch::kInt32 && owner_blk->numel() == nblk, "block maps: uint8/int32, one per block");
+    a.owner_blk = owner_blk->data_ptr<uint8_t>(); a.slot_blk = slot_blk->data_ptr<int>();
+    a.replicate_blk = replicate_blk->data_ptr<uint8_t>();
+  }
   int rc = loom_p2p_grad_step(&a, cur_stream());
   TORCH_CHECK(rc == 0, "loom_p2p_grad_step failed: ", rc);
 }

@@ -35,9 +35,19 @@ struct P2P {
   int* sync[MAXW];           // per-rank sync words (symmetric)
   float* mc_grads;           // multicast mapping of the gradient buffers, or null
   int W, rank;
-  long long blk_lo, blk_hi;  // this rank's block range
+  long long blk_lo, blk_hi;  // this rank's block range (used when owner_blk is null)
   long long nblk;
+  // sharded-parameter mode: an explicit owner per 256-element block, a compact slot index into the owner's m / v
+  // arrays, and a flag telling whether the refreshed block is stored to every peer (small replicated tensors) or
+  // only kept by its owner (GEMM weights, which the consuming GEMM of the next step fetches from the owner)
+  const uint8_t* owner_blk;
+  const int* slot_blk;
+  const uint8_t* replicate_blk;
 };
+
+__device__ __forceinline__ bool owns(const P2P& c, long long b) {
+  return c.owner_blk ? (c.owner_blk[b] == c.rank) : (b >= c.blk_lo && b < c.blk_hi);
+}
 
 // sync word layout (int32 words)
 __device__ __forceinline__ int* w_ready(int* s, int src) { return s + src; }
@@ -84,8 +94,11 @@ __global__ void __launch_bounds__(256) rs_reduce_kernel(P2P c, float* __restrict
   const float invW = 1.f / c.W;
   float ss = 0.f;
   float* mine = c.grads[c.rank];
-  const long long lo4 = c.blk_lo * (BLK / 4), hi4 = c.blk_hi * (BLK / 4);
-  for (long long i = lo4 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < hi4; i += (long long)gridDim.x * blockDim.x) {
+  // four 256-element blocks per CUDA block and iteration: 64 lanes of float4 each
+  const long long first = c.owner_blk ? 0 : c.blk_lo, last = c.owner_blk ? c.nblk : c.blk_hi;
+  for (long long b = first + (long long)blockIdx.x * 4 + (threadIdx.x >> 6); b < last; b += (long long)gridDim.x * 4) {
+    if (!owns(c, b)) continue;
+    const long long i = b * (BLK / 4) + (threadIdx.x & 63);
     float4 a;
     if (c.mc_grads) {
       asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
@@ -150,22 +163,30 @@ __global__ void __launch_bounds__(256) update_allgather_kernel(P2P c, float* __r
   const float lr0 = hyper[0], b1 = hyper[1], b2 = hyper[2], eps = hyper[3], bc1 = hyper[4], bc2 = hyper[5];
   const float* g = c.grads[c.rank];
   float* pl = c.params[c.rank];
-  for (long long b = c.blk_lo + blockIdx.x; b < c.blk_hi; b += gridDim.x) {
+  const long long first = c.owner_blk ? 0 : c.blk_lo, last = c.owner_blk ? c.nblk : c.blk_hi;
+  for (long long b = first + blockIdx.x; b < last; b += gridDim.x) {
+    if (!owns(c, b)) continue;
     const long long i = b * BLK + threadIdx.x;
+    const long long mi = (c.slot_blk ? (long long)c.slot_blk[b] : b) * BLK + threadIdx.x;   // moments may be compact
     float pp = pl[i];
     if (fin && active[b] != 0.f) {
       const float lr = lr0 * lr_mult[b];
       const float gg = g[i] * clip;
-      const float mm = m[i] + (1.f - b1) * (gg - m[i]);
-      const float vv = v[i] + (1.f - b2) * (gg * gg - v[i]);
+      const float mm = m[mi] + (1.f - b1) * (gg - m[mi]);
+      const float vv = v[mi] + (1.f - b2) * (gg * gg - v[mi]);
       pp = pp * (1.f - lr * wd_blk[b]) - lr * (mm / bc1) / (sqrtf(vv / bc2) + eps);
-      m[i] = mm; v[i] = vv;
+      m[mi] = mm; v[mi] = vv;
     }
     const __nv_bfloat16 pb = __float2bfloat16(pp);
-    for (int p = 0; p < c.W; ++p) {                 // all-gather by direct stores into every peer
-      const int q = (c.rank + p) % c.W;
-      c.params[q][i] = pp;
-      c.shadow[q][i] = pb;
+    if (c.replicate_blk == nullptr || c.replicate_blk[b]) {
+      for (int p = 0; p < c.W; ++p) {               // all-gather by direct stores into every peer
+        const int q = (c.rank + p) % c.W;
+        c.params[q][i] = pp;
+        c.shadow[q][i] = pb;
+      }
+    } else {                                        // sharded weight: the owner keeps it; readers fetch it on use
+      pl[i] = pp;
+      c.shadow[c.rank][i] = pb;
     }
   }
   __threadfence_system();
@@ -198,6 +219,7 @@ extern "C" int loom_p2p_grad_step(const LoomP2P* a, cudaStream_t stream) {
     c.shadow[p] = reinterpret_cast<__nv_bfloat16*>(a->shadow[p]); c.sync[p] = a->sync[p];
   }
   c.mc_grads = a->mc_grads; c.W = a->W; c.rank = a->rank; c.nblk = a->nblk;
+  c.owner_blk = a->owner_blk; c.slot_blk = a->slot_blk; c.replicate_blk = a->replicate_blk;
   const long long per = (a->nblk + a->W - 1) / a->W;
   c.blk_lo = per * a->rank < a->nblk ? per * a->rank : a->nblk;
   c.blk_hi = per * (a->rank + 1) < a->nblk ? per * (a->rank + 1) : a->nblk;

@@ -60,6 +60,10 @@ struct Params {
   int out_fp32;
   int a_lbo, a_sbo, b_lbo, b_sbo;
   int* status;
+  // sharded-weight gather (all-gather fused into the consuming GEMM): rank r owns the 64-row blocks
+  // [r * gather_per, (r+1) * gather_per) of B; b_peer[r] maps rank r's copy of the whole matrix (box: 64 rows)
+  int gather_world, gather_rank, gather_per;
+  CUtensorMap b_peer[8];
 };
 
 template <int BN>
@@ -72,7 +76,12 @@ struct Cfg {
   static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : 2 * BN;
 };
 
-template <int BN, bool A_MN, bool B_MN>
+// GATHER (K-major operands only): every 64-row block of B is fetched from the rank that owns it -- a TMA load from
+// that peer's memory, no multicast -- while the math of earlier tiles runs; the CTAs of the first row of output
+// tiles also deposit each remote block in this rank's own copy of B, so after this launch the local copy is
+// complete and every later kernel of the step reads it locally.  The parameter all-gather of sharded data
+// parallelism is thereby part of the first GEMM that needs the weight instead of a separate collective.
+template <int BN, bool A_MN, bool B_MN, bool GATHER>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_kernel(const __grid_constant__ Params p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -135,7 +144,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_kernel(const __grid_const
             } else {
               tma_load_3d(sa, &sg.a, &full[st], sg.a_k0 + k, m0, ag);
             }
-            if (B_MN) {
+            if (GATHER) {
+              bool remote[BN / 64];
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) {
+                const int row0 = n0 + 64 * j;
+                int owner = (row0 >> 6) / p.gather_per;
+                owner = owner < p.gather_world ? owner : p.gather_world - 1;
+                remote[j] = owner != p.gather_rank && row0 < p.n_per_head;
+                tma_load_3d(sb + j * 8192, &p.b_peer[owner], &full[st], sg.b_k0 + k, row0, 0);
+              }
+              if (tm == 0) {
+                // deposit the remote blocks locally once they have landed (this CTA alone does it for its columns)
+                if (!mbar_wait(&full[st], ph, status, 105)) { ok = false; break; }
+                bool any = false;
+#pragma unroll
+                for (int j = 0; j < BN / 64; ++j) {
+                  if (remote[j]) { tma_store_3d(&p.b_peer[p.gather_rank], sb + j * 8192, sg.b_k0 + k, n0 + 64 * j, 0); any = true; }
+                }
+                if (any) { tma_store_commit(); tma_store_wait_read(); }
+              }
+            } else if (B_MN) {
 #pragma unroll
               for (int j = 0; j < BN / 64; ++j)
                 tma_load_3d(sb + j * 8192, bmap, &full[st], n0 + 64 * j, sg.b_k0 + k, bg);
@@ -144,6 +173,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_kernel(const __grid_const
             }
           }
         }
+      if (GATHER) tma_store_wait_all();
       }
     }
   } else if (warp == 1) {
@@ -275,18 +305,18 @@ bool fill_map(CUtensorMap* map, const LoomOperand& o, bool mn_major, int box_mn)
   return r == CUDA_SUCCESS;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool GATHER = false>
 int launch(const Params& p, int sms, cudaStream_t stream) {
   using C = Cfg<BN>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, A_MN, B_MN, GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.n_per_head + BN - 1) / BN) * p.heads;
   const int grid = tiles < sms ? tiles : sms;
-  gemm_kernel<BN, A_MN, B_MN><<<grid, NUM_THREADS, C::SMEM, stream>>>(p);
+  gemm_kernel<BN, A_MN, B_MN, GATHER><<<grid, NUM_THREADS, C::SMEM, stream>>>(p);
   return (int)cudaGetLastError();
 }
 
@@ -329,6 +359,23 @@ extern "C" int loom_gemm_bf16(const LoomGemm* g, cudaStream_t stream) {
   }
   static int sms = 0;
   if (sms == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+  if (g->gather_world > 1) {
+    // weight rows fetched from their owners: plain (unbatched, single-segment, K-major) linear layers only
+    if (a_mn || b_mn || g->nseg != 1 || p.heads != 1 || p.b_per_seg || g->gather_world > 8) return -5;
+    p.gather_world = g->gather_world; p.gather_rank = g->gather_rank;
+    const int nb64 = (g->N + 63) / 64;
+    p.gather_per = (nb64 + g->gather_world - 1) / g->gather_world;
+    for (int r = 0; r < g->gather_world; ++r) {
+      LoomOperand o = g->b;
+      o.ptr = g->b_peer_ptr[r];
+      if (!fill_map(&p.b_peer[r], o, false, 64)) return -6;
+    }
+    switch (g->bn) {
+      case 64: return launch<64, false, false, true>(p, sms, stream);
+      case 128: return launch<128, false, false, true>(p, sms, stream);
+      default: return launch<256, false, false, true>(p, sms, stream);
+    }
+  }
   switch (g->bn) {
     case 64: return dispatch_major<64>(p, a_mn, b_mn, sms, stream);
     case 128: return dispatch_major<128>(p, a_mn, b_mn, sms, stream);

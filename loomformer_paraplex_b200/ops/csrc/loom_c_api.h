@@ -34,6 +34,11 @@ typedef struct {
   int bn;                // tile width: 64, 128 or 256
   int swap_mn_strides;   // debugging aid: exchange the two descriptor strides of MN-major operands
   int* status;           // device word; non-zero after a bounded wait gave up
+  // sharded-weight gather: when gather_world > 1, B's 64-row blocks are owned by ranks in contiguous runs of
+  // ceil(ceil(N/64)/gather_world) blocks; b_peer_ptr[r] is rank r's copy of B (same layout as `b`, peer-mapped
+  // memory), and `b` itself is this rank's copy, which the launch completes as a side effect.
+  int gather_world, gather_rank;
+  const void* b_peer_ptr[8];
 } LoomGemm;
 
 int loom_gemm_bf16(const LoomGemm* g, cudaStream_t stream);
@@ -149,6 +154,9 @@ typedef struct {
   float* sumsq_local;             // one float, zero before the first call
   float max_norm;
   int* status;
+  // optional sharded-parameter mode (all three null: contiguous block ranges, full-size moments, every block
+  // stored to every peer): owner rank per block, compact index of the block in the owner's m / v, replicate flag
+  const uint8_t* owner_blk; const int* slot_blk; const uint8_t* replicate_blk;
 } LoomP2P;
 int loom_p2p_grad_step(const LoomP2P* a, cudaStream_t stream);
 

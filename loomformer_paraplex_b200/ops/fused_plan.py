@@ -47,12 +47,27 @@ class FusedPlan:
         self.adt = compute_dtype or (torch.bfloat16 if dev.type == "cuda" else torch.float32)
         self._wcache: Dict[int, torch.Tensor] = {}
         self._consts: Dict[tuple, torch.Tensor] = {}
+        self._fetched: set = set()
         self.anchor_sync = None        # optional callable(sumsq [L], count) for cross-rank anchor statistics
 
     # ------------------------------------------------------------------ parameter access
     def bind(self, flat) -> None:
         self.flat = flat
         self._wcache.clear()
+
+    # sharded weights: ``gather_spec(param)`` (set by the engine in sharded data-parallel mode) says where the owners'
+    # copies live; the first linear layer of a run that consumes such a weight fetches it inside its GEMM
+    gather_spec = None
+
+    def lin(self, x, p, bias=None):
+        """``x @ p^T (+ bias)`` with ``p`` a parameter (not a weight tensor), fetching sharded weights on first use."""
+        spec = None
+        if self.gather_spec is not None and id(p) not in self._fetched:
+            self._fetched.add(id(p))
+            spec = self.gather_spec(p)
+        if spec is None:
+            return self.K.linear(x, self.w(p), bias)
+        return self.K.linear(x, self.w(p), bias, gather=spec)
 
     def w(self, p: torch.Tensor) -> torch.Tensor:
         """Weight in the compute dtype (bf16 shadow on a GPU, the fp32 parameter itself on a CPU)."""
@@ -108,6 +123,7 @@ class FusedPlan:
         m, d, K = self.model, self.d, self.K
         B, T = idx.shape
         dev = idx.device
+        self._fetched.clear()
         if position_ids is None:
             position_ids = torch.arange(T, device=dev).view(1, T).expand(B, T)
         chunked = d.tria and d.tria_temporal and not m.ablation
@@ -168,7 +184,7 @@ class FusedPlan:
                                        self._const(tuple(key_pos), dev), seg)
             h = ro["h_out"]
         hn = K.rms_norm_fwd(h, m.ln_final.weight) if m.ln_final is not None else h
-        logits = K.linear(hn.reshape(B * T, d.n), self.w(m.head.weight)).view(B, T, d.vocab)
+        logits = self.lin(hn.reshape(B * T, d.n), m.head.weight).view(B, T, d.vocab)
         if return_state:
             state = {"kc": kc, "vc": vc, "traces": traces, "temporal": temporal, "n_keys": len(keys),
                      "pending": fire[:, T - 1] if (chunked and fire is not None) else None}
@@ -231,7 +247,7 @@ class FusedPlan:
         """K/V projection of a residual-stream state into history slot ``slot``."""
         m, d, K = self.model, self.d, self.K
         M = x2d.shape[0]
-        kv = K.linear(x2d, self.w(m.depth_attn.kv_weight))
+        kv = self.lin(x2d, m.depth_attn.kv_weight)
         k, v = kv[:, :d.n].view(M, d.qh, d.hd), kv[:, d.n:].view(M, d.qh, d.hd)
         if d.depth_qkv_rms:
             tape_layer[key + "_kv_raw"] = kv
@@ -270,6 +286,10 @@ class FusedPlan:
         da = self.model.depth_attn
         return self.w(da.w_o_weight)[sub] if da.w_o is None else self.w(da.w_o.weight)
 
+    def _readout_lin(self, x, sub):
+        da = self.model.depth_attn
+        return self.K.linear(x, self.w(da.w_o_weight)[sub]) if da.w_o is None else self.lin(x, da.w_o.weight)
+
     def _readout_g(self, sub):
         da = self.model.depth_attn
         return self.g(da.w_o_weight)[sub] if da.w_o is None else self.g(da.w_o.weight)
@@ -297,17 +317,17 @@ class FusedPlan:
             last = bi == L - 1
             t: Dict[str, object] = {"h_in": h}
             # --- attention
-            qkv = K.linear(h, self.w(blk.attn.qkv_weight)).view(B, Tc, -1)
+            qkv = self.lin(h, blk.attn.qkv_weight).view(B, Tc, -1)
             qkc = torch.empty(M, 3, d.qh, d.hd, dtype=self.adt, device=dev)     # sectors: rotated Q, A@K, A@V
             K.rope_store(d, qkv, cos, sin, qkc, kc[bi], vc[bi], s)
             t["lse"] = K.attn_fwd(d, qkc, kc[bi], vc[bi], s, e, seg)
             t["qkc"] = qkc
-            a = K.linear(qkc[:, 2].reshape(M, N), self.w(blk.attn.o.weight))
+            a = self.lin(qkc[:, 2].reshape(M, N), blk.attn.o.weight)
             # --- depth read 2bi, residual, LN
             sub = 2 * bi
             m1, t["lse1"] = K.dread_fwd(d, self._depth_query(sub), hist_k, hist_v, sub + 1)
             m1 = m1.reshape(M, N)
-            s1 = K.linear(m1, self._readout_w(sub))
+            s1 = self._readout_lin(m1, sub)
             u, t["x1"], t["mean1"], t["rstd1"] = K.add_ln_fwd(s1, a, blk.ln_attn.weight.data, blk.ln_attn.bias.data,
                                                               d.branch_rms_cap)
             t["m1"], t["u"] = m1, u
@@ -316,11 +336,11 @@ class FusedPlan:
             self._project_state(u, sub + 1, hist_k, hist_v, t, "u")
             m2, t["lse2"] = K.dread_fwd(d, self._depth_query(sub + 1), hist_k, hist_v, sub + 2)
             t["m2"] = m2
-            s2 = K.linear(m2.reshape(M, N), self._readout_w(sub + 1))
+            s2 = self._readout_lin(m2.reshape(M, N), sub + 1)
             # --- Paraplex FFN
             ffn = blk.ffn
-            x_real = K.linear(u, self.w(ffn.w1_real.weight))
-            gate_lin = K.linear(u, self.w(ffn.gate_proj.weight), ffn.gate_proj.bias.data) if ffn.gate_proj is not None else None
+            x_real = self.lin(u, ffn.w1_real.weight)
+            gate_lin = self.lin(u, ffn.gate_proj.weight, ffn.gate_proj.bias.data) if ffn.gate_proj is not None else None
             beta_lin = K.imag_fwd(d, qkc, u, m2, self.w(ffn.w1_imag))
             alpha_gate = ffn.identity_gate.alpha().detach() if (ffn.identity_gate is not None and p_in is not None) else None
             gate_w = ffn.gate_selector.weights().detach() if (use_tria and not last) else None
@@ -347,7 +367,7 @@ class FusedPlan:
             t["o"] = o
             trace_out.append(out["trace_out"])
             c_prev, p_in = out["c"], out["p_out"]
-            f = K.linear(o, self.w(ffn.w2.weight), ffn.w2.bias.data)
+            f = self.lin(o, ffn.w2.weight, ffn.w2.bias.data)
             h, t["x2"], t["mean2"], t["rstd2"] = K.add_ln_fwd(s2, f, blk.ln_ffn.weight.data, blk.ln_ffn.bias.data,
                                                               d.branch_rms_cap)
             if d.branch_rms_cap is not None:
@@ -469,9 +489,9 @@ class FusedPlan:
         pooled = K.slot_pool_fwd(doc_keys, score_w)                                   # [B,Kn,9] fp32
         z = torch.addmm(agg.reader.proj.bias.data, pooled.view(B * Kn, 9), agg.reader.proj.weight.data.t())
         a = torch.addmm(agg.up.bias.data, z, agg.up.weight.data.t()).to(self.adt)     # [B*Kn,N]
-        q = K.linear(h.reshape(B * T, N), self.w(fca.w_qk.weight)).view(B, T, N)
-        k = K.linear(a, self.w(fca.w_qk.weight)).view(B, Kn, N)
-        v = K.linear(a, self.w(fca.w_v.weight)).view(B, Kn, N)
+        q = self.lin(h.reshape(B * T, N), fca.w_qk.weight).view(B, T, N)
+        k = self.lin(a, fca.w_qk.weight).view(B, Kn, N)
+        v = self.lin(a, fca.w_v.weight).view(B, Kn, N)
         allowed = key_pos.view(1, 1, Kn) <= torch.arange(T, device=h.device).view(1, T, 1)
         allowed = allowed & valid[:, None, :]
         if seg is not None:

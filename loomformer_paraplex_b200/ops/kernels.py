@@ -49,12 +49,13 @@ def _pick_bn(M: int, N: int, heads: int = 1) -> int:
 def gemm(a_list: List[torch.Tensor], k_len: List[int], b, c: torch.Tensor, *, M: int, N: int,
          heads: int = 1, a_mn: bool = False, b_mn: bool = False, a_k0: Optional[List[int]] = None,
          b_k0: Optional[List[int]] = None, bias: Optional[torch.Tensor] = None, accumulate: bool = False,
-         bn: Optional[int] = None, swap_mn: bool = False) -> None:
+         bn: Optional[int] = None, swap_mn: bool = False, peer_ptrs: Optional[List[int]] = None,
+         gather_rank: int = 0) -> None:
     ext = native.ext()
     n = len(a_list)
     ext.gemm(a_list, k_len, a_k0 or [0] * n, b_k0 or [0] * n, b if isinstance(b, (list, tuple)) else [b], a_mn, b_mn,
              c, bias, M, N, heads, accumulate,
-             bn or _pick_bn(M, N, heads), swap_mn, status_word(c.device))
+             bn or _pick_bn(M, N, heads), swap_mn, status_word(c.device), peer_ptrs or [], gather_rank)
     native.count()
 
 
@@ -130,15 +131,22 @@ class CudaKernels(TorchKernels):
             self._flush_one(key)
 
     # ------------------------------------------------------------------ GEMMs
-    def linear(self, x, w, bias=None, out_dtype=None):
+    def linear(self, x, w, bias=None, out_dtype=None, gather=None):
+        """``gather=(peer_ptrs, rank)``: ``w`` is this rank's copy of a row-sharded weight; the launch fetches every
+        64-row block from the rank that owns it and completes the local copy on the way."""
         M, Kd = x.shape
         N = w.shape[0]
         if not (_tma_ok(x) and _tma_ok(w)) or (out_dtype not in (None, torch.bfloat16, torch.float32)):
+            if gather is not None:
+                raise RuntimeError("a sharded weight needs the TMA path (16-byte aligned bf16 rows)")
             self.fallbacks["linear"] += 1
             return super().linear(x, w, bias, out_dtype)
         c = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=x.device)
         b32 = None if bias is None else bias.float().contiguous()
-        gemm([x], [Kd], w, c, M=M, N=N, bias=b32)
+        if gather is not None:
+            gemm([x], [Kd], w, c, M=M, N=N, bias=b32, peer_ptrs=list(gather[0]), gather_rank=int(gather[1]))
+        else:
+            gemm([x], [Kd], w, c, M=M, N=N, bias=b32)
         return c
 
     def linear_dgrad(self, dy, w):

@@ -256,6 +256,9 @@ class FlatOptimizer:
         ATOM: ``step/m/v/gprev_blk/pnode_blk/trust_blk`` + ``atom_meta``), grouped by
         ``(weight_decay, lr_mult)`` in model parameter order like the reference trainer."""
         state, groups, idx = {}, [], 0
+        shard = getattr(self, "shard", None)        # sharded mode keeps compact moments: rebuild the full arrays
+        full_m = self.m if shard is None else shard.expand(self.m)
+        full_v = self.v if shard is None else shard.expand(self.v)
         for (wd, mult), segs in self._groups():
             ids = []
             for s in segs:
@@ -263,11 +266,11 @@ class FlatOptimizer:
                 bs = slice(s.offset // BLOCK, (s.offset + s.padded) // BLOCK)
                 if self.kind == "adamw":
                     st = {"step": torch.tensor(float(self.step_count)),
-                          "exp_avg": self.m[sl].view_as(s.param).clone(),
-                          "exp_avg_sq": self.v[sl].view_as(s.param).clone()}
+                          "exp_avg": full_m[sl].view_as(s.param).clone(),
+                          "exp_avg_sq": full_v[sl].view_as(s.param).clone()}
                 else:
                     st = {"step": torch.tensor(self.step_count, dtype=torch.int64),
-                          "m": self.m[sl].view_as(s.param).clone(), "v": self.v[sl].view_as(s.param).clone(),
+                          "m": full_m[sl].view_as(s.param).clone(), "v": full_v[sl].view_as(s.param).clone(),
                           "gprev_blk": self.gprev_blk[bs].clone(), "pnode_blk": self.pnode_blk[bs].clone(),
                           "trust_blk": self.trust_blk[bs].clone()}
                 if self.step_count > 0:
@@ -290,6 +293,10 @@ class FlatOptimizer:
             raise ValueError("optimizer checkpoint is incompatible with the active trainable parameter groups; "
                              "keep train_lr/freeze settings unchanged or start without --resume")
         steps = []
+        shard = getattr(self, "shard", None)
+        if shard is not None:                       # load into full arrays, then keep this rank's blocks
+            self.m = torch.zeros(self.flat.total, dtype=torch.float32, device=self.flat.device)
+            self.v = torch.zeros_like(self.m)
         for idx, s in enumerate(order):
             st = sd["state"].get(idx, sd["state"].get(str(idx)))
             if st is None:
@@ -310,6 +317,8 @@ class FlatOptimizer:
             if "step" in st:
                 steps.append(int(float(st["step"])))
         self.step_count = max(steps) if steps else 0
+        if shard is not None:
+            self.m, self.v = shard.compact(self.m), shard.compact(self.v)
         meta = sd.get("atom_meta")
         if meta is not None and self.kind == "atom":
             self.step_count = int(meta.get("step", self.step_count))

@@ -32,15 +32,34 @@ class GradSync:
         self.anchor_mode = anchor_mode
         self.symm = symm
         self._anchors: Optional[List[torch.Tensor]] = None
-        if self.backend == "p2p":
+        self.shard = None
+        if self.backend in ("p2p", "fsdp"):
             if symm is None or flat.shadow is None:
-                raise RuntimeError("grad_sync='p2p' needs symmetric flat buffers on CUDA")
+                raise RuntimeError(f"grad_sync={self.backend!r} needs symmetric flat buffers on CUDA")
             dev = flat.device
             self.sync_words = symm.alloc("sync", 64, torch.int32, dev)
             self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
             self.use_multimem = False
         if self.world > 1:
             self.broadcast_parameters()
+        if self.backend == "fsdp":
+            from .fsdp import ShardPlan
+            tied = getattr(model, "head", None) is not None and getattr(model.head, "weight", None) is model.emb.weight
+            self.shard = ShardPlan(flat, model, self.world, dist.get_rank(), tied_head=tied)
+
+    def attach_optimizer(self, opt) -> None:
+        """Sharded mode: the optimizer keeps Adam moments only for the blocks this rank owns."""
+        if self.shard is not None and getattr(opt, "shard", None) is None:
+            opt.m, opt.v = self.shard.compact(opt.m), self.shard.compact(opt.v)
+            opt.shard = self.shard
+
+    def gather_spec(self, p):
+        """``(peer pointers of the weight's bf16 copy, rank)`` when ``p`` is a sharded weight that the next consuming
+        GEMM has to fetch from its owners, else ``None``."""
+        if self.shard is None or id(p) not in self.shard.gathered:
+            return None
+        seg = next(s for s in self.flat.segments if s.param is p)
+        return [base + seg.offset * 2 for base in self.symm.peer_ptrs("shadow")], self.shard.rank
 
     def fused_step(self, opt) -> None:
         """Reduce-scatter + clip + AdamW on the own shard + all-gather in three launches over peer memory."""
@@ -51,10 +70,12 @@ class GradSync:
         opt.step_count += 1
         hyper = kernels.upload_hyper(opt)
         mc = s.multicast_ptr("grads") if self.use_multimem else 0
+        sh = self.shard
         native.ext().p2p_grad_step(self.world, dist.get_rank(), f.nblk, s.peer_ptrs("grads"), s.peer_ptrs("params"),
                                    s.peer_ptrs("shadow"), s.peer_ptrs("sync"), mc, opt.m, opt.v, opt.lr_mult_blk,
                                    opt.wd_blk, opt.active_blk, hyper, opt.stats, self.sumsq, opt.grad_clip,
-                                   kernels.status_word(f.device))
+                                   kernels.status_word(f.device), None if sh is None else sh.owner_blk,
+                                   None if sh is None else sh.slot_blk, None if sh is None else sh.replicate_blk)
         native.count(3)
 
     def broadcast_parameters(self) -> None:

@@ -63,7 +63,7 @@ class TrainEngine:
         lr_mults = train_lr_overrides(model, cfg) if train_lr else {}
         self.symm = None
         alloc = None
-        if grad_sync == "p2p" and pdist.initialized() and device.type == "cuda":
+        if grad_sync in ("p2p", "fsdp") and pdist.initialized() and device.type == "cuda":
             from ..parallel.symm import SymmetricBuffers
             self.symm = SymmetricBuffers()
             alloc = self.symm.alloc
@@ -73,9 +73,12 @@ class TrainEngine:
         self.opt = FlatOptimizer(self.flat, self.opt_name, lr=cfg.lr, weight_decay=cfg.weight_decay,
                                  grad_clip=cfg.grad_clip, no_decay=no_decay, lr_mults=lr_mults)
         self.sync = GradSync(self.flat, model, backend=grad_sync, anchor_mode=anchor_mode, symm=self.symm)
+        self.sync.attach_optimizer(self.opt)
         self.plan = model._opset(model.emb.weight) if not model.ablation else None   # fused plan on CUDA
         if self.plan is not None:
             self.plan.bind(self.flat)
+            if self.sync.shard is not None:
+                self.plan.gather_spec = self.sync.gather_spec
         # Whole forward+backward of a micro-batch as one CUDA graph: the fused plan issues several thousand launches per
         # step and the host cannot enqueue them as fast as a B200 retires them.  On by default on CUDA, off with
         # LOOM_CUDA_GRAPH=0 or ``cfg.graph: false`` given explicitly through ``cuda_graph``.
@@ -187,7 +190,7 @@ class TrainEngine:
                 self.last_fire_count += fm.sum()
             total = loss.detach() if total is None else total + loss.detach()
         self.opt.set_lr(lr_at(self.cfg, self.step_idx))
-        if self.sync.backend == "p2p":
+        if self.sync.backend in ("p2p", "fsdp"):
             self.sync.fused_step(self.opt)
         else:
             self.sync.all_reduce_grads()
@@ -195,6 +198,25 @@ class TrainEngine:
         self.sync.sync_anchors()
         self.step_idx += 1
         return total / float(len(micro))
+
+    def complete_master(self) -> None:
+        """Sharded mode: make this rank's fp32 parameters complete again (collective; call on every rank before a
+        checkpoint, an export, or anything else that reads ``model.state_dict()``)."""
+        if self.sync.shard is not None:
+            self.sync.shard.gather_master()
+
+    def checkpoint_view(self):
+        """Object whose ``state_dict()`` is the optimizer state to save.  In sharded mode this completes the fp32
+        master parameters and assembles the full moments (collectives: call on every rank)."""
+        if self.sync.shard is None:
+            return self.opt
+        self.complete_master()
+        sd = self.opt.state_dict()
+
+        class _Frozen:
+            def state_dict(self_inner):
+                return sd
+        return _Frozen()
 
     def check_finite(self, loss: torch.Tensor) -> None:
         """Host-side guard (one sync): raise if the loss or the last gradient norm was not finite."""

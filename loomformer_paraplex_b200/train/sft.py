@@ -93,8 +93,9 @@ def train_sft(cfg: Config, train_path: str, val_path: Optional[str], init_checkp
         ckpt.restore_optimizer(engine.opt, blob, engine.opt_name, resume)
 
     def save(path: Optional[str], at: int) -> None:
+        opt_obj = engine.checkpoint_view()          # collective in sharded mode: every rank takes part
         if pdist.is_main():
-            ckpt.save_checkpoint(path or ckpt_out, cfg, model, engine.opt, engine.opt_name, at, 0)
+            ckpt.save_checkpoint(path or ckpt_out, cfg, model, opt_obj, engine.opt_name, at, 0)
             print(f"[loomsft] saved -> {path or ckpt_out}")
 
     def runpoint(at: int) -> None:

@@ -140,14 +140,17 @@ def train(cfg: Config, dataset: str, device: torch.device, ckpt_out: Optional[st
         ckpt.restore_optimizer(engine.opt, blob, opt_name, resume)
 
     def save(path: Optional[str] = None, step_override: Optional[int] = None) -> None:
-        if ckpt_out and pdist.is_main():
+        if not ckpt_out:
+            return
+        opt_obj = engine.checkpoint_view()          # collective in sharded mode: every rank takes part
+        if pdist.is_main():
             p = path or ckpt_out
-            ckpt.save_checkpoint(p, cfg, model, engine.opt, opt_name, step if step_override is None else step_override,
+            ckpt.save_checkpoint(p, cfg, model, opt_obj, opt_name, step if step_override is None else step_override,
                                  tokens_seen, ablation)
             print(f"[train] saved {tag} -> {p}")
 
     def save_runpoint(at: int) -> None:
-        if not (ckpt_out and pdist.is_main()):
+        if not ckpt_out:
             return
         root, ext = os.path.splitext(ckpt_out)
         ext = ext or ".pt"
@@ -156,7 +159,7 @@ def train(cfg: Config, dataset: str, device: torch.device, ckpt_out: Optional[st
             p = os.path.join(cfg.runpoints_path, f"{os.path.basename(root)}.runpoint_step{at}{ext}")
         else:
             p = f"{root}.runpoint_step{at}{ext}"
-        print(f"\n[runpoint] step {at}/{cfg.steps} -- saving, training continues.", flush=True)
+        rank0_print(f"\n[runpoint] step {at}/{cfg.steps} -- saving, training continues.", flush=True)
         save(p, at)
 
     if cfg.save_initial_checkpoint and ckpt_out and pdist.is_main():

@@ -70,7 +70,7 @@ def main() -> None:
     ap.add_argument("--resume-step", type=int, default=None)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--device", type=str, default=None)
-    ap.add_argument("--grad-sync", type=str, default="collective", choices=("collective", "p2p"))
+    ap.add_argument("--grad-sync", type=str, default="collective", choices=("collective", "p2p", "fsdp"))
     ap.add_argument("--smoke-test", action="store_true")
     args = ap.parse_args()
     if args.smoke_test:

@@ -39,3 +39,25 @@ def test_fused_p2p_step_matches_nccl_baseline(tmp_path):
     assert float(diff.mean()) < 2e-5, float(diff.mean())
     assert float((diff > 1e-3).float().mean()) < 1e-3
     assert abs(a["losses"][-1] - b["losses"][-1]) < 5e-2
+
+
+@pytest.mark.gpu
+def test_gathering_gemm_reads_owner_rows_and_completes_local_copy(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = _launch("gather", str(tmp_path / "gather.pt"), "cuda", 2, 29614)
+    assert res["all_ranks_ok"], res["cases"]
+
+
+@pytest.mark.gpu
+def test_sharded_training_matches_nccl_baseline(tmp_path):
+    """Sharded ownership + weights fetched inside the consuming GEMM give the same training run as all-reduce DDP."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    a = _launch("collective", str(tmp_path / "nccl.pt"), "cuda", 2, 29615)
+    b = _launch("fsdp", str(tmp_path / "fsdp.pt"), "cuda", 2, 29616)
+    assert a["same"] and b["same"]
+    diff = (a["params"] - b["params"]).abs()
+    assert float(diff.mean()) < 2e-5, float(diff.mean())
+    assert float((diff > 1e-3).float().mean()) < 1e-3
+    assert abs(a["losses"][-1] - b["losses"][-1]) < 5e-2
