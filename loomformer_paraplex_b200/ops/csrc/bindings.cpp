@@ -26,7 +26,9 @@ LoomOperand operand(const torch::Tensor& t, bool& ok) {
 void gemm(std::vector<torch::Tensor> a_list, std::vector<int64_t> k_len, std::vector<int64_t> a_k0,
           std::vector<int64_t> b_k0, std::vector<torch::Tensor> b_list, bool a_mn, bool b_mn, torch::Tensor c,
           c10::optional<torch::Tensor> bias, int64_t M, int64_t N, int64_t heads, bool accumulate, int64_t bn,
-          bool swap_mn, torch::Tensor status, std::vector<int64_t> b_peer_ptrs, int64_t gather_rank) {
+          bool swap_mn, torch::Tensor status, std::vector<int64_t> b_peer_ptrs, int64_t gather_rank,
+          std::vector<int64_t> a_peer_ptrs, int64_t a_rows_per_rank, std::vector<int64_t> rs_out_ptrs,
+          int64_t rs_rows_per_rank, int64_t rs_rank) {
   TORCH_CHECK(a_list.size() >= 1 && a_list.size() <= 16, "1..16 K segments");
   TORCH_CHECK(b_list.size() == 1 || b_list.size() == a_list.size(), "B: one operand, or one per segment");
   TORCH_CHECK(c.is_cuda() && c.stride(-1) == 1, "C must be a CUDA tensor with unit inner stride");
@@ -66,6 +68,16 @@ void gemm(std::vector<torch::Tensor> a_list, std::vector<int64_t> k_len, std::ve
     TORCH_CHECK(b_peer_ptrs.size() <= 8 && b_list.size() == 1, "gather: up to 8 ranks, one B operand");
     g.gather_world = (int)b_peer_ptrs.size(); g.gather_rank = (int)gather_rank;
     for (size_t i = 0; i < b_peer_ptrs.size(); ++i) g.b_peer_ptr[i] = reinterpret_cast<const void*>(b_peer_ptrs[i]);
+  }
+  if (a_peer_ptrs.size() > 1) {
+    TORCH_CHECK(a_peer_ptrs.size() <= 8, "row-sharded A: up to 8 ranks");
+    g.a_world = (int)a_peer_ptrs.size(); g.a_rows_per_rank = (int)a_rows_per_rank;
+    for (size_t i = 0; i < a_peer_ptrs.size(); ++i) g.a_peer_ptr[i] = reinterpret_cast<const void*>(a_peer_ptrs[i]);
+  }
+  if (rs_out_ptrs.size() > 1) {
+    TORCH_CHECK(rs_out_ptrs.size() <= 8, "reduce-scatter epilogue: up to 8 ranks");
+    g.rs_world = (int)rs_out_ptrs.size(); g.rs_rows_per_rank = (int)rs_rows_per_rank; g.rs_rank = (int)rs_rank;
+    for (size_t i = 0; i < rs_out_ptrs.size(); ++i) g.rs_out[i] = reinterpret_cast<float*>(rs_out_ptrs[i]);
   }
   int rc = loom_gemm_bf16(&g, cur_stream());
   TORCH_CHECK(rc == 0, "loom_gemm_bf16 failed with code ", rc);
@@ -297,6 +309,15 @@ void attn(bool bwd, torch::Tensor qkc, torch::Tensor kcache, torch::Tensor vcach
   TORCH_CHECK(rc == 0, "loom_attn failed: ", rc);
 }
 
+void tp_barrier(std::vector<int64_t> flags_peer, int64_t rank, int64_t epoch, torch::Tensor status, int64_t code) {
+  const c10::cuda::CUDAGuard guard(status.device());
+  int* ptrs[8];
+  TORCH_CHECK(flags_peer.size() <= 8, "up to 8 ranks");
+  for (size_t i = 0; i < flags_peer.size(); ++i) ptrs[i] = reinterpret_cast<int*>(flags_peer[i]);
+  int rc = loom_tp_barrier(ptrs, (int)flags_peer.size(), (int)rank, (int)epoch, status.data_ptr<int>(), (int)code, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_tp_barrier failed: ", rc);
+}
+
 void p2p_grad_step(int64_t W, int64_t rank, int64_t nblk, std::vector<int64_t> grads, std::vector<int64_t> params,
                    std::vector<int64_t> shadow, std::vector<int64_t> sync, int64_t mc_grads, torch::Tensor m,
                    torch::Tensor v, torch::Tensor lr_mult, torch::Tensor wd, torch::Tensor active, torch::Tensor hyper,
@@ -350,6 +371,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("colsum", &colsum, "column sums into an fp32 accumulator");
   m.def("ce", &ce, "cross-entropy over bf16 logits with in-place gradient");
   m.def("temporal_fwd", &temporal_fwd, "temporal carry endpoint + PolARM");
+  m.def("tp_barrier", &tp_barrier, "bounded cross-rank barrier on peer-mapped flag words");
   m.def("p2p_grad_step", &p2p_grad_step, "fused gradient reduce-scatter + AdamW + parameter all-gather over peer memory");
   m.def("attn", &attn, "dual-context causal GQA attention (forward / backward)");
   m.def("temporal_bwd", &temporal_bwd, "temporal carry endpoint backward");

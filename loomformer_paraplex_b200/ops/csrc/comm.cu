@@ -209,7 +209,24 @@ __global__ void wait_done_kernel(P2P c, int* status) {
   *w_local(my, c.W, 3) = epoch;
 }
 
+struct Peers { int* f[MAXW]; };
+
+__global__ void tp_barrier_kernel(Peers pp, int world, int rank, int epoch, int* status, int code) {
+  __threadfence_system();                                   // everything this rank sent before is visible first
+  if (threadIdx.x < world) st_release_sys(pp.f[threadIdx.x] + rank, epoch);
+  if (threadIdx.x < world) wait_flag(pp.f[rank] + threadIdx.x, epoch, status, code);
+}
+
 }  // namespace
+
+extern "C" int loom_tp_barrier(int* const* flags_peer, int world, int rank, int epoch, int* status, int code,
+                               cudaStream_t stream) {
+  if (world < 1 || world > MAXW) return -1;
+  Peers pp;
+  for (int i = 0; i < world; ++i) pp.f[i] = flags_peer[i];
+  tp_barrier_kernel<<<1, 32, 0, stream>>>(pp, world, rank, epoch, status, code);
+  return (int)cudaGetLastError();
+}
 
 extern "C" int loom_p2p_grad_step(const LoomP2P* a, cudaStream_t stream) {
   if (a->W < 1 || a->W > MAXW) return -1;

@@ -64,6 +64,12 @@ struct Params {
   // [r * gather_per, (r+1) * gather_per) of B; b_peer[r] maps rank r's copy of the whole matrix (box: 64 rows)
   int gather_world, gather_rank, gather_per;
   CUtensorMap b_peer[8];
+  // row-sharded activations (tensor-parallel all-gather -> GEMM): rank r holds rows [r*a_rows_per_rank, ...) of A
+  int a_world, a_rows_per_rank;
+  CUtensorMap a_peer[8];
+  // GEMM -> reduce-scatter: the fp32 partial product of output rows owned by rank r is stored into this rank's slot of rs_out[r]
+  int rs_world, rs_rank, rs_rows_per_rank;
+  float* rs_out[8];
 };
 
 template <int BN>
@@ -141,6 +147,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_kernel(const __grid_const
 #pragma unroll
               for (int j = 0; j < BM / 64; ++j)
                 tma_load_3d(sa + j * 8192, &sg.a, &full[st], m0 + 64 * j, sg.a_k0 + k, ag);
+            } else if (p.a_world > 1) {
+              // the tile's 128 rows live on one rank (a_rows_per_rank is a multiple of 128): fetch them from there
+              tma_load_3d(sa, &p.a_peer[m0 / p.a_rows_per_rank], &full[st], sg.a_k0 + k, m0, 0);
             } else {
               tma_load_3d(sa, &sg.a, &full[st], sg.a_k0 + k, m0, ag);
             }
@@ -238,7 +247,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_kernel(const __grid_const
 #pragma unroll
             for (int i = 0; i < 32; ++i) if (i < nvalid) v[i] += bias[n + i];
           }
-          if (p.out_fp32) {
+          if (p.rs_world > 1) {
+            // reduce-scatter epilogue: this rank's partial product of a row goes, by plain 16-byte stores over
+            // NVLink, into slot `rs_rank` of the staging buffer [world][rows_per_rank][N] of the rank that owns the
+            // row; the owner sums its slots after the closing barrier (deterministic, no atomics on the link)
+            const int owner = row / p.rs_rows_per_rank;
+            float* dst = p.rs_out[owner] +
+                         ((long long)p.rs_rank * p.rs_rows_per_rank + (row - owner * p.rs_rows_per_rank)) * p.ldc + n;
+            if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            } else {
+              for (int i = 0; i < nvalid; ++i) dst[i] = v[i];
+            }
+          } else if (p.out_fp32) {
             float* dst = reinterpret_cast<float*>(p.c) + c_row + n;
             if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
@@ -359,6 +381,20 @@ extern "C" int loom_gemm_bf16(const LoomGemm* g, cudaStream_t stream) {
   }
   static int sms = 0;
   if (sms == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+  if (g->a_world > 1) {
+    if (a_mn || g->nseg != 1 || p.heads != 1 || g->a_world > 8 || g->a_rows_per_rank % BM) return -7;
+    p.a_world = g->a_world; p.a_rows_per_rank = g->a_rows_per_rank;
+    for (int r = 0; r < g->a_world; ++r) {
+      LoomOperand o = g->a[0];
+      o.ptr = g->a_peer_ptr[r];
+      if (!fill_map(&p.a_peer[r], o, false, BM)) return -8;
+    }
+  }
+  if (g->rs_world > 1) {
+    if (!g->out_fp32 || p.heads != 1 || g->rs_world > 8 || g->rs_rows_per_rank < 1) return -9;
+    p.rs_world = g->rs_world; p.rs_rank = g->rs_rank; p.rs_rows_per_rank = g->rs_rows_per_rank;
+    for (int r = 0; r < g->rs_world; ++r) p.rs_out[r] = g->rs_out[r];
+  }
   if (g->gather_world > 1) {
     // weight rows fetched from their owners: plain (unbatched, single-segment, K-major) linear layers only
     if (a_mn || b_mn || g->nseg != 1 || p.heads != 1 || p.b_per_seg || g->gather_world > 8) return -5;

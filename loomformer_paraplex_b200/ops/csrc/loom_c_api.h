@@ -39,7 +39,20 @@ typedef struct {
   // memory), and `b` itself is this rank's copy, which the launch completes as a side effect.
   int gather_world, gather_rank;
   const void* b_peer_ptr[8];
+  // tensor parallelism.  a_world > 1: A (single segment, K-major) is row-sharded, rank r's rows live in
+  // a_peer_ptr[r] (a full-size buffer per rank; a_rows_per_rank is a multiple of 128).  rs_world > 1: instead of
+  // storing C, store the fp32 product of the rows owned by rank r into slot rs_rank of rank r's staging buffer
+  // rs_out[r] = [rs_world][rs_rows_per_rank][N] (row pitch ldc), i.e. the GEMM's epilogue is the scatter of a
+  // reduce-scatter; the caller brackets the launch with loom_tp_barrier and the owner sums its slots afterwards.
+  int a_world, a_rows_per_rank;
+  const void* a_peer_ptr[8];
+  int rs_world, rs_rank, rs_rows_per_rank;
+  float* rs_out[8];
 } LoomGemm;
+
+// Cross-rank barrier on peer-mapped flag words (one int per rank in each rank's `flags` buffer): publish `epoch`
+// to every peer, then wait (bounded; a timeout records `code` in *status) until every peer has published it.
+int loom_tp_barrier(int* const* flags_peer, int world, int rank, int epoch, int* status, int code, cudaStream_t stream);
 
 int loom_gemm_bf16(const LoomGemm* g, cudaStream_t stream);
 

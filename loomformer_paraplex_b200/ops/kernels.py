@@ -50,12 +50,14 @@ def gemm(a_list: List[torch.Tensor], k_len: List[int], b, c: torch.Tensor, *, M:
          heads: int = 1, a_mn: bool = False, b_mn: bool = False, a_k0: Optional[List[int]] = None,
          b_k0: Optional[List[int]] = None, bias: Optional[torch.Tensor] = None, accumulate: bool = False,
          bn: Optional[int] = None, swap_mn: bool = False, peer_ptrs: Optional[List[int]] = None,
-         gather_rank: int = 0) -> None:
+         gather_rank: int = 0, a_peer_ptrs: Optional[List[int]] = None, a_rows_per_rank: int = 0,
+         rs_out_ptrs: Optional[List[int]] = None, rs_rows_per_rank: int = 0, rs_rank: int = 0) -> None:
     ext = native.ext()
     n = len(a_list)
     ext.gemm(a_list, k_len, a_k0 or [0] * n, b_k0 or [0] * n, b if isinstance(b, (list, tuple)) else [b], a_mn, b_mn,
              c, bias, M, N, heads, accumulate,
-             bn or _pick_bn(M, N, heads), swap_mn, status_word(c.device), peer_ptrs or [], gather_rank)
+             bn or _pick_bn(M, N, heads), swap_mn, status_word(c.device), peer_ptrs or [], gather_rank,
+             a_peer_ptrs or [], a_rows_per_rank, rs_out_ptrs or [], rs_rows_per_rank, rs_rank)
     native.count()
 
 

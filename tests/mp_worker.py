@@ -52,12 +52,66 @@ def gather_gemm_case(out, dev, world, rank):
     pdist.shutdown()
 
 
+def tensor_parallel_case(out, dev, world, rank):
+    """Column-parallel up projection (all-gather inside the GEMM) and row-parallel down projection (reduce-scatter in
+    the epilogue) of an MLP against the single-device result; also times both fused GEMMs (max over ranks)."""
+    import torch.distributed as dist
+    from loomformer_paraplex_b200.ops import kernels
+    from loomformer_paraplex_b200.parallel.tp import TensorParallel
+    tp = TensorParallel(device=dev)
+    M, K, H = 2048, 768, 3072
+    g = torch.Generator(device="cpu").manual_seed(11)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(dev)
+    w_up = (torch.randn(H, K, generator=g) * 0.03).to(torch.bfloat16).to(dev)
+    w_dn = (torch.randn(K, H, generator=g) * 0.03).to(torch.bfloat16).to(dev)
+    per, hl = M // world, H // world
+    x_rows = x[rank * per:(rank + 1) * per].contiguous()
+    w_up_l = w_up[rank * hl:(rank + 1) * hl].contiguous()
+    w_dn_l = w_dn[:, rank * hl:(rank + 1) * hl].contiguous()
+    y_l = tp.column_parallel("x", x_rows, w_up_l, M)
+    o_l = torch.tanh(y_l.float()).to(torch.bfloat16)
+    z = tp.row_parallel("z", o_l, w_dn_l)
+    torch.cuda.synchronize(); dist.barrier()
+    kernels.check_status(dev)
+    y_ref = x.float() @ w_up.float().t()
+    o_ref = torch.tanh(y_ref[:, rank * hl:(rank + 1) * hl].to(torch.bfloat16).float()).to(torch.bfloat16)
+    up_err = float((y_l.float() - y_ref[:, rank * hl:(rank + 1) * hl]).abs().max() / y_ref.abs().max())
+    o_full = torch.tanh(y_ref.to(torch.bfloat16).float()).to(torch.bfloat16).float()
+    z_ref = (o_full @ w_dn.float().t())[rank * per:(rank + 1) * per]
+    dn_err = float((z - z_ref).abs().max() / z_ref.abs().max())
+    # timing: device events around each fused op (barriers included), max over ranks
+    def timed(fn, iters=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(); dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record(); torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / iters], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+    t_up = timed(lambda: tp.column_parallel("x", x_rows, w_up_l, M))
+    t_dn = timed(lambda: tp.row_parallel("z", o_l, w_dn_l))
+    ok = torch.tensor([float(up_err < 2e-2 and dn_err < 2e-2)], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        flops = 2.0 * M * K * hl
+        torch.save({"up_err": up_err, "dn_err": dn_err, "all_ranks_ok": bool(ok.item() > 0.5), "ms_up": t_up, "ms_down": t_dn,
+                    "flops_per_rank": flops, "nvlink_bytes_up": (world - 1) * per * K * 2,
+                    "nvlink_bytes_down": (world - 1) * per * K * 4, "world": world}, out)
+    pdist.shutdown()
+
+
 def main():
     mode, out, device_kind = sys.argv[1], sys.argv[2], sys.argv[3]
     dev, world, rank = pdist.init(device_kind)
     torch.manual_seed(0)
     if mode == "gather":
         return gather_gemm_case(out, dev, world, rank)
+    if mode == "tp":
+        return tensor_parallel_case(out, dev, world, rank)
     cfg = Config(**CFG)
     model = Model(cfg).to(dev)
     eng = TrainEngine(cfg, model, dev, optimizer="adamw", grad_sync=mode)

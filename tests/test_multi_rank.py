@@ -61,3 +61,13 @@ def test_sharded_training_matches_nccl_baseline(tmp_path):
     assert float(diff.mean()) < 2e-5, float(diff.mean())
     assert float((diff > 1e-3).float().mean()) < 1e-3
     assert abs(a["losses"][-1] - b["losses"][-1]) < 5e-2
+
+
+@pytest.mark.gpu
+def test_tensor_parallel_fused_gemms(tmp_path):
+    """All-gather fused into the column-parallel GEMM and reduce-scatter fused into the row-parallel GEMM."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = _launch("tp", str(tmp_path / "tp.pt"), "cuda", 2, 29617)
+    assert res["all_ranks_ok"], res
+    print("tensor-parallel fused GEMMs:", {k: v for k, v in res.items()})
