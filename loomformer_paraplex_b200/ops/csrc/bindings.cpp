@@ -173,6 +173,18 @@ void rope_bwd(torch::Tensor dq_attn, torch::Tensor dqkc, torch::Tensor dkc, torc
   TORCH_CHECK(rc == 0, "loom_rope_bwd failed: ", rc);
 }
 
+void decode_attn(torch::Tensor q, torch::Tensor kc, torch::Tensor vc, torch::Tensor pos, torch::Tensor out_c, torch::Tensor out_k,
+                 torch::Tensor ws, int64_t B, int64_t S, int64_t QH, int64_t KVH, int64_t HD, int64_t NS) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(q.is_contiguous() && kc.is_contiguous() && vc.is_contiguous() && pos.scalar_type() == torch::kInt64,
+              "decode_attn: contiguous bf16 operands and an int64 position");
+  TORCH_CHECK(ws.numel() >= loom_decode_attn_workspace_floats((int)B, (int)QH, (int)KVH, (int)HD, (int)NS), "workspace too small");
+  int rc = loom_decode_attn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos.data_ptr<int64_t>() ? (const long long*)pos.data_ptr<int64_t>() : nullptr,
+                            out_c.data_ptr(), out_k.data_ptr(), fptr(ws), (int)B, (int)S, (int)QH, (int)KVH, (int)HD, (int)NS,
+                            cur_stream());
+  TORCH_CHECK(rc == 0, "loom_decode_attn failed: ", rc);
+}
+
 void slot_pool(bool bwd, torch::Tensor keys, torch::Tensor w9, torch::Tensor pooled, torch::Tensor stats,
                c10::optional<torch::Tensor> dpooled, c10::optional<torch::Tensor> dkeys, c10::optional<torch::Tensor> dw9_part,
                int64_t BK, int64_t H) {
@@ -360,6 +372,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rope_store", &rope_store, "RoPE + KV cache write");
   m.def("rope_bwd", &rope_bwd, "inverse RoPE of the q/k/v gradients");
   m.def("dread", &dread, "depth-attention read (forward / backward)");
+  m.def("decode_attn", &decode_attn, "KV-cache attention for one new token per sequence, dual context, split over positions");
   m.def("slot_pool", &slot_pool, "softmax pooling of boundary carriers over neurons (forward / backward)");
   m.def("cross_attn", &cross_attn, "token rows attending to the boundary keys (forward / backward)");
   m.def("fixed_rms", &fixed_rms, "x * target / rms(x) over head_dim (forward / backward)");

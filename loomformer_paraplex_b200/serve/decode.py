@@ -48,6 +48,15 @@ class DecodeEngine:
         self.next_tok = z(B, dtype=torch.long)
         self._graph = None
         self._w = {}
+        # native KV-cache attention (bf16 on CUDA): positions are split over enough blocks to fill the GPU
+        self._native_attn = False
+        if dev.type == "cuda" and self.dt == torch.bfloat16 and d.hd % 8 == 0 and d.group <= 8:
+            from ..ops import native
+            if native.available():
+                self._native_attn = True
+                self._ns = max(1, min(16, -(-296 // (B * d.kvh))))
+                n_ws = B * d.kvh * self._ns * (2 * d.group + 2 * d.group * d.hd)
+                self._attn_ws = torch.empty(max(1, n_ws), dtype=torch.float32, device=dev)
         self.refresh_weights()
 
     # ------------------------------------------------------------------ weights in the compute dtype
@@ -175,12 +184,20 @@ class DecodeEngine:
             v = qkv[:, d.n + d.kv_dim:].view(B, d.kvh, d.hd)
             self.kc[bi].index_copy_(1, pos, k.unsqueeze(1))
             self.vc[bi].index_copy_(1, pos, v.unsqueeze(1))
-            kk = self.kc[bi].view(B, S, d.kvh, 1, d.hd).expand(B, S, d.kvh, d.group, d.hd).reshape(B, S, d.qh, d.hd)
-            vv = self.vc[bi].view(B, S, d.kvh, 1, d.hd).expand(B, S, d.kvh, d.group, d.hd).reshape(B, S, d.qh, d.hd)
-            sc = torch.einsum("bhd,bshd->bhs", q.float(), kk.float()) * scale
-            a = torch.softmax(sc.masked_fill(~key_ok, float("-inf")), dim=-1)
-            k_ctx = torch.einsum("bhs,bshd->bhd", a, kk.float()).to(dt)
-            c = torch.einsum("bhs,bshd->bhd", a, vv.float()).to(dt)
+            if self._native_attn:
+                from ..ops import native
+                q = q.contiguous()
+                c, k_ctx = torch.empty_like(q), torch.empty_like(q)
+                native.ext().decode_attn(q, self.kc[bi], self.vc[bi], pos, c, k_ctx, self._attn_ws, B, S, d.qh, d.kvh,
+                                         d.hd, self._ns)
+                native.count(2 if self._ns > 1 else 1)
+            else:
+                kk = self.kc[bi].view(B, S, d.kvh, 1, d.hd).expand(B, S, d.kvh, d.group, d.hd).reshape(B, S, d.qh, d.hd)
+                vv = self.vc[bi].view(B, S, d.kvh, 1, d.hd).expand(B, S, d.kvh, d.group, d.hd).reshape(B, S, d.qh, d.hd)
+                sc = torch.einsum("bhd,bshd->bhs", q.float(), kk.float()) * scale
+                a = torch.softmax(sc.masked_fill(~key_ok, float("-inf")), dim=-1)
+                k_ctx = torch.einsum("bhs,bshd->bhd", a, kk.float()).to(dt)
+                c = torch.einsum("bhs,bshd->bhd", a, vv.float()).to(dt)
             attn_out = self._lin(c.reshape(B, d.n), blk.attn.o.weight)
             sub = 2 * bi
             skip, _ = read(sub)

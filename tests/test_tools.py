@@ -228,3 +228,30 @@ def test_every_shipped_config_loads_and_resolves():
         assert d.n == d.qh * d.hd and d.hidden % d.qh == 0, n
     nano = resolve(Config.from_yaml(os.path.join(ROOT, "cfg", "nano.yaml")), calibrate=False)
     assert (nano.n, nano.qh, nano.kvh, nano.hd, nano.hidden, nano.layers) == (768, 8, 2, 96, 3072, 10)
+
+
+def test_replica_pool_serves_in_order_and_detects_a_dead_replica(packed):
+    """Two CPU replicas give what a single engine gives; a replica that dies is reported instead of waited for."""
+    from loomformer_paraplex_b200.serve.decode import DecodeEngine
+    from loomformer_paraplex_b200.serve.replicas import ReplicaPool
+    from loomformer_paraplex_b200.serve.runtime import load_model
+    d, tok, cfg, _ = packed
+    path = str(d / "m.pt")
+    prompts = [[(7 * i + j) % tok.vocab_size for j in range(12)] for i in range(5)]
+    model, *_ = load_model(path, torch.device("cpu"), tokenizer=tok)
+    eng = DecodeEngine(model, batch=2, use_graph=False)
+    want = []
+    for lo in range(0, 5, 2):
+        rows = torch.tensor(prompts[lo:lo + 2])
+        n = rows.shape[0]
+        if n < 2:
+            rows = torch.cat((rows, rows[:1]), 0)
+        want += eng.generate(rows, 4)[:n].tolist()
+    with ReplicaPool(path, ["cpu", "cpu"], batch=2) as pool:
+        got = pool.generate(prompts, 4)
+        assert got == want
+        pool.procs[0].terminate(); pool.procs[0].join()
+        with pytest.raises(RuntimeError):
+            pool.generate(prompts[:4], 2, timeout=3.0)
+    with pytest.raises(RuntimeError):
+        ReplicaPool(str(d / "missing.pt"), ["cpu"], batch=1, start_timeout=60)
