@@ -89,7 +89,35 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=None, help="debug only: a non-default value makes the number invalid")
     ap.add_argument("--grad-sync", default="auto", choices=["auto", "collective", "p2p", "fsdp"])
+    ap.add_argument("--workload", default="pretrain", choices=["pretrain", "sft"],
+                    help="sft: synthetic multi-turn chats rendered through the chat template, packed to seq_len, "
+                         "assistant-only loss (a secondary benchmark; the headline metric is pretrain)")
     return ap.parse_args()
+
+
+def sft_batches(vocab, micro_batch, seq_len, rank, n=4):
+    """Packed SFT batches: conversations with turn lengths uniform in 16..512 rendered through chat_template.jinja,
+    packed greedily to seq_len with per-segment positions and segment ids, loss on assistant spans only."""
+    import tempfile
+    from loomformer_paraplex_b200.data import sft as sd
+    from loomformer_paraplex_b200.data.chat import ChatTemplate
+    from loomformer_paraplex_b200.data.tokenizers import BPETokenizer, train_tokenizer
+    import io, contextlib
+    words = [f"w{i:03d}" for i in range(400)]
+    with tempfile.TemporaryDirectory() as tmp, contextlib.redirect_stdout(io.StringIO()):
+        path = os.path.join(tmp, "tok.json")
+        train_tokenizer("", min(vocab, 2048), path, texts=[" ".join(words)] * 20)
+        tok = BPETokenizer.load(path)
+    chat = ChatTemplate(tok, template_path=os.path.join(ROOT, "chat_template.jinja"))
+    convs = sd.synthetic_conversations(600, words, seed=17 + rank, min_len=16, max_len=512)
+    pool, _, _ = sd.tokenize_examples(convs, chat, seq_len)
+    packer = sd.Packer(pool, seq_len, sd.need_pad_id(tok), shuffle=True, seed=3 + rank)
+    import torch
+    out = []
+    for _ in range(n):
+        b = packer.sample_batch(micro_batch, torch.device("cpu"))
+        out.append({k: (v.pin_memory() if (torch.is_tensor(v) and torch.cuda.is_available()) else v) for k, v in b.items()})
+    return out
 
 
 def timed_loop(torch, dist, step_fn, steps, warmup, world, before=None):
@@ -136,6 +164,10 @@ def emit(args, impl, ms, clocks, world, extra):
                    "l2": "per-step working set >> 126 MB L2, no explicit flush",
                    "layers": MODEL_KW["layers"] if args.layers is None else args.layers},
     }
+    if getattr(args, "workload", "pretrain") == "sft":
+        line["metric"] = "SFT train tokens/s (113M LoomFormer-Paraplex, bf16, packed chats, seq 2048)"
+        line["data"] = "synthetic multi-turn chats through chat_template.jinja, packed, assistant-only loss; random-init weights"
+        line["vs_baseline"] = None
     line.update(extra)
     print(json.dumps(line), flush=True)
 
@@ -159,20 +191,36 @@ def run_ours(args):
     model = Model(cfg).to(dev)
     sync = "collective" if args.grad_sync == "auto" else args.grad_sync
     engine = TrainEngine(cfg, model, dev, optimizer=args.optimizer, grad_sync=sync)
-    src = SyntheticTokens(cfg.vocab, args.micro_batch, args.seq_len, seed=cfg.seed, rank=rank, pin=True, pool=4)
-    resident = [b.to(dev) for b in src.batches]
     state = {"i": 0}
-
-    def step_device():
-        engine.step(resident[state["i"] % len(resident)])
-        state["i"] += 1
-
     loss_host = torch.zeros((), dtype=torch.float32).pin_memory()
+    if args.workload == "sft":
+        host = sft_batches(cfg.vocab, args.micro_batch, args.seq_len, rank)
+        to_dev = lambda b: {k: v.to(dev, non_blocking=True) for k, v in b.items() if torch.is_tensor(v)}
+        resident = [to_dev(b) for b in host]
+        h2d = sum(v.numel() * v.element_size() for v in host[0].values() if torch.is_tensor(v))
 
-    def step_e2e():
-        loss = engine.step(src.next())
-        loss_host.copy_(loss, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        def step_device():
+            engine.step([resident[state["i"] % len(resident)]])
+            state["i"] += 1
+
+        def step_e2e():
+            loss = engine.step([to_dev(host[state["i"] % len(host)])])
+            state["i"] += 1
+            loss_host.copy_(loss, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+    else:
+        src = SyntheticTokens(cfg.vocab, args.micro_batch, args.seq_len, seed=cfg.seed, rank=rank, pin=True, pool=4)
+        resident = [b.to(dev) for b in src.batches]
+        h2d = int(src.batches[0].numel() * src.batches[0].element_size())
+
+        def step_device():
+            engine.step(resident[state["i"] % len(resident)])
+            state["i"] += 1
+
+        def step_e2e():
+            loss = engine.step(src.next())
+            loss_host.copy_(loss, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
 
     ms, clocks = timed_loop(torch, dist, step_device, args.steps, args.warmup, world, before=native.reset_launches)
     launches = native.launches()
@@ -185,7 +233,7 @@ def run_ours(args):
         fb = dict(getattr(engine.plan.K, "fallbacks", {})) if engine.plan is not None else {}
         emit(args, "ours", ms, clocks, world, {
             "e2e": {"value": tokens / (ms_e2e / 1000.0), "unit": "tokens/s",
-                    "h2d_bytes_per_step": int(src.batches[0].numel() * src.batches[0].element_size()),
+                    "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e},
             "gpu_launches": int(launches),
             "library_fallback_calls": fb, "final_loss": float(loss_host)})
