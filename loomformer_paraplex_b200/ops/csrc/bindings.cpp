@@ -360,6 +360,26 @@ void p2p_grad_step(int64_t W, int64_t rank, int64_t nblk, std::vector<int64_t> g
   TORCH_CHECK(rc == 0, "loom_p2p_grad_step failed: ", rc);
 }
 
+void p2p_grad_step_atom(int64_t W, int64_t rank, int64_t nblk, std::vector<int64_t> grads, std::vector<int64_t> params,
+                        std::vector<int64_t> shadow, std::vector<int64_t> sync, torch::Tensor m, torch::Tensor v,
+                        torch::Tensor lr_mult, torch::Tensor wd, torch::Tensor hyper, torch::Tensor stats, torch::Tensor sumsq,
+                        double max_norm, torch::Tensor status, torch::Tensor cnt_blk, torch::Tensor gprev, torch::Tensor pnode,
+                        torch::Tensor trust, torch::Tensor atom_out) {
+  const c10::cuda::CUDAGuard guard(m.device());
+  TORCH_CHECK((int64_t)grads.size() == W && (int64_t)params.size() == W && (int64_t)shadow.size() == W &&
+              (int64_t)sync.size() == W && W <= 8, "peer pointer lists must have one entry per rank (<= 8)");
+  LoomP2P a{};
+  a.W = (int)W; a.rank = (int)rank; a.nblk = nblk;
+  for (int i = 0; i < W; ++i) {
+    a.grads[i] = reinterpret_cast<float*>(grads[i]); a.params[i] = reinterpret_cast<float*>(params[i]);
+    a.shadow[i] = reinterpret_cast<void*>(shadow[i]); a.sync[i] = reinterpret_cast<int*>(sync[i]);
+  }
+  a.m = fptr(m); a.v = fptr(v); a.lr_mult = fptr(lr_mult); a.wd_blk = fptr(wd); a.hyper = fptr(hyper);
+  a.stats = fptr(stats); a.sumsq_local = fptr(sumsq); a.max_norm = (float)max_norm; a.status = status.data_ptr<int>();
+  int rc = loom_p2p_grad_step_atom(&a, fptr(cnt_blk), fptr(gprev), fptr(pnode), fptr(trust), fptr(atom_out), cur_stream());
+  TORCH_CHECK(rc == 0, "loom_p2p_grad_step_atom failed: ", rc);
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -384,6 +404,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("colsum", &colsum, "column sums into an fp32 accumulator");
   m.def("ce", &ce, "cross-entropy over bf16 logits with in-place gradient");
   m.def("temporal_fwd", &temporal_fwd, "temporal carry endpoint + PolARM");
+  m.def("p2p_grad_step_atom", &p2p_grad_step_atom, "fused gradient reduce-scatter + ATOM on the shard + parameter push over peer memory");
   m.def("tp_barrier", &tp_barrier, "bounded cross-rank barrier on peer-mapped flag words");
   m.def("p2p_grad_step", &p2p_grad_step, "fused gradient reduce-scatter + AdamW + parameter all-gather over peer memory");
   m.def("attn", &attn, "dual-context causal GQA attention (forward / backward)");

@@ -209,6 +209,58 @@ __global__ void wait_done_kernel(P2P c, int* status) {
   *w_local(my, c.W, 3) = epoch;
 }
 
+// ---- pieces for "any optimizer on the shard": exchange the shard norms, then (after the optimizer kernel of the
+// caller's choice has updated the shard in place) push the refreshed shard to every peer
+__global__ void norm_exchange_kernel(P2P c, float* __restrict__ sumsq_local, float max_norm, float* __restrict__ stats,
+                                     int* status) {
+  if (threadIdx.x != 0) return;
+  int* my = c.sync[c.rank];
+  const int epoch = *w_local(my, c.W, 3) + 1;
+  const float mine = *sumsq_local;
+  for (int p = 0; p < c.W; ++p) *reinterpret_cast<volatile float*>(w_sumsq(c.sync[p], c.W, c.rank)) = mine;
+  __threadfence_system();
+  for (int p = 0; p < c.W; ++p) st_release_sys(w_normflag(c.sync[p], c.W, c.rank), epoch);
+  bool ok = true;
+  float tot = 0.f;
+  for (int p = 0; p < c.W && ok; ++p) {
+    ok = wait_flag(w_normflag(my, c.W, p), epoch, status, 406);
+    tot += *reinterpret_cast<volatile float*>(w_sumsq(my, c.W, p));
+  }
+  const float norm = sqrtf(tot);
+  const bool fin = isfinite(norm) && ok;
+  stats[0] = norm;
+  stats[1] = (max_norm > 0.f && fin) ? fminf(1.f, max_norm / (norm + 1e-6f)) : 1.f;
+  stats[2] = fin ? 1.f : 0.f;
+  *sumsq_local = 0.f;
+}
+
+__global__ void __launch_bounds__(256) allgather_push_kernel(P2P c) {
+  int* my = c.sync[c.rank];
+  const int epoch = *w_local(my, c.W, 3) + 1;
+  const float* pl = c.params[c.rank];
+  const __nv_bfloat16* sl = c.shadow[c.rank];
+  for (long long b = c.blk_lo + blockIdx.x; b < c.blk_hi; b += gridDim.x) {
+    const long long i = b * BLK + threadIdx.x;
+    const float pp = pl[i];
+    const __nv_bfloat16 pb = sl[i];
+    for (int p = 1; p < c.W; ++p) {
+      const int q = (c.rank + p) % c.W;
+      c.params[q][i] = pp;
+      c.shadow[q][i] = pb;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int done = atomicAdd(w_local(my, c.W, 2), 1);
+    if (done == (int)gridDim.x - 1) {
+      *w_local(my, c.W, 2) = 0;
+      __threadfence_system();
+      for (int p = 0; p < c.W; ++p) st_release_sys(w_done(c.sync[p], c.W, c.rank), epoch);
+    }
+  }
+}
+
 struct Peers { int* f[MAXW]; };
 
 __global__ void tp_barrier_kernel(Peers pp, int world, int rank, int epoch, int* status, int code) {
@@ -225,6 +277,44 @@ extern "C" int loom_tp_barrier(int* const* flags_peer, int world, int rank, int 
   Peers pp;
   for (int i = 0; i < world; ++i) pp.f[i] = flags_peer[i];
   tp_barrier_kernel<<<1, 32, 0, stream>>>(pp, world, rank, epoch, status, code);
+  return (int)cudaGetLastError();
+}
+
+static void fill_p2p(const LoomP2P* a, P2P& c) {
+  for (int p = 0; p < a->W; ++p) {
+    c.grads[p] = a->grads[p]; c.params[p] = a->params[p];
+    c.shadow[p] = reinterpret_cast<__nv_bfloat16*>(a->shadow[p]); c.sync[p] = a->sync[p];
+  }
+  c.mc_grads = a->mc_grads; c.W = a->W; c.rank = a->rank; c.nblk = a->nblk;
+  c.owner_blk = nullptr; c.slot_blk = nullptr; c.replicate_blk = nullptr;
+  const long long per = (a->nblk + a->W - 1) / a->W;
+  c.blk_lo = per * a->rank < a->nblk ? per * a->rank : a->nblk;
+  c.blk_hi = per * (a->rank + 1) < a->nblk ? per * (a->rank + 1) : a->nblk;
+}
+
+// Reduce-scatter + global norm, then ATOM on this rank's contiguous shard (the one-launch kernel of optim.cu, pointed
+// at the shard), then the refreshed shard pushed to every peer.  The per-block ATOM statistics (gprev / pnode / trust)
+// and the moments are therefore current only on the rank that owns the block.
+extern "C" int loom_p2p_grad_step_atom(const LoomP2P* a, const float* cnt_blk, float* gprev, float* pnode, float* trust,
+                                       float* atom_out, cudaStream_t stream) {
+  if (a->W < 1 || a->W > MAXW) return -1;
+  P2P c;
+  fill_p2p(a, c);
+  static int sms = 0;
+  if (sms == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+  const int grid = sms * 2;
+  rs_reduce_kernel<<<grid, 256, 0, stream>>>(c, a->sumsq_local, a->status);
+  norm_exchange_kernel<<<1, 32, 0, stream>>>(c, a->sumsq_local, a->max_norm, a->stats, a->status);
+  const long long lo = c.blk_lo, n = c.blk_hi - c.blk_lo;
+  if (n > 0) {
+    cudaMemsetAsync(atom_out, 0, 3 * sizeof(float), stream);
+    int rc = loom_atom_flat(a->params[a->rank] + lo * BLK, a->grads[a->rank] + lo * BLK, a->m + lo * BLK, a->v + lo * BLK,
+                            reinterpret_cast<__nv_bfloat16*>(a->shadow[a->rank]) + lo * BLK, a->lr_mult + lo, a->wd_blk + lo,
+                            cnt_blk + lo, gprev + lo, pnode + lo, trust + lo, a->stats, a->hyper, atom_out, n, stream);
+    if (rc != 0) return rc;
+  }
+  allgather_push_kernel<<<grid, 256, 0, stream>>>(c);
+  wait_done_kernel<<<1, 1, 0, stream>>>(c, a->status);
   return (int)cudaGetLastError();
 }
 

@@ -125,33 +125,47 @@ __global__ void __launch_bounds__(256) dread_slot_bwd_kernel(const float* __rest
 #pragma unroll
         for (int i = 0; i < 8; ++i) sk[row * HD + l * 8 + i] = kf[i];
       }
-#pragma unroll 4
-      for (int jj = 0; jj < nsub; ++jj) {       // unrolled so the independent dm / lse / dd loads of four sublayers overlap
-        const long long so = (long long)(sub0 + jj);
-        float dmf[8], qv[8];
+      // The loop over reading sublayers is latency-bound (one dependent chain of load -> reduce -> exp per sublayer), so
+      // the loads of PF sublayers are issued together before any of them is consumed.
+      constexpr int PF = 4;
+      for (int j0 = 0; j0 < nsub; j0 += PF) {
+        uint4 raw[PF];
+        float lse_v[PF], dd_v[PF];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { dmf[i] = 0.f; qv[i] = 0.f; }
-        if (act && live) {
-          unpack8(*reinterpret_cast<const uint4*>(dm_all + so * MQ * HD + base), dmf);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) qv[i] = sq[jj * HD + l * 8 + i];
-        }
-        float d = 0.f, dvv = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { d += qv[i] * kf[i]; dvv += dmf[i] * vf[i]; }
-#pragma unroll
-        for (int o = G / 2; o > 0; o >>= 1) {
-          d += __shfl_xor_sync(0xffffffffu, d, o, G);
-          dvv += __shfl_xor_sync(0xffffffffu, dvv, o, G);
-        }
-        float w = 0.f, dsc = 0.f;
-        if (live) {
-          w = __expf(d * scale - lse_all[so * MQ + rh]);
-          dsc = w * (dvv - dd_all[so * MQ + rh]) * scale;
+        for (int u = 0; u < PF; ++u) {
+          const int jj = j0 + u;
+          const long long so = (long long)(sub0 + (jj < nsub ? jj : nsub - 1));
+          raw[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (act && live) raw[u] = *reinterpret_cast<const uint4*>(dm_all + so * MQ * HD + base);
+          lse_v[u] = live ? lse_all[so * MQ + rh] : 0.f;
+          dd_v[u] = live ? dd_all[so * MQ + rh] : 0.f;
         }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { ak[i] += dsc * qv[i]; av[i] += w * dmf[i]; }
-        if (l == 0) sd[row * nsub + jj] = dsc;
+        for (int u = 0; u < PF; ++u) {
+          const int jj = j0 + u;
+          if (jj < nsub) {                               // uniform across the block
+            float dmf[8], qv[8];
+            unpack8(raw[u], dmf);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) qv[i] = act ? sq[jj * HD + l * 8 + i] : 0.f;
+            float d = 0.f, dvv = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { d += qv[i] * kf[i]; dvv += dmf[i] * vf[i]; }
+#pragma unroll
+            for (int o = G / 2; o > 0; o >>= 1) {
+              d += __shfl_xor_sync(0xffffffffu, d, o, G);
+              dvv += __shfl_xor_sync(0xffffffffu, dvv, o, G);
+            }
+            float w = 0.f, dsc = 0.f;
+            if (live) {
+              w = __expf(d * scale - lse_v[u]);
+              dsc = w * (dvv - dd_v[u]) * scale;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { ak[i] += dsc * qv[i]; av[i] += w * dmf[i]; }
+            if (l == 0) sd[row * nsub + jj] = dsc;
+          }
+        }
       }
       if (act && live) {
         *reinterpret_cast<uint4*>(dk + base) = pack8(ak);

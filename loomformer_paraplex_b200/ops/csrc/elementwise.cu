@@ -129,26 +129,38 @@ __global__ void __launch_bounds__(256) dread_fwd_kernel(const float* __restrict_
   float mx = -INFINITY, den = 0.f, acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-  for (int s = 0; s < n; ++s) {
-    float kf[8], vf[8];
-    if (act) {
-      unpack8(*reinterpret_cast<const uint4*>(hk + s * stride + base), kf);
-      unpack8(*reinterpret_cast<const uint4*>(hv + s * stride + base), vf);
-    } else {
+  // the softmax over slots is one dependent chain per slot; issue the K/V loads of PF slots together so their
+  // latencies overlap instead of adding up
+  constexpr int PF = 4;
+  for (int s0 = 0; s0 < n; s0 += PF) {
+    uint4 rk[PF], rv[PF];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) { kf[i] = 0.f; vf[i] = 0.f; }
+    for (int u = 0; u < PF; ++u) {
+      const int s = (s0 + u < n) ? s0 + u : n - 1;
+      rk[u] = make_uint4(0u, 0u, 0u, 0u); rv[u] = rk[u];
+      if (act) {
+        rk[u] = *reinterpret_cast<const uint4*>(hk + s * stride + base);
+        rv[u] = *reinterpret_cast<const uint4*>(hv + s * stride + base);
+      }
     }
-    float d = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) d += qv[i] * kf[i];
+    for (int u = 0; u < PF; ++u) {
+      if (s0 + u < n) {
+        float kf[8], vf[8];
+        unpack8(rk[u], kf); unpack8(rv[u], vf);
+        float d = 0.f;
 #pragma unroll
-    for (int o = G / 2; o > 0; o >>= 1) d += __shfl_xor_sync(mask, d, o, G);
-    const float nm = fmaxf(mx, d);
-    const float corr = __expf(mx - nm), p = __expf(d - nm);
-    den = den * corr + p;
+        for (int i = 0; i < 8; ++i) d += qv[i] * kf[i];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = acc[i] * corr + p * vf[i];
-    mx = nm;
+        for (int o = G / 2; o > 0; o >>= 1) d += __shfl_xor_sync(mask, d, o, G);
+        const float nm = fmaxf(mx, d);
+        const float corr = __expf(mx - nm), p = __expf(d - nm);
+        den = den * corr + p;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = acc[i] * corr + p * vf[i];
+        mx = nm;
+      }
+    }
   }
   const float inv = 1.f / den;
   if (act) {

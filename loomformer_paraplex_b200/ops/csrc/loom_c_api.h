@@ -177,6 +177,9 @@ typedef struct {
   const uint8_t* owner_blk; const int* slot_blk; const uint8_t* replicate_blk;
 } LoomP2P;
 int loom_p2p_grad_step(const LoomP2P* a, cudaStream_t stream);
+// Same exchange with ATOM as the update rule (contiguous shards; see comm.cu)
+int loom_p2p_grad_step_atom(const LoomP2P* a, const float* cnt_blk, float* gprev, float* pnode, float* trust, float* atom_out,
+                            cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -254,7 +254,7 @@ class FusedPlan:
             k, v = K.fixed_rms_fwd(k, FANIN_GAIN), K.fixed_rms_fwd(v, FANIN_GAIN * d.deepnorm_beta)
         hist_k[slot], hist_v[slot] = k, v
 
-    def _project_state_bwd(self, x2d, slot, dstate, hist_k, hist_v, tape_layer, key):
+    def _project_state_bwd(self, x2d, slot, dstate, hist_k, hist_v, tape_layer, key, into):
         """Gradient of :meth:`_project_state` w.r.t. its input; accumulates the weight gradient.  The slot's own
         gradient is formed here, in one pass over every sublayer that read the slot."""
         m, d, K = self.model, self.d, self.K
@@ -267,7 +267,7 @@ class FusedPlan:
             dv = K.fixed_rms_bwd(dv, kv[:, d.n:].view(M, d.qh, d.hd), FANIN_GAIN * d.deepnorm_beta)
         dkv = torch.cat((dk.reshape(M, d.n), dv.reshape(M, d.n)), -1).to(self.adt)
         K.linear_wgrad(dkv, x2d, self.g(m.depth_attn.kv_weight))
-        return K.linear_dgrad(dkv, self.w(m.depth_attn.kv_weight))
+        return K.linear_dgrad(dkv, self.w(m.depth_attn.kv_weight), out=into, accumulate=True)   # into += dkv @ W
 
     def _depth_query(self, sub):
         da, d = self.model.depth_attn, self.d
@@ -414,7 +414,7 @@ class FusedPlan:
             last = bi == L - 1
             sub = 2 * bi
             if not last:
-                dh = dh + self._project_state_bwd(t["h_out"], sub + 2, dst, hist_k, hist_v, t, "h")
+                dh = self._project_state_bwd(t["h_out"], sub + 2, dst, hist_k, hist_v, t, "h", dh)
             # --- LN2 and the two addends
             ds2, df = K.add_ln_bwd(dh, t["x2"], t["mean2"], t["rstd2"], blk.ln_ffn.weight.data,
                                    self.g(blk.ln_ffn.weight), self.g(blk.ln_ffn.bias), cap, t.get("s2"), t.get("f"))
@@ -450,14 +450,14 @@ class FusedPlan:
                 dgl = gr["d_gate_lin"].to(self.adt)
                 K.linear_wgrad(dgl, u, self.g(ffn.gate_proj.weight))
                 K.colsum_add(dgl, self.g(ffn.gate_proj.bias))
-                du = du + K.linear_dgrad(dgl, self.w(ffn.gate_proj.weight))
-            dqkc, du_i, dm2_i = K.imag_bwd(d, dbeta, t["qkc"], u, t["m2"], self.w(ffn.w1_imag), self.g(ffn.w1_imag))
-            du = du + du_i
+                du = K.linear_dgrad(dgl, self.w(ffn.gate_proj.weight), out=du, accumulate=True)
+            dqkc, du, dm2_i = K.imag_bwd(d, dbeta, t["qkc"], u, t["m2"], self.w(ffn.w1_imag), self.g(ffn.w1_imag),
+                                         du_acc=du)
             # --- depth read 2bi+1 (its output feeds the readout GEMM and the imaginary projection)
             K.linear_wgrad(ds2, t["m2"].reshape(M, N), self._readout_g(sub + 1))
             K.dread_stage(d, K.linear_dgrad(ds2, self._readout_w(sub + 1)).view(M, d.qh, d.hd), dm2_i, t["m2"], t["lse2"],
                           dst, sub + 1)
-            du = du + self._project_state_bwd(u, sub + 1, dst, hist_k, hist_v, t, "u")
+            du = self._project_state_bwd(u, sub + 1, dst, hist_k, hist_v, t, "u", du)
             # --- LN1
             ds1, da = K.add_ln_bwd(du, t["x1"], t["mean1"], t["rstd1"], blk.ln_attn.weight.data,
                                    self.g(blk.ln_attn.weight), self.g(blk.ln_attn.bias), cap, t.get("s1"), t.get("a"))
@@ -467,13 +467,13 @@ class FusedPlan:
             # --- attention
             qkc = t["qkc"]
             K.linear_wgrad(da, qkc[:, 2].reshape(M, N), self.g(blk.attn.o.weight))
-            dqkc[:, 2] = dqkc[:, 2] + K.linear_dgrad(da, self.w(blk.attn.o.weight)).view(M, d.qh, d.hd)
+            K.linear_dgrad(da, self.w(blk.attn.o.weight), out=dqkc.view(M, 3, N)[:, 2], accumulate=True)
             dq_attn = K.attn_bwd(d, dqkc, qkc, kc[bi], vc[bi], t["lse"], s, e, seg, dkc[bi], dvc[bi])
             dqkv = K.rope_bwd(d, dq_attn.reshape(B, Tc, d.qh, d.hd), dqkc, dkc[bi], dvc[bi], s, e, tape["cos"],
                               tape["sin"], self.adt).view(M, -1)
             K.linear_wgrad(dqkv, t["h_in"], self.g(blk.attn.qkv_weight))
             dh = K.linear_dgrad(dqkv, self.w(blk.attn.qkv_weight))
-        dh = dh + self._project_state_bwd(tape["h_emb"], 0, dst, hist_k, hist_v, tape["emb_l"], "emb")
+        dh = self._project_state_bwd(tape["h_emb"], 0, dst, hist_k, hist_v, tape["emb_l"], "emb", dh)
         for sub in range(S):
             self._depth_query_bwd(sub, dst["gq"][sub])
         return dh, dtraces_in, dseed

@@ -151,14 +151,16 @@ class CudaKernels(TorchKernels):
             gemm([x], [Kd], w, c, M=M, N=N, bias=b32)
         return c
 
-    def linear_dgrad(self, dy, w):
+    def linear_dgrad(self, dy, w, out=None, accumulate=False):
+        """``dy @ w``; with ``out`` the product is written (or, with ``accumulate``, added) into that bf16 buffer by
+        the GEMM's epilogue, which saves the separate add that sums gradient branches."""
         M, N = dy.shape
         Kd = w.shape[1]
-        if not (_tma_ok(dy) and _tma_ok(w)):
+        if not (_tma_ok(dy) and _tma_ok(w)) or (out is not None and (out.dtype != torch.bfloat16 or out.stride(-1) != 1)):
             self.fallbacks["linear_dgrad"] += 1
-            return super().linear_dgrad(dy, w)
-        c = torch.empty(M, Kd, dtype=torch.bfloat16, device=dy.device)
-        gemm([dy], [N], w, c, M=M, N=Kd, b_mn=True)
+            return super().linear_dgrad(dy, w, out, accumulate)
+        c = out if out is not None else torch.empty(M, Kd, dtype=torch.bfloat16, device=dy.device)
+        gemm([dy], [N], w, c, M=M, N=Kd, b_mn=True, accumulate=bool(accumulate and out is not None))
         return c
 
     def linear_wgrad(self, dy, x, gw):
@@ -190,20 +192,23 @@ class CudaKernels(TorchKernels):
         gemm(segs, lens, w3, c3, M=M, N=d.hpq, heads=d.qh, b_k0=offs)
         return beta
 
-    def imag_bwd(self, d, dbeta, qkc, u, m2, w_imag, gw_imag):
+    def imag_bwd(self, d, dbeta, qkc, u, m2, w_imag, gw_imag, du_acc=None):
+        """``du_acc``: an existing bf16 ``[M, N]`` gradient of ``u`` to add this projection's share into (returned as
+        ``du``) instead of allocating a new one."""
         M = u.shape[0]
         ok = (_tma_ok(qkc) and _tma_ok(u) and _tma_ok(m2) and _tma_ok(w_imag) and _tma_ok(dbeta)
               and d.hd % 8 == 0 and d.hpq % 8 == 0 and gw_imag.dtype == torch.float32)
         if not ok:
             self.fallbacks["imag_bwd"] += 1
-            return super().imag_bwd(d, dbeta, qkc, u, m2, w_imag, gw_imag)
+            return super().imag_bwd(d, dbeta, qkc, u, m2, w_imag, gw_imag, du_acc)
         hd, n, H = d.hd, d.n, d.hidden
         dev = u.device
         w3 = w_imag.view(d.qh, d.hpq, d.imag_in).transpose(0, 1)             # [HPQ, QH, IMAG_IN]
         g3 = gw_imag.view(d.qh, d.hpq, d.imag_in).transpose(0, 1)
         db3 = dbeta.view(M, d.qh, d.hpq)
         dqkc = torch.empty_like(qkc)
-        du = torch.empty(M, n, dtype=torch.bfloat16, device=dev)
+        acc_u = du_acc is not None and du_acc.dtype == torch.bfloat16 and du_acc.stride(-1) == 1
+        du = du_acc if acc_u else torch.empty(M, n, dtype=torch.bfloat16, device=dev)
         dm2 = torch.empty(M, d.qh, hd, dtype=torch.bfloat16, device=dev)
         m2v = m2.view(M, d.qh, hd)
 
@@ -212,22 +217,24 @@ class CudaKernels(TorchKernels):
             gemm([db3], [d.hpq], w3[:, :, col0:col0 + hd], c_dst, M=M, N=hd, heads=d.qh, b_mn=True)
             self._wgrad(db3, a_src, g3[:, :, col0:col0 + hd], d.hpq, hd, d.qh)
 
-        def shared(col0, a_src2d, c_dst2d):
-            gemm([dbeta], [H], w_imag[:, col0:col0 + n], c_dst2d, M=M, N=n, b_mn=True)
+        def shared(col0, a_src2d, c_dst2d, accumulate=False):
+            gemm([dbeta], [H], w_imag[:, col0:col0 + n], c_dst2d, M=M, N=n, b_mn=True, accumulate=accumulate)
             self._wgrad(dbeta, a_src2d, gw_imag[:, col0:col0 + n], H, n)
 
         if d.open_sectors:
             per_head(0, qkc[:, 0], dqkc[:, 0])
             shared(hd, qkc[:, 1].reshape(M, n), dqkc[:, 1].reshape(M, n))
             shared(hd + n, qkc[:, 2].reshape(M, n), dqkc[:, 2].reshape(M, n))
-            shared(hd + 2 * n, u, du)
+            shared(hd + 2 * n, u, du, acc_u)
             shared(hd + 3 * n, m2v.reshape(M, n), dm2.view(M, n))
         else:
             per_head(0, qkc[:, 0], dqkc[:, 0])
             per_head(hd, qkc[:, 1], dqkc[:, 1])
             per_head(2 * hd, qkc[:, 2], dqkc[:, 2])
-            shared(3 * hd, u, du)
+            shared(3 * hd, u, du, acc_u)
             per_head(3 * hd + n, m2v, dm2)
+        if du_acc is not None and not acc_u:
+            du = du_acc + du
         return dqkc, du, dm2
 
 

@@ -37,8 +37,15 @@ class TorchKernels:
             y = y + bias.to(y.dtype)
         return y if out_dtype is None else y.to(out_dtype)
 
-    def linear_dgrad(self, dy, w):
-        return dy @ w.to(dy.dtype)
+    def linear_dgrad(self, dy, w, out=None, accumulate=False):
+        r = dy @ w.to(dy.dtype)
+        if out is None:
+            return r
+        if accumulate:
+            out.add_(r.to(out.dtype))
+        else:
+            out.copy_(r)
+        return out
 
     def linear_wgrad(self, dy, x, gw):
         gw.add_((dy.reshape(-1, dy.shape[-1]).float().t() @ x.reshape(-1, x.shape[-1]).float()).view_as(gw))
@@ -62,8 +69,13 @@ class TorchKernels:
         w = w_imag.view(d.qh, d.hpq, d.imag_in).to(a.dtype)
         return torch.einsum("mgk,ghk->mgh", a, w).reshape(u.shape[0], d.hidden)
 
-    def imag_bwd(self, d, dbeta, qkc, u, m2, w_imag, gw_imag):
-        """Returns (dqkc, du, dm2) and accumulates the weight gradient into ``gw_imag`` (fp32)."""
+    def imag_bwd(self, d, dbeta, qkc, u, m2, w_imag, gw_imag, du_acc=None):
+        """Returns (dqkc, du, dm2) and accumulates the weight gradient into ``gw_imag`` (fp32); ``du`` includes
+        ``du_acc`` when that is given."""
+        dqkc, du, dm2 = self._imag_bwd(d, dbeta, qkc, u, m2, w_imag, gw_imag)
+        return dqkc, (du if du_acc is None else du_acc + du.to(du_acc.dtype)), dm2
+
+    def _imag_bwd(self, d, dbeta, qkc, u, m2, w_imag, gw_imag):
         M = u.shape[0]
         a = self._imag_operand(d, qkc, u, m2)
         w = w_imag.view(d.qh, d.hpq, d.imag_in).to(a.dtype)

@@ -64,9 +64,19 @@ class GradSync:
     def fused_step(self, opt) -> None:
         """Reduce-scatter + clip + AdamW on the own shard + all-gather in three launches over peer memory."""
         from ..ops import kernels, native
-        if opt.kind != "adamw":
-            raise NotImplementedError("the fused NVLink step implements AdamW; use grad_sync='collective' for ATOM")
         f, s = self.flat, self.symm
+        if opt.kind != "adamw":
+            if self.shard is not None:
+                raise NotImplementedError("sharded mode implements AdamW; use grad_sync='p2p' or 'collective' for ATOM")
+            opt.step_count += 1
+            hyper = kernels.upload_hyper(opt)
+            native.ext().p2p_grad_step_atom(self.world, dist.get_rank(), f.nblk, s.peer_ptrs("grads"), s.peer_ptrs("params"),
+                                            s.peer_ptrs("shadow"), s.peer_ptrs("sync"), opt.m, opt.v, opt.lr_mult_blk,
+                                            opt.wd_blk, hyper, opt.stats, self.sumsq, opt.grad_clip,
+                                            kernels.status_word(f.device), opt.cnt_blk, opt.gprev_blk, opt.pnode_blk,
+                                            opt.trust_blk, opt.atom_out)
+            native.count(5)
+            return
         opt.step_count += 1
         hyper = kernels.upload_hyper(opt)
         mc = s.multicast_ptr("grads") if self.use_multimem else 0
@@ -77,6 +87,29 @@ class GradSync:
                                    kernels.status_word(f.device), None if sh is None else sh.owner_blk,
                                    None if sh is None else sh.slot_blk, None if sh is None else sh.replicate_blk)
         native.count(3)
+
+    def own_block_range(self):
+        """Contiguous block range this rank updates in the replicated fused step (matches comm.cu)."""
+        per = -(-self.flat.nblk // self.world)
+        r = dist.get_rank()
+        return min(per * r, self.flat.nblk), min(per * (r + 1), self.flat.nblk)
+
+    def gather_optimizer_state(self, opt) -> None:
+        """Fused-step mode: moments and per-block ATOM statistics are current only on the rank that owns a block;
+        make them complete on every rank (collective) before a checkpoint."""
+        if self.backend != "p2p" or self.world <= 1:
+            return
+        lo, hi = self.own_block_range()
+        def gather(t, per_block):
+            unit = 1 if per_block else 256
+            keep = torch.zeros_like(t)
+            keep[lo * unit:hi * unit] = t[lo * unit:hi * unit]
+            dist.all_reduce(keep)
+            t.copy_(keep)
+        gather(opt.m, False); gather(opt.v, False)
+        if opt.kind == "atom":
+            for t in (opt.gprev_blk, opt.pnode_blk, opt.trust_blk):
+                gather(t, True)
 
     def broadcast_parameters(self) -> None:
         """Every rank starts from rank 0's weights and buffers (what DDP does at construction)."""

@@ -209,6 +209,7 @@ class TrainEngine:
         """Object whose ``state_dict()`` is the optimizer state to save.  In sharded mode this completes the fp32
         master parameters and assembles the full moments (collectives: call on every rank)."""
         if self.sync.shard is None:
+            self.sync.gather_optimizer_state(self.opt)        # no-op unless the fused NVLink step owns the update
             return self.opt
         self.complete_master()
         sd = self.opt.state_dict()

@@ -114,7 +114,10 @@ def main():
         return tensor_parallel_case(out, dev, world, rank)
     cfg = Config(**CFG)
     model = Model(cfg).to(dev)
-    eng = TrainEngine(cfg, model, dev, optimizer="adamw", grad_sync=mode)
+    optimizer = "adamw"
+    if mode.endswith("+atom"):
+        mode, optimizer = mode.split("+")[0], "atom"
+    eng = TrainEngine(cfg, model, dev, optimizer=optimizer, grad_sync=mode)
     src = SyntheticTokens(cfg.vocab, 2, cfg.seq_len, seed=3, rank=rank, pool=4, pin=False)
     losses = [float(eng.step(src.next())) for _ in range(4)]
     if dev.type == "cuda":

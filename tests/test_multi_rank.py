@@ -71,3 +71,16 @@ def test_tensor_parallel_fused_gemms(tmp_path):
     res = _launch("tp", str(tmp_path / "tp.pt"), "cuda", 2, 29617)
     assert res["all_ranks_ok"], res
     print("tensor-parallel fused GEMMs:", {k: v for k, v in res.items()})
+
+
+@pytest.mark.gpu
+def test_fused_step_with_atom_matches_nccl_baseline(tmp_path):
+    """ATOM applied to the shard inside the fused NVLink exchange equals all-reduce + replicated ATOM."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    a = _launch("collective+atom", str(tmp_path / "nccl_atom.pt"), "cuda", 2, 29618)
+    b = _launch("p2p+atom", str(tmp_path / "p2p_atom.pt"), "cuda", 2, 29619)
+    assert a["same"] and b["same"]
+    diff = (a["params"] - b["params"]).abs()
+    assert float(diff.mean()) < 5e-5, float(diff.mean())
+    assert abs(a["losses"][-1] - b["losses"][-1]) < 5e-2
