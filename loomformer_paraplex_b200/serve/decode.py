@@ -12,6 +12,7 @@ Prefill runs the prompt through the chunked fused forward once and converts its 
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -57,6 +58,16 @@ class DecodeEngine:
                 self._ns = max(1, min(16, -(-296 // (B * d.kvh))))
                 n_ws = B * d.kvh * self._ns * (2 * d.group + 2 * d.group * d.hd)
                 self._attn_ws = torch.empty(max(1, n_ws), dtype=torch.float32, device=dev)
+        # fused kernels of the training plan reused at one token per sequence (fewer, larger launches per layer)
+        self._fused = bool(self._native_attn and d.activation == "pvpowlu" and d.hidden % 2 == 0 and d.hd <= 128
+                           and d.hpq % 8 == 0 and d.n % 8 == 0 and d.n <= 1024 and not model.ablation
+                           and os.environ.get("LOOM_DECODE_FUSED", "1") != "0")
+        if self._fused:
+            from ..ops.kernels import CudaKernels
+            self._K = CudaKernels(defer_wgrad=False)
+            self._hk = z(2 * L, B, d.qh, d.hd)
+            self._hv = z(2 * L, B, d.qh, d.hd)
+            self._qkc = z(B, 3, d.qh, d.hd)
         self.refresh_weights()
 
     # ------------------------------------------------------------------ weights in the compute dtype
@@ -143,6 +154,85 @@ class DecodeEngine:
         return y if bias is None else y + self.w(bias)
 
     def _step_impl(self) -> None:
+        if self._fused:
+            return self._step_fused()
+        return self._step_composed()
+
+    # ------------------------------------------------------------------ one token with the fused kernels
+    def _step_fused(self) -> None:
+        """Same arithmetic as :meth:`_step_composed` with the training plan's kernels at M = batch rows: depth reads,
+        residual-add + LayerNorm, the segmented sector GEMM, and the fused Paraplex core (gate, phase, trace, softplus,
+        PvPowLU, Tria build / compose / seed / gate readout) are one launch each."""
+        m, d, K = self.m, self.d, self._K
+        B, S, dt = self.B, self.S, self.dt
+        pos = self.pos
+        h = self.w(m.emb.weight)[self.tok_in]
+        cos = m.rope_cos.index_select(0, pos).to(dt).view(1, 1, d.hd)
+        sin = m.rope_sin.index_select(0, pos).to(dt).view(1, 1, d.hd)
+        da = m.depth_attn
+        hk, hv, qkc = self._hk, self._hv, self._qkc
+        from ..ops import native
+
+        def project(x, slot):
+            kv = self._lin(x, da.kv_weight)
+            k, v = kv[:, :d.n].view(B, d.qh, d.hd), kv[:, d.n:].view(B, d.qh, d.hd)
+            if d.depth_qkv_rms:
+                k, v = K.fixed_rms_fwd(k, FANIN_GAIN), K.fixed_rms_fwd(v, FANIN_GAIN * d.deepnorm_beta)
+            hk[slot].copy_(k); hv[slot].copy_(v)
+
+        def read(sub):
+            mm, _ = K.dread_fwd(d, da.query(sub).float(), hk, hv, sub + 1)
+            w_o = self.w(da.w_o_weight)[sub] if da.w_o is None else self.w(da.w_o.weight)
+            return F.linear(mm.view(B, d.n), w_o), mm
+
+        cap = d.branch_rms_cap if (d.branch_rms_cap is not None and m.decode_applies_rms_cap) else None
+        is_bos = pos.eq(0)
+        row_reset = is_bos.expand(B).contiguous()
+        seed_valid = self.pending & ~is_bos & self.have_carry
+        use_tria = d.tria
+        c_planes, p_in = None, None
+        project(h, 0)
+        for bi, blk in enumerate(m.blocks):
+            last = bi == d.layers - 1
+            sub = 2 * bi
+            qkv = self._lin(h, blk.attn.qkv_weight)
+            qkc[:, 0].copy_(R.apply_rope(qkv[:, :d.n].view(B, d.qh, d.hd), cos, sin))
+            k = R.apply_rope(qkv[:, d.n:d.n + d.kv_dim].view(B, d.kvh, d.hd), cos, sin)
+            self.kc[bi].index_copy_(1, pos, k.unsqueeze(1))
+            self.vc[bi].index_copy_(1, pos, qkv[:, d.n + d.kv_dim:].view(B, d.kvh, d.hd).unsqueeze(1))
+            native.ext().decode_attn(qkc[:, 0], self.kc[bi], self.vc[bi], pos, qkc[:, 2], qkc[:, 1], self._attn_ws, B, S,
+                                     d.qh, d.kvh, d.hd, self._ns)
+            native.count(2 if self._ns > 1 else 1)
+            attn_out = self._lin(qkc[:, 2].reshape(B, d.n), blk.attn.o.weight)
+            skip, _ = read(sub)
+            u = K.add_ln_fwd(skip, attn_out, blk.ln_attn.weight.data, blk.ln_attn.bias.data, cap)[0]
+            project(u, sub + 1)
+            skip2, d_sel = read(sub + 1)
+            ffn = blk.ffn
+            wx = self._lin(u, ffn.w1_real.weight)
+            gate_lin = self._lin(u, ffn.gate_proj.weight, ffn.gate_proj.bias) if ffn.gate_proj is not None else None
+            beta_lin = K.imag_fwd(d, qkc, u, d_sel, self.w(ffn.w1_imag))
+            tria_here = use_tria
+            core = K.ffn_core_fwd(
+                d, wx, p_in if ffn.identity_gate is not None else None,
+                ffn.identity_gate.alpha() if ffn.identity_gate is not None else None, ffn.w1_real.bias.data, gate_lin, beta_lin,
+                ffn.w1_imag_bias.data, ffn.w1_imag_trace.data, self.trace[bi], row_reset, None,
+                c_planes if bi > 0 else None, self.carry.view(B, d.hidden, 9) if (tria_here and bi == 0) else None,
+                seed_valid if (tria_here and bi == 0) else None,
+                ffn.gate_selector.weights().float() if (tria_here and not last) else None,
+                (bi % 3) if tria_here else None, m.tria_alpha if tria_here else 0.0, B)
+            self.trace[bi].copy_(core["trace_out"])
+            if tria_here:
+                c_planes = core["c"]
+                p_in = None if last else core["p_out"]
+            f = self._lin(core["o"], ffn.w2.weight, ffn.w2.bias)
+            h = K.add_ln_fwd(skip2, f, blk.ln_ffn.weight.data, blk.ln_ffn.bias.data, cap)[0]
+            if not last:
+                project(h, sub + 2)
+        carry_c = c_planes.float().permute(1, 2, 0).reshape(B, d.hidden, 3, 3) if use_tria else None
+        self._finish_step(h, carry_c, is_bos)
+
+    def _step_composed(self) -> None:
         m, d = self.m, self.d
         B, S, dt = self.B, self.S, self.dt
         pos = self.pos                                   # [1]
@@ -245,6 +335,14 @@ class DecodeEngine:
             if not last:
                 kh, vh = project(h)
                 hist_k.append(kh); hist_v.append(vh)
+        self._finish_step(h, carry_c if use_tria else None, is_bos)
+
+    def _finish_step(self, h, carry_c, is_bos) -> None:
+        """Temporal endpoint, boundary-key append, final cross attention, head."""
+        m, d = self.m, self.d
+        B, S, dt = self.B, self.S, self.dt
+        pos = self.pos
+        use_tria = carry_c is not None
         if use_tria:
             reset_now = self.pending | is_bos | (not d.tria_temporal) | ~self.have_carry
             cont = R.normalize9(torch.matmul(carry_c, self.carry))
