@@ -261,11 +261,17 @@ void dread(bool bwd, torch::Tensor q, torch::Tensor hk, torch::Tensor hv, torch:
 }
 
 void add_ln_fwd(torch::Tensor a, torch::Tensor b, torch::Tensor w, torch::Tensor bias, torch::Tensor y, torch::Tensor x,
-                torch::Tensor mean, torch::Tensor rstd, int64_t M, int64_t N, double eps) {
+                torch::Tensor mean, torch::Tensor rstd, int64_t M, int64_t N, double eps, double cap) {
   const c10::cuda::CUDAGuard guard(a.device());
   int rc = loom_add_ln_fwd(a.data_ptr(), b.data_ptr(), fptr(w), fptr(bias), y.data_ptr(), x.data_ptr(), fptr(mean),
-                           fptr(rstd), (int)M, (int)N, (float)eps, cur_stream());
+                           fptr(rstd), (int)M, (int)N, (float)eps, (float)cap, cur_stream());
   TORCH_CHECK(rc == 0, "loom_add_ln_fwd failed: ", rc);
+}
+
+void cap_bwd(torch::Tensor dy, torch::Tensor a, torch::Tensor da, int64_t M, int64_t N, double cap) {
+  const c10::cuda::CUDAGuard guard(a.device());
+  int rc = loom_cap_bwd(dy.data_ptr(), a.data_ptr(), da.data_ptr(), (int)M, (int)N, (float)cap, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_cap_bwd failed: ", rc);
 }
 
 void add_ln_bwd(torch::Tensor dy, torch::Tensor x, torch::Tensor mean, torch::Tensor rstd, torch::Tensor w,
@@ -402,6 +408,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("dread_stage", &dread_stage, "store a sublayer's read gradient (bf16) and its <dm, m> row scalars");
   m.def("dread_slot_bwd", &dread_slot_bwd, "gradient of one history slot over every sublayer that read it");
   m.def("add_ln_fwd", &add_ln_fwd, "residual add + LayerNorm");
+  m.def("cap_bwd", &cap_bwd, "backward of the per-row RMS cap");
   m.def("add_ln_bwd", &add_ln_bwd, "residual add + LayerNorm backward");
   m.def("colsum", &colsum, "column sums into an fp32 accumulator");
   m.def("ce", &ce, "cross-entropy over bf16 logits with in-place gradient");

@@ -107,6 +107,44 @@ __global__ void rope_bwd_kernel(const bf16* __restrict__ dq_attn, const bf16* __
   }
 }
 
+// Backward of the RMS cap y = s a, s = min(1, cap / rms(a)):  da = dy where the row is not clipped, else
+// da = s (dy - a <a, dy> / (N (mean(a^2) + 1e-6))).  One warp per row.
+template <int NCH>
+__global__ void __launch_bounds__(256) cap_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ a,
+                                                      bf16* __restrict__ da, int M, int N, float cap) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  float fa[NCH][8], g[NCH][8], q = 0.f, dot = 0.f;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int col = (lane + 32 * c) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { fa[c][i] = 0.f; g[c][i] = 0.f; }
+    if (col < N) {
+      unpack8(*reinterpret_cast<const uint4*>(a + (long long)row * N + col), fa[c]);
+      unpack8(*reinterpret_cast<const uint4*>(dy + (long long)row * N + col), g[c]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { q += fa[c][i] * fa[c][i]; dot += fa[c][i] * g[c][i]; }
+    }
+  }
+  const float ms = warp_sum(q) / N + 1e-6f;
+  dot = warp_sum(dot);
+  const float s = cap * rsqrtf(ms);
+  const bool clipped = s < 1.f;
+  const float k = clipped ? dot / (N * ms) : 0.f;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int col = (lane + 32 * c) * 8;
+    if (col < N) {
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = clipped ? s * (g[c][i] - fa[c][i] * k) : g[c][i];
+      *reinterpret_cast<uint4*>(da + (long long)row * N + col) = pack8(o);
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------------------------
 // Depth-attention read.  G lanes (G = power of two >= HD/8) own one (row, head); each lane holds 8 dims.
 // hist_k / hist_v: [S, M, QH, HD] bf16;  q: [QH, HD] fp32;  out: [M, QH, HD] bf16;  lse: [M, QH] fp32.
@@ -253,17 +291,36 @@ __global__ void __launch_bounds__(256) dread_bwd_kernel(const float* __restrict_
 // y = LayerNorm(a + b) * w + bias.  One warp per row, NCH 16-byte chunks per lane (N <= 256*NCH).
 // The pre-norm sum is rounded to bf16 first (it is what the backward pass re-reads).
 // ----------------------------------------------------------------------------------------------
+// cap > 0: each addend is first shrunk to an RMS of at most `cap` (never amplified): x = s_a a + s_b b with
+// s = min(1, cap / sqrt(mean(.^2) + 1e-6)).
 template <int NCH>
 __global__ void __launch_bounds__(256) add_ln_fwd_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b,
                                                          const float* __restrict__ w, const float* __restrict__ bias,
                                                          bf16* __restrict__ y, bf16* __restrict__ x,
                                                          float* __restrict__ mean, float* __restrict__ rstd, int M, int N,
-                                                         float eps) {
+                                                         float eps, float cap) {
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= M) return;
   float v[NCH][8];
   float sum = 0.f;
+  float sa = 1.f, sb = 1.f;
+  if (cap > 0.f) {
+    float qa = 0.f, qb = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = (lane + 32 * c) * 8;
+      if (col < N) {
+        float fa[8], fb[8];
+        unpack8(*reinterpret_cast<const uint4*>(a + (long long)row * N + col), fa);
+        unpack8(*reinterpret_cast<const uint4*>(b + (long long)row * N + col), fb);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { qa += fa[i] * fa[i]; qb += fb[i] * fb[i]; }
+      }
+    }
+    sa = fminf(1.f, cap * rsqrtf(warp_sum(qa) / N + 1e-6f));
+    sb = fminf(1.f, cap * rsqrtf(warp_sum(qb) / N + 1e-6f));
+  }
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
     const int col = (lane + 32 * c) * 8;
@@ -272,7 +329,7 @@ __global__ void __launch_bounds__(256) add_ln_fwd_kernel(const bf16* __restrict_
       unpack8(*reinterpret_cast<const uint4*>(a + (long long)row * N + col), fa);
       unpack8(*reinterpret_cast<const uint4*>(b + (long long)row * N + col), fb);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) fa[i] += fb[i];
+      for (int i = 0; i < 8; ++i) fa[i] = sa * fa[i] + sb * fb[i];
       const uint4 packed = pack8(fa);
       *reinterpret_cast<uint4*>(x + (long long)row * N + col) = packed;
       unpack8(packed, v[c]);
@@ -503,12 +560,22 @@ extern "C" int loom_dread(int bwd, const float* q, const void* hk, const void* h
   return dread_launch<16>(bwd, q, hk, hv, out, lse, dm, dhk, dhv, gq, n, MQ, QH, HD, st);
 }
 
-extern "C" int loom_add_ln_fwd(const void* a, const void* b, const float* w, const float* bias, void* y, void* x,
-                               float* mean, float* rstd, int M, int N, float eps, cudaStream_t st) {
+extern "C" int loom_cap_bwd(const void* dy, const void* a, void* da, int M, int N, float cap, cudaStream_t st) {
   if (N % 8 || N > 1024) return -1;
   const unsigned grid = (M + 7) / 8;
   const int nch = (N + 255) / 256;
-#define LN_F(K) add_ln_fwd_kernel<K><<<grid, 256, 0, st>>>((const bf16*)a, (const bf16*)b, w, bias, (bf16*)y, (bf16*)x, mean, rstd, M, N, eps)
+#define CAP_B(K) cap_bwd_kernel<K><<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)a, (bf16*)da, M, N, cap)
+  if (nch == 1) CAP_B(1); else if (nch == 2) CAP_B(2); else if (nch == 3) CAP_B(3); else CAP_B(4);
+#undef CAP_B
+  return (int)cudaGetLastError();
+}
+
+extern "C" int loom_add_ln_fwd(const void* a, const void* b, const float* w, const float* bias, void* y, void* x,
+                               float* mean, float* rstd, int M, int N, float eps, float cap, cudaStream_t st) {
+  if (N % 8 || N > 1024) return -1;
+  const unsigned grid = (M + 7) / 8;
+  const int nch = (N + 255) / 256;
+#define LN_F(K) add_ln_fwd_kernel<K><<<grid, 256, 0, st>>>((const bf16*)a, (const bf16*)b, w, bias, (bf16*)y, (bf16*)x, mean, rstd, M, N, eps, cap)
   if (nch == 1) LN_F(1); else if (nch == 2) LN_F(2); else if (nch == 3) LN_F(3); else LN_F(4);
 #undef LN_F
   return (int)cudaGetLastError();

@@ -131,8 +131,10 @@ int loom_dread_slot_bwd(const float* q_all, const void* hk_slot, const void* hv_
                         int M, int QH, int HD, cudaStream_t st);
 int loom_dread(int bwd, const float* q, const void* hk, const void* hv, void* out, float* lse, const void* dm, float* dhk,
                float* dhv, float* gq, int n, long long MQ, int QH, int HD, cudaStream_t st);
+// cap > 0 shrinks each addend to an RMS of at most `cap` before the sum (cap <= 0: plain sum)
 int loom_add_ln_fwd(const void* a, const void* b, const float* w, const float* bias, void* y, void* x, float* mean,
-                    float* rstd, int M, int N, float eps, cudaStream_t st);
+                    float* rstd, int M, int N, float eps, float cap, cudaStream_t st);
+int loom_cap_bwd(const void* dy, const void* a, void* da, int M, int N, float cap, cudaStream_t st);
 int loom_add_ln_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const float* w, void* dx,
                     float* gw, float* gb, int M, int N, cudaStream_t st);
 int loom_colsum(const void* dy, float* gb, int M, int N, long long ld, cudaStream_t st);

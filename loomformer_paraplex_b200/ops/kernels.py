@@ -362,25 +362,32 @@ class _ElementwiseMixin:
     # ------------------------------------------------------------------ add + LayerNorm
     def add_ln_fwd(self, a, b, w, bias, cap, eps=1e-5):
         M, N = a.shape
-        if cap is not None or N % 8 or N > 1024 or a.dtype != torch.bfloat16:
+        if N % 8 or N > 1024 or a.dtype != torch.bfloat16:
             self.fallbacks["add_ln_fwd"] += 1
             return super().add_ln_fwd(a, b, w, bias, cap, eps)
         y, x = torch.empty_like(a), torch.empty_like(a)
         mean = torch.empty(M, dtype=torch.float32, device=a.device)
         rstd = torch.empty(M, dtype=torch.float32, device=a.device)
-        native.ext().add_ln_fwd(a.contiguous(), _bf16c(b), w, bias, y, x, mean, rstd, M, N, eps)
+        native.ext().add_ln_fwd(a.contiguous(), _bf16c(b), w, bias, y, x, mean, rstd, M, N, eps,
+                                float(cap) if cap is not None else 0.0)
         native.count()
         return y, x, mean, rstd
 
     def add_ln_bwd(self, dy, x, mean, rstd, w, gw, gb, cap, a, b):
         M, N = x.shape
-        if cap is not None or N % 8 or N > 1024 or x.dtype != torch.bfloat16:
+        if N % 8 or N > 1024 or x.dtype != torch.bfloat16:
             self.fallbacks["add_ln_bwd"] += 1
             return super().add_ln_bwd(dy, x, mean, rstd, w, gw, gb, cap, a, b)
         dx = torch.empty_like(x)
         native.ext().add_ln_bwd(_bf16c(dy), x, mean, rstd, w, dx, gw, gb, M, N)
         native.count()
-        return dx, dx
+        if cap is None:
+            return dx, dx
+        da, db = torch.empty_like(x), torch.empty_like(x)
+        native.ext().cap_bwd(dx, _bf16c(a), da, M, N, float(cap))
+        native.ext().cap_bwd(dx, _bf16c(b), db, M, N, float(cap))
+        native.count(2)
+        return da, db
 
     def colsum_add(self, dy, gb):
         dy2 = dy.reshape(-1, dy.shape[-1])

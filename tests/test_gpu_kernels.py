@@ -373,3 +373,20 @@ def test_decode_engine_graph_matches_model_step_on_gpu():
     for t in toks:                                           # same forced tokens on both engines; crosses a fire
         l1, l2 = eng.step(t).clone(), fp.step(t).clone()
         _close(l1, l2, 6e-2, "step logits")
+
+
+def test_add_layernorm_with_rms_cap():
+    ck, tk = _sets()
+    torch.manual_seed(15)
+    M, N = 200, 768
+    a, b = bf(M, N, scale=2.0), bf(M, N, scale=0.5)          # a is clipped by the cap, b is not
+    w, bias = torch.rand(N, device="cuda") + 0.5, torch.randn(N, device="cuda") * 0.1
+    y1, x1, mu1, rs1 = ck.add_ln_fwd(a, b, w, bias, 1.0)
+    y2, x2, mu2, rs2 = tk.add_ln_fwd(a.float(), b.float(), w, bias, 1.0)
+    _close(y1, y2, 2e-2, "y"); _close(x1, x2, 1e-2, "x")
+    dy = bf(M, N, scale=0.3)
+    gw1, gb1, gw2, gb2 = (torch.zeros(N, device="cuda") for _ in range(4))
+    da1, db1 = ck.add_ln_bwd(dy, x1, mu1, rs1, w, gw1, gb1, 1.0, a, b)
+    da2, db2 = tk.add_ln_bwd(dy.float(), x2, mu2, rs2, w, gw2, gb2, 1.0, a.float(), b.float())
+    _close(da1, da2, 3e-2, "da"); _close(db1, db2, 3e-2, "db"); _close(gw1, gw2, 2e-2, "gw")
+    assert not ck.fallbacks, ck.fallbacks
