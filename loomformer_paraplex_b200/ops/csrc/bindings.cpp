@@ -178,12 +178,12 @@ void decode_attn(torch::Tensor q, torch::Tensor kc, torch::Tensor vc, torch::Ten
   // outputs may be row-strided views (e.g. slices of a [B,3,QH,HD] buffer): contiguous within a sequence
   TORCH_CHECK(out_c.stride(-1) == 1 && out_k.stride(-1) == 1 && out_c.stride(0) == out_k.stride(0), "decode_attn: output layout");
   const c10::cuda::CUDAGuard guard(q.device());
-  TORCH_CHECK(q.is_contiguous() && kc.is_contiguous() && vc.is_contiguous() && pos.scalar_type() == torch::kInt64,
-              "decode_attn: contiguous bf16 operands and an int64 position");
+  TORCH_CHECK(q.stride(-1) == 1 && q.stride(1) == q.size(2) && kc.is_contiguous() && vc.is_contiguous() &&
+              pos.scalar_type() == torch::kInt64, "decode_attn: [B,QH,HD] query rows, contiguous caches, an int64 position");
   TORCH_CHECK(ws.numel() >= loom_decode_attn_workspace_floats((int)B, (int)QH, (int)KVH, (int)HD, (int)NS), "workspace too small");
   int rc = loom_decode_attn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos.data_ptr<int64_t>() ? (const long long*)pos.data_ptr<int64_t>() : nullptr,
                             out_c.data_ptr(), out_k.data_ptr(), fptr(ws), (int)B, (int)S, (int)QH, (int)KVH, (int)HD, (int)NS,
-                            (long long)out_c.stride(0), cur_stream());
+                            (long long)out_c.stride(0), (long long)q.stride(0), cur_stream());
   TORCH_CHECK(rc == 0, "loom_decode_attn failed: ", rc);
 }
 

@@ -39,7 +39,7 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float* sh) {
 __global__ void decode_attn_partial_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                                            const long long* __restrict__ pos_ptr, bf16* __restrict__ out_c,
                                            bf16* __restrict__ out_k, float* __restrict__ ws, int S, int QH, int KVH, int HD,
-                                           int NS, int cap, float scale, long long out_ld) {
+                                           int NS, int cap, float scale, long long out_ld, long long q_ld) {
   extern __shared__ float sh[];                 // q [G][HD] | s [G][cap] | red [32]
   const int G = QH / KVH;
   const int b = blockIdx.x / KVH, kvh = blockIdx.x % KVH, z = blockIdx.y;
@@ -54,7 +54,7 @@ __global__ void decode_attn_partial_kernel(const bf16* __restrict__ q, const bf1
   if (hi > n) hi = (int)n;
   const int cnt = hi > lo ? hi - lo : 0;
   for (int i = threadIdx.x; i < G * HD; i += blockDim.x)
-    sq[i] = __bfloat162float(q[((long long)b * QH + kvh * G) * HD + i]) * scale;
+    sq[i] = __bfloat162float(q[(long long)b * q_ld + (long long)kvh * G * HD + i]) * scale;
   __syncthreads();
   const long long row_stride = (long long)KVH * HD;
   const bf16* kbase = kc + ((long long)b * S * KVH + kvh) * HD;
@@ -163,9 +163,10 @@ extern "C" int loom_decode_attn_workspace_floats(int B, int QH, int KVH, int HD,
   return B * KVH * NS * (2 * G + 2 * G * HD);
 }
 
-// out_c / out_k rows of sequence b start at b * out_ld elements (out_ld = QH * HD for a dense [B,QH,HD] output)
+// q and out_c / out_k rows of sequence b start at b * q_ld resp. b * out_ld elements (QH * HD for dense [B,QH,HD])
 extern "C" int loom_decode_attn(const void* q, const void* kc, const void* vc, const long long* pos, void* out_c, void* out_k,
-                                float* ws, int B, int S, int QH, int KVH, int HD, int NS, long long out_ld, cudaStream_t st) {
+                                float* ws, int B, int S, int QH, int KVH, int HD, int NS, long long out_ld, long long q_ld,
+                                cudaStream_t st) {
   const int G = QH / KVH;
   if (HD % 8 || G < 1 || G > MAXG || QH % KVH || NS < 1) return -1;
   const int cap = (S + NS - 1) / NS;
@@ -180,7 +181,7 @@ extern "C" int loom_decode_attn(const void* q, const void* kc, const void* vc, c
   }
   dim3 grid(B * KVH, NS);
   decode_attn_partial_kernel<<<grid, threads, shm, st>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, pos, (bf16*)out_c,
-                                                         (bf16*)out_k, ws, S, QH, KVH, HD, NS, cap, rsqrtf((float)HD), out_ld);
+                                                         (bf16*)out_k, ws, S, QH, KVH, HD, NS, cap, rsqrtf((float)HD), out_ld, q_ld);
   if (NS > 1) decode_attn_merge_kernel<<<B * KVH, threads, 0, st>>>(ws, (bf16*)out_c, (bf16*)out_k, QH, KVH, HD, NS, out_ld);
   return (int)cudaGetLastError();
 }
