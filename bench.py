@@ -189,8 +189,20 @@ def run_ours(args):
     cfg = Config(**kw)
     torch.manual_seed(cfg.seed)
     model = Model(cfg).to(dev)
-    sync = "collective" if args.grad_sync == "auto" else args.grad_sync
-    engine = TrainEngine(cfg, model, dev, optimizer=args.optimizer, grad_sync=sync)
+    # auto: one GPU needs no exchange; several GPUs use the fused NVLink step (reduce-scatter + optimizer + all-gather
+    # over peer memory) and fall back to the NCCL all-reduce only if peer-mapped buffers cannot be set up here
+    sync = ("p2p" if world > 1 else "collective") if args.grad_sync == "auto" else args.grad_sync
+    try:
+        engine = TrainEngine(cfg, model, dev, optimizer=args.optimizer, grad_sync=sync)
+    except Exception as e:
+        if args.grad_sync != "auto" or sync == "collective":
+            raise
+        print(f"[bench] fused NVLink step unavailable ({type(e).__name__}: {e}); using the NCCL all-reduce", file=sys.stderr)
+        sync = "collective"
+        torch.manual_seed(cfg.seed)
+        model = Model(cfg).to(dev)
+        engine = TrainEngine(cfg, model, dev, optimizer=args.optimizer, grad_sync=sync)
+    args.grad_sync = sync
     state = {"i": 0}
     loss_host = torch.zeros((), dtype=torch.float32).pin_memory()
     if args.workload == "sft":
