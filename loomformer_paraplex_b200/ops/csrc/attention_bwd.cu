@@ -196,12 +196,22 @@ __global__ void __launch_bounds__(THREADS, 1) attn_bwd_kernel(const __grid_const
         tmem_ld_wait();
         const int key0 = j * BKEY + c * 32;
         float pr[32], ds[32];
+        // groups entirely at or below the diagonal with no segment ids need no per-element mask test (all groups
+        // except those of the chunk's own key block)
+        if (row_ok && !segrow && key0 + 31 <= qpos) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = key0 + i;
-          const bool al = row_ok && key <= qpos && (!segrow || segrow[key] == my_seg);
-          pr[i] = al ? exp2f(__uint_as_float(sv[i]) * p.scale_log2e - lse2) : 0.f;
-          ds[i] = pr[i] * (__uint_as_float(dv[i]) - delta) * p.scale;
+          for (int i = 0; i < 32; ++i) {
+            pr[i] = exp2f(fmaf(__uint_as_float(sv[i]), p.scale_log2e, -lse2));
+            ds[i] = pr[i] * p.scale * (__uint_as_float(dv[i]) - delta);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + i;
+            const bool al = row_ok && key <= qpos && (!segrow || segrow[key] == my_seg);
+            pr[i] = al ? exp2f(fmaf(__uint_as_float(sv[i]), p.scale_log2e, -lse2)) : 0.f;
+            ds[i] = pr[i] * (__uint_as_float(dv[i]) - delta) * p.scale;
+          }
         }
         uint8_t* dp = sP + (c >> 1) * TILE;
         uint8_t* dd = sDS + (c >> 1) * TILE;

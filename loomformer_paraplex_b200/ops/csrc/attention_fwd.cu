@@ -176,21 +176,48 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_kernel(const __grid_const
           tmem_ld_32x32(tS[sc & 1] + lane_off + c * 32, v);
           tmem_ld_wait();
           const int key0 = j * BKEY + c * 32;
+          // every key of this 32-column group is visible to this row (no segment ids, group entirely at or below
+          // the diagonal): no per-element mask test.  True for all groups except those of the chunk's own block.
+          const bool full = row_ok && !segrow && key0 + 31 <= qpos;
           if (pass == 0) {
+            if (full) {
+              float m0 = mx, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;     // four independent chains
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int key = key0 + i;
-              const bool al = row_ok && key <= qpos && (!segrow || segrow[key] == my_seg);
-              if (al) mx = fmaxf(mx, __uint_as_float(v[i]));
+              for (int i = 0; i < 32; i += 4) {
+                m0 = fmaxf(m0, __uint_as_float(v[i])); m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
+                m2 = fmaxf(m2, __uint_as_float(v[i + 2])); m3 = fmaxf(m3, __uint_as_float(v[i + 3]));
+              }
+              mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const int key = key0 + i;
+                const bool al = row_ok && key <= qpos && (!segrow || segrow[key] == my_seg);
+                if (al) mx = fmaxf(mx, __uint_as_float(v[i]));
+              }
             }
           } else {
             float pr[32];
+            const float mxs = mx * p.scale_log2e;
+            if (full) {
+              float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int key = key0 + i;
-              const bool al = row_ok && key <= qpos && (!segrow || segrow[key] == my_seg);
-              pr[i] = al ? exp2f((__uint_as_float(v[i]) - mx) * p.scale_log2e) : 0.f;
-              l += pr[i];
+              for (int i = 0; i < 32; i += 4) {
+                pr[i] = exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2e, -mxs));
+                pr[i + 1] = exp2f(fmaf(__uint_as_float(v[i + 1]), p.scale_log2e, -mxs));
+                pr[i + 2] = exp2f(fmaf(__uint_as_float(v[i + 2]), p.scale_log2e, -mxs));
+                pr[i + 3] = exp2f(fmaf(__uint_as_float(v[i + 3]), p.scale_log2e, -mxs));
+                l0 += pr[i]; l1 += pr[i + 1]; l2 += pr[i + 2]; l3 += pr[i + 3];
+              }
+              l += (l0 + l1) + (l2 + l3);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const int key = key0 + i;
+                const bool al = row_ok && key <= qpos && (!segrow || segrow[key] == my_seg);
+                pr[i] = al ? exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2e, -mxs)) : 0.f;
+                l += pr[i];
+              }
             }
             uint8_t* dst = sP + (c >> 1) * TILE;
 #pragma unroll

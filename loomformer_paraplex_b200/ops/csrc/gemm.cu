@@ -22,6 +22,7 @@
 // This kernel replaces the library GEMMs of the reference (F.linear / cublasGemmStridedBatchedEx,
 // reference kernels/beta_space/beta_space_launcher.cu:57-151) and its operand pack/unpack kernels
 // (beta_space_kernel.cuh:86-271): nothing is gathered or scattered through global memory.
+#include <stdlib.h>
 #include "sm100.cuh"
 #include "tma_host.h"
 #include "loom_c_api.h"
@@ -112,6 +113,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_kernel(const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch: everything above touches only this CTA's shared memory and TMEM, so it may run
+  // while the previous kernel of the stream is still finishing.  From here on global memory is read and written:
+  // wait until every prerequisite grid has completed and its writes are visible (no-op for an ordinary launch),
+  // then let the next kernel of the stream start its own prologue early.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const int tiles_m = (p.M + BM - 1) / BM;
   const int tiles_n = (p.n_per_head + BN - 1) / BN;
@@ -338,6 +345,17 @@ int launch(const Params& p, int sms, cudaStream_t stream) {
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.n_per_head + BN - 1) / BN) * p.heads;
   const int grid = tiles < sms ? tiles : sms;
+  static int pdl = -1;          // LOOM_PDL=0 turns programmatic dependent launch off
+  if (pdl < 0) { const char* e = getenv("LOOM_PDL"); pdl = (e != nullptr && e[0] == '0') ? 0 : 1; }
+  if (pdl) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(NUM_THREADS); cfg.dynamicSmemBytes = C::SMEM; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, gemm_kernel<BN, A_MN, B_MN, GATHER>, p);
+  }
   gemm_kernel<BN, A_MN, B_MN, GATHER><<<grid, NUM_THREADS, C::SMEM, stream>>>(p);
   return (int)cudaGetLastError();
 }
