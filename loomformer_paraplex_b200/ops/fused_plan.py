@@ -27,6 +27,8 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
+from ..utils.tracing import span
+
 from ..config import FANIN_GAIN
 from .twins import TorchKernels
 
@@ -152,8 +154,9 @@ class FusedPlan:
             seed, seed_valid = None, None
             if chunked and temporal is not None:
                 seed, seed_valid = temporal, fire[:, s - 1] & ~reset[:, s]
-            tape = self._chunk_forward(h_emb[:, s:e], cos_all[:, s:e], sin_all[:, s:e], tok_reset[:, s:e], seg,
-                                       s, e, kc, vc, traces, seed, seed_valid, training, want_grad)
+            with span(f"chunk_fwd[{s}:{e}]"):
+                tape = self._chunk_forward(h_emb[:, s:e], cos_all[:, s:e], sin_all[:, s:e], tok_reset[:, s:e], seg,
+                                           s, e, kc, vc, traces, seed, seed_valid, training, want_grad)
             traces = tape["trace_out"]
             tape.update(s=s, e=e, seed=seed, seed_valid=seed_valid, temporal_in=temporal, fired=None,
                         has_endpoint=False, key_index=None)
@@ -233,7 +236,8 @@ class FusedPlan:
                     dtemporal = None
             else:
                 dtemporal = None
-            dx, dtraces, dseed = self._chunk_backward(tape, dh[:, s:e], ddepth, dtraces, kc, vc, dkc, dvc, seg)
+            with span(f"chunk_bwd[{s}:{e}]"):
+                dx, dtraces, dseed = self._chunk_backward(tape, dh[:, s:e], ddepth, dtraces, kc, vc, dkc, dvc, seg)
             d_emb[:, s:e] = dx.view(B, e - s, d.n)
             if dseed is not None:
                 dtemporal = dseed if dtemporal is None else dtemporal + dseed

@@ -175,8 +175,16 @@ def train(cfg: Config, dataset: str, device: torch.device, ckpt_out: Optional[st
     log_every = max(1, int(cfg.log_every))
     eval_every = log_every if cfg.eval_every is None else max(1, int(cfg.eval_every))
     data_wait, step, tokens_at_log, t_log = 0.0, start_step, tokens_seen, time.time()
+    # multi-rank runs: notice a rank that disappeared on the host, before the next launch, instead of inside a
+    # collective (LOOM_HEARTBEAT=0 turns the check off)
+    hb = None
+    if world > 1 and os.environ.get("LOOM_HEARTBEAT", "1") != "0":
+        from ..parallel.health import Heartbeat
+        hb = Heartbeat(interval=1.0, max_silence=float(os.environ.get("LOOM_HEARTBEAT_SILENCE", "90")))
     with GracefulInterrupt() as intr, RunpointWatcher() as rp:
         for step in range(start_step + 1, int(cfg.steps) + 1):
+            if hb is not None:
+                hb.check()
             if intr.requested:
                 flag = 0
                 if pdist.is_main():
