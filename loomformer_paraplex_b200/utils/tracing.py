@@ -26,7 +26,7 @@ FAMILIES = (("GEMMs (gemm_kernel: forward, data gradient, grouped weight gradien
             ("RoPE / cache write", ("rope_",)),
             ("readout (slot pool, sparse cross attention)", ("slot_pool", "cross_attn")),
             ("optimizer / gradient norm", ("adamw_flat", "atom_flat", "sumsq", "norm_finalize", "rs_reduce", "update_allgather")),
-            ("cross-entropy", ("ce_kernel",)))
+            ("cross-entropy", ("::ce_kernel",)))
 
 
 @contextlib.contextmanager
