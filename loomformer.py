@@ -161,7 +161,7 @@ def main() -> None:
         assert dataset, "--train needs --dataset or train_dataset in config"
         sync = args.grad_sync
         if sync == "auto":
-            sync = "p2p" if (world > 1 and dev.type == "cuda" and str(cfg.optimizer).lower() == "adamw") else "collective"
+            sync = "p2p" if (world > 1 and dev.type == "cuda") else "collective"      # fused NVLink step (AdamW and ATOM)
         res = train(cfg, dataset, dev, args.checkpoint or "loomformer.pt", args.ablation,
                     args.resume if args.resume is not None else cfg.resume, args.resume_step, grad_sync=sync)
         pdist.rank0_print("\nSummary:")
