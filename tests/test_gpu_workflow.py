@@ -63,3 +63,37 @@ def test_cli_workflows_on_gpu(tmp_path):
     out = run([os.path.join(ROOT, "loomchat.py"), "s.aio", "--device", "cuda:0", "--temperature", "0", "--max-new", "6"], d,
               stdin="/settings\nthe quick brown\n/exit\n")
     assert "loom>" in out and "temperature" in out
+
+
+@pytest.mark.parametrize("sync", ["p2p", "fsdp"])
+def test_cli_multi_gpu_training_saves_complete_checkpoints(tmp_path, sync):
+    """`--device cudas` self-launches one rank per GPU; the fused / sharded gradient paths write checkpoints whose
+    parameters and optimizer moments are complete (owners' shards gathered), and resume continues from them."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    d = str(tmp_path)
+    os.makedirs(os.path.join(d, "data"))
+    rng = np.random.default_rng(0)
+    with open(os.path.join(d, "data", "a.jsonl"), "w") as fh:
+        for _ in range(400):
+            fh.write(json.dumps({"text": " ".join(rng.choice(WORDS, 70))}) + "\n")
+    cfg = dict(vocab=320, tokenizer="tok.json", tied_embeddings=False, seq_len=256, batch_size=4, model_dim=128, n_q_heads=4,
+               head_dim=32, n_kv_heads=2, hidden=None, hidden_mult=4.0, layers=2, activation="pvpowlu",
+               phase_grad_mode="secant", tria_carry_enabled=True, tria_temporal_auto=False, tria_temporal_window=64,
+               tria_carrier_alpha=0.05, steps=8, lr=2e-3, warmup_steps=2, log_every=2, eval_every=4, eval_batches=1,
+               save_every=4, device="cuda:0,cuda:1", dataset_format="jsonl", train_dataset="data", auto_val_split_pct=5.0,
+               prefetch_batches=4, gpu_prefetch_batches=2, optimizer="adamw", amp_dtype="bf16")
+    with open(os.path.join(d, "cfg.yaml"), "w") as fh:
+        yaml.safe_dump(cfg, fh)
+    loom = os.path.join(ROOT, "loomformer.py")
+    run([loom, "--train-tokenizer", "data", "--tokenizer-out", "tok.json", "--vocab", "320", "--config", "cfg.yaml"], d)
+    out = run([loom, "--train", "--config", "cfg.yaml", "--checkpoint", "m.pt", "--grad-sync", sync], d)
+    assert "step      8" in out, out[-2000:]
+    blob = torch.load(os.path.join(d, "m.pt"), weights_only=True)
+    assert all(torch.isfinite(v).all() for v in blob["model"].values() if torch.is_tensor(v) and v.is_floating_point())
+    st = blob["optimizer"]["state"]
+    moved = [float(s["exp_avg_sq"].abs().sum()) > 0 for s in st.values() if s["exp_avg_sq"].numel() > 4096]
+    assert moved and all(moved)                   # no big tensor is left with another rank's (zero) moments
+    out = run([loom, "--train", "--config", "cfg.yaml", "--checkpoint", "m2.pt", "--resume", "m.runpoint_step4.pt",
+               "--grad-sync", sync], d)
+    assert "continuing from step 4/8" in out
