@@ -255,3 +255,22 @@ def test_replica_pool_serves_in_order_and_detects_a_dead_replica(packed):
             pool.generate(prompts[:4], 2, timeout=3.0)
     with pytest.raises(RuntimeError):
         ReplicaPool(str(d / "missing.pt"), ["cpu"], batch=1, start_timeout=60)
+
+
+def test_export_package_reproduces_the_forward(tmp_path):
+    """`--export-aoti` route: the saved program (AOTInductor package or ExportedProgram) runs without model code."""
+    from loomformer_paraplex_b200.serve.runtime import export_package
+    cfg = Config(vocab=256, seq_len=32, model_dim=32, n_q_heads=4, n_kv_heads=2, hidden=64, layers=2, activation="pvpowlu",
+                 tria_carry_enabled=True, tria_temporal_auto=False, tria_temporal_window=16)
+    torch.manual_seed(0)
+    model = Model(cfg).eval()
+    ckpt.save_checkpoint(str(tmp_path / "e.pt"), cfg, model, None, "adamw", 0, 0)
+    path = export_package(str(tmp_path / "e.pt"), str(tmp_path / "e.pt2"), torch.device("cpu"))
+    x = torch.randint(0, 256, (1, 32))
+    with torch.no_grad():
+        want = model(x)
+    try:
+        got = torch.export.load(path).module()(x)
+    except Exception:
+        got = torch._inductor.aoti_load_package(path)(x)
+    assert torch.allclose(got, want, atol=1e-4)
