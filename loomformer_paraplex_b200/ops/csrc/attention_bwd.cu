@@ -198,7 +198,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_bwd_kernel(const __grid_const
         float pr[32], ds[32];
         // groups entirely at or below the diagonal with no segment ids need no per-element mask test (all groups
         // except those of the chunk's own key block)
-        if (row_ok && !segrow && key0 + 31 <= qpos) {
+        bool full = row_ok && key0 + 31 <= qpos;
+        if (full && segrow) full = segrow[key0] == my_seg && segrow[key0 + 31] == my_seg;   // ids form contiguous runs
+        if (full) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             pr[i] = exp2f(fmaf(__uint_as_float(sv[i]), p.scale_log2e, -lse2));

@@ -176,9 +176,13 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_kernel(const __grid_const
           tmem_ld_32x32(tS[sc & 1] + lane_off + c * 32, v);
           tmem_ld_wait();
           const int key0 = j * BKEY + c * 32;
-          // every key of this 32-column group is visible to this row (no segment ids, group entirely at or below
-          // the diagonal): no per-element mask test.  True for all groups except those of the chunk's own block.
-          const bool full = row_ok && !segrow && key0 + 31 <= qpos;
+          // every key of this 32-column group is visible to this row (group entirely at or below the diagonal and in
+          // the row's own segment): no per-element mask test.  True for most groups outside the chunk's own block.
+          // With segment ids the group is fully visible when its first and last key carry this row's id: every id
+          // occupies one contiguous run of the sequence (documents and packed examples do), so equal end points
+          // mean a uniform group.
+          bool full = row_ok && key0 + 31 <= qpos;
+          if (full && segrow) full = segrow[key0] == my_seg && segrow[key0 + 31] == my_seg;
           if (pass == 0) {
             if (full) {
               float m0 = mx, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;     // four independent chains

@@ -150,7 +150,9 @@ int loom_temporal_bwd(const void* depth, const uint8_t* reset, const float* stat
 
 // ---- dual-context attention (attention_fwd.cu / attention_bwd.cu) ----
 // qkc [B*Tc, 3, QH, HD] bf16 (sector 0 = rotated queries, 1 = A@K, 2 = A@V); caches [B, T, KVH, HD] bf16;
-// lse [B, QH, Tc] fp32; seg [B, T] int32 or null.  The chunk's queries sit at absolute positions [s, e).
+// lse [B, QH, Tc] fp32; seg [B, T] int32 or null (tokens attend only within their own id; every id must occupy one
+// contiguous run of the sequence, as document counters and packed-example indices do).  The chunk's queries sit at
+// absolute positions [s, e).
 // Backward: dqkc same layout as qkc (sectors 1, 2 are read); dq_attn [B*Tc, QH, HD] bf16 out;
 // dk_heads / dv_heads [B, T, QH, HD] fp32 are per-query-head key/value gradient slabs (+=, no atomics).
 typedef struct {
