@@ -231,32 +231,44 @@ void rms_norm(bool bwd, c10::optional<torch::Tensor> dy, torch::Tensor x, torch:
 }
 
 void dread_stage(torch::Tensor a, c10::optional<torch::Tensor> b, torch::Tensor mo, torch::Tensor dm, torch::Tensor dd,
-                 int64_t MQ, int64_t HD) {
+                 torch::Tensor lse_in, torch::Tensor lse_out, int64_t MQ, int64_t HD) {
   const c10::cuda::CUDAGuard guard(a.device());
-  TORCH_CHECK(a.is_contiguous() && mo.is_contiguous() && dm.is_contiguous() && (!b.has_value() || b->is_contiguous()),
+  TORCH_CHECK(a.is_contiguous() && mo.is_contiguous() && dm.is_contiguous() && (!b.has_value() || b->is_contiguous()) &&
+                  lse_in.is_contiguous() && lse_out.is_contiguous() && lse_in.numel() == MQ && lse_out.numel() == MQ,
               "dread_stage: contiguous operands");
   int rc = loom_dread_stage(a.data_ptr(), b.has_value() ? b->data_ptr() : nullptr, mo.data_ptr(), dm.data_ptr(),
-                            dd.data_ptr<float>(), MQ, (int)HD, cur_stream());
+                            dd.data_ptr<float>(), lse_in.data_ptr<float>(), lse_out.data_ptr<float>(), MQ, (int)HD,
+                            cur_stream());
   TORCH_CHECK(rc == 0, "loom_dread_stage failed: ", rc);
 }
 
 void dread_slot_bwd(torch::Tensor q_all, torch::Tensor hk, torch::Tensor hv, torch::Tensor dm_all, torch::Tensor lse_all,
                     torch::Tensor dd_all, torch::Tensor dk, torch::Tensor dv, torch::Tensor gq_all, int64_t sub0, int64_t S,
                     int64_t M, int64_t QH, int64_t HD) {
+  // hk, hv, dk, dv: [M, QH, HD] views whose rows may be strided (K and V sharing [K | V] rows)
   const c10::cuda::CUDAGuard guard(hk.device());
-  TORCH_CHECK(hk.is_contiguous() && hv.is_contiguous() && dm_all.is_contiguous() && dk.is_contiguous() && dv.is_contiguous(),
-              "dread_slot_bwd: contiguous operands");
+  auto rows_ok = [&](const torch::Tensor& t) {
+    return t.dim() == 3 && t.size(0) == M && t.stride(2) == 1 && t.stride(1) == HD && t.stride(0) >= QH * HD;
+  };
+  TORCH_CHECK(rows_ok(hk) && rows_ok(hv) && rows_ok(dk) && rows_ok(dv) && hk.stride(0) == hv.stride(0) &&
+                  dk.stride(0) == dv.stride(0) && dm_all.is_contiguous(),
+              "dread_slot_bwd: operands must be [M,QH,HD] with unit inner strides");
   int rc = loom_dread_slot_bwd(q_all.data_ptr<float>(), hk.data_ptr(), hv.data_ptr(), dm_all.data_ptr(),
                                lse_all.data_ptr<float>(), dd_all.data_ptr<float>(), dk.data_ptr(), dv.data_ptr(),
-                               gq_all.data_ptr<float>(), (int)sub0, (int)S, (int)M, (int)QH, (int)HD, cur_stream());
+                               gq_all.data_ptr<float>(), (int)sub0, (int)S, (int)M, (int)QH, (int)HD, hk.stride(0),
+                               dk.stride(0), cur_stream());
   TORCH_CHECK(rc == 0, "loom_dread_slot_bwd failed: ", rc);
 }
 
 void dread(bool bwd, torch::Tensor q, torch::Tensor hk, torch::Tensor hv, torch::Tensor out, torch::Tensor lse, OptT dm,
            OptT dhk, OptT dhv, OptT gq, int64_t n, int64_t MQ, int64_t QH, int64_t HD) {
+  // hk, hv: [slots, M, QH, HD] with unit strides inside a row; slot and row strides are taken from hk
   const c10::cuda::CUDAGuard guard(hk.device());
+  TORCH_CHECK(hk.dim() == 4 && hv.dim() == 4 && hk.stride(3) == 1 && hk.stride(2) == HD && hv.stride(3) == 1 &&
+                  hv.stride(2) == HD && hk.stride(0) == hv.stride(0) && hk.stride(1) == hv.stride(1),
+              "dread: history must be [slots,M,QH,HD] with unit inner strides and matching K/V strides");
   int rc = loom_dread(bwd, fptr(q), hk.data_ptr(), hv.data_ptr(), out.data_ptr(), fptr(lse), cp(dm), mf(dhk), mf(dhv),
-                      mf(gq), (int)n, MQ, (int)QH, (int)HD, cur_stream());
+                      mf(gq), (int)n, MQ, (int)QH, (int)HD, hk.stride(0), hk.stride(1), cur_stream());
   TORCH_CHECK(rc == 0, "loom_dread failed: ", rc);
 }
 
@@ -280,6 +292,14 @@ void add_ln_bwd(torch::Tensor dy, torch::Tensor x, torch::Tensor mean, torch::Te
   int rc = loom_add_ln_bwd(dy.data_ptr(), x.data_ptr(), fptr(mean), fptr(rstd), fptr(w), dx.data_ptr(), fptr(gw),
                            fptr(gb), (int)M, (int)N, cur_stream());
   TORCH_CHECK(rc == 0, "loom_add_ln_bwd failed: ", rc);
+}
+
+void anchor_ema(torch::Tensor bsq, double inv_n, double decay, torch::Tensor anchor, torch::Tensor snap) {
+  TORCH_CHECK(bsq.is_cuda() && anchor.is_cuda() && snap.is_cuda(), "anchor_ema: CUDA tensors expected");
+  TORCH_CHECK(bsq.scalar_type() == torch::kFloat32 && anchor.scalar_type() == torch::kFloat32 &&
+              snap.scalar_type() == torch::kFloat32, "anchor_ema: fp32 tensors expected");
+  int rc = loom_anchor_ema(fptr(bsq), (float)inv_n, (float)decay, fptr(anchor), fptr(snap), cur_stream());
+  TORCH_CHECK(rc == 0, "loom_anchor_ema failed: ", rc);
 }
 
 void colsum(torch::Tensor dy, torch::Tensor gb, int64_t M, int64_t N) {
@@ -410,6 +430,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("add_ln_fwd", &add_ln_fwd, "residual add + LayerNorm");
   m.def("cap_bwd", &cap_bwd, "backward of the per-row RMS cap");
   m.def("add_ln_bwd", &add_ln_bwd, "residual add + LayerNorm backward");
+  m.def("anchor_ema", &anchor_ema, "running radius of the imaginary pre-activation (EMA) with a snapshot");
   m.def("colsum", &colsum, "column sums into an fp32 accumulator");
   m.def("ce", &ce, "cross-entropy over bf16 logits with in-place gradient");
   m.def("temporal_fwd", &temporal_fwd, "temporal carry endpoint + PolARM");

@@ -42,7 +42,8 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 template <int G>
 __global__ void __launch_bounds__(256) dread_stage_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b,
                                                           const bf16* __restrict__ mo, bf16* __restrict__ dm,
-                                                          float* __restrict__ dd, long long MQ, int HD) {
+                                                          float* __restrict__ dd, const float* __restrict__ lse_in,
+                                                          float* __restrict__ lse_out, long long MQ, int HD) {
   const long long gid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / G;
   const int l = threadIdx.x % G;
   if (gid >= MQ) return;
@@ -66,7 +67,10 @@ __global__ void __launch_bounds__(256) dread_stage_kernel(const bf16* __restrict
   }
 #pragma unroll
   for (int o = G / 2; o > 0; o >>= 1) s += __shfl_xor_sync(mask, s, o, G);
-  if (l == 0) dd[gid] = s;
+  if (l == 0) {
+    dd[gid] = s;
+    if (lse_in) lse_out[gid] = lse_in[gid];
+  }
 }
 
 // grid: (row blocks, QH).  q_all [S,QH,HD] fp32; dm_all [S,M,QH,HD] bf16; lse_all, dd_all [S,M,QH] fp32;
@@ -77,15 +81,16 @@ __global__ void __launch_bounds__(256) dread_stage_kernel(const bf16* __restrict
 // go to shared memory.  Phase 2: the block re-maps to (sublayer, dim) pairs and adds sum_rows dsc * k into
 // per-thread registers, so the query gradients need neither shared-memory atomics nor per-row global traffic;
 // they leave the block once, at the end.
-constexpr int MAX_PAIRS = 10;      // ceil(20 sublayers * 128 dims / 256 threads)
-
-template <int G>
+// MAX_PAIRS is the number of (sublayer, dim) pairs per thread: 10 covers 20 sublayers of 128 dims, 20 covers deep and
+// narrow stacks (65 sublayers of 64 dims).
+template <int G, int MAX_PAIRS>
 __global__ void __launch_bounds__(256) dread_slot_bwd_kernel(const float* __restrict__ q_all, const bf16* __restrict__ hk,
                                                              const bf16* __restrict__ hv, const bf16* __restrict__ dm_all,
                                                              const float* __restrict__ lse_all,
                                                              const float* __restrict__ dd_all, bf16* __restrict__ dk,
                                                              bf16* __restrict__ dv, float* __restrict__ gq_all, int sub0,
-                                                             int S, int M, int QH, int HD, float scale) {
+                                                             int S, int M, int QH, int HD, float scale, long long in_ld,
+                                                             long long out_ld) {
   constexpr int NGRP = 256 / G;
   constexpr int TILE = 2 * NGRP;              // rows per tile: every group takes two
   extern __shared__ float sh[];               // [nsub][HD] queries | [TILE][nsub] dsc | [TILE][HD] k rows
@@ -113,13 +118,15 @@ __global__ void __launch_bounds__(256) dread_slot_bwd_kernel(const float* __rest
       const int m = m0 + row;
       const bool live = m < M;                 // uniform within a group
       const long long rh = (long long)(live ? m : 0) * QH + g;
-      const long long base = rh * HD + l * 8;
+      const long long base = rh * HD + l * 8;                                     // dm rows are densely packed
+      const long long hoff = (long long)g * HD + l * 8;
+      const long long ibase = (long long)(live ? m : 0) * in_ld + hoff, obase = (long long)(live ? m : 0) * out_ld + hoff;
       float kf[8], vf[8], ak[8], av[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) { kf[i] = 0.f; vf[i] = 0.f; ak[i] = 0.f; av[i] = 0.f; }
       if (act && live) {
-        unpack8(*reinterpret_cast<const uint4*>(hk + base), kf);
-        unpack8(*reinterpret_cast<const uint4*>(hv + base), vf);
+        unpack8(*reinterpret_cast<const uint4*>(hk + ibase), kf);
+        unpack8(*reinterpret_cast<const uint4*>(hv + ibase), vf);
       }
       if (act) {
 #pragma unroll
@@ -168,8 +175,8 @@ __global__ void __launch_bounds__(256) dread_slot_bwd_kernel(const float* __rest
         }
       }
       if (act && live) {
-        *reinterpret_cast<uint4*>(dk + base) = pack8(ak);
-        *reinterpret_cast<uint4*>(dv + base) = pack8(av);
+        *reinterpret_cast<uint4*>(dk + obase) = pack8(ak);
+        *reinterpret_cast<uint4*>(dv + obase) = pack8(av);
       }
     }
     __syncthreads();
@@ -198,23 +205,24 @@ __global__ void __launch_bounds__(256) dread_slot_bwd_kernel(const float* __rest
 }
 
 template <int G>
-int launch_stage(const void* a, const void* b, const void* mo, void* dm, float* dd, long long MQ, int HD, cudaStream_t st) {
+int launch_stage(const void* a, const void* b, const void* mo, void* dm, float* dd, const float* lse_in, float* lse_out,
+                 long long MQ, int HD, cudaStream_t st) {
   const long long threads = MQ * G;
   dread_stage_kernel<G><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>((const bf16*)a, (const bf16*)b, (const bf16*)mo,
-                                                                            (bf16*)dm, dd, MQ, HD);
+                                                                            (bf16*)dm, dd, lse_in, lse_out, MQ, HD);
   return (int)cudaGetLastError();
 }
 
-template <int G>
-int launch_slot(const float* q_all, const void* hk, const void* hv, const void* dm_all, const float* lse_all,
+template <int G, int MAX_PAIRS>
+int launch_slot_mp(const float* q_all, const void* hk, const void* hv, const void* dm_all, const float* lse_all,
                 const float* dd_all, void* dk, void* dv, float* gq_all, int sub0, int S, int M, int QH, int HD,
-                cudaStream_t st) {
+                long long in_ld, long long out_ld, cudaStream_t st) {
   const int nsub = S - sub0;
   constexpr int TILE = 2 * (256 / G);
-  if ((long long)nsub * HD > 256LL * MAX_PAIRS) return -2;
   const size_t shm = ((size_t)nsub * HD + (size_t)TILE * nsub + (size_t)TILE * HD) * sizeof(float);
+  if (shm > 227 * 1024) return -2;
   if (shm > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(dread_slot_bwd_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shm);
+    cudaError_t e = cudaFuncSetAttribute(dread_slot_bwd_kernel<G, MAX_PAIRS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shm);
     if (e != cudaSuccess) return (int)e;
   }
   static int sms = 0;
@@ -224,31 +232,44 @@ int launch_slot(const float* q_all, const void* hk, const void* hv, const void* 
   if (bx > need) bx = need;
   if (bx < 1) bx = 1;
   dim3 grid(bx, QH);
-  dread_slot_bwd_kernel<G><<<grid, 256, shm, st>>>(q_all, (const bf16*)hk, (const bf16*)hv, (const bf16*)dm_all, lse_all,
+  dread_slot_bwd_kernel<G, MAX_PAIRS><<<grid, 256, shm, st>>>(q_all, (const bf16*)hk, (const bf16*)hv, (const bf16*)dm_all, lse_all,
                                                    dd_all, (bf16*)dk, (bf16*)dv, gq_all, sub0, S, M, QH, HD,
-                                                   rsqrtf((float)HD));
+                                                   rsqrtf((float)HD), in_ld, out_ld);
   return (int)cudaGetLastError();
+}
+
+template <int G>
+int launch_slot(const float* q_all, const void* hk, const void* hv, const void* dm_all, const float* lse_all,
+                const float* dd_all, void* dk, void* dv, float* gq_all, int sub0, int S, int M, int QH, int HD,
+                long long in_ld, long long out_ld, cudaStream_t st) {
+  const long long pairs = (long long)(S - sub0) * HD;
+  if (pairs <= 256LL * 10)
+    return launch_slot_mp<G, 10>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, in_ld, out_ld, st);
+  if (pairs <= 256LL * 20)
+    return launch_slot_mp<G, 20>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, in_ld, out_ld, st);
+  return -2;
 }
 
 }  // namespace
 
-extern "C" int loom_dread_stage(const void* a, const void* b, const void* mo, void* dm, float* dd, long long MQ, int HD,
-                                cudaStream_t st) {
-  if (HD % 8 || HD > 128) return -1;
+extern "C" int loom_dread_stage(const void* a, const void* b, const void* mo, void* dm, float* dd, const float* lse_in,
+                                float* lse_out, long long MQ, int HD, cudaStream_t st) {
+  if (HD % 8 || HD > 128 || ((lse_in == nullptr) != (lse_out == nullptr))) return -1;
   const int chunks = HD / 8;
-  if (chunks <= 2) return launch_stage<2>(a, b, mo, dm, dd, MQ, HD, st);
-  if (chunks <= 4) return launch_stage<4>(a, b, mo, dm, dd, MQ, HD, st);
-  if (chunks <= 8) return launch_stage<8>(a, b, mo, dm, dd, MQ, HD, st);
-  return launch_stage<16>(a, b, mo, dm, dd, MQ, HD, st);
+  if (chunks <= 2) return launch_stage<2>(a, b, mo, dm, dd, lse_in, lse_out, MQ, HD, st);
+  if (chunks <= 4) return launch_stage<4>(a, b, mo, dm, dd, lse_in, lse_out, MQ, HD, st);
+  if (chunks <= 8) return launch_stage<8>(a, b, mo, dm, dd, lse_in, lse_out, MQ, HD, st);
+  return launch_stage<16>(a, b, mo, dm, dd, lse_in, lse_out, MQ, HD, st);
 }
 
 extern "C" int loom_dread_slot_bwd(const float* q_all, const void* hk, const void* hv, const void* dm_all,
                                    const float* lse_all, const float* dd_all, void* dk, void* dv, float* gq_all, int sub0,
-                                   int S, int M, int QH, int HD, cudaStream_t st) {
+                                   int S, int M, int QH, int HD, long long in_ld, long long out_ld, cudaStream_t st) {
   if (HD % 8 || HD > 128 || sub0 < 0 || sub0 >= S) return -1;
+  if (in_ld < (long long)QH * HD || out_ld < (long long)QH * HD || in_ld % 8 || out_ld % 8) return -1;
   const int chunks = HD / 8;
-  if (chunks <= 2) return launch_slot<2>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, st);
-  if (chunks <= 4) return launch_slot<4>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, st);
-  if (chunks <= 8) return launch_slot<8>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, st);
-  return launch_slot<16>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, st);
+  if (chunks <= 2) return launch_slot<2>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, in_ld, out_ld, st);
+  if (chunks <= 4) return launch_slot<4>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, in_ld, out_ld, st);
+  if (chunks <= 8) return launch_slot<8>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, in_ld, out_ld, st);
+  return launch_slot<16>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, in_ld, out_ld, st);
 }

@@ -153,7 +153,9 @@ template <int G>
 __global__ void __launch_bounds__(256) dread_fwd_kernel(const float* __restrict__ q, const bf16* __restrict__ hk,
                                                         const bf16* __restrict__ hv, bf16* __restrict__ out,
                                                         float* __restrict__ lse, int n, long long MQ, int QH, int HD,
-                                                        float scale) {
+                                                        float scale, long long slot_stride, long long row_stride) {
+  // history element (slot s, row r, head g, dim c) lives at s * slot_stride + r * row_stride + g * HD + c, which lets
+  // K and V share one buffer whose rows are the [K | V] rows the projection GEMM writes
   const long long gid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / G;
   const int l = threadIdx.x % G;
   if (gid >= MQ) return;                    // whole G-lane groups leave together
@@ -163,7 +165,8 @@ __global__ void __launch_bounds__(256) dread_fwd_kernel(const float* __restrict_
   float qv[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) qv[i] = act ? q[g * HD + l * 8 + i] * scale : 0.f;
-  const long long stride = MQ * HD, base = gid * HD + l * 8;
+  const long long base = gid * HD + l * 8;
+  const long long hbase = (gid / QH) * row_stride + (long long)g * HD + l * 8;
   float mx = -INFINITY, den = 0.f, acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
@@ -177,8 +180,8 @@ __global__ void __launch_bounds__(256) dread_fwd_kernel(const float* __restrict_
       const int s = (s0 + u < n) ? s0 + u : n - 1;
       rk[u] = make_uint4(0u, 0u, 0u, 0u); rv[u] = rk[u];
       if (act) {
-        rk[u] = *reinterpret_cast<const uint4*>(hk + s * stride + base);
-        rv[u] = *reinterpret_cast<const uint4*>(hv + s * stride + base);
+        rk[u] = *reinterpret_cast<const uint4*>(hk + s * slot_stride + hbase);
+        rv[u] = *reinterpret_cast<const uint4*>(hv + s * slot_stride + hbase);
       }
     }
 #pragma unroll
@@ -537,12 +540,14 @@ extern "C" int loom_rope_bwd(const void* dq_attn, const void* dqkc, const float*
 
 template <int G>
 static int dread_launch(int bwd, const float* q, const void* hk, const void* hv, void* out, float* lse, const void* dm,
-                        float* dhk, float* dhv, float* gq, int n, long long MQ, int QH, int HD, cudaStream_t st) {
+                        float* dhk, float* dhv, float* gq, int n, long long MQ, int QH, int HD, long long slot_stride,
+                        long long row_stride, cudaStream_t st) {
   const float scale = rsqrtf((float)HD);
   const long long threads = MQ * G;
   const unsigned grid = (unsigned)((threads + 255) / 256);
   if (!bwd) {
-    dread_fwd_kernel<G><<<grid, 256, 0, st>>>(q, (const bf16*)hk, (const bf16*)hv, (bf16*)out, lse, n, MQ, QH, HD, scale);
+    dread_fwd_kernel<G><<<grid, 256, 0, st>>>(q, (const bf16*)hk, (const bf16*)hv, (bf16*)out, lse, n, MQ, QH, HD, scale,
+                                              slot_stride, row_stride);
   } else {
     dread_bwd_kernel<G><<<grid, 256, QH * HD * sizeof(float), st>>>(q, (const bf16*)hk, (const bf16*)hv, (const bf16*)dm,
                                                                     (const bf16*)out, lse, dhk, dhv, gq, n, MQ, QH, HD, scale);
@@ -551,13 +556,17 @@ static int dread_launch(int bwd, const float* q, const void* hk, const void* hv,
 }
 
 extern "C" int loom_dread(int bwd, const float* q, const void* hk, const void* hv, void* out, float* lse, const void* dm,
-                          float* dhk, float* dhv, float* gq, int n, long long MQ, int QH, int HD, cudaStream_t st) {
+                          float* dhk, float* dhv, float* gq, int n, long long MQ, int QH, int HD, long long slot_stride,
+                          long long row_stride, cudaStream_t st) {
   if (HD % 8 || HD > 128) return -1;
+  if (slot_stride <= 0) { slot_stride = MQ * HD; row_stride = (long long)QH * HD; }     // densely packed history
+  if (slot_stride % 8 || row_stride % 8) return -1;                                    // 16-byte vector loads
+  if (bwd && (slot_stride != MQ * HD || row_stride != (long long)QH * HD)) return -1;   // the legacy backward is dense-only
   const int chunks = HD / 8;
-  if (chunks <= 2) return dread_launch<2>(bwd, q, hk, hv, out, lse, dm, dhk, dhv, gq, n, MQ, QH, HD, st);
-  if (chunks <= 4) return dread_launch<4>(bwd, q, hk, hv, out, lse, dm, dhk, dhv, gq, n, MQ, QH, HD, st);
-  if (chunks <= 8) return dread_launch<8>(bwd, q, hk, hv, out, lse, dm, dhk, dhv, gq, n, MQ, QH, HD, st);
-  return dread_launch<16>(bwd, q, hk, hv, out, lse, dm, dhk, dhv, gq, n, MQ, QH, HD, st);
+  if (chunks <= 2) return dread_launch<2>(bwd, q, hk, hv, out, lse, dm, dhk, dhv, gq, n, MQ, QH, HD, slot_stride, row_stride, st);
+  if (chunks <= 4) return dread_launch<4>(bwd, q, hk, hv, out, lse, dm, dhk, dhv, gq, n, MQ, QH, HD, slot_stride, row_stride, st);
+  if (chunks <= 8) return dread_launch<8>(bwd, q, hk, hv, out, lse, dm, dhk, dhv, gq, n, MQ, QH, HD, slot_stride, row_stride, st);
+  return dread_launch<16>(bwd, q, hk, hv, out, lse, dm, dhk, dhv, gq, n, MQ, QH, HD, slot_stride, row_stride, st);
 }
 
 extern "C" int loom_cap_bwd(const void* dy, const void* a, void* da, int M, int N, float cap, cudaStream_t st) {
@@ -592,6 +601,24 @@ extern "C" int loom_add_ln_bwd(const void* dy, const void* x, const float* mean,
     add_ln_bwd_kernel<K><<<grid, 256, shm, st>>>((const bf16*)dy, (const bf16*)x, mean, rstd, w, (bf16*)dx, gw, gb, M, N); } while (0)
   if (nch == 1) LN_B(1); else if (nch == 2) LN_B(2); else if (nch == 3) LN_B(3); else LN_B(4);
 #undef LN_B
+  return (int)cudaGetLastError();
+}
+
+// Running radius of the imaginary pre-activation: rad = max(sqrt(sum beta^2 / n), 1e-4); anchor <- decay * anchor +
+// (1 - decay) * rad; the updated value is also written to ``snap`` (what the backward of this cell will use).
+__global__ void anchor_ema_kernel(const float* __restrict__ beta_sq_sum, float inv_n, float decay, float* __restrict__ anchor,
+                                  float* __restrict__ snap) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    const float rad = fmaxf(sqrtf(*beta_sq_sum * inv_n), 1e-4f);
+    const float a = *anchor * decay + rad * (1.f - decay);
+    *anchor = a;
+    *snap = a;
+  }
+}
+
+extern "C" int loom_anchor_ema(const float* beta_sq_sum, float inv_n, float decay, float* anchor, float* snap,
+                               cudaStream_t st) {
+  anchor_ema_kernel<<<1, 32, 0, st>>>(beta_sq_sum, inv_n, decay, anchor, snap);
   return (int)cudaGetLastError();
 }
 

@@ -124,13 +124,19 @@ int loom_rms_norm_bwd(const void* dy, const void* x, const float* w, void* dx, f
                       float eps, cudaStream_t st);
 
 // depth-attention backward organised per history slot (depth_read_bwd.cu)
-int loom_dread_stage(const void* a, const void* b_or_null, const void* m_out, void* dm, float* dd, long long MQ, int HD,
-                     cudaStream_t st);
+// lse_in/lse_out (both or neither): the sublayer's log-sum-exp rows are copied into the staging buffer by the same launch
+int loom_dread_stage(const void* a, const void* b_or_null, const void* m_out, void* dm, float* dd, const float* lse_in,
+                     float* lse_out, long long MQ, int HD, cudaStream_t st);
+// in_ld / out_ld: elements between consecutive rows of hk_slot, hv_slot / of dk, dv (QH*HD when densely packed;
+// 2*QH*HD when K and V share [K | V] rows); multiples of 8
 int loom_dread_slot_bwd(const float* q_all, const void* hk_slot, const void* hv_slot, const void* dm_all,
                         const float* lse_all, const float* dd_all, void* dk, void* dv, float* gq_all, int sub0, int S,
-                        int M, int QH, int HD, cudaStream_t st);
+                        int M, int QH, int HD, long long in_ld, long long out_ld, cudaStream_t st);
+// slot_stride / row_stride: elements between history slots / rows (0, 0 = densely packed [n, M, QH, HD]); the backward
+// form takes densely packed history only
 int loom_dread(int bwd, const float* q, const void* hk, const void* hv, void* out, float* lse, const void* dm, float* dhk,
-               float* dhv, float* gq, int n, long long MQ, int QH, int HD, cudaStream_t st);
+               float* dhv, float* gq, int n, long long MQ, int QH, int HD, long long slot_stride, long long row_stride,
+               cudaStream_t st);
 // cap > 0 shrinks each addend to an RMS of at most `cap` before the sum (cap <= 0: plain sum)
 int loom_add_ln_fwd(const void* a, const void* b, const float* w, const float* bias, void* y, void* x, float* mean,
                     float* rstd, int M, int N, float eps, float cap, cudaStream_t st);
@@ -138,6 +144,8 @@ int loom_cap_bwd(const void* dy, const void* a, void* da, int M, int N, float ca
 int loom_add_ln_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const float* w, void* dx,
                     float* gw, float* gb, int M, int N, cudaStream_t st);
 int loom_colsum(const void* dy, float* gb, int M, int N, long long ld, cudaStream_t st);
+/* anchor <- decay * anchor + (1 - decay) * max(sqrt(*beta_sq_sum * inv_n), 1e-4); *snap = the updated anchor. */
+int loom_anchor_ema(const float* beta_sq_sum, float inv_n, float decay, float* anchor, float* snap, cudaStream_t st);
 int loom_ce(void* logits, const long long* targets, float* nll, const float* scale_ptr, long long M, int V,
             long long ignore_index, int write_grad, cudaStream_t st);
 

@@ -61,15 +61,15 @@ class FusedPlan:
     # copies live; the first linear layer of a run that consumes such a weight fetches it inside its GEMM
     gather_spec = None
 
-    def lin(self, x, p, bias=None):
+    def lin(self, x, p, bias=None, out=None):
         """``x @ p^T (+ bias)`` with ``p`` a parameter (not a weight tensor), fetching sharded weights on first use."""
         spec = None
         if self.gather_spec is not None and id(p) not in self._fetched:
             self._fetched.add(id(p))
             spec = self.gather_spec(p)
         if spec is None:
-            return self.K.linear(x, self.w(p), bias)
-        return self.K.linear(x, self.w(p), bias, gather=spec)
+            return self.K.linear(x, self.w(p), bias, out=out)
+        return self.K.linear(x, self.w(p), bias, gather=spec, out=out)
 
     def w(self, p: torch.Tensor) -> torch.Tensor:
         """Weight in the compute dtype (bf16 shadow on a GPU, the fp32 parameter itself on a CPU)."""
@@ -143,6 +143,10 @@ class FusedPlan:
         L = d.layers
         kc = [torch.zeros(B, T, d.kvh, d.hd, dtype=self.adt, device=dev) for _ in range(L)]
         vc = [torch.zeros(B, T, d.kvh, d.hd, dtype=self.adt, device=dev) for _ in range(L)]
+        self._step = self._step_constants(dev, want_grad)
+        if want_grad:       # accumulators the cells ask for: sum beta^2 (1), d trace [B,H], and per chunk d seed [B,H,9]
+            n_chunks = len(stops)
+            K.begin_step(n_chunks * L * (64 + B * d.hidden + 64) + n_chunks * (B * d.hidden * 9 + 64), dev)
         traces: Optional[List[torch.Tensor]] = None
         temporal = None
         tapes, h_parts, keys, key_valid, key_pos = [], [], [], [], []
@@ -243,33 +247,77 @@ class FusedPlan:
                 dtemporal = dseed if dtemporal is None else dtemporal + dseed
             tape.clear()
         self.g(m.emb.weight).index_add_(0, idx.reshape(-1), d_emb.view(B * T, d.n).float())
+        self._step_constants_bwd()
         K.flush_wgrads()
         return loss, None
+
+    # ------------------------------------------------------------------ per-step constants
+    def _step_constants(self, dev, want_grad: bool) -> Dict[str, object]:
+        """Quantities that depend on parameters only, not on the chunk: the identity-gate strength and the carrier
+        read-out weights of every layer and the depth-attention queries.  They are evaluated once per step instead
+        of once per (layer, chunk) cell, and the gradients the cells produce for them are summed in two small
+        buffers whose chain rule runs once, after the last chunk (:meth:`_step_constants_bwd`)."""
+        m, d = self.model, self.d
+        L = d.layers
+        use_tria = d.tria and not m.ablation
+        alpha, gate_w = [], []
+        for bi, blk in enumerate(m.blocks):
+            ffn = blk.ffn
+            alpha.append(ffn.identity_gate.alpha().detach() if ffn.identity_gate is not None else None)
+            gate_w.append(ffn.gate_selector.weights().detach() if (use_tria and bi != L - 1) else None)
+        st: Dict[str, object] = {"alpha": alpha, "gate_w": gate_w,
+                                 "q_all": torch.stack([self._depth_query(sub) for sub in range(2 * L)]).contiguous()}
+        if want_grad:
+            st["gsc"] = torch.zeros(L, 10, dtype=torch.float32, device=dev)      # [d alpha | d gate_w(9)] per layer
+            st["gq"] = torch.zeros(2 * L, d.qh, d.hd, dtype=torch.float32, device=dev)
+        return st
+
+    def _step_constants_bwd(self) -> None:
+        m, st = self.model, self._step
+        gsc = st["gsc"]
+        for bi, blk in enumerate(m.blocks):
+            ffn = blk.ffn
+            ig = ffn.identity_gate
+            if ig is not None and ig.raw_alpha.requires_grad:
+                self.g(ig.raw_alpha).add_((gsc[bi, 0] * ig.alpha_max * (1.0 - torch.tanh(ig.raw_alpha.data) ** 2))
+                                          .reshape(ig.raw_alpha.shape))
+            if st["gate_w"][bi] is not None and ffn.gate_selector.logits.requires_grad:
+                w9 = st["gate_w"][bi].float()
+                gw9 = gsc[bi, 1:10]
+                self.g(ffn.gate_selector.logits).add_((w9 * (gw9 - (gw9 * w9).sum())).reshape(
+                    ffn.gate_selector.logits.shape))
+        for sub in range(st["gq"].shape[0]):
+            self._depth_query_bwd(sub, st["gq"][sub])
 
     # ------------------------------------------------------------------ depth-attention helpers
     def _project_state(self, x2d, slot, hist_k, hist_v, tape_layer, key):
         """K/V projection of a residual-stream state into history slot ``slot``."""
         m, d, K = self.model, self.d, self.K
         M = x2d.shape[0]
+        if not d.depth_qkv_rms:
+            # hist_k[slot] and hist_v[slot] are the two halves of one packed [M, 2N] block
+            assert hist_k.stride(1) == 2 * d.n and hist_v.storage_offset() == hist_k.storage_offset() + d.n
+            self.lin(x2d, m.depth_attn.kv_weight, out=hist_k[slot].as_strided((M, 2 * d.n), (2 * d.n, 1)))
+            return
         kv = self.lin(x2d, m.depth_attn.kv_weight)
         k, v = kv[:, :d.n].view(M, d.qh, d.hd), kv[:, d.n:].view(M, d.qh, d.hd)
-        if d.depth_qkv_rms:
-            tape_layer[key + "_kv_raw"] = kv
-            k, v = K.fixed_rms_fwd(k, FANIN_GAIN), K.fixed_rms_fwd(v, FANIN_GAIN * d.deepnorm_beta)
-        hist_k[slot], hist_v[slot] = k, v
+        tape_layer[key + "_kv_raw"] = kv
+        hist_k[slot] = K.fixed_rms_fwd(k, FANIN_GAIN)
+        hist_v[slot] = K.fixed_rms_fwd(v, FANIN_GAIN * d.deepnorm_beta)
 
     def _project_state_bwd(self, x2d, slot, dstate, hist_k, hist_v, tape_layer, key, into):
         """Gradient of :meth:`_project_state` w.r.t. its input; accumulates the weight gradient.  The slot's own
         gradient is formed here, in one pass over every sublayer that read the slot."""
         m, d, K = self.model, self.d, self.K
         M = x2d.shape[0]
-        dk, dv = K.dread_slot_bwd(d, slot, dstate["q"], hist_k, hist_v, dstate["dm"], dstate["lse"], dstate["dd"],
-                                  dstate["gq"])
+        dkv = K.dread_slot_bwd(d, slot, dstate["q"], hist_k, hist_v, dstate["dm"], dstate["lse"], dstate["dd"],
+                               dstate["gq"])                              # [M, 2, QH, HD]: rows [dK | dV]
         if d.depth_qkv_rms:
             kv = tape_layer[key + "_kv_raw"]
-            dk = K.fixed_rms_bwd(dk, kv[:, :d.n].view(M, d.qh, d.hd), FANIN_GAIN)
-            dv = K.fixed_rms_bwd(dv, kv[:, d.n:].view(M, d.qh, d.hd), FANIN_GAIN * d.deepnorm_beta)
-        dkv = torch.cat((dk.reshape(M, d.n), dv.reshape(M, d.n)), -1).to(self.adt)
+            dk = K.fixed_rms_bwd(dkv[:, 0], kv[:, :d.n].view(M, d.qh, d.hd), FANIN_GAIN)
+            dv = K.fixed_rms_bwd(dkv[:, 1], kv[:, d.n:].view(M, d.qh, d.hd), FANIN_GAIN * d.deepnorm_beta)
+            dkv = torch.cat((dk.reshape(M, d.n), dv.reshape(M, d.n)), -1)
+        dkv = dkv.reshape(M, 2 * d.n).to(self.adt)
         K.linear_wgrad(dkv, x2d, self.g(m.depth_attn.kv_weight))
         return K.linear_dgrad(dkv, self.w(m.depth_attn.kv_weight), out=into, accumulate=True)   # into += dkv @ W
 
@@ -307,8 +355,9 @@ class FusedPlan:
         dev = h_emb.device
         L = d.layers
         S = 2 * L
-        hist_k = torch.empty(S, M, d.qh, d.hd, dtype=self.adt, device=dev)
-        hist_v = torch.empty(S, M, d.qh, d.hd, dtype=self.adt, device=dev)
+        # depth history: slot rows are the [K | V] rows of the projection GEMM, so the GEMM stores straight into its slot
+        hist = torch.empty(S, M, 2, d.qh, d.hd, dtype=self.adt, device=dev)
+        hist_k, hist_v = hist[:, :, 0], hist[:, :, 1]
         h = h_emb.reshape(M, N).contiguous()
         tape = {"layers": [], "hist_k": hist_k, "hist_v": hist_v, "h_emb": h, "cos": cos, "sin": sin, "B": B,
                 "emb_l": {}}
@@ -329,7 +378,7 @@ class FusedPlan:
             a = self.lin(qkc[:, 2].reshape(M, N), blk.attn.o.weight)
             # --- depth read 2bi, residual, LN
             sub = 2 * bi
-            m1, t["lse1"] = K.dread_fwd(d, self._depth_query(sub), hist_k, hist_v, sub + 1)
+            m1, t["lse1"] = K.dread_fwd(d, self._step["q_all"][sub], hist_k, hist_v, sub + 1)
             m1 = m1.reshape(M, N)
             s1 = self._readout_lin(m1, sub)
             u, t["x1"], t["mean1"], t["rstd1"] = K.add_ln_fwd(s1, a, blk.ln_attn.weight.data, blk.ln_attn.bias.data,
@@ -338,7 +387,7 @@ class FusedPlan:
             if d.branch_rms_cap is not None:
                 t["s1"], t["a"] = s1, a
             self._project_state(u, sub + 1, hist_k, hist_v, t, "u")
-            m2, t["lse2"] = K.dread_fwd(d, self._depth_query(sub + 1), hist_k, hist_v, sub + 2)
+            m2, t["lse2"] = K.dread_fwd(d, self._step["q_all"][sub + 1], hist_k, hist_v, sub + 2)
             t["m2"] = m2
             s2 = self._readout_lin(m2.reshape(M, N), sub + 1)
             # --- Paraplex FFN
@@ -346,8 +395,8 @@ class FusedPlan:
             x_real = self.lin(u, ffn.w1_real.weight)
             gate_lin = self.lin(u, ffn.gate_proj.weight, ffn.gate_proj.bias.data) if ffn.gate_proj is not None else None
             beta_lin = K.imag_fwd(d, qkc, u, m2, self.w(ffn.w1_imag))
-            alpha_gate = ffn.identity_gate.alpha().detach() if (ffn.identity_gate is not None and p_in is not None) else None
-            gate_w = ffn.gate_selector.weights().detach() if (use_tria and not last) else None
+            alpha_gate = self._step["alpha"][bi] if p_in is not None else None
+            gate_w = self._step["gate_w"][bi]
             anchor = None
             core_in = {"x_real": x_real, "p_in": p_in, "alpha_gate": alpha_gate, "b_real": ffn.w1_real.bias.data,
                        "gate_lin": gate_lin, "beta_lin": beta_lin, "b_imag": ffn.w1_imag_bias.data,
@@ -360,11 +409,10 @@ class FusedPlan:
                                  core_in["seed_valid"], gate_w, core_in["axis"], m.tria_alpha, B)
             if d.phase_secant:
                 if training:
-                    n_el = float(M * d.hidden)
-                    rad = (out["beta_sq_sum"] / n_el).sqrt().clamp_min(1e-4)
-                    ffn.beta_anchor.mul_(ffn.beta_anchor_decay).add_(rad.to(ffn.beta_anchor.dtype),
-                                                                      alpha=1.0 - ffn.beta_anchor_decay)
-                anchor = ffn.beta_anchor.detach().clone()
+                    anchor = K.anchor_update(out["beta_sq_sum"], float(M * d.hidden), ffn.beta_anchor,
+                                             ffn.beta_anchor_decay)
+                else:
+                    anchor = ffn.beta_anchor.detach().clone()
             core_in["anchor"] = anchor
             t["core"] = core_in
             o = out["o"]
@@ -401,11 +449,11 @@ class FusedPlan:
         # depth attention: every sublayer's read gradient is staged; a slot's gradient is formed when the sweep reaches
         # the layer that produced the slot (by then all of its readers have been staged)
         S = 2 * L
-        dst = {"q": torch.stack([self._depth_query(sub) for sub in range(S)]).contiguous(),
+        dst = {"q": self._step["q_all"],
                "dm": torch.empty(S, M, d.qh, d.hd, dtype=self.adt, device=dev),
                "lse": torch.empty(S, M, d.qh, dtype=torch.float32, device=dev),
                "dd": torch.empty(S, M, d.qh, dtype=torch.float32, device=dev),
-               "gq": torch.zeros(S, d.qh, d.hd, dtype=torch.float32, device=dev)}
+               "gq": self._step["gq"]}                                  # summed over chunks; applied once per step
         dh = dh_out.reshape(M, N).to(self.adt)
         dc = ddepth                      # carrier-layout gradient (opaque to the plan)
         dp_out = None
@@ -430,6 +478,7 @@ class FusedPlan:
             core = t["core"]
             core["g_b_real"], core["g_b_imag"] = self.g(ffn.w1_real.bias), self.g(ffn.w1_imag_bias)
             core["g_w_trace"] = self.g(ffn.w1_imag_trace)
+            core["gsc_acc"] = self._step["gsc"][bi]     # d alpha_gate and d gate_w are summed here across chunks
             gr = K.ffn_core_bwd(d, core, do, dc, dp_out, None if dtraces_out is None else dtraces_out[bi])
             dx_real, dbeta = gr["d_x_real"].to(self.adt), gr["d_beta_lin"].to(self.adt)
             dtraces_in[bi] = gr.get("d_trace_in")
@@ -440,13 +489,6 @@ class FusedPlan:
                 core["g_b_real"].add_(gr["d_b_real"])
                 core["g_b_imag"].add_(gr["d_b_imag"])
                 core["g_w_trace"].add_(gr["d_w_trace"])
-            if gr.get("d_alpha_gate") is not None and ffn.identity_gate.raw_alpha.requires_grad:
-                ig = ffn.identity_gate
-                self.g(ig.raw_alpha).add_(gr["d_alpha_gate"] * ig.alpha_max * (1.0 - torch.tanh(ig.raw_alpha.data) ** 2))
-            if gr.get("d_gate_w") is not None and ffn.gate_selector.logits.requires_grad:
-                w9 = core["gate_w"].float()
-                gw9 = gr["d_gate_w"]
-                self.g(ffn.gate_selector.logits).add_(w9 * (gw9 - (gw9 * w9).sum()))
             u = t["u"]
             K.linear_wgrad(dx_real, u, self.g(ffn.w1_real.weight))
             du = K.linear_dgrad(dx_real, self.w(ffn.w1_real.weight))
@@ -478,8 +520,6 @@ class FusedPlan:
             K.linear_wgrad(dqkv, t["h_in"], self.g(blk.attn.qkv_weight))
             dh = K.linear_dgrad(dqkv, self.w(blk.attn.qkv_weight))
         dh = self._project_state_bwd(tape["h_emb"], 0, dst, hist_k, hist_v, tape["emb_l"], "emb", dh)
-        for sub in range(S):
-            self._depth_query_bwd(sub, dst["gq"][sub])
         return dh, dtraces_in, dseed
 
     # ------------------------------------------------------------------ readout

@@ -134,18 +134,49 @@ class CudaKernels(TorchKernels):
         for key in list(self._wq):
             self._flush_one(key)
 
+    # ------------------------------------------------------------------ small per-cell bookkeeping
+    def begin_step(self, zero_floats: int, device) -> None:
+        """One fill per step instead of one per accumulator: the step's fp32 zero-initialised buffers are slices of
+        this pool (a slice is handed out once; when the pool runs out ``zeros`` allocates as usual)."""
+        self._zpool = torch.zeros(max(int(zero_floats), 0), dtype=torch.float32, device=device)
+        self._zoff = 0
+
+    def zeros(self, *shape, device=None):
+        n = 1
+        for v in shape:
+            n *= int(v)
+        pool = getattr(self, "_zpool", None)
+        span_ = (n + 63) // 64 * 64                      # keep every slice 256-byte aligned
+        if pool is None or pool.device != torch.device(device) or self._zoff + span_ > pool.numel():
+            return torch.zeros(*shape, dtype=torch.float32, device=device)
+        out = pool[self._zoff:self._zoff + n].view(*shape)
+        self._zoff += span_
+        return out
+
+    def anchor_update(self, beta_sq_sum, n_el, anchor, decay):
+        if not (anchor.is_cuda and anchor.dtype == torch.float32 and beta_sq_sum.dtype == torch.float32):
+            self.fallbacks["anchor_update"] += 1
+            return super().anchor_update(beta_sq_sum, n_el, anchor, decay)
+        snap = torch.empty((), dtype=torch.float32, device=anchor.device)
+        native.ext().anchor_ema(beta_sq_sum, 1.0 / float(n_el), float(decay), anchor, snap)
+        native.count()
+        return snap
+
     # ------------------------------------------------------------------ GEMMs
-    def linear(self, x, w, bias=None, out_dtype=None, gather=None):
+    def linear(self, x, w, bias=None, out_dtype=None, gather=None, out=None):
         """``gather=(peer_ptrs, rank)``: ``w`` is this rank's copy of a row-sharded weight; the launch fetches every
-        64-row block from the rank that owns it and completes the local copy on the way."""
+        64-row block from the rank that owns it and completes the local copy on the way.  ``out``: a packed bf16
+        [M, N] buffer the epilogue stores into (saves the copy into a pre-allocated slot)."""
         M, Kd = x.shape
         N = w.shape[0]
-        if not (_tma_ok(x) and _tma_ok(w)) or (out_dtype not in (None, torch.bfloat16, torch.float32)):
+        out_ok = out is None or (out.dtype == torch.bfloat16 and out.is_contiguous() and tuple(out.shape) == (M, N)
+                                 and out.data_ptr() % 16 == 0 and out_dtype in (None, torch.bfloat16))
+        if not (_tma_ok(x) and _tma_ok(w) and out_ok) or (out_dtype not in (None, torch.bfloat16, torch.float32)):
             if gather is not None:
                 raise RuntimeError("a sharded weight needs the TMA path (16-byte aligned bf16 rows)")
             self.fallbacks["linear"] += 1
-            return super().linear(x, w, bias, out_dtype)
-        c = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=x.device)
+            return super().linear(x, w, bias, out_dtype, out)
+        c = out if out is not None else torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=x.device)
         b32 = None if bias is None else bias.float().contiguous()
         if gather is not None:
             gemm([x], [Kd], w, c, M=M, N=N, bias=b32, peer_ptrs=list(gather[0]), gather_rank=int(gather[1]))
@@ -316,11 +347,21 @@ class _ElementwiseMixin:
         return dq
 
     # ------------------------------------------------------------------ depth attention
-    def _dread_ok(self, d, hist_k):
-        return hist_k.dtype == torch.bfloat16 and hist_k.is_contiguous() and d.hd % 8 == 0 and d.hd <= 128
+    def _dread_ok(self, d, hist_k, hist_v=None, dense=False):
+        """History is [slots, M, QH, HD] bf16 with unit strides inside a row; K and V may interleave as [K | V] rows of
+        one buffer (slot and row strides multiples of 8 elements).  ``dense``: the kernel wants a packed tensor."""
+        if not (hist_k.dtype == torch.bfloat16 and d.hd % 8 == 0 and d.hd <= 128 and hist_k.dim() == 4):
+            return False
+        if dense:
+            return hist_k.is_contiguous()
+        ok = (hist_k.stride(3) == 1 and hist_k.stride(2) == d.hd and hist_k.stride(1) % 8 == 0
+              and hist_k.stride(0) % 8 == 0 and hist_k.data_ptr() % 16 == 0)
+        if ok and hist_v is not None:
+            ok = hist_v.stride() == hist_k.stride() and hist_v.data_ptr() % 16 == 0
+        return ok
 
     def dread_fwd(self, d, q_row, hist_k, hist_v, n):
-        if not self._dread_ok(d, hist_k):
+        if not self._dread_ok(d, hist_k, hist_v):
             self.fallbacks["dread_fwd"] += 1
             return super().dread_fwd(d, q_row, hist_k, hist_v, n)
         M = hist_k.shape[1]
@@ -331,7 +372,7 @@ class _ElementwiseMixin:
         return out, lse
 
     def dread_bwd(self, d, dm, m, lse, q_row, hist_k, hist_v, n, dhist_k, dhist_v, gq):
-        if not self._dread_ok(d, hist_k):
+        if not (self._dread_ok(d, hist_k, dense=True) and hist_v.is_contiguous()):
             self.fallbacks["dread_bwd"] += 1
             return super().dread_bwd(d, dm, m, lse, q_row, hist_k, hist_v, n, dhist_k, dhist_v, gq)
         M = hist_k.shape[1]
@@ -345,21 +386,21 @@ class _ElementwiseMixin:
             self.fallbacks["dread_stage"] += 1
             return super().dread_stage(d, a, b, m, lse, dst, sub)
         M = dm_all.shape[1]
-        native.ext().dread_stage(_bf16c(a), _opt(b, _bf16c), _bf16c(m), dm_all[sub], dst["dd"][sub], M * d.qh, d.hd)
-        dst["lse"][sub].copy_(lse)
+        native.ext().dread_stage(_bf16c(a), _opt(b, _bf16c), _bf16c(m), dm_all[sub], dst["dd"][sub], _f32c(lse),
+                                 dst["lse"][sub], M * d.qh, d.hd)
         native.count()
 
     def dread_slot_bwd(self, d, slot, q_all, hist_k, hist_v, dm_all, lse_all, dd_all, gq_all):
-        if not (self._dread_ok(d, hist_k) and dm_all.dtype == torch.bfloat16):
+        pairs = (dm_all.shape[0] - slot) * d.hd          # the kernel keeps at most 20 (sublayer, dim) pairs per thread
+        if not (self._dread_ok(d, hist_k, hist_v) and dm_all.dtype == torch.bfloat16 and pairs <= 256 * 20):
             self.fallbacks["dread_slot_bwd"] += 1
             return super().dread_slot_bwd(d, slot, q_all, hist_k, hist_v, dm_all, lse_all, dd_all, gq_all)
         S, M = dm_all.shape[0], dm_all.shape[1]
-        dk = torch.empty(M, d.qh, d.hd, dtype=torch.bfloat16, device=hist_k.device)
-        dv = torch.empty_like(dk)
-        native.ext().dread_slot_bwd(q_all, hist_k[slot], hist_v[slot], dm_all, lse_all, dd_all, dk, dv, gq_all, slot, S, M,
-                                    d.qh, d.hd)
+        dkv = torch.empty(M, 2, d.qh, d.hd, dtype=torch.bfloat16, device=hist_k.device)     # rows [dK | dV]
+        native.ext().dread_slot_bwd(q_all, hist_k[slot], hist_v[slot], dm_all, lse_all, dd_all, dkv[:, 0], dkv[:, 1],
+                                    gq_all, slot, S, M, d.qh, d.hd)
         native.count()
-        return dk, dv
+        return dkv
 
     # ------------------------------------------------------------------ add + LayerNorm
     def add_ln_fwd(self, a, b, w, bias, cap, eps=1e-5):
@@ -429,7 +470,7 @@ class _ElementwiseMixin:
         c = torch.empty(9, M, H, dtype=torch.bfloat16, device=dev) if axis is not None else None
         p_out = torch.empty(M, H, dtype=torch.bfloat16, device=dev) if (axis is not None and gate_w is not None) else None
         trace_out = torch.empty(B, H, dtype=torch.float32, device=dev)
-        bsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        bsq = self.zeros(1, device=dev)
         native.ext().ffn_core(
             False, B, M // B, H, -1 if axis is None else axis, bool(d.phase_secant), d.powlu_m, tria_alpha, d.phase_floor,
             _opt(alpha_gate if p_in is not None else None, lambda t: _f32c(t).reshape(1)), None,
@@ -458,9 +499,10 @@ class _ElementwiseMixin:
         dbeta = torch.empty(M, H, **bf)
         gz = torch.empty(M, H, dtype=torch.float32, device=dev)
         dcp = torch.empty(9, M, H, **bf) if (c_prev is not None and axis is not None) else None
-        dseed = torch.zeros(B, H, 9, dtype=torch.float32, device=dev) if (seed is not None and axis is not None) else None
-        dtr = torch.zeros(B, H, dtype=torch.float32, device=dev) if trace_in is not None else None
-        gsc = torch.zeros(10, dtype=torch.float32, device=dev)
+        dseed = self.zeros(B, H, 9, device=dev) if (seed is not None and axis is not None) else None
+        dtr = self.zeros(B, H, device=dev) if trace_in is not None else None
+        acc = saved.get("gsc_acc")
+        gsc = acc if acc is not None else torch.zeros(10, dtype=torch.float32, device=dev)
         gate_w = saved.get("gate_w")
         native.ext().ffn_core(
             True, B, M // B, H, -1 if axis is None else axis, bool(d.phase_secant), d.powlu_m, saved.get("tria_alpha") or 0.0,
@@ -478,8 +520,8 @@ class _ElementwiseMixin:
         native.count(2)
         return {"d_x_real": dx, "d_p_in": dpin, "d_gate_lin": dgl, "d_beta_lin": dbeta, "d_trace_in": dtr,
                 "d_c_prev": dcp, "d_seed": dseed, "d_b_real": None, "d_b_imag": None, "d_w_trace": None,
-                "d_alpha_gate": gsc[0] if p_in is not None else None,
-                "d_gate_w": gsc[1:10] if gate_w is not None else None}
+                "d_alpha_gate": gsc[0] if (p_in is not None and acc is None) else None,
+                "d_gate_w": gsc[1:10] if (gate_w is not None and acc is None) else None}
 
     # ------------------------------------------------------------------ readout: slot pool and sparse cross attention
     def slot_pool_fwd(self, keys, score_w):

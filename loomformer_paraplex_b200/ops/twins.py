@@ -31,10 +31,14 @@ class TorchKernels:
     name = "torch"
 
     # ------------------------------------------------------------------ GEMMs
-    def linear(self, x, w, bias=None, out_dtype=None):
+    def linear(self, x, w, bias=None, out_dtype=None, out=None):
+        """``x @ w^T (+ bias)``; with ``out`` the product is written into that buffer and the buffer returned."""
         y = F.linear(x, w.to(x.dtype))
         if bias is not None:
             y = y + bias.to(y.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
         return y if out_dtype is None else y.to(out_dtype)
 
     def linear_dgrad(self, dy, w, out=None, accumulate=False):
@@ -200,8 +204,9 @@ class TorchKernels:
         dst["lse"][sub] = lse
 
     def dread_slot_bwd(self, d, slot, q_all, hist_k, hist_v, dm_all, lse_all, dd_all, gq_all):
-        """Gradient of history slot ``slot`` summed over the sublayers ``slot..S-1`` that read it -> (dk, dv)
-        [M,QH,HD]; adds those sublayers' query gradients into ``gq_all``."""
+        """Gradient of history slot ``slot`` summed over the sublayers ``slot..S-1`` that read it -> [M,2,QH,HD]
+        (index 0: dK, index 1: dV, i.e. rows [dK | dV] as the K/V projection's gradient wants them); adds those
+        sublayers' query gradients into ``gq_all``."""
         inv = 1.0 / math.sqrt(d.hd)
         k, v = hist_k[slot].float(), hist_v[slot].float()
         q, dmf = q_all[slot:].float(), dm_all[slot:].float()
@@ -210,7 +215,7 @@ class TorchKernels:
         gq_all[slot:].add_(torch.einsum("nmg,mgh->ngh", dsc, k))
         dk = torch.einsum("nmg,ngh->mgh", dsc, q)
         dv = (w.unsqueeze(-1) * dmf).sum(0)
-        return dk.to(hist_k.dtype), dv.to(hist_v.dtype)
+        return torch.stack((dk, dv), 1).to(hist_k.dtype)
 
     def fixed_rms_fwd(self, x, target):
         return R.fixed_rms(x, target)
@@ -219,6 +224,20 @@ class TorchKernels:
         xf, g = x.float(), dy.float()
         r = torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)
         return (target * r * (g - xf * r * r * (g * xf).mean(-1, keepdim=True)))
+
+    def anchor_update(self, beta_sq_sum, n_el, anchor, decay):
+        """In-place running radius ``anchor <- decay * anchor + (1 - decay) * max(sqrt(beta_sq_sum / n_el), 1e-4)``;
+        returns a snapshot of the updated value (reference: loomformer.py:2866-2872, the beta-anchor EMA)."""
+        rad = (beta_sq_sum / n_el).sqrt().clamp_min(1e-4)
+        anchor.mul_(decay).add_(rad.to(anchor.dtype), alpha=1.0 - decay)
+        return anchor.detach().clone()
+
+    def zeros(self, *shape, device=None):
+        """fp32 zeros; a kernel set may carve them out of one buffer cleared once per step (:meth:`begin_step`)."""
+        return torch.zeros(*shape, dtype=torch.float32, device=device)
+
+    def begin_step(self, zero_floats: int, device) -> None:
+        """Called at the start of a step with an upper bound on the fp32 zeros the step will ask for."""
 
     def flush_wgrads(self) -> None:
         """Issue any weight-gradient products that a kernel set queued for grouping (nothing is queued here)."""
@@ -306,7 +325,14 @@ class TorchKernels:
                     outs.append(t); grads.append(g.float().reshape(t.shape))
             ins = [(k, v) for k, v in leaves.items() if v is not None]
             res = torch.autograd.grad(outs, [v for _, v in ins], grads, allow_unused=True)
-        return {"d_" + k: g for (k, _), g in zip(ins, res)}
+        gr = {"d_" + k: g for (k, _), g in zip(ins, res)}
+        acc = saved.get("gsc_acc")           # [10]: d alpha_gate, then d gate_w -- summed across the step's chunks
+        if acc is not None:
+            if gr.get("d_alpha_gate") is not None:
+                acc[0] += gr.pop("d_alpha_gate").reshape(())
+            if gr.get("d_gate_w") is not None:
+                acc[1:10] += gr.pop("d_gate_w").reshape(9)
+        return gr
 
     # ------------------------------------------------------------------ temporal endpoint (+ PolARM)
     def temporal_fwd(self, depth, B, Tc, H, reset, state, fired, polarm_beta):

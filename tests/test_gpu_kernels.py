@@ -74,6 +74,10 @@ def test_depth_read(hd, qh):
     tk.dread_bwd(d, dm.float(), m1.float(), l1, q, hk.float(), hv.float(), n, *g2)
     for x, y, nm in zip(g1, g2, ("dk", "dv", "gq")):
         _close(x, y, 2e-2, nm)
+    # K and V interleaved as [K | V] rows of one buffer (the layout the training plan keeps)
+    both = torch.stack((hk, hv), 2).contiguous()
+    m3, l3 = ck.dread_fwd(d, q, both[:, :, 0], both[:, :, 1], n)
+    _close(m3, m2); _close(l3, l2, 1e-3)
     assert not ck.fallbacks, ck.fallbacks
 
 
@@ -254,14 +258,18 @@ def test_attention_backward(hd, qh, kvh, Tc, s):
     _close(dv1.view(B, T, kvh, g, hd).sum(3), dv2, 3e-2, "dv")
 
 
-@pytest.mark.parametrize("hd,qh", [(96, 8), (32, 4)])
-def test_depth_read_backward_per_slot(hd, qh):
-    """Staged per-slot backward equals the sum of per-sublayer contributions evaluated in fp32."""
+@pytest.mark.parametrize("hd,qh,S", [(96, 8, 6), (32, 4, 6), (64, 3, 65)])
+def test_depth_read_backward_per_slot(hd, qh, S):
+    """Staged per-slot backward equals the sum of per-sublayer contributions evaluated in fp32 (S=65 is the 32-layer
+    stack, which takes the kernel's 20-pairs-per-thread instantiation)."""
     ck, tk = _sets()
     d = _dims(qh=qh, hd=hd, kvh=qh)
-    S, M = 6, 200
+    M = 200
     torch.manual_seed(9)
     hk, hv = bf(S, M, qh, hd), bf(S, M, qh, hd)
+    if S == 65:                                  # interleaved [K | V] rows, as the training plan stores them
+        both = torch.stack((hk, hv), 2).contiguous()
+        hk, hv = both[:, :, 0], both[:, :, 1]
     q_all = torch.randn(S, qh, hd, device="cuda")
     mk = lambda dt: {"q": q_all, "dm": torch.zeros(S, M, qh, hd, dtype=dt, device="cuda"),
                      "lse": torch.zeros(S, M, qh, device="cuda"), "dd": torch.zeros(S, M, qh, device="cuda"),
@@ -272,11 +280,11 @@ def test_depth_read_backward_per_slot(hd, qh):
         a, b = bf(M, qh, hd, scale=0.3), (bf(M, qh, hd, scale=0.3) if sub % 2 else None)
         ck.dread_stage(d, a, b, m_out.to(torch.bfloat16), lse, d1, sub)
         tk.dread_stage(d, a.float(), None if b is None else b.float(), m_out.to(torch.bfloat16).float(), lse, d2, sub)
-    _close(d1["dm"], d2["dm"], 1e-2, "dm"); _close(d1["dd"], d2["dd"], 2e-2, "dd")
+    _close(d1["dm"], d2["dm"], 1e-2, "dm"); _close(d1["dd"], d2["dd"], 2e-2, "dd"); _close(d1["lse"], d2["lse"], 1e-5, "lse")
     for slot in (0, 3, S - 1):
-        k1, v1 = ck.dread_slot_bwd(d, slot, q_all, hk, hv, d1["dm"], d1["lse"], d1["dd"], d1["gq"])
-        k2, v2 = tk.dread_slot_bwd(d, slot, q_all, hk.float(), hv.float(), d2["dm"], d2["lse"], d2["dd"], d2["gq"])
-        _close(k1, k2, 2e-2, "dk"); _close(v1, v2, 2e-2, "dv")
+        kv1 = ck.dread_slot_bwd(d, slot, q_all, hk, hv, d1["dm"], d1["lse"], d1["dd"], d1["gq"])
+        kv2 = tk.dread_slot_bwd(d, slot, q_all, hk.float(), hv.float(), d2["dm"], d2["lse"], d2["dd"], d2["gq"])
+        _close(kv1[:, 0], kv2[:, 0], 2e-2, "dk"); _close(kv1[:, 1], kv2[:, 1], 2e-2, "dv")
     _close(d1["gq"], d2["gq"], 2e-2, "gq")
     assert not ck.fallbacks, ck.fallbacks
 
