@@ -159,7 +159,9 @@ class FusedPlan:
             if chunked and temporal is not None:
                 seed, seed_valid = temporal, fire[:, s - 1] & ~reset[:, s]
             with span(f"chunk_fwd[{s}:{e}]"):
-                tape = self._chunk_forward(h_emb[:, s:e], cos_all[:, s:e], sin_all[:, s:e], tok_reset[:, s:e], seg,
+                # one packed copy per chunk; every layer's RoPE kernels (forward and backward) read it
+                tape = self._chunk_forward(h_emb[:, s:e], cos_all[:, s:e].contiguous(), sin_all[:, s:e].contiguous(),
+                                           tok_reset[:, s:e], seg,
                                            s, e, kc, vc, traces, seed, seed_valid, training, want_grad)
             traces = tape["trace_out"]
             tape.update(s=s, e=e, seed=seed, seed_valid=seed_valid, temporal_in=temporal, fired=None,
