@@ -22,6 +22,7 @@ replay tape (``tria.py:279-709``) have no counterpart because carriers are store
 """
 from __future__ import annotations
 
+import dataclasses
 import math
 from typing import Dict, List, Optional, Tuple
 
@@ -41,12 +42,37 @@ def make_kernels(device: torch.device):
 
 
 class FusedPlan:
-    def __init__(self, model, kernels=None, flat=None, compute_dtype: Optional[torch.dtype] = None) -> None:
-        self.model, self.d = model, model.d
+    def __init__(self, model, kernels=None, flat=None, compute_dtype: Optional[torch.dtype] = None,
+                 pad_hidden: Optional[bool] = None) -> None:
+        """``pad_hidden``: run the Paraplex FFN with every head's hidden sector rounded up to a multiple of 8
+        neurons (None = do so on a GPU exactly when the sector width is not one already).  A transplanted SmolLM2
+        has 171 neurons per head: its [M, H] activations would have rows that start off a 16-byte boundary, which
+        neither TMA nor the vectorised kernels take.  The padded neurons have zero weights in and out, so they
+        change neither the loss nor any gradient (``_refresh_padded`` / ``_unpad_grads``)."""
+        self.model, self.d_true = model, model.d
         dev = model.emb.weight.device
         self.K = kernels if kernels is not None else make_kernels(dev)
         self.flat = flat
         self.adt = compute_dtype or (torch.bfloat16 if dev.type == "cuda" else torch.float32)
+        d = model.d
+        if pad_hidden is None:
+            pad_hidden = dev.type == "cuda" and d.hpq % 8 != 0
+        self._hpad: Dict[int, Tuple[torch.Tensor, int]] = {}      # id(param) -> (param, axis that indexes neurons)
+        self._wp: Dict[int, torch.Tensor] = {}                    # padded values (compute dtype; fp32 for vectors)
+        self._gp: Dict[int, torch.Tensor] = {}                    # padded fp32 gradients of the current run
+        if pad_hidden and d.hpq % 8 != 0:
+            hpq_p = (d.hpq + 7) // 8 * 8
+            self.d = dataclasses.replace(d, hidden=d.qh * hpq_p, hpq=hpq_p)
+            for blk in model.blocks:
+                f = blk.ffn
+                rows = [f.w1_real.weight, f.w1_real.bias, f.w1_imag, f.w1_imag_bias, f.w1_imag_trace]
+                if f.gate_proj is not None:
+                    rows += [f.gate_proj.weight, f.gate_proj.bias]
+                for q in rows:
+                    self._hpad[id(q)] = (q, 0)
+                self._hpad[id(f.w2.weight)] = (f.w2.weight, 1)
+        else:
+            self.d = d
         self._wcache: Dict[int, torch.Tensor] = {}
         self._consts: Dict[tuple, torch.Tensor] = {}
         self._fetched: set = set()
@@ -69,10 +95,74 @@ class FusedPlan:
             spec = self.gather_spec(p)
         if spec is None:
             return self.K.linear(x, self.w(p), bias, out=out)
+        if id(p) in self._hpad:
+            raise NotImplementedError("row-sharded weights and padded hidden sectors are not combined; use the "
+                                      "replicated or fused-step gradient modes for this model shape")
         return self.K.linear(x, self.w(p), bias, gather=spec, out=out)
 
+    # ------------------------------------------------------------------ padded hidden sectors
+    def _sector_view(self, t: torch.Tensor, axis: int, width: int) -> torch.Tensor:
+        """View of ``t`` with the neuron axis split into (heads, width)."""
+        qh = self.d.qh
+        if axis == 0:
+            return t.view(qh, width, *t.shape[1:])
+        return t.view(t.shape[0], qh, width)
+
+    def _refresh_padded(self) -> None:
+        """Copy the current values of the neuron-indexed FFN parameters into their padded buffers (pads stay zero)."""
+        hp, hpp = self.d_true.hpq, self.d.hpq
+        for key, (p, axis) in self._hpad.items():
+            src = self._w_plain(p) if p.dim() == 2 else p.data
+            buf = self._wp.get(key)
+            if buf is None:
+                shape = list(p.shape)
+                shape[axis] = self.d.hidden
+                buf = self._wp[key] = torch.zeros(shape, dtype=src.dtype if p.dim() == 2 else torch.float32,
+                                                  device=p.device)
+            dst = self._sector_view(buf, axis, hpp)
+            (dst[:, :hp] if axis == 0 else dst[:, :, :hp]).copy_(self._sector_view(src, axis, hp))
+        self._gp.clear()
+
+    def _unpad_grads(self) -> None:
+        """Add the real neurons' share of every padded gradient into the parameter's own gradient."""
+        hp, hpp = self.d_true.hpq, self.d.hpq
+        for key, gp in self._gp.items():
+            p, axis = self._hpad[key]
+            src = self._sector_view(gp, axis, hpp)
+            self._sector_view(FusedPlan._g_plain(p), axis, hp).add_(src[:, :hp] if axis == 0 else src[:, :, :hp])
+        self._gp.clear()
+
+    def _unpad_neurons(self, t: torch.Tensor, axis: int) -> torch.Tensor:
+        """Drop the padded neurons of an activation-like tensor whose ``axis`` indexes (padded) hidden neurons."""
+        if not self._hpad:
+            return t
+        hp, hpp, qh = self.d_true.hpq, self.d.hpq, self.d.qh
+        shape = list(t.shape)
+        v = t.reshape(*shape[:axis], qh, hpp, *shape[axis + 1:]).narrow(axis + 1, 0, hp)
+        return v.reshape(*shape[:axis], qh * hp, *shape[axis + 1:])
+
+    def _pad_neurons(self, t: torch.Tensor, axis: int) -> torch.Tensor:
+        """Inverse of :meth:`_unpad_neurons` with zeros in the padded positions."""
+        if not self._hpad:
+            return t
+        hp, hpp, qh = self.d_true.hpq, self.d.hpq, self.d.qh
+        shape = list(t.shape)
+        out = torch.zeros(*shape[:axis], qh, hpp, *shape[axis + 1:], dtype=t.dtype, device=t.device)
+        out.narrow(axis + 1, 0, hp).copy_(t.reshape(*shape[:axis], qh, hp, *shape[axis + 1:]))
+        return out.reshape(*shape[:axis], qh * hpp, *shape[axis + 1:])
+
+    def v(self, p: torch.Tensor) -> torch.Tensor:
+        """A neuron-indexed vector parameter (bias, trace weight) in fp32, padded when the plan pads."""
+        return self._wp[id(p)] if id(p) in self._hpad else p.data
+
     def w(self, p: torch.Tensor) -> torch.Tensor:
-        """Weight in the compute dtype (bf16 shadow on a GPU, the fp32 parameter itself on a CPU)."""
+        """Weight in the compute dtype (bf16 shadow on a GPU, the fp32 parameter itself on a CPU); the padded copy for
+        a neuron-indexed FFN weight when the plan pads."""
+        if id(p) in self._hpad:
+            return self._wp[id(p)]
+        return self._w_plain(p)
+
+    def _w_plain(self, p: torch.Tensor) -> torch.Tensor:
         if self.adt == torch.float32:
             return p.data
         if self.flat is not None and self.flat.shadow is not None:
@@ -93,8 +183,19 @@ class FusedPlan:
             t = self._consts[key] = torch.tensor(values, device=dev)
         return t
 
+    def g(self, p: torch.Tensor) -> torch.Tensor:
+        """fp32 gradient accumulator of ``p`` (for a padded FFN parameter: this run's padded accumulator, folded into
+        the parameter's own gradient by :meth:`_unpad_grads`)."""
+        key = id(p)
+        if key in self._hpad:
+            gp = self._gp.get(key)
+            if gp is None:
+                gp = self._gp[key] = torch.zeros(self._wp[key].shape, dtype=torch.float32, device=p.device)
+            return gp
+        return FusedPlan._g_plain(p)
+
     @staticmethod
-    def g(p: torch.Tensor) -> torch.Tensor:
+    def _g_plain(p: torch.Tensor) -> torch.Tensor:
         if p.grad is None:
             p.grad = torch.zeros_like(p.data, dtype=torch.float32)
         return p.grad
@@ -126,6 +227,8 @@ class FusedPlan:
         B, T = idx.shape
         dev = idx.device
         self._fetched.clear()
+        if self._hpad:
+            self._refresh_padded()
         if position_ids is None:
             position_ids = torch.arange(T, device=dev).view(1, T).expand(B, T)
         chunked = d.tria and d.tria_temporal and not m.ablation
@@ -189,12 +292,15 @@ class FusedPlan:
         # ---- sparse readout of the boundary keys
         ro = None
         if keys:
-            ro = self._readout_forward(h, torch.stack(keys, 1), torch.stack(key_valid, 1),
+            ro = self._readout_forward(h, self._unpad_neurons(torch.stack(keys, 1), 2), torch.stack(key_valid, 1),
                                        self._const(tuple(key_pos), dev), seg)
             h = ro["h_out"]
         hn = K.rms_norm_fwd(h, m.ln_final.weight) if m.ln_final is not None else h
         logits = self.lin(hn.reshape(B * T, d.n), m.head.weight).view(B, T, d.vocab)
         if return_state:
+            if self._hpad:                       # a decoder continues with the model's own hidden width
+                traces = None if traces is None else [self._unpad_neurons(t, 1) for t in traces]
+                temporal = None if temporal is None else self._unpad_neurons(temporal, 1)
             state = {"kc": kc, "vc": vc, "traces": traces, "temporal": temporal, "n_keys": len(keys),
                      "pending": fire[:, T - 1] if (chunked and fire is not None) else None}
             if temporal is None and chunked:
@@ -221,6 +327,7 @@ class FusedPlan:
         dkeys = None
         if ro is not None:
             dh, dkeys = self._readout_backward(ro, dh)
+            dkeys = self._pad_neurons(dkeys, 2)
         dkc = [K.alloc_kv_grad(d, B, T, dev) for _ in range(L)]
         dvc = [K.alloc_kv_grad(d, B, T, dev) for _ in range(L)]
         d_emb = torch.empty(B, T, d.n, dtype=self.adt, device=dev)
@@ -251,6 +358,8 @@ class FusedPlan:
         self.g(m.emb.weight).index_add_(0, idx.reshape(-1), d_emb.view(B * T, d.n).float())
         self._step_constants_bwd()
         K.flush_wgrads()
+        if self._hpad:
+            self._unpad_grads()
         return loss, None
 
     # ------------------------------------------------------------------ per-step constants
@@ -395,14 +504,14 @@ class FusedPlan:
             # --- Paraplex FFN
             ffn = blk.ffn
             x_real = self.lin(u, ffn.w1_real.weight)
-            gate_lin = self.lin(u, ffn.gate_proj.weight, ffn.gate_proj.bias.data) if ffn.gate_proj is not None else None
+            gate_lin = self.lin(u, ffn.gate_proj.weight, self.v(ffn.gate_proj.bias)) if ffn.gate_proj is not None else None
             beta_lin = K.imag_fwd(d, qkc, u, m2, self.w(ffn.w1_imag))
             alpha_gate = self._step["alpha"][bi] if p_in is not None else None
             gate_w = self._step["gate_w"][bi]
             anchor = None
-            core_in = {"x_real": x_real, "p_in": p_in, "alpha_gate": alpha_gate, "b_real": ffn.w1_real.bias.data,
-                       "gate_lin": gate_lin, "beta_lin": beta_lin, "b_imag": ffn.w1_imag_bias.data,
-                       "w_trace": ffn.w1_imag_trace.data, "trace_in": None if traces_in is None else traces_in[bi],
+            core_in = {"x_real": x_real, "p_in": p_in, "alpha_gate": alpha_gate, "b_real": self.v(ffn.w1_real.bias),
+                       "gate_lin": gate_lin, "beta_lin": beta_lin, "b_imag": self.v(ffn.w1_imag_bias),
+                       "w_trace": self.v(ffn.w1_imag_trace), "trace_in": None if traces_in is None else traces_in[bi],
                        "reset": reset_flat, "c_prev": c_prev, "seed": seed if bi == 0 else None,
                        "seed_valid": seed_valid if bi == 0 else None, "gate_w": gate_w,
                        "axis": (bi % 3) if use_tria else None, "tria_alpha": m.tria_alpha, "B": B}
@@ -411,7 +520,7 @@ class FusedPlan:
                                  core_in["seed_valid"], gate_w, core_in["axis"], m.tria_alpha, B)
             if d.phase_secant:
                 if training:
-                    anchor = K.anchor_update(out["beta_sq_sum"], float(M * d.hidden), ffn.beta_anchor,
+                    anchor = K.anchor_update(out["beta_sq_sum"], float(M * self.d_true.hidden), ffn.beta_anchor,
                                              ffn.beta_anchor_decay)
                 else:
                     anchor = ffn.beta_anchor.detach().clone()

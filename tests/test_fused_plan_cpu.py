@@ -36,7 +36,20 @@ def _model(extra):
 
 @pytest.mark.parametrize("name", list(VARIANTS))
 def test_fused_plan_matches_autograd(name):
-    m = _model(VARIANTS[name])
+    _check(name, _model(VARIANTS[name]))
+
+
+@pytest.mark.parametrize("name", ["head_secant", "open_rich"])
+def test_fused_plan_padded_sectors(name):
+    """Five neurons per head, executed with every head's sector padded to eight: the padded neurons must change
+    neither the loss nor any gradient (the GPU plan pads this way when a sector is not a multiple of 8 wide)."""
+    m = _model(dict(VARIANTS[name], hidden=20, hidden_mult=None))
+    assert m.d.hpq == 5
+    plan = _check(name, m, pad_hidden=True)
+    assert plan.d.hpq == 8 and plan.d.hidden == 32 and plan.d_true.hidden == 20
+
+
+def _check(name, m, **plan_kw):
     m.train()
     torch.manual_seed(1)
     x = torch.randint(0, 61, (3, 20))
@@ -62,7 +75,7 @@ def test_fused_plan_matches_autograd(name):
     for b, a in zip(m.blocks, anchors0):
         b.ffn.beta_anchor.copy_(a)
     # fused plan with torch twins
-    plan = FusedPlan(m, kernels=TorchKernels(), compute_dtype=torch.float32)
+    plan = FusedPlan(m, kernels=TorchKernels(), compute_dtype=torch.float32, **plan_kw)
     with torch.no_grad():
         loss, _ = plan.run(x, y, pos, seg, want_grad=True)
     assert abs(float(loss) - float(loss_ref)) < 1e-5
@@ -76,6 +89,7 @@ def test_fused_plan_matches_autograd(name):
         scale = float(ref[n].abs().max()) + 1e-8
         err = float((p.grad - ref[n]).abs().max())
         assert err <= 3e-4 * scale + 1e-7, (n, err, scale)
+    return plan
 
 
 def test_fused_forward_logits_match():

@@ -40,11 +40,14 @@ def test_native_optimizer_matches_torch(kind):
         assert torch.allclose(o1.atom_out[1:], o2.atom_out[1:], rtol=1e-3)
 
 
-def test_fused_plan_bf16_tracks_fp32_reference():
+@pytest.mark.parametrize("hidden", [None, 172])
+def test_fused_plan_bf16_tracks_fp32_reference(hidden):
+    """``hidden=172`` gives 43 neurons per head, a sector width the kernels do not take: the plan pads every sector to
+    48 and must still run on the native kernels only."""
     from loomformer_paraplex_b200.ops import kernels
     from loomformer_paraplex_b200.ops.fused_plan import FusedPlan
     torch.manual_seed(0)
-    cfg = Config(**CFG)
+    cfg = Config(**(CFG if hidden is None else dict(CFG, hidden=hidden, hidden_mult=None)))
     cpu = Model(cfg).train()
     with torch.no_grad():
         for _, p in cpu.named_parameters():
@@ -59,6 +62,8 @@ def test_fused_plan_bf16_tracks_fp32_reference():
     with torch.no_grad():
         loss, _ = plan.run(x.cuda(), y.cuda(), None, None, want_grad=True)
     kernels.check_status(torch.device("cuda"))
+    assert not plan.K.fallbacks, dict(plan.K.fallbacks)
+    assert (plan.d.hpq, plan.d_true.hpq) == ((48, 43) if hidden else (128, 128))
     assert abs(float(loss) - float(loss_ref)) < 3e-2, (float(loss), float(loss_ref))
     bad = []
     for (n, pc), (_, pg) in zip(cpu.named_parameters(), gpu.named_parameters()):
