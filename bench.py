@@ -85,14 +85,20 @@ def parse():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--optimizer", default="adamw", choices=["adamw", "atom"])
-    ap.add_argument("--micro-batch", type=int, default=16)
+    ap.add_argument("--model", default="113m", choices=["113m", "smol360"],
+                    help="113m: the headline architecture (cfg/nano.yaml dims); smol360: cfg/smol360.yaml (SmolLM2 "
+                         "transplant shape, 467M parameters), default micro-batch 8")
+    ap.add_argument("--micro-batch", type=int, default=None)
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=None, help="debug only: a non-default value makes the number invalid")
     ap.add_argument("--grad-sync", default="auto", choices=["auto", "collective", "p2p", "fsdp"])
     ap.add_argument("--workload", default="pretrain", choices=["pretrain", "sft"],
                     help="sft: synthetic multi-turn chats rendered through the chat template, packed to seq_len, "
                          "assistant-only loss (a secondary benchmark; the headline metric is pretrain)")
-    return ap.parse_args()
+    a = ap.parse_args()
+    if a.micro_batch is None:
+        a.micro_batch = 8 if a.model == "smol360" else 16
+    return a
 
 
 def sft_batches(vocab, micro_batch, seq_len, rank, n=4):
@@ -164,6 +170,11 @@ def emit(args, impl, ms, clocks, world, extra):
                    "l2": "per-step working set >> 126 MB L2, no explicit flush",
                    "layers": MODEL_KW["layers"] if args.layers is None else args.layers},
     }
+    if getattr(args, "model", "113m") == "smol360":
+        line["metric"] = "train tokens/s (cfg/smol360.yaml, 467M LoomFormer-Paraplex, bf16, seq 2048)"
+        line["config"]["model"] = "cfg/smol360.yaml (SmolLM2-360M transplant shape)"
+        line["config"]["layers"] = 32 if args.layers is None else args.layers
+        line["vs_baseline"] = None
     if getattr(args, "workload", "pretrain") == "sft":
         line["metric"] = "SFT train tokens/s (113M LoomFormer-Paraplex, bf16, packed chats, seq 2048)"
         line["data"] = "synthetic multi-turn chats through chat_template.jinja, packed, assistant-only loss; random-init weights"
@@ -183,10 +194,17 @@ def run_ours(args):
     from loomformer_paraplex_b200.train.engine import TrainEngine
 
     dev, world, rank = pdist.init("cuda")
-    kw = dict(MODEL_KW, batch_size=args.micro_batch, seq_len=args.seq_len, optimizer=args.optimizer)
-    if args.layers is not None:
-        kw["layers"] = args.layers
-    cfg = Config(**kw)
+    if args.model == "smol360":
+        cfg = Config.from_yaml(os.path.join(ROOT, "cfg", "smol360.yaml"))
+        cfg.batch_size, cfg.seq_len, cfg.optimizer, cfg.tokenizer = args.micro_batch, args.seq_len, args.optimizer, None
+        cfg.grad_checkpointing = False            # 180 GB of HBM holds the activations of 8 x 2048 tokens
+        if args.layers is not None:
+            cfg.layers = args.layers
+    else:
+        kw = dict(MODEL_KW, batch_size=args.micro_batch, seq_len=args.seq_len, optimizer=args.optimizer)
+        if args.layers is not None:
+            kw["layers"] = args.layers
+        cfg = Config(**kw)
     torch.manual_seed(cfg.seed)
     model = Model(cfg).to(dev)
     # auto: one GPU needs no exchange; several GPUs use the fused NVLink step (reduce-scatter + optimizer + all-gather
@@ -278,7 +296,7 @@ def run_reference(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     lf.device_auto(f"cuda:{local}")
-    cfg = lf.Config.from_yaml(os.path.join(ref_dir, "cfg", "nano.yaml"))
+    cfg = lf.Config.from_yaml(os.path.join(ref_dir, "cfg", "smol360.yaml" if args.model == "smol360" else "nano.yaml"))
     cfg.seq_len, cfg.batch_size, cfg.optimizer, cfg.device = args.seq_len, args.micro_batch, args.optimizer, f"cuda:{local}"
     if args.layers is not None:
         cfg.layers = args.layers

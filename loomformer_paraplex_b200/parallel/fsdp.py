@@ -46,12 +46,17 @@ class ShardPlan:
         repl = torch.ones(nblk, dtype=torch.uint8)
         self.gathered: Dict[int, str] = {}                 # id(param) -> name, for weights fetched on use
         small: List[Tuple[int, int]] = []
+        # a hidden sector that is not a multiple of 8 neurons wide makes the execution plan work on padded copies of
+        # the neuron-indexed FFN weights, which it rebuilds from complete local values: those stay replicated
+        padded_ffn = getattr(getattr(model, "d", None), "hpq", 8) % 8 != 0
+        ffn_suffixes = ("ffn.w1_real.weight", "ffn.gate_proj.weight", "ffn.w2.weight")
         for s in flat.segments:
             b0, b1 = s.offset // BLOCK, (s.offset + s.padded) // BLOCK
             p = s.param
             ok = (p.dim() == 2 and s.name.endswith(GATHERED_SUFFIXES) and p.shape[0] >= 64 * world
                   and (64 * p.shape[1]) % BLOCK == 0 and (p.shape[1] * 2) % 16 == 0
-                  and not (tied_head and s.name in ("head.weight", "emb.weight")))
+                  and not (tied_head and s.name in ("head.weight", "emb.weight"))
+                  and not (padded_ffn and s.name.endswith(ffn_suffixes)))
             if ok:
                 _, blocks = row_block_owner(p.shape[0], world)
                 per64 = 64 * p.shape[1] // BLOCK           # flat blocks per 64-row block
