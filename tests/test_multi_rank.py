@@ -20,8 +20,9 @@ def _launch(mode, out, device_kind, nproc, port):
     return torch.load(out)
 
 
-def test_gloo_ddp_two_ranks_stay_in_sync(tmp_path):
-    res = _launch("collective", str(tmp_path / "cpu.pt"), "cpu", 2, 29611)
+@pytest.mark.parametrize("nproc", [2, 4])
+def test_gloo_ddp_ranks_stay_in_sync(tmp_path, nproc):
+    res = _launch("collective", str(tmp_path / "cpu.pt"), "cpu", nproc, 29611 + 10 * nproc)
     assert res["same"]
     assert res["losses"][-1] < res["losses"][0]
 
