@@ -239,6 +239,9 @@ class FusedPlan:
         cut_set = set(cuts)
         stops = cuts + ([T - 1] if not cuts or cuts[-1] != T - 1 else [])
         training = m.training and want_grad
+        # activation checkpointing per temporal chunk (reference: loomformer.py:3720-3749): the forward keeps only what
+        # crosses chunk boundaries; the backward sweep rebuilds each chunk's tape right before it is consumed
+        ckpt = bool(d.grad_checkpointing and want_grad and not return_state)
         emb_w = self.w(m.emb.weight)
         h_emb = emb_w[idx]                                              # [B,T,N]
         cos_all, sin_all = m.rope_cos[position_ids], m.rope_sin[position_ids]     # [B,T,HD] fp32
@@ -266,7 +269,7 @@ class FusedPlan:
                 tape = self._chunk_forward(h_emb[:, s:e], cos_all[:, s:e].contiguous(), sin_all[:, s:e].contiguous(),
                                            tok_reset[:, s:e], seg,
                                            s, e, kc, vc, traces, seed, seed_valid, training, want_grad)
-            traces = tape["trace_out"]
+            traces_in, traces = traces, tape["trace_out"]
             tape.update(s=s, e=e, seed=seed, seed_valid=seed_valid, temporal_in=temporal, fired=None,
                         has_endpoint=False, key_index=None)
             if chunked:
@@ -285,6 +288,13 @@ class FusedPlan:
             h_parts.append(tape["h_out"].view(B, e - s, d.n))
             if not want_grad:
                 tape = {"s": s, "e": e}
+            elif ckpt:
+                keep = ("s", "e", "seed", "seed_valid", "temporal_in", "fired", "has_endpoint", "key_index",
+                        "local_reset", "t_aux")
+                light = {k: tape[k] for k in keep if k in tape}
+                light["traces_in"] = traces_in
+                light["anchors"] = [t["core"]["anchor"] for t in tape["layers"]]
+                tape = light
             tapes.append(tape)
             s = e
         h = torch.cat(h_parts, dim=1) if len(h_parts) > 1 else h_parts[0]
@@ -335,6 +345,14 @@ class FusedPlan:
         dtemporal = None                      # gradient w.r.t. the temporal state entering the NEXT chunk
         for tape in reversed(tapes):
             s, e = tape["s"], tape["e"]
+            if ckpt:
+                with span(f"chunk_recompute[{s}:{e}]"):
+                    full = self._chunk_forward(h_emb[:, s:e], cos_all[:, s:e].contiguous(),
+                                               sin_all[:, s:e].contiguous(), tok_reset[:, s:e], seg, s, e, kc, vc,
+                                               tape["traces_in"], tape["seed"], tape["seed_valid"], False, True,
+                                               anchors=tape["anchors"])
+                full.update({k: v for k, v in tape.items() if k not in ("traces_in", "anchors")})
+                tape = full
             ddepth = None
             if tape["has_endpoint"]:
                 dstate = dtemporal
@@ -459,7 +477,9 @@ class FusedPlan:
 
     # ------------------------------------------------------------------ chunk forward
     def _chunk_forward(self, h_emb, cos, sin, tok_reset, seg, s, e, kc, vc, traces_in, seed, seed_valid,
-                       training, want_grad):
+                       training, want_grad, anchors=None):
+        """``anchors``: per-layer running radii recorded by an earlier pass over this chunk; given them, the pass
+        rebuilds the chunk's tape without touching the running statistics (activation checkpointing)."""
         m, d, K = self.model, self.d, self.K
         B, Tc, N = h_emb.shape
         M = B * Tc
@@ -519,7 +539,9 @@ class FusedPlan:
                                  core_in["w_trace"], core_in["trace_in"], reset_flat, None, c_prev, core_in["seed"],
                                  core_in["seed_valid"], gate_w, core_in["axis"], m.tria_alpha, B)
             if d.phase_secant:
-                if training:
+                if anchors is not None:
+                    anchor = anchors[bi]
+                elif training:
                     anchor = K.anchor_update(out["beta_sq_sum"], float(M * self.d_true.hidden), ffn.beta_anchor,
                                              ffn.beta_anchor_decay)
                 else:

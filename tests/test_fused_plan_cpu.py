@@ -49,6 +49,15 @@ def test_fused_plan_padded_sectors(name):
     assert plan.d.hpq == 8 and plan.d.hidden == 32 and plan.d_true.hidden == 20
 
 
+@pytest.mark.parametrize("name", ["head_secant", "open_rich"])
+def test_fused_plan_with_chunk_checkpointing(name):
+    """With ``grad_checkpointing`` the plan keeps only what crosses chunk boundaries and rebuilds each chunk's tape in
+    the backward sweep; loss, gradients and the running radii must be what the stored-tape run gives."""
+    m = _model(dict(VARIANTS[name], grad_checkpointing=True))
+    assert m.d.grad_checkpointing
+    _check(name, m)
+
+
 def _check(name, m, **plan_kw):
     m.train()
     torch.manual_seed(1)

@@ -398,3 +398,34 @@ def test_add_layernorm_with_rms_cap():
     da2, db2 = tk.add_ln_bwd(dy.float(), x2, mu2, rs2, w, gw2, gb2, 1.0, a.float(), b.float())
     _close(da1, da2, 3e-2, "da"); _close(db1, db2, 3e-2, "db"); _close(gw1, gw2, 2e-2, "gw")
     assert not ck.fallbacks, ck.fallbacks
+
+
+def test_step_bookkeeping_helpers():
+    """The per-cell helpers of the training plan: running-radius kernel, zero pool, GEMM output into a given buffer."""
+    ck, tk = _sets()
+    dev = torch.device("cuda")
+    # running radius: in-place EMA + snapshot, against the PyTorch statement
+    bsq = torch.tensor(3.7e5, device=dev)
+    a1, a2 = torch.tensor(1.25, device=dev), torch.tensor(1.25, device=dev)
+    s1 = ck.anchor_update(bsq, 2048.0 * 3072.0, a1, 0.99)
+    s2 = tk.anchor_update(bsq, 2048.0 * 3072.0, a2, 0.99)
+    assert torch.allclose(a1, a2, rtol=1e-6) and torch.allclose(s1, s2, rtol=1e-6) and s1.data_ptr() != a1.data_ptr()
+    tiny = ck.anchor_update(torch.zeros((), device=dev), 10.0, torch.zeros((), device=dev), 0.0)
+    assert abs(float(tiny) - 1e-4) < 1e-9                                   # the floor of the radius
+    # zero pool: disjoint, aligned, zero slices; ordinary allocation once it is used up
+    ck.begin_step(64 + 5 * 7 + 64, dev)
+    z1, z2 = ck.zeros(1, device=dev), ck.zeros(5, 7, device=dev)
+    z3 = ck.zeros(1000, device=dev)
+    assert z1.data_ptr() % 256 == 0 and z2.data_ptr() % 256 == 0 and z2.data_ptr() - z1.data_ptr() == 256
+    assert z2.shape == (5, 7) and float(z2.abs().sum()) == 0.0 and float(z3.abs().sum()) == 0.0
+    z2.add_(1.0)
+    assert float(z1.sum()) == 0.0
+    # GEMM storing into a caller's packed buffer (a depth-history slot)
+    x, w = bf(300, 256), bf(192, 256, scale=0.1)
+    hist = torch.zeros(3, 300, 2, 6, 16, dtype=torch.bfloat16, device=dev)
+    out = hist[1].view(300, 192)
+    y = ck.linear(x, w, out=out)
+    assert y.data_ptr() == out.data_ptr()
+    _close(hist[1].view(300, 192), x.float() @ w.float().t(), 2e-2, "linear out=")
+    assert float(hist[0].abs().sum()) == 0.0 and float(hist[2].abs().sum()) == 0.0
+    assert not ck.fallbacks, ck.fallbacks

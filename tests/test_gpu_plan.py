@@ -115,3 +115,34 @@ def test_graph_replayed_step_equals_eager_step():
     # compare in the mean and bound the share of visibly different elements
     diff = (p0 - p1).abs()
     assert float(diff.mean()) < 2e-4 and float((diff > 2e-3).float().mean()) < 0.01
+
+
+def test_chunk_checkpointing_reproduces_stored_tape_run():
+    """Activation checkpointing per temporal chunk: same loss, same gradients (up to atomic-order noise), same running
+    radii as the run that keeps every chunk's tape, on the native kernels."""
+    import dataclasses
+    from loomformer_paraplex_b200.ops import kernels
+    from loomformer_paraplex_b200.ops.fused_plan import FusedPlan
+    torch.manual_seed(0)
+    base = Model(Config(**CFG)).cuda().train()
+    with torch.no_grad():
+        for _, p in base.named_parameters():
+            if p.abs().max() == 0:
+                p.normal_(0.0, 0.1)
+    x = torch.randint(0, 512, (4, 256), device="cuda"); y = torch.randint(0, 512, (4, 256), device="cuda")
+    res = []
+    for ckpt in (False, True):
+        m = copy.deepcopy(base)
+        plan = FusedPlan(m, flat=FlatParams(m, want_bf16_shadow=True))
+        plan.d = dataclasses.replace(plan.d, grad_checkpointing=ckpt)
+        with torch.no_grad():
+            loss, _ = plan.run(x, y, None, None, want_grad=True)
+        kernels.check_status(torch.device("cuda"))
+        assert not plan.K.fallbacks, dict(plan.K.fallbacks)
+        res.append((float(loss), torch.cat([p.grad.flatten() for p in m.parameters() if p.grad is not None]),
+                    torch.stack([b.ffn.beta_anchor for b in m.blocks])))
+    (l0, g0, a0), (l1, g1, a1) = res
+    assert abs(l0 - l1) < 1e-6
+    assert torch.allclose(a0, a1, rtol=1e-6)
+    cos = float((g0.double() @ g1.double()) / (g0.double().norm() * g1.double().norm()))
+    assert cos > 0.9999, cos
