@@ -12,6 +12,7 @@ Prefill runs the prompt through the chunked fused forward once and converts its 
 from __future__ import annotations
 
 import math
+import dataclasses
 import os
 from typing import Optional, Tuple
 
@@ -58,9 +59,15 @@ class DecodeEngine:
                 self._ns = max(1, min(16, -(-296 // (B * d.kvh))))
                 n_ws = B * d.kvh * self._ns * (2 * d.group + 2 * d.group * d.hd)
                 self._attn_ws = torch.empty(max(1, n_ws), dtype=torch.float32, device=dev)
-        # fused kernels of the training plan reused at one token per sequence (fewer, larger launches per layer)
-        self._fused = bool(self._native_attn and d.activation == "pvpowlu" and d.hidden % 2 == 0 and d.hd <= 128
-                           and d.hpq % 8 == 0 and d.n % 8 == 0 and d.n <= 1024 and not model.ablation
+        # fused kernels of the training plan reused at one token per sequence (fewer, larger launches per layer).  A
+        # hidden sector that is not a multiple of 8 neurons wide (a SmolLM2 transplant has 171 per head) is padded
+        # with inert neurons inside the FFN part of the step, exactly as the training plan does; the engine's own
+        # state (trace, carry) keeps the model's width.
+        self._dk = d if d.hpq % 8 == 0 else dataclasses.replace(d, hidden=d.qh * ((d.hpq + 7) // 8 * 8),
+                                                                hpq=(d.hpq + 7) // 8 * 8)
+        self._wpad = {}
+        self._fused = bool(self._native_attn and d.activation == "pvpowlu" and d.hd <= 128
+                           and d.n % 8 == 0 and d.n <= 1024 and not model.ablation
                            and os.environ.get("LOOM_DECODE_FUSED", "1") != "0")
         if self._fused:
             from ..ops.kernels import CudaKernels
@@ -73,7 +80,43 @@ class DecodeEngine:
     # ------------------------------------------------------------------ weights in the compute dtype
     def refresh_weights(self) -> None:
         self._w = {id(p): p.detach().to(self.dt) for p in self.m.parameters()}
+        self._wpad = {}
+        if getattr(self, "_fused", False) and self._dk is not self.d:
+            for blk in self.m.blocks:
+                f = blk.ffn
+                rows = [f.w1_real.weight, f.w1_real.bias, f.w1_imag, f.w1_imag_bias, f.w1_imag_trace]
+                if f.gate_proj is not None:
+                    rows += [f.gate_proj.weight, f.gate_proj.bias]
+                for q in rows:
+                    src = q.detach().to(self.dt if q.dim() == 2 else torch.float32)
+                    self._wpad[id(q)] = self._pad(src, 0)
+                self._wpad[id(f.w2.weight)] = self._pad(f.w2.weight.detach().to(self.dt), 1)
         self._graph = None
+
+    def _pad(self, t: torch.Tensor, axis: int) -> torch.Tensor:
+        """Zero-padded copy of ``t`` whose ``axis`` indexes hidden neurons (heads x sector): sector width d.hpq ->
+        the kernels' width."""
+        d, dk = self.d, self._dk
+        if dk is d:
+            return t
+        shape = list(t.shape)
+        out = torch.zeros(*shape[:axis], d.qh, dk.hpq, *shape[axis + 1:], dtype=t.dtype, device=t.device)
+        out.narrow(axis + 1, 0, d.hpq).copy_(t.reshape(*shape[:axis], d.qh, d.hpq, *shape[axis + 1:]))
+        return out.reshape(*shape[:axis], dk.hidden, *shape[axis + 1:])
+
+    def _unpad(self, t: torch.Tensor, axis: int) -> torch.Tensor:
+        d, dk = self.d, self._dk
+        if dk is d:
+            return t
+        shape = list(t.shape)
+        v = t.reshape(*shape[:axis], d.qh, dk.hpq, *shape[axis + 1:]).narrow(axis + 1, 0, d.hpq)
+        return v.reshape(*shape[:axis], d.hidden, *shape[axis + 1:])
+
+    def wk(self, p):
+        """Weight as the fused kernels want it: the padded copy for a neuron-indexed FFN parameter (2-D in the compute
+        dtype, vectors in fp32), the compute-dtype copy otherwise."""
+        v = self._wpad.get(id(p))
+        return v if v is not None else self._w[id(p)]
 
     def w(self, p):
         return self._w[id(p)]
@@ -163,7 +206,7 @@ class DecodeEngine:
         """Same arithmetic as :meth:`_step_composed` with the training plan's kernels at M = batch rows: depth reads,
         residual-add + LayerNorm, the segmented sector GEMM, and the fused Paraplex core (gate, phase, trace, softplus,
         PvPowLU, Tria build / compose / seed / gate readout) are one launch each."""
-        m, d, K = self.m, self.d, self._K
+        m, d, K, dk = self.m, self.d, self._K, self._dk
         B, S, dt = self.B, self.S, self.dt
         pos = self.pos
         h = self.w(m.emb.weight)[self.tok_in]
@@ -209,27 +252,34 @@ class DecodeEngine:
             project(u, sub + 1)
             skip2, d_sel = read(sub + 1)
             ffn = blk.ffn
-            wx = self._lin(u, ffn.w1_real.weight)
-            gate_lin = self._lin(u, ffn.gate_proj.weight, ffn.gate_proj.bias) if ffn.gate_proj is not None else None
-            beta_lin = K.imag_fwd(d, qkc, u, d_sel, self.w(ffn.w1_imag))
+            wx = F.linear(u, self.wk(ffn.w1_real.weight))
+            gate_lin = None
+            if ffn.gate_proj is not None:
+                gate_lin = F.linear(u, self.wk(ffn.gate_proj.weight)) + self.wk(ffn.gate_proj.bias).to(dt)
+            beta_lin = K.imag_fwd(dk, qkc, u, d_sel, self.wk(ffn.w1_imag))
             tria_here = use_tria
+            padded = dk is not d
+            vec = (lambda q: self.wk(q)) if padded else (lambda q: q.data)
             core = K.ffn_core_fwd(
-                d, wx, p_in if ffn.identity_gate is not None else None,
-                ffn.identity_gate.alpha() if ffn.identity_gate is not None else None, ffn.w1_real.bias.data, gate_lin, beta_lin,
-                ffn.w1_imag_bias.data, ffn.w1_imag_trace.data, self.trace[bi], row_reset, None,
-                c_planes if bi > 0 else None, self.carry.view(B, d.hidden, 9) if (tria_here and bi == 0) else None,
+                dk, wx, p_in if ffn.identity_gate is not None else None,
+                ffn.identity_gate.alpha() if ffn.identity_gate is not None else None, vec(ffn.w1_real.bias), gate_lin, beta_lin,
+                vec(ffn.w1_imag_bias), vec(ffn.w1_imag_trace), self._pad(self.trace[bi], 1), row_reset, None,
+                c_planes if bi > 0 else None,
+                self._pad(self.carry.view(B, d.hidden, 9), 1) if (tria_here and bi == 0) else None,
                 seed_valid if (tria_here and bi == 0) else None,
                 ffn.gate_selector.weights().float() if (tria_here and not last) else None,
                 (bi % 3) if tria_here else None, m.tria_alpha if tria_here else 0.0, B)
-            self.trace[bi].copy_(core["trace_out"])
+            self.trace[bi].copy_(self._unpad(core["trace_out"], 1))
             if tria_here:
                 c_planes = core["c"]
                 p_in = None if last else core["p_out"]
-            f = self._lin(core["o"], ffn.w2.weight, ffn.w2.bias)
+            f = F.linear(core["o"], self.wk(ffn.w2.weight)) + self.w(ffn.w2.bias)
             h = K.add_ln_fwd(skip2, f, blk.ln_ffn.weight.data, blk.ln_ffn.bias.data, cap)[0]
             if not last:
                 project(h, sub + 2)
-        carry_c = c_planes.float().permute(1, 2, 0).reshape(B, d.hidden, 3, 3) if use_tria else None
+        carry_c = None
+        if use_tria:
+            carry_c = self._unpad(c_planes.float().permute(1, 2, 0), 1).reshape(B, d.hidden, 3, 3)
         self._finish_step(h, carry_c, is_bos)
 
     def _step_composed(self) -> None:

@@ -362,17 +362,19 @@ def test_decode_attention_kernel(B, S, pos, ns):
     _close(k_ctx, torch.einsum("bhs,bshd->bhd", a, kk), 2e-2, "kctx")
 
 
-def test_decode_engine_graph_matches_model_step_on_gpu():
-    """Graph-replayed decode with the native cache attention follows the module's own step path (bf16 tolerance)."""
+@pytest.mark.parametrize("hidden", [256, 172])
+def test_decode_engine_graph_matches_model_step_on_gpu(hidden):
+    """Graph-replayed decode with the native cache attention follows the module's own step path (bf16 tolerance).
+    ``hidden=172`` is 43 neurons per head: the fused step pads every sector to 48 inert-padded neurons."""
     from loomformer_paraplex_b200.config import Config
     from loomformer_paraplex_b200.models.loomformer import Model
     from loomformer_paraplex_b200.serve.decode import DecodeEngine
     torch.manual_seed(0)
-    cfg = Config(vocab=256, seq_len=96, model_dim=128, n_q_heads=4, head_dim=32, n_kv_heads=2, hidden=256, layers=2,
+    cfg = Config(vocab=256, seq_len=96, model_dim=128, n_q_heads=4, head_dim=32, n_kv_heads=2, hidden=hidden, layers=2,
                  activation="pvpowlu", tria_carry_enabled=True, tria_temporal_auto=False, tria_temporal_window=16)
     model = Model(cfg).cuda().eval()
     eng = DecodeEngine(model, batch=3, use_graph=True)
-    assert eng._native_attn
+    assert eng._native_attn and eng._fused and eng._dk.hpq == (64 if hidden == 256 else 48)
     prompt = torch.randint(0, 256, (3, 40), device="cuda")
     fp = DecodeEngine(model, batch=3, use_graph=False, dtype=torch.float32)
     l1, l2 = eng.prefill(prompt).clone(), fp.prefill(prompt).clone()
@@ -381,6 +383,7 @@ def test_decode_engine_graph_matches_model_step_on_gpu():
     for t in toks:                                           # same forced tokens on both engines; crosses a fire
         l1, l2 = eng.step(t).clone(), fp.step(t).clone()
         _close(l1, l2, 6e-2, "step logits")
+    assert not eng._K.fallbacks, dict(eng._K.fallbacks)
 
 
 def test_add_layernorm_with_rms_cap():
