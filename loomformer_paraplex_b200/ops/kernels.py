@@ -147,7 +147,9 @@ class CudaKernels(TorchKernels):
             n *= int(v)
         pool = getattr(self, "_zpool", None)
         span_ = (n + 63) // 64 * 64                      # keep every slice 256-byte aligned
-        if pool is None or pool.device != torch.device(device) or self._zoff + span_ > pool.numel():
+        dv = torch.device(device)
+        same = pool is not None and pool.device.type == dv.type and dv.index in (None, pool.device.index)
+        if not same or self._zoff + span_ > pool.numel():
             return torch.zeros(*shape, dtype=torch.float32, device=device)
         out = pool[self._zoff:self._zoff + n].view(*shape)
         self._zoff += span_
