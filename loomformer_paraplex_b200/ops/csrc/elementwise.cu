@@ -485,6 +485,9 @@ __global__ void __launch_bounds__(256) ce_kernel(bf16* __restrict__ logits, cons
   bf16* L = logits + row * V;
   const long long tgt = targets[row];
   const bool valid = tgt != ignore_index;
+  // the target's logit is read here, before the block's first barrier: the gradient pass below overwrites the row in
+  // place, and other warps may reach it while thread 0 is still forming the loss
+  const float tgt_logit = (threadIdx.x == 0 && valid) ? __bfloat162float(L[tgt]) : 0.f;
   float mx = -INFINITY;
   for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
     float f[8];
@@ -502,7 +505,7 @@ __global__ void __launch_bounds__(256) ce_kernel(bf16* __restrict__ logits, cons
   }
   se = block_reduce(se, sh, false);
   const float lse = mx + __logf(se);
-  if (threadIdx.x == 0) nll[row] = valid ? lse - __bfloat162float(L[valid ? tgt : 0]) : 0.f;
+  if (threadIdx.x == 0) nll[row] = valid ? lse - tgt_logit : 0.f;
   if (!write_grad) return;
   const float sc = valid ? *scale_ptr : 0.f;
   const float inv = 1.f / se;
