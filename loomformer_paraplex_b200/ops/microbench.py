@@ -143,18 +143,20 @@ def case_attn_bwd(K, M, Tc=128, T=1024):
 def case_dread_slot_bwd(K, M, S=20, slot=5):
     """Gradient of one depth-history slot over the 15 sublayers that read it (10-layer model)."""
     d = dims()
-    hk, hv = bf(S, M, d.qh, d.hd), bf(S, M, d.qh, d.hd)
+    hist = bf(S, M, 2, d.qh, d.hd)                        # rows [K | V], as the training plan keeps the history
+    hk, hv = hist[:, :, 0], hist[:, :, 1]
     q_all = torch.randn(S, d.qh, d.hd, device="cuda")
     dm, lse, dd = bf(S, M, d.qh, d.hd, scale=0.3), torch.randn(S, M, d.qh, device="cuda") + 3, torch.randn(S, M, d.qh, device="cuda")
     gq = torch.zeros(S, d.qh, d.hd, device="cuda")
     run = lambda: K.dread_slot_bwd(d, slot, q_all, hk, hv, dm, lse, dd, gq)
-    dk, dv = run()
-    return run, nbytes(hk[slot], hv[slot], dk, dv) + nbytes(dm[slot:], lse[slot:], dd[slot:]), 0.0
+    dkv = run()                                           # [M, 2, QH, HD]: rows [dK | dV]
+    return run, nbytes(hist[slot], dkv) + nbytes(dm[slot:], lse[slot:], dd[slot:]), 0.0
 
 
 def case_dread_fwd(K, M, S=20, n=11):
     d = dims()
-    hk, hv = bf(S, M, d.qh, d.hd), bf(S, M, d.qh, d.hd)
+    hist = bf(S, M, 2, d.qh, d.hd)
+    hk, hv = hist[:, :, 0], hist[:, :, 1]
     q = torch.randn(d.qh, d.hd, device="cuda")
     run = lambda: K.dread_fwd(d, q, hk, hv, n)
     out, lse = run()
