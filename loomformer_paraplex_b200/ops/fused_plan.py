@@ -24,6 +24,7 @@ from __future__ import annotations
 
 import dataclasses
 import math
+import os
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -73,6 +74,12 @@ class FusedPlan:
                 self._hpad[id(f.w2.weight)] = (f.w2.weight, 1)
         else:
             self.d = d
+        # The depth-read branch of a sublayer (read + readout GEMM) runs on a second stream beside the branch it does
+        # not depend on (attention, resp. the real up-projection), forked and joined inside the cell; in the backward
+        # a slot's gradient is formed beside the attention backward of the layer above.  LOOM_OVERLAP=0 keeps
+        # everything on one stream.  Measured on one B200: 176.4 -> 173.8 ms per step (113M model, 16 x 2048).
+        self._overlap = dev.type == "cuda" and os.environ.get("LOOM_OVERLAP", "1") != "0"
+        self._side = None
         self._wcache: Dict[int, torch.Tensor] = {}
         self._consts: Dict[tuple, torch.Tensor] = {}
         self._fetched: set = set()
@@ -434,11 +441,10 @@ class FusedPlan:
         hist_k[slot] = K.fixed_rms_fwd(k, FANIN_GAIN)
         hist_v[slot] = K.fixed_rms_fwd(v, FANIN_GAIN * d.deepnorm_beta)
 
-    def _project_state_bwd(self, x2d, slot, dstate, hist_k, hist_v, tape_layer, key, into):
-        """Gradient of :meth:`_project_state` w.r.t. its input; accumulates the weight gradient.  The slot's own
-        gradient is formed here, in one pass over every sublayer that read the slot."""
-        m, d, K = self.model, self.d, self.K
-        M = x2d.shape[0]
+    def _slot_grad(self, slot, dstate, hist_k, hist_v, tape_layer, key, M):
+        """Gradient of history slot ``slot`` w.r.t. the K/V projection output, rows [dK | dV], formed in one pass over
+        every sublayer that read the slot (all of them must have been staged)."""
+        d, K = self.d, self.K
         dkv = K.dread_slot_bwd(d, slot, dstate["q"], hist_k, hist_v, dstate["dm"], dstate["lse"], dstate["dd"],
                                dstate["gq"])                              # [M, 2, QH, HD]: rows [dK | dV]
         if d.depth_qkv_rms:
@@ -446,7 +452,14 @@ class FusedPlan:
             dk = K.fixed_rms_bwd(dkv[:, 0], kv[:, :d.n].view(M, d.qh, d.hd), FANIN_GAIN)
             dv = K.fixed_rms_bwd(dkv[:, 1], kv[:, d.n:].view(M, d.qh, d.hd), FANIN_GAIN * d.deepnorm_beta)
             dkv = torch.cat((dk.reshape(M, d.n), dv.reshape(M, d.n)), -1)
-        dkv = dkv.reshape(M, 2 * d.n).to(self.adt)
+        return dkv.reshape(M, 2 * d.n).to(self.adt)
+
+    def _project_state_bwd(self, x2d, slot, dstate, hist_k, hist_v, tape_layer, key, into, dkv=None):
+        """Gradient of :meth:`_project_state` w.r.t. its input; accumulates the weight gradient.  ``dkv``: the slot's
+        gradient if it has been formed already (:meth:`_slot_grad` on the second stream)."""
+        m, K = self.model, self.K
+        if dkv is None:
+            dkv = self._slot_grad(slot, dstate, hist_k, hist_v, tape_layer, key, x2d.shape[0])
         K.linear_wgrad(dkv, x2d, self.g(m.depth_attn.kv_weight))
         return K.linear_dgrad(dkv, self.w(m.depth_attn.kv_weight), out=into, accumulate=True)   # into += dkv @ W
 
@@ -497,9 +510,24 @@ class FusedPlan:
         c_prev, p_in = None, None
         trace_out = []
         use_tria = d.tria and not m.ablation
+        overlap = self._overlap and self.gather_spec is None
+        if overlap:
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=dev)
+            side, main = self._side, torch.cuda.current_stream(dev)
+
+        def depth_branch(sub_):
+            mm, lse_ = K.dread_fwd(d, self._step["q_all"][sub_], hist_k, hist_v, sub_ + 1)
+            return mm, lse_, self._readout_lin(mm.reshape(M, N), sub_)
+
         for bi, blk in enumerate(m.blocks):
             last = bi == L - 1
             t: Dict[str, object] = {"h_in": h}
+            sub = 2 * bi
+            if overlap:                     # depth read 2bi needs only the history: fork it beside attention
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    m1, t["lse1"], s1 = depth_branch(sub)
             # --- attention
             qkv = self.lin(h, blk.attn.qkv_weight).view(B, Tc, -1)
             qkc = torch.empty(M, 3, d.qh, d.hd, dtype=self.adt, device=dev)     # sectors: rotated Q, A@K, A@V
@@ -508,23 +536,30 @@ class FusedPlan:
             t["qkc"] = qkc
             a = self.lin(qkc[:, 2].reshape(M, N), blk.attn.o.weight)
             # --- depth read 2bi, residual, LN
-            sub = 2 * bi
-            m1, t["lse1"] = K.dread_fwd(d, self._step["q_all"][sub], hist_k, hist_v, sub + 1)
+            if overlap:
+                main.wait_stream(side)
+            else:
+                m1, t["lse1"], s1 = depth_branch(sub)
             m1 = m1.reshape(M, N)
-            s1 = self._readout_lin(m1, sub)
             u, t["x1"], t["mean1"], t["rstd1"] = K.add_ln_fwd(s1, a, blk.ln_attn.weight.data, blk.ln_attn.bias.data,
                                                               d.branch_rms_cap)
             t["m1"], t["u"] = m1, u
             if d.branch_rms_cap is not None:
                 t["s1"], t["a"] = s1, a
             self._project_state(u, sub + 1, hist_k, hist_v, t, "u")
-            m2, t["lse2"] = K.dread_fwd(d, self._step["q_all"][sub + 1], hist_k, hist_v, sub + 2)
+            if overlap:                     # depth read 2bi+1 beside the real (and gate) up-projection
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    m2, t["lse2"], s2 = depth_branch(sub + 1)
+            else:
+                m2, t["lse2"], s2 = depth_branch(sub + 1)
             t["m2"] = m2
-            s2 = self._readout_lin(m2.reshape(M, N), sub + 1)
             # --- Paraplex FFN
             ffn = blk.ffn
             x_real = self.lin(u, ffn.w1_real.weight)
             gate_lin = self.lin(u, ffn.gate_proj.weight, self.v(ffn.gate_proj.bias)) if ffn.gate_proj is not None else None
+            if overlap:
+                main.wait_stream(side)
             beta_lin = K.imag_fwd(d, qkc, u, m2, self.w(ffn.w1_imag))
             alpha_gate = self._step["alpha"][bi] if p_in is not None else None
             gate_w = self._step["gate_w"][bi]
@@ -593,13 +628,22 @@ class FusedPlan:
         dseed = None
         dtraces_in: List[Optional[torch.Tensor]] = [None] * L
         cap = d.branch_rms_cap
+        # with the second stream: once sublayer 2bi has been staged, every reader of history slot 2bi is known, so the
+        # slot's gradient is formed beside this layer's attention backward and picked up by the layer below
+        overlap = self._overlap and self.gather_spec is None and self._side is not None
+        if overlap:
+            side, main = self._side, torch.cuda.current_stream(dev)
+        pending = None
         for bi in range(L - 1, -1, -1):
             blk, t = m.blocks[bi], tape["layers"][bi]
             ffn = blk.ffn
             last = bi == L - 1
             sub = 2 * bi
             if not last:
-                dh = self._project_state_bwd(t["h_out"], sub + 2, dst, hist_k, hist_v, t, "h", dh)
+                if pending is not None:
+                    main.wait_stream(side)
+                dh = self._project_state_bwd(t["h_out"], sub + 2, dst, hist_k, hist_v, t, "h", dh, dkv=pending)
+                pending = None
             # --- LN2 and the two addends
             ds2, df = K.add_ln_bwd(dh, t["x2"], t["mean2"], t["rstd2"], blk.ln_ffn.weight.data,
                                    self.g(blk.ln_ffn.weight), self.g(blk.ln_ffn.bias), cap, t.get("s2"), t.get("f"))
@@ -643,6 +687,11 @@ class FusedPlan:
             K.linear_wgrad(ds1, t["m1"], self._readout_g(sub))
             K.dread_stage(d, K.linear_dgrad(ds1, self._readout_w(sub)).view(M, d.qh, d.hd), None,
                           t["m1"].view(M, d.qh, d.hd), t["lse1"], dst, sub)
+            if overlap:
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    below = (tape["layers"][bi - 1], "h") if bi > 0 else (tape["emb_l"], "emb")
+                    pending = self._slot_grad(sub, dst, hist_k, hist_v, below[0], below[1], M)
             # --- attention
             qkc = t["qkc"]
             K.linear_wgrad(da, qkc[:, 2].reshape(M, N), self.g(blk.attn.o.weight))
@@ -652,7 +701,9 @@ class FusedPlan:
                               tape["sin"], self.adt).view(M, -1)
             K.linear_wgrad(dqkv, t["h_in"], self.g(blk.attn.qkv_weight))
             dh = K.linear_dgrad(dqkv, self.w(blk.attn.qkv_weight))
-        dh = self._project_state_bwd(tape["h_emb"], 0, dst, hist_k, hist_v, tape["emb_l"], "emb", dh)
+        if pending is not None:
+            main.wait_stream(side)
+        dh = self._project_state_bwd(tape["h_emb"], 0, dst, hist_k, hist_v, tape["emb_l"], "emb", dh, dkv=pending)
         return dh, dtraces_in, dseed
 
     # ------------------------------------------------------------------ readout
