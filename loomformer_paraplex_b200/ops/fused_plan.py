@@ -380,9 +380,10 @@ class FusedPlan:
             if dseed is not None:
                 dtemporal = dseed if dtemporal is None else dtemporal + dseed
             tape.clear()
+        K.flush_wgrads()           # also joins the weight-gradient stream: with tied embeddings the head's weight
+        #                            gradient and the embedding rows below share one buffer
         self.g(m.emb.weight).index_add_(0, idx.reshape(-1), d_emb.view(B * T, d.n).float())
         self._step_constants_bwd()
-        K.flush_wgrads()
         if self._hpad:
             self._unpad_grads()
         return loss, None

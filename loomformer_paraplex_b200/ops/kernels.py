@@ -10,6 +10,8 @@ from __future__ import annotations
 from collections import Counter
 from typing import List, Optional
 
+import os
+
 import torch
 
 from . import native
@@ -106,6 +108,12 @@ class CudaKernels(TorchKernels):
         self.fallbacks: Counter = Counter()
         self.defer_wgrad = defer_wgrad
         self._wq: dict = {}
+        # grouped weight-gradient launches go to a second stream (nothing reads a weight gradient before the end of
+        # the backward pass); their operands stay referenced until the join in flush_wgrads.  LOOM_WGRAD_STREAM=0
+        # keeps them on the launching stream.
+        self._wg_side = None
+        self._wg_inflight: list = []
+        self._wg_overlap = defer_wgrad and os.environ.get("LOOM_WGRAD_STREAM", "1") != "0"
 
     # ------------------------------------------------------------------ grouped weight gradients
     def _wgrad(self, dy, x, gw, M, N, heads=1):
@@ -128,11 +136,25 @@ class CudaKernels(TorchKernels):
     def _flush_one(self, key):
         dys, xs, gw = self._wq.pop(key)
         _, M, N, heads, _ = key
-        gemm(dys, [t.shape[0] for t in dys], xs, gw, M=M, N=N, heads=heads, a_mn=True, b_mn=True, accumulate=True)
+        if not self._wg_overlap:
+            gemm(dys, [t.shape[0] for t in dys], xs, gw, M=M, N=N, heads=heads, a_mn=True, b_mn=True, accumulate=True)
+            return
+        dev = gw.device
+        if self._wg_side is None:
+            self._wg_side = torch.cuda.Stream(device=dev)
+        side = self._wg_side
+        side.wait_stream(torch.cuda.current_stream(dev))       # the operands were produced on the launching stream
+        with torch.cuda.stream(side):
+            gemm(dys, [t.shape[0] for t in dys], xs, gw, M=M, N=N, heads=heads, a_mn=True, b_mn=True, accumulate=True)
+        self._wg_inflight.append((dys, xs, gw))                # keep the memory from being reused before the join
 
     def flush_wgrads(self) -> None:
+        """Issue what is still queued and make the launching stream wait for every weight-gradient launch."""
         for key in list(self._wq):
             self._flush_one(key)
+        if self._wg_inflight:
+            torch.cuda.current_stream(self._wg_inflight[0][2].device).wait_stream(self._wg_side)
+            self._wg_inflight.clear()
 
     # ------------------------------------------------------------------ small per-cell bookkeeping
     def begin_step(self, zero_floats: int, device) -> None:
