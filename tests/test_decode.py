@@ -51,3 +51,21 @@ def test_prefill_then_decode_matches_stepping(T0):
     for t in range(T0, 30):
         a, b = ref.step(x[:, t]), eng.step(x[:, t])
         assert torch.allclose(a, b, atol=5e-5, rtol=1e-4), (t, float((a - b).abs().max()))
+
+
+def test_sector_padding_helpers_round_trip():
+    """The fused decode step pads every head's hidden sector to a multiple of 8 neurons: padding places sector j of
+    head g at g * padded_width + j, leaves zeros behind it, and un-padding restores the tensor (any axis)."""
+    cfg = Config(vocab=64, seq_len=16, model_dim=32, n_q_heads=4, head_dim=8, n_kv_heads=2, hidden=20, layers=1,
+                 activation="pvpowlu", tria_carry_enabled=True, tria_temporal_auto=False, tria_temporal_window=4)
+    eng = DecodeEngine(Model(cfg).eval(), batch=2, use_graph=False)
+    assert (eng.d.hpq, eng._dk.hpq, eng._dk.hidden) == (5, 8, 32)
+    x = torch.arange(2 * 20 * 3, dtype=torch.float32).view(2, 20, 3) + 1.0
+    p = eng._pad(x, 1)
+    assert p.shape == (2, 32, 3)
+    assert torch.equal(p.view(2, 4, 8, 3)[:, :, :5], x.view(2, 4, 5, 3)) and float(p.view(2, 4, 8, 3)[:, :, 5:].abs().sum()) == 0
+    assert torch.equal(eng._unpad(p, 1), x)
+    w = torch.randn(20, 7)
+    assert torch.equal(eng._unpad(eng._pad(w, 0), 0), w) and eng._pad(w, 0).shape == (32, 7)
+    w2 = torch.randn(6, 20)
+    assert torch.equal(eng._unpad(eng._pad(w2, 1), 1), w2) and eng._pad(w2, 1).shape == (6, 32)
