@@ -63,13 +63,21 @@ class TrainEngine:
         lr_mults = train_lr_overrides(model, cfg) if train_lr else {}
         self.symm = None
         alloc = None
+        self.opt_name = str(optimizer or cfg.optimizer or "adamw").lower()
+        if grad_sync == "fsdp" and self.opt_name != "adamw":
+            # the sharded update exists for AdamW; ATOM keeps its per-block state replicated and runs in the fused
+            # NVLink step (reduce-scatter, ATOM on the own slice, parameter push), which is what is selected instead
+            if not pdist.initialized() or pdist.rank() == 0:
+                print(f"[engine] grad_sync='fsdp' implements AdamW; optimizer {self.opt_name!r} uses the replicated "
+                      "fused step (grad_sync='p2p')", flush=True)
+            grad_sync = "p2p"
+        self.grad_sync = grad_sync
         if grad_sync in ("p2p", "fsdp") and pdist.initialized() and device.type == "cuda":
             from ..parallel.symm import SymmetricBuffers
             self.symm = SymmetricBuffers()
             alloc = self.symm.alloc
         self.flat = FlatParams(model, want_bf16_shadow=(device.type == "cuda"), alloc=alloc)
         no_decay = {"tria_agg.pool.logit_scale_raw"}
-        self.opt_name = str(optimizer or cfg.optimizer or "adamw").lower()
         self.opt = FlatOptimizer(self.flat, self.opt_name, lr=cfg.lr, weight_decay=cfg.weight_decay,
                                  grad_clip=cfg.grad_clip, no_decay=no_decay, lr_mults=lr_mults)
         self.sync = GradSync(self.flat, model, backend=grad_sync, anchor_mode=anchor_mode, symm=self.symm)

@@ -58,3 +58,16 @@ def test_padded_sector_model_keeps_ffn_weights_replicated():
     names = set(sp.gathered.values())
     assert not any(n.endswith(("ffn.w1_real.weight", "ffn.gate_proj.weight", "ffn.w2.weight")) for n in names)
     assert any(n.endswith("attn.qkv_weight") for n in names)
+
+
+def test_sharded_mode_with_atom_selects_the_replicated_fused_step(capsys):
+    """The sharded update exists for AdamW only; asking for it with ATOM must not fail at the first optimizer step but
+    select the replicated fused step when the engine is built."""
+    from loomformer_paraplex_b200.train.engine import TrainEngine
+    cfg = Config(**dict(CFG, batch_size=2, optimizer="atom"))
+    torch.manual_seed(0)
+    eng = TrainEngine(cfg, Model(cfg), torch.device("cpu"), grad_sync="fsdp")
+    assert eng.grad_sync == "p2p" and eng.opt_name == "atom" and eng.sync.shard is None
+    assert "replicated" in capsys.readouterr().out
+    eng2 = TrainEngine(cfg, Model(cfg), torch.device("cpu"), optimizer="adamw", grad_sync="fsdp")
+    assert eng2.grad_sync == "fsdp"
