@@ -101,7 +101,8 @@ def optimizer_step(opt) -> None:
 class CudaKernels(TorchKernels):
     name = "cuda"
 
-    WGRAD_GROUP = 16      # weight-gradient products of this many chunks go out as one launch
+    # weight-gradient products of this many chunks go out as one launch (LOOM_WGRAD_GROUP overrides, 1..16)
+    WGRAD_GROUP = max(1, min(16, int(os.environ.get("LOOM_WGRAD_GROUP", "16"))))
 
     def __init__(self, defer_wgrad: bool = True) -> None:
         native.ext()
