@@ -30,7 +30,6 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--use_fast_math", "-Xcompiler", "-fPIC",
               "--expt-relaxed-constexpr", "-Xptxas", "-v"]
-SINGLE_GPU_ONLY = {"multicast_gemm.cu"}   # sources that multi-GPU snapshots leave out
 
 
 def _hash(paths: List[str], extra: str) -> str:

@@ -97,6 +97,13 @@ void grad_norm(torch::Tensor grads, double max_norm, torch::Tensor partial, torc
   TORCH_CHECK(rc == 0, "loom_grad_norm failed: ", rc);
 }
 
+void status_gate(torch::Tensor status, torch::Tensor stats) {
+  const c10::cuda::CUDAGuard guard(stats.device());
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == torch::kInt32, "status word: int32 CUDA tensor");
+  int rc = loom_status_gate(status.data_ptr<int>(), fptr(stats), cur_stream());
+  TORCH_CHECK(rc == 0, "loom_status_gate failed: ", rc);
+}
+
 void adamw_flat(torch::Tensor p, torch::Tensor g, torch::Tensor m, torch::Tensor v, c10::optional<torch::Tensor> shadow,
                 torch::Tensor lr_mult, torch::Tensor wd, torch::Tensor active, torch::Tensor stats, torch::Tensor hyper) {
   const c10::cuda::CUDAGuard guard(p.device());
@@ -413,6 +420,7 @@ void p2p_grad_step_atom(int64_t W, int64_t rank, int64_t nblk, std::vector<int64
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "segmented-K batched bf16 GEMM (tcgen05 + TMA)");
   m.def("grad_norm", &grad_norm, "global gradient norm, clip coefficient and finite flag");
+  m.def("status_gate", &status_gate, "finite flag &= status word clear; count skipped updates");
   m.def("adamw_flat", &adamw_flat, "AdamW over the flat parameter buffer");
   m.def("atom_flat", &atom_flat, "ATOM over the flat parameter buffer");
   m.def("cast_shadow", &cast_shadow, "fp32 -> bf16 parameter shadow");

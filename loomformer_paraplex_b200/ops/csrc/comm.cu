@@ -138,7 +138,9 @@ __global__ void __launch_bounds__(256) update_allgather_kernel(P2P c, float* __r
   int* my = c.sync[c.rank];
   const int epoch = *w_local(my, c.W, 3) + 1;
   if (blockIdx.x == 0 && threadIdx.x == 0) {
-    const float mine = *sumsq_local;
+    // a bounded wait that gave up anywhere in this step (GEMM barriers, the gradient-ready wait above) makes this
+    // rank's contribution NaN: every rank then sees a non-finite norm and skips the update together
+    const float mine = (*reinterpret_cast<volatile int*>(status) != 0) ? __int_as_float(0x7fc00000) : *sumsq_local;
     for (int p = 0; p < c.W; ++p) *reinterpret_cast<volatile float*>(w_sumsq(c.sync[p], c.W, c.rank)) = mine;
     __threadfence_system();
     for (int p = 0; p < c.W; ++p) st_release_sys(w_normflag(c.sync[p], c.W, c.rank), epoch);
@@ -153,6 +155,7 @@ __global__ void __launch_bounds__(256) update_allgather_kernel(P2P c, float* __r
     stats[0] = norm;
     stats[1] = (max_norm > 0.f && fin) ? fminf(1.f, max_norm / (norm + 1e-6f)) : 1.f;
     stats[2] = fin ? 1.f : 0.f;
+    if (!fin) stats[3] += 1.f;          // sticky count of skipped updates, read at log cadence
     *sumsq_local = 0.f;
     __threadfence();
     st_release_sys(w_local(my, c.W, 1), epoch);
@@ -216,7 +219,7 @@ __global__ void norm_exchange_kernel(P2P c, float* __restrict__ sumsq_local, flo
   if (threadIdx.x != 0) return;
   int* my = c.sync[c.rank];
   const int epoch = *w_local(my, c.W, 3) + 1;
-  const float mine = *sumsq_local;
+  const float mine = (*reinterpret_cast<volatile int*>(status) != 0) ? __int_as_float(0x7fc00000) : *sumsq_local;
   for (int p = 0; p < c.W; ++p) *reinterpret_cast<volatile float*>(w_sumsq(c.sync[p], c.W, c.rank)) = mine;
   __threadfence_system();
   for (int p = 0; p < c.W; ++p) st_release_sys(w_normflag(c.sync[p], c.W, c.rank), epoch);
@@ -231,6 +234,7 @@ __global__ void norm_exchange_kernel(P2P c, float* __restrict__ sumsq_local, flo
   stats[0] = norm;
   stats[1] = (max_norm > 0.f && fin) ? fminf(1.f, max_norm / (norm + 1e-6f)) : 1.f;
   stats[2] = fin ? 1.f : 0.f;
+  if (!fin) stats[3] += 1.f;
   *sumsq_local = 0.f;
 }
 

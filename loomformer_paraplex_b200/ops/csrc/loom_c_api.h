@@ -59,6 +59,8 @@ int loom_gemm_bf16(const LoomGemm* g, cudaStream_t stream);
 // ---- flat optimizer (optim.cu) ----
 int loom_grad_norm(const float* grads, long long n, float max_norm, float* partial, int nparts, float* stats,
                    float* atom_out, cudaStream_t stream);
+// finite flag &= (status word == 0); stats[3] counts skipped updates (sticky)
+int loom_status_gate(const int* status, float* stats, cudaStream_t stream);
 int loom_adamw_flat(float* p, const float* g, float* m, float* v, void* shadow_bf16, const float* lr_mult,
                     const float* wd_blk, const float* active, const float* stats, const float* hyper,
                     long long nblk, cudaStream_t stream);

@@ -153,6 +153,18 @@ extern "C" int loom_grad_norm(const float* grads, long long n, float max_norm, f
   return (int)cudaGetLastError();
 }
 
+// A bounded wait that gave up somewhere in this step (status word != 0) invalidates the gradients as surely as a
+// NaN does: clear the finite flag so the update kernels skip, and keep a sticky count of skipped updates in stats[3].
+__global__ void status_gate_kernel(const int* __restrict__ status, float* __restrict__ stats) {
+  if (status != nullptr && *status != 0) stats[2] = 0.f;
+  if (stats[2] == 0.f) stats[3] += 1.f;
+}
+
+extern "C" int loom_status_gate(const int* status, float* stats, cudaStream_t stream) {
+  status_gate_kernel<<<1, 1, 0, stream>>>(status, stats);
+  return (int)cudaGetLastError();
+}
+
 extern "C" int loom_adamw_flat(float* p, const float* g, float* m, float* v, void* shadow, const float* lr_mult,
                                const float* wd_blk, const float* active, const float* stats, const float* hyper,
                                long long nblk, cudaStream_t stream) {

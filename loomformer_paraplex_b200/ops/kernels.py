@@ -28,6 +28,10 @@ def status_word(device) -> torch.Tensor:
     return _STATUS[key]
 
 
+def has_status_word(device) -> bool:
+    return str(device) in _STATUS
+
+
 def check_status(device) -> None:
     code = int(status_word(device).item())
     if code != 0:
@@ -83,19 +87,20 @@ def upload_hyper(opt) -> torch.Tensor:
 
 
 def optimizer_step(opt) -> None:
-    """Native flat optimizer step (norm -> clip -> AdamW/ATOM -> bf16 shadow), three launches."""
+    """Native flat optimizer step (norm -> clip -> status gate -> AdamW/ATOM -> bf16 shadow), four launches."""
     ext = native.ext()
     f = opt.flat
     upload_hyper(opt)
     atom_out = opt.atom_out if opt.kind == "atom" else None
     ext.grad_norm(f.grads, opt.grad_clip, opt._partial, opt.stats, atom_out)
+    ext.status_gate(status_word(f.device), opt.stats)     # a timed-out wait skips the update like a NaN does
     if opt.kind == "adamw":
         ext.adamw_flat(f.params, f.grads, opt.m, opt.v, f.shadow, opt.lr_mult_blk, opt.wd_blk, opt.active_blk,
                        opt.stats, opt._hyper_dev)
     else:
         ext.atom_flat(f.params, f.grads, opt.m, opt.v, f.shadow, opt.lr_mult_blk, opt.wd_blk, opt.cnt_blk,
                       opt.gprev_blk, opt.pnode_blk, opt.trust_blk, opt.stats, opt._hyper_dev, opt.atom_out)
-    native.count(3)
+    native.count(4)
 
 
 class CudaKernels(TorchKernels):

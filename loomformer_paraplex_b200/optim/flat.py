@@ -139,7 +139,7 @@ class FlatOptimizer:
         self.m = torch.zeros_like(flat.params)
         self.v = torch.zeros_like(flat.params)
         self.step_count = 0
-        # device scalars: [grad_norm, clip_coef, finite(1/0)]
+        # device scalars: [grad_norm, clip_coef, finite(1/0), sticky count of skipped updates]
         self.stats = torch.zeros(4, dtype=torch.float32, device=dev)
         if kind == "atom":
             self.meta_scale = max(1, min(8, int(os.getenv("ATOM_META_SCALE", "1"))))
@@ -168,9 +168,15 @@ class FlatOptimizer:
         else:
             self.stats[1] = 1.0
         self.stats[2] = torch.isfinite(norm).float()
+        self.stats[3] += 1.0 - self.stats[2]
 
     def grads_finite(self) -> bool:
         return bool(self.stats[2].item() > 0.5)
+
+    def skipped_updates(self) -> int:
+        """Updates skipped on the device so far (non-finite gradient norm, or a kernel that gave up a bounded wait);
+        one host sync, meant for log cadence."""
+        return int(self.stats[3].item())
 
     # ------------------------------------------------------------------ update
     @torch.no_grad()
@@ -231,7 +237,13 @@ class FlatOptimizer:
         """Pull ATOM's global statistics to the host (one sync; call at log cadence)."""
         if self.kind != "atom":
             return {}
-        proxy, commits, count = (float(x) for x in self.atom_out.tolist())
+        out = self.atom_out
+        if getattr(self, "stats_shard_local", False):
+            # the fused NVLink step runs ATOM on this rank's block range only: its three sums are partial
+            import torch.distributed as dist
+            out = self.atom_out.clone()
+            dist.all_reduce(out)
+        proxy, commits, count = (float(x) for x in out.tolist())
         if count > 0:
             pm, cf = proxy / count, commits / count
             live = self.cnt_blk > 0

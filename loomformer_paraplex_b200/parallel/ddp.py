@@ -49,6 +49,8 @@ class GradSync:
 
     def attach_optimizer(self, opt) -> None:
         """Sharded mode: the optimizer keeps Adam moments only for the blocks this rank owns."""
+        # fused NVLink step with ATOM: each rank's [proxy, commits, count] sums cover its own block range only
+        opt.stats_shard_local = bool(self.backend == "p2p" and self.world > 1 and opt.kind == "atom")
         if self.shard is not None and getattr(opt, "shard", None) is None:
             opt.m, opt.v = self.shard.compact(opt.m), self.shard.compact(opt.v)
             opt.shard = self.shard

@@ -168,3 +168,44 @@ def broadcast_int(value: int, device: torch.device, src: int = 0) -> int:
 def shutdown() -> None:
     if initialized():
         dist.destroy_process_group()
+
+
+class StepControl:
+    """Rank 0's per-step decisions (interrupt, run-point key, wall-clock stop) made collective.
+
+    Saving a checkpoint is a collective in the fused and sharded gradient modes, so every rank must reach the same
+    decision at the same step.  Only rank 0 watches the keyboard and its clock counts; before each step it publishes
+    a small bit set and every rank acts on that value, never on its own flags.  The value travels through the job's
+    key-value store (a host round trip; no device synchronisation, so the launch queue keeps running ahead) and falls
+    back to a one-int broadcast when no store is reachable.  Single-process runs return the local bits unchanged.
+    """
+    INTERRUPT, RUNPOINT, STOP = 1, 2, 4
+
+    def __init__(self, device: torch.device, prefix: str = "loom/ctl", use_store: bool = True) -> None:
+        self.device, self.prefix = device, prefix
+        self.store = None
+        self._n = 0
+        if initialized() and use_store:
+            try:
+                from torch.distributed import distributed_c10d as c10d
+                self.store = c10d._get_default_store()
+            except Exception:
+                self.store = None
+
+    def agree(self, local_bits: int) -> int:
+        """Call on every rank, once per step, in the same order.  Returns rank 0's ``local_bits``."""
+        if not initialized():
+            return int(local_bits)
+        self._n += 1
+        if self.store is None:
+            return broadcast_int(int(local_bits) if is_main() else 0, self.device)
+        key = f"{self.prefix}/{self._n}"
+        if is_main():
+            self.store.set(key, str(int(local_bits)))
+            if self._n > 64:                       # keep the store small: every rank has long read this one
+                try:
+                    self.store.delete_key(f"{self.prefix}/{self._n - 64}")
+                except Exception:
+                    pass
+            return int(local_bits)
+        return int(self.store.get(key).decode())

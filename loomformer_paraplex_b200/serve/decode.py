@@ -23,6 +23,17 @@ from ..config import FANIN_GAIN
 from ..ops import reference as R
 
 
+def check_request(prompt_len: int, max_new: int, max_len: int) -> None:
+    """Refuse, on the host, a request whose positions would leave the KV cache / RoPE table of ``max_len`` rows."""
+    if prompt_len < 1:
+        raise ValueError("empty prompt")
+    if max_new < 1:
+        raise ValueError(f"max_new={max_new} must be at least 1")
+    if prompt_len + max_new - 1 > max_len:
+        raise ValueError(f"prompt of {prompt_len} tokens + {max_new} new tokens needs {prompt_len + max_new - 1} "
+                         f"positions; this engine holds max_len={max_len}")
+
+
 class DecodeEngine:
     def __init__(self, model, batch: int, max_len: Optional[int] = None, use_graph: bool = True,
                  dtype: Optional[torch.dtype] = None) -> None:
@@ -30,6 +41,10 @@ class DecodeEngine:
         d = self.d
         self.B = int(batch)
         self.S = int(max_len or d.seq_len)
+        if self.S < 1 or self.S > int(d.seq_len):
+            raise ValueError(f"max_len={self.S} is outside 1..seq_len={int(d.seq_len)} (the RoPE table and the "
+                             "position grid end there)")
+        self._host_pos = 0          # host mirror of the device-side position: bounds are refused before any launch
         dev = model.emb.weight.device
         self.dev = dev
         self.dt = dtype or (torch.bfloat16 if dev.type == "cuda" else torch.float32)
@@ -131,13 +146,17 @@ class DecodeEngine:
         for t in (self.kc, self.vc, self.trace, self.carry, self.ca_k, self.ca_v):
             t.zero_()
         self.have_carry.zero_(); self.pending.zero_(); self.ca_valid.zero_(); self.ca_len.zero_(); self.pos.zero_()
+        self._host_pos = 0
 
     @torch.no_grad()
     def prefill(self, prompt: torch.Tensor) -> torch.Tensor:
         """Ingest ``prompt`` [B, T0] (equal lengths) and return the logits of its last position [B, V]."""
-        self.reset()
         B, T0 = prompt.shape
-        assert B == self.B and T0 <= self.S
+        if B != self.B:
+            raise ValueError(f"prompt batch {B} does not match the engine's batch {self.B}")
+        if T0 < 1 or T0 > self.S:
+            raise ValueError(f"prompt length {T0} is outside 1..max_len={self.S}")
+        self.reset()
         plan = self.m._opset(self.m.emb.weight)
         if plan is not None and not self.m.ablation:
             _, logits, st = plan.run(prompt, None, None, None, want_grad=False, return_state=True)
@@ -156,6 +175,7 @@ class DecodeEngine:
                 self.ca_valid[:, :n] = st["ca_valid"]
             self.ca_len.fill_(n)
             self.pos.fill_(T0)
+            self._host_pos = T0
             return logits[:, -1].float()
         out = None
         for t in range(T0):
@@ -165,7 +185,12 @@ class DecodeEngine:
     # ------------------------------------------------------------------ one token
     @torch.no_grad()
     def step(self, tokens: torch.Tensor) -> torch.Tensor:
-        """Feed ``tokens`` [B] at the current position; returns logits [B, V] (a view that the next call overwrites)."""
+        """Feed ``tokens`` [B] at the current position; returns logits [B, V] (a view that the next call overwrites).
+        Raises ``ValueError`` on the host, before anything is launched, when the cache is full."""
+        if self._host_pos >= self.S:
+            raise ValueError(f"decode position {self._host_pos} would pass max_len={self.S}: the KV cache and the "
+                             "RoPE table end there")
+        self._host_pos += 1
         self.tok_in.copy_(tokens)
         if not self.use_graph:
             self._step_impl()
@@ -428,9 +453,14 @@ class DecodeEngine:
         self.pos.add_(1)
 
     # ------------------------------------------------------------------ convenience
+    def check_request(self, prompt_len: int, max_new: int) -> None:
+        """Host-side admission check: the last generated token is fed at position ``prompt_len + max_new - 2``."""
+        check_request(prompt_len, max_new, self.S)
+
     @torch.no_grad()
     def generate(self, prompt: torch.Tensor, max_new: int) -> torch.Tensor:
         """Greedy continuation of an equal-length prompt batch; returns ``[B, max_new]`` token ids."""
+        self.check_request(int(prompt.shape[1]), int(max_new))
         logits = self.prefill(prompt)
         tok = logits.argmax(-1)
         out = [tok]

@@ -44,6 +44,7 @@ def _replica_main(index: int, device: str, path: str, batch: int, max_len: Optio
             return
         rid, prompts, max_new = msg
         try:
+            eng.check_request(len(prompts[0]), int(max_new))     # refuse on the host, before touching the device
             rows = torch.tensor(prompts, dtype=torch.long, device=dev)
             n = rows.shape[0]
             if n < batch:                                   # pad the batch with copies of the first row
@@ -62,6 +63,7 @@ class ReplicaPool:
                  start_timeout: float = 600.0) -> None:
         self.ctx = mp.get_context("spawn")
         self.batch = int(batch)
+        self.max_len = max_len          # None: the replicas use the model's seq_len and check there
         self.outbox = self.ctx.Queue()
         self.inboxes, self.procs = [], []
         for i, dev in enumerate(devices):
@@ -90,6 +92,9 @@ class ReplicaPool:
             return []
         if len({len(p) for p in prompts}) != 1:
             raise ValueError("prompts of one call must have equal length (pad or bucket them first)")
+        if self.max_len is not None:
+            from .decode import check_request
+            check_request(len(prompts[0]), int(max_new), int(self.max_len))
         pending: Dict[int, int] = {}
         for lo in range(0, len(prompts), self.batch):
             rid = self._next_id

@@ -97,6 +97,7 @@ class TrainEngine:
         self.step_idx = 0           # completed optimizer steps
         self.ignore_index = loss_mask_ignore
         self.last_fire_count = torch.zeros((), dtype=torch.long, device=device)
+        self._skipped_seen = 0
 
     # ------------------------------------------------------------------ pieces
     def _autocast(self):
@@ -216,6 +217,7 @@ class TrainEngine:
     def checkpoint_view(self):
         """Object whose ``state_dict()`` is the optimizer state to save.  In sharded mode this completes the fp32
         master parameters and assembles the full moments (collectives: call on every rank)."""
+        self.check_device_status()                  # never checkpoint the result of a step whose waits timed out
         if self.sync.shard is None:
             self.sync.gather_optimizer_state(self.opt)        # no-op unless the fused NVLink step owns the update
             return self.opt
@@ -227,11 +229,26 @@ class TrainEngine:
                 return sd
         return _Frozen()
 
+    def check_device_status(self) -> None:
+        """Raise if a kernel gave up a bounded wait since the last check (status word of this device)."""
+        from ..ops import kernels
+        if kernels.has_status_word(self.device):
+            kernels.check_status(self.device)
+
     def check_finite(self, loss: torch.Tensor) -> None:
-        """Host-side guard (one sync): raise if the loss or the last gradient norm was not finite."""
+        """Host-side guard (one sync): raise if a kernel gave up a bounded wait, if the loss or the last gradient norm
+        was not finite, or if any update since the previous check was skipped on the device."""
+        self.check_device_status()
         lv = float(loss)
         if not math.isfinite(lv):
             raise RuntimeError(f"non-finite training loss: loss={lv:.9g} optimizer={self.opt_name} step={self.step_idx}")
         if not self.opt.grads_finite():
             raise RuntimeError("non-finite gradient detected before optimizer step: "
                                f"optimizer={self.opt_name} step={self.step_idx} (update was skipped on device)")
+        skipped = self.opt.skipped_updates()
+        if skipped > self._skipped_seen:
+            n = skipped - self._skipped_seen
+            self._skipped_seen = skipped
+            raise RuntimeError(f"{n} optimizer update(s) since the last check were skipped on the device "
+                               f"(non-finite gradients or a timed-out wait): optimizer={self.opt_name} "
+                               f"step={self.step_idx}")

@@ -112,9 +112,12 @@ def train_sft(cfg: Config, train_path: str, val_path: Optional[str], init_checkp
     pre = sd.BatchPrefetcher(packer, cfg.batch_size, device, depth=max(2, accum // 4 + 1))
     step, t0, loss = start, time.time(), None
     try:
+        ctl = pdist.StepControl(device)
         with GracefulInterrupt() as intr, RunpointWatcher() as rp:
             while step < int(cfg.steps):
                 loss = engine.step([pre.next() for _ in range(accum)])
+                # rank 0's keyboard and Ctrl-C decide for every rank (saving is a collective)
+                bits = ctl.agree((ctl.INTERRUPT if intr.requested else 0) | (ctl.RUNPOINT if rp.consume() else 0))
                 if step % max(1, int(cfg.log_every)) == 0:
                     engine.check_finite(loss)
                     tl = pdist.mean_float(float(loss), device)
@@ -125,9 +128,9 @@ def train_sft(cfg: Config, train_path: str, val_path: Optional[str], init_checkp
                     if val_packer is not None and step % (max(1, int(cfg.log_every)) * 5) == 0:
                         msg += f"  eval_loss {eval_sft(model, val_packer, cfg.batch_size, device):.4f}"
                     rank0_print(msg)
-                if rp.consume() or (cfg.save_every and (step + 1) % int(cfg.save_every) == 0):
+                if (bits & ctl.RUNPOINT) or (cfg.save_every and (step + 1) % int(cfg.save_every) == 0):
                     runpoint(step + 1)
-                if intr.requested:
+                if bits & ctl.INTERRUPT:
                     rank0_print(f"\n[interrupt] Ctrl-C at step {step}/{cfg.steps} -- saving a runpoint and stopping.")
                     runpoint(step + 1)
                     step += 1

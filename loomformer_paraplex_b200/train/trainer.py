@@ -162,10 +162,12 @@ def train(cfg: Config, dataset: str, device: torch.device, ckpt_out: Optional[st
         rank0_print(f"\n[runpoint] step {at}/{cfg.steps} -- saving, training continues.", flush=True)
         save(p, at)
 
-    if cfg.save_initial_checkpoint and ckpt_out and pdist.is_main():
+    if cfg.save_initial_checkpoint and ckpt_out:
         root, ext = os.path.splitext(ckpt_out)
-        ckpt.save_checkpoint(f"{root}.init{ext or '.pt'}", cfg, model, engine.opt, opt_name, 0, 0, ablation)
-        print(f"[train] saved initial {tag} with optimizer state -> {root}.init{ext or '.pt'}")
+        opt_obj = engine.checkpoint_view()          # collective in the fused / sharded modes: every rank takes part
+        if pdist.is_main():
+            ckpt.save_checkpoint(f"{root}.init{ext or '.pt'}", cfg, model, opt_obj, opt_name, 0, 0, ablation)
+            print(f"[train] saved initial {tag} with optimizer state -> {root}.init{ext or '.pt'}")
 
     note = f"{train_bpt:.3f} bytes/token" if same_eval else f"{train_bpt:.3f} train bytes/token  ·  {eval_bpt:.3f} eval bytes/token"
     rank0_print(f"--- {tag}: {model.num_params():,} params  ·  optimizer={opt_name}  ·  {note} ---")
@@ -181,11 +183,20 @@ def train(cfg: Config, dataset: str, device: torch.device, ckpt_out: Optional[st
     if world > 1 and os.environ.get("LOOM_HEARTBEAT", "1") != "0":
         from ..parallel.health import Heartbeat
         hb = Heartbeat(interval=1.0, max_silence=float(os.environ.get("LOOM_HEARTBEAT_SILENCE", "90")))
+    ctl = pdist.StepControl(device)
+    stop_now = False
     with GracefulInterrupt() as intr, RunpointWatcher() as rp:
         for step in range(start_step + 1, int(cfg.steps) + 1):
             if hb is not None:
                 hb.check()
-            if intr.requested:
+            # rank 0 decides, every rank acts: a checkpoint is a collective, so the keyboard, Ctrl-C and the wall
+            # clock of one rank must never send that rank into it alone
+            bits = ctl.agree((ctl.INTERRUPT if intr.requested else 0) | (ctl.RUNPOINT if rp.consume() else 0) |
+                             (ctl.STOP if stop_now else 0))
+            if bits & ctl.STOP:
+                step -= 1
+                break
+            if bits & ctl.INTERRUPT:
                 flag = 0
                 if pdist.is_main():
                     print(f"\n[interrupt] Ctrl-C at step {step}/{cfg.steps} ({tag}, {time.time() - t0:.0f}s elapsed).", flush=True)
@@ -205,7 +216,7 @@ def train(cfg: Config, dataset: str, device: torch.device, ckpt_out: Optional[st
                 pdist.barrier()
                 pdist.shutdown()
                 raise SystemExit(130)
-            if rp.consume():
+            if bits & ctl.RUNPOINT:
                 save_runpoint(step - 1)
             w0 = time.time()
             micro = [stream.next_batch() for _ in range(accum)]
@@ -243,7 +254,9 @@ def train(cfg: Config, dataset: str, device: torch.device, ckpt_out: Optional[st
             if cfg.save_every and step % int(cfg.save_every) == 0:
                 save_runpoint(step)
             if max_seconds is not None and time.time() - t0 > max_seconds:
-                break
+                if world == 1:
+                    break
+                stop_now = True                     # published by rank 0 before the next step; all ranks leave together
     seconds = time.time() - t0
     save()
     out = {"final_eval_loss": final_eval, "best_eval_loss": best_eval, "full_eval_loss": float("nan"),

@@ -104,10 +104,34 @@ def tensor_parallel_case(out, dev, world, rank):
     pdist.shutdown()
 
 
+def control_case(out, dev, world, rank):
+    """Only rank 0 sees the run-point key / Ctrl-C / the wall clock; every rank must act on rank 0's value at the same
+    step, and flags raised on other ranks must not leak into the decision."""
+    import torch.distributed as dist
+    ctl = pdist.StepControl(dev)
+    seen = []
+    for it in range(8):
+        if rank == 0:
+            local = (ctl.RUNPOINT if it == 3 else 0) | (ctl.STOP if it == 6 else 0)
+        else:
+            local = ctl.INTERRUPT if it == 2 else 0          # must be ignored: only rank 0 decides
+        seen.append(ctl.agree(local))
+    fallback = pdist.StepControl(dev, use_store=False)
+    seen.append(fallback.agree(ctl.RUNPOINT if rank == 0 else ctl.INTERRUPT))
+    t = torch.tensor(seen, dtype=torch.long)
+    lst = [torch.zeros_like(t) for _ in range(world)]
+    dist.all_gather(lst, t)
+    if rank == 0:
+        torch.save({"per_rank": [x.tolist() for x in lst]}, out)
+    pdist.shutdown()
+
+
 def main():
     mode, out, device_kind = sys.argv[1], sys.argv[2], sys.argv[3]
     dev, world, rank = pdist.init(device_kind)
     torch.manual_seed(0)
+    if mode == "control":
+        return control_case(out, dev, world, rank)
     if mode == "gather":
         return gather_gemm_case(out, dev, world, rank)
     if mode == "tp":

@@ -69,3 +69,28 @@ def test_sector_padding_helpers_round_trip():
     assert torch.equal(eng._unpad(eng._pad(w, 0), 0), w) and eng._pad(w, 0).shape == (32, 7)
     w2 = torch.randn(6, 20)
     assert torch.equal(eng._unpad(eng._pad(w2, 1), 1), w2) and eng._pad(w2, 1).shape == (6, 32)
+
+
+def test_decode_requests_beyond_the_cache_are_refused_on_the_host():
+    """A prompt + continuation that would pass the KV cache / RoPE table must raise before anything is launched."""
+    from loomformer_paraplex_b200.serve import decode as dec
+    with pytest.raises(ValueError):
+        dec.check_request(100, 30, 128)
+    dec.check_request(100, 29, 128)
+    with pytest.raises(ValueError):
+        dec.check_request(0, 4, 128)
+    with pytest.raises(ValueError):
+        dec.check_request(4, 0, 128)
+    model = _model()
+    with pytest.raises(ValueError):
+        dec.DecodeEngine(model, batch=1, max_len=41, use_graph=False)
+    eng = dec.DecodeEngine(model, batch=1, max_len=8, use_graph=False)
+    prompt = torch.randint(0, 61, (1, 6))
+    with pytest.raises(ValueError):
+        eng.generate(prompt, 4)                  # needs 9 positions
+    out = eng.generate(prompt, 3)                # needs exactly 8
+    assert out.shape == (1, 3)
+    with pytest.raises(ValueError):
+        eng.step(out[:, -1])                     # position 8 does not exist
+    with pytest.raises(ValueError):
+        eng.prefill(torch.randint(0, 61, (1, 9)))

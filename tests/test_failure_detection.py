@@ -53,3 +53,52 @@ def test_bounded_device_wait_reports_instead_of_hanging():
         kernels.check_status(dev)
     assert int(status.item()) == 0                                 # cleared by the check; later work is unaffected
     assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0
+
+
+def _tiny_engine():
+    from loomformer_paraplex_b200.config import Config
+    from loomformer_paraplex_b200.models.loomformer import Model
+    from loomformer_paraplex_b200.train.engine import TrainEngine
+    torch.manual_seed(0)
+    cfg = Config(vocab=64, seq_len=16, model_dim=None, n_q_heads=2, head_dim=8, n_kv_heads=1, hidden=None,
+                 hidden_mult=2.0, layers=2, tied_embeddings=False, tria_carry_enabled=True, tria_temporal_auto=False,
+                 tria_temporal_window=8, tria_carrier_alpha=0.05, lr=1e-3, warmup_steps=1, steps=4, grad_clip=1.0,
+                 amp_dtype="fp32")
+    dev = torch.device("cpu")
+    return TrainEngine(cfg, Model(cfg), dev, optimizer="adamw"), cfg
+
+
+def test_training_loop_raises_when_a_kernel_gave_up_a_wait():
+    """The status word that bounded device waits set must surface in the training loop's own guard (log cadence and
+    before every checkpoint), not only in benchmarks."""
+    from loomformer_paraplex_b200.ops import kernels
+    eng, cfg = _tiny_engine()
+    batch = torch.randint(0, cfg.vocab, (2, cfg.seq_len + 1))
+    loss = eng.step(batch)
+    eng.check_finite(loss)                                   # healthy step passes
+    word = kernels.status_word(eng.device)
+    try:
+        word.fill_(401)
+        with pytest.raises(RuntimeError, match="bounded wait"):
+            eng.check_finite(loss)
+        assert int(word.item()) == 0                         # reported once, then cleared
+        word.fill_(103)
+        with pytest.raises(RuntimeError, match="bounded wait"):
+            eng.checkpoint_view()
+    finally:
+        word.zero_()
+        kernels._STATUS.pop(str(eng.device), None)
+
+
+def test_skipped_updates_between_log_lines_are_reported():
+    """A non-finite step is skipped on the device; the next guard call must say so even if later steps were fine."""
+    eng, cfg = _tiny_engine()
+    batch = torch.randint(0, cfg.vocab, (2, cfg.seq_len + 1))
+    before = eng.flat.params.clone()
+    eng.flat.grads.fill_(float("nan"))
+    eng.opt.step()                                           # skipped: parameters untouched
+    assert torch.equal(before, eng.flat.params)
+    loss = eng.step(batch)                                   # a healthy step afterwards
+    with pytest.raises(RuntimeError, match="skipped"):
+        eng.check_finite(loss)
+    eng.check_finite(eng.step(batch))                        # counted once

@@ -27,6 +27,15 @@ def test_gloo_ddp_ranks_stay_in_sync(tmp_path, nproc):
     assert res["losses"][-1] < res["losses"][0]
 
 
+def test_rank0_decisions_reach_every_rank(tmp_path):
+    """A run-point key pressed on rank 0 (the only rank that watches the keyboard) must send every rank into the
+    collective checkpoint at the same step; flags raised elsewhere are ignored."""
+    res = _launch("control", str(tmp_path / "ctl.pt"), "cpu", 2, 29631)
+    r0, r1 = res["per_rank"]
+    assert r0 == r1
+    assert r0 == [0, 0, 0, 2, 0, 0, 4, 0, 2]
+
+
 @pytest.mark.gpu
 def test_fused_p2p_step_matches_nccl_baseline(tmp_path):
     if torch.cuda.device_count() < 2:

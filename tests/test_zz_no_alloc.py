@@ -37,11 +37,18 @@ def test_static_scratch_grad_norm_matches_regular_entry_point_twice():
         rc = lib.loom_grad_norm(grads.data_ptr(), n, max_norm, partial.data_ptr(), nparts, want.data_ptr(),
                                 atom_a.data_ptr(), stream)
         assert rc == 0
+        if call == 1:
+            # the first call on a device looked the array's address up; from the second call on the driver's own count
+            # of free bytes must not move (torch's counter alone would not see a raw cudaMalloc inside the library)
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info(dev)[0]
         before = torch.cuda.memory_allocated()
         rc = lib.loom_grad_norm_static(grads.data_ptr(), n, max_norm, nparts, got.data_ptr(), atom_b.data_ptr(), stream)
         assert rc == 0, lib.loom_static_strerror(rc)
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        if call == 1:
+            assert torch.cuda.mem_get_info(dev)[0] == free_before
         ref = grads.double().norm().item()
         assert abs(got[0].item() - ref) <= 1e-4 * ref
         assert torch.allclose(got[:3], want[:3], rtol=1e-6, atol=0.0)
@@ -55,6 +62,23 @@ def test_static_scratch_grad_norm_matches_regular_entry_point_twice():
     rc = lib.loom_grad_norm_static(grads.data_ptr(), n, 1.0, nparts, got.data_ptr(), None, stream)
     torch.cuda.synchronize()
     assert rc == 0 and got[2].item() == 0.0 and got[1].item() == 1.0
+
+
+def test_static_scratch_has_its_own_array_on_a_second_device():
+    """Each device that loads the library holds its own copy of the array and its own cached address."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    lib = _lib()
+    for idx in (1, 0, 1):
+        dev = torch.device("cuda", idx)
+        with torch.cuda.device(dev):
+            stream = torch.cuda.current_stream(dev).cuda_stream
+            grads = torch.full((256 * 64,), 0.5, device=dev)
+            got = torch.zeros(4, device=dev)
+            rc = lib.loom_grad_norm_static(grads.data_ptr(), grads.numel(), 0.0, 16, got.data_ptr(), None, stream)
+            assert rc == 0, lib.loom_static_strerror(rc)
+            torch.cuda.synchronize(dev)
+            assert abs(got[0].item() - 0.5 * (256 * 64) ** 0.5) < 1e-3 and got[2].item() == 1.0
 
 
 def test_static_scratch_refuses_what_does_not_fit():
