@@ -92,12 +92,21 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=None, help="debug only: a non-default value makes the number invalid")
     ap.add_argument("--grad-sync", default="auto", choices=["auto", "collective", "p2p", "fsdp"])
+    ap.add_argument("--secondary", default="auto", choices=["auto", "on", "off"],
+                    help="after the headline, measure the other benchmark configurations in the same process and report "
+                         "them under 'secondary' (smol360 training, decode at batch 1 and 64, SFT); auto: on for the "
+                         "default headline run")
+    ap.add_argument("--secondary-budget", type=float, default=240.0,
+                    help="wall-clock seconds the secondary measurements may take in total; what does not fit is "
+                         "reported as unavailable")
     ap.add_argument("--workload", default="pretrain", choices=["pretrain", "sft"],
                     help="sft: synthetic multi-turn chats rendered through the chat template, packed to seq_len, "
                          "assistant-only loss (a secondary benchmark; the headline metric is pretrain)")
     a = ap.parse_args()
     if a.micro_batch is None:
         a.micro_batch = 8 if a.model == "smol360" else 16
+    if a.secondary == "auto":
+        a.secondary = "on" if (a.model == "113m" and a.workload == "pretrain" and a.layers is None) else "off"
     return a
 
 
@@ -165,8 +174,7 @@ def emit(args, impl, ms, clocks, world, extra):
         "clocks": clocks,
         "config": {"model": "113M reference architecture (cfg/nano.yaml dims; BASELINE names it cfg/chk.yaml)",
                    "global_batch": args.micro_batch * world, "seq_len": args.seq_len,
-                   "parallelism": (f"fsdp{world}" if getattr(args, "grad_sync", "") == "fsdp" else f"dp{world}"),
-                   "grad_sync": getattr(args, "grad_sync", "auto"), "optimizer": args.optimizer,
+                   "parallelism": f"dp{world}", "optimizer": args.optimizer,
                    "l2": "per-step working set >> 126 MB L2, no explicit flush",
                    "layers": MODEL_KW["layers"] if args.layers is None else args.layers},
     }
@@ -183,47 +191,51 @@ def emit(args, impl, ms, clocks, world, extra):
     print(json.dumps(line), flush=True)
 
 
-def run_ours(args):
-    import torch
-    import torch.distributed as dist
+def make_cfg(args, model_name):
     from loomformer_paraplex_b200.config import Config
-    from loomformer_paraplex_b200.data.synthetic import SyntheticTokens
-    from loomformer_paraplex_b200.models.loomformer import Model
-    from loomformer_paraplex_b200.ops import native
-    from loomformer_paraplex_b200.parallel import dist as pdist
-    from loomformer_paraplex_b200.train.engine import TrainEngine
-
-    dev, world, rank = pdist.init("cuda")
-    if args.model == "smol360":
+    if model_name == "smol360":
         cfg = Config.from_yaml(os.path.join(ROOT, "cfg", "smol360.yaml"))
         cfg.batch_size, cfg.seq_len, cfg.optimizer, cfg.tokenizer = args.micro_batch, args.seq_len, args.optimizer, None
         cfg.grad_checkpointing = False            # 180 GB of HBM holds the activations of 8 x 2048 tokens
         if args.layers is not None:
             cfg.layers = args.layers
-    else:
-        kw = dict(MODEL_KW, batch_size=args.micro_batch, seq_len=args.seq_len, optimizer=args.optimizer)
-        if args.layers is not None:
-            kw["layers"] = args.layers
-        cfg = Config(**kw)
+        return cfg
+    kw = dict(MODEL_KW, batch_size=args.micro_batch, seq_len=args.seq_len, optimizer=args.optimizer)
+    if args.layers is not None:
+        kw["layers"] = args.layers
+    return Config(**kw)
+
+
+def make_engine(args, cfg, dev, world):
+    """Model + engine.  auto: one GPU needs no exchange; several GPUs use the fused NVLink step (reduce-scatter +
+    optimizer + all-gather over peer memory) and fall back to the NCCL all-reduce only if peer-mapped buffers cannot
+    be set up here.  Returns (engine, name of the gradient path)."""
+    import torch
+    from loomformer_paraplex_b200.models.loomformer import Model
+    from loomformer_paraplex_b200.train.engine import TrainEngine
+    sync = ("p2p" if world > 1 else "collective") if args.grad_sync == "auto" else args.grad_sync
     torch.manual_seed(cfg.seed)
     model = Model(cfg).to(dev)
-    # auto: one GPU needs no exchange; several GPUs use the fused NVLink step (reduce-scatter + optimizer + all-gather
-    # over peer memory) and fall back to the NCCL all-reduce only if peer-mapped buffers cannot be set up here
-    sync = ("p2p" if world > 1 else "collective") if args.grad_sync == "auto" else args.grad_sync
     try:
-        engine = TrainEngine(cfg, model, dev, optimizer=args.optimizer, grad_sync=sync)
+        return TrainEngine(cfg, model, dev, optimizer=args.optimizer, grad_sync=sync), sync
     except Exception as e:
         if args.grad_sync != "auto" or sync == "collective":
             raise
         print(f"[bench] fused NVLink step unavailable ({type(e).__name__}: {e}); using the NCCL all-reduce", file=sys.stderr)
-        sync = "collective"
         torch.manual_seed(cfg.seed)
         model = Model(cfg).to(dev)
-        engine = TrainEngine(cfg, model, dev, optimizer=args.optimizer, grad_sync=sync)
-    args.grad_sync = sync
+        return TrainEngine(cfg, model, dev, optimizer=args.optimizer, grad_sync="collective"), "collective"
+
+
+def measure_training(args, cfg, engine, dev, world, rank, workload, steps, warmup):
+    """Device-timed and end-to-end step time of `engine` on `workload`; returns a dict of raw figures."""
+    import torch
+    import torch.distributed as dist
+    from loomformer_paraplex_b200.data.synthetic import SyntheticTokens
+    from loomformer_paraplex_b200.ops import kernels, native
     state = {"i": 0}
     loss_host = torch.zeros((), dtype=torch.float32).pin_memory()
-    if args.workload == "sft":
+    if workload == "sft":
         host = sft_batches(cfg.vocab, args.micro_batch, args.seq_len, rank)
         to_dev = lambda b: {k: v.to(dev, non_blocking=True) for k, v in b.items() if torch.is_tensor(v)}
         resident = [to_dev(b) for b in host]
@@ -252,26 +264,185 @@ def run_ours(args):
             loss_host.copy_(loss, non_blocking=True)
             torch.cuda.current_stream().synchronize()
 
-    ms, clocks = timed_loop(torch, dist, step_device, args.steps, args.warmup, world, before=native.reset_launches)
+    ms, clocks = timed_loop(torch, dist, step_device, steps, warmup, world, before=native.reset_launches)
     launches = native.launches()
-    ms_e2e, _ = timed_loop(torch, dist, step_e2e, args.steps, 3, world)
+    ms_e2e, _ = timed_loop(torch, dist, step_e2e, steps, 3, world)
     engine.check_finite(loss_host)
-    from loomformer_paraplex_b200.ops import kernels
     kernels.check_status(dev)
+    fb = dict(getattr(engine.plan.K, "fallbacks", {})) if engine.plan is not None else {}
+    return {"ms": ms, "ms_e2e": ms_e2e, "clocks": clocks, "launches": int(launches), "h2d": int(h2d),
+            "fallbacks": fb, "loss": float(loss_host)}
+
+
+def measure_decode(cfg_kw, dev, world, batch, prompt_len, new):
+    """Greedy decode under CUDA-graph replay: `batch` prompts of `prompt_len` uniform-random tokens, `new` steps.
+    One replica per rank; device-timed, max over ranks; tokens/s summed over replicas."""
+    import torch
+    import torch.distributed as dist
+    from loomformer_paraplex_b200.config import Config
+    from loomformer_paraplex_b200.models.loomformer import Model
+    from loomformer_paraplex_b200.serve.decode import DecodeEngine
+    cfg = Config(**cfg_kw)
+    torch.manual_seed(1)
+    model = Model(cfg).to(dev).eval()
+    eng = DecodeEngine(model, batch=batch, max_len=prompt_len + new + 1, use_graph=True)
+    g = torch.Generator(device="cpu").manual_seed(5 + int(os.environ.get("RANK", "0")))
+    prompt_host = torch.randint(0, cfg.vocab, (batch, prompt_len), generator=g).pin_memory()
+    prompt = prompt_host.to(dev)
+    for _ in range(3):                                        # warm-up incl. graph capture
+        eng.generate(prompt, 4)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    e0.record()
+    logits = eng.prefill(prompt)
+    tok = logits.argmax(-1)
+    e1.record()
+    for _ in range(new):
+        eng.step(tok)
+        tok = eng.next_tok
+    e2.record()
+    torch.cuda.synchronize()
+    # end to end through the public call: prompt from pinned host memory, generated ids back to the host
+    t0 = time.perf_counter()
+    out = eng.generate(prompt_host.to(dev, non_blocking=True), new).cpu()
+    wall = time.perf_counter() - t0
+    t = torch.tensor([e0.elapsed_time(e1), e1.elapsed_time(e2), wall * 1e3], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    pre_ms, dec_ms, e2e_ms = (float(x) for x in t.tolist())
+    del eng, model
+    return {"replicas": world, "batch_per_replica": batch, "prompt": prompt_len, "new": new,
+            "prefill_tok_s": world * batch * prompt_len / (pre_ms / 1e3),
+            "decode_tok_s": world * batch * new / (dec_ms / 1e3), "ms_per_decode_step": dec_ms / new,
+            "e2e_generate_tok_s": world * batch * new / (e2e_ms / 1e3),
+            "h2d_bytes": int(prompt_host.numel() * 8), "d2h_bytes": int(out.numel() * 8),
+            "unit": "tokens/s", "graph_replay": True}
+
+
+def secondary_ours(args, dev, world, rank, deadline):
+    """The benchmark configurations that are not the headline, measured after it in the same process."""
+    import copy
+    import gc
+    import torch
+    out = {}
+
+    def guarded(name, fn):
+        skip = deadline - time.time() < 20.0
+        if world > 1:
+            from loomformer_paraplex_b200.parallel import dist as pdist
+            skip = bool(pdist.max_float(1.0 if skip else 0.0, dev) > 0.5)       # one decision for all ranks
+        if skip:
+            out[name] = {"unavailable": f"secondary time budget used up before this measurement ({args.secondary_budget:.0f}s)"}
+            return
+        try:
+            out[name] = fn()
+        except Exception as e:
+            out[name] = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+        gc.collect()
+        torch.cuda.empty_cache()
+
+    for batch in (1, 64):
+        guarded(f"decode_b{batch}", lambda: measure_decode(dict(MODEL_KW), dev, world, batch, 512, 256))
+
+    def smol():
+        a = copy.copy(args)
+        a.model, a.micro_batch = "smol360", 8
+        cfg = make_cfg(a, "smol360")
+        engine, path = make_engine(a, cfg, dev, world)
+        r = measure_training(a, cfg, engine, dev, world, rank, "pretrain", 5, 3)
+        tokens = a.micro_batch * a.seq_len * world
+        return {"metric": "train tokens/s (cfg/smol360.yaml, 467M parameters, bf16, micro-batch 8 x seq 2048 per GPU)",
+                "value": tokens / (r["ms"] / 1e3), "unit": "tokens/s", "ms_per_step": r["ms"], "steps": 5, "warmup": 3,
+                "e2e_value": tokens / (r["ms_e2e"] / 1e3), "grad_path": path, "gpu_launches": r["launches"],
+                "library_fallback_calls": r["fallbacks"], "final_loss": r["loss"]}
+    guarded("smol360", smol)
+
+    def sft():
+        a = copy.copy(args)
+        cfg = make_cfg(a, "113m")
+        engine, path = make_engine(a, cfg, dev, world)
+        r = measure_training(a, cfg, engine, dev, world, rank, "sft", 6, 3)
+        tokens = a.micro_batch * a.seq_len * world
+        return {"metric": "SFT train tokens/s (113M, packed synthetic chats, assistant-only loss, seq 2048)",
+                "value": tokens / (r["ms"] / 1e3), "unit": "tokens/s", "ms_per_step": r["ms"], "steps": 6, "warmup": 3,
+                "e2e_value": tokens / (r["ms_e2e"] / 1e3), "grad_path": path, "gpu_launches": r["launches"],
+                "library_fallback_calls": r["fallbacks"], "final_loss": r["loss"]}
+    guarded("sft", sft)
+    return out
+
+
+def run_ours(args):
+    import gc
+    import torch
+    from loomformer_paraplex_b200.parallel import dist as pdist
+
+    dev, world, rank = pdist.init("cuda")
+    cfg = make_cfg(args, args.model)
+    engine, path = make_engine(args, cfg, dev, world)
+    r = measure_training(args, cfg, engine, dev, world, rank, args.workload, args.steps, args.warmup)
+    extra = {}
+    if args.secondary == "on":
+        del engine
+        gc.collect()
+        torch.cuda.empty_cache()
+        extra["secondary"] = secondary_ours(args, dev, world, rank, time.time() + args.secondary_budget)
     if rank == 0:
         tokens = args.micro_batch * args.seq_len * world
-        fb = dict(getattr(engine.plan.K, "fallbacks", {})) if engine.plan is not None else {}
-        emit(args, "ours", ms, clocks, world, {
-            "e2e": {"value": tokens / (ms_e2e / 1000.0), "unit": "tokens/s",
-                    "h2d_bytes_per_step": int(h2d),
-                    "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e},
-            "gpu_launches": int(launches),
-            "library_fallback_calls": fb, "final_loss": float(loss_host)})
+        emit(args, "ours", r["ms"], r["clocks"], world, dict({
+            "e2e": {"value": tokens / (r["ms_e2e"] / 1000.0), "unit": "tokens/s", "h2d_bytes_per_step": r["h2d"],
+                    "d2h_bytes_per_step": 4, "ms_per_step": r["ms_e2e"]},
+            "gpu_launches": r["launches"], "grad_path": path,
+            "library_fallback_calls": r["fallbacks"], "final_loss": r["loss"]}, **extra))
     pdist.shutdown()
 
 
+def reference_dir():
+    """Where the unmodified reference tree lives.  Its own loader rebuilds an extension whenever the absolute source
+    paths recorded in its ninja files change, so when those files name a path that still points at this tree (a
+    symbolic link to the same folder) that path is used: the pre-built objects are then reused instead of compiled
+    again (several minutes per fresh machine otherwise)."""
+    here = os.path.join(ROOT, "baseline", "_ref")
+    ninja = os.path.join(here, "kernels", "build", "loomformer_pvpowlu", "build.ninja")
+    try:
+        with open(ninja) as fh:
+            for line in fh:
+                if "cuda_compile" in line and line.startswith("build "):
+                    built = line.split("cuda_compile", 1)[1].strip()
+                    cand = built.split(os.sep + "kernels" + os.sep)[0]
+                    if os.path.isdir(cand) and os.path.samefile(cand, here):
+                        return cand
+    except OSError:
+        pass
+    return here
+
+
+def settle_reference_mtimes(ref_dir):
+    """A copy of the tree to another machine may scramble file times; ninja compares them.  Order them the way a
+    finished build leaves them (sources < objects < libraries).  File contents are untouched."""
+    kdir = os.path.join(ref_dir, "kernels")
+    now = time.time()
+    try:
+        for base, dirs, files in os.walk(kdir):
+            in_build = os.sep + "build" in base[len(kdir):]
+            for f in files:
+                path = os.path.join(base, f)
+                if not in_build:
+                    stamp = now - 3 * 86400
+                elif f.endswith(".o"):
+                    stamp = now - 2 * 86400
+                elif f.endswith(".so"):
+                    stamp = now - 86400
+                else:
+                    continue
+                os.utime(path, (stamp, stamp))
+    except OSError:
+        pass
+
+
 def run_reference(args):
-    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    ref_dir = reference_dir()
     if not os.path.isfile(os.path.join(ref_dir, "loomformer.py")):
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is absent (the reference is a script "
                           "tree without setup.py/pyproject.toml; it is installed by copying it there)"}))
@@ -279,11 +450,13 @@ def run_reference(args):
     sys.dont_write_bytecode = True
     sys.path.insert(0, ref_dir)
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0")
+    if int(os.environ.get("LOCAL_RANK", "0")) == 0:
+        settle_reference_mtimes(ref_dir)
     import math
-    import contextlib
     import torch
     import torch.distributed as dist
     import torch.nn.functional as F
+    t_start = time.time()
     import loomformer as lf            # the reference's module (baseline/_ref is first on sys.path)
     from torch.nn.parallel import DistributedDataParallel as DDP
 
@@ -293,82 +466,207 @@ def run_reference(args):
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl")
+        dist.barrier(device_ids=[local])        # rank 0 of the node has settled the file times
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     lf.device_auto(f"cuda:{local}")
-    cfg = lf.Config.from_yaml(os.path.join(ref_dir, "cfg", "smol360.yaml" if args.model == "smol360" else "nano.yaml"))
-    cfg.seq_len, cfg.batch_size, cfg.optimizer, cfg.device = args.seq_len, args.micro_batch, args.optimizer, f"cuda:{local}"
-    if args.layers is not None:
-        cfg.layers = args.layers
-    lf.CARRY_TOKEN_ID = None
-    lf.set_seed(int(cfg.seed) + 1000003 * rank)
-    lf.apply_config(cfg)
-    base = lf.Model(cfg).to(dev)
-    model = base
-    if world > 1:           # same wrapper arguments as the reference trainer
-        model = DDP(base, device_ids=[local], output_device=local, find_unused_parameters=False,
-                    bucket_cap_mb=64, gradient_as_bucket_view=True, static_graph=True)
-    named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
-    params = [p for _, p in named]
-    Opt, opt_name = lf.optimizer_class_from_name(cfg.optimizer)
-    nodecay = {id(base.tria_agg.pool.logit_scale_raw)} if base.tria_agg is not None else set()
-    groups = {}
-    for p in params:
-        groups.setdefault((0.0 if id(p) in nodecay else cfg.weight_decay, 1.0), []).append(p)
-    opt = Opt([{"params": ps, "weight_decay": wd, "lr_mult": mult} for (wd, mult), ps in groups.items()],
-              lr=cfg.lr, weight_decay=cfg.weight_decay)
-    g = torch.Generator().manual_seed(int(cfg.seed) + 1000003 * rank)
-    host = [torch.randint(0, lf.VOCAB, (args.micro_batch, args.seq_len + 1), generator=g).pin_memory() for _ in range(4)]
-    resident = [b.to(dev) for b in host]
-    state = {"i": 0, "step": 0, "loss": 0.0}
 
-    def nonfinite(which):
-        for _, p in named:
-            t = p.grad if which == "grad" else p
-            if t is not None and not torch.isfinite(t.detach()).all():
-                return True
-        return False
+    def train_arm(model_name, micro_batch, workload, steps, warmup, deadline=None):
+        """Body of the reference training loop (loomformer.py:5071-5170) on its own Model, DDP wrapper and optimizer."""
+        cfg = lf.Config.from_yaml(os.path.join(ref_dir, "cfg", "smol360.yaml" if model_name == "smol360" else "nano.yaml"))
+        cfg.seq_len, cfg.batch_size, cfg.optimizer, cfg.device = args.seq_len, micro_batch, args.optimizer, f"cuda:{local}"
+        if args.layers is not None:
+            cfg.layers = args.layers
+        lf.CARRY_TOKEN_ID = None
+        lf.set_seed(int(cfg.seed) + 1000003 * rank)
+        lf.apply_config(cfg)
+        if rank == 0:
+            print(f"[bench] reference: extensions loaded and config applied {time.time() - t_start:.0f}s after start "
+                  f"({model_name}, {workload})", file=sys.stderr, flush=True)
+        base = lf.Model(cfg).to(dev)
+        model = base
+        if world > 1:           # same wrapper arguments as the reference trainer
+            model = DDP(base, device_ids=[local], output_device=local, find_unused_parameters=False,
+                        bucket_cap_mb=64, gradient_as_bucket_view=True, static_graph=True)
+        named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        params = [p for _, p in named]
+        Opt, opt_name = lf.optimizer_class_from_name(cfg.optimizer)
+        nodecay = {id(base.tria_agg.pool.logit_scale_raw)} if base.tria_agg is not None else set()
+        groups = {}
+        for p in params:
+            groups.setdefault((0.0 if id(p) in nodecay else cfg.weight_decay, 1.0), []).append(p)
+        opt = Opt([{"params": ps, "weight_decay": wd, "lr_mult": mult} for (wd, mult), ps in groups.items()],
+                  lr=cfg.lr, weight_decay=cfg.weight_decay)
+        if workload == "sft":
+            packed = sft_batches(lf.VOCAB, micro_batch, args.seq_len, rank)
+            host = packed
+            h2d = sum(v.numel() * v.element_size() for v in host[0].values() if torch.is_tensor(v))
+            put = lambda b: {k: v.to(dev, non_blocking=True) for k, v in b.items() if torch.is_tensor(v)}
+        else:
+            g = torch.Generator().manual_seed(int(cfg.seed) + 1000003 * rank)
+            host = [torch.randint(0, lf.VOCAB, (micro_batch, args.seq_len + 1), generator=g).pin_memory() for _ in range(4)]
+            h2d = int(host[0].numel() * 8)
+            put = lambda b: b.to(dev, non_blocking=True)
+        resident = [put(b) for b in host]
+        state = {"i": 0, "step": 0, "loss": 0.0}
 
-    def one_step(batch):
-        # body of the reference training loop (loomformer.py:5071-5170), one micro-batch per step
-        opt.zero_grad(set_to_none=True)
-        x, y = batch[:, :-1], batch[:, 1:]
-        position_ids, attn_mask = lf.build_doc_reset_state(x, None)
-        with lf.amp_autocast(dev):
-            logits = model(x, attn_mask=attn_mask, position_ids=position_ids)
-        loss = F.cross_entropy(logits.float().reshape(-1, lf.VOCAB), y.reshape(-1), reduction="none").mean()
-        before = float(loss.detach().item())
-        loss.backward()
-        after = float(loss.detach().item())
-        if not (math.isfinite(before) and math.isfinite(after)) or nonfinite("grad"):
-            raise RuntimeError("reference arm: non-finite loss or gradient")
-        if cfg.grad_clip and cfg.grad_clip > 0:
-            torch.nn.utils.clip_grad_norm_(params, cfg.grad_clip)
-        lr = lf.lr_at(cfg, state["step"])
-        for grp in opt.param_groups:
-            grp["lr"] = lr * float(grp.get("lr_mult", 1.0))
-        opt.step()
-        if nonfinite("param"):
-            raise RuntimeError("reference arm: non-finite parameter")
-        state["step"] += 1
-        state["loss"] = before
+        def nonfinite(which):
+            for _, p in named:
+                t = p.grad if which == "grad" else p
+                if t is not None and not torch.isfinite(t.detach()).all():
+                    return True
+            return False
 
-    def step_device():
-        one_step(resident[state["i"] % 4]); state["i"] += 1
+        def one_step(batch):
+            opt.zero_grad(set_to_none=True)
+            if workload == "sft":          # packed rows: per-segment positions, block-diagonal causal mask, masked targets
+                x, y, position_ids = batch["x"], batch["y"], batch["position_ids"]
+                seg = batch["segment_ids"]
+                T = x.shape[1]
+                attn_mask = ((seg[:, :, None] == seg[:, None, :]) &
+                             torch.ones(T, T, dtype=torch.bool, device=x.device).tril()).unsqueeze(1)
+            else:
+                x, y = batch[:, :-1], batch[:, 1:]
+                position_ids, attn_mask = lf.build_doc_reset_state(x, None)
+            with lf.amp_autocast(dev):
+                logits = model(x, attn_mask=attn_mask, position_ids=position_ids)
+            if workload == "sft":
+                loss = F.cross_entropy(logits.float().reshape(-1, lf.VOCAB), y.reshape(-1), ignore_index=-100)
+            else:
+                loss = F.cross_entropy(logits.float().reshape(-1, lf.VOCAB), y.reshape(-1), reduction="none").mean()
+            before = float(loss.detach().item())
+            loss.backward()
+            after = float(loss.detach().item())
+            if not (math.isfinite(before) and math.isfinite(after)) or nonfinite("grad"):
+                raise RuntimeError("reference arm: non-finite loss or gradient")
+            if cfg.grad_clip and cfg.grad_clip > 0:
+                torch.nn.utils.clip_grad_norm_(params, cfg.grad_clip)
+            lr = lf.lr_at(cfg, state["step"])
+            for grp in opt.param_groups:
+                grp["lr"] = lr * float(grp.get("lr_mult", 1.0))
+            opt.step()
+            if nonfinite("param"):
+                raise RuntimeError("reference arm: non-finite parameter")
+            state["step"] += 1
+            state["loss"] = before
 
-    def step_e2e():
-        one_step(host[state["i"] % 4].to(dev, non_blocking=True)); state["i"] += 1
+        def step_device():
+            one_step(resident[state["i"] % 4]); state["i"] += 1
 
-    model.train()
-    ms, clocks = timed_loop(torch, dist, step_device, args.steps, args.warmup, world)
-    ms_e2e, _ = timed_loop(torch, dist, step_e2e, args.steps, 3, world)
+        def step_e2e():
+            one_step(put(host[state["i"] % 4])); state["i"] += 1
+
+        model.train()
+        ms, clocks = timed_loop(torch, dist, step_device, steps, warmup, world)
+        ms_e2e, _ = timed_loop(torch, dist, step_e2e, steps, 3, world)
+        return {"ms": ms, "ms_e2e": ms_e2e, "clocks": clocks, "h2d": h2d, "loss": state["loss"]}
+
+    def decode_arm(batch, prompt_len, new, budget_s):
+        """The reference's own decode path: Model.step token by token (it has no batched prefill), bf16 autocast."""
+        kw = {k: v for k, v in MODEL_KW.items() if k in lf.Config.__dataclass_fields__}
+        cfg = lf.Config(**kw)
+        lf.CARRY_TOKEN_ID = None
+        lf.apply_config(cfg)
+        torch.manual_seed(1)
+        model = lf.Model(cfg).to(dev).eval()
+        g = torch.Generator(device="cpu").manual_seed(5 + rank)
+        prompt = torch.randint(0, cfg.vocab, (batch, prompt_len), generator=g).to(dev)
+        t_end = time.time() + budget_s
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        with torch.inference_mode(), torch.autocast("cuda", dtype=torch.bfloat16):
+            st = None
+            for t in range(8):
+                lg, st = model.step(prompt[:, t], t, st)
+            torch.cuda.synchronize()
+            st, done_p, done_n = None, 0, 0
+            e0.record()
+            for t in range(prompt_len):
+                lg, st = model.step(prompt[:, t], t, st)
+                done_p += 1
+                if time.time() > t_end:
+                    break
+            e1.record()
+            tok = lg.argmax(-1)
+            if done_p == prompt_len:
+                for i in range(new):
+                    lg, st = model.step(tok, prompt_len + i, st)
+                    tok = lg.argmax(-1)
+                    done_n += 1
+                    if time.time() > t_end:
+                        break
+            e2.record()
+            torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1), e1.elapsed_time(e2), float(done_p), float(done_n)], device=dev)
+        if world > 1:
+            mx = t.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+            mn = t.clone(); dist.all_reduce(mn, op=dist.ReduceOp.MIN)
+            t = torch.stack((mx[0], mx[1], mn[2], mn[3]))
+        pre_ms, dec_ms, done_p, done_n = float(t[0]), float(t[1]), int(t[2]), int(t[3])
+        res = {"replicas": world, "batch_per_replica": batch, "prompt": done_p, "new": done_n,
+               "prefill_tok_s": world * batch * done_p / (pre_ms / 1e3), "unit": "tokens/s", "graph_replay": False,
+               "note": "Model.step loop of the reference, prompt ingested token by token"}
+        if done_n:
+            res["decode_tok_s"] = world * batch * done_n / (dec_ms / 1e3)
+            res["ms_per_decode_step"] = dec_ms / done_n
+        if done_p < prompt_len or done_n < new:
+            res["truncated"] = f"stopped by the {budget_s:.0f}s guard after {done_p} prompt and {done_n} new tokens"
+        return res
+
+    def agree_skip(flag):
+        if world <= 1:
+            return bool(flag)
+        t = torch.tensor([1 if flag else 0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return bool(t.item())
+
+    r = train_arm(args.model, args.micro_batch, args.workload, args.steps, args.warmup)
+    extra = {}
+    if args.secondary == "on":
+        import gc
+        sec = {}
+        deadline = time.time() + args.secondary_budget
+
+        def guarded(name, fn):
+            if agree_skip(deadline - time.time() < 30.0):
+                sec[name] = {"unavailable": f"secondary time budget used up before this measurement ({args.secondary_budget:.0f}s)"}
+                return
+            try:
+                sec[name] = fn()
+            except Exception as e:
+                sec[name] = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+            gc.collect()
+            torch.cuda.empty_cache()
+
+        guarded("decode_b1", lambda: decode_arm(1, 512, 256, 45.0))
+        guarded("decode_b64", lambda: decode_arm(64, 512, 256, 45.0))
+
+        def smol():
+            q = train_arm("smol360", 8, "pretrain", 3, 3)
+            tokens = 8 * args.seq_len * world
+            return {"metric": "train tokens/s (cfg/smol360.yaml, 467M parameters, bf16, micro-batch 8 x seq 2048 per GPU)",
+                    "value": tokens / (q["ms"] / 1e3), "unit": "tokens/s", "ms_per_step": q["ms"], "steps": 3, "warmup": 3,
+                    "e2e_value": tokens / (q["ms_e2e"] / 1e3), "grad_path": "its DistributedDataParallel wrapper",
+                    "final_loss": q["loss"], "note": "cfg/smol360.yaml as shipped (activation checkpointing on)"}
+        guarded("smol360", smol)
+
+        def sft():
+            q = train_arm("113m", args.micro_batch, "sft", 3, 3)
+            tokens = args.micro_batch * args.seq_len * world
+            return {"metric": "SFT train tokens/s (113M, packed synthetic chats, assistant-only loss, seq 2048)",
+                    "value": tokens / (q["ms"] / 1e3), "unit": "tokens/s", "ms_per_step": q["ms"], "steps": 3, "warmup": 3,
+                    "e2e_value": tokens / (q["ms_e2e"] / 1e3), "final_loss": q["loss"],
+                    "note": "the reference's Model under its DDP wrapper on this repository's packed batches (its own SFT "
+                            "script is single-device)"}
+        guarded("sft", sft)
+        extra["secondary"] = sec
     if rank == 0:
         tokens = args.micro_batch * args.seq_len * world
-        emit(args, "reference", ms, clocks, world, {
-            "e2e": {"value": tokens / (ms_e2e / 1000.0), "unit": "tokens/s",
-                    "h2d_bytes_per_step": int(host[0].numel() * 8), "d2h_bytes_per_step": 8, "ms_per_step": ms_e2e},
-            "gpu_launches": None, "final_loss": state["loss"],
-            "note": "unmodified reference Model/DDP/optimizer from baseline/_ref; loop body replicated from its trainer"})
+        emit(args, "reference", r["ms"], r["clocks"], world, dict({
+            "e2e": {"value": tokens / (r["ms_e2e"] / 1000.0), "unit": "tokens/s",
+                    "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": 8, "ms_per_step": r["ms_e2e"]},
+            "gpu_launches": None, "final_loss": r["loss"],
+            "note": "unmodified reference Model/DDP/optimizer from baseline/_ref; loop body replicated from its trainer"},
+            **extra))
     if world > 1:
         dist.destroy_process_group()
 

@@ -28,7 +28,7 @@ void gemm(std::vector<torch::Tensor> a_list, std::vector<int64_t> k_len, std::ve
           c10::optional<torch::Tensor> bias, int64_t M, int64_t N, int64_t heads, bool accumulate, int64_t bn,
           bool swap_mn, torch::Tensor status, std::vector<int64_t> b_peer_ptrs, int64_t gather_rank,
           std::vector<int64_t> a_peer_ptrs, int64_t a_rows_per_rank, std::vector<int64_t> rs_out_ptrs,
-          int64_t rs_rows_per_rank, int64_t rs_rank) {
+          int64_t rs_rows_per_rank, int64_t rs_rank, int64_t pair) {
   TORCH_CHECK(a_list.size() >= 1 && a_list.size() <= 16, "1..16 K segments");
   TORCH_CHECK(b_list.size() == 1 || b_list.size() == a_list.size(), "B: one operand, or one per segment");
   TORCH_CHECK(c.is_cuda() && c.stride(-1) == 1, "C must be a CUDA tensor with unit inner stride");
@@ -62,7 +62,7 @@ void gemm(std::vector<torch::Tensor> a_list, std::vector<int64_t> k_len, std::ve
   }
   g.M = (int)M; g.N = (int)N; g.heads = (int)heads;
   g.accumulate = accumulate; g.out_fp32 = c.scalar_type() == torch::kFloat32;
-  g.bn = (int)bn; g.swap_mn_strides = swap_mn;
+  g.bn = (int)bn; g.swap_mn_strides = swap_mn; g.pair = (int)pair;
   g.status = status.data_ptr<int>();
   if (b_peer_ptrs.size() > 1) {
     TORCH_CHECK(b_peer_ptrs.size() <= 8 && b_list.size() == 1, "gather: up to 8 ranks, one B operand");

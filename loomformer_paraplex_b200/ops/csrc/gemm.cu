@@ -316,6 +316,226 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_kernel(const __grid_const
   if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// CTA-pair variant: a cluster of two CTAs computes one 256 x BN output tile with tcgen05.mma.cta_group::2.
+// Each CTA stages its own 128 rows of A and its own BN/2 columns of B (24-32 KB per k-block and SM instead of the
+// 32-48 KB of the single-CTA tiles), holds its own 128 x BN accumulator rows in TMEM (double buffered) and runs its
+// own epilogue.  The even CTA's MMA thread issues for both; its operand barrier counts the bytes of both CTAs'
+// loads.  Same operand layouts, segments, batching and epilogue options as gemm_kernel; the collective variants
+// (gather / row-sharded A / reduce-scatter epilogue) stay on the single-CTA kernel.
+template <int BN>
+struct PairCfg {
+  static constexpr int HALF = BN / 2;                 // B columns staged per CTA
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = HALF * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN >= 256) ? 6 : 8;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int TMEM_COLS = 2 * BN;
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_pair_kernel(const __grid_constant__ Params p) {
+  using C = PairCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* empty = full + C::STAGES;
+  uint64_t* acc_full = empty + C::STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0: leader (issues the MMAs), 1: peer
+  volatile int* status = p.status;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    // acc_empty of the leader collects the epilogue threads of both CTAs
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 256); }
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc_pair(tmem_slot, C::TMEM_COLS); tmem_relinquish_pair(); }
+  tc_fence_before();
+  __syncthreads();
+  // both CTAs' barriers exist and both allocations are done before anything crosses the pair
+  cluster_arrive();
+  cluster_wait();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int tiles_n = (p.n_per_head + BN - 1) / BN;
+  const int total = tiles_m * tiles_n * p.heads;
+  const int npairs = gridDim.x >> 1;
+  const int pair = blockIdx.x >> 1;
+  int kblocks = 0;
+  for (int s = 0; s < p.nseg; ++s) kblocks += (p.seg[s].k_len + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer (both CTAs, own halves)
+    if (elect_one()) {
+      if (!p.b_per_seg) tma_prefetch_desc(&p.b);
+      for (int s = 0; s < p.nseg; ++s) { tma_prefetch_desc(&p.seg[s].a); if (p.b_per_seg) tma_prefetch_desc(&p.seg[s].b); }
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total && ok; tile += npairs) {
+        const int tm = tile % tiles_m;
+        const int tn = (tile / tiles_m) % tiles_n;
+        const int g = tile / (tiles_m * tiles_n);
+        const int m0 = tm * (2 * BM) + (int)rank * BM;
+        const int n0 = tn * BN + (int)rank * C::HALF;
+        for (int s = 0; s < p.nseg && ok; ++s) {
+          const Seg& sg = p.seg[s];
+          const CUtensorMap* bmap = p.b_per_seg ? &sg.b : &p.b;
+          const int ag = sg.a_batched ? g : 0;
+          const int bg = p.b_batched ? g : 0;
+          for (int k = 0; k < sg.k_len; k += BK, ++it) {
+            const int st = it % C::STAGES;
+            const uint32_t ph = (it / C::STAGES) & 1;
+            if (!mbar_wait(&empty[st], ph ^ 1, status, 111)) { ok = false; break; }
+            const uint32_t sa = smem_u32(smem + st * C::STAGE_BYTES);
+            const uint32_t sb = sa + C::A_BYTES;
+            // the leader's barrier of this stage expects the bytes of both CTAs
+            const uint32_t bar = mapa_shared(smem_u32(&full[st]), 0);
+            if (rank == 0) mbar_expect_tx(&full[st], 2 * C::STAGE_BYTES);
+            if (A_MN) {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j)
+                tma_load_3d_pair(sa + j * 8192, &sg.a, bar, m0 + 64 * j, sg.a_k0 + k, ag);
+            } else {
+              tma_load_3d_pair(sa, &sg.a, bar, sg.a_k0 + k, m0, ag);
+            }
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < C::HALF / 64; ++j)
+                tma_load_3d_pair(sb + j * 8192, bmap, bar, n0 + 64 * j, sg.b_k0 + k, bg);
+            } else {
+              tma_load_3d_pair(sb, bmap, bar, sg.b_k0 + k, n0, bg);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer (leader CTA only)
+    if (rank == 0 && elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total && ok; tile += npairs, ++tcount) {
+        const uint32_t acc = tcount & 1;
+        if (!mbar_wait(&acc_empty[acc], ((tcount >> 1) & 1) ^ 1, status, 112)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int st = it % C::STAGES;
+          if (!mbar_wait(&full[st], (it / C::STAGES) & 1, status, 113)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + st * C::STAGE_BYTES);
+          const uint32_t sb = sa + C::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint32_t a_off = A_MN ? k * (UMMA_K * 128) : k * (UMMA_K * 2);
+            const uint32_t b_off = B_MN ? k * (UMMA_K * 128) : k * (UMMA_K * 2);
+            const uint64_t da = make_smem_desc_sw128(sa + a_off, p.a_lbo, p.a_sbo);
+            const uint64_t db = make_smem_desc_sw128(sb + b_off, p.b_lbo, p.b_sbo);
+            mma_bf16_ss_pair(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          mma_commit_pair(&empty[st], 3);       // frees this stage in both CTAs when these MMAs retire
+        }
+        if (ok) mma_commit_pair(&acc_full[acc], 3);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5 of both CTAs)
+    const int q = warp & 3;
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int tile = pair; tile < total && ok; tile += npairs, ++tcount) {
+      const int tm = tile % tiles_m;
+      const int tn = (tile / tiles_m) % tiles_n;
+      const int g = tile / (tiles_m * tiles_n);
+      const uint32_t acc = tcount & 1;
+      if (!mbar_wait(&acc_full[acc], (tcount >> 1) & 1, status, 114)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tm * (2 * BM) + (int)rank * BM + q * 32 + lane;
+      const int n0 = tn * BN;
+      const uint32_t taddr = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
+      const long long c_row = (long long)row * p.ldc + (long long)g * p.ldc_head;
+      const float* bias = p.bias ? p.bias + (long long)g * p.n_per_head : nullptr;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c0, r);
+        tmem_ld_wait();
+        const int n = n0 + c0;
+        if (row < p.M && n < p.n_per_head) {
+          const int nvalid = min(32, p.n_per_head - n);
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if (bias) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (i < nvalid) v[i] += bias[n + i];
+          }
+          if (p.out_fp32) {
+            float* dst = reinterpret_cast<float*>(p.c) + c_row + n;
+            if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                if (p.accumulate) { float4 old = *reinterpret_cast<float4*>(dst + i); o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
+                *reinterpret_cast<float4*>(dst + i) = o;
+              }
+            } else {
+              for (int i = 0; i < nvalid; ++i) dst[i] = p.accumulate ? dst[i] + v[i] : v[i];
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + c_row + n;
+            if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                if (p.accumulate) {
+                  uint4 old = *reinterpret_cast<uint4*>(dst + i);
+                  const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(ob[j]); v[i + 2 * j] += f.x; v[i + 2 * j + 1] += f.y; }
+                }
+                uint4 o;
+                __nv_bfloat162* ob2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) ob2[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
+                *reinterpret_cast<uint4*>(dst + i) = o;
+              }
+            } else {
+              for (int i = 0; i < nvalid; ++i) {
+                float x = v[i];
+                if (p.accumulate) x += __bfloat162float(dst[i]);
+                dst[i] = __float2bfloat16(x);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      // this accumulator buffer may be overwritten once the epilogue threads of BOTH CTAs have read it
+      mbar_arrive_cluster(mapa_shared(smem_u32(&acc_empty[acc]), 0));
+    }
+  }
+
+  // neither CTA may leave (or free its TMEM) while the other can still touch its shared memory or barriers
+  tc_fence_before();
+  __syncwarp();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+}
+
 bool fill_map(CUtensorMap* map, const LoomOperand& o, bool mn_major, int box_mn) {
   // view [rows, heads, cols]: dims (cols, rows, heads)
   tma_host::EncodeTiledFn fn = tma_host::encode_fn();
@@ -366,19 +586,64 @@ int dispatch_major(const Params& p, bool a_mn, bool b_mn, int sms, cudaStream_t 
   return b_mn ? launch<BN, false, true>(p, sms, stream) : launch<BN, false, false>(p, sms, stream);
 }
 
+template <int BN, bool A_MN, bool B_MN>
+int launch_pair(const Params& p, int sms, cudaStream_t stream) {
+  using C = PairCfg<BN>;
+  static bool configured = false;
+  static int max_pairs = 0;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    // how many clusters of two fit the device at once (a GPC with an odd number of free SMs loses one)
+    cudaLaunchConfig_t q = {};
+    q.gridDim = dim3(sms & ~1); q.blockDim = dim3(NUM_THREADS); q.dynamicSmemBytes = C::SMEM;
+    cudaLaunchAttribute qa[1];
+    qa[0].id = cudaLaunchAttributeClusterDimension;
+    qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+    q.attrs = qa; q.numAttrs = 1;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<BN, A_MN, B_MN>, &q);
+    if (e != cudaSuccess || n < 1) { cudaGetLastError(); n = sms / 2; }
+    max_pairs = n;
+    configured = true;
+  }
+  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.n_per_head + BN - 1) / BN) * p.heads;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  static int pdl = -1;
+  if (pdl < 0) { const char* e = getenv("LOOM_PDL"); pdl = (e != nullptr && e[0] == '0') ? 0 : 1; }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(NUM_THREADS); cfg.dynamicSmemBytes = C::SMEM; cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 2 : 1;
+  return (int)cudaLaunchKernelEx(&cfg, gemm_pair_kernel<BN, A_MN, B_MN>, p);
+}
+
+template <int BN>
+int dispatch_major_pair(const Params& p, bool a_mn, bool b_mn, int sms, cudaStream_t stream) {
+  if (a_mn) return b_mn ? launch_pair<BN, true, true>(p, sms, stream) : launch_pair<BN, true, false>(p, sms, stream);
+  return b_mn ? launch_pair<BN, false, true>(p, sms, stream) : launch_pair<BN, false, false>(p, sms, stream);
+}
+
 }  // namespace
 
 extern "C" int loom_gemm_bf16(const LoomGemm* g, cudaStream_t stream) {
   if (g->nseg < 1 || g->nseg > MAX_SEG) return -1;
   if (g->bn != 64 && g->bn != 128 && g->bn != 256) return -2;
+  const bool pair = g->pair != 0;
+  if (pair && (g->bn < 128 || g->gather_world > 1 || g->a_world > 1 || g->rs_world > 1)) return -10;
+  const int b_box = pair ? g->bn / 2 : g->bn;      // B rows staged per CTA
   Params p;
   memset(&p, 0, sizeof(p));
   const bool a_mn = g->a_mn_major != 0, b_mn = g->b_mn_major != 0;
   p.b_per_seg = g->b_per_seg ? 1 : 0;
-  if (!p.b_per_seg && !fill_map(&p.b, g->b, b_mn, g->bn)) return -3;
+  if (!p.b_per_seg && !fill_map(&p.b, g->b, b_mn, b_box)) return -3;
   for (int s = 0; s < g->nseg; ++s) {
     if (!fill_map(&p.seg[s].a, g->a[s], a_mn, BM)) return -4;
-    if (p.b_per_seg && !fill_map(&p.seg[s].b, g->bseg[s], b_mn, g->bn)) return -3;
+    if (p.b_per_seg && !fill_map(&p.seg[s].b, g->bseg[s], b_mn, b_box)) return -3;
     p.seg[s].k_len = g->k_len[s];
     p.seg[s].a_k0 = g->a_k0[s];
     p.seg[s].b_k0 = g->b_k0[s];
@@ -430,6 +695,8 @@ extern "C" int loom_gemm_bf16(const LoomGemm* g, cudaStream_t stream) {
       default: return launch<256, false, false, true>(p, sms, stream);
     }
   }
+  if (pair) return g->bn == 128 ? dispatch_major_pair<128>(p, a_mn, b_mn, sms, stream)
+                                : dispatch_major_pair<256>(p, a_mn, b_mn, sms, stream);
   switch (g->bn) {
     case 64: return dispatch_major<64>(p, a_mn, b_mn, sms, stream);
     case 128: return dispatch_major<128>(p, a_mn, b_mn, sms, stream);

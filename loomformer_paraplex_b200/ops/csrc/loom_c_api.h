@@ -48,6 +48,9 @@ typedef struct {
   const void* a_peer_ptr[8];
   int rs_world, rs_rank, rs_rows_per_rank;
   float* rs_out[8];
+  // pair != 0: 256 x bn tiles computed by clusters of two CTAs (tcgen05 cta_group::2); bn must be 128 or 256 and
+  // none of the collective variants above may be active
+  int pair;
 } LoomGemm;
 
 // Cross-rank barrier on peer-mapped flag words (one int per rank in each rank's `flags` buffer): publish `epoch`

@@ -54,18 +54,49 @@ def _pick_bn(M: int, N: int, heads: int = 1) -> int:
     return 128 if N >= 128 else 64
 
 
+_FORCED_TILE = {"cta64": (64, 0), "cta128": (128, 0), "cta256": (256, 0), "pair128": (128, 1), "pair256": (256, 1)}
+
+
+def _pick_tile(M: int, N: int, heads: int = 1, plain: bool = True):
+    """``(tile width, pair)``.  ``pair`` selects 256-row tiles computed by clusters of two CTAs
+    (``tcgen05.mma.cta_group::2``): each SM then stages 128 rows of A and only half of the tile's B columns per
+    k-block, which is what the kernel is bound by (operand delivery from L2).  Pair tiles are used when they still
+    fill the 74 SM pairs; small problems keep single-CTA tiles, which give twice as many schedulable units.
+    ``LOOM_GEMM_TILE`` (cta64|cta128|cta256|pair128|pair256) forces one shape for sweeps; ``LOOM_GEMM_PAIR=0`` turns
+    pair tiles off."""
+    forced = os.environ.get("LOOM_GEMM_TILE")
+    if forced in _FORCED_TILE:
+        bn, pair = _FORCED_TILE[forced]
+        if not pair or (plain and N >= 128 and M >= 256):
+            return bn, pair
+    if plain and M >= 256 and N >= 128 and os.environ.get("LOOM_GEMM_PAIR", "0") != "0":
+        rows = -(-M // 256)
+        if N >= 256 and rows * (-(-N // 256)) * heads >= 2 * 74:
+            return 256, 1
+        if rows * (-(-N // 128)) * heads >= 74:
+            return 128, 1
+    return _pick_bn(M, N, heads), 0
+
+
 def gemm(a_list: List[torch.Tensor], k_len: List[int], b, c: torch.Tensor, *, M: int, N: int,
          heads: int = 1, a_mn: bool = False, b_mn: bool = False, a_k0: Optional[List[int]] = None,
          b_k0: Optional[List[int]] = None, bias: Optional[torch.Tensor] = None, accumulate: bool = False,
          bn: Optional[int] = None, swap_mn: bool = False, peer_ptrs: Optional[List[int]] = None,
          gather_rank: int = 0, a_peer_ptrs: Optional[List[int]] = None, a_rows_per_rank: int = 0,
-         rs_out_ptrs: Optional[List[int]] = None, rs_rows_per_rank: int = 0, rs_rank: int = 0) -> None:
+         rs_out_ptrs: Optional[List[int]] = None, rs_rows_per_rank: int = 0, rs_rank: int = 0,
+         pair: Optional[int] = None) -> None:
     ext = native.ext()
     n = len(a_list)
+    plain = not (peer_ptrs or a_peer_ptrs or rs_out_ptrs)
+    if pair is None:
+        if bn:
+            pair = 0
+        else:
+            bn, pair = _pick_tile(M, N, heads, plain)
     ext.gemm(a_list, k_len, a_k0 or [0] * n, b_k0 or [0] * n, b if isinstance(b, (list, tuple)) else [b], a_mn, b_mn,
              c, bias, M, N, heads, accumulate,
              bn or _pick_bn(M, N, heads), swap_mn, status_word(c.device), peer_ptrs or [], gather_rank,
-             a_peer_ptrs or [], a_rows_per_rank, rs_out_ptrs or [], rs_rows_per_rank, rs_rank)
+             a_peer_ptrs or [], a_rows_per_rank, rs_out_ptrs or [], rs_rows_per_rank, rs_rank, int(pair))
     native.count()
 
 

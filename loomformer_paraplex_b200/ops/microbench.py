@@ -211,14 +211,72 @@ def run(op: str, tokens: int, iters: int, warmup: int) -> Dict[str, float]:
             "frac_bf16": tfl / pk["bf16_tflops"], "peaks": kind}
 
 
+GEMM_SHAPES = [(2048, 768, 3072), (2048, 768, 768), (2048, 1152, 768), (2048, 3072, 768), (2048, 8192, 768),
+               (32768, 3072, 768)]          # (M, N, K): the linear layers of the 113M training step + one large case
+
+
+def time_burst(fn, n: int = 20) -> float:
+    """Milliseconds per launch over ``n`` back-to-back launches (operands stay in L2: what a graph replay sees)."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(n):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / n
+
+
+def gemm_table(iters: int, warmup: int, variants=("auto", "cta128", "cta256", "pair128", "pair256")) -> None:
+    """Every forward-linear shape of the step: this repository's kernel with each tile shape, and the library GEMM
+    (``torch.nn.functional.linear`` -> cuBLAS) timed in the same run the same way.  Two timings per entry: one launch
+    after an L2 flush (cold), and back-to-back launches (warm)."""
+    import torch.nn.functional as F
+    K = kmod.CudaKernels()
+    flush = torch.zeros(160 * 1024 * 1024 // 4, device="cuda")
+    pk, kind = peaks()
+    print(f"{'M,N,K':>18s} " + " ".join(f"{v:>15s}" for v in variants) + f" {'library':>15s}   us cold/warm; best ours "
+          f"as TFLOP/s warm and fraction of {kind} bf16 peak")
+    for (M, N, Kd) in GEMM_SHAPES:
+        x, w = bf(M, Kd), bf(N, Kd, scale=0.03)
+        ref = F.linear(x, w)
+        cells, best = [], 1e9
+        for v in variants:
+            if v == "auto":
+                os.environ.pop("LOOM_GEMM_TILE", None)
+            else:
+                os.environ["LOOM_GEMM_TILE"] = v
+            y = K.linear(x, w)
+            err = float((y.float() - ref.float()).abs().max() / (ref.float().abs().max() + 1e-6))
+            assert err < 2e-2, (M, N, Kd, v, err)
+            cold = time_op(lambda: K.linear(x, w), iters, warmup, flush) * 1e3
+            warm = time_burst(lambda: K.linear(x, w)) * 1e3
+            best = min(best, warm)
+            cells.append(f"{cold:7.1f}/{warm:7.1f}")
+        os.environ.pop("LOOM_GEMM_TILE", None)
+        lib_cold = time_op(lambda: F.linear(x, w), iters, warmup, flush) * 1e3
+        lib_warm = time_burst(lambda: F.linear(x, w)) * 1e3
+        tfl = 2.0 * M * N * Kd / best / 1e6
+        print(f"{M:6d},{N:5d},{Kd:5d} " + " ".join(cells) + f" {lib_cold:7.1f}/{lib_warm:7.1f}   {tfl:7.1f} "
+              f"{tfl / pk['bf16_tflops']:.2f}")
+    kmod.check_status(torch.device("cuda"))
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--op", default="all", choices=["all"] + sorted(CASES))
+    ap.add_argument("--op", default="all", choices=["all", "gemm_shapes"] + sorted(CASES))
+    ap.add_argument("--vs", default=None, choices=[None, "library"],
+                    help="with --op gemm_shapes: also time the library GEMM on every shape (always on for that op)")
     ap.add_argument("--tokens", type=int, default=32768, help="rows M = batch x chunk tokens")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args(argv)
     torch.manual_seed(0)
+    if a.op == "gemm_shapes":
+        gemm_table(a.iters, a.warmup)
+        return
     print(f"{'op':14s} {'tokens':>7s} {'ms':>9s} {'GB/s':>9s} {'of HBM':>7s} {'TFLOP/s':>9s} {'of bf16':>8s}")
     for op in (sorted(CASES) if a.op == "all" else [a.op]):
         r = run(op, a.tokens, a.iters, a.warmup)

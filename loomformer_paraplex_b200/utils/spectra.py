@@ -106,92 +106,128 @@ def analyze(blob: Dict[str, Any], init: Optional[Dict[str, torch.Tensor]] = None
             f"| {row['o_smax']:6.3f} {row['w2_smax']:7.3f} | {'/'.join(f'{100 * s:.0f}' for s in shares):>14s} "
             f"| {dup['dup98']:5d} {dead:4d} | {gcos:4.2f} | {dr}")
 
-    log("\n=== [4] depth-attn ===")
-    qp = F.normalize(sd["depth_attn.q_params"].float(), dim=-1).permute(1, 0, 2)      # [qh, 2L, hd]
-    gram = (qp @ qp.transpose(1, 2)).abs().mean(0).fill_diagonal_(0)
-    nsub = gram.shape[0]
-    log(f"  query Gram over {nsub} sublayers (mean over heads): offdiag |cos| mean={float(gram.mean()):.3f} "
-        f"p99={float(torch.quantile(gram.flatten(), 0.99)):.3f} pairs>0.9={int((gram > 0.9).sum()) // 2}")
-    out["depth"] = {"gram_mean": float(gram.mean())}
-    wo = sd.get("depth_attn.w_o_weight")
-    if wo is not None:
-        wvd = sd["depth_attn.kv_weight"].float()[n:]
-        wo = wo.float()
-        if wo.dim() == 2:
-            wo = wo.unsqueeze(0)
-        ers = spectrum(wo @ wvd)["erank"].tolist()
-        smx = spectrum(wo)["smax"].tolist()
-        log("  value-circuit erank per sublayer:\n  " + " ".join(f"{v:.0f}" for v in ers))
-        log("  w_o smax per sublayer:\n  " + " ".join(f"{v:.2f}" for v in smx))
-        out["depth"].update(vc_erank=ers, wo_smax=smx)
+    out["depth"] = _depth_section(sd, n, log)
+    out["embedding"] = _embedding_section(sd, init, L, log)
+    out["axes"] = _axis_section(sd, out["layers"], L, log)
+    out["flags"] = _flag_section(out["layers"], {"hd": hd, "n": n, "hidden": hidden}, log)
+    return out
 
+
+# ---------------------------------------------------------------------------------------------- report sections 4-7
+def _depth_section(sd, n: int, log) -> Dict[str, Any]:
+    """[4] How distinct the per-sublayer depth queries are, and how much rank the depth value circuit keeps."""
+    log("\n=== [4] depth-attn ===")
+    q = F.normalize(sd["depth_attn.q_params"].float(), dim=-1)                  # [2L, qh, hd]
+    cos = torch.einsum("ahd,bhd->hab", q, q).abs().mean(0)                      # head-averaged |cos| between sublayers
+    off = cos[~torch.eye(cos.shape[0], dtype=torch.bool, device=cos.device)]
+    close = int((off > 0.9).sum()) // 2
+    res: Dict[str, Any] = {"gram_mean": float(cos.fill_diagonal_(0).mean())}
+    log(f"  {cos.shape[0]} sublayer queries, |cos| between different sublayers: mean {res['gram_mean']:.3f}, "
+        f"99th pct {float(torch.quantile(off, 0.99)):.3f}, near-parallel pairs (>0.9): {close}")
+    w_o = sd.get("depth_attn.w_o_weight")
+    if w_o is None:
+        return res
+    w_o = w_o.float()
+    w_o = w_o[None] if w_o.dim() == 2 else w_o
+    value_rows = sd["depth_attn.kv_weight"].float()[n:]
+    res["vc_erank"] = spectrum(w_o @ value_rows)["erank"].tolist()
+    res["wo_smax"] = spectrum(w_o)["smax"].tolist()
+    for label, vals, fmt in (("readout @ value projection, effective rank", res["vc_erank"], "{:.0f}"),
+                             ("readout spectral norm", res["wo_smax"], "{:.2f}")):
+        log(f"  {label} by sublayer: " + ", ".join(fmt.format(v) for v in vals))
+    return res
+
+
+_MEMORY_HEAD = ("tria_final_ca.w_qk.weight", "tria_final_ca.w_v.weight", "tria_agg.up.weight",
+                "tria_agg.reader.proj.weight", "tria_agg.reader.key_proj.weight")
+
+
+def _embedding_section(sd, init, L: int, log) -> Dict[str, Any]:
+    """[5] Token embedding geometry, the matrices of the boundary-memory read-out, and normalisation gains."""
     log("\n=== [5] embedding / memory head / norms ===")
     emb = sd["emb.weight"].float()
-    es = spectrum1(emb)
-    rows = emb.norm(dim=1)
-    cone = float(emb.mean(0).norm() / rows.mean().clamp_min(1e-12))
-    low = int((rows < 0.25 * rows.median()).sum())
-    log(f"  emb: erank={es['erank']:.1f}/{es['full']} top1={es['top1']:.3f} cone(|mean|/|row|)={cone:.3f} low-norm tokens={low}")
-    out["embedding"] = {"spectrum": es, "cone": cone, "low_norm_tokens": low}
-    for name in ("tria_final_ca.w_qk.weight", "tria_final_ca.w_v.weight", "tria_agg.up.weight", "tria_agg.reader.proj.weight",
-                 "tria_agg.reader.key_proj.weight"):
-        if name in sd:
-            s = spectrum1(sd[name])
-            d = f" drift={drift(sd[name], init[name]):.3f}" if init is not None and name in init else ""
-            log(f"  {name}: erank={s['erank']:.1f}/{s['full']} smax={s['smax']:.3f} top1={s['top1']:.3f}{d}")
-    gains = torch.cat([sd[f"blocks.{li}.{ln}.weight"].float() for li in range(L) for ln in ("ln_attn", "ln_ffn")])
-    gs = vector_stats(gains)
-    log(f"  LN gains overall: mean={gs['mean']:.3f} std={gs['std']:.3f} min={gs['min']:.3f} max={gs['max']:.3f} "
-        f"|g|<0.05: {gs['near_zero']}")
-    biases = [sd[k].float() for li in range(L) for ln in ("ln_attn", "ln_ffn") if (k := f"blocks.{li}.{ln}.bias") in sd]
-    if biases:
-        b = torch.cat(biases)
-        log(f"  LN biases: rms={float(b.square().mean().sqrt()):.3f} absmax={float(b.abs().max()):.3f}")
-    if "ln_final.weight" in sd:
-        log(f"  ln_final: {vector_stats(sd['ln_final.weight'])}")
-
-    log("\n=== [6] axis aggregates (layer % 3: 0=Rz 1=Rx 2=Ry) ===")
-    out["axes"] = []
-    for ax in range(3):
-        idx = [li for li in range(L) if li % 3 == ax]
-        if not idx:
+    spec = spectrum1(emb)
+    norms = emb.norm(dim=1)
+    res = {"spectrum": spec, "cone": float(emb.mean(0).norm() / norms.mean().clamp_min(1e-12)),
+           "low_norm_tokens": int((norms < 0.25 * norms.median()).sum())}
+    log(f"  embedding table: effective rank {spec['erank']:.1f} of {spec['full']}, leading share {spec['top1']:.3f}, "
+        f"common direction {res['cone']:.3f} of a row norm, {res['low_norm_tokens']} rows under a quarter of the median norm")
+    for name in _MEMORY_HEAD:
+        if name not in sd:
             continue
-        rows_ = [out["layers"][li] for li in idx]
-        agg = {"axis": ax, "layers": idx,
-               "U": sum(r["imag_sector_share"]["U"] for r in rows_) / len(idx),
-               "D": sum(r["imag_sector_share"]["D"] for r in rows_) / len(idx),
-               "ffn_sk_erank": sum(r["ffn_skeleton"]["erank"] for r in rows_) / len(idx),
-               "imag_bias_rms": float(torch.stack([sd[f"blocks.{li}.ffn.w1_imag_bias"].float().square().mean().sqrt() for li in idx]).mean()),
-               "imag_std": float(torch.stack([sd[f"blocks.{li}.ffn.w1_imag"].float().std() for li in idx]).mean())}
-        out["axes"].append(agg)
-        log(f"  axis {ax}: layers={idx}\n          U%={100 * agg['U']:.1f} D%={100 * agg['D']:.1f} "
-            f"ffn_sk_erank={agg['ffn_sk_erank']:.1f} imag_bias_rms={agg['imag_bias_rms']:.4f} imag_std={agg['imag_std']:.4f}")
+        sp = spectrum1(sd[name])
+        moved = f", moved {drift(sd[name], init[name]):.3f} from init" if init is not None and name in init else ""
+        log(f"  {name:34s} rank {sp['erank']:.1f}/{sp['full']}  norm {sp['smax']:.3f}  leading share {sp['top1']:.3f}{moved}")
+    per_norm = [f"blocks.{li}.{which}" for li in range(L) for which in ("ln_attn", "ln_ffn")]
+    g = vector_stats(torch.cat([sd[k + ".weight"].float() for k in per_norm]))
+    log(f"  block LayerNorm gains: {g['mean']:.3f} +- {g['std']:.3f}, range [{g['min']:.3f}, {g['max']:.3f}], "
+        f"{g['near_zero']} with magnitude under 0.05")
+    shifts = [sd[k + ".bias"].float() for k in per_norm if k + ".bias" in sd]
+    if shifts:
+        b = torch.cat(shifts)
+        log(f"  block LayerNorm shifts: rms {float(b.square().mean().sqrt()):.3f}, largest {float(b.abs().max()):.3f}")
+    if "ln_final.weight" in sd:
+        f = vector_stats(sd["ln_final.weight"])
+        log(f"  final norm gains: {f['mean']:.3f} +- {f['std']:.3f}, range [{f['min']:.3f}, {f['max']:.3f}]")
+    return res
 
+
+def _axis_section(sd, layer_rows: List[Dict[str, Any]], L: int, log) -> List[Dict[str, Any]]:
+    """[6] Layers share a carrier rotation axis every third layer; average a few per-layer figures per axis."""
+    log("\n=== [6] axis aggregates (layer % 3: 0=Rz 1=Rx 2=Ry) ===")
+    res = []
+    for axis, name in enumerate(("Rz", "Rx", "Ry")):
+        members = list(range(axis, L, 3))
+        if not members:
+            continue
+        mean = lambda vals: float(sum(vals) / len(vals))
+        imag = [sd[f"blocks.{li}.ffn.w1_imag"].float() for li in members]
+        ibias = [sd[f"blocks.{li}.ffn.w1_imag_bias"].float() for li in members]
+        agg = {"axis": axis, "layers": members,
+               "U": mean([layer_rows[li]["imag_sector_share"]["U"] for li in members]),
+               "D": mean([layer_rows[li]["imag_sector_share"]["D"] for li in members]),
+               "ffn_sk_erank": mean([layer_rows[li]["ffn_skeleton"]["erank"] for li in members]),
+               "imag_bias_rms": mean([float(b.square().mean().sqrt()) for b in ibias]),
+               "imag_std": mean([float(w.std()) for w in imag])}
+        res.append(agg)
+        log(f"  axis {axis} ({name}), layers {members}: phase input energy from the block input {100 * agg['U']:.1f}% and "
+            f"from the depth read {100 * agg['D']:.1f}%; skeleton rank {agg['ffn_sk_erank']:.1f}; "
+            f"phase bias rms {agg['imag_bias_rms']:.4f}; phase weight std {agg['imag_std']:.4f}")
+    return res
+
+
+# One rule per line: (what it looks at, predicate over (row, sizes), message).  A rule fires per layer.
+_LAYER_RULES = (
+    ("qk", lambda r, z: r["qk_erank_min"] < z["hd"] / 4,
+     lambda r, z: f"a query-key head has collapsed: smallest effective rank {r['qk_erank_min']:.0f} of {z['hd']}"),
+    ("ov", lambda r, z: r["ov_erank_min"] < z["hd"] / 4,
+     lambda r, z: f"an output-value head has collapsed: smallest effective rank {r['ov_erank_min']:.0f} of {z['hd']}"),
+    ("skeleton", lambda r, z: r["ffn_skeleton"]["erank_frac"] < 0.2,
+     lambda r, z: f"w2 @ w1_real spans few directions: effective rank {r['ffn_skeleton']['erank']:.0f} of {z['n']}"),
+    ("duplicates", lambda r, z: r["dup"]["dup98"] > z["hidden"] / 200,
+     lambda r, z: f"{r['dup']['dup98']} hidden units nearly repeat another one (|cos| above 0.98)"),
+    ("dead", lambda r, z: r["dead_hidden"] > z["hidden"] / 100,
+     lambda r, z: f"{r['dead_hidden']} hidden units carry almost no signal"),
+    ("gate", lambda r, z: (not math.isnan(r["gate_w1_cos"])) and r["gate_w1_cos"] > 0.9,
+     lambda r, z: f"gate_proj rows line up with w1_real rows (mean |cos| {r['gate_w1_cos']:.2f})"),
+)
+
+
+def _flag_section(layer_rows: List[Dict[str, Any]], sizes: Dict[str, int], log) -> List[str]:
+    """[7] Degeneracy checks over the per-layer table, plus a z-score test for one outlying ``w2`` norm."""
     log("\n=== [7] flags ===")
-    flags: List[str] = []
-    for r in out["layers"]:
-        li = r["layer"]
-        if r["qk_erank_min"] < 0.25 * hd:
-            flags.append(f"L{li}: degenerate QK head (min erank {r['qk_erank_min']:.0f}/{hd})")
-        if r["ov_erank_min"] < 0.25 * hd:
-            flags.append(f"L{li}: degenerate OV head (min erank {r['ov_erank_min']:.0f}/{hd})")
-        if r["ffn_skeleton"]["erank_frac"] < 0.2:
-            flags.append(f"L{li}: low-rank FFN skeleton ({r['ffn_skeleton']['erank']:.0f}/{n})")
-        if r["dup"]["dup98"] > 0.005 * hidden:
-            flags.append(f"L{li}: {r['dup']['dup98']} duplicate hidden units (cos>0.98)")
-        if r["dead_hidden"] > 0.01 * hidden:
-            flags.append(f"L{li}: {r['dead_hidden']} dead hidden units")
-        if not math.isnan(r["gate_w1_cos"]) and r["gate_w1_cos"] > 0.9:
-            flags.append(f"L{li}: gate_proj collapsed onto w1_real (cos {r['gate_w1_cos']:.2f})")
-    sm = torch.tensor([r["w2_smax"] for r in out["layers"]])
-    if sm.numel() > 1:
-        z = (sm - sm.mean()) / sm.std().clamp_min(1e-9)
-        for li in torch.nonzero(z.abs() > 3).flatten().tolist():
-            flags.append(f"L{li}: w2 spectral-norm outlier ({float(sm[li]):.2f}, z={float(z[li]):+.1f})")
-    out["flags"] = flags or ["none -- no degeneracy criteria triggered"]
-    for f in out["flags"]:
-        log("  * " + f)
-    return out
+    found = [f"layer {r['layer']}: {message(r, sizes)}"
+             for r in layer_rows for _, fires, message in _LAYER_RULES if fires(r, sizes)]
+    norms = torch.tensor([r["w2_smax"] for r in layer_rows])
+    if norms.numel() > 1:
+        z = (norms - norms.mean()) / norms.std().clamp_min(1e-9)
+        found += [f"layer {li}: w2 spectral norm {float(norms[li]):.2f} stands {float(z[li]):+.1f} sigma from the other layers"
+                  for li in range(norms.numel()) if abs(float(z[li])) > 3]
+    if not found:
+        found = ["nothing flagged"]
+    for line in found:
+        log("  - " + line)
+    return found
 
 
 def main(argv=None) -> None:

@@ -30,6 +30,56 @@ def test_kmajor_linear(M, N, K, bn):
     assert _rel(c, ref) < 1e-2
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (2048, 768, 768), (300, 200, 136), (4096, 3072, 768), (520, 1160, 200)])
+@pytest.mark.parametrize("bn", [128, 256])
+def test_pair_tiles_kmajor_linear(M, N, K, bn):
+    """256-row tiles computed by clusters of two CTAs (tcgen05 cta_group::2), ragged edges in both directions, more
+    tiles than SM pairs (the persistent loop and both accumulator buffers are exercised), bias and accumulate."""
+    k = _k()
+    torch.manual_seed(0)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda")
+    c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    k.gemm([x], [K], w, c, M=M, N=N, bias=bias, bn=bn, pair=1)
+    ref = x.float() @ w.float().t() + bias
+    k.check_status(c.device)
+    assert _rel(c, ref) < 1e-2
+    c32 = torch.ones(M, N, device="cuda")
+    k.gemm([x], [K], w, c32, M=M, N=N, bn=bn, pair=1, accumulate=True)
+    k.check_status(c.device)
+    assert _rel(c32, ref - bias + 1.0) < 1e-2
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, True), (True, False)])
+def test_pair_tiles_other_operand_layouts(a_mn, b_mn):
+    k = _k()
+    torch.manual_seed(4)
+    M, N, K = 776, 392, 264
+    a = torch.randn(K, M, device="cuda", dtype=torch.bfloat16) if a_mn else torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(K, N, device="cuda", dtype=torch.bfloat16) if b_mn else torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    c = torch.zeros(M, N, device="cuda")
+    k.gemm([a], [K], b, c, M=M, N=N, a_mn=a_mn, b_mn=b_mn, bn=128, pair=1)
+    k.check_status(c.device)
+    ref = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
+    assert _rel(c, ref) < 1e-2
+
+
+def test_pair_tiles_batched_heads_and_segments():
+    """Per-head batched operands with two K segments on pair tiles."""
+    k = _k()
+    torch.manual_seed(6)
+    M, heads, N, K1, K2 = 512, 4, 384, 96, 200
+    a1 = torch.randn(M, heads, K1, device="cuda", dtype=torch.bfloat16)
+    a2 = torch.randn(M, K2, device="cuda", dtype=torch.bfloat16)            # shared by all heads
+    w = (torch.randn(N, heads, K1 + K2, device="cuda") * 0.1).to(torch.bfloat16)
+    c = torch.empty(M, heads, N, device="cuda", dtype=torch.bfloat16)
+    k.gemm([a1, a2], [K1, K2], w, c, M=M, N=N, heads=heads, b_k0=[0, K1], bn=128, pair=1)
+    k.check_status(c.device)
+    ref = torch.einsum("mhk,nhk->mhn", a1.float(), w.float()[:, :, :K1]) + torch.einsum("mk,nhk->mhn", a2.float(), w.float()[:, :, K1:])
+    assert _rel(c, ref) < 1.5e-2
+
+
 @pytest.mark.parametrize("M,N,K", [(256, 128, 128), (2048, 768, 3072), (264, 200, 136)])
 def test_dgrad_mn_major_b(M, N, K):
     k = _k()

@@ -76,6 +76,67 @@ def test_fused_plan_bf16_tracks_fp32_reference(hidden):
     assert not bad, bad
 
 
+PLAN_VARIANTS = {
+    # the flag-rich configuration: open sectors, gate projection, per-sublayer readout, q/k/v RMS, capped residual
+    # branches, final norm, tied embeddings
+    "open_rich": (dict(phase_sectors="open", paraplex_gate_proj=True, depth_attn_readout="per-sublayer",
+                       depth_attn_qkv_rms=True, residual_branch_rms_cap=1.0, final_norm=True, tied_embeddings=True), 4, 256),
+    "head_floor": (dict(phase_grad_mode="floor"), 4, 256),
+    # one layer at the dimensions of the 113M benchmark model (8 x 96 heads, 2 KV heads, hidden 3072, window 128)
+    "dims_113m": (dict(model_dim=768, n_q_heads=8, head_dim=96, gqa_group_size=4, hidden_mult=4.0, layers=1,
+                       tria_temporal_window=128, vocab=1024), 2, 384),
+    # one layer at the dimensions of cfg/smol360.yaml (15 x 64 heads, 5 KV heads, 171 neurons per head -> padded)
+    "dims_smol360": (dict(model_dim=960, n_q_heads=15, head_dim=64, gqa_group_size=3, hidden=2565, hidden_mult=None,
+                          layers=1, tria_temporal_window=128, vocab=1024, paraplex_gate_proj=True, final_norm=True,
+                          tied_embeddings=True), 2, 256),
+}
+
+
+@pytest.mark.parametrize("name", list(PLAN_VARIANTS))
+def test_fused_plan_variants_track_fp32_reference(name):
+    """Every model variant the CPU plan test covers, and the two benchmark shapes, on the native kernels: no library
+    fallback, loss within bf16 noise of the fp32 composed model, per-parameter gradient cosine >= 0.995 (0.99 for the
+    handful of tiny tensors whose gradients are sums of few bf16 terms)."""
+    from loomformer_paraplex_b200.ops import kernels
+    from loomformer_paraplex_b200.ops.fused_plan import FusedPlan
+    extra, B, T = PLAN_VARIANTS[name]
+    torch.manual_seed(0)
+    cfg = Config(**dict(CFG, **extra))
+    V = int(cfg.vocab)
+    cpu = Model(cfg).train()
+    with torch.no_grad():
+        for _, p in cpu.named_parameters():
+            if p.abs().max() == 0:
+                p.normal_(0.0, 0.1)
+    gpu = copy.deepcopy(cpu).cuda().train()
+    x = torch.randint(0, V, (B, T)); y = torch.randint(0, V, (B, T))
+    pos, seg, mask = None, None, None
+    if name == "head_floor":            # packed rows: two documents per row, positions restart, attention stays inside
+        cut = 100
+        pos = torch.cat((torch.arange(cut), torch.arange(T - cut))).view(1, T).expand(B, T).contiguous()
+        seg = torch.cat((torch.zeros(cut), torch.ones(T - cut))).long().view(1, T).expand(B, T).contiguous()
+        mask = ((seg[:, :, None] == seg[:, None, :]) & torch.ones(T, T, dtype=torch.bool).tril()).unsqueeze(1)
+    loss_ref = F.cross_entropy(cpu(x, attn_mask=mask, position_ids=pos).reshape(-1, V), y.reshape(-1))
+    loss_ref.backward()
+    flat = FlatParams(gpu, want_bf16_shadow=True)
+    plan = FusedPlan(gpu, flat=flat)
+    with torch.no_grad():
+        loss, _ = plan.run(x.cuda(), y.cuda(), None if pos is None else pos.cuda(), None if seg is None else seg.cuda(),
+                           want_grad=True)
+    kernels.check_status(torch.device("cuda"))
+    assert not plan.K.fallbacks, dict(plan.K.fallbacks)
+    assert abs(float(loss) - float(loss_ref)) < 3e-2, (float(loss), float(loss_ref))
+    bad = []
+    for (n, pc), (_, pg) in zip(cpu.named_parameters(), gpu.named_parameters()):
+        if pc.grad is None or float(pc.grad.norm()) < 1e-6:
+            continue
+        a, b = pc.grad.flatten().double(), pg.grad.detach().cpu().flatten().double()
+        cos = float((a @ b) / (a.norm() * b.norm() + 1e-30))
+        if cos < (0.995 if a.numel() >= 4096 else 0.99):
+            bad.append((n, round(cos, 5), a.numel()))
+    assert not bad, bad
+
+
 def test_engine_trains_on_gpu():
     from loomformer_paraplex_b200.data.synthetic import SyntheticTokens
     from loomformer_paraplex_b200.ops import kernels, native
