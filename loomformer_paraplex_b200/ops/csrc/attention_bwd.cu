@@ -33,7 +33,8 @@ struct Params {
   const void* qkc; const void* dqkc;
   const float* lse; const int* seg;
   void* dq_attn; float* dk_heads; float* dv_heads;
-  int B, QH, KVH, HD, Tc, T, s, e;
+  int B, QH, KVH, HD, Tc, T, s, e;   // Tc, s, e describe this launch's query tile (<= 128 rows)
+  int Tc_total, q0;                  // rows per batch entry in qkc / lse, and the tile's first row among them
   long long row_pitch;
   float scale, scale_log2e;
   int* status;
@@ -69,7 +70,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_bwd_kernel(const __grid_const
   const int kvh = qh / (p.QH / p.KVH);
   volatile int* status = p.status;
   const int nblk = (p.e + BKEY - 1) / BKEY;
-  const int ksteps = p.HD / 16;
+  const int ksteps = (p.HD + 15) / 16;   // the TMA unit zero-fills columns past HD
   const int hdp = (p.HD <= 64) ? 64 : 128;
   const int ntile = (p.HD > 64) ? 2 : 1;
 
@@ -93,9 +94,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_bwd_kernel(const __grid_const
       tma_prefetch_desc(&p.k); tma_prefetch_desc(&p.v);
       mbar_expect_tx(q_full, 3 * ntile * TILE);
       for (int i = 0; i < ntile; ++i) {
-        tma_load_4d(sQ + i * TILE, &p.q, q_full, 64 * i, qh, 0, b * p.Tc);
-        tma_load_4d(sDOk + i * TILE, &p.dok, q_full, 64 * i, qh, 1, b * p.Tc);
-        tma_load_4d(sDOv + i * TILE, &p.dov, q_full, 64 * i, qh, 2, b * p.Tc);
+        tma_load_4d(sQ + i * TILE, &p.q, q_full, 64 * i, qh, 0, b * p.Tc_total + p.q0);
+        tma_load_4d(sDOk + i * TILE, &p.dok, q_full, 64 * i, qh, 1, b * p.Tc_total + p.q0);
+        tma_load_4d(sDOv + i * TILE, &p.dov, q_full, 64 * i, qh, 2, b * p.Tc_total + p.q0);
       }
       for (int j = 0; j < nblk; ++j) {
         if (!mbar_wait(kv_empty, (j & 1) ^ 1, status, 301)) break;
@@ -167,7 +168,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_bwd_kernel(const __grid_const
     const int* segrow = p.seg ? p.seg + (long long)b * p.T : nullptr;
     const int my_seg = (segrow && row_ok) ? segrow[qpos] : 0;
     const uint32_t lane_off = uint32_t(quad * 32) << 16;
-    const long long row = (long long)b * p.Tc + r;
+    const long long row = (long long)b * p.Tc_total + p.q0 + r;
     // delta = rowsum(dO_v o O_v + dO_k o O_k); lse in log2 units
     float delta = 0.f, lse2 = 0.f;
     if (row_ok) {
@@ -181,7 +182,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_bwd_kernel(const __grid_const
         const float2 g2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(g + sec + c));
         delta += a1.x * g1.x + a1.y * g1.y + a2.x * g2.x + a2.y * g2.y;
       }
-      lse2 = p.lse[((long long)b * p.QH + qh) * p.Tc + r] * 1.4426950408889634f;
+      lse2 = p.lse[((long long)b * p.QH + qh) * p.Tc_total + p.q0 + r] * 1.4426950408889634f;
     }
     bool ok = true;
     for (int j = 0; j < nblk && ok; ++j) {
@@ -290,7 +291,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_bwd_kernel(const __grid_const
 }  // namespace
 
 extern "C" int loom_attn_bwd(const LoomAttn* a, cudaStream_t stream) {
-  if (a->HD % 16 || a->HD > 128 || a->Tc > BQ || a->Tc < 1) return -1;
+  if (a->HD % 8 || a->HD > 128 || a->Tc < 1) return -1;
   Params p;
   memset(&p, 0, sizeof(p));
   const long long N = (long long)a->QH * a->HD;
@@ -303,7 +304,8 @@ extern "C" int loom_attn_bwd(const LoomAttn* a, cudaStream_t stream) {
   if (!tma_host::make_4d_bf16(&p.v, a->vcache, a->HD, a->KVH, a->T, a->B, a->HD, kvd, kvd * a->T, 64, 1, BKEY, 1)) return -3;
   p.qkc = a->qkc; p.dqkc = a->dqkc; p.lse = a->lse; p.seg = a->seg;
   p.dq_attn = a->dq_attn; p.dk_heads = a->dk_heads; p.dv_heads = a->dv_heads;
-  p.B = a->B; p.QH = a->QH; p.KVH = a->KVH; p.HD = a->HD; p.Tc = a->Tc; p.T = a->T; p.s = a->s; p.e = a->e;
+  p.B = a->B; p.QH = a->QH; p.KVH = a->KVH; p.HD = a->HD; p.T = a->T;
+  p.Tc_total = a->Tc;
   p.row_pitch = 3 * N;
   p.scale = 1.0f / sqrtf((float)a->HD);
   p.scale_log2e = p.scale * 1.4426950408889634f;
@@ -314,6 +316,14 @@ extern "C" int loom_attn_bwd(const LoomAttn* a, cudaStream_t stream) {
     if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
     configured = true;
   }
-  attn_bwd_kernel<<<a->B * a->QH, THREADS, smem, stream>>>(p);
+  // one launch per 128-row query tile; launches are stream-ordered, so the tiles' additions into the key / value
+  // gradient slabs keep a fixed order
+  for (int q0 = 0; q0 < a->Tc; q0 += BQ) {
+    p.q0 = q0;
+    p.Tc = a->Tc - q0 < BQ ? a->Tc - q0 : BQ;
+    p.s = a->s + q0;
+    p.e = a->s + q0 + p.Tc;
+    attn_bwd_kernel<<<a->B * a->QH, THREADS, smem, stream>>>(p);
+  }
   return (int)cudaGetLastError();
 }

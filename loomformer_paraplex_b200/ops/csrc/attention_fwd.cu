@@ -35,7 +35,8 @@ struct Params {
   void* out_ctx;             // qkc + sector 2
   float* lse;                // [B, QH, Tc]
   const int* seg;            // [B, T] or null
-  int B, QH, KVH, HD, Tc, T, s, e;
+  int B, QH, KVH, HD, Tc, T, s, e;   // Tc, s, e describe this launch's query tile (<= 128 rows)
+  int Tc_total, q0;          // rows per batch entry in qkc / lse, and the tile's first row among them
   long long row_pitch;       // elements between consecutive query rows of qkc (3*N)
   float scale_log2e;         // softmax scale * log2(e)
   float scale;
@@ -66,7 +67,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_kernel(const __grid_const
   const int kvh = qh / (p.QH / p.KVH);
   volatile int* status = p.status;
   const int nblk = (p.e + BKEY - 1) / BKEY;
-  const int ksteps = p.HD / 16;             // MMA K steps over the head dimension
+  const int ksteps = (p.HD + 15) / 16;   // the TMA unit zero-fills columns past HD             // MMA K steps over the head dimension
   const int hdp = (p.HD <= 64) ? 64 : 128;  // padded head dim = N of the P.V products
 
   if (threadIdx.x == 0) {
@@ -90,7 +91,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_kernel(const __grid_const
       tma_prefetch_desc(&p.q); tma_prefetch_desc(&p.k); tma_prefetch_desc(&p.v);
       const int ntile = (p.HD > 64) ? 2 : 1;
       mbar_expect_tx(q_full, ntile * TILE);
-      for (int i = 0; i < ntile; ++i) tma_load_4d(sQ + i * TILE, &p.q, q_full, 64 * i, qh, 0, b * p.Tc);
+      for (int i = 0; i < ntile; ++i) tma_load_4d(sQ + i * TILE, &p.q, q_full, 64 * i, qh, 0, b * p.Tc_total + p.q0);
       uint32_t it = 0;
       bool ok = true;
       for (int pass = 0; pass < 2 && ok; ++pass) {
@@ -243,7 +244,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_kernel(const __grid_const
     if (ok && mbar_wait(o_full, 0, status, 208)) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      const long long row = (long long)b * p.Tc + r;
+      const long long row = (long long)b * p.Tc_total + p.q0 + r;
       __nv_bfloat16* ok_out = reinterpret_cast<__nv_bfloat16*>(p.out_kctx) + row * p.row_pitch + qh * p.HD;
       __nv_bfloat16* ov_out = reinterpret_cast<__nv_bfloat16*>(p.out_ctx) + row * p.row_pitch + qh * p.HD;
 #pragma unroll 1
@@ -268,7 +269,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_kernel(const __grid_const
           }
         }
       }
-      if (row_ok) p.lse[((long long)b * p.QH + qh) * p.Tc + r] = mx * p.scale + __logf(fmaxf(l, 1e-37f));
+      if (row_ok) p.lse[((long long)b * p.QH + qh) * p.Tc_total + p.q0 + r] = mx * p.scale + __logf(fmaxf(l, 1e-37f));
     }
   }
   tc_fence_before();
@@ -279,7 +280,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_kernel(const __grid_const
 }  // namespace
 
 extern "C" int loom_attn_fwd(const LoomAttn* a, cudaStream_t stream) {
-  if (a->HD % 16 || a->HD > 128 || a->Tc > BQ || a->Tc < 1) return -1;
+  if (a->HD % 8 || a->HD > 128 || a->Tc < 1) return -1;
   Params p;
   memset(&p, 0, sizeof(p));
   const long long N = (long long)a->QH * a->HD;
@@ -292,7 +293,8 @@ extern "C" int loom_attn_fwd(const LoomAttn* a, cudaStream_t stream) {
   p.out_kctx = (__nv_bfloat16*)a->qkc + N;
   p.out_ctx = (__nv_bfloat16*)a->qkc + 2 * N;
   p.lse = a->lse; p.seg = a->seg;
-  p.B = a->B; p.QH = a->QH; p.KVH = a->KVH; p.HD = a->HD; p.Tc = a->Tc; p.T = a->T; p.s = a->s; p.e = a->e;
+  p.B = a->B; p.QH = a->QH; p.KVH = a->KVH; p.HD = a->HD; p.T = a->T;
+  p.Tc_total = a->Tc;
   p.row_pitch = 3 * N;
   p.scale = 1.0f / sqrtf((float)a->HD);
   p.scale_log2e = p.scale * 1.4426950408889634f;
@@ -303,6 +305,14 @@ extern "C" int loom_attn_fwd(const LoomAttn* a, cudaStream_t stream) {
     if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
     configured = true;
   }
-  attn_fwd_kernel<<<a->B * a->QH, THREADS, smem, stream>>>(p);
+  // a chunk longer than 128 queries (wide temporal windows, the unchunked forward) goes out as one launch per
+  // 128-row query tile; a tile's keys end at its own last query
+  for (int q0 = 0; q0 < a->Tc; q0 += BQ) {
+    p.q0 = q0;
+    p.Tc = a->Tc - q0 < BQ ? a->Tc - q0 : BQ;
+    p.s = a->s + q0;
+    p.e = a->s + q0 + p.Tc;
+    attn_fwd_kernel<<<a->B * a->QH, THREADS, smem, stream>>>(p);
+  }
   return (int)cudaGetLastError();
 }

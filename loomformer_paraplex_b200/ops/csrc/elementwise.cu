@@ -573,7 +573,7 @@ extern "C" int loom_dread(int bwd, const float* q, const void* hk, const void* h
 }
 
 extern "C" int loom_cap_bwd(const void* dy, const void* a, void* da, int M, int N, float cap, cudaStream_t st) {
-  if (N % 8 || N > 1024) return -1;
+  if (N % 8 || N > 2048) return -1;
   const unsigned grid = (M + 7) / 8;
   const int nch = (N + 255) / 256;
 #define CAP_B(K) cap_bwd_kernel<K><<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)a, (bf16*)da, M, N, cap)
@@ -584,25 +584,27 @@ extern "C" int loom_cap_bwd(const void* dy, const void* a, void* da, int M, int 
 
 extern "C" int loom_add_ln_fwd(const void* a, const void* b, const float* w, const float* bias, void* y, void* x,
                                float* mean, float* rstd, int M, int N, float eps, float cap, cudaStream_t st) {
-  if (N % 8 || N > 1024) return -1;
+  if (N % 8 || N > 2048) return -1;
   const unsigned grid = (M + 7) / 8;
   const int nch = (N + 255) / 256;
 #define LN_F(K) add_ln_fwd_kernel<K><<<grid, 256, 0, st>>>((const bf16*)a, (const bf16*)b, w, bias, (bf16*)y, (bf16*)x, mean, rstd, M, N, eps, cap)
-  if (nch == 1) LN_F(1); else if (nch == 2) LN_F(2); else if (nch == 3) LN_F(3); else LN_F(4);
+  if (nch == 1) LN_F(1); else if (nch == 2) LN_F(2); else if (nch == 3) LN_F(3); else if (nch == 4) LN_F(4);
+  else if (nch <= 6) LN_F(6); else LN_F(8);
 #undef LN_F
   return (int)cudaGetLastError();
 }
 
 extern "C" int loom_add_ln_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const float* w,
                                void* dx, float* gw, float* gb, int M, int N, cudaStream_t st) {
-  if (N % 8 || N > 1024) return -1;
+  if (N % 8 || N > 2048) return -1;
   unsigned grid = (M + 7) / 8;
   if (grid > 592) grid = 592;
   const int nch = (N + 255) / 256;
   const size_t shm = 2 * 8 * N * sizeof(float);
 #define LN_B(K) do { if (shm > 48 * 1024) cudaFuncSetAttribute(add_ln_bwd_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shm); \
     add_ln_bwd_kernel<K><<<grid, 256, shm, st>>>((const bf16*)dy, (const bf16*)x, mean, rstd, w, (bf16*)dx, gw, gb, M, N); } while (0)
-  if (nch == 1) LN_B(1); else if (nch == 2) LN_B(2); else if (nch == 3) LN_B(3); else LN_B(4);
+  if (nch == 1) LN_B(1); else if (nch == 2) LN_B(2); else if (nch == 3) LN_B(3); else if (nch == 4) LN_B(4);
+  else if (nch <= 6) LN_B(6); else LN_B(8);
 #undef LN_B
   return (int)cudaGetLastError();
 }

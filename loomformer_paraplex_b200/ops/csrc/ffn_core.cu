@@ -27,6 +27,12 @@ typedef __nv_bfloat162 bf2;
 __device__ __forceinline__ float2 ld2(const __nv_bfloat16* p) { return __bfloat1622float2(*reinterpret_cast<const bf2*>(p)); }
 __device__ __forceinline__ void st2(__nv_bfloat16* p, float a, float b) { *reinterpret_cast<bf2*>(p) = __floats2bfloat162_rn(a, b); }
 
+// one MUFU instruction (relative error about 2^-11, below the bf16 resolution of everything stored from it)
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float phase_s0(float beta) { return sinf(HALF_PI * beta * rsqrtf(1.f + beta * beta)); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
@@ -97,7 +103,7 @@ __device__ __forceinline__ void core_forward_elem(const CoreScalars& S, float x,
   if (AXIS >= 0) {
     const float x0 = E.r * E.i, x1 = E.r * E.o, x2 = E.i * E.o;
     const float n3 = rsqrtf((x0 * x0 + x1 * x1 + x2 * x2) * (1.f / 3.f) + 1e-6f);
-    const float a = S.tria_alpha * tanhf(x0 * n3), b = S.tria_alpha * tanhf(x1 * n3), c = S.tria_alpha * tanhf(x2 * n3);
+    const float a = S.tria_alpha * tanh_fast(x0 * n3), b = S.tria_alpha * tanh_fast(x1 * n3), c = S.tria_alpha * tanh_fast(x2 * n3);
     float T[9], pre[9];
     build_T<AXIS>(a, b, c, T);
     if (has_R) {
@@ -243,7 +249,7 @@ __device__ __forceinline__ void core_backward_elem(const CoreScalars& S, float x
     const float x0 = r * i, x1 = r * o, x2 = i * o;
     const float n3 = rsqrtf((x0 * x0 + x1 * x1 + x2 * x2) * (1.f / 3.f) + 1e-6f);
     const float y0 = x0 * n3, y1 = x1 * n3, y2 = x2 * n3;
-    const float t0 = tanhf(y0), t1 = tanhf(y1), t2 = tanhf(y2);
+    const float t0 = tanh_fast(y0), t1 = tanh_fast(y1), t2 = tanh_fast(y2);
     float T[9], pre[9], C[9], gC[9], gpre[9], gT[9];
     build_T<AXIS>(S.tria_alpha * t0, S.tria_alpha * t1, S.tria_alpha * t2, T);
     if (has_R) {

@@ -57,8 +57,13 @@ struct Params {
   long long ldc_head;   // group pitch of C (elements)
   const float* bias;    // [heads * n_per_head] or nullptr
   int M, n_per_head, heads;
-  int accumulate;       // C += result (read-modify-write in the epilogue)
+  int accumulate;       // C += result
   int out_fp32;
+  // c_tma != 0: the epilogue stages 32-row x 128-byte boxes in shared memory and hands them to the TMA unit (plain
+  // store, or element-wise add in L2 when `accumulate`), so global memory sees full lines written asynchronously
+  // instead of one 16-byte store per row and thread.  cmap describes C as (N, M, heads).
+  int c_tma;
+  CUtensorMap cmap;
   int a_lbo, a_sbo, b_lbo, b_sbo;
   int* status;
   // sharded-weight gather (all-gather fused into the consuming GEMM): rank r owns the 64-row blocks
@@ -73,13 +78,162 @@ struct Params {
   float* rs_out[8];
 };
 
+constexpr int OUT_STAGE_BYTES = 4 * 2 * 4096;   // four epilogue warps x two 32-row x 128-byte staging boxes
+
+// 16-byte chunk `chunk` of row `row` inside a 128-byte-swizzled box with 128-byte rows
+__device__ __forceinline__ uint32_t swz128(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
+
+__device__ __forceinline__ void tma_reduce_add_3d(const void* tmap, const void* smem_src, int x, int y, int z) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+
+// Accumulator rows [32 lanes of this warp] x [BN columns] -> C through shared memory and the TMA unit.
+// `taddr`: TMEM address of the warp's lane quadrant and accumulator buffer; `row0`: output row of lane 0;
+// `stage`: this warp's two staging boxes; `nstore`: boxes this warp has issued so far (selects the box, bounds reuse).
+template <int BN>
+__device__ __forceinline__ void store_tile_tma(const Params& p, uint32_t taddr, int row0, int n0, int g, int lane,
+                                               uint8_t* stage, uint32_t& nstore) {
+  const float* bias = p.bias ? p.bias + (long long)g * p.n_per_head : nullptr;
+  const int W = p.out_fp32 ? 32 : 64;            // columns per 128-byte row
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += W) {
+    const int n = n0 + c0;
+    if (n >= p.n_per_head) break;                // nothing of this tile is left of here (uniform over the warp)
+    uint8_t* buf = stage + (nstore & 1) * 4096;
+    if (nstore >= 2) {                           // the box issued two steps ago must have been read out
+      if (lane == 0) tma_store_wait_read1();
+      __syncwarp();
+    }
+    uint32_t r[32];
+    tmem_ld_32x32(taddr + c0, r);
+    if (p.out_fp32) {
+      tmem_ld_wait();
+      if (bias) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) if (n + i < p.n_per_head) r[i] = __float_as_uint(__uint_as_float(r[i]) + bias[n + i]);
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(buf + swz128(lane, c)) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+    } else {
+      uint32_t r2[32];
+      tmem_ld_32x32(taddr + c0 + 32, r2);
+      tmem_ld_wait();
+      if (bias) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (n + i < p.n_per_head) r[i] = __float_as_uint(__uint_as_float(r[i]) + bias[n + i]);
+          if (n + 32 + i < p.n_per_head) r2[i] = __float_as_uint(__uint_as_float(r2[i]) + bias[n + 32 + i]);
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint4 o;
+        __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(__uint_as_float(r[8 * c + 2 * j]), __uint_as_float(r[8 * c + 2 * j + 1]));
+        *reinterpret_cast<uint4*>(buf + swz128(lane, c)) = o;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(__uint_as_float(r2[8 * c + 2 * j]), __uint_as_float(r2[8 * c + 2 * j + 1]));
+        *reinterpret_cast<uint4*>(buf + swz128(lane, 4 + c)) = o;
+      }
+    }
+    fence_proxy_async();                         // generic-proxy writes above -> visible to the TMA unit
+    __syncwarp();
+    if (lane == 0) {
+      if (p.accumulate) tma_reduce_add_3d(&p.cmap, buf, n, row0, g);
+      else tma_store_3d(&p.cmap, buf, n, row0, g);
+      tma_store_commit();
+    }
+    ++nstore;
+  }
+}
+
+// Direct epilogue: every thread stores its own row (used when C cannot be described to the TMA unit -- pitch or base
+// not 16-byte aligned -- and by the reduce-scatter variant, whose destination is another rank's memory).
+template <int BN>
+__device__ __forceinline__ void store_tile_direct(const Params& p, uint32_t taddr, int row, int n0, int g) {
+  const long long c_row = (long long)row * p.ldc + (long long)g * p.ldc_head;
+  const float* bias = p.bias ? p.bias + (long long)g * p.n_per_head : nullptr;
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += 32) {
+    uint32_t r[32];
+    tmem_ld_32x32(taddr + c0, r);
+    tmem_ld_wait();
+    const int n = n0 + c0;
+    if (row < p.M && n < p.n_per_head) {
+      const int nvalid = min(32, p.n_per_head - n);
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+      if (bias) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) if (i < nvalid) v[i] += bias[n + i];
+      }
+      if (p.rs_world > 1) {
+        // reduce-scatter epilogue: this rank's partial product of a row goes, by plain 16-byte stores over
+        // NVLink, into slot `rs_rank` of the staging buffer [world][rows_per_rank][N] of the rank that owns the
+        // row; the owner sums its slots after the closing barrier (deterministic, no atomics on the link)
+        const int owner = row / p.rs_rows_per_rank;
+        float* dst = p.rs_out[owner] +
+                     ((long long)p.rs_rank * p.rs_rows_per_rank + (row - owner * p.rs_rows_per_rank)) * p.ldc + n;
+        if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        } else {
+          for (int i = 0; i < nvalid; ++i) dst[i] = v[i];
+        }
+      } else if (p.out_fp32) {
+        float* dst = reinterpret_cast<float*>(p.c) + c_row + n;
+        if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            if (p.accumulate) { float4 old = *reinterpret_cast<float4*>(dst + i); o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
+            *reinterpret_cast<float4*>(dst + i) = o;
+          }
+        } else {
+          for (int i = 0; i < nvalid; ++i) dst[i] = p.accumulate ? dst[i] + v[i] : v[i];
+        }
+      } else {
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + c_row + n;
+        if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            if (p.accumulate) {
+              uint4 old = *reinterpret_cast<uint4*>(dst + i);
+              const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(ob[j]); v[i + 2 * j] += f.x; v[i + 2 * j + 1] += f.y; }
+            }
+            uint4 o;
+            __nv_bfloat162* ob2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) ob2[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
+            *reinterpret_cast<uint4*>(dst + i) = o;
+          }
+        } else {
+          for (int i = 0; i < nvalid; ++i) {
+            float x = v[i];
+            if (p.accumulate) x += __bfloat162float(dst[i]);
+            dst[i] = __float2bfloat16(x);
+          }
+        }
+      }
+    }
+  }
+}
+
 template <int BN>
 struct Cfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN >= 256) ? 4 : ((BN >= 128) ? 6 : 8);
-  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + OUT_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
   static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : 2 * BN;
 };
 
@@ -93,7 +247,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_kernel(const __grid_const
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint8_t* out_stage = smem + C::STAGES * C::STAGE_BYTES;      // 1024-byte aligned: every stage is a multiple of 1024
+  uint64_t* full = reinterpret_cast<uint64_t*>(out_stage + OUT_STAGE_BYTES);
   uint64_t* empty = full + C::STAGES;
   uint64_t* acc_full = empty + C::STAGES;
   uint64_t* acc_empty = acc_full + 2;
@@ -225,7 +380,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_kernel(const __grid_const
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5)
     const int q = warp & 3;             // TMEM lane quadrant this warp may access
-    uint32_t tcount = 0;
+    uint32_t tcount = 0, nstore = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++tcount) {
       const int tm = tile % tiles_m;
@@ -237,78 +392,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_kernel(const __grid_const
       const int row = tm * BM + q * 32 + lane;
       const int n0 = tn * BN;
       const uint32_t taddr = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
-      const long long c_row = (long long)row * p.ldc + (long long)g * p.ldc_head;
-      const float* bias = p.bias ? p.bias + (long long)g * p.n_per_head : nullptr;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c0, r);
-        tmem_ld_wait();
-        const int n = n0 + c0;
-        if (row < p.M && n < p.n_per_head) {
-          const int nvalid = min(32, p.n_per_head - n);
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          if (bias) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) if (i < nvalid) v[i] += bias[n + i];
-          }
-          if (p.rs_world > 1) {
-            // reduce-scatter epilogue: this rank's partial product of a row goes, by plain 16-byte stores over
-            // NVLink, into slot `rs_rank` of the staging buffer [world][rows_per_rank][N] of the rank that owns the
-            // row; the owner sums its slots after the closing barrier (deterministic, no atomics on the link)
-            const int owner = row / p.rs_rows_per_rank;
-            float* dst = p.rs_out[owner] +
-                         ((long long)p.rs_rank * p.rs_rows_per_rank + (row - owner * p.rs_rows_per_rank)) * p.ldc + n;
-            if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-            } else {
-              for (int i = 0; i < nvalid; ++i) dst[i] = v[i];
-            }
-          } else if (p.out_fp32) {
-            float* dst = reinterpret_cast<float*>(p.c) + c_row + n;
-            if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 4) {
-                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                if (p.accumulate) { float4 old = *reinterpret_cast<float4*>(dst + i); o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
-                *reinterpret_cast<float4*>(dst + i) = o;
-              }
-            } else {
-              for (int i = 0; i < nvalid; ++i) dst[i] = p.accumulate ? dst[i] + v[i] : v[i];
-            }
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + c_row + n;
-            if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 8) {
-                if (p.accumulate) {
-                  uint4 old = *reinterpret_cast<uint4*>(dst + i);
-                  const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(ob[j]); v[i + 2 * j] += f.x; v[i + 2 * j + 1] += f.y; }
-                }
-                uint4 o;
-                __nv_bfloat162* ob2 = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) ob2[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
-                *reinterpret_cast<uint4*>(dst + i) = o;
-              }
-            } else {
-              for (int i = 0; i < nvalid; ++i) {
-                float x = v[i];
-                if (p.accumulate) x += __bfloat162float(dst[i]);
-                dst[i] = __float2bfloat16(x);
-              }
-            }
-          }
-        }
-      }
+      if (p.c_tma) store_tile_tma<BN>(p, taddr, tm * BM + q * 32, n0, g, lane, out_stage + q * 8192, nstore);
+      else store_tile_direct<BN>(p, taddr, row, n0, g);
       tc_fence_before();
       mbar_arrive(&acc_empty[acc]);
     }
+    if (nstore > 0 && lane == 0) tma_store_wait_all();      // staged boxes must be out before shared memory goes away
   }
 
   tc_fence_before();
@@ -330,7 +419,7 @@ struct PairCfg {
   static constexpr int B_BYTES = HALF * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN >= 256) ? 6 : 8;
-  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + OUT_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
   static constexpr int TMEM_COLS = 2 * BN;
 };
 
@@ -339,7 +428,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_pair_kernel(const __grid_
   using C = PairCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint8_t* out_stage = smem + C::STAGES * C::STAGE_BYTES;      // 1024-byte aligned: every stage is a multiple of 1024
+  uint64_t* full = reinterpret_cast<uint64_t*>(out_stage + OUT_STAGE_BYTES);
   uint64_t* empty = full + C::STAGES;
   uint64_t* acc_full = empty + C::STAGES;
   uint64_t* acc_empty = acc_full + 2;
@@ -453,7 +543,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_pair_kernel(const __grid_
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5 of both CTAs)
     const int q = warp & 3;
-    uint32_t tcount = 0;
+    uint32_t tcount = 0, nstore = 0;
     bool ok = true;
     for (int tile = pair; tile < total && ok; tile += npairs, ++tcount) {
       const int tm = tile % tiles_m;
@@ -465,66 +555,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_pair_kernel(const __grid_
       const int row = tm * (2 * BM) + (int)rank * BM + q * 32 + lane;
       const int n0 = tn * BN;
       const uint32_t taddr = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
-      const long long c_row = (long long)row * p.ldc + (long long)g * p.ldc_head;
-      const float* bias = p.bias ? p.bias + (long long)g * p.n_per_head : nullptr;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c0, r);
-        tmem_ld_wait();
-        const int n = n0 + c0;
-        if (row < p.M && n < p.n_per_head) {
-          const int nvalid = min(32, p.n_per_head - n);
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          if (bias) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) if (i < nvalid) v[i] += bias[n + i];
-          }
-          if (p.out_fp32) {
-            float* dst = reinterpret_cast<float*>(p.c) + c_row + n;
-            if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 4) {
-                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                if (p.accumulate) { float4 old = *reinterpret_cast<float4*>(dst + i); o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
-                *reinterpret_cast<float4*>(dst + i) = o;
-              }
-            } else {
-              for (int i = 0; i < nvalid; ++i) dst[i] = p.accumulate ? dst[i] + v[i] : v[i];
-            }
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + c_row + n;
-            if (nvalid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 8) {
-                if (p.accumulate) {
-                  uint4 old = *reinterpret_cast<uint4*>(dst + i);
-                  const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(ob[j]); v[i + 2 * j] += f.x; v[i + 2 * j + 1] += f.y; }
-                }
-                uint4 o;
-                __nv_bfloat162* ob2 = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) ob2[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
-                *reinterpret_cast<uint4*>(dst + i) = o;
-              }
-            } else {
-              for (int i = 0; i < nvalid; ++i) {
-                float x = v[i];
-                if (p.accumulate) x += __bfloat162float(dst[i]);
-                dst[i] = __float2bfloat16(x);
-              }
-            }
-          }
-        }
-      }
+      if (p.c_tma) store_tile_tma<BN>(p, taddr, tm * (2 * BM) + (int)rank * BM + q * 32, n0, g, lane, out_stage + q * 8192, nstore);
+      else store_tile_direct<BN>(p, taddr, row, n0, g);
       tc_fence_before();
       // this accumulator buffer may be overwritten once the epilogue threads of BOTH CTAs have read it
       mbar_arrive_cluster(mapa_shared(smem_u32(&acc_empty[acc]), 0));
     }
+    if (nstore > 0 && lane == 0) tma_store_wait_all();
   }
 
   // neither CTA may leave (or free its TMEM) while the other can still touch its shared memory or barriers
@@ -550,6 +587,21 @@ bool fill_map(CUtensorMap* map, const LoomOperand& o, bool mn_major, int box_mn)
   cuuint32_t elem[3] = {1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(o.ptr), dims, strides, box, elem,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// C viewed as (N, M, heads) for the staged epilogue: boxes of 128 bytes x 32 rows, 128-byte swizzle
+bool fill_c_map(CUtensorMap* map, void* c, int M, int N, int heads, long long ldc, long long ldc_head, bool fp32) {
+  tma_host::EncodeTiledFn fn = tma_host::encode_fn();
+  if (!fn) return false;
+  const cuuint64_t es = fp32 ? 4 : 2;
+  cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)(heads > 1 ? heads : 1)};
+  cuuint64_t strides[2] = {(cuuint64_t)ldc * es, (cuuint64_t)(heads > 1 ? ldc_head : ldc * (long long)M) * es};
+  cuuint32_t box[3] = {fp32 ? 32u : 64u, 32u, 1u};
+  cuuint32_t elem[3] = {1, 1, 1};
+  CUresult r = fn(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, c, dims, strides, box,
+                  elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
@@ -654,6 +706,15 @@ extern "C" int loom_gemm_bf16(const LoomGemm* g, cudaStream_t stream) {
   p.c = g->c; p.ldc = g->ldc; p.ldc_head = g->ldc_head; p.bias = g->bias;
   p.M = g->M; p.n_per_head = g->N; p.heads = g->heads > 0 ? g->heads : 1;
   p.accumulate = g->accumulate; p.out_fp32 = g->out_fp32; p.status = g->status;
+  {
+    // staged TMA epilogue whenever C can be described to the TMA unit (LOOM_GEMM_EPILOGUE=direct turns it off)
+    static int want = -1;
+    if (want < 0) { const char* e = getenv("LOOM_GEMM_EPILOGUE"); want = (e != nullptr && e[0] == 'd') ? 0 : 1; }
+    const long long es = g->out_fp32 ? 4 : 2;
+    const bool ok = want && g->rs_world <= 1 && (reinterpret_cast<uintptr_t>(g->c) & 15) == 0 && (g->ldc * es) % 16 == 0 &&
+                    (p.heads <= 1 || (g->ldc_head * es) % 16 == 0);
+    p.c_tma = (ok && fill_c_map(&p.cmap, g->c, p.M, p.n_per_head, p.heads, g->ldc, g->ldc_head, g->out_fp32 != 0)) ? 1 : 0;
+  }
   // K-major: 8-row groups are 1024 B apart (SBO); LBO unused.  MN-major: 64-element blocks along MN are
   // 8192 B apart (LBO), 8-row groups along K are 1024 B apart (SBO).
   p.a_lbo = a_mn ? 8192 : 0; p.a_sbo = 1024;

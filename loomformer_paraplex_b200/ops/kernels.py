@@ -57,24 +57,26 @@ def _pick_bn(M: int, N: int, heads: int = 1) -> int:
 _FORCED_TILE = {"cta64": (64, 0), "cta128": (128, 0), "cta256": (256, 0), "pair128": (128, 1), "pair256": (256, 1)}
 
 
-def _pick_tile(M: int, N: int, heads: int = 1, plain: bool = True):
+def _pick_tile(M: int, N: int, heads: int = 1, plain: bool = True, K: int = 0):
     """``(tile width, pair)``.  ``pair`` selects 256-row tiles computed by clusters of two CTAs
-    (``tcgen05.mma.cta_group::2``): each SM then stages 128 rows of A and only half of the tile's B columns per
-    k-block, which is what the kernel is bound by (operand delivery from L2).  Pair tiles are used when they still
-    fill the 74 SM pairs; small problems keep single-CTA tiles, which give twice as many schedulable units.
-    ``LOOM_GEMM_TILE`` (cta64|cta128|cta256|pair128|pair256) forces one shape for sweeps; ``LOOM_GEMM_PAIR=0`` turns
-    pair tiles off."""
+    (``tcgen05.mma.cta_group::2``): each SM stages 128 rows of A and only half of the tile's B columns per k-block.
+    Measured on B200 against the single-CTA tiles (back-to-back launches, M = 2048): pair tiles are as fast or faster
+    on every linear shape of the training step, 256-wide ones unless the reduction is long and only the 128-wide ones
+    give enough tiles to occupy the 74 SM pairs.  ``LOOM_GEMM_TILE`` (cta64|cta128|cta256|pair128|pair256) forces one
+    shape for sweeps; ``LOOM_GEMM_PAIR=0`` turns pair tiles off."""
     forced = os.environ.get("LOOM_GEMM_TILE")
     if forced in _FORCED_TILE:
         bn, pair = _FORCED_TILE[forced]
-        if not pair or (plain and N >= 128 and M >= 256):
+        if not pair or (plain and N > 64 and M >= 256):
             return bn, pair
-    if plain and M >= 256 and N >= 128 and os.environ.get("LOOM_GEMM_PAIR", "0") != "0":
+    small_n = int(os.environ.get("LOOM_GEMM_PAIR_MIN_N", "65"))      # narrowest output that still takes pair tiles
+    if plain and M >= 256 and N >= small_n and os.environ.get("LOOM_GEMM_PAIR", "1") != "0":
         rows = -(-M // 256)
-        if N >= 256 and rows * (-(-N // 256)) * heads >= 2 * 74:
+        t256 = rows * (-(-N // 256)) * heads
+        # 256-wide pair tiles when they occupy at least half of the 74 SM pairs (a long reduction wants all of them)
+        if N >= 256 and (t256 >= 74 or (K < 4096 and t256 >= 37)):
             return 256, 1
-        if rows * (-(-N // 128)) * heads >= 74:
-            return 128, 1
+        return 128, 1
     return _pick_bn(M, N, heads), 0
 
 
@@ -92,7 +94,7 @@ def gemm(a_list: List[torch.Tensor], k_len: List[int], b, c: torch.Tensor, *, M:
         if bn:
             pair = 0
         else:
-            bn, pair = _pick_tile(M, N, heads, plain)
+            bn, pair = _pick_tile(M, N, heads, plain, sum(int(k) for k in k_len))
     ext.gemm(a_list, k_len, a_k0 or [0] * n, b_k0 or [0] * n, b if isinstance(b, (list, tuple)) else [b], a_mn, b_mn,
              c, bias, M, N, heads, accumulate,
              bn or _pick_bn(M, N, heads), swap_mn, status_word(c.device), peer_ptrs or [], gather_rank,
@@ -371,7 +373,8 @@ class _ElementwiseMixin:
 
     # ------------------------------------------------------------------ attention
     def _attn_ok(self, d, qkc, s, e):
-        return qkc.dtype == torch.bfloat16 and d.hd % 16 == 0 and d.hd <= 128 and (e - s) <= 128
+        # any chunk length (the kernels walk 128-row query tiles) and any head dim that keeps rows 16-byte aligned
+        return qkc.dtype == torch.bfloat16 and d.hd % 8 == 0 and d.hd <= 128 and e > s
 
     def attn_fwd(self, d, qkc, kcache, vcache, s, e, seg):
         if not self._attn_ok(d, qkc, s, e):
@@ -388,7 +391,7 @@ class _ElementwiseMixin:
 
     def alloc_kv_grad(self, d, B, T, device):
         """Per-query-head key/value gradient slabs (the GQA group sum happens in rope_bwd)."""
-        if d.hd % 16 or d.hd > 128:
+        if d.hd % 8 or d.hd > 128:
             return super().alloc_kv_grad(d, B, T, device)
         return torch.zeros(B, T, d.qh, d.hd, dtype=torch.float32, device=device)
 
@@ -466,7 +469,7 @@ class _ElementwiseMixin:
     # ------------------------------------------------------------------ add + LayerNorm
     def add_ln_fwd(self, a, b, w, bias, cap, eps=1e-5):
         M, N = a.shape
-        if N % 8 or N > 1024 or a.dtype != torch.bfloat16:
+        if N % 8 or N > 2048 or a.dtype != torch.bfloat16:
             self.fallbacks["add_ln_fwd"] += 1
             return super().add_ln_fwd(a, b, w, bias, cap, eps)
         y, x = torch.empty_like(a), torch.empty_like(a)
@@ -479,7 +482,7 @@ class _ElementwiseMixin:
 
     def add_ln_bwd(self, dy, x, mean, rstd, w, gw, gb, cap, a, b):
         M, N = x.shape
-        if N % 8 or N > 1024 or x.dtype != torch.bfloat16:
+        if N % 8 or N > 2048 or x.dtype != torch.bfloat16:
             self.fallbacks["add_ln_bwd"] += 1
             return super().add_ln_bwd(dy, x, mean, rstd, w, gw, gb, cap, a, b)
         dx = torch.empty_like(x)

@@ -77,6 +77,22 @@ def case_dgrad(K, M, n_in=768, n_out=3072):
     return (lambda: K.linear_dgrad(dy, w)), nbytes(dy, w, dx), 2.0 * M * n_in * n_out
 
 
+def case_imag_bwd(K, M):
+    """Backward of the per-head imaginary projection (head sectors): four batched per-head data-gradient GEMMs
+    (N = head dim), the shared-sector one, and their queued weight gradients."""
+    d = dims()
+    d.open_sectors, d.imag_in = False, d.n + 4 * d.hd
+    qkc, u, m2 = bf(M, 3, d.qh, d.hd), bf(M, d.n), bf(M, d.qh, d.hd)
+    w = bf(d.hidden, d.imag_in, scale=0.05)
+    dbeta = bf(M, d.hidden, scale=0.1)
+    gw = torch.zeros(d.hidden, d.imag_in, device="cuda")
+    def run():
+        K.imag_bwd(d, dbeta, qkc, u, m2, w, gw)
+        K.flush_wgrads()
+    flops = 2 * 2.0 * M * d.hidden * d.imag_in // d.qh * 1.0          # data + weight gradient of the per-head product
+    return run, nbytes(qkc, u, m2, w, dbeta, gw) + nbytes(qkc, u, m2, gw), flops
+
+
 def _core_inputs(M, B, H):
     x_real, beta_lin, pin = bf(M, H), bf(M, H, scale=1.5), bf(M, H, scale=0.5)
     alpha = torch.tensor(0.17, device="cuda")
@@ -173,7 +189,7 @@ def case_optimizer(K, M):
     return (lambda: opt.step()), n * (4 * 7 + 2) + n * 4, 0.0     # norm pass reads g; update reads p,g,m,v writes p,m,v,shadow
 
 
-CASES: Dict[str, Callable] = {"linear": case_linear, "dgrad": case_dgrad, "wgrad": case_wgrad,
+CASES: Dict[str, Callable] = {"imag_bwd": case_imag_bwd, "linear": case_linear, "dgrad": case_dgrad, "wgrad": case_wgrad,
                               "wgrad_grouped": case_wgrad_grouped, "ffn_core_fwd": case_ffn_core_fwd,
                               "ffn_core_bwd": case_ffn_core_bwd, "attn_fwd": case_attn_fwd, "attn_bwd": case_attn_bwd,
                               "dread_slot_bwd": case_dread_slot_bwd, "dread_fwd": case_dread_fwd,

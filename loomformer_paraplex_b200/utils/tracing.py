@@ -17,7 +17,8 @@ import torch
 
 _NVTX = os.environ.get("LOOM_NVTX", "0") == "1"
 
-FAMILIES = (("GEMMs (gemm_kernel: forward, data gradient, grouped weight gradient)", ("gemm_kernel",)),
+FAMILIES = (("GEMMs (gemm_kernel / gemm_pair_kernel: forward, data gradient, grouped weight gradient)",
+             ("gemm_kernel", "gemm_pair_kernel")),
             ("fused Paraplex core + Tria step (ffn_core_*)", ("ffn_core",)),
             ("attention (attn_fwd, attn_bwd)", ("attn_fwd", "attn_bwd")),
             ("depth attention (dread_*)", ("dread",)),

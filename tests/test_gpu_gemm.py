@@ -51,6 +51,24 @@ def test_pair_tiles_kmajor_linear(M, N, K, bn):
     assert _rel(c32, ref - bias + 1.0) < 1e-2
 
 
+@pytest.mark.parametrize("pair", [0, 1])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_output_the_tma_unit_cannot_describe_takes_the_direct_epilogue(pair, dtype):
+    """A row pitch that is not a multiple of 16 bytes (a column slice of a wider buffer) cannot go through the staged
+    TMA epilogue; the per-row store path must give the same numbers and touch nothing outside the slice."""
+    k = _k()
+    torch.manual_seed(8)
+    M, N, K = 520, 200, 136
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    wide = torch.full((M, N + (3 if dtype == torch.float32 else 2)), 7.0, device="cuda", dtype=dtype)
+    c = wide[:, :N]
+    k.gemm([x], [K], w, c, M=M, N=N, bn=128, pair=pair)
+    k.check_status(c.device)
+    assert _rel(c, x.float() @ w.float().t()) < 1e-2
+    assert bool((wide[:, N:] == 7.0).all())
+
+
 @pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, True), (True, False)])
 def test_pair_tiles_other_operand_layouts(a_mn, b_mn):
     k = _k()

@@ -217,7 +217,10 @@ def test_temporal_endpoint(Tc):
             _close(p1, p2, 3e-2, "dstate_in")
 
 
-@pytest.mark.parametrize("hd,qh,kvh,Tc,s", [(96, 8, 2, 128, 256), (64, 4, 2, 128, 0), (32, 4, 4, 100, 128), (96, 8, 2, 40, 88)])
+# the last three: windows wider than one 128-row query tile (cfg/alt.yaml 192, cfg/mini.yaml 256), head dim 24
+# (cfg/alt2.yaml) and a whole 512-token sequence as one chunk (the unchunked forward)
+@pytest.mark.parametrize("hd,qh,kvh,Tc,s", [(96, 8, 2, 128, 256), (64, 4, 2, 128, 0), (32, 4, 4, 100, 128), (96, 8, 2, 40, 88),
+                                            (96, 8, 2, 192, 192), (24, 4, 2, 256, 0), (64, 4, 2, 512, 0)])
 def test_attention_forward(hd, qh, kvh, Tc, s):
     from loomformer_paraplex_b200.ops import kernels
     ck, tk = _sets()
@@ -240,7 +243,10 @@ def test_attention_forward(hd, qh, kvh, Tc, s):
         _close(qkc1[:, 2], qkc2[:, 2], 2e-2, "ctx")
 
 
-@pytest.mark.parametrize("hd,qh,kvh,Tc,s", [(96, 8, 2, 128, 256), (64, 4, 2, 128, 0), (32, 4, 4, 100, 128), (96, 8, 2, 40, 88)])
+# the last three: windows wider than one 128-row query tile (cfg/alt.yaml 192, cfg/mini.yaml 256), head dim 24
+# (cfg/alt2.yaml) and a whole 512-token sequence as one chunk (the unchunked forward)
+@pytest.mark.parametrize("hd,qh,kvh,Tc,s", [(96, 8, 2, 128, 256), (64, 4, 2, 128, 0), (32, 4, 4, 100, 128), (96, 8, 2, 40, 88),
+                                            (96, 8, 2, 192, 192), (24, 4, 2, 256, 0), (64, 4, 2, 512, 0)])
 def test_attention_backward(hd, qh, kvh, Tc, s):
     from loomformer_paraplex_b200.ops import kernels
     ck, tk = _sets()

@@ -84,11 +84,23 @@ PLAN_VARIANTS = {
     "head_floor": (dict(phase_grad_mode="floor"), 4, 256),
     # one layer at the dimensions of the 113M benchmark model (8 x 96 heads, 2 KV heads, hidden 3072, window 128)
     "dims_113m": (dict(model_dim=768, n_q_heads=8, head_dim=96, gqa_group_size=4, hidden_mult=4.0, layers=1,
-                       tria_temporal_window=128, vocab=1024), 2, 384),
+                       tria_temporal_window=128, vocab=1024, seq_len=384), 2, 384),
     # one layer at the dimensions of cfg/smol360.yaml (15 x 64 heads, 5 KV heads, 171 neurons per head -> padded)
     "dims_smol360": (dict(model_dim=960, n_q_heads=15, head_dim=64, gqa_group_size=3, hidden=2565, hidden_mult=None,
                           layers=1, tria_temporal_window=128, vocab=1024, paraplex_gate_proj=True, final_norm=True,
                           tied_embeddings=True), 2, 256),
+    # one layer each at the dimensions of the shipped configurations whose attention shapes used to leave the native
+    # path: a 192-token window (cfg/alt.yaml), head dim 24 with open sectors and a 256-token window (cfg/alt2.yaml),
+    # model dim 1536 with a 256-token window (cfg/mini.yaml)
+    "dims_alt": (dict(model_dim=576, n_q_heads=6, head_dim=96, gqa_group_size=3, hidden_mult=4.0, layers=1, final_norm=True,
+                      paraplex_gate_proj=True, tria_temporal_window=192, vocab=1024, seq_len=384), 2, 384),
+    "dims_alt2": (dict(model_dim=576, n_q_heads=24, head_dim=24, gqa_group_size=4, hidden_mult=6.0, layers=1,
+                       final_norm=True, paraplex_gate_proj=True, phase_sectors="open", tria_temporal_window=256, vocab=1024,
+                       seq_len=512), 2, 512),
+    "dims_mini": (dict(model_dim=1536, n_q_heads=16, head_dim=96, gqa_group_size=4, hidden_mult=4.0, layers=1,
+                       final_norm=True, paraplex_gate_proj=True, tria_temporal_window=256, vocab=1024, seq_len=512), 2, 512),
+    # no Tria: the whole sequence is one chunk, attention walks several query tiles
+    "no_tria": (dict(tria_carry_enabled=False, seq_len=512), 2, 512),
 }
 
 
