@@ -370,7 +370,7 @@ void p2p_grad_step(int64_t W, int64_t rank, int64_t nblk, std::vector<int64_t> g
                    torch::Tensor v, torch::Tensor lr_mult, torch::Tensor wd, torch::Tensor active, torch::Tensor hyper,
                    torch::Tensor stats, torch::Tensor sumsq, double max_norm, torch::Tensor status,
                    c10::optional<torch::Tensor> owner_blk, c10::optional<torch::Tensor> slot_blk,
-                   c10::optional<torch::Tensor> replicate_blk) {
+                   c10::optional<torch::Tensor> replicate_blk, c10::optional<torch::Tensor> anchors, bool anchor_rank0) {
   const c10::cuda::CUDAGuard guard(m.device());
   TORCH_CHECK((int64_t)grads.size() == W && (int64_t)params.size() == W && (int64_t)shadow.size() == W &&
               (int64_t)sync.size() == W && W <= 8, "peer pointer lists must have one entry per rank (<= 8)");
@@ -391,6 +391,7 @@ void p2p_grad_step(int64_t W, int64_t rank, int64_t nblk, std::vector<int64_t> g
     a.owner_blk = owner_blk->data_ptr<uint8_t>(); a.slot_blk = slot_blk->data_ptr<int>();
     a.replicate_blk = replicate_blk->data_ptr<uint8_t>();
   }
+  if (anchors.has_value()) { a.anchors = fptr(*anchors); a.n_anchor = (int)anchors->numel(); a.anchor_rank0 = anchor_rank0 ? 1 : 0; }
   int rc = loom_p2p_grad_step(&a, cur_stream());
   TORCH_CHECK(rc == 0, "loom_p2p_grad_step failed: ", rc);
 }
@@ -399,7 +400,8 @@ void p2p_grad_step_atom(int64_t W, int64_t rank, int64_t nblk, std::vector<int64
                         std::vector<int64_t> shadow, std::vector<int64_t> sync, torch::Tensor m, torch::Tensor v,
                         torch::Tensor lr_mult, torch::Tensor wd, torch::Tensor hyper, torch::Tensor stats, torch::Tensor sumsq,
                         double max_norm, torch::Tensor status, torch::Tensor cnt_blk, torch::Tensor gprev, torch::Tensor pnode,
-                        torch::Tensor trust, torch::Tensor atom_out) {
+                        torch::Tensor trust, torch::Tensor atom_out, c10::optional<torch::Tensor> anchors,
+                        bool anchor_rank0) {
   const c10::cuda::CUDAGuard guard(m.device());
   TORCH_CHECK((int64_t)grads.size() == W && (int64_t)params.size() == W && (int64_t)shadow.size() == W &&
               (int64_t)sync.size() == W && W <= 8, "peer pointer lists must have one entry per rank (<= 8)");
@@ -411,6 +413,7 @@ void p2p_grad_step_atom(int64_t W, int64_t rank, int64_t nblk, std::vector<int64
   }
   a.m = fptr(m); a.v = fptr(v); a.lr_mult = fptr(lr_mult); a.wd_blk = fptr(wd); a.hyper = fptr(hyper);
   a.stats = fptr(stats); a.sumsq_local = fptr(sumsq); a.max_norm = (float)max_norm; a.status = status.data_ptr<int>();
+  if (anchors.has_value()) { a.anchors = fptr(*anchors); a.n_anchor = (int)anchors->numel(); a.anchor_rank0 = anchor_rank0 ? 1 : 0; }
   int rc = loom_p2p_grad_step_atom(&a, fptr(cnt_blk), fptr(gprev), fptr(pnode), fptr(trust), fptr(atom_out), cur_stream());
   TORCH_CHECK(rc == 0, "loom_p2p_grad_step_atom failed: ", rc);
 }

@@ -43,6 +43,10 @@ struct P2P {
   const uint8_t* owner_blk;
   const int* slot_blk;
   const uint8_t* replicate_blk;
+  // per-layer running radii of the phase input (one float per layer), made identical on every rank by the same
+  // exchange that carries the shard norms: mean over ranks, or rank 0's values
+  float* anchors;
+  int n_anchor, anchor_rank0;
 };
 
 __device__ __forceinline__ bool owns(const P2P& c, long long b) {
@@ -55,6 +59,27 @@ __device__ __forceinline__ int* w_sumsq(int* s, int W, int src) { return s + W +
 __device__ __forceinline__ int* w_normflag(int* s, int W, int src) { return s + 2 * W + src; }
 __device__ __forceinline__ int* w_done(int* s, int W, int src) { return s + 3 * W + src; }
 __device__ __forceinline__ int* w_local(int* s, int W, int i) { return s + 4 * W + i; }   // 0: gate1, 1: gate2, 2: counter, 3: epoch
+constexpr int ANCHOR_BASE = 64, ANCHOR_MAX = 64;   // words [64 + src * 64, ...): rank src's radii, written by src
+__device__ __forceinline__ float* w_anchor(int* s, int src) { return reinterpret_cast<float*>(s + ANCHOR_BASE + src * ANCHOR_MAX); }
+
+// thread 0, before the norm flag is released: this rank's radii go into its slot on every peer
+__device__ void anchors_push(const P2P& c) {
+  for (int p = 0; p < c.W; ++p) {
+    volatile float* dst = w_anchor(c.sync[p], c.rank);
+    for (int i = 0; i < c.n_anchor; ++i) dst[i] = c.anchors[i];
+  }
+}
+// thread 0, after every peer's norm flag has arrived: all slots of the local sync buffer are complete
+__device__ void anchors_pull(const P2P& c) {
+  int* my = c.sync[c.rank];
+  const float inv = 1.f / c.W;
+  for (int i = 0; i < c.n_anchor; ++i) {
+    float v = 0.f;
+    if (c.anchor_rank0) v = *reinterpret_cast<volatile float*>(w_anchor(my, 0) + i);
+    else { for (int p = 0; p < c.W; ++p) v += *reinterpret_cast<volatile float*>(w_anchor(my, p) + i); v *= inv; }
+    c.anchors[i] = v;
+  }
+}
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   int v;
@@ -142,6 +167,7 @@ __global__ void __launch_bounds__(256) update_allgather_kernel(P2P c, float* __r
     // rank's contribution NaN: every rank then sees a non-finite norm and skips the update together
     const float mine = (*reinterpret_cast<volatile int*>(status) != 0) ? __int_as_float(0x7fc00000) : *sumsq_local;
     for (int p = 0; p < c.W; ++p) *reinterpret_cast<volatile float*>(w_sumsq(c.sync[p], c.W, c.rank)) = mine;
+    if (c.n_anchor > 0) anchors_push(c);
     __threadfence_system();
     for (int p = 0; p < c.W; ++p) st_release_sys(w_normflag(c.sync[p], c.W, c.rank), epoch);
     bool ok = true;
@@ -150,6 +176,7 @@ __global__ void __launch_bounds__(256) update_allgather_kernel(P2P c, float* __r
       ok = wait_flag(w_normflag(my, c.W, p), epoch, status, 403);
       tot += *reinterpret_cast<volatile float*>(w_sumsq(my, c.W, p));
     }
+    if (ok && c.n_anchor > 0) anchors_pull(c);
     const float norm = sqrtf(tot);
     const bool fin = isfinite(norm) && ok;
     stats[0] = norm;
@@ -221,6 +248,7 @@ __global__ void norm_exchange_kernel(P2P c, float* __restrict__ sumsq_local, flo
   const int epoch = *w_local(my, c.W, 3) + 1;
   const float mine = (*reinterpret_cast<volatile int*>(status) != 0) ? __int_as_float(0x7fc00000) : *sumsq_local;
   for (int p = 0; p < c.W; ++p) *reinterpret_cast<volatile float*>(w_sumsq(c.sync[p], c.W, c.rank)) = mine;
+  if (c.n_anchor > 0) anchors_push(c);
   __threadfence_system();
   for (int p = 0; p < c.W; ++p) st_release_sys(w_normflag(c.sync[p], c.W, c.rank), epoch);
   bool ok = true;
@@ -229,6 +257,7 @@ __global__ void norm_exchange_kernel(P2P c, float* __restrict__ sumsq_local, flo
     ok = wait_flag(w_normflag(my, c.W, p), epoch, status, 406);
     tot += *reinterpret_cast<volatile float*>(w_sumsq(my, c.W, p));
   }
+  if (ok && c.n_anchor > 0) anchors_pull(c);
   const float norm = sqrtf(tot);
   const bool fin = isfinite(norm) && ok;
   stats[0] = norm;
@@ -291,6 +320,7 @@ static void fill_p2p(const LoomP2P* a, P2P& c) {
   }
   c.mc_grads = a->mc_grads; c.W = a->W; c.rank = a->rank; c.nblk = a->nblk;
   c.owner_blk = nullptr; c.slot_blk = nullptr; c.replicate_blk = nullptr;
+  c.anchors = a->anchors; c.n_anchor = a->anchors ? a->n_anchor : 0; c.anchor_rank0 = a->anchor_rank0;
   const long long per = (a->nblk + a->W - 1) / a->W;
   c.blk_lo = per * a->rank < a->nblk ? per * a->rank : a->nblk;
   c.blk_hi = per * (a->rank + 1) < a->nblk ? per * (a->rank + 1) : a->nblk;
@@ -302,6 +332,7 @@ static void fill_p2p(const LoomP2P* a, P2P& c) {
 extern "C" int loom_p2p_grad_step_atom(const LoomP2P* a, const float* cnt_blk, float* gprev, float* pnode, float* trust,
                                        float* atom_out, cudaStream_t stream) {
   if (a->W < 1 || a->W > MAXW) return -1;
+  if (a->anchors && (a->n_anchor < 0 || a->n_anchor > ANCHOR_MAX)) return -2;
   P2P c;
   fill_p2p(a, c);
   static int sms = 0;
@@ -324,6 +355,7 @@ extern "C" int loom_p2p_grad_step_atom(const LoomP2P* a, const float* cnt_blk, f
 
 extern "C" int loom_p2p_grad_step(const LoomP2P* a, cudaStream_t stream) {
   if (a->W < 1 || a->W > MAXW) return -1;
+  if (a->anchors && (a->n_anchor < 0 || a->n_anchor > ANCHOR_MAX)) return -2;
   P2P c;
   for (int p = 0; p < a->W; ++p) {
     c.grads[p] = a->grads[p]; c.params[p] = a->params[p];
@@ -331,6 +363,7 @@ extern "C" int loom_p2p_grad_step(const LoomP2P* a, cudaStream_t stream) {
   }
   c.mc_grads = a->mc_grads; c.W = a->W; c.rank = a->rank; c.nblk = a->nblk;
   c.owner_blk = a->owner_blk; c.slot_blk = a->slot_blk; c.replicate_blk = a->replicate_blk;
+  c.anchors = a->anchors; c.n_anchor = a->anchors ? a->n_anchor : 0; c.anchor_rank0 = a->anchor_rank0;
   const long long per = (a->nblk + a->W - 1) / a->W;
   c.blk_lo = per * a->rank < a->nblk ? per * a->rank : a->nblk;
   c.blk_hi = per * (a->rank + 1) < a->nblk ? per * (a->rank + 1) : a->nblk;

@@ -17,6 +17,7 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include "loom_c_api.h"
 
 namespace {
@@ -33,6 +34,8 @@ __device__ __forceinline__ float tanh_fast(float x) {
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// pull a line into L1 ahead of its use; needs no destination register, so it costs the register-bound backward nothing
+__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
 __device__ __forceinline__ float phase_s0(float beta) { return sinf(HALF_PI * beta * rsqrtf(1.f + beta * beta)); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
@@ -321,8 +324,8 @@ __device__ __forceinline__ void core_backward_elem(const CoreScalars& S, float x
 
 constexpr int TILE_ROWS = 32;
 
-template <int AXIS>
-__global__ void __launch_bounds__(256, 2) ffn_core_bwd_a_kernel(
+template <int AXIS, int OCC>
+__global__ void __launch_bounds__(256, OCC) ffn_core_bwd_a_kernel(
     CoreScalars S_in, const __nv_bfloat16* __restrict__ x_real, const __nv_bfloat16* __restrict__ p_in,
     const float* __restrict__ b_real, const __nv_bfloat16* __restrict__ gate_lin,
     const __nv_bfloat16* __restrict__ beta_lin, const float* __restrict__ b_imag, const float* __restrict__ w_trace,
@@ -331,7 +334,8 @@ __global__ void __launch_bounds__(256, 2) ffn_core_bwd_a_kernel(
     const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ d_c, const __nv_bfloat16* __restrict__ d_pout,
     __nv_bfloat16* __restrict__ dx_real, __nv_bfloat16* __restrict__ dp_in, __nv_bfloat16* __restrict__ dgate_lin,
     float* __restrict__ gz, __nv_bfloat16* __restrict__ dc_prev, float* __restrict__ dseed, float* __restrict__ dtrace_in,
-    float* __restrict__ g_b_real, float* __restrict__ g_w_trace, float* __restrict__ g_scalars /* [0]=alpha, [1..9]=w9 */) {
+    float* __restrict__ g_b_real, float* __restrict__ g_w_trace, float* __restrict__ g_scalars /* [0]=alpha, [1..9]=w9 */,
+    int prefetch) {
   CoreScalars S = S_in;
   S.alpha_gate = S.alpha_ptr ? *S.alpha_ptr : 0.f;
   const int H = S.H;
@@ -355,6 +359,22 @@ __global__ void __launch_bounds__(256, 2) ffn_core_bwd_a_kernel(
       if (m >= S.M) break;
       const int b = m / S.Tc, t = m % S.Tc;
       const long long e = (long long)m * H + h;
+      if (prefetch && m + 4 < S.M && j + 1 < TILE_ROWS / 4) {
+        // the row this thread takes next: with 16 resident warps per SM the ~24 loads of an iteration are otherwise
+        // exposed, one memory latency after another
+        const long long en = e + 4ll * H;
+        prefetch_l1(x_real + en); prefetch_l1(beta_lin + en); prefetch_l1(d_o + en);
+        if (p_in) prefetch_l1(p_in + en);
+        if (gate_lin) prefetch_l1(gate_lin + en);
+        if (has_w) prefetch_l1(d_pout + en);
+        if (AXIS >= 0) {
+#pragma unroll
+          for (int k = 0; k < 9; ++k) {
+            if (c_prev) prefetch_l1(c_prev + k * plane + en);
+            if (d_c) prefetch_l1(d_c + k * plane + en);
+          }
+        }
+      }
       const float2 x = ld2(x_real + e);
       float2 pin = make_float2(0.f, 0.f), gl = make_float2(0.f, 0.f), dpo = make_float2(0.f, 0.f);
       if (p_in) pin = ld2(p_in + e);
@@ -532,13 +552,21 @@ extern "C" int loom_ffn_core_bwd(const LoomFfnCore* a, cudaStream_t stream) {
   if (a->H % 2) return -1;
   CoreScalars S = make_scalars(a);
   dim3 grid((S.H / 2 + 63) / 64, (S.M + TILE_ROWS - 1) / TILE_ROWS);
+  // blocks per SM pass A is compiled for: 2 (128 registers) or 3 (80 registers, more spills, 24 resident warps);
+  // LOOM_CORE_BWD_OCC selects
+  static int pf = -1;               // LOOM_CORE_PREFETCH=0 turns the next-row L1 prefetch of pass A off
+  if (pf < 0) { const char* e = getenv("LOOM_CORE_PREFETCH"); pf = (e != nullptr && e[0] == '0') ? 0 : 1; }
+  static int occ = 0;
+  if (occ == 0) { const char* e = getenv("LOOM_CORE_BWD_OCC"); occ = (e != nullptr && e[0] == '3') ? 3 : 2; }
 #define LOOM_BWD(AX)                                                                                              \
-  ffn_core_bwd_a_kernel<AX><<<grid, 256, 0, stream>>>(                                                            \
+  if (occ == 3) LOOM_BWD_OCC(AX, 3); else LOOM_BWD_OCC(AX, 2)
+#define LOOM_BWD_OCC(AX, OC)                                                                                      \
+  ffn_core_bwd_a_kernel<AX, OC><<<grid, 256, 0, stream>>>(                                                            \
       S, (const __nv_bfloat16*)a->x_real, (const __nv_bfloat16*)a->p_in, a->b_real, (const __nv_bfloat16*)a->gate_lin, \
       (const __nv_bfloat16*)a->beta_lin, a->b_imag, a->w_trace, a->trace_in, a->reset, (const __nv_bfloat16*)a->c_prev, \
       a->seed, a->seed_valid, a->gate_w, (const __nv_bfloat16*)a->d_o, (const __nv_bfloat16*)a->d_c,                  \
       (const __nv_bfloat16*)a->d_pout, (__nv_bfloat16*)a->dx_real, (__nv_bfloat16*)a->dp_in, (__nv_bfloat16*)a->dgate_lin, \
-      a->gz, (__nv_bfloat16*)a->dc_prev, a->dseed, a->dtrace_in, a->g_b_real, a->g_w_trace, a->g_scalars)
+      a->gz, (__nv_bfloat16*)a->dc_prev, a->dseed, a->dtrace_in, a->g_b_real, a->g_w_trace, a->g_scalars, pf)
   switch (S.axis) {
     case 0: LOOM_BWD(0); break;
     case 1: LOOM_BWD(1); break;
@@ -546,6 +574,7 @@ extern "C" int loom_ffn_core_bwd(const LoomFfnCore* a, cudaStream_t stream) {
     default: LOOM_BWD(-1); break;
   }
 #undef LOOM_BWD
+#undef LOOM_BWD_OCC
   ffn_core_bwd_b_kernel<<<grid, 256, 0, stream>>>(S, a->gz, (const __nv_bfloat16*)a->beta_lin, a->b_imag, a->w_trace,
                                                   a->reset, a->dtrace_out, (__nv_bfloat16*)a->dbeta, a->g_b_imag);
   return (int)cudaGetLastError();

@@ -192,6 +192,9 @@ typedef struct {
   // optional sharded-parameter mode (all three null: contiguous block ranges, full-size moments, every block
   // stored to every peer): owner rank per block, compact index of the block in the owner's m / v, replicate flag
   const uint8_t* owner_blk; const int* slot_blk; const uint8_t* replicate_blk;
+  // optional: n_anchor (<= 64) per-layer phase radii kept identical on all ranks by the same exchange (mean over
+  // ranks, or rank 0's values with anchor_rank0); needs sync buffers of at least 64 + 64 * W words
+  float* anchors; int n_anchor; int anchor_rank0;
 } LoomP2P;
 int loom_p2p_grad_step(const LoomP2P* a, cudaStream_t stream);
 // Same exchange with ATOM as the update rule (contiguous shards; see comm.cu)

@@ -475,12 +475,13 @@ extern "C" int loom_slot_pool_bwd(const float* keys, const float* w9, const floa
 #define LOOM_NCH(N, CALL)                                  \
   do {                                                     \
     const int nch_ = ((N) + 255) / 256;                    \
-    if (nch_ == 1) { CALL(1); } else if (nch_ == 2) { CALL(2); } else if (nch_ == 3) { CALL(3); } else { CALL(4); } \
+    if (nch_ == 1) { CALL(1); } else if (nch_ == 2) { CALL(2); } else if (nch_ == 3) { CALL(3); }                   \
+    else if (nch_ == 4) { CALL(4); } else if (nch_ <= 6) { CALL(6); } else { CALL(8); }                             \
   } while (0)
 
 extern "C" int loom_cross_attn_fwd(const void* q, const void* k, const void* v, const uint8_t* allowed, void* out, float* prob,
                                    int B, int T, int Kn, int N, float scale, cudaStream_t st) {
-  if (N % 8 || N > 1024 || Kn < 1 || Kn > 1024) return -1;
+  if (N % 8 || N > 2048 || Kn < 1 || Kn > 1024) return -1;
   const unsigned grid = (unsigned)(((long long)B * T + 7) / 8);
   const size_t shm = (size_t)8 * Kn * sizeof(float);
 #define CA_F(K) cross_attn_fwd_kernel<K><<<grid, 256, shm, st>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, allowed, (bf16*)out, prob, B, T, Kn, N, scale)
@@ -491,7 +492,7 @@ extern "C" int loom_cross_attn_fwd(const void* q, const void* k, const void* v, 
 
 extern "C" int loom_cross_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const float* prob, float* ds,
                                    void* dq, void* dk, void* dv, int B, int T, int Kn, int N, float scale, cudaStream_t st) {
-  if (N % 8 || N > 1024 || Kn < 1 || Kn > 1024) return -1;
+  if (N % 8 || N > 2048 || Kn < 1 || Kn > 1024) return -1;
   const unsigned grid = (unsigned)(((long long)B * T + 7) / 8);
   const size_t shm = (size_t)8 * Kn * sizeof(float);
 #define CA_B(K) cross_attn_bwd_rows_kernel<K><<<grid, 256, shm, st>>>((const bf16*)dout, (const bf16*)k, (const bf16*)v, prob, ds, (bf16*)dq, B, T, Kn, N, scale)
@@ -523,7 +524,7 @@ extern "C" int loom_fixed_rms(int bwd, const void* dy, const void* x, void* out,
 }
 
 extern "C" int loom_rms_norm_fwd(const void* x, const float* w, void* y, int M, int N, float eps, cudaStream_t st) {
-  if (N % 8 || N > 1024) return -1;
+  if (N % 8 || N > 2048) return -1;
   const unsigned grid = (M + 7) / 8;
 #define RN_F(K) rms_norm_fwd_kernel<K><<<grid, 256, 0, st>>>((const bf16*)x, w, (bf16*)y, M, N, eps)
   LOOM_NCH(N, RN_F);
@@ -533,7 +534,7 @@ extern "C" int loom_rms_norm_fwd(const void* x, const float* w, void* y, int M, 
 
 extern "C" int loom_rms_norm_bwd(const void* dy, const void* x, const float* w, void* dx, float* gw_part, int nblocks, int M,
                                  int N, float eps, cudaStream_t st) {
-  if (N % 8 || N > 1024) return -1;
+  if (N % 8 || N > 2048) return -1;
   const size_t shm = (size_t)8 * N * sizeof(float);
 #define RN_B(K) rms_norm_bwd_kernel<K><<<nblocks, 256, shm, st>>>((const bf16*)dy, (const bf16*)x, w, (bf16*)dx, gw_part, M, N, eps)
   LOOM_NCH(N, RN_B);

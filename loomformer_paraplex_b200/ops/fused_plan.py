@@ -455,14 +455,16 @@ class FusedPlan:
             dkv = torch.cat((dk.reshape(M, d.n), dv.reshape(M, d.n)), -1)
         return dkv.reshape(M, 2 * d.n).to(self.adt)
 
-    def _project_state_bwd(self, x2d, slot, dstate, hist_k, hist_v, tape_layer, key, into, dkv=None):
-        """Gradient of :meth:`_project_state` w.r.t. its input; accumulates the weight gradient.  ``dkv``: the slot's
-        gradient if it has been formed already (:meth:`_slot_grad` on the second stream)."""
+    def _project_state_bwd(self, x2d, slot, dstate, hist_k, hist_v, tape_layer, key, dkv=None):
+        """Backward of :meth:`_project_state`: accumulates the weight gradient and returns the data-gradient term as a
+        segment ``(dkv, W)`` for :meth:`linear_dgrad_multi` (the caller folds it into one launch with the other
+        products that end in the same tensor).  ``dkv``: the slot's gradient if it has been formed already
+        (:meth:`_slot_grad` on the second stream)."""
         m, K = self.model, self.K
         if dkv is None:
             dkv = self._slot_grad(slot, dstate, hist_k, hist_v, tape_layer, key, x2d.shape[0])
         K.linear_wgrad(dkv, x2d, self.g(m.depth_attn.kv_weight))
-        return K.linear_dgrad(dkv, self.w(m.depth_attn.kv_weight), out=into, accumulate=True)   # into += dkv @ W
+        return (dkv, self.w(m.depth_attn.kv_weight))
 
     def _depth_query(self, sub):
         da, d = self.model.depth_attn, self.d
@@ -635,6 +637,7 @@ class FusedPlan:
         if overlap:
             side, main = self._side, torch.cuda.current_stream(dev)
         pending = None
+        dh_seg = None                    # (d qkv, W_qkv) of the layer above: its product is the other half of dh
         for bi in range(L - 1, -1, -1):
             blk, t = m.blocks[bi], tape["layers"][bi]
             ffn = blk.ffn
@@ -643,7 +646,9 @@ class FusedPlan:
             if not last:
                 if pending is not None:
                     main.wait_stream(side)
-                dh = self._project_state_bwd(t["h_out"], sub + 2, dst, hist_k, hist_v, t, "h", dh, dkv=pending)
+                # d h_out = d qkv @ W_qkv (layer above) + d[K|V] @ W_kv (this state's history slot): one launch
+                dh = K.linear_dgrad_multi([dh_seg, self._project_state_bwd(t["h_out"], sub + 2, dst, hist_k, hist_v, t, "h",
+                                                                            dkv=pending)])
                 pending = None
             # --- LN2 and the two addends
             ds2, df = K.add_ln_bwd(dh, t["x2"], t["mean2"], t["rstd2"], blk.ln_ffn.weight.data,
@@ -668,20 +673,24 @@ class FusedPlan:
                 core["g_b_imag"].add_(gr["d_b_imag"])
                 core["g_w_trace"].add_(gr["d_w_trace"])
             u = t["u"]
+            # d u collects four products (real up-projection, gate projection, the shared sector of the imaginary
+            # projection, this state's history slot); they leave as one launch once the last of them is known
             K.linear_wgrad(dx_real, u, self.g(ffn.w1_real.weight))
-            du = K.linear_dgrad(dx_real, self.w(ffn.w1_real.weight))
+            du_segs = [(dx_real, self.w(ffn.w1_real.weight))]
             if ffn.gate_proj is not None:
                 dgl = gr["d_gate_lin"].to(self.adt)
                 K.linear_wgrad(dgl, u, self.g(ffn.gate_proj.weight))
                 K.colsum_add(dgl, self.g(ffn.gate_proj.bias))
-                du = K.linear_dgrad(dgl, self.w(ffn.gate_proj.weight), out=du, accumulate=True)
-            dqkc, du, dm2_i = K.imag_bwd(d, dbeta, t["qkc"], u, t["m2"], self.w(ffn.w1_imag), self.g(ffn.w1_imag),
-                                         du_acc=du)
+                du_segs.append((dgl, self.w(ffn.gate_proj.weight)))
+            dqkc, _, dm2_i, u_seg = K.imag_bwd(d, dbeta, t["qkc"], u, t["m2"], self.w(ffn.w1_imag), self.g(ffn.w1_imag),
+                                               defer_u=True)
+            du_segs.append(u_seg)
             # --- depth read 2bi+1 (its output feeds the readout GEMM and the imaginary projection)
             K.linear_wgrad(ds2, t["m2"].reshape(M, N), self._readout_g(sub + 1))
             K.dread_stage(d, K.linear_dgrad(ds2, self._readout_w(sub + 1)).view(M, d.qh, d.hd), dm2_i, t["m2"], t["lse2"],
                           dst, sub + 1)
-            du = self._project_state_bwd(u, sub + 1, dst, hist_k, hist_v, t, "u", du)
+            du_segs.append(self._project_state_bwd(u, sub + 1, dst, hist_k, hist_v, t, "u"))
+            du = K.linear_dgrad_multi(du_segs)
             # --- LN1
             ds1, da = K.add_ln_bwd(du, t["x1"], t["mean1"], t["rstd1"], blk.ln_attn.weight.data,
                                    self.g(blk.ln_attn.weight), self.g(blk.ln_attn.bias), cap, t.get("s1"), t.get("a"))
@@ -701,10 +710,11 @@ class FusedPlan:
             dqkv = K.rope_bwd(d, dq_attn.reshape(B, Tc, d.qh, d.hd), dqkc, dkc[bi], dvc[bi], s, e, tape["cos"],
                               tape["sin"], self.adt).view(M, -1)
             K.linear_wgrad(dqkv, t["h_in"], self.g(blk.attn.qkv_weight))
-            dh = K.linear_dgrad(dqkv, self.w(blk.attn.qkv_weight))
+            dh_seg = (dqkv, self.w(blk.attn.qkv_weight))
         if pending is not None:
             main.wait_stream(side)
-        dh = self._project_state_bwd(tape["h_emb"], 0, dst, hist_k, hist_v, tape["emb_l"], "emb", dh, dkv=pending)
+        dh = K.linear_dgrad_multi([dh_seg, self._project_state_bwd(tape["h_emb"], 0, dst, hist_k, hist_v, tape["emb_l"],
+                                                                    "emb", dkv=pending)])
         return dh, dtraces_in, dseed
 
     # ------------------------------------------------------------------ readout

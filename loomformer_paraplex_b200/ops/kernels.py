@@ -259,6 +259,25 @@ class CudaKernels(TorchKernels):
         gemm([dy], [N], w, c, M=M, N=Kd, b_mn=True, accumulate=bool(accumulate and out is not None))
         return c
 
+    def linear_dgrad_multi(self, segs):
+        """``sum_i dy_i @ w_i`` as ONE launch: the reduction runs over the concatenation of the segments, each with its
+        own weight operand, so gradient branches that end in the same tensor need neither separate launches nor
+        read-modify-write accumulation.  Segments ``(None, value)`` are added afterwards."""
+        prod = [(dy, w) for dy, w in segs if dy is not None]
+        vals = [w for dy, w in segs if dy is None]
+        if not prod or len(prod) > 16 or not all(_tma_ok(dy) and _tma_ok(w) for dy, w in prod):
+            self.fallbacks["linear_dgrad_multi"] += 1
+            return super().linear_dgrad_multi(segs)
+        M, N = prod[0][0].shape[0], prod[0][1].shape[1]
+        c = torch.empty(M, N, dtype=torch.bfloat16, device=prod[0][0].device)
+        if len(prod) == 1:
+            gemm([prod[0][0]], [prod[0][0].shape[1]], prod[0][1], c, M=M, N=N, b_mn=True)
+        else:
+            gemm([dy for dy, _ in prod], [dy.shape[1] for dy, _ in prod], [w for _, w in prod], c, M=M, N=N, b_mn=True)
+        for v in vals:
+            c += v.to(c.dtype)
+        return c
+
     def linear_wgrad(self, dy, x, gw):
         dy2, x2 = dy.reshape(-1, dy.shape[-1]), x.reshape(-1, x.shape[-1])
         if not (_tma_ok(dy2) and _tma_ok(x2) and gw.dtype == torch.float32 and gw.stride(-1) == 1 and gw.dim() == 2):
@@ -288,15 +307,17 @@ class CudaKernels(TorchKernels):
         gemm(segs, lens, w3, c3, M=M, N=d.hpq, heads=d.qh, b_k0=offs)
         return beta
 
-    def imag_bwd(self, d, dbeta, qkc, u, m2, w_imag, gw_imag, du_acc=None):
+    def imag_bwd(self, d, dbeta, qkc, u, m2, w_imag, gw_imag, du_acc=None, defer_u=False):
         """``du_acc``: an existing bf16 ``[M, N]`` gradient of ``u`` to add this projection's share into (returned as
-        ``du``) instead of allocating a new one."""
+        ``du``) instead of allocating a new one.  ``defer_u``: leave the data gradient of the shared ``u`` sector to
+        the caller: ``du`` is ``None`` and a fourth element ``(dbeta, weight slice)`` is returned, a segment for
+        :meth:`linear_dgrad_multi`."""
         M = u.shape[0]
         ok = (_tma_ok(qkc) and _tma_ok(u) and _tma_ok(m2) and _tma_ok(w_imag) and _tma_ok(dbeta)
               and d.hd % 8 == 0 and d.hpq % 8 == 0 and gw_imag.dtype == torch.float32)
         if not ok:
             self.fallbacks["imag_bwd"] += 1
-            return super().imag_bwd(d, dbeta, qkc, u, m2, w_imag, gw_imag, du_acc)
+            return super().imag_bwd(d, dbeta, qkc, u, m2, w_imag, gw_imag, du_acc, defer_u)
         hd, n, H = d.hd, d.n, d.hidden
         dev = u.device
         w3 = w_imag.view(d.qh, d.hpq, d.imag_in).transpose(0, 1)             # [HPQ, QH, IMAG_IN]
@@ -304,7 +325,8 @@ class CudaKernels(TorchKernels):
         db3 = dbeta.view(M, d.qh, d.hpq)
         dqkc = torch.empty_like(qkc)
         acc_u = du_acc is not None and du_acc.dtype == torch.bfloat16 and du_acc.stride(-1) == 1
-        du = du_acc if acc_u else torch.empty(M, n, dtype=torch.bfloat16, device=dev)
+        du = None if defer_u else (du_acc if acc_u else torch.empty(M, n, dtype=torch.bfloat16, device=dev))
+        u_seg = None
         dm2 = torch.empty(M, d.qh, hd, dtype=torch.bfloat16, device=dev)
         m2v = m2.view(M, d.qh, hd)
 
@@ -314,7 +336,8 @@ class CudaKernels(TorchKernels):
             self._wgrad(db3, a_src, g3[:, :, col0:col0 + hd], d.hpq, hd, d.qh)
 
         def shared(col0, a_src2d, c_dst2d, accumulate=False):
-            gemm([dbeta], [H], w_imag[:, col0:col0 + n], c_dst2d, M=M, N=n, b_mn=True, accumulate=accumulate)
+            if c_dst2d is not None:
+                gemm([dbeta], [H], w_imag[:, col0:col0 + n], c_dst2d, M=M, N=n, b_mn=True, accumulate=accumulate)
             self._wgrad(dbeta, a_src2d, gw_imag[:, col0:col0 + n], H, n)
 
         if d.open_sectors:
@@ -322,13 +345,17 @@ class CudaKernels(TorchKernels):
             shared(hd, qkc[:, 1].reshape(M, n), dqkc[:, 1].reshape(M, n))
             shared(hd + n, qkc[:, 2].reshape(M, n), dqkc[:, 2].reshape(M, n))
             shared(hd + 2 * n, u, du, acc_u)
+            u_seg = (dbeta, w_imag[:, hd + 2 * n:hd + 3 * n])
             shared(hd + 3 * n, m2v.reshape(M, n), dm2.view(M, n))
         else:
             per_head(0, qkc[:, 0], dqkc[:, 0])
             per_head(hd, qkc[:, 1], dqkc[:, 1])
             per_head(2 * hd, qkc[:, 2], dqkc[:, 2])
             shared(3 * hd, u, du, acc_u)
+            u_seg = (dbeta, w_imag[:, 3 * hd:3 * hd + n])
             per_head(3 * hd + n, m2v, dm2)
+        if defer_u:
+            return dqkc, None, dm2, u_seg
         if du_acc is not None and not acc_u:
             du = du_acc + du
         return dqkc, du, dm2
@@ -615,7 +642,7 @@ class _ElementwiseMixin:
     def cross_attn_fwd(self, q, k, v, allowed, scale):
         B, T, N = q.shape
         Kn = k.shape[1]
-        if not (q.dtype == torch.bfloat16 and N % 8 == 0 and N <= 1024 and 1 <= Kn <= 1024):
+        if not (q.dtype == torch.bfloat16 and N % 8 == 0 and N <= 2048 and 1 <= Kn <= 1024):
             self.fallbacks["cross_attn_fwd"] += 1
             return super().cross_attn_fwd(q, k, v, allowed, scale)
         out = torch.empty_like(q)
@@ -675,7 +702,7 @@ class _ElementwiseMixin:
 
     def rms_norm_fwd(self, x, w, eps=1e-6):
         N = x.shape[-1]
-        if not (x.dtype == torch.bfloat16 and x.is_contiguous() and N % 8 == 0 and N <= 1024):
+        if not (x.dtype == torch.bfloat16 and x.is_contiguous() and N % 8 == 0 and N <= 2048):
             self.fallbacks["rms_norm_fwd"] += 1
             return super().rms_norm_fwd(x, w, eps)
         y = torch.empty_like(x)
@@ -685,7 +712,7 @@ class _ElementwiseMixin:
 
     def rms_norm_bwd(self, dy, x, w, gw, eps=1e-6):
         N = x.shape[-1]
-        if not (x.dtype == torch.bfloat16 and x.is_contiguous() and N % 8 == 0 and N <= 1024):
+        if not (x.dtype == torch.bfloat16 and x.is_contiguous() and N % 8 == 0 and N <= 2048):
             self.fallbacks["rms_norm_bwd"] += 1
             return super().rms_norm_bwd(dy, x, w, gw, eps)
         M = x.numel() // N

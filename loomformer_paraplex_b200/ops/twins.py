@@ -51,6 +51,15 @@ class TorchKernels:
             out.copy_(r)
         return out
 
+    def linear_dgrad_multi(self, segs):
+        """``sum_i dy_i @ w_i`` over segments ``(dy_i [M, K_i], w_i [K_i, N])``; a segment ``(None, value)`` contributes
+        an already formed ``[M, N]`` term.  The native kernel set runs all products as one launch."""
+        acc = None
+        for dy, w in segs:
+            r = w if dy is None else dy @ w.to(dy.dtype)
+            acc = r if acc is None else acc + r.to(acc.dtype)
+        return acc
+
     def linear_wgrad(self, dy, x, gw):
         gw.add_((dy.reshape(-1, dy.shape[-1]).float().t() @ x.reshape(-1, x.shape[-1]).float()).view_as(gw))
 
@@ -73,10 +82,14 @@ class TorchKernels:
         w = w_imag.view(d.qh, d.hpq, d.imag_in).to(a.dtype)
         return torch.einsum("mgk,ghk->mgh", a, w).reshape(u.shape[0], d.hidden)
 
-    def imag_bwd(self, d, dbeta, qkc, u, m2, w_imag, gw_imag, du_acc=None):
+    def imag_bwd(self, d, dbeta, qkc, u, m2, w_imag, gw_imag, du_acc=None, defer_u=False):
         """Returns (dqkc, du, dm2) and accumulates the weight gradient into ``gw_imag`` (fp32); ``du`` includes
-        ``du_acc`` when that is given."""
+        ``du_acc`` when that is given.  ``defer_u``: do not form the gradient of ``u`` here; return it as a fourth
+        element, a segment for :meth:`linear_dgrad_multi`, so the caller can fold it into one launch with the other
+        products that end in the same tensor."""
         dqkc, du, dm2 = self._imag_bwd(d, dbeta, qkc, u, m2, w_imag, gw_imag)
+        if defer_u:
+            return dqkc, None, dm2, (None, du)
         return dqkc, (du if du_acc is None else du_acc + du.to(du_acc.dtype)), dm2
 
     def _imag_bwd(self, d, dbeta, qkc, u, m2, w_imag, gw_imag):

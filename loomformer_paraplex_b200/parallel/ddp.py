@@ -37,9 +37,19 @@ class GradSync:
             if symm is None or flat.shadow is None:
                 raise RuntimeError(f"grad_sync={self.backend!r} needs symmetric flat buffers on CUDA")
             dev = flat.device
-            self.sync_words = symm.alloc("sync", 64, torch.int32, dev)
+            # words 0..63: flags of the exchange; from word 64 on, 64 words per rank for the phase radii
+            self.sync_words = symm.alloc("sync", 64 + 64 * 8, torch.int32, dev)
             self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
             self.use_multimem = False
+            self.fused_anchors = None
+            blocks = list(getattr(model, "blocks", []))
+            if blocks and len(blocks) <= 64 and all(hasattr(b.ffn, "beta_anchor") for b in blocks):
+                # the per-layer running radii become views of one array, so the fused step can average them across
+                # ranks in the kernel that already exchanges the shard norms (no separate collective per step)
+                arr = torch.stack([b.ffn.beta_anchor.detach().float().reshape(()) for b in blocks]).contiguous()
+                for i, b in enumerate(blocks):
+                    b.ffn.beta_anchor = arr[i]
+                self.fused_anchors = arr
         if self.world > 1:
             self.broadcast_parameters()
         if self.backend == "fsdp":
@@ -76,7 +86,7 @@ class GradSync:
                                             s.peer_ptrs("shadow"), s.peer_ptrs("sync"), opt.m, opt.v, opt.lr_mult_blk,
                                             opt.wd_blk, hyper, opt.stats, self.sumsq, opt.grad_clip,
                                             kernels.status_word(f.device), opt.cnt_blk, opt.gprev_blk, opt.pnode_blk,
-                                            opt.trust_blk, opt.atom_out)
+                                            opt.trust_blk, opt.atom_out, self.fused_anchors, self.anchor_mode == "rank0")
             native.count(5)
             return
         opt.step_count += 1
@@ -87,7 +97,8 @@ class GradSync:
                                    s.peer_ptrs("shadow"), s.peer_ptrs("sync"), mc, opt.m, opt.v, opt.lr_mult_blk,
                                    opt.wd_blk, opt.active_blk, hyper, opt.stats, self.sumsq, opt.grad_clip,
                                    kernels.status_word(f.device), None if sh is None else sh.owner_blk,
-                                   None if sh is None else sh.slot_blk, None if sh is None else sh.replicate_blk)
+                                   None if sh is None else sh.slot_blk, None if sh is None else sh.replicate_blk,
+                                   self.fused_anchors, self.anchor_mode == "rank0")
         native.count(3)
 
     def own_block_range(self):
@@ -137,6 +148,8 @@ class GradSync:
         """
         if self.world <= 1:
             return
+        if self.backend in ("p2p", "fsdp") and self.fused_anchors is not None:
+            return                                   # done inside the fused step's norm exchange
         if self._anchors is None:
             self._anchors = [b.ffn.beta_anchor for b in self.model.blocks]
         packed = torch.stack([a.detach().float() for a in self._anchors])

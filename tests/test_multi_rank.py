@@ -36,12 +36,17 @@ def test_rank0_decisions_reach_every_rank(tmp_path):
     assert r0 == [0, 0, 0, 2, 0, 0, 4, 0, 2]
 
 
+def _need(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+
+
 @pytest.mark.gpu
-def test_fused_p2p_step_matches_nccl_baseline(tmp_path):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    a = _launch("collective", str(tmp_path / "nccl.pt"), "cuda", 2, 29612)
-    b = _launch("p2p", str(tmp_path / "p2p.pt"), "cuda", 2, 29613)
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_p2p_step_matches_nccl_baseline(tmp_path, world):
+    _need(world)
+    a = _launch("collective", str(tmp_path / "nccl.pt"), "cuda", world, 29612)
+    b = _launch("p2p", str(tmp_path / "p2p.pt"), "cuda", world, 29613)
     assert a["same"] and b["same"]
     # Adam's first steps move every weight by ~lr regardless of gradient size, so a few weights whose tiny
     # gradients differ in the last bits between the two reduction orders may differ by O(lr); the bulk must agree.
@@ -60,12 +65,12 @@ def test_gathering_gemm_reads_owner_rows_and_completes_local_copy(tmp_path):
 
 
 @pytest.mark.gpu
-def test_sharded_training_matches_nccl_baseline(tmp_path):
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_training_matches_nccl_baseline(tmp_path, world):
     """Sharded ownership + weights fetched inside the consuming GEMM give the same training run as all-reduce DDP."""
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    a = _launch("collective", str(tmp_path / "nccl.pt"), "cuda", 2, 29615)
-    b = _launch("fsdp", str(tmp_path / "fsdp.pt"), "cuda", 2, 29616)
+    _need(world)
+    a = _launch("collective", str(tmp_path / "nccl.pt"), "cuda", world, 29615)
+    b = _launch("fsdp", str(tmp_path / "fsdp.pt"), "cuda", world, 29616)
     assert a["same"] and b["same"]
     diff = (a["params"] - b["params"]).abs()
     assert float(diff.mean()) < 2e-5, float(diff.mean())
@@ -84,12 +89,12 @@ def test_tensor_parallel_fused_gemms(tmp_path):
 
 
 @pytest.mark.gpu
-def test_fused_step_with_atom_matches_nccl_baseline(tmp_path):
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_step_with_atom_matches_nccl_baseline(tmp_path, world):
     """ATOM applied to the shard inside the fused NVLink exchange equals all-reduce + replicated ATOM."""
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    a = _launch("collective+atom", str(tmp_path / "nccl_atom.pt"), "cuda", 2, 29618)
-    b = _launch("p2p+atom", str(tmp_path / "p2p_atom.pt"), "cuda", 2, 29619)
+    _need(world)
+    a = _launch("collective+atom", str(tmp_path / "nccl_atom.pt"), "cuda", world, 29618)
+    b = _launch("p2p+atom", str(tmp_path / "p2p_atom.pt"), "cuda", world, 29619)
     assert a["same"] and b["same"]
     diff = (a["params"] - b["params"]).abs()
     assert float(diff.mean()) < 5e-5, float(diff.mean())
