@@ -271,7 +271,7 @@ def measure_training(args, cfg, engine, dev, world, rank, workload, steps, warmu
     kernels.check_status(dev)
     fb = dict(getattr(engine.plan.K, "fallbacks", {})) if engine.plan is not None else {}
     return {"ms": ms, "ms_e2e": ms_e2e, "clocks": clocks, "launches": int(launches), "h2d": int(h2d),
-            "fallbacks": fb, "loss": float(loss_host)}
+            "fallbacks": fb, "loss": float(loss_host), "peak_gb": torch.cuda.max_memory_allocated(dev) / 2 ** 30}
 
 
 def measure_decode(cfg_kw, dev, world, batch, prompt_len, new):
@@ -345,6 +345,7 @@ def secondary_ours(args, dev, world, rank, deadline):
 
     for batch in (1, 64):
         guarded(f"decode_b{batch}", lambda: measure_decode(dict(MODEL_KW), dev, world, batch, 512, 256))
+    torch.cuda.reset_peak_memory_stats(dev)
 
     def smol():
         a = copy.copy(args)
@@ -356,7 +357,7 @@ def secondary_ours(args, dev, world, rank, deadline):
         return {"metric": "train tokens/s (cfg/smol360.yaml, 467M parameters, bf16, micro-batch 8 x seq 2048 per GPU)",
                 "value": tokens / (r["ms"] / 1e3), "unit": "tokens/s", "ms_per_step": r["ms"], "steps": 5, "warmup": 3,
                 "e2e_value": tokens / (r["ms_e2e"] / 1e3), "grad_path": path, "gpu_launches": r["launches"],
-                "library_fallback_calls": r["fallbacks"], "final_loss": r["loss"]}
+                "library_fallback_calls": r["fallbacks"], "final_loss": r["loss"], "peak_memory_gib": round(r["peak_gb"], 2)}
     guarded("smol360", smol)
 
     def sft():
@@ -393,7 +394,7 @@ def run_ours(args):
         emit(args, "ours", r["ms"], r["clocks"], world, dict({
             "e2e": {"value": tokens / (r["ms_e2e"] / 1000.0), "unit": "tokens/s", "h2d_bytes_per_step": r["h2d"],
                     "d2h_bytes_per_step": 4, "ms_per_step": r["ms_e2e"]},
-            "gpu_launches": r["launches"], "grad_path": path,
+            "gpu_launches": r["launches"], "grad_path": path, "peak_memory_gib": round(r["peak_gb"], 2),
             "library_fallback_calls": r["fallbacks"], "final_loss": r["loss"]}, **extra))
     pdist.shutdown()
 

@@ -36,6 +36,12 @@ __device__ __forceinline__ float tanh_fast(float x) {
 }
 // pull a line into L1 ahead of its use; needs no destination register, so it costs the register-bound backward nothing
 __device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
+__device__ __forceinline__ void cp_async4(uint32_t* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait1() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+__device__ __forceinline__ float2 ld2s(const uint32_t* p) { return __bfloat1622float2(*reinterpret_cast<const bf2*>(p)); }
 __device__ __forceinline__ float phase_s0(float beta) { return sinf(HALF_PI * beta * rsqrtf(1.f + beta * beta)); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
@@ -130,6 +136,84 @@ __device__ __forceinline__ void core_forward_elem(const CoreScalars& S, float x,
   }
 }
 
+// one (token, neuron pair): loads, both elements' forward, stores; returns the pair's sum of beta^2
+template <int AXIS>
+__device__ __forceinline__ float core_forward_pair(
+    const CoreScalars& S, int m, int h, const __nv_bfloat16* __restrict__ x_real, const __nv_bfloat16* __restrict__ p_in,
+    const float* __restrict__ b_real, const __nv_bfloat16* __restrict__ gate_lin,
+    const __nv_bfloat16* __restrict__ beta_lin, const float* __restrict__ b_imag, const float* __restrict__ w_trace,
+    const float* __restrict__ trace_in, const uint8_t* __restrict__ reset, const __nv_bfloat16* __restrict__ c_prev,
+    const float* __restrict__ seed, const uint8_t* __restrict__ seed_valid, const float* __restrict__ gate_w,
+    __nv_bfloat16* __restrict__ o_out, __nv_bfloat16* __restrict__ c_out, __nv_bfloat16* __restrict__ p_out,
+    float* __restrict__ trace_out) {
+  const int H = S.H;
+  const int b = m / S.Tc, t = m % S.Tc;
+  const long long e = (long long)m * H + h;
+  const float2 x = ld2(x_real + e);
+  float2 pin = make_float2(0.f, 0.f), gl = make_float2(0.f, 0.f);
+  if (p_in) pin = ld2(p_in + e);
+  if (gate_lin) gl = ld2(gate_lin + e);
+  const float2 bl = ld2(beta_lin + e);
+  const float bi0 = b_imag[h], bi1 = b_imag[h + 1];
+  const float beta0 = bl.x + bi0, beta1 = bl.y + bi1;
+  float prev0 = 0.f, prev1 = 0.f;
+  const bool rs = reset && reset[m];
+  if (!rs) {
+    if (t == 0) { if (trace_in) { prev0 = trace_in[(long long)b * H + h]; prev1 = trace_in[(long long)b * H + h + 1]; } }
+    else { const float2 bp = ld2(beta_lin + e - H); prev0 = phase_s0(bp.x + bi0); prev1 = phase_s0(bp.y + bi1); }
+  }
+  float w9[9];
+  const bool has_w = gate_w != nullptr;
+#pragma unroll
+  for (int k = 0; k < 9; ++k) w9[k] = has_w ? gate_w[k] : 0.f;
+  float cp0[9], cp1[9];          // carrier entering the step (previous depth, or the temporal seed at t = 0)
+  bool has_R = false;
+  const long long plane = (long long)S.M * H;
+  if (AXIS >= 0) {
+    if (c_prev) {
+#pragma unroll
+      for (int k = 0; k < 9; ++k) { float2 v = ld2(c_prev + k * plane + e); cp0[k] = v.x; cp1[k] = v.y; }
+      has_R = true;
+    } else if (seed && t == 0 && seed_valid[b]) {
+      const float* sp = seed + ((long long)b * H + h) * 9;
+#pragma unroll
+      for (int k = 0; k < 9; ++k) { cp0[k] = sp[k]; cp1[k] = sp[9 + k]; }
+      has_R = true;
+    }
+  }
+  if (!has_R) {
+#pragma unroll
+    for (int k = 0; k < 9; ++k) { cp0[k] = 0.f; cp1[k] = 0.f; }
+  }
+  FwdElem E0, E1;
+  core_forward_elem<AXIS>(S, x.x, pin.x, p_in != nullptr, b_real[h], gl.x, gate_lin != nullptr, beta0, prev0, w_trace[h],
+                          cp0, has_R, w9, has_w, E0);
+  core_forward_elem<AXIS>(S, x.y, pin.y, p_in != nullptr, b_real[h + 1], gl.y, gate_lin != nullptr, beta1, prev1,
+                          w_trace[h + 1], cp1, has_R, w9, has_w, E1);
+  st2(o_out + e, E0.o, E1.o);
+  if (t == S.Tc - 1) { trace_out[(long long)b * H + h] = E0.s0; trace_out[(long long)b * H + h + 1] = E1.s0; }
+  if (AXIS >= 0) {
+#pragma unroll
+    for (int k = 0; k < 9; ++k) st2(c_out + k * plane + e, E0.C[k], E1.C[k]);
+    if (has_w) st2(p_out + e, E0.p, E1.p);
+  }
+  return beta0 * beta0 + beta1 * beta1;
+}
+
+__device__ __forceinline__ void block_add_256(float v, float* __restrict__ dst) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __shared__ float sh[8];
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int i = 0; i < 8; ++i) tot += sh[i];
+    atomicAdd(dst, tot);
+  }
+}
+
+// one thread per (m, h-pair)
 template <int AXIS>
 __global__ void __launch_bounds__(256) ffn_core_fwd_kernel(
     CoreScalars S_in, const __nv_bfloat16* __restrict__ x_real, const __nv_bfloat16* __restrict__ p_in,
@@ -141,74 +225,53 @@ __global__ void __launch_bounds__(256) ffn_core_fwd_kernel(
     float* __restrict__ trace_out, float* __restrict__ beta_sq_sum) {
   CoreScalars S = S_in;
   S.alpha_gate = S.alpha_ptr ? *S.alpha_ptr : 0.f;
-  const int H = S.H, Hp = H >> 1;
+  const int Hp = S.H >> 1;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   float bsq = 0.f;
-  if (idx < (long long)S.M * Hp) {
-    const int m = (int)(idx / Hp), h = (int)(idx % Hp) * 2;
-    const int b = m / S.Tc, t = m % S.Tc;
-    const long long e = (long long)m * H + h;
-    const float2 x = ld2(x_real + e);
-    float2 pin = make_float2(0.f, 0.f), gl = make_float2(0.f, 0.f);
-    if (p_in) pin = ld2(p_in + e);
-    if (gate_lin) gl = ld2(gate_lin + e);
-    const float2 bl = ld2(beta_lin + e);
-    const float bi0 = b_imag[h], bi1 = b_imag[h + 1];
-    const float beta0 = bl.x + bi0, beta1 = bl.y + bi1;
-    bsq = beta0 * beta0 + beta1 * beta1;
-    float prev0 = 0.f, prev1 = 0.f;
-    const bool rs = reset && reset[m];
-    if (!rs) {
-      if (t == 0) { if (trace_in) { prev0 = trace_in[(long long)b * H + h]; prev1 = trace_in[(long long)b * H + h + 1]; } }
-      else { const float2 bp = ld2(beta_lin + e - H); prev0 = phase_s0(bp.x + bi0); prev1 = phase_s0(bp.y + bi1); }
-    }
-    float w9[9];
-    const bool has_w = gate_w != nullptr;
+  if (idx < (long long)S.M * Hp)
+    bsq = core_forward_pair<AXIS>(S, (int)(idx / Hp), (int)(idx % Hp) * 2, x_real, p_in, b_real, gate_lin, beta_lin, b_imag,
+                                  w_trace, trace_in, reset, c_prev, seed, seed_valid, gate_w, o_out, c_out, p_out, trace_out);
+  block_add_256(bsq, beta_sq_sum);
+}
+
+// Tiled variant: a block owns 64 neuron pairs x FWD_ROWS tokens, every thread walks FWD_ROWS / 4 rows and asks L1 for
+// its next row's lines before working on the current one.
+constexpr int FWD_ROWS = 16;
+template <int AXIS>
+__global__ void __launch_bounds__(256) ffn_core_fwd_tiled_kernel(
+    CoreScalars S_in, const __nv_bfloat16* __restrict__ x_real, const __nv_bfloat16* __restrict__ p_in,
+    const float* __restrict__ b_real, const __nv_bfloat16* __restrict__ gate_lin,
+    const __nv_bfloat16* __restrict__ beta_lin, const float* __restrict__ b_imag, const float* __restrict__ w_trace,
+    const float* __restrict__ trace_in, const uint8_t* __restrict__ reset, const __nv_bfloat16* __restrict__ c_prev,
+    const float* __restrict__ seed, const uint8_t* __restrict__ seed_valid, const float* __restrict__ gate_w,
+    __nv_bfloat16* __restrict__ o_out, __nv_bfloat16* __restrict__ c_out, __nv_bfloat16* __restrict__ p_out,
+    float* __restrict__ trace_out, float* __restrict__ beta_sq_sum) {
+  CoreScalars S = S_in;
+  S.alpha_gate = S.alpha_ptr ? *S.alpha_ptr : 0.f;
+  const int H = S.H;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  const int h = (blockIdx.x * 64 + tx) * 2;
+  const long long plane = (long long)S.M * H;
+  float bsq = 0.f;
+  if (h < H) {
+    for (int j = 0; j < FWD_ROWS / 4; ++j) {
+      const int m = blockIdx.y * FWD_ROWS + ty + 4 * j;
+      if (m >= S.M) break;
+      if (m + 4 < S.M && j + 1 < FWD_ROWS / 4) {
+        const long long en = (long long)(m + 4) * H + h;
+        prefetch_l1(x_real + en); prefetch_l1(beta_lin + en);
+        if (p_in) prefetch_l1(p_in + en);
+        if (gate_lin) prefetch_l1(gate_lin + en);
+        if (AXIS >= 0 && c_prev) {
 #pragma unroll
-    for (int k = 0; k < 9; ++k) w9[k] = has_w ? gate_w[k] : 0.f;
-    float cp0[9], cp1[9];          // carrier entering the step (previous depth, or the temporal seed at t = 0)
-    bool has_R = false;
-    const long long plane = (long long)S.M * H;
-    if (AXIS >= 0) {
-      if (c_prev) {
-#pragma unroll
-        for (int k = 0; k < 9; ++k) { float2 v = ld2(c_prev + k * plane + e); cp0[k] = v.x; cp1[k] = v.y; }
-        has_R = true;
-      } else if (seed && t == 0 && seed_valid[b]) {
-        const float* sp = seed + ((long long)b * H + h) * 9;
-#pragma unroll
-        for (int k = 0; k < 9; ++k) { cp0[k] = sp[k]; cp1[k] = sp[9 + k]; }
-        has_R = true;
+          for (int k = 0; k < 9; ++k) prefetch_l1(c_prev + k * plane + en);
+        }
       }
-    }
-    if (!has_R) {
-#pragma unroll
-      for (int k = 0; k < 9; ++k) { cp0[k] = 0.f; cp1[k] = 0.f; }
-    }
-    FwdElem E0, E1;
-    core_forward_elem<AXIS>(S, x.x, pin.x, p_in != nullptr, b_real[h], gl.x, gate_lin != nullptr, beta0, prev0, w_trace[h],
-                            cp0, has_R, w9, has_w, E0);
-    core_forward_elem<AXIS>(S, x.y, pin.y, p_in != nullptr, b_real[h + 1], gl.y, gate_lin != nullptr, beta1, prev1,
-                            w_trace[h + 1], cp1, has_R, w9, has_w, E1);
-    st2(o_out + e, E0.o, E1.o);
-    if (t == S.Tc - 1) { trace_out[(long long)b * H + h] = E0.s0; trace_out[(long long)b * H + h + 1] = E1.s0; }
-    if (AXIS >= 0) {
-#pragma unroll
-      for (int k = 0; k < 9; ++k) st2(c_out + k * plane + e, E0.C[k], E1.C[k]);
-      if (has_w) st2(p_out + e, E0.p, E1.p);
+      bsq += core_forward_pair<AXIS>(S, m, h, x_real, p_in, b_real, gate_lin, beta_lin, b_imag, w_trace, trace_in, reset,
+                                     c_prev, seed, seed_valid, gate_w, o_out, c_out, p_out, trace_out);
     }
   }
-  // sum of beta^2 for the anchor statistic
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) bsq += __shfl_xor_sync(0xffffffffu, bsq, o);
-  __shared__ float sh[8];
-  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = bsq;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float tot = 0.f;
-    for (int i = 0; i < 8; ++i) tot += sh[i];
-    atomicAdd(beta_sq_sum, tot);
-  }
+  block_add_256(bsq, beta_sq_sum);
 }
 
 
@@ -324,8 +387,8 @@ __device__ __forceinline__ void core_backward_elem(const CoreScalars& S, float x
 
 constexpr int TILE_ROWS = 32;
 
-template <int AXIS, int OCC>
-__global__ void __launch_bounds__(256, OCC) ffn_core_bwd_a_kernel(
+template <int AXIS, int PF>
+__global__ void __launch_bounds__(256, 2) ffn_core_bwd_a_kernel(
     CoreScalars S_in, const __nv_bfloat16* __restrict__ x_real, const __nv_bfloat16* __restrict__ p_in,
     const float* __restrict__ b_real, const __nv_bfloat16* __restrict__ gate_lin,
     const __nv_bfloat16* __restrict__ beta_lin, const float* __restrict__ b_imag, const float* __restrict__ w_trace,
@@ -334,8 +397,8 @@ __global__ void __launch_bounds__(256, OCC) ffn_core_bwd_a_kernel(
     const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ d_c, const __nv_bfloat16* __restrict__ d_pout,
     __nv_bfloat16* __restrict__ dx_real, __nv_bfloat16* __restrict__ dp_in, __nv_bfloat16* __restrict__ dgate_lin,
     float* __restrict__ gz, __nv_bfloat16* __restrict__ dc_prev, float* __restrict__ dseed, float* __restrict__ dtrace_in,
-    float* __restrict__ g_b_real, float* __restrict__ g_w_trace, float* __restrict__ g_scalars /* [0]=alpha, [1..9]=w9 */,
-    int prefetch) {
+    float* __restrict__ g_b_real, float* __restrict__ g_w_trace, float* __restrict__ g_scalars /* [0]=alpha, [1..9]=w9 */) {
+  constexpr int prefetch = PF;
   CoreScalars S = S_in;
   S.alpha_gate = S.alpha_ptr ? *S.alpha_ptr : 0.f;
   const int H = S.H;
@@ -351,17 +414,52 @@ __global__ void __launch_bounds__(256, OCC) ffn_core_bwd_a_kernel(
   float acc_w9[9];
 #pragma unroll
   for (int k = 0; k < 9; ++k) acc_w9[k] = 0.f;
+  // prefetch == 2: every thread copies the (up to 25) bf16 pairs of its NEXT row into its own shared-memory slots with
+  // cp.async while it works on the current row, and reads the current row from the slots filled one iteration
+  // earlier.  The slots are private to the thread, so cp.async.wait_group is the only synchronisation.  With 16
+  // resident warps per SM the loads would otherwise be exposed, and holding a prefetched row in registers is not an
+  // option (the 3x3 chain already spills).  prefetch == 1 asks L1 for the lines instead; 0 loads on demand.
+  extern __shared__ uint32_t stg[];                     // [2 stages][NSLOT][256 threads]
+  constexpr int NSLOT = 25;                             // x, p_in, gate, d_pout, beta, d_o, beta of the row above, 9 + 9 carrier planes
+  constexpr bool staged = prefetch == 2;
+  auto slot = [&](int st, int k) -> uint32_t* { return stg + (st * NSLOT + k) * 256 + threadIdx.x; };
+  auto issue = [&](int mn, int st) {
+    const long long en = (long long)mn * H + h;
+    cp_async4(slot(st, 0), x_real + en);
+    if (p_in) cp_async4(slot(st, 1), p_in + en);
+    if (gate_lin) cp_async4(slot(st, 2), gate_lin + en);
+    if (has_w) cp_async4(slot(st, 3), d_pout + en);
+    cp_async4(slot(st, 4), beta_lin + en);
+    cp_async4(slot(st, 5), d_o + en);
+    if (mn % S.Tc != 0) cp_async4(slot(st, 6), beta_lin + en - H);
+    if (AXIS >= 0) {
+#pragma unroll
+      for (int k = 0; k < 9; ++k) {
+        if (c_prev) cp_async4(slot(st, 7 + k), c_prev + k * plane + en);
+        if (d_c) cp_async4(slot(st, 16 + k), d_c + k * plane + en);
+      }
+    }
+  };
   if (col_ok) {
     const float br0 = b_real[h], br1 = b_real[h + 1], bi0 = b_imag[h], bi1 = b_imag[h + 1];
     const float wt0 = w_trace[h], wt1 = w_trace[h + 1];
+    if (staged) {
+      const int m_first = blockIdx.y * TILE_ROWS + ty;
+      if (m_first < S.M) issue(m_first, 0);
+      cp_async_commit();
+    }
     for (int j = 0; j < TILE_ROWS / 4; ++j) {
       const int m = blockIdx.y * TILE_ROWS + ty + 4 * j;
       if (m >= S.M) break;
       const int b = m / S.Tc, t = m % S.Tc;
       const long long e = (long long)m * H + h;
-      if (prefetch && m + 4 < S.M && j + 1 < TILE_ROWS / 4) {
-        // the row this thread takes next: with 16 resident warps per SM the ~24 loads of an iteration are otherwise
-        // exposed, one memory latency after another
+      const int st = j & 1;
+      const bool more = m + 4 < S.M && j + 1 < TILE_ROWS / 4;
+      if (staged) {
+        if (more) issue(m + 4, st ^ 1);
+        cp_async_commit();                              // possibly empty: keeps "all but the newest group" = this row
+        cp_async_wait1();
+      } else if (prefetch == 1 && more) {
         const long long en = e + 4ll * H;
         prefetch_l1(x_real + en); prefetch_l1(beta_lin + en); prefetch_l1(d_o + en);
         if (p_in) prefetch_l1(p_in + en);
@@ -375,25 +473,26 @@ __global__ void __launch_bounds__(256, OCC) ffn_core_bwd_a_kernel(
           }
         }
       }
-      const float2 x = ld2(x_real + e);
+#define LOOM_LD(SLOT, GPTR) (staged ? ld2s(slot(st, SLOT)) : ld2(GPTR))
+      const float2 x = LOOM_LD(0, x_real + e);
       float2 pin = make_float2(0.f, 0.f), gl = make_float2(0.f, 0.f), dpo = make_float2(0.f, 0.f);
-      if (p_in) pin = ld2(p_in + e);
-      if (gate_lin) gl = ld2(gate_lin + e);
-      if (has_w) dpo = ld2(d_pout + e);
-      const float2 bl = ld2(beta_lin + e);
-      const float2 dO = ld2(d_o + e);
+      if (p_in) pin = LOOM_LD(1, p_in + e);
+      if (gate_lin) gl = LOOM_LD(2, gate_lin + e);
+      if (has_w) dpo = LOOM_LD(3, d_pout + e);
+      const float2 bl = LOOM_LD(4, beta_lin + e);
+      const float2 dO = LOOM_LD(5, d_o + e);
       float prev0 = 0.f, prev1 = 0.f;
       const bool rs = reset && reset[m];
       if (!rs) {
         if (t == 0) { if (trace_in) { prev0 = trace_in[(long long)b * H + h]; prev1 = trace_in[(long long)b * H + h + 1]; } }
-        else { const float2 bp = ld2(beta_lin + e - H); prev0 = phase_s0(bp.x + bi0); prev1 = phase_s0(bp.y + bi1); }
+        else { const float2 bp = LOOM_LD(6, beta_lin + e - H); prev0 = phase_s0(bp.x + bi0); prev1 = phase_s0(bp.y + bi1); }
       }
       float R0[9], R1[9], dC0[9], dC1[9];
       bool has_R = false, from_seed = false;
       if (AXIS >= 0) {
         if (c_prev) {
 #pragma unroll
-          for (int k = 0; k < 9; ++k) { float2 v = ld2(c_prev + k * plane + e); R0[k] = v.x; R1[k] = v.y; }
+          for (int k = 0; k < 9; ++k) { float2 v = LOOM_LD(7 + k, c_prev + k * plane + e); R0[k] = v.x; R1[k] = v.y; }
           has_R = true;
         } else if (seed && t == 0 && seed_valid[b]) {
           const float* sp = seed + ((long long)b * H + h) * 9;
@@ -403,9 +502,10 @@ __global__ void __launch_bounds__(256, OCC) ffn_core_bwd_a_kernel(
         }
         if (d_c) {
 #pragma unroll
-          for (int k = 0; k < 9; ++k) { float2 v = ld2(d_c + k * plane + e); dC0[k] = v.x; dC1[k] = v.y; }
+          for (int k = 0; k < 9; ++k) { float2 v = LOOM_LD(16 + k, d_c + k * plane + e); dC0[k] = v.x; dC1[k] = v.y; }
         }
       }
+#undef LOOM_LD
       if (!has_R) {
 #pragma unroll
         for (int k = 0; k < 9; ++k) { R0[k] = 0.f; R1[k] = 0.f; }
@@ -532,8 +632,13 @@ extern "C" int loom_ffn_core_fwd(const LoomFfnCore* a, cudaStream_t stream) {
   if (a->H % 2) return -1;
   CoreScalars S = make_scalars(a);
   const long long n = (long long)S.M * (S.H / 2);
+  static int tiled = -1;           // LOOM_CORE_FWD=flat selects the one-pair-per-thread forward
+  if (tiled < 0) { const char* e = getenv("LOOM_CORE_FWD"); tiled = (e != nullptr && e[0] == 'f') ? 0 : 1; }
+  dim3 grid_t((S.H / 2 + 63) / 64, (S.M + FWD_ROWS - 1) / FWD_ROWS);
 #define LOOM_FWD(AX)                                                                                              \
-  ffn_core_fwd_kernel<AX><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(                                       \
+  if (tiled) { LOOM_FWD_K(ffn_core_fwd_tiled_kernel<AX>, grid_t); } else { LOOM_FWD_K(ffn_core_fwd_kernel<AX>, (unsigned)((n + 255) / 256)); }
+#define LOOM_FWD_K(KERNEL, GRID)                                                                                  \
+  KERNEL<<<GRID, 256, 0, stream>>>(                                       \
       S, (const __nv_bfloat16*)a->x_real, (const __nv_bfloat16*)a->p_in, a->b_real, (const __nv_bfloat16*)a->gate_lin, \
       (const __nv_bfloat16*)a->beta_lin, a->b_imag, a->w_trace, a->trace_in, a->reset, (const __nv_bfloat16*)a->c_prev, \
       a->seed, a->seed_valid, a->gate_w, (__nv_bfloat16*)a->o_out, (__nv_bfloat16*)a->c_out, (__nv_bfloat16*)a->p_out,  \
@@ -545,6 +650,7 @@ extern "C" int loom_ffn_core_fwd(const LoomFfnCore* a, cudaStream_t stream) {
     default: LOOM_FWD(-1); break;
   }
 #undef LOOM_FWD
+#undef LOOM_FWD_K
   return (int)cudaGetLastError();
 }
 
@@ -552,21 +658,22 @@ extern "C" int loom_ffn_core_bwd(const LoomFfnCore* a, cudaStream_t stream) {
   if (a->H % 2) return -1;
   CoreScalars S = make_scalars(a);
   dim3 grid((S.H / 2 + 63) / 64, (S.M + TILE_ROWS - 1) / TILE_ROWS);
-  // blocks per SM pass A is compiled for: 2 (128 registers) or 3 (80 registers, more spills, 24 resident warps);
-  // LOOM_CORE_BWD_OCC selects
-  static int pf = -1;               // LOOM_CORE_PREFETCH=0 turns the next-row L1 prefetch of pass A off
-  if (pf < 0) { const char* e = getenv("LOOM_CORE_PREFETCH"); pf = (e != nullptr && e[0] == '0') ? 0 : 1; }
-  static int occ = 0;
-  if (occ == 0) { const char* e = getenv("LOOM_CORE_BWD_OCC"); occ = (e != nullptr && e[0] == '3') ? 3 : 2; }
+  // how pass A gets its next row: 2 = cp.async into per-thread shared-memory slots (default), 1 = L1 prefetch,
+  // 0 = loads on demand (LOOM_CORE_PREFETCH)
+  static int pf = -1;
+  if (pf < 0) { const char* e = getenv("LOOM_CORE_PREFETCH"); pf = (e != nullptr && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 2; }
+  const size_t stage_bytes = pf == 2 ? (size_t)2 * 25 * 256 * sizeof(uint32_t) : 0;
 #define LOOM_BWD(AX)                                                                                              \
-  if (occ == 3) LOOM_BWD_OCC(AX, 3); else LOOM_BWD_OCC(AX, 2)
-#define LOOM_BWD_OCC(AX, OC)                                                                                      \
-  ffn_core_bwd_a_kernel<AX, OC><<<grid, 256, 0, stream>>>(                                                            \
+  if (pf == 2) { LOOM_BWD_PF(AX, 2); } else if (pf == 1) { LOOM_BWD_PF(AX, 1); } else { LOOM_BWD_PF(AX, 0); }
+#define LOOM_BWD_PF(AX, PFM)                                                                                      \
+  { static bool big_ = false;                                                                                     \
+    if (!big_) { cudaFuncSetAttribute(ffn_core_bwd_a_kernel<AX, PFM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 25 * 256 * 4); big_ = true; } } \
+  ffn_core_bwd_a_kernel<AX, PFM><<<grid, 256, stage_bytes, stream>>>(                                             \
       S, (const __nv_bfloat16*)a->x_real, (const __nv_bfloat16*)a->p_in, a->b_real, (const __nv_bfloat16*)a->gate_lin, \
       (const __nv_bfloat16*)a->beta_lin, a->b_imag, a->w_trace, a->trace_in, a->reset, (const __nv_bfloat16*)a->c_prev, \
       a->seed, a->seed_valid, a->gate_w, (const __nv_bfloat16*)a->d_o, (const __nv_bfloat16*)a->d_c,                  \
       (const __nv_bfloat16*)a->d_pout, (__nv_bfloat16*)a->dx_real, (__nv_bfloat16*)a->dp_in, (__nv_bfloat16*)a->dgate_lin, \
-      a->gz, (__nv_bfloat16*)a->dc_prev, a->dseed, a->dtrace_in, a->g_b_real, a->g_w_trace, a->g_scalars, pf)
+      a->gz, (__nv_bfloat16*)a->dc_prev, a->dseed, a->dtrace_in, a->g_b_real, a->g_w_trace, a->g_scalars)
   switch (S.axis) {
     case 0: LOOM_BWD(0); break;
     case 1: LOOM_BWD(1); break;
@@ -574,7 +681,7 @@ extern "C" int loom_ffn_core_bwd(const LoomFfnCore* a, cudaStream_t stream) {
     default: LOOM_BWD(-1); break;
   }
 #undef LOOM_BWD
-#undef LOOM_BWD_OCC
+#undef LOOM_BWD_PF
   ffn_core_bwd_b_kernel<<<grid, 256, 0, stream>>>(S, a->gz, (const __nv_bfloat16*)a->beta_lin, a->b_imag, a->w_trace,
                                                   a->reset, a->dtrace_out, (__nv_bfloat16*)a->dbeta, a->g_b_imag);
   return (int)cudaGetLastError();

@@ -508,7 +508,6 @@ class FusedPlan:
         h = h_emb.reshape(M, N).contiguous()
         tape = {"layers": [], "hist_k": hist_k, "hist_v": hist_v, "h_emb": h, "cos": cos, "sin": sin, "B": B,
                 "emb_l": {}}
-        self._project_state(h, 0, hist_k, hist_v, tape["emb_l"], "emb")
         reset_flat = tok_reset.reshape(M)
         c_prev, p_in = None, None
         trace_out = []
@@ -523,6 +522,9 @@ class FusedPlan:
             mm, lse_ = K.dread_fwd(d, self._step["q_all"][sub_], hist_k, hist_v, sub_ + 1)
             return mm, lse_, self._readout_lin(mm.reshape(M, N), sub_)
 
+        # the projection of a state into its history slot is needed first by the depth read of the next sublayer, so it
+        # travels with that read: on the second stream both run beside the main stream's GEMMs
+        proj = (h, 0, tape["emb_l"], "emb")
         for bi, blk in enumerate(m.blocks):
             last = bi == L - 1
             t: Dict[str, object] = {"h_in": h}
@@ -530,7 +532,10 @@ class FusedPlan:
             if overlap:                     # depth read 2bi needs only the history: fork it beside attention
                 side.wait_stream(main)
                 with torch.cuda.stream(side):
+                    self._project_state(proj[0], proj[1], hist_k, hist_v, proj[2], proj[3])
                     m1, t["lse1"], s1 = depth_branch(sub)
+            else:
+                self._project_state(proj[0], proj[1], hist_k, hist_v, proj[2], proj[3])
             # --- attention
             qkv = self.lin(h, blk.attn.qkv_weight).view(B, Tc, -1)
             qkc = torch.empty(M, 3, d.qh, d.hd, dtype=self.adt, device=dev)     # sectors: rotated Q, A@K, A@V
@@ -549,12 +554,13 @@ class FusedPlan:
             t["m1"], t["u"] = m1, u
             if d.branch_rms_cap is not None:
                 t["s1"], t["a"] = s1, a
-            self._project_state(u, sub + 1, hist_k, hist_v, t, "u")
             if overlap:                     # depth read 2bi+1 beside the real (and gate) up-projection
                 side.wait_stream(main)
                 with torch.cuda.stream(side):
+                    self._project_state(u, sub + 1, hist_k, hist_v, t, "u")
                     m2, t["lse2"], s2 = depth_branch(sub + 1)
             else:
+                self._project_state(u, sub + 1, hist_k, hist_v, t, "u")
                 m2, t["lse2"], s2 = depth_branch(sub + 1)
             t["m2"] = m2
             # --- Paraplex FFN
@@ -596,8 +602,7 @@ class FusedPlan:
             if d.branch_rms_cap is not None:
                 t["s2"], t["f"] = s2, f
             t["h_out"] = h
-            if not last:
-                self._project_state(h, sub + 2, hist_k, hist_v, t, "h")
+            proj = (h, sub + 2, t, "h")     # taken up by the next block (the last block's state has no slot)
             tape["layers"].append(t)
         tape["h_out"] = h
         tape["depth"] = c_prev
