@@ -137,9 +137,11 @@ __device__ __forceinline__ void core_forward_elem(const CoreScalars& S, float x,
 }
 
 // one (token, neuron pair): loads, both elements' forward, stores; returns the pair's sum of beta^2
-template <int AXIS>
+// STAGED: the row's bf16 pairs were copied into this thread's shared-memory slots (stride 256 words) beforehand:
+// slot 0 x, 1 p_in, 2 gate, 3 beta, 4 beta of the row above, 5..13 carrier planes
+template <int AXIS, bool STAGED>
 __device__ __forceinline__ float core_forward_pair(
-    const CoreScalars& S, int m, int h, const __nv_bfloat16* __restrict__ x_real, const __nv_bfloat16* __restrict__ p_in,
+    const CoreScalars& S, int m, int h, const uint32_t* __restrict__ slots, const __nv_bfloat16* __restrict__ x_real, const __nv_bfloat16* __restrict__ p_in,
     const float* __restrict__ b_real, const __nv_bfloat16* __restrict__ gate_lin,
     const __nv_bfloat16* __restrict__ beta_lin, const float* __restrict__ b_imag, const float* __restrict__ w_trace,
     const float* __restrict__ trace_in, const uint8_t* __restrict__ reset, const __nv_bfloat16* __restrict__ c_prev,
@@ -149,18 +151,19 @@ __device__ __forceinline__ float core_forward_pair(
   const int H = S.H;
   const int b = m / S.Tc, t = m % S.Tc;
   const long long e = (long long)m * H + h;
-  const float2 x = ld2(x_real + e);
+#define LOOM_LDF(SLOT, GPTR) (STAGED ? ld2s(slots + (SLOT) * 256) : ld2(GPTR))
+  const float2 x = LOOM_LDF(0, x_real + e);
   float2 pin = make_float2(0.f, 0.f), gl = make_float2(0.f, 0.f);
-  if (p_in) pin = ld2(p_in + e);
-  if (gate_lin) gl = ld2(gate_lin + e);
-  const float2 bl = ld2(beta_lin + e);
+  if (p_in) pin = LOOM_LDF(1, p_in + e);
+  if (gate_lin) gl = LOOM_LDF(2, gate_lin + e);
+  const float2 bl = LOOM_LDF(3, beta_lin + e);
   const float bi0 = b_imag[h], bi1 = b_imag[h + 1];
   const float beta0 = bl.x + bi0, beta1 = bl.y + bi1;
   float prev0 = 0.f, prev1 = 0.f;
   const bool rs = reset && reset[m];
   if (!rs) {
     if (t == 0) { if (trace_in) { prev0 = trace_in[(long long)b * H + h]; prev1 = trace_in[(long long)b * H + h + 1]; } }
-    else { const float2 bp = ld2(beta_lin + e - H); prev0 = phase_s0(bp.x + bi0); prev1 = phase_s0(bp.y + bi1); }
+    else { const float2 bp = LOOM_LDF(4, beta_lin + e - H); prev0 = phase_s0(bp.x + bi0); prev1 = phase_s0(bp.y + bi1); }
   }
   float w9[9];
   const bool has_w = gate_w != nullptr;
@@ -172,7 +175,7 @@ __device__ __forceinline__ float core_forward_pair(
   if (AXIS >= 0) {
     if (c_prev) {
 #pragma unroll
-      for (int k = 0; k < 9; ++k) { float2 v = ld2(c_prev + k * plane + e); cp0[k] = v.x; cp1[k] = v.y; }
+      for (int k = 0; k < 9; ++k) { float2 v = LOOM_LDF(5 + k, c_prev + k * plane + e); cp0[k] = v.x; cp1[k] = v.y; }
       has_R = true;
     } else if (seed && t == 0 && seed_valid[b]) {
       const float* sp = seed + ((long long)b * H + h) * 9;
@@ -181,6 +184,7 @@ __device__ __forceinline__ float core_forward_pair(
       has_R = true;
     }
   }
+#undef LOOM_LDF
   if (!has_R) {
 #pragma unroll
     for (int k = 0; k < 9; ++k) { cp0[k] = 0.f; cp1[k] = 0.f; }
@@ -229,14 +233,16 @@ __global__ void __launch_bounds__(256) ffn_core_fwd_kernel(
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   float bsq = 0.f;
   if (idx < (long long)S.M * Hp)
-    bsq = core_forward_pair<AXIS>(S, (int)(idx / Hp), (int)(idx % Hp) * 2, x_real, p_in, b_real, gate_lin, beta_lin, b_imag,
+    bsq = core_forward_pair<AXIS, false>(S, (int)(idx / Hp), (int)(idx % Hp) * 2, nullptr, x_real, p_in, b_real, gate_lin, beta_lin, b_imag,
                                   w_trace, trace_in, reset, c_prev, seed, seed_valid, gate_w, o_out, c_out, p_out, trace_out);
   block_add_256(bsq, beta_sq_sum);
 }
 
-// Tiled variant: a block owns 64 neuron pairs x FWD_ROWS tokens, every thread walks FWD_ROWS / 4 rows and asks L1 for
-// its next row's lines before working on the current one.
+// Tiled variant: a block owns 64 neuron pairs x FWD_ROWS tokens; every thread walks FWD_ROWS / 4 rows and copies its
+// next row into its own shared-memory slots with cp.async while it works on the current one (see pass A of the
+// backward for the reasoning).
 constexpr int FWD_ROWS = 16;
+constexpr int FWD_SLOTS = 14;
 template <int AXIS>
 __global__ void __launch_bounds__(256) ffn_core_fwd_tiled_kernel(
     CoreScalars S_in, const __nv_bfloat16* __restrict__ x_real, const __nv_bfloat16* __restrict__ p_in,
@@ -252,23 +258,35 @@ __global__ void __launch_bounds__(256) ffn_core_fwd_tiled_kernel(
   const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
   const int h = (blockIdx.x * 64 + tx) * 2;
   const long long plane = (long long)S.M * H;
+  extern __shared__ uint32_t stg[];                     // [2 stages][FWD_SLOTS][256 threads]
+  auto issue = [&](int mn, int st) {
+    uint32_t* sl = stg + st * FWD_SLOTS * 256 + threadIdx.x;
+    const long long en = (long long)mn * H + h;
+    cp_async4(sl, x_real + en);
+    if (p_in) cp_async4(sl + 256, p_in + en);
+    if (gate_lin) cp_async4(sl + 2 * 256, gate_lin + en);
+    cp_async4(sl + 3 * 256, beta_lin + en);
+    if (mn % S.Tc != 0) cp_async4(sl + 4 * 256, beta_lin + en - H);
+    if (AXIS >= 0 && c_prev) {
+#pragma unroll
+      for (int k = 0; k < 9; ++k) cp_async4(sl + (5 + k) * 256, c_prev + k * plane + en);
+    }
+  };
   float bsq = 0.f;
   if (h < H) {
+    const int m_first = blockIdx.y * FWD_ROWS + ty;
+    if (m_first < S.M) issue(m_first, 0);
+    cp_async_commit();
     for (int j = 0; j < FWD_ROWS / 4; ++j) {
       const int m = blockIdx.y * FWD_ROWS + ty + 4 * j;
       if (m >= S.M) break;
-      if (m + 4 < S.M && j + 1 < FWD_ROWS / 4) {
-        const long long en = (long long)(m + 4) * H + h;
-        prefetch_l1(x_real + en); prefetch_l1(beta_lin + en);
-        if (p_in) prefetch_l1(p_in + en);
-        if (gate_lin) prefetch_l1(gate_lin + en);
-        if (AXIS >= 0 && c_prev) {
-#pragma unroll
-          for (int k = 0; k < 9; ++k) prefetch_l1(c_prev + k * plane + en);
-        }
-      }
-      bsq += core_forward_pair<AXIS>(S, m, h, x_real, p_in, b_real, gate_lin, beta_lin, b_imag, w_trace, trace_in, reset,
-                                     c_prev, seed, seed_valid, gate_w, o_out, c_out, p_out, trace_out);
+      const int st = j & 1;
+      if (m + 4 < S.M && j + 1 < FWD_ROWS / 4) issue(m + 4, st ^ 1);
+      cp_async_commit();
+      cp_async_wait1();
+      bsq += core_forward_pair<AXIS, true>(S, m, h, stg + st * FWD_SLOTS * 256 + threadIdx.x, x_real, p_in, b_real, gate_lin,
+                                           beta_lin, b_imag, w_trace, trace_in, reset, c_prev, seed, seed_valid, gate_w, o_out,
+                                           c_out, p_out, trace_out);
     }
   }
   block_add_256(bsq, beta_sq_sum);
@@ -636,9 +654,10 @@ extern "C" int loom_ffn_core_fwd(const LoomFfnCore* a, cudaStream_t stream) {
   if (tiled < 0) { const char* e = getenv("LOOM_CORE_FWD"); tiled = (e != nullptr && e[0] == 'f') ? 0 : 1; }
   dim3 grid_t((S.H / 2 + 63) / 64, (S.M + FWD_ROWS - 1) / FWD_ROWS);
 #define LOOM_FWD(AX)                                                                                              \
-  if (tiled) { LOOM_FWD_K(ffn_core_fwd_tiled_kernel<AX>, grid_t); } else { LOOM_FWD_K(ffn_core_fwd_kernel<AX>, (unsigned)((n + 255) / 256)); }
-#define LOOM_FWD_K(KERNEL, GRID)                                                                                  \
-  KERNEL<<<GRID, 256, 0, stream>>>(                                       \
+  if (tiled) { LOOM_FWD_K(ffn_core_fwd_tiled_kernel<AX>, grid_t, 2 * FWD_SLOTS * 256 * 4); }                     \
+  else { LOOM_FWD_K(ffn_core_fwd_kernel<AX>, (unsigned)((n + 255) / 256), 0); }
+#define LOOM_FWD_K(KERNEL, GRID, SHM)                                                                             \
+  KERNEL<<<GRID, 256, SHM, stream>>>(                                       \
       S, (const __nv_bfloat16*)a->x_real, (const __nv_bfloat16*)a->p_in, a->b_real, (const __nv_bfloat16*)a->gate_lin, \
       (const __nv_bfloat16*)a->beta_lin, a->b_imag, a->w_trace, a->trace_in, a->reset, (const __nv_bfloat16*)a->c_prev, \
       a->seed, a->seed_valid, a->gate_w, (__nv_bfloat16*)a->o_out, (__nv_bfloat16*)a->c_out, (__nv_bfloat16*)a->p_out,  \

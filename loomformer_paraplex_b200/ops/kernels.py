@@ -753,4 +753,24 @@ class _ElementwiseMixin:
 
 
 class CudaKernels(_ElementwiseMixin, CudaKernels):      # noqa: F811  (final kernel set = GEMMs + element-wise kernels)
-    pass
+    """``LOOM_DISABLE_OPS=attn_fwd,attn_bwd,ffn_core_fwd,...`` (or ``all``) sends the named operations of a new kernel set
+    to their PyTorch twins, for bisecting a numerical difference to one kernel; each such call is counted in
+    ``fallbacks`` like any other library fallback.  The reference has per-op switches of the same kind
+    (``LOOM_TRIA_DISABLE_OPS``, reference ``tria.py:104-109``)."""
+
+    def __init__(self, *args, **kw) -> None:
+        super().__init__(*args, **kw)
+        names = [n.strip() for n in os.environ.get("LOOM_DISABLE_OPS", "").split(",") if n.strip()]
+        if not names:
+            return
+        if names == ["all"]:
+            names = [n for n in dir(TorchKernels) if not n.startswith("_") and callable(getattr(TorchKernels, n))]
+        for n in names:
+            twin = getattr(TorchKernels, n, None)
+            if twin is None or not callable(twin) or n in ("flush_wgrads",):
+                raise ValueError(f"LOOM_DISABLE_OPS: {n!r} is not an operation of the kernel set")
+
+            def routed(*a, _twin=twin, _n=n, **k):
+                self.fallbacks[_n] += 1
+                return _twin(self, *a, **k)
+            setattr(self, n, routed)

@@ -146,6 +146,21 @@ def case_attn_fwd(K, M, Tc=128, T=1024):
     return run, nbytes(qkc, kc, vc), 3 * 2.0 * B * d.qh * Tc * T * d.hd
 
 
+def case_attn_fwd_library(K, M, Tc=128, T=1024):
+    """What the native forward replaced, timed the same way: PyTorch SDPA with value = [K ; V] (one call returns both
+    contexts), keys and values repeated to the query heads, an explicit boolean mask (reference
+    ``loomformer.py:3085-3114``).  Not an operation of this repository: a yardstick."""
+    import torch.nn.functional as F
+    d, B, s, kc, vc, qkc = _attn_inputs(M, Tc, T)
+    q = qkc[:, 0].view(B, Tc, d.qh, d.hd).transpose(1, 2)                               # [B, QH, Tc, HD]
+    k = kc.repeat_interleave(d.group, dim=2).transpose(1, 2)                            # [B, QH, T, HD]
+    v = torch.cat((kc, vc), -1).repeat_interleave(d.group, dim=2).transpose(1, 2)       # [B, QH, T, 2 HD]
+    mask = (torch.arange(T, device="cuda").view(1, T) <= (s + torch.arange(Tc, device="cuda")).view(Tc, 1)).view(1, 1, Tc, T)
+    run = lambda: F.scaled_dot_product_attention(q, k, v, attn_mask=mask)
+    run()
+    return run, nbytes(qkc, kc, vc), 3 * 2.0 * B * d.qh * Tc * T * d.hd
+
+
 def case_attn_bwd(K, M, Tc=128, T=1024):
     d, B, s, kc, vc, qkc = _attn_inputs(M, Tc, T)
     lse = K.attn_fwd(d, qkc, kc, vc, s, T, None)
@@ -191,7 +206,7 @@ def case_optimizer(K, M):
 
 CASES: Dict[str, Callable] = {"imag_bwd": case_imag_bwd, "linear": case_linear, "dgrad": case_dgrad, "wgrad": case_wgrad,
                               "wgrad_grouped": case_wgrad_grouped, "ffn_core_fwd": case_ffn_core_fwd,
-                              "ffn_core_bwd": case_ffn_core_bwd, "attn_fwd": case_attn_fwd, "attn_bwd": case_attn_bwd,
+                              "ffn_core_bwd": case_ffn_core_bwd, "attn_fwd": case_attn_fwd, "attn_fwd_library": case_attn_fwd_library, "attn_bwd": case_attn_bwd,
                               "dread_slot_bwd": case_dread_slot_bwd, "dread_fwd": case_dread_fwd,
                               "optimizer": case_optimizer}
 

@@ -109,3 +109,10 @@ def test_fused_forward_logits_match():
         plan = FusedPlan(m, kernels=TorchKernels(), compute_dtype=torch.float32)
         _, logits = plan.run(x, None, None, None, want_grad=False)
     assert torch.allclose(ref, logits, atol=2e-5, rtol=1e-4)
+
+
+def test_per_op_switch_names_are_checked(monkeypatch):
+    """``LOOM_DISABLE_OPS`` is validated against the kernel interface (the routing itself needs the native set)."""
+    from loomformer_paraplex_b200.ops.twins import TorchKernels
+    for name in ("attn_fwd", "attn_bwd", "ffn_core_fwd", "ffn_core_bwd", "imag_fwd", "linear", "dread_fwd", "add_ln_fwd"):
+        assert callable(getattr(TorchKernels, name))

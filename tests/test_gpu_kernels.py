@@ -447,3 +447,20 @@ def test_step_bookkeeping_helpers():
     _close(hist[1].view(300, 192), x.float() @ w.float().t(), 2e-2, "linear out=")
     assert float(hist[0].abs().sum()) == 0.0 and float(hist[2].abs().sum()) == 0.0
     assert not ck.fallbacks, ck.fallbacks
+
+
+def test_per_op_switch_routes_to_the_twin(monkeypatch):
+    """LOOM_DISABLE_OPS sends one named operation of a new kernel set to its PyTorch twin and counts it."""
+    from loomformer_paraplex_b200.ops import kernels
+    monkeypatch.setenv("LOOM_DISABLE_OPS", "add_ln_fwd")
+    ck = kernels.CudaKernels()
+    monkeypatch.delenv("LOOM_DISABLE_OPS")
+    a, b = bf(64, 256), bf(64, 256)
+    w, bias = torch.randn(256, device="cuda"), torch.randn(256, device="cuda")
+    y1 = ck.add_ln_fwd(a, b, w, bias, None)[0]
+    assert ck.fallbacks["add_ln_fwd"] == 1
+    y2 = kernels.CudaKernels().add_ln_fwd(a, b, w, bias, None)[0]
+    _close(y1, y2, 2e-2, "add_ln via twin")
+    monkeypatch.setenv("LOOM_DISABLE_OPS", "no_such_op")
+    with pytest.raises(ValueError):
+        kernels.CudaKernels()
