@@ -321,12 +321,85 @@ def measure_decode(cfg_kw, dev, world, batch, prompt_len, new):
             "unit": "tokens/s", "graph_replay": True}
 
 
-def secondary_ours(args, dev, world, rank, deadline):
+def measure_tp_ops(dev, world, rank):
+    """The two fused tensor-parallel GEMMs over all ranks of the job on the 113M FFN shape (2048 tokens): all-gather of
+    the row-sharded activations inside the column-parallel up-projection, reduce-scatter inside the row-parallel
+    down-projection's epilogue.  Device-timed with the bracketing barriers, max over ranks; roofline = the slower of
+    the per-rank FLOPs at the measured GEMM peak and the bytes that cross NVLink at 770 GB/s per direction."""
+    import torch
+    import torch.distributed as dist
+    from loomformer_paraplex_b200.ops import kernels
+    from loomformer_paraplex_b200.parallel.tp import TensorParallel
+    tp = TensorParallel(device=dev)
+    M, K, H = 2048, 768, 3072
+    per, hl = M // world, H // world
+    g = torch.Generator(device="cpu").manual_seed(11)
+    x_rows = torch.randn(per, K, generator=g).to(torch.bfloat16).to(dev)
+    w_up = (torch.randn(hl, K, generator=g) * 0.03).to(torch.bfloat16).to(dev)
+    w_dn = (torch.randn(K, hl, generator=g) * 0.03).to(torch.bfloat16).to(dev)
+    o_l = torch.randn(M, hl, generator=g).to(torch.bfloat16).to(dev)
+
+    def timed(fn, iters=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(); dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record(); torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / iters], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+    t_up = timed(lambda: tp.column_parallel("x", x_rows, w_up, M))
+    t_dn = timed(lambda: tp.row_parallel("z", o_l, w_dn))
+    kernels.check_status(dev)
+    peak = 1608.7e12
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            peak = float(json.load(fh)["bf16_tflops"]) * 1e12
+    except Exception:
+        pass
+    flops = 2.0 * M * K * hl
+    up_bytes, dn_bytes = (world - 1) * per * K * 2, (world - 1) * per * K * 4
+    roof_up = max(flops / peak, up_bytes / 770e9) * 1e3
+    roof_dn = max(flops / peak, dn_bytes / 770e9) * 1e3
+    return {"world": world, "shape": "2048 tokens, 768 -> 3072/world -> 768", "ms_all_gather_up_gemm": t_up,
+            "ms_down_gemm_reduce_scatter": t_dn, "roofline_ms": [roof_up, roof_dn],
+            "fraction_of_roofline": [roof_up / t_up, roof_dn / t_dn],
+            "note": "op-level: the model itself is not tensor-parallel"}
+
+
+class LineGuard:
+    """Guarantees that the one JSON line is printed.  The secondary measurements run after the headline; should one of
+    them block (a rank lost inside a collective), a timer prints the headline with whatever secondary results exist,
+    marks the line, and ends the process, instead of leaving the caller without a number."""
+
+    def __init__(self, rank, limit_s, emit_fn):
+        self.rank, self.emit_fn, self.done = rank, emit_fn, threading.Lock()
+        self.timer = threading.Timer(limit_s, self._expire)
+        self.timer.daemon = True
+        self.timer.start()
+
+    def _expire(self):
+        if self.done.acquire(blocking=False):
+            if self.rank == 0:
+                self.emit_fn(True)
+            sys.stdout.flush()
+            os._exit(0)
+
+    def finish(self):
+        if self.done.acquire(blocking=False):
+            self.timer.cancel()
+            if self.rank == 0:
+                self.emit_fn(False)
+
+
+def secondary_ours(args, dev, world, rank, deadline, out):
     """The benchmark configurations that are not the headline, measured after it in the same process."""
     import copy
     import gc
     import torch
-    out = {}
 
     def guarded(name, fn):
         skip = deadline - time.time() < 20.0
@@ -347,9 +420,11 @@ def secondary_ours(args, dev, world, rank, deadline):
         guarded(f"decode_b{batch}", lambda: measure_decode(dict(MODEL_KW), dev, world, batch, 512, 256))
     torch.cuda.reset_peak_memory_stats(dev)
 
-    def smol():
+    def smol(grad_sync=None):
         a = copy.copy(args)
         a.model, a.micro_batch = "smol360", 8
+        if grad_sync is not None:
+            a.grad_sync = grad_sync
         cfg = make_cfg(a, "smol360")
         engine, path = make_engine(a, cfg, dev, world)
         r = measure_training(a, cfg, engine, dev, world, rank, "pretrain", 5, 3)
@@ -359,6 +434,10 @@ def secondary_ours(args, dev, world, rank, deadline):
                 "e2e_value": tokens / (r["ms_e2e"] / 1e3), "grad_path": path, "gpu_launches": r["launches"],
                 "library_fallback_calls": r["fallbacks"], "final_loss": r["loss"], "peak_memory_gib": round(r["peak_gb"], 2)}
     guarded("smol360", smol)
+    if world > 1:
+        # sharded data parallelism (owner-only update, weights fetched from their owners inside the consuming GEMM)
+        guarded("smol360_fsdp", lambda: smol("fsdp"))
+        guarded("tp_fused_gemms", lambda: measure_tp_ops(dev, world, rank))
 
     def sft():
         a = copy.copy(args)
@@ -371,7 +450,6 @@ def secondary_ours(args, dev, world, rank, deadline):
                 "e2e_value": tokens / (r["ms_e2e"] / 1e3), "grad_path": path, "gpu_launches": r["launches"],
                 "library_fallback_calls": r["fallbacks"], "final_loss": r["loss"]}
     guarded("sft", sft)
-    return out
 
 
 def run_ours(args):
@@ -383,19 +461,26 @@ def run_ours(args):
     cfg = make_cfg(args, args.model)
     engine, path = make_engine(args, cfg, dev, world)
     r = measure_training(args, cfg, engine, dev, world, rank, args.workload, args.steps, args.warmup)
-    extra = {}
-    if args.secondary == "on":
-        del engine
-        gc.collect()
-        torch.cuda.empty_cache()
-        extra["secondary"] = secondary_ours(args, dev, world, rank, time.time() + args.secondary_budget)
-    if rank == 0:
-        tokens = args.micro_batch * args.seq_len * world
+    sec = {}
+    tokens = args.micro_batch * args.seq_len * world
+
+    def emit_line(aborted):
+        extra = {"secondary": dict(sec)} if args.secondary == "on" else {}
+        if aborted:
+            extra["secondary_aborted"] = "a secondary measurement did not return in time; the headline above is complete"
         emit(args, "ours", r["ms"], r["clocks"], world, dict({
             "e2e": {"value": tokens / (r["ms_e2e"] / 1000.0), "unit": "tokens/s", "h2d_bytes_per_step": r["h2d"],
                     "d2h_bytes_per_step": 4, "ms_per_step": r["ms_e2e"]},
             "gpu_launches": r["launches"], "grad_path": path, "peak_memory_gib": round(r["peak_gb"], 2),
             "library_fallback_calls": r["fallbacks"], "final_loss": r["loss"]}, **extra))
+
+    guard = LineGuard(rank, args.secondary_budget + 150.0, emit_line)
+    if args.secondary == "on":
+        del engine
+        gc.collect()
+        torch.cuda.empty_cache()
+        secondary_ours(args, dev, world, rank, time.time() + args.secondary_budget, sec)
+    guard.finish()
     pdist.shutdown()
 
 
@@ -417,6 +502,27 @@ def reference_dir():
     except OSError:
         pass
     return here
+
+
+def adopt_reference_toolchain(ref_dir):
+    """The command lines in the reference's ninja files name the host compiler its extensions were built with (torch
+    takes it from CC / CXX).  With a different CC in the environment every command line changes and ninja compiles
+    everything again, so the recorded compilers are put back into the environment when they exist here."""
+    ninja = os.path.join(ref_dir, "kernels", "build", "loomformer_pvpowlu", "build.ninja")
+    try:
+        with open(ninja) as fh:
+            text = fh.read()
+    except OSError:
+        return
+    for line in text.splitlines():
+        if line.startswith("cxx = "):
+            cxx = line.split("=", 1)[1].strip()
+            if os.path.isfile(cxx):
+                os.environ["CXX"] = cxx
+        if line.startswith("cuda_cflags = ") and "-ccbin " in line:
+            cc = line.split("-ccbin ", 1)[1].split()[0]
+            if os.path.isfile(cc):
+                os.environ["CC"] = cc
 
 
 def settle_reference_mtimes(ref_dir):
@@ -451,6 +557,7 @@ def run_reference(args):
     sys.dont_write_bytecode = True
     sys.path.insert(0, ref_dir)
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0")
+    adopt_reference_toolchain(ref_dir)
     if int(os.environ.get("LOCAL_RANK", "0")) == 0:
         settle_reference_mtimes(ref_dir)
     import math
@@ -621,10 +728,23 @@ def run_reference(args):
         return bool(t.item())
 
     r = train_arm(args.model, args.micro_batch, args.workload, args.steps, args.warmup)
-    extra = {}
+    sec = {}
+    tokens_head = args.micro_batch * args.seq_len * world
+
+    def emit_line(aborted):
+        extra = {"secondary": dict(sec)} if args.secondary == "on" else {}
+        if aborted:
+            extra["secondary_aborted"] = "a secondary measurement did not return in time; the headline above is complete"
+        emit(args, "reference", r["ms"], r["clocks"], world, dict({
+            "e2e": {"value": tokens_head / (r["ms_e2e"] / 1000.0), "unit": "tokens/s",
+                    "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": 8, "ms_per_step": r["ms_e2e"]},
+            "gpu_launches": None, "final_loss": r["loss"],
+            "note": "unmodified reference Model/DDP/optimizer from baseline/_ref; loop body replicated from its trainer"},
+            **extra))
+
+    guard = LineGuard(rank, args.secondary_budget + 240.0, emit_line)
     if args.secondary == "on":
         import gc
-        sec = {}
         deadline = time.time() + args.secondary_budget
 
         def guarded(name, fn):
@@ -649,6 +769,9 @@ def run_reference(args):
                     "e2e_value": tokens / (q["ms_e2e"] / 1e3), "grad_path": "its DistributedDataParallel wrapper",
                     "final_loss": q["loss"], "note": "cfg/smol360.yaml as shipped (activation checkpointing on)"}
         guarded("smol360", smol)
+        if world > 1:
+            sec["smol360_fsdp"] = {"unavailable": "the reference has no sharded data parallelism (its only strategy is DDP)"}
+            sec["tp_fused_gemms"] = {"unavailable": "the reference has no tensor parallelism"}
 
         def sft():
             q = train_arm("113m", args.micro_batch, "sft", 3, 3)
@@ -659,15 +782,7 @@ def run_reference(args):
                     "note": "the reference's Model under its DDP wrapper on this repository's packed batches (its own SFT "
                             "script is single-device)"}
         guarded("sft", sft)
-        extra["secondary"] = sec
-    if rank == 0:
-        tokens = args.micro_batch * args.seq_len * world
-        emit(args, "reference", r["ms"], r["clocks"], world, dict({
-            "e2e": {"value": tokens / (r["ms_e2e"] / 1000.0), "unit": "tokens/s",
-                    "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": 8, "ms_per_step": r["ms_e2e"]},
-            "gpu_launches": None, "final_loss": r["loss"],
-            "note": "unmodified reference Model/DDP/optimizer from baseline/_ref; loop body replicated from its trainer"},
-            **extra))
+    guard.finish()
     if world > 1:
         dist.destroy_process_group()
 
