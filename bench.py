@@ -506,8 +506,9 @@ def reference_dir():
 
 def adopt_reference_toolchain(ref_dir):
     """The command lines in the reference's ninja files name the host compiler its extensions were built with (torch
-    takes it from CC / CXX).  With a different CC in the environment every command line changes and ninja compiles
-    everything again, so the recorded compilers are put back into the environment when they exist here."""
+    takes it from CC / CXX) and the GPU target (from TORCH_CUDA_ARCH_LIST).  With different values in the environment
+    every command line changes and ninja compiles everything again (about a minute per extension), so the recorded
+    values are put back into the environment; the compilers only when they exist here."""
     ninja = os.path.join(ref_dir, "kernels", "build", "loomformer_pvpowlu", "build.ninja")
     try:
         with open(ninja) as fh:
@@ -523,6 +524,14 @@ def adopt_reference_toolchain(ref_dir):
             cc = line.split("-ccbin ", 1)[1].split()[0]
             if os.path.isfile(cc):
                 os.environ["CC"] = cc
+        if line.startswith("cuda_cflags = ") and "-gencode=arch=compute_" in line:
+            # the target the objects were compiled for: torch derives the -gencode flag from TORCH_CUDA_ARCH_LIST, and a
+            # value inherited from the environment (e.g. 10.0a instead of 10.0) changes every nvcc command line
+            arch = line.split("-gencode=arch=compute_", 1)[1].split(",")[0]          # "100" or "100a"
+            digits = "".join(ch for ch in arch if ch.isdigit())
+            suffix = arch[len(digits):]
+            if len(digits) >= 2:
+                os.environ["TORCH_CUDA_ARCH_LIST"] = f"{digits[:-1]}.{digits[-1]}{suffix}"
 
 
 def settle_reference_mtimes(ref_dir):

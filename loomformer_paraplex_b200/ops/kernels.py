@@ -348,9 +348,16 @@ class CudaKernels(TorchKernels):
             u_seg = (dbeta, w_imag[:, hd + 2 * n:hd + 3 * n])
             shared(hd + 3 * n, m2v.reshape(M, n), dm2.view(M, n))
         else:
-            per_head(0, qkc[:, 0], dqkc[:, 0])
-            per_head(hd, qkc[:, 1], dqkc[:, 1])
-            per_head(2 * hd, qkc[:, 2], dqkc[:, 2])
+            # the three attention sectors of a head are adjacent columns of its weight block: one batched data-gradient
+            # GEMM with N = 3 * head_dim into [M, QH, 3, HD], then one strided copy into the [M, 3, QH, HD] order the
+            # attention backward reads (two launches instead of three GEMMs); the weight gradients stay per sector
+            # because their inputs are the sectors of qkc
+            tmp = torch.empty(M, d.qh, 3 * hd, dtype=torch.bfloat16, device=dev)
+            gemm([db3], [d.hpq], w3[:, :, 0:3 * hd], tmp, M=M, N=3 * hd, heads=d.qh, b_mn=True)
+            dqkc.copy_(tmp.view(M, d.qh, 3, hd).transpose(1, 2))
+            native.count()
+            for s_ in range(3):
+                self._wgrad(db3, qkc[:, s_], g3[:, :, s_ * hd:(s_ + 1) * hd], d.hpq, hd, d.qh)
             shared(3 * hd, u, du, acc_u)
             u_seg = (dbeta, w_imag[:, 3 * hd:3 * hd + n])
             per_head(3 * hd + n, m2v, dm2)
