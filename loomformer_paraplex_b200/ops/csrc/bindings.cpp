@@ -194,6 +194,37 @@ void decode_attn(torch::Tensor q, torch::Tensor kc, torch::Tensor vc, torch::Ten
   TORCH_CHECK(rc == 0, "loom_decode_attn failed: ", rc);
 }
 
+void skinny_linear(torch::Tensor x, torch::Tensor w, c10::optional<torch::Tensor> bias, torch::Tensor y) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && y.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && y.stride(1) == 1,
+              "skinny_linear: 2-D operands with unit inner stride");
+  TORCH_CHECK(x.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16, "skinny_linear: bf16 inputs");
+  TORCH_CHECK(y.scalar_type() == torch::kBFloat16 || y.scalar_type() == torch::kFloat32, "skinny_linear: bf16 or fp32 output");
+  TORCH_CHECK(x.size(1) == w.size(1) && y.size(0) == x.size(0) && y.size(1) == w.size(0), "skinny_linear: shapes");
+  const float* b = nullptr;
+  if (bias.has_value()) { TORCH_CHECK(bias->numel() == w.size(0), "skinny_linear: bias length"); b = fptr(*bias); }
+  int rc = loom_skinny_linear(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), b, y.data_ptr(), y.stride(0),
+                              y.scalar_type() == torch::kFloat32, (int)x.size(0), (int)w.size(0), (int)x.size(1), cur_stream());
+  TORCH_CHECK(rc == 0, "loom_skinny_linear failed: ", rc);
+}
+
+void decode_rope_store(torch::Tensor qkv, torch::Tensor cos_tab, torch::Tensor sin_tab, torch::Tensor pos, torch::Tensor q_out,
+                       torch::Tensor kc, torch::Tensor vc, int64_t QH, int64_t KVH, int64_t HD) {
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.scalar_type() == torch::kBFloat16, "decode_rope_store: qkv rows");
+  TORCH_CHECK(qkv.size(1) == (QH + 2 * KVH) * HD, "decode_rope_store: qkv width");
+  TORCH_CHECK(kc.is_contiguous() && vc.is_contiguous() && kc.dim() == 4 && kc.size(2) == KVH && kc.size(3) == HD,
+              "decode_rope_store: caches [B, S, KVH, HD]");
+  TORCH_CHECK(q_out.stride(-1) == 1 && q_out.scalar_type() == torch::kBFloat16 && pos.scalar_type() == torch::kInt64,
+              "decode_rope_store: q_out rows, int64 position");
+  TORCH_CHECK(cos_tab.dim() == 2 && cos_tab.size(1) == HD && sin_tab.sizes() == cos_tab.sizes(), "decode_rope_store: tables");
+  int rc = loom_decode_rope_store(qkv.data_ptr(), qkv.stride(0), fptr(cos_tab), fptr(sin_tab),
+                                  (const long long*)pos.data_ptr<int64_t>(), q_out.data_ptr(), q_out.stride(0), kc.data_ptr(),
+                                  vc.data_ptr(), (int)qkv.size(0), (int)kc.size(1), (int)cos_tab.size(0), (int)QH, (int)KVH,
+                                  (int)HD, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_decode_rope_store failed: ", rc);
+}
+
 void slot_pool(bool bwd, torch::Tensor keys, torch::Tensor w9, torch::Tensor pooled, torch::Tensor stats,
                c10::optional<torch::Tensor> dpooled, c10::optional<torch::Tensor> dkeys, c10::optional<torch::Tensor> dw9_part,
                int64_t BK, int64_t H) {
@@ -432,6 +463,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rope_bwd", &rope_bwd, "inverse RoPE of the q/k/v gradients");
   m.def("dread", &dread, "depth-attention read (forward / backward)");
   m.def("decode_attn", &decode_attn, "KV-cache attention for one new token per sequence, dual context, split over positions");
+  m.def("skinny_linear", &skinny_linear, "y = x W^T (+ bias) for up to 16 rows: weights streamed once, output may be a strided view");
+  m.def("decode_rope_store", &decode_rope_store, "RoPE of the new token's Q / K at the device-side position + KV cache append");
   m.def("slot_pool", &slot_pool, "softmax pooling of boundary carriers over neurons (forward / backward)");
   m.def("cross_attn", &cross_attn, "token rows attending to the boundary keys (forward / backward)");
   m.def("fixed_rms", &fixed_rms, "x * target / rms(x) over head_dim (forward / backward)");

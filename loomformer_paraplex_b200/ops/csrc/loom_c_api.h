@@ -177,6 +177,17 @@ typedef struct {
 int loom_attn_fwd(const LoomAttn* a, cudaStream_t stream);
 int loom_attn_bwd(const LoomAttn* a, cudaStream_t stream);
 
+// ---- small-batch pieces of the decode step (decode_step.cu) ----
+// y[M, N] = x[M, K] . W[N, K]^T (+ bias[N]); bf16 inputs, bf16 or fp32 output, M <= 16, K a multiple of 8; ld* are row
+// pitches in elements (the output may be a strided view)
+int loom_skinny_linear(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* y,
+                       long long ldy, int out_fp32, int M, int N, int K, cudaStream_t st);
+// rotate-half RoPE of Q and K of one new token per sequence at the position stored in *pos (device int64): qkv rows
+// [Q | K | V] -> q_out rows (pitch ld_q), kc / vc [B, S, KVH, HD] row *pos; cos / sin tables [table_rows, HD] fp32
+int loom_decode_rope_store(const void* qkv, long long ld_qkv, const float* cos_tab, const float* sin_tab,
+                           const long long* pos, void* q_out, long long ld_q, void* kc, void* vc, int B, int S,
+                           int table_rows, int QH, int KVH, int HD, cudaStream_t st);
+
 // ---- fused gradient reduce-scatter + AdamW + parameter all-gather over peer memory (comm.cu) ----
 typedef struct {
   int W, rank;

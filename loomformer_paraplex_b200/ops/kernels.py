@@ -247,6 +247,25 @@ class CudaKernels(TorchKernels):
             gemm([x], [Kd], w, c, M=M, N=N, bias=b32)
         return c
 
+    def linear_small(self, x, w, bias=None, out=None, out_dtype=None):
+        """``x @ w^T (+ bias)`` for a handful of rows (the decode step): up to 16 rows go through the weight-streaming
+        kernel (``csrc/decode_step.cu``), more through the tensor-core GEMM.  ``out`` may be a row-strided bf16 / fp32
+        view (a history slot), which saves the copy."""
+        M, Kd = x.shape
+        N = w.shape[0]
+        ok = (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
+              and Kd % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+              and w.data_ptr() % 16 == 0)
+        if M > 16 or not ok:
+            if out is not None and not (out.is_contiguous() and out.dtype == torch.bfloat16):
+                out.copy_(self.linear(x, w, bias, out_dtype))
+                return out
+            return self.linear(x, w, bias, out_dtype, out=out)
+        y = out if out is not None else torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=x.device)
+        native.ext().skinny_linear(x, w, None if bias is None else _f32c(bias), y)
+        native.count()
+        return y
+
     def linear_dgrad(self, dy, w, out=None, accumulate=False):
         """``dy @ w``; with ``out`` the product is written (or, with ``accumulate``, added) into that bf16 buffer by
         the GEMM's epilogue, which saves the separate add that sums gradient branches."""

@@ -41,6 +41,15 @@ class TorchKernels:
             return out
         return y if out_dtype is None else y.to(out_dtype)
 
+    def linear_small(self, x, w, bias=None, out=None, out_dtype=None):
+        y = F.linear(x, w.to(x.dtype), None if bias is None else bias.to(x.dtype))
+        if out_dtype is not None:
+            y = y.to(out_dtype)
+        if out is None:
+            return y
+        out.copy_(y)
+        return out
+
     def linear_dgrad(self, dy, w, out=None, accumulate=False):
         r = dy @ w.to(dy.dtype)
         if out is None:

@@ -87,9 +87,12 @@ class DecodeEngine:
         if self._fused:
             from ..ops.kernels import CudaKernels
             self._K = CudaKernels(defer_wgrad=False)
-            self._hk = z(2 * L, B, d.qh, d.hd)
-            self._hv = z(2 * L, B, d.qh, d.hd)
+            # depth history: a slot's row is the [K | V] row of the projection GEMM, which stores straight into it
+            self._hist = z(2 * L, B, 2, d.qh, d.hd)
+            self._hk, self._hv = self._hist[:, :, 0], self._hist[:, :, 1]
             self._qkc = z(B, 3, d.qh, d.hd)
+            self._rope_cos = model.rope_cos.detach().float().reshape(-1, d.hd).contiguous()
+            self._rope_sin = model.rope_sin.detach().float().reshape(-1, d.hd).contiguous()
         self.refresh_weights()
 
     # ------------------------------------------------------------------ weights in the compute dtype
@@ -235,23 +238,25 @@ class DecodeEngine:
         B, S, dt = self.B, self.S, self.dt
         pos = self.pos
         h = self.w(m.emb.weight)[self.tok_in]
-        cos = m.rope_cos.index_select(0, pos).to(dt).view(1, 1, d.hd)
-        sin = m.rope_sin.index_select(0, pos).to(dt).view(1, 1, d.hd)
         da = m.depth_attn
         hk, hv, qkc = self._hk, self._hv, self._qkc
         from ..ops import native
 
+        def lin(x, p, bias=None, out=None):
+            return K.linear_small(x, self.w(p), None if bias is None else bias.data, out=out)
+
         def project(x, slot):
-            kv = self._lin(x, da.kv_weight)
+            if not d.depth_qkv_rms:
+                lin(x, da.kv_weight, out=self._hist[slot].view(B, 2 * d.n))      # [K | V] row, in place
+                return
+            kv = lin(x, da.kv_weight)
             k, v = kv[:, :d.n].view(B, d.qh, d.hd), kv[:, d.n:].view(B, d.qh, d.hd)
-            if d.depth_qkv_rms:
-                k, v = K.fixed_rms_fwd(k, FANIN_GAIN), K.fixed_rms_fwd(v, FANIN_GAIN * d.deepnorm_beta)
-            hk[slot].copy_(k); hv[slot].copy_(v)
+            hk[slot].copy_(K.fixed_rms_fwd(k, FANIN_GAIN)); hv[slot].copy_(K.fixed_rms_fwd(v, FANIN_GAIN * d.deepnorm_beta))
 
         def read(sub):
             mm, _ = K.dread_fwd(d, da.query(sub).float(), hk, hv, sub + 1)
             w_o = self.w(da.w_o_weight)[sub] if da.w_o is None else self.w(da.w_o.weight)
-            return F.linear(mm.view(B, d.n), w_o), mm
+            return K.linear_small(mm.view(B, d.n), w_o), mm
 
         cap = d.branch_rms_cap if (d.branch_rms_cap is not None and m.decode_applies_rms_cap) else None
         is_bos = pos.eq(0)
@@ -263,24 +268,23 @@ class DecodeEngine:
         for bi, blk in enumerate(m.blocks):
             last = bi == d.layers - 1
             sub = 2 * bi
-            qkv = self._lin(h, blk.attn.qkv_weight)
-            qkc[:, 0].copy_(R.apply_rope(qkv[:, :d.n].view(B, d.qh, d.hd), cos, sin))
-            k = R.apply_rope(qkv[:, d.n:d.n + d.kv_dim].view(B, d.kvh, d.hd), cos, sin)
-            self.kc[bi].index_copy_(1, pos, k.unsqueeze(1))
-            self.vc[bi].index_copy_(1, pos, qkv[:, d.n + d.kv_dim:].view(B, d.kvh, d.hd).unsqueeze(1))
+            qkv = lin(h, blk.attn.qkv_weight)
+            # RoPE of Q and K at the device-side position, rotated Q into the attention operand, K / V appended: one launch
+            native.ext().decode_rope_store(qkv, self._rope_cos, self._rope_sin, pos, qkc[:, 0].view(B, d.n), self.kc[bi],
+                                           self.vc[bi], d.qh, d.kvh, d.hd)
             native.ext().decode_attn(qkc[:, 0], self.kc[bi], self.vc[bi], pos, qkc[:, 2], qkc[:, 1], self._attn_ws, B, S,
                                      d.qh, d.kvh, d.hd, self._ns)
-            native.count(2 if self._ns > 1 else 1)
-            attn_out = self._lin(qkc[:, 2].reshape(B, d.n), blk.attn.o.weight)
+            native.count(3 if self._ns > 1 else 2)
+            attn_out = lin(qkc[:, 2].reshape(B, d.n), blk.attn.o.weight)
             skip, _ = read(sub)
             u = K.add_ln_fwd(skip, attn_out, blk.ln_attn.weight.data, blk.ln_attn.bias.data, cap)[0]
             project(u, sub + 1)
             skip2, d_sel = read(sub + 1)
             ffn = blk.ffn
-            wx = F.linear(u, self.wk(ffn.w1_real.weight))
+            wx = K.linear_small(u, self.wk(ffn.w1_real.weight))
             gate_lin = None
             if ffn.gate_proj is not None:
-                gate_lin = F.linear(u, self.wk(ffn.gate_proj.weight)) + self.wk(ffn.gate_proj.bias).to(dt)
+                gate_lin = K.linear_small(u, self.wk(ffn.gate_proj.weight), self.wk(ffn.gate_proj.bias))
             beta_lin = K.imag_fwd(dk, qkc, u, d_sel, self.wk(ffn.w1_imag))
             tria_here = use_tria
             padded = dk is not d
@@ -298,7 +302,7 @@ class DecodeEngine:
             if tria_here:
                 c_planes = core["c"]
                 p_in = None if last else core["p_out"]
-            f = F.linear(core["o"], self.wk(ffn.w2.weight)) + self.w(ffn.w2.bias)
+            f = K.linear_small(core["o"], self.wk(ffn.w2.weight), ffn.w2.bias.data)
             h = K.add_ln_fwd(skip2, f, blk.ln_ffn.weight.data, blk.ln_ffn.bias.data, cap)[0]
             if not last:
                 project(h, sub + 2)

@@ -464,3 +464,50 @@ def test_per_op_switch_routes_to_the_twin(monkeypatch):
     monkeypatch.setenv("LOOM_DISABLE_OPS", "no_such_op")
     with pytest.raises(ValueError):
         kernels.CudaKernels()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 3072, 768), (3, 1536, 768), (8, 768, 3072), (16, 200, 136), (64, 1152, 768)])
+def test_small_batch_linear(M, N, K):
+    """The weight-streaming linear of the decode step (up to 16 rows; more rows take the tensor-core GEMM), with bias,
+    fp32 output and a row-strided output view."""
+    from loomformer_paraplex_b200.ops import kernels
+    ck = kernels.CudaKernels(defer_wgrad=False)
+    torch.manual_seed(9)
+    x, w = bf(M, K), bf(N, K, scale=0.05)
+    bias = torch.randn(N, device="cuda")
+    ref = x.float() @ w.float().t() + bias
+    y = ck.linear_small(x, w, bias)
+    _close(y, ref, 2e-2, "bf16 out")
+    wide = torch.full((M, N + 8), 7.0, device="cuda", dtype=torch.bfloat16)
+    ck.linear_small(x, w, bias, out=wide[:, :N])
+    _close(wide[:, :N], ref, 2e-2, "strided out")
+    assert bool((wide[:, N:] == 7.0).all())
+    if M <= 16:
+        y32 = ck.linear_small(x, w, None, out_dtype=torch.float32)
+        _close(y32, x.float() @ w.float().t(), 2e-3, "fp32 out")
+    kernels.check_status(x.device)
+
+
+@pytest.mark.parametrize("hd,qh,kvh", [(96, 8, 2), (64, 15, 5), (24, 4, 2)])
+def test_decode_rope_store(hd, qh, kvh):
+    """RoPE of one new token's Q / K at a device-side position with the KV-cache append, against the PyTorch statement."""
+    from loomformer_paraplex_b200.ops import native
+    from loomformer_paraplex_b200.ops import reference as R
+    torch.manual_seed(10)
+    B, S, rows = 3, 40, 64
+    n, kv = qh * hd, kvh * hd
+    qkv = bf(B, n + 2 * kv)
+    cos, sin = torch.randn(rows, hd, device="cuda"), torch.randn(rows, hd, device="cuda")
+    kc = torch.zeros(B, S, kvh, hd, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    qkc = torch.zeros(B, 3, qh, hd, device="cuda", dtype=torch.bfloat16)
+    for p in (0, 17, 39):
+        pos = torch.tensor([p], device="cuda", dtype=torch.long)
+        native.ext().decode_rope_store(qkv, cos, sin, pos, qkc[:, 0].view(B, n), kc, vc, qh, kvh, hd)
+        c, s_ = cos[p].view(1, 1, hd), sin[p].view(1, 1, hd)
+        q_ref = R.apply_rope(qkv[:, :n].float().view(B, qh, hd), c, s_)
+        k_ref = R.apply_rope(qkv[:, n:n + kv].float().view(B, kvh, hd), c, s_)
+        _close(qkc[:, 0], q_ref, 2e-2, "q")
+        _close(kc[:, p], k_ref, 2e-2, "k")
+        assert torch.equal(vc[:, p].reshape(B, kv), qkv[:, n + kv:])
+    assert float(qkc[:, 1:].abs().sum()) == 0.0
