@@ -2,6 +2,8 @@
 #include <torch/extension.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
+#include <cstring>
+#include <tuple>
 #include <vector>
 #include "loom_c_api.h"
 
@@ -206,6 +208,86 @@ void skinny_linear(torch::Tensor x, torch::Tensor w, c10::optional<torch::Tensor
   int rc = loom_skinny_linear(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), b, y.data_ptr(), y.stride(0),
                               y.scalar_type() == torch::kFloat32, (int)x.size(0), (int)w.size(0), (int)x.size(1), cur_stream());
   TORCH_CHECK(rc == 0, "loom_skinny_linear failed: ", rc);
+}
+
+// segs: list of (pieces, w, bias or None, y): pieces = list of [M, len] bf16 views (unit inner stride), w [N, K] bf16 rows,
+// y [M, N] bf16 or fp32 view
+void skinny_multi(std::vector<std::tuple<std::vector<torch::Tensor>, torch::Tensor, c10::optional<torch::Tensor>, torch::Tensor>> segs,
+                  bool weights_static) {
+  TORCH_CHECK(!segs.empty() && (int)segs.size() <= LOOM_SKINNY_MAX_SEG, "skinny_multi: 1..", LOOM_SKINNY_MAX_SEG, " segments");
+  LoomSkinnyArgs a;
+  memset(&a, 0, sizeof(a));
+  a.nseg = (int)segs.size();
+  a.weights_static = weights_static ? 1 : 0;
+  const torch::Tensor& y0 = std::get<3>(segs[0]);
+  const c10::cuda::CUDAGuard guard(y0.device());
+  a.M = (int)y0.size(0);
+  for (int i = 0; i < a.nseg; ++i) {
+    const auto& pieces = std::get<0>(segs[i]);
+    const torch::Tensor& w = std::get<1>(segs[i]);
+    const auto& bias = std::get<2>(segs[i]);
+    const torch::Tensor& y = std::get<3>(segs[i]);
+    LoomSkinnySeg& sg = a.seg[i];
+    TORCH_CHECK(!pieces.empty() && (int)pieces.size() <= LOOM_SKINNY_MAX_PIECE, "skinny_multi: 1..", LOOM_SKINNY_MAX_PIECE, " pieces");
+    TORCH_CHECK(w.dim() == 2 && w.stride(1) == 1 && w.scalar_type() == torch::kBFloat16, "skinny_multi: bf16 weight rows");
+    TORCH_CHECK(y.dim() == 2 && y.stride(1) == 1 && y.size(0) == a.M && y.size(1) == w.size(0) &&
+                (y.scalar_type() == torch::kBFloat16 || y.scalar_type() == torch::kFloat32), "skinny_multi: output view");
+    int k = 0;
+    for (size_t p = 0; p < pieces.size(); ++p) {
+      const torch::Tensor& x = pieces[p];
+      TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.size(0) == a.M && x.scalar_type() == torch::kBFloat16,
+                  "skinny_multi: bf16 [M, len] input pieces");
+      sg.piece[p].x = x.data_ptr(); sg.piece[p].ld = a.M > 1 ? x.stride(0) : 0; sg.piece[p].len = (int)x.size(1);
+      k += (int)x.size(1);
+    }
+    TORCH_CHECK(k == w.size(1), "skinny_multi: pieces do not add up to the weight's width");
+    sg.npiece = (int)pieces.size();
+    sg.w = w.data_ptr(); sg.ldw = w.stride(0);
+    sg.bias = nullptr;
+    if (bias.has_value()) { TORCH_CHECK(bias->numel() == w.size(0), "skinny_multi: bias length"); sg.bias = fptr(*bias); }
+    sg.y = y.data_ptr(); sg.ldy = y.stride(0);
+    sg.N = (int)w.size(0); sg.K = k; sg.out_fp32 = y.scalar_type() == torch::kFloat32 ? 1 : 0;
+  }
+  int rc = loom_skinny_multi(&a, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_skinny_multi failed: ", rc);
+}
+
+void decode_step_flags(torch::Tensor pos, torch::Tensor tok, torch::Tensor pending, torch::Tensor have_carry, torch::Tensor fire,
+                       torch::Tensor reset, torch::Tensor row_reset, torch::Tensor seed_valid, int64_t window, int64_t seq_len,
+                       bool hard_enabled, int64_t carry_token, bool temporal) {
+  const c10::cuda::CUDAGuard guard(pos.device());
+  const int64_t B = tok.numel();
+  TORCH_CHECK(pos.scalar_type() == torch::kInt64 && tok.scalar_type() == torch::kInt64 && tok.is_contiguous(), "decode_step_flags: int64 position and tokens");
+  for (const torch::Tensor* t : {&pending, &fire, &reset, &row_reset, &seed_valid})
+    TORCH_CHECK(t->element_size() == 1 && t->numel() == B && t->is_contiguous(), "decode_step_flags: [B] byte flags");
+  TORCH_CHECK(have_carry.element_size() == 1 && have_carry.numel() == 1, "decode_step_flags: have_carry");
+  int rc = loom_decode_step_flags((const long long*)pos.data_ptr<int64_t>(), (const long long*)tok.data_ptr<int64_t>(), pending.data_ptr(),
+                                  have_carry.data_ptr(), fire.data_ptr(), reset.data_ptr(), row_reset.data_ptr(), seed_valid.data_ptr(),
+                                  (int)B, (long long)window, (long long)seq_len, hard_enabled ? 1 : 0, (long long)carry_token,
+                                  temporal ? 1 : 0, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_decode_step_flags failed: ", rc);
+}
+
+void decode_ca_append(torch::Tensor newk, torch::Tensor newv, torch::Tensor fire, torch::Tensor ca_k, torch::Tensor ca_v,
+                      torch::Tensor ca_valid, torch::Tensor ca_len, torch::Tensor allowed, torch::Tensor any_out, torch::Tensor pending,
+                      torch::Tensor have_carry) {
+  const c10::cuda::CUDAGuard guard(newk.device());
+  TORCH_CHECK(ca_k.dim() == 3 && ca_k.is_contiguous() && ca_v.is_contiguous() && ca_v.sizes() == ca_k.sizes() &&
+              ca_k.scalar_type() == torch::kBFloat16 && ca_v.scalar_type() == torch::kBFloat16, "decode_ca_append: bf16 [B, cap, N] stores");
+  const int64_t B = ca_k.size(0), cap = ca_k.size(1), N = ca_k.size(2);
+  TORCH_CHECK(newk.dim() == 2 && newk.size(0) == B && newk.size(1) == N && newk.stride(1) == 1 && newv.sizes() == newk.sizes() &&
+              newv.stride(1) == 1 && newv.stride(0) == newk.stride(0) && newk.scalar_type() == torch::kBFloat16 &&
+              newv.scalar_type() == torch::kBFloat16, "decode_ca_append: new rows");
+  TORCH_CHECK(ca_valid.element_size() == 1 && ca_valid.numel() == B * cap && ca_valid.is_contiguous() && allowed.element_size() == 1 &&
+              allowed.numel() == B * cap && allowed.is_contiguous(), "decode_ca_append: [B, cap] byte masks");
+  TORCH_CHECK(fire.element_size() == 1 && fire.numel() == B && pending.element_size() == 1 && pending.numel() == B &&
+              have_carry.element_size() == 1 && have_carry.numel() == 1, "decode_ca_append: flags");
+  TORCH_CHECK(ca_len.scalar_type() == torch::kInt64 && any_out.scalar_type() == torch::kInt64, "decode_ca_append: int64 counters");
+  int rc = loom_decode_ca_append(newk.data_ptr(), newv.data_ptr(), newk.stride(0), fire.data_ptr(), ca_k.data_ptr(), ca_v.data_ptr(),
+                                 ca_valid.data_ptr(), (const long long*)ca_len.data_ptr<int64_t>(), allowed.data_ptr(),
+                                 (long long*)any_out.data_ptr<int64_t>(), pending.data_ptr(), have_carry.data_ptr(), (int)B, (int)cap,
+                                 (int)N, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_decode_ca_append failed: ", rc);
 }
 
 void decode_rope_store(torch::Tensor qkv, torch::Tensor cos_tab, torch::Tensor sin_tab, torch::Tensor pos, torch::Tensor q_out,
@@ -464,6 +546,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("dread", &dread, "depth-attention read (forward / backward)");
   m.def("decode_attn", &decode_attn, "KV-cache attention for one new token per sequence, dual context, split over positions");
   m.def("skinny_linear", &skinny_linear, "y = x W^T (+ bias) for up to 16 rows: weights streamed once, output may be a strided view");
+  m.def("skinny_multi", &skinny_multi, "several small-batch products (own inputs, weights, outputs) in one launch");
+  m.def("decode_step_flags", &decode_step_flags, "fire / reset / first-position / seed flags of one decode step");
+  m.def("decode_ca_append", &decode_ca_append, "boundary-key append and visibility mask of one decode step");
   m.def("decode_rope_store", &decode_rope_store, "RoPE of the new token's Q / K at the device-side position + KV cache append");
   m.def("slot_pool", &slot_pool, "softmax pooling of boundary carriers over neurons (forward / backward)");
   m.def("cross_attn", &cross_attn, "token rows attending to the boundary keys (forward / backward)");

@@ -188,6 +188,32 @@ int loom_decode_rope_store(const void* qkv, long long ld_qkv, const float* cos_t
                            const long long* pos, void* q_out, long long ld_q, void* kc, void* vc, int B, int S,
                            int table_rows, int QH, int KVH, int HD, cudaStream_t st);
 
+// several such products in one launch; segment i owns blocks [block0_i, block0_{i+1}) of the grid (filled in by the
+// call).  The input rows of a segment are the concatenation of its pieces (each `len` elements at row pitch `ld`).
+#define LOOM_SKINNY_MAX_SEG 12
+#define LOOM_SKINNY_MAX_PIECE 5
+typedef struct { const void* x; long long ld; int len; int pad_; } LoomSkinnyPiece;
+typedef struct {
+  LoomSkinnyPiece piece[LOOM_SKINNY_MAX_PIECE];
+  const void* w; const float* bias; void* y;
+  long long ldw, ldy;
+  int npiece, N, K, out_fp32, block0, pad_;
+} LoomSkinnySeg;
+// weights_static: no kernel earlier in the stream writes the weights or biases, so they may be fetched before the
+// previous kernel has finished
+typedef struct { LoomSkinnySeg seg[LOOM_SKINNY_MAX_SEG]; int nseg, M, weights_static, pad_; } LoomSkinnyArgs;
+int loom_skinny_multi(LoomSkinnyArgs* a, cudaStream_t st);
+// booleans of one decode step (all [B] bytes) from the device-side position, the incoming tokens and the flags of the
+// previous step; carry_token < 0: no carry token
+int loom_decode_step_flags(const long long* pos, const long long* tok, const void* pending, const void* have_carry,
+                           void* fire, void* reset, void* row_reset, void* seed_valid, int B, long long window,
+                           long long seq_len, int hard_enabled, long long carry_token, int temporal, cudaStream_t st);
+// boundary-key append of one decode step: ca_k / ca_v [B, cap, N] bf16, ca_valid / allowed [B, cap] bytes, *ca_len the
+// slot count before the append (the caller adds *any_out afterwards)
+int loom_decode_ca_append(const void* newk, const void* newv, long long ld_new, const void* fire, void* ca_k, void* ca_v,
+                          void* ca_valid, const long long* ca_len, void* allowed, long long* any_out, void* pending,
+                          void* have_carry, int B, int cap, int N, cudaStream_t st);
+
 // ---- fused gradient reduce-scatter + AdamW + parameter all-gather over peer memory (comm.cu) ----
 typedef struct {
   int W, rank;

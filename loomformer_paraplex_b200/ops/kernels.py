@@ -266,6 +266,28 @@ class CudaKernels(TorchKernels):
         native.count()
         return y
 
+    def linear_multi(self, segs, static_weights=False):
+        """Several small-batch products in one launch (``csrc/decode_step.cu``, up to 16 rows, 12 segments per launch);
+        more rows fall back to one GEMM per segment.  ``static_weights``: nothing earlier in the stream writes the
+        weights or biases (an inference engine's copies), so the kernel may fetch them while its predecessor runs."""
+        M = segs[0][3].shape[0]
+
+        def piece_ok(t):
+            return (t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1 and t.shape[1] % 8 == 0
+                    and (M == 1 or t.stride(0) % 8 == 0) and t.data_ptr() % 16 == 0)
+
+        ok = M <= 16 and all(all(piece_ok(x) for x in pieces) and piece_ok(w) and out.stride(1) == 1
+                             and out.dtype in (torch.bfloat16, torch.float32) for pieces, w, _, out in segs)
+        if not ok:
+            for pieces, w, bias, out in segs:
+                x = pieces[0] if len(pieces) == 1 else torch.cat(list(pieces), -1)
+                self.linear_small(x.contiguous(), w, bias, out=out)
+            return
+        packed = [(list(pieces), w, None if bias is None else _f32c(bias), out) for pieces, w, bias, out in segs]
+        for i in range(0, len(packed), 12):
+            native.ext().skinny_multi(packed[i:i + 12], bool(static_weights))
+            native.count()
+
     def linear_dgrad(self, dy, w, out=None, accumulate=False):
         """``dy @ w``; with ``out`` the product is written (or, with ``accumulate``, added) into that bf16 buffer by
         the GEMM's epilogue, which saves the separate add that sums gradient branches."""
@@ -576,18 +598,21 @@ class _ElementwiseMixin:
         return x_real.dtype == torch.bfloat16 and d.hidden % 2 == 0 and d.activation == "pvpowlu"
 
     def ffn_core_fwd(self, d, x_real, p_in, alpha_gate, b_real, gate_lin, beta_lin, b_imag, w_trace, trace_in,
-                     reset, anchor, c_prev, seed, seed_valid, gate_w, axis, tria_alpha, B):
+                     reset, anchor, c_prev, seed, seed_valid, gate_w, axis, tria_alpha, B, trace_out=None, bsq=None):
         if not self._core_ok(d, x_real):
             self.fallbacks["ffn_core_fwd"] += 1
             return super().ffn_core_fwd(d, x_real, p_in, alpha_gate, b_real, gate_lin, beta_lin, b_imag, w_trace,
-                                        trace_in, reset, anchor, c_prev, seed, seed_valid, gate_w, axis, tria_alpha, B)
+                                        trace_in, reset, anchor, c_prev, seed, seed_valid, gate_w, axis, tria_alpha, B,
+                                        trace_out, bsq)
         M, H = x_real.shape
         dev = x_real.device
         o = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
         c = torch.empty(9, M, H, dtype=torch.bfloat16, device=dev) if axis is not None else None
         p_out = torch.empty(M, H, dtype=torch.bfloat16, device=dev) if (axis is not None and gate_w is not None) else None
-        trace_out = torch.empty(B, H, dtype=torch.float32, device=dev)
-        bsq = self.zeros(1, device=dev)
+        if trace_out is None:
+            trace_out = torch.empty(B, H, dtype=torch.float32, device=dev)
+        if bsq is None:
+            bsq = self.zeros(1, device=dev)
         native.ext().ffn_core(
             False, B, M // B, H, -1 if axis is None else axis, bool(d.phase_secant), d.powlu_m, tria_alpha, d.phase_floor,
             _opt(alpha_gate if p_in is not None else None, lambda t: _f32c(t).reshape(1)), None,

@@ -50,6 +50,13 @@ class TorchKernels:
         out.copy_(y)
         return out
 
+    def linear_multi(self, segs, static_weights=False):
+        """Several independent ``out = cat(pieces, -1) @ w^T (+ bias)`` products that wait for the same producers;
+        ``segs``: ``(pieces, w, bias or None, out)`` with ``out`` a ``[M, N]`` view that is written in place."""
+        for pieces, w, bias, out in segs:
+            x = pieces[0] if len(pieces) == 1 else torch.cat(list(pieces), -1)
+            out.copy_(F.linear(x.float(), w.float(), None if bias is None else bias.float()))
+
     def linear_dgrad(self, dy, w, out=None, accumulate=False):
         r = dy @ w.to(dy.dtype)
         if out is None:
@@ -298,8 +305,10 @@ class TorchKernels:
 
     # ------------------------------------------------------------------ paraplex core + tria step
     def ffn_core_fwd(self, d, x_real, p_in, alpha_gate, b_real, gate_lin, beta_lin, b_imag, w_trace, trace_in,
-                     reset, anchor, c_prev, seed, seed_valid, gate_w, axis, tria_alpha, B):
+                     reset, anchor, c_prev, seed, seed_valid, gate_w, axis, tria_alpha, B, trace_out=None, bsq=None):
         """Gate, bias, phase, trace, softplus, PvPowLU and the Tria depth step in one pass.
+        ``trace_out`` / ``bsq``: caller-owned fp32 buffers for the new trace ``[B,H]`` (not ``trace_in``) and the
+        squared-phase sum (inference paths that run every token pass persistent ones).
 
         x_real/gate_lin/beta_lin: [M,H] (gate_lin None = self-referential gate); p_in [M,H] or None;
         trace_in [B,H] or None; reset [M] bool or None; c_prev [M,H,9] or None; seed [B,H,9].
@@ -323,6 +332,9 @@ class TorchKernels:
                 seed=None if seed is None else seed.view(B, H, 3, 3), seed_valid=seed_valid, gate_w=gate_w)
             out["c"] = c.reshape(M, H, 9)
             out["p_out"] = None if p is None else p.reshape(M, H)
+        if trace_out is not None:
+            trace_out.copy_(out["trace_out"])
+            out["trace_out"] = trace_out
         return out
 
     def ffn_core_bwd(self, d, saved, do, dc, dp_out, dtrace_out):

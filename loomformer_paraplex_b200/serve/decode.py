@@ -56,8 +56,11 @@ class DecodeEngine:
         self.carry = z(B, d.hidden, 3, 3, dtype=torch.float32)
         self.have_carry = z(1, dtype=torch.bool)
         self.pending = z(B, dtype=torch.bool)
-        self.ca_k, self.ca_v = z(B, S, d.n), z(B, S, d.n)
-        self.ca_valid = z(B, S, dtype=torch.bool)
+        # boundary keys: one per hard window boundary; any token can fire when the model has a carry token
+        W = max(1, int(model.tria_window or 1))
+        self.ca_cap = S if model.carry_token_id is not None else S // W + 1
+        self.ca_k, self.ca_v = z(B, self.ca_cap, d.n), z(B, self.ca_cap, d.n)
+        self.ca_valid = z(B, self.ca_cap, dtype=torch.bool)
         self.ca_len = z(1, dtype=torch.long)
         self.pos = z(1, dtype=torch.long)
         self.tok_in = z(B, dtype=torch.long)
@@ -71,9 +74,10 @@ class DecodeEngine:
             from ..ops import native
             if native.available():
                 self._native_attn = True
-                self._ns = max(1, min(16, -(-296 // (B * d.kvh))))
-                n_ws = B * d.kvh * self._ns * (2 * d.group + 2 * d.group * d.hd)
-                self._attn_ws = torch.empty(max(1, n_ws), dtype=torch.float32, device=dev)
+                # position slices per (sequence, KV head): about eight blocks per SM, at least 32 positions each
+                self._ns = max(1, min(32, -(-1184 // (B * d.kvh)), -(-S // 32)))
+                n_ws = B * d.kvh * self._ns * (2 * d.group + 2 * d.group * d.hd) + B * d.kvh
+                self._attn_ws = torch.zeros(n_ws, dtype=torch.float32, device=dev)     # partial states | ticket counters
         # fused kernels of the training plan reused at one token per sequence (fewer, larger launches per layer).  A
         # hidden sector that is not a multiple of 8 neurons wide (a SmolLM2 transplant has 171 per head) is padded
         # with inert neurons inside the FFN part of the step, exactly as the training plan does; the engine's own
@@ -93,6 +97,12 @@ class DecodeEngine:
             self._qkc = z(B, 3, d.qh, d.hd)
             self._rope_cos = model.rope_cos.detach().float().reshape(-1, d.hd).contiguous()
             self._rope_sin = model.rope_sin.detach().float().reshape(-1, d.hd).contiguous()
+            # per-step flags, scratch that every step overwrites
+            self._fire, self._reset, self._row_reset, self._seed_valid = (z(B, dtype=torch.bool) for _ in range(4))
+            self._allowed = z(B, self.ca_cap, dtype=torch.uint8)
+            self._any = z(1, dtype=torch.long)
+            self._trace_new = z(L, B, self._dk.hidden, dtype=torch.float32)
+            self._bsq = z(1, dtype=torch.float32)
         self.refresh_weights()
 
     # ------------------------------------------------------------------ weights in the compute dtype
@@ -109,6 +119,24 @@ class DecodeEngine:
                     src = q.detach().to(self.dt if q.dim() == 2 else torch.float32)
                     self._wpad[id(q)] = self._pad(src, 0)
                 self._wpad[id(f.w2.weight)] = self._pad(f.w2.weight.detach().to(self.dt), 1)
+        if getattr(self, "_fused", False):
+            # parameter-derived constants of the step (softmaxes, tanh gains, normalised depth queries): evaluated once
+            # per weight refresh instead of once per token
+            m, da = self.m, self.m.depth_attn
+            c = {"query": [da.query(sub).detach().float().contiguous() for sub in range(2 * self.d.layers)],
+                 "gate_w": [None if getattr(b.ffn, "gate_selector", None) is None
+                            else b.ffn.gate_selector.weights().detach().float().contiguous() for b in m.blocks],
+                 "alpha": [None if b.ffn.identity_gate is None else b.ffn.identity_gate.alpha().detach().float().reshape(1)
+                           for b in m.blocks]}
+            if self.d.tria:
+                agg, fca = m.tria_agg, m.tria_final_ca
+                c["score_w"] = agg.score_w().detach().float().contiguous()
+                c["proj_wT"] = agg.reader.proj.weight.detach().float().t().contiguous()
+                c["proj_b"] = agg.reader.proj.bias.detach().float()
+                c["up_wT"] = agg.up.weight.detach().float().t().contiguous()
+                c["up_b"] = agg.up.bias.detach().float()
+                c["gamma"] = float(fca.gamma().detach())
+            self._const = c
         self._graph = None
 
     def _pad(self, t: torch.Tensor, axis: int) -> torch.Tensor:
@@ -146,6 +174,15 @@ class DecodeEngine:
 
     # ------------------------------------------------------------------ state management
     def reset(self) -> None:
+        if self.m.carry_token_id is not None and self.ca_cap < self.S:
+            # the model was given a carry token after this engine was built: any token may now append a boundary key
+            z = lambda *shape, dtype=self.dt: torch.zeros(*shape, dtype=dtype, device=self.dev)
+            self.ca_cap = self.S
+            self.ca_k, self.ca_v = z(self.B, self.S, self.d.n), z(self.B, self.S, self.d.n)
+            self.ca_valid = z(self.B, self.S, dtype=torch.bool)
+            if self._fused:
+                self._allowed = z(self.B, self.S, dtype=torch.uint8)
+            self._graph = None
         for t in (self.kc, self.vc, self.trace, self.carry, self.ca_k, self.ca_v):
             t.zero_()
         self.have_carry.zero_(); self.pending.zero_(); self.ca_valid.zero_(); self.ca_len.zero_(); self.pos.zero_()
@@ -231,85 +268,148 @@ class DecodeEngine:
 
     # ------------------------------------------------------------------ one token with the fused kernels
     def _step_fused(self) -> None:
-        """Same arithmetic as :meth:`_step_composed` with the training plan's kernels at M = batch rows: depth reads,
-        residual-add + LayerNorm, the segmented sector GEMM, and the fused Paraplex core (gate, phase, trace, softplus,
-        PvPowLU, Tria build / compose / seed / gate readout) are one launch each."""
+        """Same arithmetic as :meth:`_step_composed` with the training plan's kernels at M = batch rows.  The step is
+        bound by the number of dependent launches, so everything that waits for the same producer leaves in one launch:
+        the linear layers of a layer are four multi-segment launches (QKV + depth K/V of the incoming stream; attention
+        output + first depth readout; real / gate projections + depth K/V of the normalised stream; the per-head
+        imaginary projection + second depth readout) and the down projection, RoPE and the cache append are one kernel,
+        attention (with its merge) one, the Paraplex core with the Tria step one."""
         m, d, K, dk = self.m, self.d, self._K, self._dk
-        B, S, dt = self.B, self.S, self.dt
-        pos = self.pos
+        B, S = self.B, self.S
+        pos, cst = self.pos, self._const
+        from ..ops import native
+        ext = native.ext()
+        bf = dict(dtype=self.dt, device=self.dev)
+        ext.decode_step_flags(pos, self.tok_in, self.pending, self.have_carry, self._fire, self._reset, self._row_reset,
+                              self._seed_valid, int(m.tria_window or 0), int(d.seq_len), bool(m.tria_hard_fire_enabled),
+                              -1 if m.carry_token_id is None else int(m.carry_token_id), bool(d.tria_temporal))
+        native.count()
         h = self.w(m.emb.weight)[self.tok_in]
         da = m.depth_attn
         hk, hv, qkc = self._hk, self._hv, self._qkc
-        from ..ops import native
+        small = B <= 16
+        after = []
 
-        def lin(x, p, bias=None, out=None):
-            return K.linear_small(x, self.w(p), None if bias is None else bias.data, out=out)
-
-        def project(x, slot):
+        def project_seg(x, slot):
+            """Segment that projects ``x`` into history slot ``slot`` ([K | V] row, written in place)."""
             if not d.depth_qkv_rms:
-                lin(x, da.kv_weight, out=self._hist[slot].view(B, 2 * d.n))      # [K | V] row, in place
-                return
-            kv = lin(x, da.kv_weight)
-            k, v = kv[:, :d.n].view(B, d.qh, d.hd), kv[:, d.n:].view(B, d.qh, d.hd)
-            hk[slot].copy_(K.fixed_rms_fwd(k, FANIN_GAIN)); hv[slot].copy_(K.fixed_rms_fwd(v, FANIN_GAIN * d.deepnorm_beta))
+                return ([x], self.w(da.kv_weight), None, self._hist[slot].view(B, 2 * d.n))
+            kv = torch.empty(B, 2 * d.n, **bf)
 
-        def read(sub):
-            mm, _ = K.dread_fwd(d, da.query(sub).float(), hk, hv, sub + 1)
-            w_o = self.w(da.w_o_weight)[sub] if da.w_o is None else self.w(da.w_o.weight)
-            return K.linear_small(mm.view(B, d.n), w_o), mm
+            def norm():
+                k, v = kv[:, :d.n].view(B, d.qh, d.hd), kv[:, d.n:].view(B, d.qh, d.hd)
+                hk[slot].copy_(K.fixed_rms_fwd(k, FANIN_GAIN)); hv[slot].copy_(K.fixed_rms_fwd(v, FANIN_GAIN * d.deepnorm_beta))
+            after.append(norm)
+            return ([x], self.w(da.kv_weight), None, kv)
+
+        def multi(segs):
+            K.linear_multi(segs, static_weights=True)
+            while after:
+                after.pop()()
+
+        def w_o(sub):
+            return self.w(da.w_o_weight)[sub] if da.w_o is None else self.w(da.w_o.weight)
 
         cap = d.branch_rms_cap if (d.branch_rms_cap is not None and m.decode_applies_rms_cap) else None
-        is_bos = pos.eq(0)
-        row_reset = is_bos.expand(B).contiguous()
-        seed_valid = self.pending & ~is_bos & self.have_carry
         use_tria = d.tria
+        padded = dk is not d
+        vec = (lambda q: self.wk(q)) if padded else (lambda q: q.data)
         c_planes, p_in = None, None
-        project(h, 0)
         for bi, blk in enumerate(m.blocks):
             last = bi == d.layers - 1
             sub = 2 * bi
-            qkv = lin(h, blk.attn.qkv_weight)
-            # RoPE of Q and K at the device-side position, rotated Q into the attention operand, K / V appended: one launch
-            native.ext().decode_rope_store(qkv, self._rope_cos, self._rope_sin, pos, qkc[:, 0].view(B, d.n), self.kc[bi],
-                                           self.vc[bi], d.qh, d.kvh, d.hd)
-            native.ext().decode_attn(qkc[:, 0], self.kc[bi], self.vc[bi], pos, qkc[:, 2], qkc[:, 1], self._attn_ws, B, S,
-                                     d.qh, d.kvh, d.hd, self._ns)
-            native.count(3 if self._ns > 1 else 2)
-            attn_out = lin(qkc[:, 2].reshape(B, d.n), blk.attn.o.weight)
-            skip, _ = read(sub)
-            u = K.add_ln_fwd(skip, attn_out, blk.ln_attn.weight.data, blk.ln_attn.bias.data, cap)[0]
-            project(u, sub + 1)
-            skip2, d_sel = read(sub + 1)
             ffn = blk.ffn
-            wx = K.linear_small(u, self.wk(ffn.w1_real.weight))
+            qkv = torch.empty(B, d.n + 2 * d.kv_dim, **bf)
+            multi([([h], self.w(blk.attn.qkv_weight), None, qkv), project_seg(h, sub)])
+            # RoPE of Q and K at the device-side position, rotated Q into the attention operand, K / V appended
+            ext.decode_rope_store(qkv, self._rope_cos, self._rope_sin, pos, qkc[:, 0].view(B, d.n), self.kc[bi],
+                                  self.vc[bi], d.qh, d.kvh, d.hd)
+            ext.decode_attn(qkc[:, 0], self.kc[bi], self.vc[bi], pos, qkc[:, 2], qkc[:, 1], self._attn_ws, B, S,
+                            d.qh, d.kvh, d.hd, self._ns)
+            native.count(2)
+            mm_a, _ = K.dread_fwd(d, cst["query"][sub], hk, hv, sub + 1)
+            attn_out, skip = torch.empty(B, d.n, **bf), torch.empty(B, d.n, **bf)
+            multi([([qkc[:, 2].reshape(B, d.n)], self.w(blk.attn.o.weight), None, attn_out),
+                   ([mm_a.view(B, d.n)], w_o(sub), None, skip)])
+            u = K.add_ln_fwd(skip, attn_out, blk.ln_attn.weight.data, blk.ln_attn.bias.data, cap)[0]
+            wx = torch.empty(B, dk.hidden, **bf)
+            segs = [project_seg(u, sub + 1), ([u], self.wk(ffn.w1_real.weight), None, wx)]
             gate_lin = None
             if ffn.gate_proj is not None:
-                gate_lin = K.linear_small(u, self.wk(ffn.gate_proj.weight), self.wk(ffn.gate_proj.bias))
-            beta_lin = K.imag_fwd(dk, qkc, u, d_sel, self.wk(ffn.w1_imag))
+                gate_lin = torch.empty(B, dk.hidden, **bf)
+                segs.append(([u], self.wk(ffn.gate_proj.weight), self.wk(ffn.gate_proj.bias), gate_lin))
+            multi(segs)
+            d_sel, _ = K.dread_fwd(d, cst["query"][sub + 1], hk, hv, sub + 2)
+            skip2 = torch.empty(B, d.n, **bf)
+            read2 = ([d_sel.view(B, d.n)], w_o(sub + 1), None, skip2)
+            if small:
+                # the per-head operand [q | k-context | context | u | depth read] of the imaginary projection is gathered
+                # from its pieces by the kernel; one segment per head
+                beta_lin = torch.empty(B, dk.hidden, **bf)
+                w3 = self.wk(ffn.w1_imag).view(d.qh, dk.hpq, d.imag_in)
+                b3 = beta_lin.view(B, d.qh, dk.hpq)
+                segs = [read2]
+                for g in range(d.qh):
+                    if d.open_sectors:
+                        pieces = [qkc[:, 0, g], qkc[:, 1].reshape(B, d.n), qkc[:, 2].reshape(B, d.n), u, d_sel.view(B, d.n)]
+                    else:
+                        pieces = [qkc[:, 0, g], qkc[:, 1, g], qkc[:, 2, g], u, d_sel[:, g]]
+                    segs.append((pieces, w3[g], None, b3[:, g]))
+                multi(segs)
+            else:
+                multi([read2])
+                beta_lin = K.imag_fwd(dk, qkc, u, d_sel, self.wk(ffn.w1_imag))
             tria_here = use_tria
-            padded = dk is not d
-            vec = (lambda q: self.wk(q)) if padded else (lambda q: q.data)
             core = K.ffn_core_fwd(
                 dk, wx, p_in if ffn.identity_gate is not None else None,
-                ffn.identity_gate.alpha() if ffn.identity_gate is not None else None, vec(ffn.w1_real.bias), gate_lin, beta_lin,
-                vec(ffn.w1_imag_bias), vec(ffn.w1_imag_trace), self._pad(self.trace[bi], 1), row_reset, None,
+                cst["alpha"][bi], vec(ffn.w1_real.bias), gate_lin, beta_lin,
+                vec(ffn.w1_imag_bias), vec(ffn.w1_imag_trace), self._pad(self.trace[bi], 1), self._row_reset, None,
                 c_planes if bi > 0 else None,
                 self._pad(self.carry.view(B, d.hidden, 9), 1) if (tria_here and bi == 0) else None,
-                seed_valid if (tria_here and bi == 0) else None,
-                ffn.gate_selector.weights().float() if (tria_here and not last) else None,
-                (bi % 3) if tria_here else None, m.tria_alpha if tria_here else 0.0, B)
-            self.trace[bi].copy_(self._unpad(core["trace_out"], 1))
+                self._seed_valid if (tria_here and bi == 0) else None,
+                cst["gate_w"][bi] if (tria_here and not last) else None,
+                (bi % 3) if tria_here else None, m.tria_alpha if tria_here else 0.0, B,
+                trace_out=self._trace_new[bi], bsq=self._bsq)
             if tria_here:
                 c_planes = core["c"]
                 p_in = None if last else core["p_out"]
-            f = K.linear_small(core["o"], self.wk(ffn.w2.weight), ffn.w2.bias.data)
+            f = torch.empty(B, d.n, **bf)
+            multi([([core["o"]], self.wk(ffn.w2.weight), ffn.w2.bias.data, f)])
             h = K.add_ln_fwd(skip2, f, blk.ln_ffn.weight.data, blk.ln_ffn.bias.data, cap)[0]
-            if not last:
-                project(h, sub + 2)
-        carry_c = None
-        if use_tria:
-            carry_c = self._unpad(c_planes.float().permute(1, 2, 0), 1).reshape(B, d.hidden, 3, 3)
-        self._finish_step(h, carry_c, is_bos)
+        self.trace.copy_(self._unpad(self._trace_new, 2))
+        self._finish_fused(h, c_planes if use_tria else None)
+
+    def _finish_fused(self, h, c_planes) -> None:
+        """Temporal endpoint, boundary-key append, final cross attention, head: the training plan's kernels at one
+        token per sequence (``temporal_fwd`` at a chunk of one token, the slot pool, the masked cross attention)."""
+        m, d, K, dk = self.m, self.d, self._K, self._dk
+        B, cst = self.B, self._const
+        from ..ops import native
+        ext = native.ext()
+        bf = dict(dtype=self.dt, device=self.dev)
+        if c_planes is not None:
+            state = self._pad(self.carry.view(B, d.hidden, 9), 1)
+            doc, _ = K.temporal_fwd(c_planes, B, 1, dk.hidden, self._reset.view(B, 1), state, self._fire,
+                                    float(m.d_polarm_beta))
+            doc = self._unpad(doc, 1)                                              # [B,H,9] fp32
+            self.carry.copy_(doc.reshape(B, d.hidden, 3, 3))
+            pooled = K.slot_pool_fwd(self.carry.view(B, 1, d.hidden, 9), cst["score_w"])   # [B,1,9]
+            z = torch.addmm(cst["proj_b"], pooled.view(B, 9), cst["proj_wT"])
+            a_t = torch.addmm(cst["up_b"], z, cst["up_wT"]).to(self.dt)             # [B,N]
+            fca = m.tria_final_ca
+            newk, newv, qv = (torch.empty(B, d.n, **bf) for _ in range(3))
+            K.linear_multi([([a_t], self.w(fca.w_qk.weight), None, newk), ([a_t], self.w(fca.w_v.weight), None, newv),
+                            ([h], self.w(fca.w_qk.weight), None, qv)], static_weights=True)
+            ext.decode_ca_append(newk, newv, self._fire, self.ca_k, self.ca_v, self.ca_valid, self.ca_len, self._allowed,
+                                 self._any, self.pending, self.have_carry)
+            native.count()
+            self.ca_len.add_(self._any)
+            out = K.cross_attn_fwd(qv.view(B, 1, d.n), self.ca_k, self.ca_v, self._allowed.view(B, 1, self.ca_cap), fca.scale)
+            h = torch.add(h, out.view(B, d.n), alpha=cst["gamma"])
+        hn = K.rms_norm_fwd(h, m.ln_final.weight.data) if m.ln_final is not None else h
+        K.linear_small(hn, self.w(m.head.weight), None, out=self.logits)
+        self.next_tok.copy_(self.logits.argmax(-1))
+        self.pos.add_(1)
 
     def _step_composed(self) -> None:
         m, d = self.m, self.d
@@ -435,7 +535,7 @@ class DecodeEngine:
             fca, agg = m.tria_final_ca, m.tria_agg
             a_t = agg(doc.unsqueeze(1)).to(dt)[:, 0]                                   # [B,N]
             any_fire = fire.any()
-            slot = self.ca_len.clamp(max=S - 1)
+            slot = self.ca_len.clamp(max=self.ca_cap - 1)
             newk, newv = self._lin(a_t, fca.w_qk.weight), self._lin(a_t, fca.w_v.weight)
             oldk, oldv = self.ca_k.index_select(1, slot), self.ca_v.index_select(1, slot)
             oldm = self.ca_valid.index_select(1, slot)
@@ -443,7 +543,7 @@ class DecodeEngine:
             self.ca_v.index_copy_(1, slot, torch.where(any_fire, newv.unsqueeze(1), oldv))
             self.ca_valid.index_copy_(1, slot, torch.where(any_fire, fire.unsqueeze(1), oldm))
             self.ca_len.add_(any_fire.long())
-            allowed = self.ca_valid & (torch.arange(S, device=self.dev).view(1, S) < self.ca_len)
+            allowed = self.ca_valid & (torch.arange(self.ca_cap, device=self.dev).view(1, -1) < self.ca_len)
             qv = self._lin(h, fca.w_qk.weight)
             out = R.masked_cross_attention(qv.float().unsqueeze(1), self.ca_k.float(), self.ca_v.float(),
                                            allowed.unsqueeze(1), fca.scale)[:, 0]
