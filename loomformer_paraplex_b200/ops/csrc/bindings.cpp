@@ -212,44 +212,57 @@ void skinny_linear(torch::Tensor x, torch::Tensor w, c10::optional<torch::Tensor
 
 // segs: list of (pieces, w, bias or None, y): pieces = list of [M, len] bf16 views (unit inner stride), w [N, K] bf16 rows,
 // y [M, N] bf16 or fp32 view
-void skinny_multi(std::vector<std::tuple<std::vector<torch::Tensor>, torch::Tensor, c10::optional<torch::Tensor>, torch::Tensor>> segs,
-                  bool weights_static) {
-  TORCH_CHECK(!segs.empty() && (int)segs.size() <= LOOM_SKINNY_MAX_SEG, "skinny_multi: 1..", LOOM_SKINNY_MAX_SEG, " segments");
-  LoomSkinnyArgs a;
+typedef std::vector<std::tuple<std::vector<torch::Tensor>, torch::Tensor, c10::optional<torch::Tensor>, torch::Tensor>> SkinnySegs;
+
+static void fill_skinny_args(const SkinnySegs& segs, bool weights_static, LoomSkinnyArgs& a) {
+  TORCH_CHECK(!segs.empty() && (int)segs.size() <= LOOM_SKINNY_MAX_SEG, "small-batch product: 1..", LOOM_SKINNY_MAX_SEG, " segments");
   memset(&a, 0, sizeof(a));
   a.nseg = (int)segs.size();
   a.weights_static = weights_static ? 1 : 0;
-  const torch::Tensor& y0 = std::get<3>(segs[0]);
-  const c10::cuda::CUDAGuard guard(y0.device());
-  a.M = (int)y0.size(0);
+  a.M = (int)std::get<3>(segs[0]).size(0);
   for (int i = 0; i < a.nseg; ++i) {
     const auto& pieces = std::get<0>(segs[i]);
     const torch::Tensor& w = std::get<1>(segs[i]);
     const auto& bias = std::get<2>(segs[i]);
     const torch::Tensor& y = std::get<3>(segs[i]);
     LoomSkinnySeg& sg = a.seg[i];
-    TORCH_CHECK(!pieces.empty() && (int)pieces.size() <= LOOM_SKINNY_MAX_PIECE, "skinny_multi: 1..", LOOM_SKINNY_MAX_PIECE, " pieces");
-    TORCH_CHECK(w.dim() == 2 && w.stride(1) == 1 && w.scalar_type() == torch::kBFloat16, "skinny_multi: bf16 weight rows");
+    TORCH_CHECK(!pieces.empty() && (int)pieces.size() <= LOOM_SKINNY_MAX_PIECE, "small-batch product: 1..", LOOM_SKINNY_MAX_PIECE, " pieces");
+    TORCH_CHECK(w.dim() == 2 && w.stride(1) == 1 && w.scalar_type() == torch::kBFloat16, "small-batch product: bf16 weight rows");
     TORCH_CHECK(y.dim() == 2 && y.stride(1) == 1 && y.size(0) == a.M && y.size(1) == w.size(0) &&
-                (y.scalar_type() == torch::kBFloat16 || y.scalar_type() == torch::kFloat32), "skinny_multi: output view");
+                (y.scalar_type() == torch::kBFloat16 || y.scalar_type() == torch::kFloat32), "small-batch product: output view");
     int k = 0;
     for (size_t p = 0; p < pieces.size(); ++p) {
       const torch::Tensor& x = pieces[p];
       TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.size(0) == a.M && x.scalar_type() == torch::kBFloat16,
-                  "skinny_multi: bf16 [M, len] input pieces");
+                  "small-batch product: bf16 [M, len] input pieces");
       sg.piece[p].x = x.data_ptr(); sg.piece[p].ld = a.M > 1 ? x.stride(0) : 0; sg.piece[p].len = (int)x.size(1);
       k += (int)x.size(1);
     }
-    TORCH_CHECK(k == w.size(1), "skinny_multi: pieces do not add up to the weight's width");
+    TORCH_CHECK(k == w.size(1), "small-batch product: pieces do not add up to the weight's width");
     sg.npiece = (int)pieces.size();
     sg.w = w.data_ptr(); sg.ldw = w.stride(0);
     sg.bias = nullptr;
-    if (bias.has_value()) { TORCH_CHECK(bias->numel() == w.size(0), "skinny_multi: bias length"); sg.bias = fptr(*bias); }
+    if (bias.has_value()) { TORCH_CHECK(bias->numel() == w.size(0), "small-batch product: bias length"); sg.bias = fptr(*bias); }
     sg.y = y.data_ptr(); sg.ldy = y.stride(0);
     sg.N = (int)w.size(0); sg.K = k; sg.out_fp32 = y.scalar_type() == torch::kFloat32 ? 1 : 0;
   }
+}
+
+void skinny_multi(SkinnySegs segs, bool weights_static) {
+  LoomSkinnyArgs a;
+  fill_skinny_args(segs, weights_static, a);
+  const c10::cuda::CUDAGuard guard(std::get<3>(segs[0]).device());
   int rc = loom_skinny_multi(&a, cur_stream());
   TORCH_CHECK(rc == 0, "loom_skinny_multi failed: ", rc);
+}
+
+void decode_gemm(SkinnySegs segs, bool weights_static, torch::Tensor status) {
+  LoomSkinnyArgs a;
+  fill_skinny_args(segs, weights_static, a);
+  const c10::cuda::CUDAGuard guard(std::get<3>(segs[0]).device());
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == torch::kInt32, "status word: int32 CUDA tensor");
+  int rc = loom_decode_gemm(&a, status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "loom_decode_gemm failed: ", rc);
 }
 
 void decode_step_flags(torch::Tensor pos, torch::Tensor tok, torch::Tensor pending, torch::Tensor have_carry, torch::Tensor fire,
@@ -547,6 +560,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("decode_attn", &decode_attn, "KV-cache attention for one new token per sequence, dual context, split over positions");
   m.def("skinny_linear", &skinny_linear, "y = x W^T (+ bias) for up to 16 rows: weights streamed once, output may be a strided view");
   m.def("skinny_multi", &skinny_multi, "several small-batch products (own inputs, weights, outputs) in one launch");
+  m.def("decode_gemm", &decode_gemm, "several 17..128-row products in one launch: weight rows as the M side of tcgen05.mma, batch as N");
   m.def("decode_step_flags", &decode_step_flags, "fire / reset / first-position / seed flags of one decode step");
   m.def("decode_ca_append", &decode_ca_append, "boundary-key append and visibility mask of one decode step");
   m.def("decode_rope_store", &decode_rope_store, "RoPE of the new token's Q / K at the device-side position + KV cache append");

@@ -525,6 +525,76 @@ __global__ void __launch_bounds__(256) ce_kernel(bf16* __restrict__ logits, cons
   }
 }
 
+
+// Few rows (a decode step): one block per row instead of one warp, so a single row is spread over 8 warps' worth of
+// loads in flight.  Same arithmetic as add_ln_fwd_kernel; two values are reduced per block reduction.
+__device__ __forceinline__ float2 block_sum2(float2 v, float2* sh) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    v.x += __shfl_xor_sync(0xffffffffu, v.x, o);
+    v.y += __shfl_xor_sync(0xffffffffu, v.y, o);
+  }
+  const int w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) sh[w] = v;
+  __syncthreads();
+  float2 r = sh[0];
+  for (int i = 1; i < nw; ++i) { r.x += sh[i].x; r.y += sh[i].y; }
+  return r;
+}
+
+__global__ void __launch_bounds__(256) add_ln_fwd_row_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b,
+                                                             const float* __restrict__ w, const float* __restrict__ bias,
+                                                             bf16* __restrict__ y, bf16* __restrict__ x,
+                                                             float* __restrict__ mean, float* __restrict__ rstd, int N,
+                                                             float eps, float cap) {
+  __shared__ float2 sh[8];
+  loom::pdl_trigger();
+  const int row = blockIdx.x;
+  const int col = threadIdx.x * 8;
+  const bool on = col < N;
+  float fa[8], fb[8], v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { fa[i] = 0.f; fb[i] = 0.f; v[i] = 0.f; }
+  if (on) {
+    unpack8(*reinterpret_cast<const uint4*>(a + (long long)row * N + col), fa);
+    unpack8(*reinterpret_cast<const uint4*>(b + (long long)row * N + col), fb);
+  }
+  float sa = 1.f, sb = 1.f;
+  if (cap > 0.f) {
+    float2 q = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { q.x += fa[i] * fa[i]; q.y += fb[i] * fb[i]; }
+    q = block_sum2(q, sh);
+    sa = fminf(1.f, cap * rsqrtf(q.x / N + 1e-6f));
+    sb = fminf(1.f, cap * rsqrtf(q.y / N + 1e-6f));
+  }
+  float2 s1 = make_float2(0.f, 0.f);
+  if (on) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) fa[i] = sa * fa[i] + sb * fb[i];
+    const uint4 packed = pack8(fa);
+    *reinterpret_cast<uint4*>(x + (long long)row * N + col) = packed;
+    unpack8(packed, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s1.x += v[i];
+  }
+  const float mu = block_sum2(s1, sh).x / N;
+  float2 s2 = make_float2(0.f, 0.f);
+  if (on) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { const float d = v[i] - mu; s2.x += d * d; }
+  }
+  const float rs = rsqrtf(block_sum2(s2, sh).x / N + eps);
+  if (on) {
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = (v[i] - mu) * rs * w[col + i] + bias[col + i];
+    *reinterpret_cast<uint4*>(y + (long long)row * N + col) = pack8(o);
+  }
+  if (threadIdx.x == 0) { mean[row] = mu; rstd[row] = rs; }
+}
+
 }  // namespace
 
 extern "C" int loom_rope_store(const void* qkv, const float* cs, const float* sn, void* qkc, void* kcache, void* vcache,
@@ -588,6 +658,11 @@ extern "C" int loom_cap_bwd(const void* dy, const void* a, void* da, int M, int 
 extern "C" int loom_add_ln_fwd(const void* a, const void* b, const float* w, const float* bias, void* y, void* x,
                                float* mean, float* rstd, int M, int N, float eps, float cap, cudaStream_t st) {
   if (N % 8 || N > 2048) return -1;
+  if (M <= 64) {                                          // a decode step: one block per row
+    const int threads = ((N / 8 + 31) / 32) * 32;
+    add_ln_fwd_row_kernel<<<M, threads, 0, st>>>((const bf16*)a, (const bf16*)b, w, bias, (bf16*)y, (bf16*)x, mean, rstd, N, eps, cap);
+    return (int)cudaGetLastError();
+  }
   const unsigned grid = (M + 7) / 8;
   const int nch = (N + 255) / 256;
 #define LN_F(K) add_ln_fwd_kernel<K><<<grid, 256, 0, st>>>((const bf16*)a, (const bf16*)b, w, bias, (bf16*)y, (bf16*)x, mean, rstd, M, N, eps, cap)

@@ -203,6 +203,9 @@ typedef struct {
 // previous kernel has finished
 typedef struct { LoomSkinnySeg seg[LOOM_SKINNY_MAX_SEG]; int nseg, M, weights_static, pad_; } LoomSkinnyArgs;
 int loom_skinny_multi(LoomSkinnyArgs* a, cudaStream_t st);
+// the same products for up to 128 rows on the tensor cores (decode_gemm.cu): a CTA owns 128 rows of one weight matrix
+// (M side of tcgen05.mma), the batch is the N side; `status`: device word set when a bounded wait gives up
+int loom_decode_gemm(const LoomSkinnyArgs* a, int* status, cudaStream_t st);
 // booleans of one decode step (all [B] bytes) from the device-side position, the incoming tokens and the flags of the
 // previous step; carry_token < 0: no carry token
 int loom_decode_step_flags(const long long* pos, const long long* tok, const void* pending, const void* have_carry,

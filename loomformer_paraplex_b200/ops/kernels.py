@@ -267,17 +267,19 @@ class CudaKernels(TorchKernels):
         return y
 
     def linear_multi(self, segs, static_weights=False):
-        """Several small-batch products in one launch (``csrc/decode_step.cu``, up to 16 rows, 12 segments per launch);
-        more rows fall back to one GEMM per segment.  ``static_weights``: nothing earlier in the stream writes the
-        weights or biases (an inference engine's copies), so the kernel may fetch them while its predecessor runs."""
+        """Several small-batch products in one launch, at most 12 segments each: up to 16 rows through the
+        weight-streaming kernel (``csrc/decode_step.cu``), up to 128 through the weight-stationary tensor-core kernel
+        (``csrc/decode_gemm.cu``: weight rows as the M side of the MMA, batch as N); more rows fall back to one GEMM
+        per segment.  ``static_weights``: nothing earlier in the stream writes the weights or biases (an inference
+        engine's copies), so the kernels may fetch them while their predecessor runs."""
         M = segs[0][3].shape[0]
 
         def piece_ok(t):
             return (t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1 and t.shape[1] % 8 == 0
-                    and (M == 1 or t.stride(0) % 8 == 0) and t.data_ptr() % 16 == 0)
+                    and (M == 1 or (t.stride(0) % 8 == 0 and t.stride(0) >= t.shape[1])) and t.data_ptr() % 16 == 0)
 
-        ok = M <= 16 and all(all(piece_ok(x) for x in pieces) and piece_ok(w) and out.stride(1) == 1
-                             and out.dtype in (torch.bfloat16, torch.float32) for pieces, w, _, out in segs)
+        ok = M <= 128 and all(all(piece_ok(x) for x in pieces) and piece_ok(w) and out.stride(1) == 1
+                              and out.dtype in (torch.bfloat16, torch.float32) for pieces, w, _, out in segs)
         if not ok:
             for pieces, w, bias, out in segs:
                 x = pieces[0] if len(pieces) == 1 else torch.cat(list(pieces), -1)
@@ -285,7 +287,10 @@ class CudaKernels(TorchKernels):
             return
         packed = [(list(pieces), w, None if bias is None else _f32c(bias), out) for pieces, w, bias, out in segs]
         for i in range(0, len(packed), 12):
-            native.ext().skinny_multi(packed[i:i + 12], bool(static_weights))
+            if M <= 16:
+                native.ext().skinny_multi(packed[i:i + 12], bool(static_weights))
+            else:
+                native.ext().decode_gemm(packed[i:i + 12], bool(static_weights), status_word(segs[0][3].device))
             native.count()
 
     def linear_dgrad(self, dy, w, out=None, accumulate=False):

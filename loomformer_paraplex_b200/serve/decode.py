@@ -74,8 +74,9 @@ class DecodeEngine:
             from ..ops import native
             if native.available():
                 self._native_attn = True
-                # position slices per (sequence, KV head): about eight blocks per SM, at least 32 positions each
-                self._ns = max(1, min(32, -(-1184 // (B * d.kvh)), -(-S // 32)))
+                # position slices per (sequence, KV head): about four blocks per SM, at least 64 positions each (the
+                # merge of the slices by the last block grows with their number)
+                self._ns = max(1, min(16, -(-592 // (B * d.kvh)), -(-S // 64)))
                 n_ws = B * d.kvh * self._ns * (2 * d.group + 2 * d.group * d.hd) + B * d.kvh
                 self._attn_ws = torch.zeros(n_ws, dtype=torch.float32, device=dev)     # partial states | ticket counters
         # fused kernels of the training plan reused at one token per sequence (fewer, larger launches per layer).  A
@@ -287,7 +288,7 @@ class DecodeEngine:
         h = self.w(m.emb.weight)[self.tok_in]
         da = m.depth_attn
         hk, hv, qkc = self._hk, self._hv, self._qkc
-        small = B <= 16
+        small = B <= 128          # products of up to 128 rows have a multi-segment kernel (16: CUDA cores, 128: tcgen05)
         after = []
 
         def project_seg(x, slot):

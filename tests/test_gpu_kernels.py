@@ -102,6 +102,22 @@ def test_add_layernorm(N):
     assert not ck.fallbacks, ck.fallbacks
 
 
+@pytest.mark.parametrize("N", [128, 768, 960, 2048])
+@pytest.mark.parametrize("cap", [None, 1.0])
+def test_add_layernorm_few_rows(N, cap):
+    """Up to 64 rows (a decode step) take the block-per-row kernel: same numbers as the PyTorch statement, with and
+    without the RMS cap on the addends."""
+    ck, tk = _sets()
+    torch.manual_seed(22)
+    for M in (1, 5, 64):
+        a, b = bf(M, N, scale=2.0), bf(M, N, scale=0.5)
+        w, bias = torch.rand(N, device="cuda") + 0.5, torch.randn(N, device="cuda") * 0.1
+        y1, x1, mu1, rs1 = ck.add_ln_fwd(a, b, w, bias, cap)
+        y2, x2, mu2, rs2 = tk.add_ln_fwd(a.float(), b.float(), w, bias, cap)
+        _close(y1, y2, 2e-2, "y"); _close(x1, x2, 1e-2, "x"); _close(mu1, mu2, 1e-2, "mean"); _close(rs1, rs2, 1e-2, "rstd")
+    assert not ck.fallbacks, ck.fallbacks
+
+
 def test_cross_entropy():
     ck, tk = _sets()
     torch.manual_seed(3)
@@ -384,11 +400,11 @@ def test_decode_attention_kernel(B, S, pos, ns, qh, kvh, hd):
     assert int(ws[-B * kvh:].view(torch.int32).abs().sum()) == 0
 
 
-@pytest.mark.parametrize("hidden,batch,carry", [(256, 3, None), (172, 3, None), (256, 20, None), (256, 2, 7)])
+@pytest.mark.parametrize("hidden,batch,carry", [(256, 3, None), (172, 3, None), (256, 20, None), (172, 40, None), (256, 2, 7)])
 def test_decode_engine_graph_matches_model_step_on_gpu(hidden, batch, carry):
     """Graph-replayed decode with the fused kernels follows the fp32 composed step (bf16 tolerance).
-    ``hidden=172`` is 43 neurons per head: the fused step pads every sector to 48 inert-padded neurons.  Twenty rows
-    take the tensor-core GEMMs instead of the weight-streaming launches; a carry token makes boundary keys fire from
+    ``hidden=172`` is 43 neurons per head: the fused step pads every sector to 48 inert-padded neurons.  Twenty and forty
+    rows take the weight-stationary tensor-core kernel instead of the weight-streaming one; a carry token makes boundary keys fire from
     the token stream as well as from the window."""
     from loomformer_paraplex_b200.config import Config
     from loomformer_paraplex_b200.models.loomformer import Model
@@ -423,26 +439,35 @@ def test_decode_engine_graph_matches_model_step_on_gpu(hidden, batch, carry):
     assert not eng._K.fallbacks, dict(eng._K.fallbacks)
 
 
-def test_multi_segment_small_batch_linear():
-    """Several products in one launch: own inputs (one gathered from strided pieces), weights, biases, output views of
-    different dtypes; thirteen segments take two launches."""
+@pytest.mark.parametrize("static", [False, True])
+def test_multi_segment_small_batch_linear(static):
+    """Several products in one launch: own inputs (one gathered from strided pieces, one of them 96 wide so that a
+    k-block straddles two pieces), weights, biases, output views of different dtypes; thirteen segments take two
+    launches.  Up to 16 rows run on the weight-streaming kernel, 17..128 on the weight-stationary tcgen05 kernel."""
     from loomformer_paraplex_b200.ops import kernels
     ck = kernels.CudaKernels(defer_wgrad=False)
     torch.manual_seed(21)
-    for M in (1, 3, 16):
-        x1, x2 = bf(M, 768), bf(M, 3, 4, 32)
-        w1, w2, w3 = bf(1152, 768, scale=0.05), bf(200, 768 + 32 + 128, scale=0.05), bf(64, 768, scale=0.05)
+    for M in (1, 3, 16, 17, 20, 64, 100, 128):
+        x1, x2, x3 = bf(M, 768), bf(M, 3, 4, 32), bf(M, 2, 96)
+        w1, w2, w3 = bf(1152, 768, scale=0.05), bf(200, 768 + 32 + 96 + 128, scale=0.05), bf(64, 768, scale=0.05)
+        w4 = bf(300, 3072, scale=0.03)
+        x4 = bf(M, 3072)
         b2 = torch.randn(200, device="cuda")
         y1 = torch.empty(M, 1152, device="cuda", dtype=torch.bfloat16)
+        y4 = torch.empty(M, 300, device="cuda", dtype=torch.bfloat16)
         wide = torch.full((M, 208), 7.0, device="cuda")                       # fp32, strided view
-        segs = [([x1], w1, None, y1), ([x1, x2[:, 1, 2], x2[:, 2].reshape(M, 128)], w2, b2, wide[:, :200])]
-        outs = [torch.empty(M, 64, device="cuda", dtype=torch.bfloat16) for _ in range(11)]
+        pieces = [x1, x2[:, 1, 2], x3[:, 1], x2[:, 2].reshape(M, 128)]
+        segs = [([x1], w1, None, y1), (pieces, w2, b2, wide[:, :200]), ([x4], w4, None, y4)]
+        outs = [torch.empty(M, 64, device="cuda", dtype=torch.bfloat16) for _ in range(10)]
         segs += [([x1], w3, None, o) for o in outs]
-        ck.linear_multi(segs)
+        torch.cuda.synchronize()
+        ck.linear_multi(segs, static_weights=static)
+        kernels.check_status(x1.device)
         _close(y1, x1.float() @ w1.float().t(), 2e-2, "seg 0")
-        xc = torch.cat((x1, x2[:, 1, 2], x2[:, 2].reshape(M, 128)), -1).float()
-        _close(wide[:, :200], xc @ w2.float().t() + b2, 2e-3, "gathered fp32 seg")
+        xc = torch.cat(pieces, -1).float()
+        _close(wide[:, :200], xc @ w2.float().t() + b2, 3e-3, "gathered fp32 seg")
         assert bool((wide[:, 200:] == 7.0).all())
+        _close(y4, x4.float() @ w4.float().t(), 2e-2, "long-K seg")
         for o in outs:
             _close(o, x1.float() @ w3.float().t(), 2e-2, "small seg")
     assert not ck.fallbacks, ck.fallbacks
