@@ -183,7 +183,8 @@ void rope_bwd(torch::Tensor dq_attn, torch::Tensor dqkc, torch::Tensor dkc, torc
 }
 
 void decode_attn(torch::Tensor q, torch::Tensor kc, torch::Tensor vc, torch::Tensor pos, torch::Tensor out_c, torch::Tensor out_k,
-                 torch::Tensor ws, int64_t B, int64_t S, int64_t QH, int64_t KVH, int64_t HD, int64_t NS) {
+                 torch::Tensor ws, int64_t B, int64_t S, int64_t QH, int64_t KVH, int64_t HD, int64_t NS,
+                 c10::optional<torch::Tensor> status) {
   // outputs may be row-strided views (e.g. slices of a [B,3,QH,HD] buffer): contiguous within a sequence
   TORCH_CHECK(out_c.stride(-1) == 1 && out_k.stride(-1) == 1 && out_c.stride(0) == out_k.stride(0), "decode_attn: output layout");
   const c10::cuda::CUDAGuard guard(q.device());
@@ -192,7 +193,8 @@ void decode_attn(torch::Tensor q, torch::Tensor kc, torch::Tensor vc, torch::Ten
   TORCH_CHECK(ws.numel() >= loom_decode_attn_workspace_floats((int)B, (int)QH, (int)KVH, (int)HD, (int)NS), "workspace too small");
   int rc = loom_decode_attn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos.data_ptr<int64_t>() ? (const long long*)pos.data_ptr<int64_t>() : nullptr,
                             out_c.data_ptr(), out_k.data_ptr(), fptr(ws), (int)B, (int)S, (int)QH, (int)KVH, (int)HD, (int)NS,
-                            (long long)out_c.stride(0), (long long)q.stride(0), cur_stream());
+                            (long long)out_c.stride(0), (long long)q.stride(0),
+                            status.has_value() ? status->data_ptr<int>() : nullptr, cur_stream());
   TORCH_CHECK(rc == 0, "loom_decode_attn failed: ", rc);
 }
 

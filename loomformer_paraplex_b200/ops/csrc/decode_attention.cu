@@ -11,14 +11,27 @@
 // (head, dim pair) per thread out of shared memory.  Each block leaves its partial state in a workspace and takes a
 // ticket; the block that draws the last ticket of its (sequence, KV head) merges the partial states and resets the
 // ticket counter, so there is no second launch and nothing waits on anything.
+//
+// Tensor-core variant (decode_attn_tc_kernel, the default when a slice fits one tile of 128 positions): the CUDA-core
+// kernel above spends its time on shared-memory traffic, not on the cache rows.  Here the positions are the M side of
+// tcgen05.mma: S^T[128 positions, 16] = K_tile[128, HD] . Q^T (the group's query rows are the N side, padded to 16 by
+// the rows of the neighbouring heads, whose columns are ignored), one position per thread for the softmax (TMEM lane ==
+// position), P^T written to shared memory as a swizzled K-major operand, and the two contexts as
+// O^T[HD, 16] = V_tile^T . P^T and K_tile^T . P^T with the TMA-loaded tiles re-read as MN-major operands.  One TMA
+// transaction brings the whole slice (K and V tile, Q rows); three small MMA batches; 72 KB of shared memory, so three
+// CTAs share an SM.
 // The reference does this with matmul + softmax + two matmuls over cache[:, :len] in PyTorch
 // (reference loomformer.py, Attention.step), re-launching per token from the host.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
 #include "launch_util.cuh"
 #include "loom_c_api.h"
+#include "sm100.cuh"
+#include "tma_host.h"
 
 namespace {
 
@@ -34,6 +47,51 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
 }
 __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+// Run by every thread of the block that drew the last ticket of its (sequence, KV head): merge the NS partial states at
+// `base`.  The softmax statistics of every slice are staged first and turned into one weight per (head, slice), so that
+// the sums are plain independent loads (a data-dependent branch per slice would serialise the loop on memory latency).
+// f_m, f_l: shared scratch of G * NS floats each; inv_l: shared, MAXG floats; obase: first output element of the group.
+__device__ __forceinline__ void merge_slices(const float* __restrict__ base, int per, int NS, int G, int HD, float* f_m,
+                                             float* f_l, float* inv_l, bf16* __restrict__ out_c, bf16* __restrict__ out_k,
+                                             long long obase) {
+  const int tid = threadIdx.x, nthr = blockDim.x, HD2 = HD >> 1;
+  for (int i = tid; i < G * NS; i += nthr) {
+    const int g = i / NS, zz = i - g * NS;
+    f_m[i] = __ldcg(base + zz * per + g);
+    f_l[i] = __ldcg(base + zz * per + G + g);
+  }
+  __syncthreads();
+  if (tid < G) {
+    float M = -INFINITY, l = 0.f;
+    for (int zz = 0; zz < NS; ++zz) M = fmaxf(M, f_m[tid * NS + zz]);
+    for (int zz = 0; zz < NS; ++zz) {
+      const float f = __expf(f_m[tid * NS + zz] - M);      // empty slice: exp(-inf) = 0
+      l += f_l[tid * NS + zz] * f;
+      f_m[tid * NS + zz] = f;
+    }
+    inv_l[tid] = 1.f / l;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < G * HD2; idx += nthr) {
+    const int g = idx / HD2, c2 = idx - g * HD2;
+    const float* fw = f_m + g * NS;
+    const float* pv = base + 2 * G + g * HD + 2 * c2;
+    const float* pk = pv + G * HD;
+    float v0 = 0.f, v1 = 0.f, k0 = 0.f, k1 = 0.f;
+#pragma unroll 8
+    for (int zz = 0; zz < NS; ++zz) {
+      const float f = fw[zz];
+      const float2 a = __ldcg(reinterpret_cast<const float2*>(pv + (long long)zz * per));
+      const float2 k = __ldcg(reinterpret_cast<const float2*>(pk + (long long)zz * per));
+      v0 = fmaf(a.x, f, v0); v1 = fmaf(a.y, f, v1); k0 = fmaf(k.x, f, k0); k1 = fmaf(k.y, f, k1);
+    }
+    const float inv = inv_l[g];
+    const long long o = obase + (long long)g * HD + 2 * c2;
+    *reinterpret_cast<__nv_bfloat162*>(out_c + o) = __floats2bfloat162_rn(v0 * inv, v1 * inv);
+    *reinterpret_cast<__nv_bfloat162*>(out_k + o) = __floats2bfloat162_rn(k0 * inv, k1 * inv);
+  }
 }
 
 // q [B,QH,HD] (row pitch q_ld); kc, vc [B,S,KVH,HD]; out_c, out_k [B,QH,HD] (row pitch out_ld)
@@ -184,52 +242,216 @@ __global__ void __launch_bounds__(THREADS) decode_attn_kernel(
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  // the last block of this (sequence, KV head): merge all partial states.  The softmax statistics of every slice are
-  // staged first and turned into one weight per (head, slice), so that the sums below are plain independent loads
-  // (a data-dependent branch per slice would serialise the loop on memory latency).
-  const float* base = ws + (long long)blockIdx.x * NS * per;
-  float* f_m = ps;                                         // [G][NS], NS <= TP
-  float* f_l = reinterpret_cast<float*>(kt);               // [G][NS]
-  for (int i = tid; i < G * NS; i += THREADS) {
-    const int g = i / NS, zz = i - g * NS;
-    f_m[i] = __ldcg(base + zz * per + g);
-    f_l[i] = __ldcg(base + zz * per + G + g);
-  }
-  __syncthreads();
-  if (tid < G) {
-    float M = -INFINITY, l = 0.f;
-    for (int zz = 0; zz < NS; ++zz) M = fmaxf(M, f_m[tid * NS + zz]);
-    for (int zz = 0; zz < NS; ++zz) {
-      const float f = __expf(f_m[tid * NS + zz] - M);      // empty slice: exp(-inf) = 0
-      l += f_l[tid * NS + zz] * f;
-      f_m[tid * NS + zz] = f;
-    }
-    sm_l[tid] = 1.f / l;
-  }
-  __syncthreads();
-#pragma unroll
-  for (int j = 0; j < MAXIT; ++j) {
-    const int idx = tid + j * THREADS;
-    if (idx < G * HD2) {
-      const int g = idx / HD2, c2 = idx - g * HD2;
-      const float* fw = f_m + g * NS;
-      const float* pv = base + 2 * G + g * HD + 2 * c2;
-      const float* pk = pv + G * HD;
-      float v0 = 0.f, v1 = 0.f, k0 = 0.f, k1 = 0.f;
-#pragma unroll 8
-      for (int zz = 0; zz < NS; ++zz) {
-        const float f = fw[zz];
-        const float2 a = __ldcg(reinterpret_cast<const float2*>(pv + (long long)zz * per));
-        const float2 k = __ldcg(reinterpret_cast<const float2*>(pk + (long long)zz * per));
-        v0 = fmaf(a.x, f, v0); v1 = fmaf(a.y, f, v1); k0 = fmaf(k.x, f, k0); k1 = fmaf(k.y, f, k1);
-      }
-      const float inv = sm_l[g];
-      const long long o = (long long)b * out_ld + (long long)(kvh * G + g) * HD + 2 * c2;
-      *reinterpret_cast<__nv_bfloat162*>(out_c + o) = __floats2bfloat162_rn(v0 * inv, v1 * inv);
-      *reinterpret_cast<__nv_bfloat162*>(out_k + o) = __floats2bfloat162_rn(k0 * inv, k1 * inv);
-    }
-  }
+  merge_slices(ws + (long long)blockIdx.x * NS * per, per, NS, G, HD, ps, reinterpret_cast<float*>(kt), sm_l, out_c, out_k,
+               (long long)b * out_ld + (long long)kvh * G * HD);
   if (tid == 0) tickets[blockIdx.x] = 0;
+}
+
+
+// ---------------------------------------------------------------------------------------------------------------------
+// tensor-core variant: one CTA per (sequence, KV head, slice of <= 128 positions)
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int TC_THREADS = 128;
+constexpr int TC_TILE = 16384;                 // [128 rows x 128 B] swizzled box
+constexpr int TC_NPAD = 16;                    // query rows of the MMA (N side)
+
+struct TcParams {
+  CUtensorMap q;                               // (HD, QH, B), box 64 x 16
+  CUtensorMap k, v;                            // (HD, KVH, S, B), box 64 x 1 x 128
+  const long long* pos;
+  bf16* out_c; bf16* out_k;
+  float* ws; int* tickets;
+  int S, QH, KVH, HD, NS;
+  float scale;
+  long long out_ld;
+  int* status;
+};
+
+__global__ void __launch_bounds__(TC_THREADS) decode_attn_tc_kernel(const __grid_constant__ TcParams p) {
+  using namespace sm100;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;                          // 2 boxes: head dims 0-63, 64-127
+  uint8_t* sV = sK + 2 * TC_TILE;
+  uint8_t* sQ = sV + 2 * TC_TILE;              // 2 boxes of [16 rows x 128 B]
+  uint8_t* sP = sQ + 2 * 2048;                 // 2 boxes of [16 rows x 128 B]: positions 0-63, 64-127
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * 2048);     // load, scores, contexts
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
+  float* red = reinterpret_cast<float*>(tmem_slot + 2);            // [4 warps][MAXG]
+  float* sm_m = red + 4 * MAXG;
+  float* sm_l = sm_m + MAXG;
+  float* f_m = reinterpret_cast<float*>(sQ);   // merge scratch, MAXG * TP floats each: the operand boxes are dead by then
+  float* f_l = reinterpret_cast<float*>(sP);
+  __shared__ int s_last;
+
+  const int G = p.QH / p.KVH, HD = p.HD, NS = p.NS;
+  const int b = blockIdx.x / p.KVH, kvh = blockIdx.x % p.KVH, z = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  volatile int* status = p.status;
+
+  if (tid == 0) {
+    mbar_init(&bars[0], 1); mbar_init(&bars[1], 1); mbar_init(&bars[2], 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) { tmem_alloc(tmem_slot, 64); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  loom::pdl_trigger();
+  loom::pdl_wait();                            // the new token's K / V rows and Q come from the previous kernels
+
+  long long n = *p.pos + 1;
+  if (n > p.S) n = p.S;
+  if (n < 0) n = 0;
+  int chunk = (int)((n + NS - 1) / NS);
+  chunk = (chunk + 63) & ~63;                  // whole 64-position blocks, at most one 128-position tile (host-checked)
+  const int lo = z * chunk;
+  int hi = lo + chunk;
+  if (hi > n) hi = (int)n;
+  const int cnt = hi > lo ? hi - lo : 0;
+  const int per = 2 * G + 2 * G * HD;
+  float* wsb = p.ws + ((long long)blockIdx.x * NS + z) * per;
+  bool ok = true;
+
+  if (cnt > 0) {
+    if (tid == 0) {
+      mbar_expect_tx(&bars[0], 4 * TC_TILE + 2 * 2048);
+      tma_load_3d(sQ, &p.q, &bars[0], 0, kvh * G, b);
+      tma_load_3d(sQ + 2048, &p.q, &bars[0], 64, kvh * G, b);
+      tma_load_4d(sK, &p.k, &bars[0], 0, kvh, lo, b);
+      tma_load_4d(sK + TC_TILE, &p.k, &bars[0], 64, kvh, lo, b);
+      tma_load_4d(sV, &p.v, &bars[0], 0, kvh, lo, b);
+      tma_load_4d(sV + TC_TILE, &p.v, &bars[0], 64, kvh, lo, b);
+    }
+    ok = mbar_wait(&bars[0], 0, status, 121);
+    // rows past the slice hold other positions' (or no) data: they get probability zero, and zero times a non-finite
+    // leftover would still poison the sums, so they are cleared before the tensor core reads the tiles as operands
+    if (ok && tid >= cnt) {
+      const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        uint4* rk = reinterpret_cast<uint4*>(sK + j * TC_TILE + tid * 128);
+        uint4* rv = reinterpret_cast<uint4*>(sV + j * TC_TILE + tid * 128);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) { rk[c] = zero; rv[c] = zero; }
+      }
+    }
+    fence_proxy_async();
+    __syncthreads();
+    const int ksteps = (HD + 15) >> 4;
+    if (ok && tid == 0) {
+      // S^T[128 positions, 16] = K_tile . Q^T
+      constexpr uint32_t idesc = make_idesc_bf16(128, TC_NPAD, 0, 0);
+      for (int ks = 0; ks < ksteps; ++ks) {
+        const uint32_t off = (ks >> 2) * TC_TILE + (ks & 3) * 32;
+        const uint32_t qoff = (ks >> 2) * 2048 + (ks & 3) * 32;
+        mma_bf16_ss(tmem_base, make_smem_desc_sw128(smem_u32(sK) + off, 0, 1024),
+                    make_smem_desc_sw128(smem_u32(sQ) + qoff, 0, 1024), idesc, ks > 0 ? 1u : 0u);
+      }
+      mma_commit(&bars[1]);
+    }
+    ok = ok && mbar_wait(&bars[1], 0, status, 122);
+    tc_fence_after();
+    // softmax over the slice: thread == position
+    float sc[MAXG];
+    {
+      uint32_t r[16];
+      tmem_ld_32x16(tmem_base + (uint32_t(warp * 32) << 16), r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int g = 0; g < MAXG; ++g) sc[g] = (g < G && tid < cnt) ? __uint_as_float(r[g]) * p.scale : -INFINITY;
+    }
+#pragma unroll
+    for (int g = 0; g < MAXG; ++g) {
+      float mx = sc[g];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      if (lane == 0) red[warp * MAXG + g] = mx;
+    }
+    __syncthreads();
+    if (tid < MAXG) sm_m[tid] = fmaxf(fmaxf(red[tid], red[MAXG + tid]), fmaxf(red[2 * MAXG + tid], red[3 * MAXG + tid]));
+    __syncthreads();
+    const int kb = tid >> 6, kk = tid & 63;
+#pragma unroll
+    for (int g = 0; g < MAXG; ++g) {
+      float e = 0.f;
+      if (g < G) {
+        e = __expf(sc[g] - sm_m[g]);             // masked position: exp(-inf) = 0
+        // P^T as a K-major operand: row g, position kk of 64-position block kb, 16-byte chunks swizzled by the row
+        *reinterpret_cast<bf16*>(sP + kb * 2048 + g * 128 + (((kk >> 3) ^ (g & 7)) << 4) + (kk & 7) * 2) = __float2bfloat16(e);
+      }
+      float sum = e;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      if (lane == 0) red[warp * MAXG + g] = sum;
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    if (tid < MAXG) sm_l[tid] = red[tid] + red[MAXG + tid] + red[2 * MAXG + tid] + red[3 * MAXG + tid];
+    if (ok && tid == 0) {
+      tc_fence_after();
+      // O_v^T[HD, 16] = V_tile^T . P^T and O_k^T = K_tile^T . P^T: the tiles as MN-major A operands (64-wide head-dim
+      // chunks one box apart), 16 positions per instruction
+      constexpr uint32_t idesc = make_idesc_bf16(128, TC_NPAD, 1, 0);
+      const int psteps = (cnt + 15) >> 4;
+      for (int ks = 0; ks < psteps; ++ks) {
+        const uint64_t dp = make_smem_desc_sw128(smem_u32(sP) + (ks >> 2) * 2048 + (ks & 3) * 32, 0, 1024);
+        mma_bf16_ss(tmem_base + 16, make_smem_desc_sw128(smem_u32(sV) + ks * 2048, TC_TILE, 1024), dp, idesc, ks > 0 ? 1u : 0u);
+        mma_bf16_ss(tmem_base + 32, make_smem_desc_sw128(smem_u32(sK) + ks * 2048, TC_TILE, 1024), dp, idesc, ks > 0 ? 1u : 0u);
+      }
+      mma_commit(&bars[2]);
+    }
+    ok = ok && mbar_wait(&bars[2], 0, status, 123);
+    tc_fence_after();
+    __syncthreads();                           // sm_l visible
+    // thread == head dim: 16 query columns of both contexts
+    uint32_t ov[16], okk[16];
+    tmem_ld_32x16(tmem_base + (uint32_t(warp * 32) << 16) + 16, ov);
+    tmem_ld_32x16(tmem_base + (uint32_t(warp * 32) << 16) + 32, okk);
+    tmem_ld_wait();
+    if (tid < HD) {
+      if (NS == 1) {
+#pragma unroll
+        for (int g = 0; g < MAXG; ++g) {
+          if (g < G) {
+            const float inv = 1.f / sm_l[g];
+            const long long o = (long long)b * p.out_ld + (long long)(kvh * G + g) * HD + tid;
+            p.out_c[o] = __float2bfloat16(__uint_as_float(ov[g]) * inv);
+            p.out_k[o] = __float2bfloat16(__uint_as_float(okk[g]) * inv);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int g = 0; g < MAXG; ++g) {
+          if (g < G) {
+            wsb[2 * G + g * HD + tid] = __uint_as_float(ov[g]);
+            wsb[2 * G + G * HD + g * HD + tid] = __uint_as_float(okk[g]);
+          }
+        }
+      }
+    }
+  } else if (NS > 1) {
+    for (int i = tid; i < 2 * G * HD; i += TC_THREADS) wsb[2 * G + i] = 0.f;       // an empty slice leaves zeros
+  }
+
+  if (NS > 1) {
+    if (tid < G) { wsb[tid] = cnt > 0 ? sm_m[tid] : -INFINITY; wsb[G + tid] = cnt > 0 ? sm_l[tid] : 0.f; }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(p.tickets + blockIdx.x, 1) == NS - 1;
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      merge_slices(p.ws + (long long)blockIdx.x * NS * per, per, NS, G, HD, f_m, f_l, sm_l, p.out_c, p.out_k,
+                   (long long)b * p.out_ld + (long long)kvh * G * HD);
+      if (tid == 0) p.tickets[blockIdx.x] = 0;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, 64);
 }
 
 }  // namespace
@@ -241,20 +463,47 @@ extern "C" int loom_decode_attn_workspace_floats(int B, int QH, int KVH, int HD,
   return B * KVH * NS * (2 * G + 2 * G * HD) + B * KVH;
 }
 
-// q and out_c / out_k rows of sequence b start at b * q_ld resp. b * out_ld elements (QH * HD for dense [B,QH,HD])
+// q and out_c / out_k rows of sequence b start at b * q_ld resp. b * out_ld elements (QH * HD for dense [B,QH,HD]).
+// `status`: device word that a bounded wait of the tensor-core variant sets when it gives up (may be null).
+// LOOM_DECODE_ATTN=simt forces the CUDA-core variant.
 extern "C" int loom_decode_attn(const void* q, const void* kc, const void* vc, const long long* pos, void* out_c, void* out_k,
                                 float* ws, int B, int S, int QH, int KVH, int HD, int NS, long long out_ld, long long q_ld,
-                                cudaStream_t st) {
+                                int* status, cudaStream_t st) {
   const int G = QH / KVH;
   if (HD % 8 || HD > 128 || G < 1 || G > MAXG || QH % KVH || NS < 1 || NS > TP || (out_ld & 1)) return -1;
-  if ((2 * G + 2 * G * HD) & 1) return -1;
+  int* tickets = reinterpret_cast<int*>(ws + (size_t)B * KVH * NS * (2 * G + 2 * G * HD));
+  dim3 grid(B * KVH, NS);
+  static int simt = -1;
+  if (simt < 0) { const char* e = getenv("LOOM_DECODE_ATTN"); simt = (e != nullptr && e[0] == 's') ? 1 : 0; }
+  const int slice = (((S + NS - 1) / NS) + 63) & ~63;
+  const bool aligned = !(reinterpret_cast<uintptr_t>(q) & 15) && !(reinterpret_cast<uintptr_t>(kc) & 15) &&
+                       !(reinterpret_cast<uintptr_t>(vc) & 15) && !(q_ld & 7);
+  if (!simt && slice <= 128 && aligned && (long long)slice * NS >= S) {
+    static TcParams p;
+    memset(&p, 0, sizeof(p));
+    const bool maps = tma_host::make_3d_bf16(&p.q, q, (uint64_t)B, (uint64_t)QH, (uint64_t)HD, (uint64_t)HD, (uint64_t)q_ld, 64, TC_NPAD) &&
+                      tma_host::make_4d_bf16(&p.k, kc, (uint64_t)HD, (uint64_t)KVH, (uint64_t)S, (uint64_t)B, (uint64_t)HD,
+                                             (uint64_t)KVH * HD, (uint64_t)S * KVH * HD, 64, 1, 128, 1) &&
+                      tma_host::make_4d_bf16(&p.v, vc, (uint64_t)HD, (uint64_t)KVH, (uint64_t)S, (uint64_t)B, (uint64_t)HD,
+                                             (uint64_t)KVH * HD, (uint64_t)S * KVH * HD, 64, 1, 128, 1);
+    if (maps) {
+      p.pos = pos; p.out_c = (bf16*)out_c; p.out_k = (bf16*)out_k; p.ws = ws; p.tickets = tickets;
+      p.S = S; p.QH = QH; p.KVH = KVH; p.HD = HD; p.NS = NS; p.scale = rsqrtf((float)HD); p.out_ld = out_ld; p.status = status;
+      const size_t shm = 4 * TC_TILE + 4 * 2048 + 64 + (4 * MAXG + 2 * MAXG) * sizeof(float) + 1024;   // 73.3 KB: three CTAs per SM
+      static bool configured = false;
+      if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(decode_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shm);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+      }
+      return (int)loom::launch_pdl(decode_attn_tc_kernel, grid, dim3(TC_THREADS), shm, st, p);
+    }
+  }
   const size_t shm = ((size_t)G * HD + (size_t)G * TP + 32 + 3 * MAXG) * sizeof(float) + (size_t)2 * TP * (HD + 8) * sizeof(bf16);
   if (shm > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(decode_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shm);
     if (e != cudaSuccess) return (int)e;
   }
-  int* tickets = reinterpret_cast<int*>(ws + (size_t)B * KVH * NS * (2 * G + 2 * G * HD));
-  dim3 grid(B * KVH, NS);
   return (int)loom::launch_pdl(decode_attn_kernel, grid, dim3(THREADS), shm, st, (const bf16*)q, (const bf16*)kc, (const bf16*)vc, pos,
                                (bf16*)out_c, (bf16*)out_k, ws, tickets, S, QH, KVH, HD, NS, rsqrtf((float)HD), out_ld, q_ld);
 }

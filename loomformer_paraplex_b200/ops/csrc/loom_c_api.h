@@ -112,7 +112,8 @@ int loom_rope_bwd(const void* dq_attn, const void* dqkc, const float* dkc, const
 // ---- KV-cache attention for decode (decode_attention.cu) ----
 int loom_decode_attn_workspace_floats(int B, int QH, int KVH, int HD, int NS);
 int loom_decode_attn(const void* q, const void* kc, const void* vc, const long long* pos, void* out_c, void* out_k, float* ws,
-                     int B, int S, int QH, int KVH, int HD, int NS, long long out_ld, long long q_ld, cudaStream_t st);
+                     int B, int S, int QH, int KVH, int HD, int NS, long long out_ld, long long q_ld, int* status,
+                     cudaStream_t st);
 
 // ---- Tria readout and RMS-type norms (readout.cu) ----
 int loom_slot_pool_fwd(const float* keys, const float* w9, float* pooled, float* stats, int BK, int H, cudaStream_t st);

@@ -74,11 +74,16 @@ class DecodeEngine:
             from ..ops import native
             if native.available():
                 self._native_attn = True
-                # position slices per (sequence, KV head): about four blocks per SM, at least 64 positions each (the
+                # position slices per (sequence, KV head): 128 positions each (one tile of the tensor-core kernel) while
+                # that needs no more than 64 slices, else about four blocks per SM with at least 64 positions each (the
                 # merge of the slices by the last block grows with their number)
-                self._ns = max(1, min(16, -(-592 // (B * d.kvh)), -(-S // 64)))
+                self._ns = -(-S // 128)
+                if self._ns > 64:
+                    self._ns = max(1, min(16, -(-592 // (B * d.kvh)), -(-S // 64)))
                 n_ws = B * d.kvh * self._ns * (2 * d.group + 2 * d.group * d.hd) + B * d.kvh
                 self._attn_ws = torch.zeros(n_ws, dtype=torch.float32, device=dev)     # partial states | ticket counters
+                from ..ops.kernels import status_word
+                self._status = status_word(dev)        # set by a bounded wait that gave up; read by check_status
         # fused kernels of the training plan reused at one token per sequence (fewer, larger launches per layer).  A
         # hidden sector that is not a multiple of 8 neurons wide (a SmolLM2 transplant has 171 per head) is padded
         # with inert neurons inside the FFN part of the step, exactly as the training plan does; the engine's own
@@ -326,7 +331,7 @@ class DecodeEngine:
             ext.decode_rope_store(qkv, self._rope_cos, self._rope_sin, pos, qkc[:, 0].view(B, d.n), self.kc[bi],
                                   self.vc[bi], d.qh, d.kvh, d.hd)
             ext.decode_attn(qkc[:, 0], self.kc[bi], self.vc[bi], pos, qkc[:, 2], qkc[:, 1], self._attn_ws, B, S,
-                            d.qh, d.kvh, d.hd, self._ns)
+                            d.qh, d.kvh, d.hd, self._ns, self._status)
             native.count(2)
             mm_a, _ = K.dread_fwd(d, cst["query"][sub], hk, hv, sub + 1)
             attn_out, skip = torch.empty(B, d.n, **bf), torch.empty(B, d.n, **bf)
@@ -459,7 +464,7 @@ class DecodeEngine:
                 q = q.contiguous()
                 c, k_ctx = torch.empty_like(q), torch.empty_like(q)
                 native.ext().decode_attn(q, self.kc[bi], self.vc[bi], pos, c, k_ctx, self._attn_ws, B, S, d.qh, d.kvh,
-                                         d.hd, self._ns)
+                                         d.hd, self._ns, self._status)
                 native.count(2 if self._ns > 1 else 1)
             else:
                 kk = self.kc[bi].view(B, S, d.kvh, 1, d.hd).expand(B, S, d.kvh, d.group, d.hd).reshape(B, S, d.qh, d.hd)

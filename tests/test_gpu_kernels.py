@@ -378,11 +378,14 @@ def test_rms_type_norms():
 
 @pytest.mark.parametrize("B,S,pos,ns,qh,kvh,hd", [(1, 700, 650, 16, 8, 2, 96), (5, 300, 299, 3, 8, 2, 96), (3, 128, 0, 1, 8, 2, 96),
                                                    (2, 2048, 1500, 1, 8, 2, 96), (1, 769, 30, 32, 8, 2, 96),
-                                                   (2, 400, 333, 5, 15, 5, 64), (3, 200, 150, 4, 16, 2, 128), (2, 90, 77, 2, 4, 4, 24)])
+                                                   (2, 400, 333, 5, 15, 5, 64), (3, 200, 150, 4, 16, 2, 128), (2, 90, 77, 2, 4, 4, 24),
+                                                   (1, 769, 768, 7, 8, 2, 96), (64, 769, 600, 7, 8, 2, 96), (3, 100, 99, 1, 8, 2, 96),
+                                                   (2, 128, 127, 1, 15, 5, 64), (2, 1000, 5, 8, 16, 2, 128)])
 def test_decode_attention_kernel(B, S, pos, ns, qh, kvh, hd):
-    """Tiled KV-cache attention with the merge done by the last block of each (sequence, KV head): run twice on one
-    workspace (the ticket counters must come back to zero), slices that are empty, partial tiles, several tiles."""
-    from loomformer_paraplex_b200.ops import native
+    """KV-cache attention with the merge done by the last block of each (sequence, KV head): run twice on one workspace
+    (the ticket counters must come back to zero), slices that are empty, partial tiles, several tiles.  Slices of at most
+    128 positions take the tcgen05 variant, longer ones the CUDA-core variant."""
+    from loomformer_paraplex_b200.ops import kernels, native
     torch.manual_seed(14)
     G = qh // kvh
     q, kc, vc = bf(B, qh, hd), bf(B, S, kvh, hd), bf(B, S, kvh, hd)
@@ -394,7 +397,8 @@ def test_decode_attention_kernel(B, S, pos, ns, qh, kvh, hd):
     a = torch.softmax(torch.einsum("bhd,bshd->bhs", q.float(), kk) / hd ** 0.5, -1)
     for _ in range(2):
         c, k_ctx = torch.zeros_like(q), torch.zeros_like(q)
-        native.ext().decode_attn(q, kc, vc, p, c, k_ctx, ws, B, S, qh, kvh, hd, ns)
+        native.ext().decode_attn(q, kc, vc, p, c, k_ctx, ws, B, S, qh, kvh, hd, ns, kernels.status_word(q.device))
+        kernels.check_status(q.device)
         _close(c, torch.einsum("bhs,bshd->bhd", a, vv), 2e-2, "ctx")
         _close(k_ctx, torch.einsum("bhs,bshd->bhd", a, kk), 2e-2, "kctx")
     assert int(ws[-B * kvh:].view(torch.int32).abs().sum()) == 0
