@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(256) dread_fwd_kernel(const float* __restrict_
                                                         float scale, long long slot_stride, long long row_stride) {
   // history element (slot s, row r, head g, dim c) lives at s * slot_stride + r * row_stride + g * HD + c, which lets
   // K and V share one buffer whose rows are the [K | V] rows the projection GEMM writes
-  loom::pdl_trigger();        // a dependent launched programmatically may start its prologue now
+  if (MQ <= 4096) loom::pdl_trigger();        // decode-sized problem: a dependent launched programmatically may start its prologue now
   const long long gid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / G;
   const int l = threadIdx.x % G;
   if (gid >= MQ) return;                    // whole G-lane groups leave together
@@ -304,7 +304,6 @@ __global__ void __launch_bounds__(256) add_ln_fwd_kernel(const bf16* __restrict_
                                                          bf16* __restrict__ y, bf16* __restrict__ x,
                                                          float* __restrict__ mean, float* __restrict__ rstd, int M, int N,
                                                          float eps, float cap) {
-  loom::pdl_trigger();        // a dependent launched programmatically may start its prologue now
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= M) return;

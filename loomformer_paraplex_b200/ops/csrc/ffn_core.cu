@@ -228,7 +228,7 @@ __global__ void __launch_bounds__(256) ffn_core_fwd_kernel(
     const float* __restrict__ seed, const uint8_t* __restrict__ seed_valid, const float* __restrict__ gate_w,
     __nv_bfloat16* __restrict__ o_out, __nv_bfloat16* __restrict__ c_out, __nv_bfloat16* __restrict__ p_out,
     float* __restrict__ trace_out, float* __restrict__ beta_sq_sum) {
-  loom::pdl_trigger();        // a dependent launched programmatically may start its prologue now
+  if (S_in.M <= 256) loom::pdl_trigger();     // decode-sized problem: a dependent launched programmatically may start its prologue now
   CoreScalars S = S_in;
   S.alpha_gate = S.alpha_ptr ? *S.alpha_ptr : 0.f;
   const int Hp = S.H >> 1;
@@ -254,7 +254,7 @@ __global__ void __launch_bounds__(256) ffn_core_fwd_tiled_kernel(
     const float* __restrict__ seed, const uint8_t* __restrict__ seed_valid, const float* __restrict__ gate_w,
     __nv_bfloat16* __restrict__ o_out, __nv_bfloat16* __restrict__ c_out, __nv_bfloat16* __restrict__ p_out,
     float* __restrict__ trace_out, float* __restrict__ beta_sq_sum) {
-  loom::pdl_trigger();        // a dependent launched programmatically may start its prologue now
+  if (S_in.M <= 256) loom::pdl_trigger();     // decode-sized problem: a dependent launched programmatically may start its prologue now
   CoreScalars S = S_in;
   S.alpha_gate = S.alpha_ptr ? *S.alpha_ptr : 0.f;
   const int H = S.H;
