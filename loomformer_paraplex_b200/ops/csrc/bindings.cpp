@@ -99,6 +99,42 @@ void grad_norm(torch::Tensor grads, double max_norm, torch::Tensor partial, torc
   TORCH_CHECK(rc == 0, "loom_grad_norm failed: ", rc);
 }
 
+// [Q | K | V] projection with RoPE and the cache write in the epilogue (pair tiles): x [M, K] bf16, w [(QH + 2 KVH) HD, K]
+// bf16, cos / sin [M, HD] fp32, q_out rows [M, QH * HD] (row pitch taken from the view), caches [B, T, KVH, HD]
+void gemm_qkv_rope(torch::Tensor x, torch::Tensor w, c10::optional<torch::Tensor> bias, torch::Tensor cos_t, torch::Tensor sin_t,
+                   torch::Tensor q_out, torch::Tensor kcache, torch::Tensor vcache, int64_t Tc, int64_t s, int64_t QH, int64_t KVH,
+                   int64_t HD, int64_t bn, torch::Tensor status) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.size(1) == w.size(1) && w.size(0) == (QH + 2 * KVH) * HD, "gemm_qkv_rope: shapes");
+  const int64_t M = x.size(0);
+  TORCH_CHECK(cos_t.scalar_type() == torch::kFloat32 && sin_t.scalar_type() == torch::kFloat32 && cos_t.is_contiguous() &&
+              sin_t.is_contiguous() && cos_t.numel() == M * HD && sin_t.numel() == M * HD, "gemm_qkv_rope: cos / sin [M, HD] fp32");
+  TORCH_CHECK(q_out.dim() == 2 && q_out.size(0) == M && q_out.size(1) == QH * HD && q_out.stride(1) == 1 &&
+              q_out.scalar_type() == torch::kBFloat16, "gemm_qkv_rope: q_out rows");
+  TORCH_CHECK(kcache.dim() == 4 && kcache.is_contiguous() && vcache.is_contiguous() && vcache.sizes() == kcache.sizes() &&
+              kcache.size(2) == KVH && kcache.size(3) == HD && kcache.scalar_type() == torch::kBFloat16 &&
+              vcache.scalar_type() == torch::kBFloat16 && M == kcache.size(0) * Tc, "gemm_qkv_rope: caches [B, T, KVH, HD]");
+  LoomGemm g{};
+  bool ok = true;
+  g.a[0] = operand(x, ok);
+  g.b = operand(w, ok);
+  TORCH_CHECK(ok, "gemm_qkv_rope: bad operand");
+  g.k_len[0] = (int)x.size(1); g.nseg = 1;
+  g.c = q_out.data_ptr(); g.ldc = q_out.stride(0);
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->scalar_type() == torch::kFloat32 && bias->is_contiguous() && bias->numel() == w.size(0), "bias: contiguous fp32 [N]");
+    g.bias = bias->data_ptr<float>();
+  }
+  g.M = (int)M; g.N = (int)w.size(0); g.heads = 1; g.bn = (int)bn; g.pair = 1;
+  g.status = status.data_ptr<int>();
+  g.rope_hd = (int)HD; g.rope_qh = (int)QH; g.rope_kvh = (int)KVH; g.rope_tc = (int)Tc; g.rope_t = (int)kcache.size(1); g.rope_s = (int)s;
+  g.rope_q_ld = q_out.stride(0);
+  g.rope_cos = cos_t.data_ptr<float>(); g.rope_sin = sin_t.data_ptr<float>();
+  g.rope_q = q_out.data_ptr(); g.rope_k = kcache.data_ptr(); g.rope_v = vcache.data_ptr();
+  int rc = loom_gemm_bf16(&g, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_gemm_bf16 (QKV + RoPE) failed: ", rc);
+}
+
 void status_gate(torch::Tensor status, torch::Tensor stats) {
   const c10::cuda::CUDAGuard guard(stats.device());
   TORCH_CHECK(status.is_cuda() && status.scalar_type() == torch::kInt32, "status word: int32 CUDA tensor");
@@ -551,6 +587,7 @@ void p2p_grad_step_atom(int64_t W, int64_t rank, int64_t nblk, std::vector<int64
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "segmented-K batched bf16 GEMM (tcgen05 + TMA)");
   m.def("grad_norm", &grad_norm, "global gradient norm, clip coefficient and finite flag");
+  m.def("gemm_qkv_rope", &gemm_qkv_rope, "[Q | K | V] projection whose epilogue applies RoPE and writes the attention operand and the caches");
   m.def("status_gate", &status_gate, "finite flag &= status word clear; count skipped updates");
   m.def("adamw_flat", &adamw_flat, "AdamW over the flat parameter buffer");
   m.def("atom_flat", &atom_flat, "ATOM over the flat parameter buffer");

@@ -76,6 +76,11 @@ struct Params {
   // GEMM -> reduce-scatter: the fp32 partial product of output rows owned by rank r is stored into this rank's slot of rs_out[r]
   int rs_world, rs_rank, rs_rows_per_rank;
   float* rs_out[8];
+  // [Q | K | V] projection whose epilogue applies RoPE and writes the attention operand and the caches (pair tiles)
+  int rope_hd, rope_qh, rope_kvh, rope_tc, rope_t, rope_s;
+  long long rope_q_ld;
+  const float* rope_cos; const float* rope_sin;
+  __nv_bfloat16* rope_q; __nv_bfloat16* rope_k; __nv_bfloat16* rope_v;
 };
 
 constexpr int OUT_STAGE_BYTES = 4 * 2 * 4096;   // four epilogue warps x two 32-row x 128-byte staging boxes
@@ -223,6 +228,66 @@ __device__ __forceinline__ void store_tile_direct(const Params& p, uint32_t tadd
           }
         }
       }
+    }
+  }
+}
+
+// Epilogue of the [Q | K | V] projection: a tile holds whole heads (BN is a multiple of HD), a thread holds one token's
+// row.  Q and K heads are rotated in fp32 straight from the accumulator (rotate-half: pair (j, j + HD/2)), V heads pass
+// through; rotated Q goes to the attention operand buffer, K and V to the caches at the token's position, so neither
+// the unrotated projection nor a second launch exists.
+template <int BN, int HD>
+__device__ __forceinline__ void store_tile_rope(const Params& p, uint32_t taddr, int row, int n0) {
+  constexpr int HALF = HD / 2;
+  const bool live = row < p.M;
+  const int rr = live ? row : 0;
+  const int b = rr / p.rope_tc, t = rr - b * p.rope_tc;
+  const float* cs = p.rope_cos + (long long)rr * HD;
+  const float* sn = p.rope_sin + (long long)rr * HD;
+  const int heads = p.rope_qh + 2 * p.rope_kvh;
+#pragma unroll 1
+  for (int h = 0; h < BN / HD; ++h) {
+    const int hh = n0 / HD + h;                        // head among Q heads, K heads, V heads (uniform in the warp)
+    if (hh >= heads) break;
+    uint32_t r[HD];
+#pragma unroll
+    for (int c = 0; c < HD / 32; ++c) tmem_ld_32x32(taddr + h * HD + c * 32, reinterpret_cast<uint32_t(&)[32]>(r[c * 32]));
+    tmem_ld_wait();
+    if (!live) continue;
+    float v[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) v[i] = __uint_as_float(r[i]);
+    if (p.bias) {
+#pragma unroll
+      for (int i = 0; i < HD; ++i) v[i] += p.bias[hh * HD + i];
+    }
+    __nv_bfloat16* dst;
+    if (hh < p.rope_qh + p.rope_kvh) {
+#pragma unroll
+      for (int j = 0; j < HALF; j += 4) {
+        const float4 c1 = *reinterpret_cast<const float4*>(cs + j), c2 = *reinterpret_cast<const float4*>(cs + j + HALF);
+        const float4 s1 = *reinterpret_cast<const float4*>(sn + j), s2 = *reinterpret_cast<const float4*>(sn + j + HALF);
+        const float c1a[4] = {c1.x, c1.y, c1.z, c1.w}, c2a[4] = {c2.x, c2.y, c2.z, c2.w};
+        const float s1a[4] = {s1.x, s1.y, s1.z, s1.w}, s2a[4] = {s2.x, s2.y, s2.z, s2.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float x1 = v[j + i], x2 = v[j + i + HALF];
+          v[j + i] = x1 * c1a[i] - x2 * s1a[i];
+          v[j + i + HALF] = x2 * c2a[i] + x1 * s2a[i];
+        }
+      }
+      dst = hh < p.rope_qh ? p.rope_q + (long long)rr * p.rope_q_ld + (long long)hh * HD
+                           : p.rope_k + (((long long)b * p.rope_t + p.rope_s + t) * p.rope_kvh + (hh - p.rope_qh)) * HD;
+    } else {
+      dst = p.rope_v + (((long long)b * p.rope_t + p.rope_s + t) * p.rope_kvh + (hh - p.rope_qh - p.rope_kvh)) * HD;
+    }
+#pragma unroll
+    for (int i = 0; i < HD; i += 8) {
+      uint4 o;
+      __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
+      *reinterpret_cast<uint4*>(dst + i) = o;
     }
   }
 }
@@ -418,9 +483,9 @@ struct PairCfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = HALF * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN >= 256) ? 6 : 8;
+  static constexpr int STAGES = (BN >= 192) ? 6 : 8;
   static constexpr int SMEM = STAGES * STAGE_BYTES + OUT_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int TMEM_COLS = BN <= 128 ? 256 : 512;        // two accumulators of BN columns, a power of two
 };
 
 template <int BN, bool A_MN, bool B_MN>
@@ -555,7 +620,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_pair_kernel(const __grid_
       const int row = tm * (2 * BM) + (int)rank * BM + q * 32 + lane;
       const int n0 = tn * BN;
       const uint32_t taddr = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
-      if (p.c_tma) store_tile_tma<BN>(p, taddr, tm * (2 * BM) + (int)rank * BM + q * 32, n0, g, lane, out_stage + q * 8192, nstore);
+      if (!A_MN && !B_MN && p.rope_hd != 0) {
+        if (BN % 96 == 0 && p.rope_hd == 96) store_tile_rope<BN, (BN % 96 == 0 ? 96 : 32)>(p, taddr, row, n0);
+        else if (BN % 64 == 0 && p.rope_hd == 64) store_tile_rope<BN, (BN % 64 == 0 ? 64 : 32)>(p, taddr, row, n0);
+        else if (BN % 128 == 0 && p.rope_hd == 128) store_tile_rope<BN, (BN % 128 == 0 ? 128 : 32)>(p, taddr, row, n0);
+      }
+      else if (p.c_tma) store_tile_tma<BN>(p, taddr, tm * (2 * BM) + (int)rank * BM + q * 32, n0, g, lane, out_stage + q * 8192, nstore);
       else store_tile_direct<BN>(p, taddr, row, n0, g);
       tc_fence_before();
       // this accumulator buffer may be overwritten once the epilogue threads of BOTH CTAs have read it
@@ -684,8 +754,9 @@ int dispatch_major_pair(const Params& p, bool a_mn, bool b_mn, int sms, cudaStre
 
 extern "C" int loom_gemm_bf16(const LoomGemm* g, cudaStream_t stream) {
   if (g->nseg < 1 || g->nseg > MAX_SEG) return -1;
-  if (g->bn != 64 && g->bn != 128 && g->bn != 256) return -2;
+  if (g->bn != 64 && g->bn != 128 && g->bn != 192 && g->bn != 256) return -2;
   const bool pair = g->pair != 0;
+  if (g->bn == 192 && (!pair || g->a_mn_major || g->b_mn_major)) return -2;     // 192-wide tiles: K-major pair tiles only
   if (pair && (g->bn < 128 || g->gather_world > 1 || g->a_world > 1 || g->rs_world > 1)) return -10;
   const int b_box = pair ? g->bn / 2 : g->bn;      // B rows staged per CTA
   Params p;
@@ -706,12 +777,25 @@ extern "C" int loom_gemm_bf16(const LoomGemm* g, cudaStream_t stream) {
   p.c = g->c; p.ldc = g->ldc; p.ldc_head = g->ldc_head; p.bias = g->bias;
   p.M = g->M; p.n_per_head = g->N; p.heads = g->heads > 0 ? g->heads : 1;
   p.accumulate = g->accumulate; p.out_fp32 = g->out_fp32; p.status = g->status;
+  if (g->rope_hd != 0) {
+    const int hd = g->rope_hd;
+    if (!pair || a_mn || b_mn || p.heads != 1 || (hd != 64 && hd != 96 && hd != 128) || g->bn % hd || g->accumulate ||
+        g->N != (g->rope_qh + 2 * g->rope_kvh) * hd || g->rope_tc < 1 || g->M % g->rope_tc || g->rope_s < 0 ||
+        g->rope_s + g->rope_tc > g->rope_t || !g->rope_cos || !g->rope_sin || !g->rope_q || !g->rope_k || !g->rope_v ||
+        (g->rope_q_ld & 7) || (reinterpret_cast<uintptr_t>(g->rope_q) & 15) || (reinterpret_cast<uintptr_t>(g->rope_k) & 15) ||
+        (reinterpret_cast<uintptr_t>(g->rope_v) & 15) || (reinterpret_cast<uintptr_t>(g->rope_cos) & 15) ||
+        (reinterpret_cast<uintptr_t>(g->rope_sin) & 15))
+      return -11;
+    p.rope_hd = hd; p.rope_qh = g->rope_qh; p.rope_kvh = g->rope_kvh; p.rope_tc = g->rope_tc; p.rope_t = g->rope_t;
+    p.rope_s = g->rope_s; p.rope_q_ld = g->rope_q_ld; p.rope_cos = g->rope_cos; p.rope_sin = g->rope_sin;
+    p.rope_q = (__nv_bfloat16*)g->rope_q; p.rope_k = (__nv_bfloat16*)g->rope_k; p.rope_v = (__nv_bfloat16*)g->rope_v;
+  }
   {
     // staged TMA epilogue whenever C can be described to the TMA unit (LOOM_GEMM_EPILOGUE=direct turns it off)
     static int want = -1;
     if (want < 0) { const char* e = getenv("LOOM_GEMM_EPILOGUE"); want = (e != nullptr && e[0] == 'd') ? 0 : 1; }
     const long long es = g->out_fp32 ? 4 : 2;
-    const bool ok = want && g->rs_world <= 1 && (reinterpret_cast<uintptr_t>(g->c) & 15) == 0 && (g->ldc * es) % 16 == 0 &&
+    const bool ok = want && g->rope_hd == 0 && g->rs_world <= 1 && (reinterpret_cast<uintptr_t>(g->c) & 15) == 0 && (g->ldc * es) % 16 == 0 &&
                     (p.heads <= 1 || (g->ldc_head * es) % 16 == 0);
     p.c_tma = (ok && fill_c_map(&p.cmap, g->c, p.M, p.n_per_head, p.heads, g->ldc, g->ldc_head, g->out_fp32 != 0)) ? 1 : 0;
   }
@@ -756,8 +840,11 @@ extern "C" int loom_gemm_bf16(const LoomGemm* g, cudaStream_t stream) {
       default: return launch<256, false, false, true>(p, sms, stream);
     }
   }
-  if (pair) return g->bn == 128 ? dispatch_major_pair<128>(p, a_mn, b_mn, sms, stream)
-                                : dispatch_major_pair<256>(p, a_mn, b_mn, sms, stream);
+  if (pair) {
+    if (g->bn == 192) return launch_pair<192, false, false>(p, sms, stream);
+    return g->bn == 128 ? dispatch_major_pair<128>(p, a_mn, b_mn, sms, stream)
+                        : dispatch_major_pair<256>(p, a_mn, b_mn, sms, stream);
+  }
   switch (g->bn) {
     case 64: return dispatch_major<64>(p, a_mn, b_mn, sms, stream);
     case 128: return dispatch_major<128>(p, a_mn, b_mn, sms, stream);

@@ -48,9 +48,17 @@ typedef struct {
   const void* a_peer_ptr[8];
   int rs_world, rs_rank, rs_rows_per_rank;
   float* rs_out[8];
-  // pair != 0: 256 x bn tiles computed by clusters of two CTAs (tcgen05 cta_group::2); bn must be 128 or 256 and
+  // pair != 0: 256 x bn tiles computed by clusters of two CTAs (tcgen05 cta_group::2); bn must be 128, 192 or 256 and
   // none of the collective variants above may be active
   int pair;
+  // rope_hd != 0 (pair tiles, K-major operands, bn a multiple of rope_hd): the product is the [Q | K | V] projection
+  // of M = B * Tc tokens and the epilogue, instead of storing C, rotates the Q and K heads (rotate-half, fp32, tables
+  // [M, HD]) and writes rotated Q rows into rope_q (row pitch rope_q_ld), rotated K and plain V into the caches
+  // [B, T, KVH, HD] at positions rope_s + t.
+  int rope_hd, rope_qh, rope_kvh, rope_tc, rope_t, rope_s;
+  long long rope_q_ld;
+  const float* rope_cos; const float* rope_sin;
+  void* rope_q; void* rope_k; void* rope_v;
 } LoomGemm;
 
 // Cross-rank barrier on peer-mapped flag words (one int per rank in each rank's `flags` buffer): publish `epoch`

@@ -537,9 +537,12 @@ class FusedPlan:
             else:
                 self._project_state(proj[0], proj[1], hist_k, hist_v, proj[2], proj[3])
             # --- attention
-            qkv = self.lin(h, blk.attn.qkv_weight).view(B, Tc, -1)
             qkc = torch.empty(M, 3, d.qh, d.hd, dtype=self.adt, device=dev)     # sectors: rotated Q, A@K, A@V
-            K.rope_store(d, qkv, cos, sin, qkc, kc[bi], vc[bi], s)
+            if self.gather_spec is None:    # projection, rotation and cache write as one launch
+                K.qkv_rope(d, h, self.w(blk.attn.qkv_weight), cos, sin, qkc, kc[bi], vc[bi], s)
+            else:                           # a sharded weight is fetched by its GEMM on first use
+                qkv = self.lin(h, blk.attn.qkv_weight).view(B, Tc, -1)
+                K.rope_store(d, qkv, cos, sin, qkc, kc[bi], vc[bi], s)
             t["lse"] = K.attn_fwd(d, qkc, kc[bi], vc[bi], s, e, seg)
             t["qkc"] = qkc
             a = self.lin(qkc[:, 2].reshape(M, N), blk.attn.o.weight)

@@ -54,7 +54,8 @@ def _pick_bn(M: int, N: int, heads: int = 1) -> int:
     return 128 if N >= 128 else 64
 
 
-_FORCED_TILE = {"cta64": (64, 0), "cta128": (128, 0), "cta256": (256, 0), "pair128": (128, 1), "pair256": (256, 1)}
+_FORCED_TILE = {"cta64": (64, 0), "cta128": (128, 0), "cta256": (256, 0), "pair128": (128, 1), "pair192": (192, 1),
+                "pair256": (256, 1)}
 
 
 def _pick_tile(M: int, N: int, heads: int = 1, plain: bool = True, K: int = 0):
@@ -62,7 +63,7 @@ def _pick_tile(M: int, N: int, heads: int = 1, plain: bool = True, K: int = 0):
     (``tcgen05.mma.cta_group::2``): each SM stages 128 rows of A and only half of the tile's B columns per k-block.
     Measured on B200 against the single-CTA tiles (back-to-back launches, M = 2048): pair tiles are as fast or faster
     on every linear shape of the training step, 256-wide ones unless the reduction is long and only the 128-wide ones
-    give enough tiles to occupy the 74 SM pairs.  ``LOOM_GEMM_TILE`` (cta64|cta128|cta256|pair128|pair256) forces one
+    give enough tiles to occupy the 74 SM pairs.  ``LOOM_GEMM_TILE`` (cta64|cta128|cta256|pair128|pair192|pair256) forces one
     shape for sweeps; ``LOOM_GEMM_PAIR=0`` turns pair tiles off."""
     forced = os.environ.get("LOOM_GEMM_TILE")
     if forced in _FORCED_TILE:
@@ -95,6 +96,8 @@ def gemm(a_list: List[torch.Tensor], k_len: List[int], b, c: torch.Tensor, *, M:
             pair = 0
         else:
             bn, pair = _pick_tile(M, N, heads, plain, sum(int(k) for k in k_len))
+    if bn == 192 and (a_mn or b_mn or not pair):
+        bn = 128                                     # 192-wide tiles exist for K-major operands on pair tiles only
     ext.gemm(a_list, k_len, a_k0 or [0] * n, b_k0 or [0] * n, b if isinstance(b, (list, tuple)) else [b], a_mn, b_mn,
              c, bias, M, N, heads, accumulate,
              bn or _pick_bn(M, N, heads), swap_mn, status_word(c.device), peer_ptrs or [], gather_rank,
@@ -246,6 +249,24 @@ class CudaKernels(TorchKernels):
         else:
             gemm([x], [Kd], w, c, M=M, N=N, bias=b32)
         return c
+
+    def qkv_rope(self, d, x, w, cos, sin, qkc, kcache, vcache, s):
+        """The projection and the rotation as one launch: 192- or 256-wide CTA-pair tiles hold whole heads, and the
+        epilogue rotates Q and K in fp32 straight from the accumulator and writes the attention operand and the caches
+        (``csrc/gemm.cu: store_tile_rope``).  Off unless ``LOOM_QKV_ROPE=1``: on the 113M training step the per-row
+        stores of this epilogue cost what the separate rotation launch costs (145.8 against 145.2 ms per step)."""
+        B, Tc = cos.shape[:2]
+        M = x.shape[0]
+        bn = 192 if 192 % d.hd == 0 else (256 if 256 % d.hd == 0 else 0)
+        ok = (bn and d.hd in (64, 96, 128) and M >= 256 and M == B * Tc and _tma_ok(x) and _tma_ok(w)
+              and qkc.dtype == torch.bfloat16 and qkc.is_contiguous() and kcache.dtype == torch.bfloat16
+              and kcache.is_contiguous() and vcache.is_contiguous() and kcache.shape[0] == B
+              and os.environ.get("LOOM_QKV_ROPE", "0") == "1" and os.environ.get("LOOM_GEMM_PAIR", "1") != "0")
+        if not ok:
+            return super().qkv_rope(d, x, w, cos, sin, qkc, kcache, vcache, s)
+        native.ext().gemm_qkv_rope(x, w, None, _f32c(cos).view(M, d.hd), _f32c(sin).view(M, d.hd), qkc[:, 0].view(M, d.n),
+                                   kcache, vcache, Tc, int(s), d.qh, d.kvh, d.hd, bn, status_word(x.device))
+        native.count()
 
     def linear_small(self, x, w, bias=None, out=None, out_dtype=None):
         """``x @ w^T (+ bias)`` for a handful of rows (the decode step): up to 16 rows go through the weight-streaming

@@ -260,7 +260,7 @@ def time_burst(fn, n: int = 20) -> float:
     return a.elapsed_time(b) / n
 
 
-def gemm_table(iters: int, warmup: int, variants=("auto", "cta64", "cta128", "cta256", "pair128", "pair256")) -> None:
+def gemm_table(iters: int, warmup: int, variants=("auto", "cta64", "cta128", "cta256", "pair128", "pair192", "pair256")) -> None:
     """Every forward-linear shape of the step: this repository's kernel with each tile shape, and the library GEMM
     (``torch.nn.functional.linear`` -> cuBLAS) timed in the same run the same way.  Two timings per entry: one launch
     after an L2 flush (cold), and back-to-back launches (warm)."""

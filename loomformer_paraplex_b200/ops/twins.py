@@ -137,6 +137,12 @@ class TorchKernels:
         kcache[:, s:s + Tc] = R.apply_rope(k.view(B, Tc, d.kvh, d.hd), c, s_)
         vcache[:, s:s + Tc] = v.view(B, Tc, d.kvh, d.hd)
 
+    def qkv_rope(self, d, x, w, cos, sin, qkc, kcache, vcache, s):
+        """[Q | K | V] projection of ``x`` [B*Tc, N] followed by :meth:`rope_store`: rotated Q into ``qkc[:, 0]``, rotated
+        K and V into the caches at rows [s, s+Tc)."""
+        B, Tc = cos.shape[:2]
+        self.rope_store(d, self.linear(x, w).view(B, Tc, -1), cos, sin, qkc, kcache, vcache, s)
+
     def rope_bwd(self, d, dq_attn, dqkc, dkc, dvc, s, e, cos, sin, out_dtype):
         """Inverse rotation of the q / k gradients and packing into d(qkv) [B,Tc,N+2KV].  The q gradient is the
         attention part plus sector 0 of ``dqkc``; k/v gradients are rows [s,e) of the fp32 cache gradients."""

@@ -181,3 +181,52 @@ def test_grouped_wgrad_queue_equals_per_chunk_products():
         k.check_status(g.device)
         assert not ck.fallbacks and not ck._wq
         assert _rel(g, ref) < 1e-2 and _rel(g3, ref3) < 1e-2
+
+
+@pytest.mark.parametrize("qh,kvh,hd,B,Tc,T,s", [(8, 2, 96, 4, 128, 384, 128), (15, 5, 64, 3, 100, 300, 200), (4, 2, 128, 2, 192, 192, 0),
+                                               (8, 2, 96, 16, 128, 2048, 1920)])
+def test_qkv_projection_with_rope_epilogue(qh, kvh, hd, B, Tc, T, s, monkeypatch):
+    """The [Q | K | V] projection whose epilogue rotates Q and K and writes the attention operand and the caches, against
+    the projection followed by the PyTorch statement of RoPE + cache write.  Rows of the caches outside [s, s+Tc) and
+    the other two sectors of the operand buffer must stay untouched."""
+    from types import SimpleNamespace
+    from loomformer_paraplex_b200.ops.twins import TorchKernels
+    monkeypatch.setenv("LOOM_QKV_ROPE", "1")
+    k = _k()
+    torch.manual_seed(9)
+    n, kv = qh * hd, kvh * hd
+    d = SimpleNamespace(qh=qh, kvh=kvh, hd=hd, n=n, kv_dim=kv)
+    M, K_in = B * Tc, 256
+    x = torch.randn(M, K_in, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(n + 2 * kv, K_in, device="cuda") * 0.06).to(torch.bfloat16)
+    cos, sin = torch.randn(B, Tc, hd, device="cuda"), torch.randn(B, Tc, hd, device="cuda")
+    ck, tk = k.CudaKernels(), TorchKernels()
+    qkc1 = torch.full((M, 3, qh, hd), 7.0, device="cuda", dtype=torch.bfloat16)
+    kc1 = torch.full((B, T, kvh, hd), 5.0, device="cuda", dtype=torch.bfloat16)
+    vc1 = torch.full((B, T, kvh, hd), 3.0, device="cuda", dtype=torch.bfloat16)
+    before = k.native.launches() if hasattr(k.native, "launches") else None
+    ck.qkv_rope(d, x, w, cos, sin, qkc1, kc1, vc1, s)
+    k.check_status(x.device)
+    assert not ck.fallbacks, ck.fallbacks
+    if before is not None:
+        assert k.native.launches() - before == 1            # one launch: the fused path ran
+    qkc2, kc2, vc2 = torch.full_like(qkc1, 7.0).float(), torch.full_like(kc1, 5.0).float(), torch.full_like(vc1, 3.0).float()
+    tk.qkv_rope(d, x.float(), w.float(), cos, sin, qkc2, kc2, vc2, s)
+    assert _rel(qkc1[:, 0], qkc2[:, 0]) < 1.5e-2
+    assert _rel(kc1[:, s:s + Tc], kc2[:, s:s + Tc]) < 1.5e-2 and _rel(vc1[:, s:s + Tc], vc2[:, s:s + Tc]) < 1.5e-2
+    assert bool((qkc1[:, 1:] == 7.0).all())
+    keep = torch.ones(T, dtype=torch.bool, device="cuda"); keep[s:s + Tc] = False
+    assert bool((kc1[:, keep] == 5.0).all()) and bool((vc1[:, keep] == 3.0).all())
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 1152, 768), (520, 200, 136), (256, 1600, 960)])
+def test_pair_tiles_192_wide(M, N, K):
+    k = _k()
+    torch.manual_seed(10)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda")
+    c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    k.gemm([x], [K], w, c, M=M, N=N, bias=bias, bn=192, pair=1)
+    k.check_status(c.device)
+    assert _rel(c, x.float() @ w.float().t() + bias) < 1e-2
