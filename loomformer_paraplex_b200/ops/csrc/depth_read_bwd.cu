@@ -19,6 +19,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include "loom_c_api.h"
 
 namespace {
@@ -204,6 +205,187 @@ __global__ void __launch_bounds__(256) dread_slot_bwd_kernel(const float* __rest
   }
 }
 
+// Same kernel with G * 4 NV == HD exactly: a lane owns NV vectors of four dims (12 dims of a 96-wide head on 8 lanes
+// instead of 8 dims on 16 lanes of which 4 idle), so no lane is idle, a warp serves four rows instead of two, the
+// reductions are one shuffle level shorter and the per-(row, sublayer) overhead (exponential, addressing, shuffles) is
+// spread over half again as many dims.  The loop body below is about 125 instructions per (row, sublayer) for 8 lanes
+// against about 160 for 16 lanes above.
+__device__ __forceinline__ void unpack4(const uint2& u, float* f) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+  const float2 a = __bfloat1622float2(p[0]), b = __bfloat1622float2(p[1]);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+__device__ __forceinline__ uint2 pack4(const float* f) {
+  uint2 u;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&u);
+  p[0] = __floats2bfloat162_rn(f[0], f[1]);
+  p[1] = __floats2bfloat162_rn(f[2], f[3]);
+  return u;
+}
+
+template <int G, int NV, int MAX_PAIRS>
+__global__ void __launch_bounds__(256, 2) dread_slot_bwd_wide_kernel(
+    const float* __restrict__ q_all, const bf16* __restrict__ hk, const bf16* __restrict__ hv, const bf16* __restrict__ dm_all,
+    const float* __restrict__ lse_all, const float* __restrict__ dd_all, bf16* __restrict__ dk, bf16* __restrict__ dv,
+    float* __restrict__ gq_all, int sub0, int S, int M, int QH, int HD, float scale, long long in_ld, long long out_ld) {
+  constexpr int DPL = 4 * NV;
+  constexpr int NGRP = 256 / G;
+  constexpr int TILE = 2 * NGRP;              // rows per tile: every group takes two
+  extern __shared__ float sh[];               // [nsub][HD] queries | [TILE][nsub] dsc | [TILE][HD] k rows
+  const int g = blockIdx.y;
+  const int nsub = S - sub0;
+  float* sq = sh;
+  float* sd = sq + nsub * HD;
+  float* sk = sd + TILE * nsub;
+  for (int i = threadIdx.x; i < nsub * HD; i += blockDim.x) {
+    const int jj = i / HD, c = i % HD;
+    sq[i] = q_all[((long long)(sub0 + jj) * QH + g) * HD + c];
+  }
+  float gacc[MAX_PAIRS];
+#pragma unroll
+  for (int i = 0; i < MAX_PAIRS; ++i) gacc[i] = 0.f;
+  __syncthreads();
+  const int l = threadIdx.x % G, grp = threadIdx.x / G;
+  const long long MQ = (long long)M * QH;
+  const int npairs = nsub * HD;
+  for (int m0 = blockIdx.x * TILE; m0 < M; m0 += gridDim.x * TILE) {
+#pragma unroll 1
+    for (int rr = 0; rr < 2; ++rr) {
+      const int row = grp * 2 + rr;
+      const int m = m0 + row;
+      const bool live = m < M;                 // uniform within a group
+      const long long rh = (long long)(live ? m : 0) * QH + g;
+      const long long base = rh * HD + l * DPL;                                   // dm rows are densely packed
+      const long long hoff = (long long)g * HD + l * DPL;
+      const long long ibase = (long long)(live ? m : 0) * in_ld + hoff, obase = (long long)(live ? m : 0) * out_ld + hoff;
+      float kf[DPL], vf[DPL], ak[DPL], av[DPL];
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) { kf[i] = 0.f; vf[i] = 0.f; ak[i] = 0.f; av[i] = 0.f; }
+      if (live) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          unpack4(*reinterpret_cast<const uint2*>(hk + ibase + 4 * v), kf + 4 * v);
+          unpack4(*reinterpret_cast<const uint2*>(hv + ibase + 4 * v), vf + 4 * v);
+        }
+      }
+#pragma unroll
+      for (int v = 0; v < NV; ++v)
+        *reinterpret_cast<float4*>(sk + row * HD + l * DPL + 4 * v) = make_float4(kf[4 * v], kf[4 * v + 1], kf[4 * v + 2], kf[4 * v + 3]);
+      // the loop over reading sublayers is one dependent chain of load -> reduce -> exp per sublayer: the loads of PF
+      // sublayers are issued together
+      constexpr int PF = 2;
+      for (int j0 = 0; j0 < nsub; j0 += PF) {
+        uint2 raw[PF][NV];
+        float lse_v[PF], dd_v[PF];
+#pragma unroll
+        for (int u = 0; u < PF; ++u) {
+          const int jj = j0 + u;
+          const long long so = (long long)(sub0 + (jj < nsub ? jj : nsub - 1));
+#pragma unroll
+          for (int v = 0; v < NV; ++v)
+            raw[u][v] = live ? *reinterpret_cast<const uint2*>(dm_all + so * MQ * HD + base + 4 * v) : make_uint2(0u, 0u);
+          lse_v[u] = live ? lse_all[so * MQ + rh] : 0.f;
+          dd_v[u] = live ? dd_all[so * MQ + rh] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < PF; ++u) {
+          const int jj = j0 + u;
+          if (jj < nsub) {                               // uniform across the block
+            float dmf[DPL], qv[DPL];
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+              unpack4(raw[u][v], dmf + 4 * v);
+              const float4 qq = *reinterpret_cast<const float4*>(sq + jj * HD + l * DPL + 4 * v);
+              qv[4 * v] = qq.x; qv[4 * v + 1] = qq.y; qv[4 * v + 2] = qq.z; qv[4 * v + 3] = qq.w;
+            }
+            float d = 0.f, dvv = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) { d += qv[i] * kf[i]; dvv += dmf[i] * vf[i]; }
+#pragma unroll
+            for (int o = G / 2; o > 0; o >>= 1) {
+              d += __shfl_xor_sync(0xffffffffu, d, o, G);
+              dvv += __shfl_xor_sync(0xffffffffu, dvv, o, G);
+            }
+            float w = 0.f, dsc = 0.f;
+            if (live) {
+              w = __expf(d * scale - lse_v[u]);
+              dsc = w * (dvv - dd_v[u]) * scale;
+            }
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) { ak[i] += dsc * qv[i]; av[i] += w * dmf[i]; }
+            if (l == 0) sd[row * nsub + jj] = dsc;
+          }
+        }
+      }
+      if (live) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          *reinterpret_cast<uint2*>(dk + obase + 4 * v) = pack4(ak + 4 * v);
+          *reinterpret_cast<uint2*>(dv + obase + 4 * v) = pack4(av + 4 * v);
+        }
+      }
+    }
+    __syncthreads();
+    // phase 2: query-gradient partials of this tile
+#pragma unroll
+    for (int pi = 0; pi < MAX_PAIRS; ++pi) {
+      const int pidx = threadIdx.x + pi * 256;
+      if (pidx < npairs) {
+        const int jj = pidx / HD, c = pidx % HD;
+        float a = 0.f;
+#pragma unroll 8
+        for (int r = 0; r < TILE; ++r) a += sd[r * nsub + jj] * sk[r * HD + c];
+        gacc[pi] += a;
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int pi = 0; pi < MAX_PAIRS; ++pi) {
+    const int pidx = threadIdx.x + pi * 256;
+    if (pidx < npairs && gacc[pi] != 0.f) {
+      const int jj = pidx / HD, c = pidx % HD;
+      atomicAdd(gq_all + ((long long)(sub0 + jj) * QH + g) * HD + c, gacc[pi]);
+    }
+  }
+}
+
+template <int G, int NV, int MAX_PAIRS>
+int launch_slot_wide_mp(const float* q_all, const void* hk, const void* hv, const void* dm_all, const float* lse_all,
+                        const float* dd_all, void* dk, void* dv, float* gq_all, int sub0, int S, int M, int QH, int HD,
+                        long long in_ld, long long out_ld, cudaStream_t st) {
+  const int nsub = S - sub0;
+  constexpr int TILE = 2 * (256 / G);
+  const size_t shm = ((size_t)nsub * HD + (size_t)TILE * nsub + (size_t)TILE * HD) * sizeof(float);
+  if (shm > 100 * 1024) return -2;
+  if (shm > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(dread_slot_bwd_wide_kernel<G, NV, MAX_PAIRS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shm);
+    if (e != cudaSuccess) return (int)e;
+  }
+  static int sms = 0;
+  if (sms == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+  int bx = (sms * 2 + QH - 1) / QH;                 // two resident blocks per SM over all heads
+  const int need = (M + TILE - 1) / TILE;
+  if (bx > need) bx = need;
+  if (bx < 1) bx = 1;
+  dim3 grid(bx, QH);
+  dread_slot_bwd_wide_kernel<G, NV, MAX_PAIRS><<<grid, 256, shm, st>>>(q_all, (const bf16*)hk, (const bf16*)hv, (const bf16*)dm_all,
+                                                                        lse_all, dd_all, (bf16*)dk, (bf16*)dv, gq_all, sub0, S, M,
+                                                                        QH, HD, rsqrtf((float)HD), in_ld, out_ld);
+  return (int)cudaGetLastError();
+}
+
+// -3: this head width has no (lanes, dims per lane) split of the wide kernel, or the sublayer count is too large for it
+template <int G, int NV>
+int launch_slot_wide(const float* q_all, const void* hk, const void* hv, const void* dm_all, const float* lse_all,
+                     const float* dd_all, void* dk, void* dv, float* gq_all, int sub0, int S, int M, int QH, int HD,
+                     long long in_ld, long long out_ld, cudaStream_t st) {
+  const long long pairs = (long long)(S - sub0) * HD;
+  if (pairs <= 256LL * 10)
+    return launch_slot_wide_mp<G, NV, 10>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, in_ld, out_ld, st);
+  return -3;
+}
+
 template <int G>
 int launch_stage(const void* a, const void* b, const void* mo, void* dm, float* dd, const float* lse_in, float* lse_out,
                  long long MQ, int HD, cudaStream_t st) {
@@ -267,6 +449,20 @@ extern "C" int loom_dread_slot_bwd(const float* q_all, const void* hk, const voi
                                    int S, int M, int QH, int HD, long long in_ld, long long out_ld, cudaStream_t st) {
   if (HD % 8 || HD > 128 || sub0 < 0 || sub0 >= S) return -1;
   if (in_ld < (long long)QH * HD || out_ld < (long long)QH * HD || in_ld % 8 || out_ld % 8) return -1;
+  {
+    // head widths that split exactly into 8 / 4 / 2 lanes of 8, 12 or 16 dims take the wide kernel (LOOM_DREAD_BWD=narrow
+    // keeps the 8-dims-per-lane kernel)
+    static int narrow = -1;
+    if (narrow < 0) { const char* e = getenv("LOOM_DREAD_BWD"); narrow = (e != nullptr && e[0] == 'n') ? 1 : 0; }
+    int rc = -3;
+    if (!narrow) {
+#define WIDE(G_, NV_) rc = launch_slot_wide<G_, NV_>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, in_ld, out_ld, st)
+      if (HD == 96) WIDE(8, 3); else if (HD == 64) WIDE(8, 2); else if (HD == 128) WIDE(8, 4); else if (HD == 48) WIDE(4, 3);
+      else if (HD == 32) WIDE(4, 2); else if (HD == 24) WIDE(2, 3);
+#undef WIDE
+    }
+    if (rc != -3) return rc;
+  }
   const int chunks = HD / 8;
   if (chunks <= 2) return launch_slot<2>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, in_ld, out_ld, st);
   if (chunks <= 4) return launch_slot<4>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, in_ld, out_ld, st);

@@ -289,10 +289,12 @@ def test_attention_backward(hd, qh, kvh, Tc, s):
     _close(dv1.view(B, T, kvh, g, hd).sum(3), dv2, 3e-2, "dv")
 
 
-@pytest.mark.parametrize("hd,qh,S", [(96, 8, 6), (32, 4, 6), (64, 3, 65)])
+@pytest.mark.parametrize("hd,qh,S", [(96, 8, 6), (32, 4, 6), (64, 3, 65), (96, 8, 20), (64, 15, 20), (128, 2, 8), (48, 4, 6), (24, 6, 9),
+                                     (40, 2, 5)])
 def test_depth_read_backward_per_slot(hd, qh, S):
     """Staged per-slot backward equals the sum of per-sublayer contributions evaluated in fp32 (S=65 is the 32-layer
-    stack, which takes the kernel's 20-pairs-per-thread instantiation)."""
+    stack, which takes the 20-pairs-per-thread instantiation of the 8-dims-per-lane kernel; head widths 96 / 64 / 128 /
+    48 / 32 / 24 take the kernel whose lanes own 12, 8 or 16 dims; 40 has no such split)."""
     ck, tk = _sets()
     d = _dims(qh=qh, hd=hd, kvh=qh)
     M = 200
