@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include "launch_util.cuh"
 #include "loom_c_api.h"
 
@@ -211,6 +212,78 @@ __global__ void __launch_bounds__(256) dread_fwd_kernel(const float* __restrict_
 #pragma unroll
     for (int i = 0; i < 8; ++i) o8[i] = acc[i] * inv;
     *reinterpret_cast<uint4*>(out + base) = pack8(o8);
+  }
+  if (l == 0) lse[gid] = mx + __logf(den);
+}
+
+// The same read with G * 4 NV == HD exactly: a lane owns NV vectors of four dims (12 dims of a 96-wide head on 8 lanes
+// instead of 8 dims on 16 lanes of which 4 idle), so a warp serves four (row, head) pairs instead of two and the
+// per-slot chain (reduce, two exponentials) is shared by half again as many dims.
+__device__ __forceinline__ void unpack4(const uint2& u, float* f) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+  const float2 a = __bfloat1622float2(p[0]), b = __bfloat1622float2(p[1]);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+template <int G, int NV>
+__global__ void __launch_bounds__(256) dread_fwd_wide_kernel(const float* __restrict__ q, const bf16* __restrict__ hk,
+                                                             const bf16* __restrict__ hv, bf16* __restrict__ out,
+                                                             float* __restrict__ lse, int n, long long MQ, int QH, int HD,
+                                                             float scale, long long slot_stride, long long row_stride) {
+  constexpr int DPL = 4 * NV;
+  if (MQ <= 4096) loom::pdl_trigger();        // decode-sized problem: a dependent launched programmatically may start its prologue now
+  const long long gid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / G;
+  const int l = threadIdx.x % G;
+  if (gid >= MQ) return;                    // whole G-lane groups leave together
+  const unsigned mask = __activemask();
+  const int g = (int)(gid % QH);
+  float qv[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) qv[i] = q[g * HD + l * DPL + i] * scale;
+  const long long base = gid * HD + l * DPL;
+  const long long hbase = (gid / QH) * row_stride + (long long)g * HD + l * DPL;
+  float mx = -INFINITY, den = 0.f, acc[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+  constexpr int PF = 4;
+  for (int s0 = 0; s0 < n; s0 += PF) {
+    uint2 rk[PF][NV], rv[PF][NV];
+#pragma unroll
+    for (int u = 0; u < PF; ++u) {
+      const int s = (s0 + u < n) ? s0 + u : n - 1;
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        rk[u][v] = *reinterpret_cast<const uint2*>(hk + s * slot_stride + hbase + 4 * v);
+        rv[u][v] = *reinterpret_cast<const uint2*>(hv + s * slot_stride + hbase + 4 * v);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < PF; ++u) {
+      if (s0 + u < n) {
+        float kf[DPL], vf[DPL];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) { unpack4(rk[u][v], kf + 4 * v); unpack4(rv[u][v], vf + 4 * v); }
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) d += qv[i] * kf[i];
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) d += __shfl_xor_sync(mask, d, o, G);
+        const float nm = fmaxf(mx, d);
+        const float corr = __expf(mx - nm), p = __expf(d - nm);
+        den = den * corr + p;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[i] = acc[i] * corr + p * vf[i];
+        mx = nm;
+      }
+    }
+  }
+  const float inv = 1.f / den;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    uint2 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+    o2[0] = __floats2bfloat162_rn(acc[4 * v] * inv, acc[4 * v + 1] * inv);
+    o2[1] = __floats2bfloat162_rn(acc[4 * v + 2] * inv, acc[4 * v + 3] * inv);
+    *reinterpret_cast<uint2*>(out + base + 4 * v) = o;
   }
   if (l == 0) lse[gid] = mx + __logf(den);
 }
@@ -637,6 +710,21 @@ extern "C" int loom_dread(int bwd, const float* q, const void* hk, const void* h
   if (slot_stride <= 0) { slot_stride = MQ * HD; row_stride = (long long)QH * HD; }     // densely packed history
   if (slot_stride % 8 || row_stride % 8) return -1;                                    // 16-byte vector loads
   if (bwd && (slot_stride != MQ * HD || row_stride != (long long)QH * HD)) return -1;   // the legacy backward is dense-only
+  if (!bwd) {
+    // head widths that split exactly into 8 / 4 / 2 lanes of 8, 12 or 16 dims (LOOM_DREAD_FWD=narrow keeps 8 dims per lane)
+    static int narrow = -1;
+    if (narrow < 0) { const char* e = getenv("LOOM_DREAD_FWD"); narrow = (e != nullptr && e[0] == 'n') ? 1 : 0; }
+    const float scale = rsqrtf((float)HD);
+#define WIDE_F(G_, NV_) do { const long long threads = MQ * G_; \
+      dread_fwd_wide_kernel<G_, NV_><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(q, (const bf16*)hk, (const bf16*)hv, (bf16*)out, lse, \
+                                                                                       n, MQ, QH, HD, scale, slot_stride, row_stride); \
+      return (int)cudaGetLastError(); } while (0)
+    if (!narrow) {
+      if (HD == 96) WIDE_F(8, 3); if (HD == 64) WIDE_F(8, 2); if (HD == 128) WIDE_F(8, 4); if (HD == 48) WIDE_F(4, 3);
+      if (HD == 32) WIDE_F(4, 2); if (HD == 24) WIDE_F(2, 3);
+    }
+#undef WIDE_F
+  }
   const int chunks = HD / 8;
   if (chunks <= 2) return dread_launch<2>(bwd, q, hk, hv, out, lse, dm, dhk, dhv, gq, n, MQ, QH, HD, slot_stride, row_stride, st);
   if (chunks <= 4) return dread_launch<4>(bwd, q, hk, hv, out, lse, dm, dhk, dhv, gq, n, MQ, QH, HD, slot_stride, row_stride, st);

@@ -56,7 +56,7 @@ def test_rope_store_and_bwd(hd):
     _close(a, b, 1e-2)
 
 
-@pytest.mark.parametrize("hd,qh", [(32, 4), (64, 15), (96, 8)])
+@pytest.mark.parametrize("hd,qh", [(32, 4), (64, 15), (96, 8), (128, 2), (48, 4), (24, 6), (40, 2)])
 def test_depth_read(hd, qh):
     ck, tk = _sets()
     d = _dims(qh=qh, hd=hd, kvh=1)
