@@ -223,7 +223,44 @@ __device__ __forceinline__ uint2 pack4(const float* f) {
   return u;
 }
 
-template <int G, int NV, int MAX_PAIRS>
+// staging with G * 4 NV == HD exactly (no idle lanes, see the slot kernel below)
+template <int G, int NV>
+__global__ void __launch_bounds__(256) dread_stage_wide_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b,
+                                                               const bf16* __restrict__ mo, bf16* __restrict__ dm,
+                                                               float* __restrict__ dd, const float* __restrict__ lse_in,
+                                                               float* __restrict__ lse_out, long long MQ, int HD) {
+  constexpr int DPL = 4 * NV;
+  const long long gid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / G;
+  const int l = threadIdx.x % G;
+  if (gid >= MQ) return;
+  const unsigned mask = __activemask();
+  const long long base = gid * HD + l * DPL;
+  float s = 0.f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    float x[4], y[4], m[4];
+    unpack4(*reinterpret_cast<const uint2*>(a + base + 4 * v), x);
+    if (b) {
+      unpack4(*reinterpret_cast<const uint2*>(b + base + 4 * v), y);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) x[i] += y[i];
+    }
+    const uint2 packed = pack4(x);
+    *reinterpret_cast<uint2*>(dm + base + 4 * v) = packed;
+    unpack4(packed, x);                       // dd must see the rounded values the slot kernel will read
+    unpack4(*reinterpret_cast<const uint2*>(mo + base + 4 * v), m);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s += x[i] * m[i];
+  }
+#pragma unroll
+  for (int o = G / 2; o > 0; o >>= 1) s += __shfl_xor_sync(mask, s, o, G);
+  if (l == 0) {
+    dd[gid] = s;
+    if (lse_in) lse_out[gid] = lse_in[gid];
+  }
+}
+
+template <int G, int NV>
 __global__ void __launch_bounds__(256, 2) dread_slot_bwd_wide_kernel(
     const float* __restrict__ q_all, const bf16* __restrict__ hk, const bf16* __restrict__ hv, const bf16* __restrict__ dm_all,
     const float* __restrict__ lse_all, const float* __restrict__ dd_all, bf16* __restrict__ dk, bf16* __restrict__ dv,
@@ -231,19 +268,28 @@ __global__ void __launch_bounds__(256, 2) dread_slot_bwd_wide_kernel(
   constexpr int DPL = 4 * NV;
   constexpr int NGRP = 256 / G;
   constexpr int TILE = 2 * NGRP;              // rows per tile: every group takes two
-  extern __shared__ float sh[];               // [nsub][HD] queries | [TILE][nsub] dsc | [TILE][HD] k rows
+  constexpr int NACC = 20;                    // query-gradient accumulators per thread
+  extern __shared__ float sh[];               // [nsub][HD] queries | [TILE][nsubp] dsc | [TILE][HD] k rows
   const int g = blockIdx.y;
   const int nsub = S - sub0;
+  const int nsubp = (nsub + 3) & ~3;          // dsc rows padded to whole float4s (the pad stays zero)
   float* sq = sh;
   float* sd = sq + nsub * HD;
-  float* sk = sd + TILE * nsub;
+  float* sk = sd + TILE * nsubp;
   for (int i = threadIdx.x; i < nsub * HD; i += blockDim.x) {
     const int jj = i / HD, c = i % HD;
     sq[i] = q_all[((long long)(sub0 + jj) * QH + g) * HD + c];
   }
-  float gacc[MAX_PAIRS];
+  for (int i = threadIdx.x; i < TILE * nsubp; i += blockDim.x) sd[i] = 0.f;
+  float gacc[NACC];
 #pragma unroll
-  for (int i = 0; i < MAX_PAIRS; ++i) gacc[i] = 0.f;
+  for (int i = 0; i < NACC; ++i) gacc[i] = 0.f;
+  // Query gradients gq[sub, c] = sum_rows dsc[row, sub] k[row, c].  Up to 20 reading sublayers: a thread owns one dim c
+  // and a share of the tile's rows and keeps one accumulator per sublayer, so a k value is loaded once per row and the
+  // dsc row arrives as float4s (one shared-memory load per four multiply-adds).  More sublayers (deep, narrow stacks):
+  // a thread owns up to 20 (sublayer, dim) pairs, two loads per multiply-add.
+  const bool per_dim = nsub <= NACC;
+  const int parts = 256 / HD, part = threadIdx.x / HD, cdim = threadIdx.x - part * HD;
   __syncthreads();
   const int l = threadIdx.x % G, grp = threadIdx.x / G;
   const long long MQ = (long long)M * QH;
@@ -313,7 +359,7 @@ __global__ void __launch_bounds__(256, 2) dread_slot_bwd_wide_kernel(
             }
 #pragma unroll
             for (int i = 0; i < DPL; ++i) { ak[i] += dsc * qv[i]; av[i] += w * dmf[i]; }
-            if (l == 0) sd[row * nsub + jj] = dsc;
+            if (l == 0) sd[row * nsubp + jj] = dsc;
           }
         }
       }
@@ -327,40 +373,70 @@ __global__ void __launch_bounds__(256, 2) dread_slot_bwd_wide_kernel(
     }
     __syncthreads();
     // phase 2: query-gradient partials of this tile
+    if (per_dim) {
+      if (part < parts) {
+        for (int r = part; r < TILE; r += parts) {
+          const float kv = sk[r * HD + cdim];
+          const float4* dr = reinterpret_cast<const float4*>(sd + r * nsubp);
 #pragma unroll
-    for (int pi = 0; pi < MAX_PAIRS; ++pi) {
-      const int pidx = threadIdx.x + pi * 256;
-      if (pidx < npairs) {
-        const int jj = pidx / HD, c = pidx % HD;
-        float a = 0.f;
+          for (int j4 = 0; j4 < NACC / 4; ++j4) {
+            if (4 * j4 < nsub) {
+              const float4 s4 = dr[j4];
+              gacc[4 * j4] += s4.x * kv; gacc[4 * j4 + 1] += s4.y * kv; gacc[4 * j4 + 2] += s4.z * kv; gacc[4 * j4 + 3] += s4.w * kv;
+            }
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int pi = 0; pi < NACC; ++pi) {
+        const int pidx = threadIdx.x + pi * 256;
+        if (pidx < npairs) {
+          const int jj = pidx / HD, c = pidx % HD;
+          float a = 0.f;
 #pragma unroll 8
-        for (int r = 0; r < TILE; ++r) a += sd[r * nsub + jj] * sk[r * HD + c];
-        gacc[pi] += a;
+          for (int r = 0; r < TILE; ++r) a += sd[r * nsubp + jj] * sk[r * HD + c];
+          gacc[pi] += a;
+        }
       }
     }
     __syncthreads();
   }
+  if (per_dim) {
+    if (part < parts) {
 #pragma unroll
-  for (int pi = 0; pi < MAX_PAIRS; ++pi) {
-    const int pidx = threadIdx.x + pi * 256;
-    if (pidx < npairs && gacc[pi] != 0.f) {
-      const int jj = pidx / HD, c = pidx % HD;
-      atomicAdd(gq_all + ((long long)(sub0 + jj) * QH + g) * HD + c, gacc[pi]);
+      for (int jj = 0; jj < NACC; ++jj)
+        if (jj < nsub && gacc[jj] != 0.f) atomicAdd(gq_all + ((long long)(sub0 + jj) * QH + g) * HD + cdim, gacc[jj]);
+    }
+  } else {
+#pragma unroll
+    for (int pi = 0; pi < NACC; ++pi) {
+      const int pidx = threadIdx.x + pi * 256;
+      if (pidx < npairs && gacc[pi] != 0.f) {
+        const int jj = pidx / HD, c = pidx % HD;
+        atomicAdd(gq_all + ((long long)(sub0 + jj) * QH + g) * HD + c, gacc[pi]);
+      }
     }
   }
 }
 
-template <int G, int NV, int MAX_PAIRS>
-int launch_slot_wide_mp(const float* q_all, const void* hk, const void* hv, const void* dm_all, const float* lse_all,
-                        const float* dd_all, void* dk, void* dv, float* gq_all, int sub0, int S, int M, int QH, int HD,
-                        long long in_ld, long long out_ld, cudaStream_t st) {
-  const int nsub = S - sub0;
+// -3: the sublayer count is too large for this kernel
+template <int G, int NV>
+int launch_slot_wide(const float* q_all, const void* hk, const void* hv, const void* dm_all, const float* lse_all,
+                     const float* dd_all, void* dk, void* dv, float* gq_all, int sub0, int S, int M, int QH, int HD,
+                     long long in_ld, long long out_ld, cudaStream_t st) {
+  const int nsub = S - sub0, nsubp = (nsub + 3) & ~3;
+  if ((long long)nsub * HD > 256LL * 20) return -3;
   constexpr int TILE = 2 * (256 / G);
-  const size_t shm = ((size_t)nsub * HD + (size_t)TILE * nsub + (size_t)TILE * HD) * sizeof(float);
-  if (shm > 100 * 1024) return -2;
+  const size_t shm = ((size_t)nsub * HD + (size_t)TILE * nsubp + (size_t)TILE * HD) * sizeof(float);
+  if (shm > 100 * 1024) return -3;
   if (shm > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(dread_slot_bwd_wide_kernel<G, NV, MAX_PAIRS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shm);
-    if (e != cudaSuccess) return (int)e;
+    static size_t configured = 0;
+    if (shm > configured) {
+      cudaError_t e = cudaFuncSetAttribute(dread_slot_bwd_wide_kernel<G, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shm);
+      if (e != cudaSuccess) return (int)e;
+      configured = shm;
+    }
   }
   static int sms = 0;
   if (sms == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
@@ -369,21 +445,10 @@ int launch_slot_wide_mp(const float* q_all, const void* hk, const void* hv, cons
   if (bx > need) bx = need;
   if (bx < 1) bx = 1;
   dim3 grid(bx, QH);
-  dread_slot_bwd_wide_kernel<G, NV, MAX_PAIRS><<<grid, 256, shm, st>>>(q_all, (const bf16*)hk, (const bf16*)hv, (const bf16*)dm_all,
-                                                                        lse_all, dd_all, (bf16*)dk, (bf16*)dv, gq_all, sub0, S, M,
-                                                                        QH, HD, rsqrtf((float)HD), in_ld, out_ld);
+  dread_slot_bwd_wide_kernel<G, NV><<<grid, 256, shm, st>>>(q_all, (const bf16*)hk, (const bf16*)hv, (const bf16*)dm_all, lse_all,
+                                                           dd_all, (bf16*)dk, (bf16*)dv, gq_all, sub0, S, M, QH, HD,
+                                                           rsqrtf((float)HD), in_ld, out_ld);
   return (int)cudaGetLastError();
-}
-
-// -3: this head width has no (lanes, dims per lane) split of the wide kernel, or the sublayer count is too large for it
-template <int G, int NV>
-int launch_slot_wide(const float* q_all, const void* hk, const void* hv, const void* dm_all, const float* lse_all,
-                     const float* dd_all, void* dk, void* dv, float* gq_all, int sub0, int S, int M, int QH, int HD,
-                     long long in_ld, long long out_ld, cudaStream_t st) {
-  const long long pairs = (long long)(S - sub0) * HD;
-  if (pairs <= 256LL * 10)
-    return launch_slot_wide_mp<G, NV, 10>(q_all, hk, hv, dm_all, lse_all, dd_all, dk, dv, gq_all, sub0, S, M, QH, HD, in_ld, out_ld, st);
-  return -3;
 }
 
 template <int G>
@@ -437,6 +502,13 @@ int launch_slot(const float* q_all, const void* hk, const void* hv, const void* 
 extern "C" int loom_dread_stage(const void* a, const void* b, const void* mo, void* dm, float* dd, const float* lse_in,
                                 float* lse_out, long long MQ, int HD, cudaStream_t st) {
   if (HD % 8 || HD > 128 || ((lse_in == nullptr) != (lse_out == nullptr))) return -1;
+#define WIDE_S(G_, NV_) do { const long long threads = MQ * G_; \
+    dread_stage_wide_kernel<G_, NV_><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>((const bf16*)a, (const bf16*)b, (const bf16*)mo, \
+                                                                                        (bf16*)dm, dd, lse_in, lse_out, MQ, HD); \
+    return (int)cudaGetLastError(); } while (0)
+  if (HD == 96) WIDE_S(8, 3); if (HD == 64) WIDE_S(8, 2); if (HD == 128) WIDE_S(8, 4); if (HD == 48) WIDE_S(4, 3);
+  if (HD == 32) WIDE_S(4, 2); if (HD == 24) WIDE_S(2, 3);
+#undef WIDE_S
   const int chunks = HD / 8;
   if (chunks <= 2) return launch_stage<2>(a, b, mo, dm, dd, lse_in, lse_out, MQ, HD, st);
   if (chunks <= 4) return launch_stage<4>(a, b, mo, dm, dd, lse_in, lse_out, MQ, HD, st);
