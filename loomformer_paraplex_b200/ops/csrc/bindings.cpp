@@ -135,6 +135,14 @@ void gemm_qkv_rope(torch::Tensor x, torch::Tensor w, c10::optional<torch::Tensor
   TORCH_CHECK(rc == 0, "loom_gemm_bf16 (QKV + RoPE) failed: ", rc);
 }
 
+void sector_fold(torch::Tensor src, torch::Tensor dst, int64_t M, int64_t QH, int64_t HD) {
+  const c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(src.is_contiguous() && dst.is_contiguous() && src.scalar_type() == torch::kBFloat16 && dst.scalar_type() == torch::kBFloat16 &&
+              src.numel() == M * QH * 3 * HD && dst.numel() == src.numel(), "sector_fold: packed bf16 [M, QH, 3, HD] -> [M, 3, QH, HD]");
+  int rc = loom_sector_fold(src.data_ptr(), dst.data_ptr(), (long long)M, (int)QH, (int)HD, cur_stream());
+  TORCH_CHECK(rc == 0, "loom_sector_fold failed: ", rc);
+}
+
 void status_gate(torch::Tensor status, torch::Tensor stats) {
   const c10::cuda::CUDAGuard guard(stats.device());
   TORCH_CHECK(status.is_cuda() && status.scalar_type() == torch::kInt32, "status word: int32 CUDA tensor");
@@ -588,6 +596,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "segmented-K batched bf16 GEMM (tcgen05 + TMA)");
   m.def("grad_norm", &grad_norm, "global gradient norm, clip coefficient and finite flag");
   m.def("gemm_qkv_rope", &gemm_qkv_rope, "[Q | K | V] projection whose epilogue applies RoPE and writes the attention operand and the caches");
+  m.def("sector_fold", &sector_fold, "[M, QH, 3, HD] -> [M, 3, QH, HD] copy, 16 bytes per thread");
   m.def("status_gate", &status_gate, "finite flag &= status word clear; count skipped updates");
   m.def("adamw_flat", &adamw_flat, "AdamW over the flat parameter buffer");
   m.def("atom_flat", &atom_flat, "ATOM over the flat parameter buffer");

@@ -109,6 +109,117 @@ __global__ void rope_bwd_kernel(const bf16* __restrict__ dq_attn, const bf16* __
   }
 }
 
+// ---- four pairs per thread (HD a multiple of 8): 8- and 16-byte accesses instead of 2- and 4-byte ones -------------
+__device__ __forceinline__ void ld4(const bf16* p, float (&f)[4]) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+__device__ __forceinline__ void st4(bf16* p, const float (&f)[4]) {
+  uint2 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+  h[0] = __floats2bfloat162_rn(f[0], f[1]);
+  h[1] = __floats2bfloat162_rn(f[2], f[3]);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+__device__ __forceinline__ void ldf4(const float* p, float (&f)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+
+__global__ void rope_store_v4_kernel(const bf16* __restrict__ qkv, const float* __restrict__ cs, const float* __restrict__ sn,
+                                     bf16* __restrict__ qkc, bf16* __restrict__ kcache, bf16* __restrict__ vcache,
+                                     int M, int Tc, int T, int s_off, int QH, int KVH, int HD) {
+  const int half = HD / 2, q4 = half / 4;
+  const int heads = QH + 2 * KVH;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)M * heads * q4) return;
+  const int j = (int)(idx % q4) * 4;
+  const int hh = (int)((idx / q4) % heads);
+  const int m = (int)(idx / ((long long)q4 * heads));
+  const int N = QH * HD, ld = N + 2 * KVH * HD;
+  const bf16* src = qkv + (long long)m * ld + hh * HD;
+  float x1[4], x2[4];
+  ld4(src + j, x1); ld4(src + j + half, x2);
+  const int b = m / Tc, t = m % Tc;
+  bf16* dst;
+  if (hh < QH + KVH) {
+    float c1[4], c2[4], s1[4], s2[4];
+    ldf4(cs + (long long)m * HD + j, c1); ldf4(cs + (long long)m * HD + j + half, c2);
+    ldf4(sn + (long long)m * HD + j, s1); ldf4(sn + (long long)m * HD + j + half, s2);
+    float y1[4], y2[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { y1[i] = x1[i] * c1[i] - x2[i] * s1[i]; y2[i] = x2[i] * c2[i] + x1[i] * s2[i]; }
+    dst = (hh < QH) ? qkc + (long long)m * 3 * N + hh * HD
+                    : kcache + (((long long)b * T + s_off + t) * KVH + (hh - QH)) * HD;
+    st4(dst + j, y1); st4(dst + j + half, y2);
+  } else {
+    dst = vcache + (((long long)b * T + s_off + t) * KVH + (hh - QH - KVH)) * HD;
+    st4(dst + j, x1); st4(dst + j + half, x2);
+  }
+}
+
+__global__ void rope_bwd_v4_kernel(const bf16* __restrict__ dq_attn, const bf16* __restrict__ dqkc,
+                                   const float* __restrict__ dkc, const float* __restrict__ dvc,
+                                   const float* __restrict__ cs, const float* __restrict__ sn, bf16* __restrict__ dqkv,
+                                   int M, int Tc, int T, int s_off, int QH, int KVH, int HD, int G) {
+  const int half = HD / 2, q4 = half / 4;
+  const int heads = QH + 2 * KVH;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)M * heads * q4) return;
+  const int j = (int)(idx % q4) * 4;
+  const int hh = (int)((idx / q4) % heads);
+  const int m = (int)(idx / ((long long)q4 * heads));
+  const int N = QH * HD, ld = N + 2 * KVH * HD;
+  const int b = m / Tc, t = m % Tc;
+  bf16* dst = dqkv + (long long)m * ld + hh * HD;
+  float g1[4], g2[4];
+  if (hh < QH) {
+    const long long a = ((long long)m * QH + hh) * HD, d = (long long)m * 3 * N + hh * HD;
+    float e1[4], e2[4];
+    ld4(dq_attn + a + j, g1); ld4(dq_attn + a + j + half, g2);
+    ld4(dqkc + d + j, e1); ld4(dqkc + d + j + half, e2);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { g1[i] += e1[i]; g2[i] += e2[i]; }
+  } else {
+    const int kh = (hh < QH + KVH) ? hh - QH : hh - QH - KVH;
+    const float* src = ((hh < QH + KVH) ? dkc : dvc) + (((long long)b * T + s_off + t) * KVH * G + kh * G) * HD;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { g1[i] = 0.f; g2[i] = 0.f; }
+    for (int gq = 0; gq < G; ++gq) {
+      float e1[4], e2[4];
+      ldf4(src + gq * HD + j, e1); ldf4(src + gq * HD + j + half, e2);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { g1[i] += e1[i]; g2[i] += e2[i]; }
+    }
+  }
+  if (hh < QH + KVH) {
+    float c1[4], c2[4], s1[4], s2[4];
+    ldf4(cs + (long long)m * HD + j, c1); ldf4(cs + (long long)m * HD + j + half, c2);
+    ldf4(sn + (long long)m * HD + j, s1); ldf4(sn + (long long)m * HD + j + half, s2);
+    float o1[4], o2[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { o1[i] = g1[i] * c1[i] + g2[i] * s2[i]; o2[i] = g2[i] * c2[i] - g1[i] * s1[i]; }
+    st4(dst + j, o1); st4(dst + j + half, o2);
+  } else {
+    st4(dst + j, g1); st4(dst + j + half, g2);
+  }
+}
+
+// [M, QH, 3, HD] -> [M, 3, QH, HD]: the three attention sectors of a head leave the batched data-gradient GEMM side by
+// side; the attention backward reads them sector-major.  16 bytes per thread on both sides.
+__global__ void sector_fold_kernel(const bf16* __restrict__ src, bf16* __restrict__ dst, long long M, int QH, int HD) {
+  const int c8n = HD / 8;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= M * QH * 3 * c8n) return;
+  const int c8 = (int)(idx % c8n);
+  const int s = (int)((idx / c8n) % 3);
+  const int g = (int)((idx / (3LL * c8n)) % QH);
+  const long long m = idx / (3LL * c8n * QH);
+  *reinterpret_cast<uint4*>(dst + ((m * 3 + s) * QH + g) * HD + c8 * 8) = *reinterpret_cast<const uint4*>(src + idx * 8);
+}
+
 // Backward of the RMS cap y = s a, s = min(1, cap / rms(a)):  da = dy where the row is not clipped, else
 // da = s (dy - a <a, dy> / (N (mean(a^2) + 1e-6))).  One warp per row.
 template <int NCH>
@@ -244,7 +355,7 @@ __global__ void __launch_bounds__(256) dread_fwd_wide_kernel(const float* __rest
   float mx = -INFINITY, den = 0.f, acc[DPL];
 #pragma unroll
   for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
-  constexpr int PF = 4;
+  constexpr int PF = NV <= 3 ? 8 : 4;         // slots whose loads are in flight together (one memory round trip each)
   for (int s0 = 0; s0 < n; s0 += PF) {
     uint2 rk[PF][NV], rv[PF][NV];
 #pragma unroll
@@ -671,15 +782,34 @@ __global__ void __launch_bounds__(256) add_ln_fwd_row_kernel(const bf16* __restr
 
 extern "C" int loom_rope_store(const void* qkv, const float* cs, const float* sn, void* qkc, void* kcache, void* vcache,
                                int M, int Tc, int T, int s_off, int QH, int KVH, int HD, cudaStream_t st) {
+  if (HD % 8 == 0) {
+    const long long n4 = (long long)M * (QH + 2 * KVH) * (HD / 8);
+    rope_store_v4_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>((const bf16*)qkv, cs, sn, (bf16*)qkc, (bf16*)kcache,
+                                                                        (bf16*)vcache, M, Tc, T, s_off, QH, KVH, HD);
+    return (int)cudaGetLastError();
+  }
   const long long n = (long long)M * (QH + 2 * KVH) * (HD / 2);
   rope_store_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const bf16*)qkv, cs, sn, (bf16*)qkc, (bf16*)kcache,
                                                                  (bf16*)vcache, M, Tc, T, s_off, QH, KVH, HD);
   return (int)cudaGetLastError();
 }
 
+extern "C" int loom_sector_fold(const void* src, void* dst, long long M, int QH, int HD, cudaStream_t st) {
+  if (HD % 8 || M < 1 || QH < 1 || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) return -1;
+  const long long n = M * QH * 3 * (HD / 8);
+  sector_fold_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const bf16*)src, (bf16*)dst, M, QH, HD);
+  return (int)cudaGetLastError();
+}
+
 extern "C" int loom_rope_bwd(const void* dq_attn, const void* dqkc, const float* dkc, const float* dvc, const float* cs,
                              const float* sn, void* dqkv, int M, int Tc, int T, int s_off, int QH, int KVH, int HD,
                              int G, cudaStream_t st) {
+  if (HD % 8 == 0) {
+    const long long n4 = (long long)M * (QH + 2 * KVH) * (HD / 8);
+    rope_bwd_v4_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>((const bf16*)dq_attn, (const bf16*)dqkc, dkc, dvc, cs, sn,
+                                                                      (bf16*)dqkv, M, Tc, T, s_off, QH, KVH, HD, G);
+    return (int)cudaGetLastError();
+  }
   const long long n = (long long)M * (QH + 2 * KVH) * (HD / 2);
   rope_bwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const bf16*)dq_attn, (const bf16*)dqkc, dkc, dvc, cs, sn,
                                                                (bf16*)dqkv, M, Tc, T, s_off, QH, KVH, HD, G);

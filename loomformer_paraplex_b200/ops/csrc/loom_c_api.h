@@ -114,6 +114,8 @@ int loom_ffn_core_bwd(const LoomFfnCore* a, cudaStream_t stream);
 // ---- bandwidth-bound kernels (elementwise.cu) ----
 int loom_rope_store(const void* qkv, const float* cs, const float* sn, void* qkc, void* kcache, void* vcache, int M,
                     int Tc, int T, int s_off, int QH, int KVH, int HD, cudaStream_t st);
+// [M, QH, 3, HD] -> [M, 3, QH, HD] (bf16, HD a multiple of 8)
+int loom_sector_fold(const void* src, void* dst, long long M, int QH, int HD, cudaStream_t st);
 int loom_rope_bwd(const void* dq_attn, const void* dqkc, const float* dkc, const float* dvc, const float* cs,
                   const float* sn, void* dqkv, int M, int Tc, int T, int s_off, int QH, int KVH, int HD, int G,
                   cudaStream_t st);

@@ -421,7 +421,10 @@ class CudaKernels(TorchKernels):
             # because their inputs are the sectors of qkc
             tmp = torch.empty(M, d.qh, 3 * hd, dtype=torch.bfloat16, device=dev)
             gemm([db3], [d.hpq], w3[:, :, 0:3 * hd], tmp, M=M, N=3 * hd, heads=d.qh, b_mn=True)
-            dqkc.copy_(tmp.view(M, d.qh, 3, hd).transpose(1, 2))
+            if dqkc.is_contiguous():
+                native.ext().sector_fold(tmp, dqkc, M, d.qh, hd)
+            else:
+                dqkc.copy_(tmp.view(M, d.qh, 3, hd).transpose(1, 2))
             native.count()
             for s_ in range(3):
                 self._wgrad(db3, qkc[:, s_], g3[:, :, s_ * hd:(s_ + 1) * hd], d.hpq, hd, d.qh)
