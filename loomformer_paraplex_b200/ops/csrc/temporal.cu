@@ -119,25 +119,43 @@ __global__ void __launch_bounds__(128) temporal_fwd_kernel(const bf16* __restric
 #pragma unroll
     for (int k = 0; k < 9; ++k) acc[k] = state_in[idx * 9 + k];
   }
-  for (int t = 0; t < Tc; ++t) {
-    const long long e = ((long long)b * Tc + t) * H + h;
-    float D[9], pre[9];
+  // The recurrence is one dependent chain per thread; the carriers it consumes do not depend on it.  Loading them inside
+  // the chain would pay a memory round trip per token, so the loads of UF tokens are issued together.
+  constexpr int UF = 4;
+  for (int t0 = 0; t0 < Tc; t0 += UF) {
+    bf16 rawd[UF][9];
+    uint8_t rs[UF];
 #pragma unroll
-    for (int k = 0; k < 9; ++k) D[k] = __bfloat162float(depth[k * plane + e]);
-    if (have && !reset[b * Tc + t]) {
-      mat3(D, acc, pre);
+    for (int u = 0; u < UF; ++u) {
+      const int tt = t0 + u < Tc ? t0 + u : Tc - 1;
+      const long long e = ((long long)b * Tc + tt) * H + h;
 #pragma unroll
-      for (int k = 0; k < 9; ++k) acc[k] = pre[k];
-    } else {
-#pragma unroll
-      for (int k = 0; k < 9; ++k) acc[k] = D[k];
+      for (int k = 0; k < 9; ++k) rawd[u][k] = depth[k * plane + e];
+      rs[u] = reset[b * Tc + tt];
     }
-    norm9(acc);
-    have = true;
-    if (ckpt && ((t + 1) % CKPT == 0)) {
-      float* c = ckpt + ((long long)(t / CKPT) * B * H + idx) * 9;
 #pragma unroll
-      for (int k = 0; k < 9; ++k) c[k] = acc[k];
+    for (int u = 0; u < UF; ++u) {
+      const int t = t0 + u;
+      if (t < Tc) {
+        float D[9], pre[9];
+#pragma unroll
+        for (int k = 0; k < 9; ++k) D[k] = __bfloat162float(rawd[u][k]);
+        if (have && !rs[u]) {
+          mat3(D, acc, pre);
+#pragma unroll
+          for (int k = 0; k < 9; ++k) acc[k] = pre[k];
+        } else {
+#pragma unroll
+          for (int k = 0; k < 9; ++k) acc[k] = D[k];
+        }
+        norm9(acc);
+        have = true;
+        if (ckpt && ((t + 1) % CKPT == 0)) {
+          float* c = ckpt + ((long long)(t / CKPT) * B * H + idx) * 9;
+#pragma unroll
+          for (int k = 0; k < 9; ++k) c[k] = acc[k];
+        }
+      }
     }
   }
   if (raw_out) {
@@ -174,65 +192,81 @@ __global__ void __launch_bounds__(128) temporal_bwd_kernel(const bf16* __restric
     for (int k = 0; k < 9; ++k) g[k] = gm[k];
   }
   bool alive = true;      // gradient still flows to earlier tokens
-  for (int t = Tc - 1; t >= 0; --t) {
-    const long long e = ((long long)b * Tc + t) * H + h;
-    if (!alive) {
+  constexpr int UB = 4;                 // tokens whose carriers are loaded together (see the forward kernel)
+  for (int t0 = Tc - 1; t0 >= 0; t0 -= UB) {
+    bf16 rawd[UB][9];
+    uint8_t rs[UB];
 #pragma unroll
-      for (int k = 0; k < 9; ++k) ddepth[k * plane + e] = __float2bfloat16(0.f);
-      continue;
+    for (int u = 0; u < UB; ++u) {
+      const int tt = t0 - u >= 0 ? t0 - u : 0;
+      const long long e = ((long long)b * Tc + tt) * H + h;
+#pragma unroll
+      for (int k = 0; k < 9; ++k) rawd[u][k] = depth[k * plane + e];
+      rs[u] = reset[b * Tc + tt];
     }
-    float D[9];
 #pragma unroll
-    for (int k = 0; k < 9; ++k) D[k] = __bfloat162float(depth[k * plane + e]);
-    const bool cont = !reset[b * Tc + t] && (t > 0 || state_in != nullptr);
-    float prev[9], pre[9];
-    if (cont) {
-      if (t == 0) {
+    for (int u = 0; u < UB; ++u) {
+      const int t = t0 - u;
+      if (t < 0) continue;
+      const long long e = ((long long)b * Tc + t) * H + h;
+      if (!alive) {
 #pragma unroll
-        for (int k = 0; k < 9; ++k) prev[k] = state_in[idx * 9 + k];
-      } else if (ckpt && (t % CKPT == 0)) {
-        const float* c = ckpt + ((long long)(t / CKPT - 1) * B * H + idx) * 9;
-#pragma unroll
-        for (int k = 0; k < 9; ++k) prev[k] = c[k];
-      } else {
-        float Di[9];
-        if (inv3(D, Di)) { mat3(Di, acc, prev); norm9(prev); }
-        else {
-#pragma unroll
-          for (int k = 0; k < 9; ++k) prev[k] = 0.f;
-        }
+        for (int k = 0; k < 9; ++k) ddepth[k * plane + e] = __float2bfloat16(0.f);
+        continue;
       }
-      mat3(D, prev, pre);
-    } else {
+      float D[9];
 #pragma unroll
-      for (int k = 0; k < 9; ++k) pre[k] = D[k];
-    }
-    float ss = 0.f;
+      for (int k = 0; k < 9; ++k) D[k] = __bfloat162float(rawd[u][k]);
+      const bool cont = !rs[u] && (t > 0 || state_in != nullptr);
+      float prev[9], pre[9];
+      if (cont) {
+        if (t == 0) {
 #pragma unroll
-    for (int k = 0; k < 9; ++k) ss += pre[k] * pre[k];
-    const float inv = rsqrtf(ss * (1.f / 9.f) + EPS);
-    float dot = 0.f, gp[9];
+          for (int k = 0; k < 9; ++k) prev[k] = state_in[idx * 9 + k];
+        } else if (ckpt && (t % CKPT == 0)) {
+          const float* c = ckpt + ((long long)(t / CKPT - 1) * B * H + idx) * 9;
 #pragma unroll
-    for (int k = 0; k < 9; ++k) dot += g[k] * pre[k] * inv;
-    dot *= (1.f / 9.f);
+          for (int k = 0; k < 9; ++k) prev[k] = c[k];
+        } else {
+          float Di[9];
+          if (inv3(D, Di)) { mat3(Di, acc, prev); norm9(prev); }
+          else {
 #pragma unroll
-    for (int k = 0; k < 9; ++k) gp[k] = (g[k] - pre[k] * inv * dot) * inv;
-    if (cont) {
-      // gD = gp prev^T ; g_prev = D^T gp
-#pragma unroll
-      for (int r = 0; r < 3; ++r)
-#pragma unroll
-        for (int c = 0; c < 3; ++c) {
-          const float gd = gp[r * 3] * prev[c * 3] + gp[r * 3 + 1] * prev[c * 3 + 1] + gp[r * 3 + 2] * prev[c * 3 + 2];
-          ddepth[(r * 3 + c) * plane + e] = __float2bfloat16(gd);
-          g[r * 3 + c] = D[r] * gp[c] + D[3 + r] * gp[3 + c] + D[6 + r] * gp[6 + c];
+            for (int k = 0; k < 9; ++k) prev[k] = 0.f;
+          }
         }
+        mat3(D, prev, pre);
+      } else {
 #pragma unroll
-      for (int k = 0; k < 9; ++k) acc[k] = prev[k];
-    } else {
+        for (int k = 0; k < 9; ++k) pre[k] = D[k];
+      }
+      float ss = 0.f;
 #pragma unroll
-      for (int k = 0; k < 9; ++k) { ddepth[k * plane + e] = __float2bfloat16(gp[k]); g[k] = 0.f; }
-      alive = false;
+      for (int k = 0; k < 9; ++k) ss += pre[k] * pre[k];
+      const float inv = rsqrtf(ss * (1.f / 9.f) + EPS);
+      float dot = 0.f, gp[9];
+#pragma unroll
+      for (int k = 0; k < 9; ++k) dot += g[k] * pre[k] * inv;
+      dot *= (1.f / 9.f);
+#pragma unroll
+      for (int k = 0; k < 9; ++k) gp[k] = (g[k] - pre[k] * inv * dot) * inv;
+      if (cont) {
+        // gD = gp prev^T ; g_prev = D^T gp
+#pragma unroll
+        for (int r = 0; r < 3; ++r)
+#pragma unroll
+          for (int c = 0; c < 3; ++c) {
+            const float gd = gp[r * 3] * prev[c * 3] + gp[r * 3 + 1] * prev[c * 3 + 1] + gp[r * 3 + 2] * prev[c * 3 + 2];
+            ddepth[(r * 3 + c) * plane + e] = __float2bfloat16(gd);
+            g[r * 3 + c] = D[r] * gp[c] + D[3 + r] * gp[3 + c] + D[6 + r] * gp[6 + c];
+          }
+#pragma unroll
+        for (int k = 0; k < 9; ++k) acc[k] = prev[k];
+      } else {
+#pragma unroll
+        for (int k = 0; k < 9; ++k) { ddepth[k * plane + e] = __float2bfloat16(gp[k]); g[k] = 0.f; }
+        alive = false;
+      }
     }
   }
   if (dstate_in) {
