@@ -319,7 +319,10 @@ __global__ void __launch_bounds__(256, 2) dread_slot_bwd_wide_kernel(
         *reinterpret_cast<float4*>(sk + row * HD + l * DPL + 4 * v) = make_float4(kf[4 * v], kf[4 * v + 1], kf[4 * v + 2], kf[4 * v + 3]);
       // the loop over reading sublayers is one dependent chain of load -> reduce -> exp per sublayer: the loads of PF
       // sublayers are issued together
-      constexpr int PF = 2;
+#ifndef LOOM_SLOT_PF
+#define LOOM_SLOT_PF 3
+#endif
+      constexpr int PF = LOOM_SLOT_PF;
       for (int j0 = 0; j0 < nsub; j0 += PF) {
         uint2 raw[PF][NV];
         float lse_v[PF], dd_v[PF];
