@@ -321,19 +321,31 @@ class DecodeEngine:
         padded = dk is not d
         vec = (lambda q: self.wk(q)) if padded else (lambda q: q.data)
         c_planes, p_in = None, None
+        fork = os.environ.get("LOOM_DECODE_FORK", "1") != "0"     # second stream for the branch that needs only the history
+        if fork:
+            if getattr(self, "_side", None) is None:
+                self._side = torch.cuda.Stream()
+            side, main = self._side, torch.cuda.current_stream()
         for bi, blk in enumerate(m.blocks):
             last = bi == d.layers - 1
             sub = 2 * bi
             ffn = blk.ffn
             qkv = torch.empty(B, d.n + 2 * d.kv_dim, **bf)
             multi([([h], self.w(blk.attn.qkv_weight), None, qkv), project_seg(h, sub)])
+            if fork:        # the first depth read needs only the history: it runs beside RoPE and attention
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    mm_a, _ = K.dread_fwd(d, cst["query"][sub], hk, hv, sub + 1)
             # RoPE of Q and K at the device-side position, rotated Q into the attention operand, K / V appended
             ext.decode_rope_store(qkv, self._rope_cos, self._rope_sin, pos, qkc[:, 0].view(B, d.n), self.kc[bi],
                                   self.vc[bi], d.qh, d.kvh, d.hd)
             ext.decode_attn(qkc[:, 0], self.kc[bi], self.vc[bi], pos, qkc[:, 2], qkc[:, 1], self._attn_ws, B, S,
                             d.qh, d.kvh, d.hd, self._ns, self._status)
             native.count(2)
-            mm_a, _ = K.dread_fwd(d, cst["query"][sub], hk, hv, sub + 1)
+            if fork:
+                main.wait_stream(side)
+            else:
+                mm_a, _ = K.dread_fwd(d, cst["query"][sub], hk, hv, sub + 1)
             attn_out, skip = torch.empty(B, d.n, **bf), torch.empty(B, d.n, **bf)
             multi([([qkc[:, 2].reshape(B, d.n)], self.w(blk.attn.o.weight), None, attn_out),
                    ([mm_a.view(B, d.n)], w_o(sub), None, skip)])
