@@ -262,6 +262,7 @@ struct TcParams {
   bf16* out_c; bf16* out_k;
   float* ws; int* tickets;
   int S, QH, KVH, HD, NS;
+  int cluster;                                 // the NS slices of a (sequence, KV head) are one thread-block cluster
   float scale;
   long long out_ld;
   int* status;
@@ -311,7 +312,9 @@ __global__ void __launch_bounds__(TC_THREADS) decode_attn_tc_kernel(const __grid
   if (hi > n) hi = (int)n;
   const int cnt = hi > lo ? hi - lo : 0;
   const int per = 2 * G + 2 * G * HD;
-  float* wsb = p.ws + ((long long)blockIdx.x * NS + z) * per;
+  // partial state of this slice: in the workspace, or (cluster launch) in this CTA's shared memory, where the other
+  // CTAs of the cluster read it; the K tile it overlays is dead once the last MMA batch has completed
+  float* wsb = p.cluster ? reinterpret_cast<float*>(sK) : p.ws + ((long long)blockIdx.x * NS + z) * per;
   bool ok = true;
 
   if (cnt > 0) {
@@ -436,7 +439,50 @@ __global__ void __launch_bounds__(TC_THREADS) decode_attn_tc_kernel(const __grid
     for (int i = tid; i < 2 * G * HD; i += TC_THREADS) wsb[2 * G + i] = 0.f;       // an empty slice leaves zeros
   }
 
-  if (NS > 1) {
+  if (NS > 1 && p.cluster) {
+    // merge through distributed shared memory: no global partial states, no fence, no ticket.  Every CTA gathers the
+    // softmax statistics of all slices, then sums and stores its share of the (head, dim) outputs.
+    if (tid < G) { wsb[tid] = cnt > 0 ? sm_m[tid] : -INFINITY; wsb[G + tid] = cnt > 0 ? sm_l[tid] : 0.f; }
+    __syncthreads();
+    cluster_arrive();
+    cluster_wait();
+    const uint32_t local = smem_u32(wsb);
+    const int crank = (int)cluster_ctarank();
+    for (int i = tid; i < G * NS; i += TC_THREADS) {
+      const int g = i / NS, zz = i - g * NS;
+      const uint32_t a = mapa_shared(local, zz);
+      f_m[i] = ld_shared_cluster_f32(a + g * 4);
+      f_l[i] = ld_shared_cluster_f32(a + (G + g) * 4);
+    }
+    __syncthreads();
+    if (tid < G) {
+      float M = -INFINITY, l = 0.f;
+      for (int zz = 0; zz < NS; ++zz) M = fmaxf(M, f_m[tid * NS + zz]);
+      for (int zz = 0; zz < NS; ++zz) {
+        const float f = __expf(f_m[tid * NS + zz] - M);      // empty slice: exp(-inf) = 0
+        l += f_l[tid * NS + zz] * f;
+        f_m[tid * NS + zz] = f;
+      }
+      sm_l[tid] = 1.f / l;
+    }
+    __syncthreads();
+    for (int pidx = crank + NS * tid; pidx < G * HD; pidx += NS * TC_THREADS) {
+      const int g = pidx / HD, dd = pidx - g * HD;
+      float v = 0.f, k = 0.f;
+      for (int zz = 0; zz < NS; ++zz) {
+        const uint32_t a = mapa_shared(local, zz);
+        const float f = f_m[g * NS + zz];
+        v = fmaf(ld_shared_cluster_f32(a + (2 * G + g * HD + dd) * 4), f, v);
+        k = fmaf(ld_shared_cluster_f32(a + (2 * G + G * HD + g * HD + dd) * 4), f, k);
+      }
+      const float inv = sm_l[g];
+      const long long o = (long long)b * p.out_ld + (long long)(kvh * G + g) * HD + dd;
+      p.out_c[o] = __float2bfloat16(v * inv);
+      p.out_k[o] = __float2bfloat16(k * inv);
+    }
+    cluster_arrive();                          // nobody leaves while its shared memory may still be read
+    cluster_wait();
+  } else if (NS > 1) {
     if (tid < G) { wsb[tid] = cnt > 0 ? sm_m[tid] : -INFINITY; wsb[G + tid] = cnt > 0 ? sm_l[tid] : 0.f; }
     __threadfence();
     __syncthreads();
@@ -495,6 +541,26 @@ extern "C" int loom_decode_attn(const void* q, const void* kc, const void* vc, c
         cudaError_t e = cudaFuncSetAttribute(decode_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shm);
         if (e != cudaSuccess) return (int)e;
         configured = true;
+      }
+      // up to eight slices: one cluster per (sequence, KV head), merged through distributed shared memory
+      // (LOOM_DECODE_ATTN_CLUSTER=0 keeps the workspace + ticket merge)
+      static int want_cluster = -1;
+      if (want_cluster < 0) { const char* e = getenv("LOOM_DECODE_ATTN_CLUSTER"); want_cluster = (e != nullptr && e[0] == '0') ? 0 : 1; }
+      static int sms = 0;
+      if (sms == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+      // (only while all CTAs fit the GPU at once: with more, co-scheduling whole clusters costs more than the merge saves:
+      // 1.13 against 1.03 ms per step at 64 sequences, 0.492 against 0.512 ms at one)
+      if (want_cluster && NS > 1 && NS <= 8 && B * KVH * NS <= sms) {
+        p.cluster = 1;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid; cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = shm; cfg.stream = st;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = NS; attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = loom::pdl_enabled() ? 2 : 1;
+        return (int)cudaLaunchKernelEx(&cfg, decode_attn_tc_kernel, p);
       }
       return (int)loom::launch_pdl(decode_attn_tc_kernel, grid, dim3(TC_THREADS), shm, st, p);
     }

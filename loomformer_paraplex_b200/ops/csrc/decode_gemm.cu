@@ -64,12 +64,6 @@ struct Params {
   int* status;
 };
 
-__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
-  return v;
-}
-
 template <int MB, int KS>
 __global__ void __launch_bounds__(THREADS, 1) decode_gemm_kernel(const __grid_constant__ Params p) {
   constexpr int A_BYTES = WT * BK * 2;
@@ -236,7 +230,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_gemm_kernel(const __grid_co
         for (int m = rank; m < p.M; m += KS) {
           float v = b;
 #pragma unroll
-          for (int r = 0; r < KS; ++r) v += ld_cluster_f32(peer[r] + uint32_t(m) * WT * 4);
+          for (int r = 0; r < KS; ++r) v += ld_shared_cluster_f32(peer[r] + uint32_t(m) * WT * 4);
           if (sg.out_fp32) reinterpret_cast<float*>(sg.y)[(long long)m * sg.ldy + n] = v;
           else reinterpret_cast<bf16*>(sg.y)[(long long)m * sg.ldy + n] = __float2bfloat16(v);
         }
