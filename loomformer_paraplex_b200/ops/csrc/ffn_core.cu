@@ -228,6 +228,7 @@ __global__ void __launch_bounds__(256) ffn_core_fwd_kernel(
     const float* __restrict__ seed, const uint8_t* __restrict__ seed_valid, const float* __restrict__ gate_w,
     __nv_bfloat16* __restrict__ o_out, __nv_bfloat16* __restrict__ c_out, __nv_bfloat16* __restrict__ p_out,
     float* __restrict__ trace_out, float* __restrict__ beta_sq_sum) {
+  loom::pdl_wait();                           // returns at once unless launched programmatically dependent (decode-sized problems)
   if (S_in.M <= 256) loom::pdl_trigger();     // decode-sized problem: a dependent launched programmatically may start its prologue now
   CoreScalars S = S_in;
   S.alpha_gate = S.alpha_ptr ? *S.alpha_ptr : 0.f;
@@ -254,6 +255,7 @@ __global__ void __launch_bounds__(256) ffn_core_fwd_tiled_kernel(
     const float* __restrict__ seed, const uint8_t* __restrict__ seed_valid, const float* __restrict__ gate_w,
     __nv_bfloat16* __restrict__ o_out, __nv_bfloat16* __restrict__ c_out, __nv_bfloat16* __restrict__ p_out,
     float* __restrict__ trace_out, float* __restrict__ beta_sq_sum) {
+  loom::pdl_wait();                           // returns at once unless launched programmatically dependent (decode-sized problems)
   if (S_in.M <= 256) loom::pdl_trigger();     // decode-sized problem: a dependent launched programmatically may start its prologue now
   CoreScalars S = S_in;
   S.alpha_gate = S.alpha_ptr ? *S.alpha_ptr : 0.f;
@@ -660,7 +662,13 @@ extern "C" int loom_ffn_core_fwd(const LoomFfnCore* a, cudaStream_t stream) {
   if (tiled) { LOOM_FWD_K(ffn_core_fwd_tiled_kernel<AX>, grid_t, 2 * FWD_SLOTS * 256 * 4); }                     \
   else { LOOM_FWD_K(ffn_core_fwd_kernel<AX>, (unsigned)((n + 255) / 256), 0); }
 #define LOOM_FWD_K(KERNEL, GRID, SHM)                                                                             \
-  KERNEL<<<GRID, 256, SHM, stream>>>(                                       \
+  if (S.M <= 16)                                                                                                  \
+    loom::launch_pdl(KERNEL, dim3(GRID), dim3(256), (size_t)(SHM), stream,                                        \
+      S, (const __nv_bfloat16*)a->x_real, (const __nv_bfloat16*)a->p_in, a->b_real, (const __nv_bfloat16*)a->gate_lin, \
+      (const __nv_bfloat16*)a->beta_lin, a->b_imag, a->w_trace, a->trace_in, a->reset, (const __nv_bfloat16*)a->c_prev, \
+      a->seed, a->seed_valid, a->gate_w, (__nv_bfloat16*)a->o_out, (__nv_bfloat16*)a->c_out, (__nv_bfloat16*)a->p_out,  \
+      a->trace_out, a->beta_sq_sum);                                                                              \
+  else KERNEL<<<GRID, 256, SHM, stream>>>(                                       \
       S, (const __nv_bfloat16*)a->x_real, (const __nv_bfloat16*)a->p_in, a->b_real, (const __nv_bfloat16*)a->gate_lin, \
       (const __nv_bfloat16*)a->beta_lin, a->b_imag, a->w_trace, a->trace_in, a->reset, (const __nv_bfloat16*)a->c_prev, \
       a->seed, a->seed_valid, a->gate_w, (__nv_bfloat16*)a->o_out, (__nv_bfloat16*)a->c_out, (__nv_bfloat16*)a->p_out,  \
