@@ -3,7 +3,9 @@
 ``python -m loomformer_paraplex_b200.serve.bench_decode --batch 64 --prompt 512 --new 256`` prints one JSON line with
 prefill and decode tokens/s (device-timed).  ``--impl reference`` times the reference implementation's own
 ``Model.step`` loop (from ``baseline/_ref``) on the same shapes.  With ``--replicas N`` (or under torchrun) every rank
-serves its own batch -- data-parallel serving -- and the line reports the sum over ranks, timed as the max over ranks."""
+serves its own batch -- data-parallel serving -- and the line reports the sum over ranks, timed as the max over ranks.
+``--histogram`` instead prints, per kernel, launches and device time of one decode step run eagerly under the PyTorch
+profiler (shares only: the step itself is timed by the plain run, under graph replay)."""
 from __future__ import annotations
 
 import argparse
@@ -49,6 +51,37 @@ def run_ours(a, dev):
     return e0.elapsed_time(e1), e1.elapsed_time(e2)
 
 
+def histogram(a, dev, top: int = 30) -> None:
+    """Kernel histogram of one eager decode step at position ``a.prompt`` (three steps, averaged)."""
+    import collections
+    from torch.profiler import ProfilerActivity, profile
+    from ..config import Config
+    from ..models.loomformer import Model
+    from .decode import DecodeEngine
+    cfg = Config(**model_kw())
+    torch.manual_seed(1)
+    model = Model(cfg).to(dev).eval()
+    eng = DecodeEngine(model, batch=a.batch, max_len=a.prompt + a.new + 1, use_graph=False)
+    prompt = torch.randint(0, cfg.vocab, (a.batch, a.prompt), device=dev)
+    eng.generate(prompt, 4)
+    tok = eng.next_tok.clone()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        for _ in range(3):
+            eng.step(tok)
+        torch.cuda.synchronize()
+    cnt, tim = collections.Counter(), collections.Counter()
+    for e in prof.events():
+        if e.device_type == torch.autograd.DeviceType.CUDA:
+            name = e.name.replace("(anonymous namespace)::", "").replace("void ", "")[:64]
+            cnt[name] += 1
+            tim[name] += e.device_time
+    print(f"batch {a.batch}, position {a.prompt}: {sum(cnt.values()) / 3:.0f} launches per step, "
+          f"{sum(tim.values()) / 3:.0f} us of kernel time per step (eager; the replayed graph overlaps launches)")
+    for k, v in tim.most_common(top):
+        print(f"  {v / 3:8.1f} us {cnt[k] / 3:6.1f} x  {k}")
+
+
 def run_reference(a, dev):
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(ref):
@@ -89,11 +122,15 @@ def main(argv=None) -> None:
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--new", type=int, default=256)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--histogram", action="store_true", help="kernel histogram of one eager decode step instead of timing")
     a = ap.parse_args(argv)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
+    if a.histogram:
+        histogram(a, dev)
+        return
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
