@@ -204,8 +204,123 @@ __global__ void __launch_bounds__(256) skinny_multi_kernel(const __grid_constant
   }
 }
 
+// Variant for launches whose segments all have few columns and a long reduction (the down projection: 768 x 3072 would
+// keep 96 blocks busy): `wpc` warps share a column, each with a slice of K, and their partial sums meet in shared
+// memory.  Kept apart from the kernel above, whose launches it would slow down (more registers, two barriers per pass).
 template <int MT>
-int launch_skinny_multi(const LoomSkinnyArgs& a, int grid, int kmax, cudaStream_t st) {
+__global__ void __launch_bounds__(256) skinny_multi_split_kernel(const __grid_constant__ LoomSkinnyArgs a) {
+  extern __shared__ uint4 sx[];                       // [MT][K / 8] of this block's segment
+  __shared__ float red[8][MT];
+  int si = 0;
+  for (int i = 1; i < a.nseg; ++i)
+    if ((int)blockIdx.x >= a.seg[i].block0) si = i;
+  const LoomSkinnySeg& sg = a.seg[si];
+  const int nb = (si + 1 < a.nseg ? a.seg[si + 1].block0 : (int)gridDim.x) - sg.block0;
+  const int lb = blockIdx.x - sg.block0;
+  const int K8 = sg.K >> 3, M = a.M;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const bf16* w = reinterpret_cast<const bf16*>(sg.w);
+  const int wpc = sg.wpc, cpb = warps / wpc;             // columns per block pass
+  const int wcol = warp / wpc, sub = warp - wcol * wpc;
+  const int per = (K8 + wpc - 1) / wpc;
+  const int c_lo = sub * per, c_hi = c_lo + per < K8 ? c_lo + per : K8;
+  loom::pdl_trigger();
+  constexpr int PRE = 4;
+  uint4 pre[PRE];
+  const bool early = a.weights_static != 0;
+  if (!early) loom::pdl_wait();
+  {
+    const int n = lb * cpb + wcol;
+    if (n < sg.N) {
+      const uint4* wr = reinterpret_cast<const uint4*>(w + (long long)n * sg.ldw);
+#pragma unroll
+      for (int j = 0; j < PRE; ++j) pre[j] = c_lo + lane + 32 * j < c_hi ? wr[c_lo + lane + 32 * j] : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  if (early) loom::pdl_wait();
+  int k0 = 0;
+  for (int pi = 0; pi < sg.npiece; ++pi) {
+    const bf16* px = reinterpret_cast<const bf16*>(sg.piece[pi].x);
+    const long long ld = sg.piece[pi].ld;
+    const int L8 = sg.piece[pi].len >> 3;
+    for (int i = threadIdx.x; i < MT * L8; i += blockDim.x) {
+      const int m = i / L8, c = i - m * L8;
+      sx[m * K8 + k0 + c] = m < M ? *reinterpret_cast<const uint4*>(px + (long long)m * ld + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    k0 += L8;
+  }
+  __syncthreads();
+  bool first = true;
+  for (int nbase = lb * cpb; nbase < sg.N; nbase += nb * cpb) {          // the same trip count for every warp of the block
+    const int n = nbase + wcol;
+    const bool valid = n < sg.N;
+    float acc[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m] = 0.f;
+    if (valid) {
+      const uint4* wr = reinterpret_cast<const uint4*>(w + (long long)n * sg.ldw);
+      int c = c_lo + lane;
+      if (first) {
+#pragma unroll
+        for (int j = 0; j < PRE; ++j) {
+          if (c_lo + lane + 32 * j < c_hi) {
+            float wf[8];
+            unpack8(pre[j], wf);
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+              float xf[8];
+              unpack8(sx[m * K8 + c_lo + lane + 32 * j], xf);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) acc[m] = fmaf(wf[i], xf[i], acc[m]);
+            }
+          }
+        }
+        c = c_lo + lane + 32 * PRE;
+      }
+#pragma unroll 4
+      for (; c < c_hi; c += 32) {
+        float wf[8];
+        unpack8(wr[c], wf);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          float xf[8];
+          unpack8(sx[m * K8 + c], xf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[m] = fmaf(wf[i], xf[i], acc[m]);
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
+      }
+    }
+    first = false;
+    if (lane == 0) {
+#pragma unroll
+      for (int m = 0; m < MT; ++m) red[warp][m] = acc[m];
+    }
+    __syncthreads();
+    if (valid && sub == 0 && lane == 0) {
+      for (int s2 = 1; s2 < wpc; ++s2) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[m] += red[warp + s2][m];
+      }
+      const float b = sg.bias ? sg.bias[n] : 0.f;
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        if (m < M) {
+          if (sg.out_fp32) reinterpret_cast<float*>(sg.y)[(long long)m * sg.ldy + n] = acc[m] + b;
+          else reinterpret_cast<bf16*>(sg.y)[(long long)m * sg.ldy + n] = __float2bfloat16(acc[m] + b);
+        }
+      }
+    }
+    __syncthreads();
+  }
+}
+
+template <int MT>
+int launch_skinny_multi(const LoomSkinnyArgs& a, int grid, int kmax, bool split, cudaStream_t st) {
   const size_t shm = (size_t)MT * kmax * sizeof(bf16);
   if (shm > 200 * 1024) return -2;
   if (shm > 48 * 1024) {
@@ -215,6 +330,17 @@ int launch_skinny_multi(const LoomSkinnyArgs& a, int grid, int kmax, cudaStream_
       if (e != cudaSuccess) return (int)e;
       configured = shm;
     }
+  }
+  if (split) {
+    if (shm > 48 * 1024) {
+      static size_t configured2 = 0;
+      if (shm > configured2) {
+        cudaError_t e = cudaFuncSetAttribute(skinny_multi_split_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shm);
+        if (e != cudaSuccess) return (int)e;
+        configured2 = shm;
+      }
+    }
+    return (int)loom::launch_pdl(skinny_multi_split_kernel<MT>, dim3(grid), dim3(256), shm, st, a);
   }
   return (int)loom::launch_pdl(skinny_multi_kernel<MT>, dim3(grid), dim3(256), shm, st, a);
 }
@@ -344,6 +470,7 @@ extern "C" int loom_skinny_multi(LoomSkinnyArgs* a, cudaStream_t st) {
   static int sms = 0;
   if (sms == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
   int kmax = 0, want = 0;
+  bool split = true;                    // every segment has few columns and a long reduction
   for (int i = 0; i < a->nseg; ++i) {
     LoomSkinnySeg& sg = a->seg[i];
     if (sg.N < 1 || sg.K < 8 || (sg.K & 7) || (sg.ldw & 7) || sg.npiece < 1 || sg.npiece > LOOM_SKINNY_MAX_PIECE) return -1;
@@ -356,23 +483,32 @@ extern "C" int loom_skinny_multi(LoomSkinnyArgs* a, cudaStream_t st) {
     }
     if (k != sg.K) return -1;
     if (sg.K > kmax) kmax = sg.K;
+    sg.wpc = 1;
+    while (sg.wpc < 8 && (sg.N * sg.wpc + 7) / 8 < 2 * sms && (sg.K >> 3) / (sg.wpc * 2) >= 96) sg.wpc *= 2;
+    if (sg.wpc == 1) split = false;
     want += (sg.N + 7) / 8;
+  }
+  if (!split) {
+    for (int i = 0; i < a->nseg; ++i) a->seg[i].wpc = 1;
+  } else {
+    want = 0;
+    for (int i = 0; i < a->nseg; ++i) want += (a->seg[i].N * a->seg[i].wpc + 7) / 8;
   }
   // a block per eight output columns, thinned evenly when that is more than eight blocks per SM
   const int limit = 8 * sms;
   int grid = 0;
   for (int i = 0; i < a->nseg; ++i) {
-    int nb = (a->seg[i].N + 7) / 8;
+    int nb = (a->seg[i].N * a->seg[i].wpc + 7) / 8;
     if (want > limit) { nb = (int)((long long)nb * limit / want); if (nb < 1) nb = 1; }
     a->seg[i].block0 = grid;
     grid += nb;
   }
   const int M = a->M;
-  if (M == 1) return launch_skinny_multi<1>(*a, grid, kmax, st);
-  if (M == 2) return launch_skinny_multi<2>(*a, grid, kmax, st);
-  if (M <= 4) return launch_skinny_multi<4>(*a, grid, kmax, st);
-  if (M <= 8) return launch_skinny_multi<8>(*a, grid, kmax, st);
-  return launch_skinny_multi<16>(*a, grid, kmax, st);
+  if (M == 1) return launch_skinny_multi<1>(*a, grid, kmax, split, st);
+  if (M == 2) return launch_skinny_multi<2>(*a, grid, kmax, split, st);
+  if (M <= 4) return launch_skinny_multi<4>(*a, grid, kmax, split, st);
+  if (M <= 8) return launch_skinny_multi<8>(*a, grid, kmax, split, st);
+  return launch_skinny_multi<16>(*a, grid, kmax, split, st);
 }
 
 extern "C" int loom_decode_step_flags(const long long* pos, const long long* tok, const void* pending, const void* have_carry,

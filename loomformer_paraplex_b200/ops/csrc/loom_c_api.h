@@ -208,7 +208,8 @@ typedef struct {
   LoomSkinnyPiece piece[LOOM_SKINNY_MAX_PIECE];
   const void* w; const float* bias; void* y;
   long long ldw, ldy;
-  int npiece, N, K, out_fp32, block0, pad_;
+  int npiece, N, K, out_fp32, block0;
+  int wpc;                            // warps that share one output column (K split inside a block); filled in by the call
 } LoomSkinnySeg;
 // weights_static: no kernel earlier in the stream writes the weights or biases, so they may be fetched before the
 // previous kernel has finished

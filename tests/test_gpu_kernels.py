@@ -476,6 +476,14 @@ def test_multi_segment_small_batch_linear(static):
         _close(y4, x4.float() @ w4.float().t(), 2e-2, "long-K seg")
         for o in outs:
             _close(o, x1.float() @ w3.float().t(), 2e-2, "small seg")
+        if M <= 16:
+            # a launch whose segments all have few columns and a long reduction: several warps share a column
+            w5, b5 = bf(768, 3072, scale=0.03), torch.randn(768, device="cuda")
+            y5 = torch.empty(M, 768, device="cuda", dtype=torch.bfloat16)
+            y6 = torch.empty(M, 300, device="cuda")
+            ck.linear_multi([([x4], w5, b5, y5), ([x4[:, :1536], x4[:, 1536:]], w4, None, y6)], static_weights=static)
+            _close(y5, x4.float() @ w5.float().t() + b5, 2e-2, "split-K seg")
+            _close(y6, x4.float() @ w4.float().t(), 3e-3, "split-K seg, two pieces, fp32")
     assert not ck.fallbacks, ck.fallbacks
 
 
