@@ -94,3 +94,26 @@ def test_decode_requests_beyond_the_cache_are_refused_on_the_host():
         eng.step(out[:, -1])                     # position 8 does not exist
     with pytest.raises(ValueError):
         eng.prefill(torch.randint(0, 61, (1, 9)))
+
+
+def test_boundary_key_store_is_sized_by_what_can_fire():
+    """Without a carry token only window boundaries append keys (one per window); with one, any token may.  A carry
+    token given to the model after the engine was built grows the store at the next reset, and the engine then follows
+    the module's own step through token-triggered boundaries."""
+    m = _model()
+    eng = DecodeEngine(m, batch=2, use_graph=False)
+    assert eng.ca_cap == eng.S // 6 + 1 and eng.ca_k.shape[1] == eng.ca_cap
+    x = torch.randint(1, 61, (2, 30))
+    x[0, 4] = 0; x[:, 9] = 0; x[1, 10] = 0                     # token 0 becomes the carry token below
+    m.carry_token_id = 0
+    try:
+        eng.reset()
+        assert eng.ca_cap == eng.S and eng.ca_k.shape[1] == eng.S and eng.ca_valid.shape[1] == eng.S
+        st = None
+        for t in range(30):
+            ref, st = m.step(x[:, t], t, st)
+            got = eng.step(x[:, t])
+            assert torch.allclose(ref, got, atol=3e-5, rtol=1e-4), (t, float((ref - got).abs().max()))
+        assert int(eng.ca_len) >= 30 // 6 + 2                   # window fires plus the token-triggered ones
+    finally:
+        m.carry_token_id = None
