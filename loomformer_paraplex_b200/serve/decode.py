@@ -391,29 +391,47 @@ class DecodeEngine:
             if tria_here:
                 c_planes = core["c"]
                 p_in = None if last else core["p_out"]
+            a_t = None
+            if last and fork:
+                # the temporal endpoint and the boundary key need only the last layer's carriers: they (and the trace
+                # hand-over) run beside the last down projection and its add + LayerNorm
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    self.trace.copy_(self._unpad(self._trace_new, 2))
+                    if use_tria:
+                        a_t = self._boundary_key(c_planes)
             f = torch.empty(B, d.n, **bf)
             multi([([core["o"]], self.wk(ffn.w2.weight), ffn.w2.bias.data, f)])
             h = K.add_ln_fwd(skip2, f, blk.ln_ffn.weight.data, blk.ln_ffn.bias.data, cap)[0]
-        self.trace.copy_(self._unpad(self._trace_new, 2))
-        self._finish_fused(h, c_planes if use_tria else None)
+        if fork:
+            main.wait_stream(side)
+        else:
+            self.trace.copy_(self._unpad(self._trace_new, 2))
+            if use_tria:
+                a_t = self._boundary_key(c_planes)
+        self._finish_fused(h, a_t)
 
-    def _finish_fused(self, h, c_planes) -> None:
-        """Temporal endpoint, boundary-key append, final cross attention, head: the training plan's kernels at one
-        token per sequence (``temporal_fwd`` at a chunk of one token, the slot pool, the masked cross attention)."""
+    def _boundary_key(self, c_planes) -> torch.Tensor:
+        """Temporal endpoint of this token's carriers (the training plan's ``temporal_fwd`` at a chunk of one token), new
+        carried state, and the pooled boundary-key vector ``[B, N]`` (slot pool, reader projection, up projection)."""
+        m, d, K, dk = self.m, self.d, self._K, self._dk
+        B, cst = self.B, self._const
+        state = self._pad(self.carry.view(B, d.hidden, 9), 1)
+        doc, _ = K.temporal_fwd(c_planes, B, 1, dk.hidden, self._reset.view(B, 1), state, self._fire, float(m.d_polarm_beta))
+        doc = self._unpad(doc, 1)                                              # [B,H,9] fp32
+        self.carry.copy_(doc.reshape(B, d.hidden, 3, 3))
+        pooled = K.slot_pool_fwd(self.carry.view(B, 1, d.hidden, 9), cst["score_w"])   # [B,1,9]
+        z = torch.addmm(cst["proj_b"], pooled.view(B, 9), cst["proj_wT"])
+        return torch.addmm(cst["up_b"], z, cst["up_wT"]).to(self.dt)
+
+    def _finish_fused(self, h, a_t) -> None:
+        """Boundary-key append, final cross attention (the training plan's masked cross-attention kernel), head."""
         m, d, K, dk = self.m, self.d, self._K, self._dk
         B, cst = self.B, self._const
         from ..ops import native
         ext = native.ext()
         bf = dict(dtype=self.dt, device=self.dev)
-        if c_planes is not None:
-            state = self._pad(self.carry.view(B, d.hidden, 9), 1)
-            doc, _ = K.temporal_fwd(c_planes, B, 1, dk.hidden, self._reset.view(B, 1), state, self._fire,
-                                    float(m.d_polarm_beta))
-            doc = self._unpad(doc, 1)                                              # [B,H,9] fp32
-            self.carry.copy_(doc.reshape(B, d.hidden, 3, 3))
-            pooled = K.slot_pool_fwd(self.carry.view(B, 1, d.hidden, 9), cst["score_w"])   # [B,1,9]
-            z = torch.addmm(cst["proj_b"], pooled.view(B, 9), cst["proj_wT"])
-            a_t = torch.addmm(cst["up_b"], z, cst["up_wT"]).to(self.dt)             # [B,N]
+        if a_t is not None:
             fca = m.tria_final_ca
             newk, newv, qv = (torch.empty(B, d.n, **bf) for _ in range(3))
             K.linear_multi([([a_t], self.w(fca.w_qk.weight), None, newk), ([a_t], self.w(fca.w_v.weight), None, newv),
